@@ -1,0 +1,261 @@
+/* libyuuka_cuda: B200 (sm_100a) backend for yuuka's speculative-decoding
+ * verify path. Plain C ABI for cgo; no C++ types, no PyTorch, no CPU fallback.
+ *
+ * Conventions follow the reference's HIP bridge (backend/hip/bridge/yuuka_hip.h):
+ * opaque handles owned by the caller and freed exactly once, every call
+ * returns a yuuka_status, yuuka_last_error() is thread-local, no exception
+ * crosses the boundary, host transfers are synchronous with respect to the
+ * host buffer, asynchronous work touches device buffers only.
+ *
+ * Each declaration cites the reference interface it replaces or extends.
+ */
+#ifndef YUUKA_CUDA_H
+#define YUUKA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define YUUKA_CUDA_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define YUUKA_API __attribute__((visibility("default")))
+#else
+#define YUUKA_API
+#endif
+
+/* yuuka_hip.h:21-35 */
+typedef struct yuuka_device yuuka_device;
+typedef struct yuuka_buffer yuuka_buffer;
+typedef struct yuuka_stream yuuka_stream;
+typedef struct yuuka_event yuuka_event;
+
+typedef enum yuuka_status {
+    YUUKA_OK = 0,
+    YUUKA_ERR_INVALID_ARGUMENT = 1,
+    YUUKA_ERR_UNSUPPORTED = 2,
+    YUUKA_ERR_DEVICE = 3,
+    YUUKA_ERR_ALLOCATION = 4,
+    YUUKA_ERR_INTERNAL = 5
+} yuuka_status;
+
+/* yuuka_hip.h:37-47 (gcn_arch/hip_version become sm arch / CUDA version) */
+typedef struct yuuka_device_info {
+    char name[256];
+    char arch[64];
+    char cuda_version[64];
+    uint64_t total_memory;
+    uint32_t multiprocessors;
+    uint32_t clock_mhz;
+    uint32_t l2_bytes;
+    uint32_t smem_per_block_optin;
+    int32_t pci_domain;
+    int32_t pci_bus;
+    int32_t pci_device;
+} yuuka_device_info;
+
+/* GGML dtype ids, as yuuka_hip.h:198-207. BF16 (GGML id 30) is accepted for
+ * activations of the kernel-level GEMM only. */
+typedef enum yuuka_dtype {
+    YUUKA_DTYPE_F32 = 0,
+    YUUKA_DTYPE_F16 = 1,
+    YUUKA_DTYPE_Q8_0 = 8,
+    YUUKA_DTYPE_Q4_K = 12,
+    YUUKA_DTYPE_Q5_K = 13,
+    YUUKA_DTYPE_Q6_K = 14,
+    YUUKA_DTYPE_BF16 = 30
+} yuuka_dtype;
+
+/* KV pool formats: model/qwen35/kv_format.go:16-24 */
+typedef enum yuuka_kv_format { YUUKA_KV_F32 = 0, YUUKA_KV_F16 = 1, YUUKA_KV_Q8_0 = 2 } yuuka_kv_format;
+
+/* yuuka_hip.h:49-53 */
+YUUKA_API uint32_t yuuka_abi_version(void);
+YUUKA_API const char * yuuka_last_error(void);
+
+/* yuuka_hip.h:55-58 */
+YUUKA_API yuuka_status yuuka_device_open(int32_t index, yuuka_device ** out);
+YUUKA_API void yuuka_device_close(yuuka_device * dev);
+YUUKA_API yuuka_status yuuka_device_info_get(const yuuka_device * dev, yuuka_device_info * info);
+
+/* yuuka_hip.h:60-64 */
+YUUKA_API yuuka_status yuuka_buffer_alloc(yuuka_device * dev, uint64_t bytes, yuuka_buffer ** out);
+YUUKA_API void yuuka_buffer_free(yuuka_buffer * buf);
+YUUKA_API uint64_t yuuka_buffer_size(const yuuka_buffer * buf);
+YUUKA_API void * yuuka_buffer_ptr(const yuuka_buffer * buf);
+
+/* yuuka_hip.h:66-72. Events here can also be recorded explicitly and timed,
+ * which the reference does inside yuuka_plan_execute_profiled (:491-496). */
+YUUKA_API yuuka_status yuuka_stream_create(yuuka_device * dev, yuuka_stream ** out);
+YUUKA_API void yuuka_stream_destroy(yuuka_stream * stream);
+YUUKA_API yuuka_status yuuka_stream_synchronize(yuuka_stream * stream);
+YUUKA_API yuuka_status yuuka_event_create(yuuka_device * dev, yuuka_event ** out);
+YUUKA_API void yuuka_event_destroy(yuuka_event * event);
+YUUKA_API yuuka_status yuuka_event_record(yuuka_stream * stream, yuuka_event * event);
+YUUKA_API yuuka_status yuuka_event_wait(yuuka_event * event);
+YUUKA_API yuuka_status yuuka_event_elapsed_ms(yuuka_event * start, yuuka_event * end, float * ms);
+
+/* yuuka_hip.h:74-79 (+ an offset form for uploads) */
+YUUKA_API yuuka_status yuuka_memcpy_h2d(yuuka_buffer * dst, const void * src, uint64_t bytes);
+YUUKA_API yuuka_status yuuka_memcpy_h2d_at(yuuka_buffer * dst, uint64_t offset, const void * src, uint64_t bytes);
+YUUKA_API yuuka_status yuuka_memcpy_d2h(void * dst, const yuuka_buffer * src, uint64_t bytes);
+YUUKA_API yuuka_status yuuka_memcpy_d2h_at(void * dst, const yuuka_buffer * src, uint64_t offset, uint64_t bytes);
+YUUKA_API yuuka_status yuuka_memset(yuuka_stream * stream, yuuka_buffer * dst, int value, uint64_t bytes);
+/* yuuka_hip.h:81-86 */
+YUUKA_API yuuka_status yuuka_buffer_copy(yuuka_stream * stream, yuuka_buffer * dst, uint64_t dst_offset,
+                                         const yuuka_buffer * src, uint64_t src_offset, uint64_t bytes,
+                                         yuuka_event * completion);
+
+/* ------------------------------------------------------------------------
+ * Kernel-level entry points (what yuuka_gemv_batch / yuuka_gemm_wmma and the
+ * LM_HEAD, ATTENTION_PREFILL_PAGED and RECURRENT_CHUNK plan ops are in the
+ * reference: yuuka_hip.h:209-300,340-440). All are asynchronous on stream.
+ * ---------------------------------------------------------------------- */
+
+/* GEMM route. AUTO picks by row count; the others force one kernel family. */
+#define YUUKA_GEMM_PATH_AUTO 0u
+#define YUUKA_GEMM_PATH_FP32 1u /* CUDA-core dot products, fp32 weights and activations */
+#define YUUKA_GEMM_PATH_MMA 2u  /* fp16-operand tensor-core MMA, fp32 accumulate */
+
+/* out[rows, n_out] (f32) = x[rows, n_in] * W[n_out, n_in]^T, W in the packed
+ * GGUF row layout of w_dtype (replaces yuuka_gemv_batch, yuuka_hip.h:291-300,
+ * and YUUKA_OP_LM_HEAD). x_dtype is F32 or BF16. Byte offsets select
+ * sub-ranges of the buffers. flags: bit 0 adds the product to out instead of
+ * overwriting it (GEMV_RESIDUAL, yuuka_hip.h:398-401). */
+#define YUUKA_GEMM_ACCUMULATE 0x1u
+YUUKA_API yuuka_status yuuka_gemm_quant(yuuka_stream * stream,
+                                        yuuka_buffer * out, uint64_t out_offset,
+                                        const yuuka_buffer * x, uint64_t x_offset, uint32_t x_dtype,
+                                        const yuuka_buffer * w, uint64_t w_offset, uint32_t w_dtype,
+                                        uint64_t n_in, uint64_t n_out, uint64_t rows,
+                                        uint32_t path, uint32_t flags, yuuka_event * completion);
+
+/* ------------------------------------------------------------------------
+ * Model and verify session (what engine/gpu's Model/Session/plan builders do
+ * in Go through yuuka_plan_*; here the plan lives behind the ABI so that one
+ * call runs the whole verify step).
+ * ---------------------------------------------------------------------- */
+
+typedef struct yuuka_model yuuka_model;
+typedef struct yuuka_session yuuka_session;
+
+/* model/qwen35/config.go:18-44 */
+typedef struct yuuka_model_config {
+    int32_t block_count, context_length, hidden, ffn;
+    int32_t heads, kv_heads, head_dim, rope_dim;
+    double rope_freq_base;
+    float rms_eps;
+    int32_t vocab;
+    int32_t conv_kernel, state_size, group_count, time_step_rank, inner_size;
+    int32_t full_attention_interval;
+    int32_t expert_count, expert_used, expert_ffn, shared_ffn;
+} yuuka_model_config;
+
+/* Validates cfg with the rules of model/qwen35/config.go:231-276. */
+YUUKA_API yuuka_status yuuka_model_create(yuuka_device * dev, const yuuka_model_config * cfg, yuuka_model ** out);
+YUUKA_API void yuuka_model_destroy(yuuka_model * model);
+/* Uploads one GGUF tensor verbatim (engine/gpu/model.go:288-301). name is the
+ * GGUF tensor name read by model/qwen35/load.go:80-215; rows/cols the logical
+ * shape (vectors: rows = 1; expert tensors: rows = per-expert rows * experts). */
+YUUKA_API yuuka_status yuuka_model_set_tensor(yuuka_model * model, const char * name, uint32_t dtype,
+                                              const void * data, uint64_t rows, uint64_t cols);
+/* Checks that every required tensor is present with the right shape. */
+YUUKA_API yuuka_status yuuka_model_finalize(yuuka_model * model);
+YUUKA_API uint64_t yuuka_model_weight_bytes(const yuuka_model * model);
+
+/* A session owns a paged KV pool, per-sequence block tables, positions and
+ * recurrent state for max_batch sequences (engine/gpu/session.go:58-182 holds
+ * one; serving needs many), plus the activations of one verify step of up to
+ * max_nodes rows per sequence. */
+typedef struct yuuka_session_config {
+    int32_t max_batch;     /* sequences */
+    int32_t max_nodes;     /* rows per sequence per step, pending token included (<= 64) */
+    int32_t capacity;      /* positions per sequence, <= context_length */
+    int32_t block_size;    /* tokens per KV block; 0 = 16 (model/qwen35/state.go:68) */
+    int32_t pool_blocks;   /* 0 = max_batch * ceil(capacity / block_size) */
+    int32_t kv_format;     /* yuuka_kv_format */
+    int32_t want_logits;   /* keep f32 logits [max_batch*max_nodes, vocab] for download */
+} yuuka_session_config;
+
+YUUKA_API yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_config * cfg,
+                                            yuuka_session ** out);
+YUUKA_API void yuuka_session_destroy(yuuka_session * s);
+/* Block table of one sequence: int32 block ids, as memory.Table.Blocks()
+ * returns them (memory/memory.go:199). Ids must be < pool_blocks. The default
+ * is the identity mapping over the sequence's own slice of the pool. */
+YUUKA_API yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const int32_t * blocks,
+                                                     int32_t count);
+/* State.Reset / State.SetPos (model/qwen35/state.go:174-208) */
+YUUKA_API yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq);
+YUUKA_API yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t position);
+YUUKA_API yuuka_status yuuka_session_position(yuuka_session * s, int32_t seq, int32_t * position);
+/* State.Snapshot / Restore byte format (model/qwen35/state.go:211-263): for each
+ * recurrent layer in order, conv then s, little-endian f32. */
+YUUKA_API uint64_t yuuka_session_snapshot_bytes(const yuuka_session * s);
+YUUKA_API yuuka_status yuuka_session_snapshot(yuuka_session * s, int32_t seq, void * dst, uint64_t bytes);
+YUUKA_API yuuka_status yuuka_session_restore(yuuka_session * s, int32_t seq, const void * src, uint64_t bytes);
+
+/* engine.SpeculativeRuntime.PrefillLogits (engine/engine.go:55-63;
+ * engine/gpu/session.go:246-303): runs n tokens of sequence seq as a chain,
+ * commits all of them, and (logits != NULL) returns f32 logits [n, vocab].
+ * n may exceed max_nodes; it is processed in chunks. Synchronous. */
+YUUKA_API yuuka_status yuuka_session_prefill_logits(yuuka_session * s, int32_t seq, const int32_t * tokens,
+                                                    int32_t n, float * logits);
+/* Runtime.Forward (engine/engine.go:67-74): as above but only the last row's
+ * logits are computed and returned (last_logits may be NULL). */
+YUUKA_API yuuka_status yuuka_session_forward(yuuka_session * s, int32_t seq, const int32_t * tokens, int32_t n,
+                                             float * last_logits);
+
+/* Acceptance modes of a verify step. */
+#define YUUKA_ACCEPT_GREEDY 0u    /* engine/speculative.go:193-202 with argmaxLogit :263-271 */
+#define YUUKA_ACCEPT_REJECTION 1u /* not in the reference; rule documented in DESIGN.md */
+#define YUUKA_ACCEPT_NONE 2u      /* run and commit nothing: logits only */
+
+/* One verify step over `batch` sequences (seq ids 0..batch-1 of the session).
+ * Per sequence, `nodes` rows: row 0 is the pending token (the last emitted
+ * token that has not been run), rows 1.. are draft tokens; parent[b][i] is the
+ * row that precedes row i (-1 for row 0, < i otherwise; a chain is i-1).
+ * All pointers are HOST memory; the call uploads them, runs the step, performs
+ * acceptance and the KV / recurrent-state commit on the device, downloads the
+ * results and returns when they are in the output arrays.
+ *   accepted[b]        number of accepted draft rows a
+ *   emitted[b][0..a]   a accepted draft tokens followed by the correction or
+ *                      bonus token (which is the next pending token)
+ *   path[b][0..a-1]    accepted row ids (may be NULL)
+ * For rejection sampling draft_probs is f32 [batch, nodes, vocab] (row i holds
+ * the distribution token i was drawn from; row 0 unused), uniforms f32
+ * [batch, nodes, 2]. */
+typedef struct yuuka_verify_batch {
+    int32_t batch;
+    int32_t nodes;
+    const int32_t * tokens;      /* [batch, nodes] */
+    const int32_t * parent;      /* [batch, nodes]; NULL = chain */
+    uint32_t mode;
+    float temperature;
+    const yuuka_buffer * draft_probs; /* device buffer, rejection mode only */
+    const float * uniforms;      /* host, rejection mode only */
+    int32_t * accepted;          /* [batch] */
+    int32_t * emitted;           /* [batch, nodes] */
+    int32_t * path;              /* [batch, nodes] or NULL */
+    float * logits;              /* optional host [batch, nodes, vocab]; needs want_logits */
+} yuuka_verify_batch;
+
+YUUKA_API yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_batch * batch);
+
+/* Device-resident variant for benchmarking and pipelined serving: inputs were
+ * staged with yuuka_verify_stage, the step only enqueues kernels on the
+ * session stream (no host synchronisation); results are fetched later. */
+YUUKA_API yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * batch);
+YUUKA_API yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion);
+YUUKA_API yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * batch);
+YUUKA_API yuuka_stream * yuuka_session_stream(yuuka_session * s);
+/* Kernel launches enqueued by the last yuuka_verify_launch. */
+YUUKA_API uint32_t yuuka_session_last_launch_count(const yuuka_session * s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

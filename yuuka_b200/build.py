@@ -19,7 +19,7 @@ SYNTH_LIB = os.path.join(HERE, "libyuuka_synth.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math=false", "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2,-Wall",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2,-Wall",
     "--expt-relaxed-constexpr",
 ]
 

@@ -1,0 +1,103 @@
+// Shared host-side plumbing of libyuuka_cuda: handle types, error reporting
+// and the guard that keeps C++ exceptions behind the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <exception>
+#include <new>
+#include <string>
+
+#include "yuuka_cuda.h"
+
+namespace yk {
+
+// Thread-local message of the most recent failed call (the reference keeps the
+// same contract: backend/hip/bridge/bridge.cpp:47-57).
+std::string & last_error_ref();
+yuuka_status fail(yuuka_status code, const char * fmt, ...);
+
+struct StatusError {
+    yuuka_status code;
+};
+
+#define YK_CUDA(expr)                                                                         \
+    do {                                                                                      \
+        cudaError_t err__ = (expr);                                                           \
+        if (err__ != cudaSuccess) {                                                           \
+            yk::fail(YUUKA_ERR_DEVICE, "%s failed: %s", #expr, cudaGetErrorString(err__));    \
+            throw yk::StatusError{YUUKA_ERR_DEVICE};                                          \
+        }                                                                                     \
+    } while (0)
+
+#define YK_REQUIRE(cond, code, ...)                                                           \
+    do {                                                                                      \
+        if (!(cond)) {                                                                        \
+            yk::fail(code, __VA_ARGS__);                                                      \
+            throw yk::StatusError{code};                                                      \
+        }                                                                                     \
+    } while (0)
+
+// Runs fn and converts every failure into a status (bridge.cpp:1893-1904).
+template <typename F>
+yuuka_status guard(F && fn) {
+    try {
+        fn();
+        return YUUKA_OK;
+    } catch (const StatusError & e) {
+        return e.code;
+    } catch (const std::bad_alloc &) {
+        return fail(YUUKA_ERR_ALLOCATION, "host allocation failed");
+    } catch (const std::exception & e) {
+        return fail(YUUKA_ERR_INTERNAL, "%s", e.what());
+    } catch (...) {
+        return fail(YUUKA_ERR_INTERNAL, "unknown failure");
+    }
+}
+
+inline uint64_t row_bytes(uint32_t dtype, uint64_t cols) {
+    switch (dtype) {
+    case YUUKA_DTYPE_F32: return cols * 4;
+    case YUUKA_DTYPE_F16: return cols * 2;
+    case YUUKA_DTYPE_BF16: return cols * 2;
+    case YUUKA_DTYPE_Q8_0: return cols % 32 ? 0 : cols / 32 * 34;
+    case YUUKA_DTYPE_Q4_K: return cols % 256 ? 0 : cols / 256 * 144;
+    case YUUKA_DTYPE_Q5_K: return cols % 256 ? 0 : cols / 256 * 176;
+    case YUUKA_DTYPE_Q6_K: return cols % 256 ? 0 : cols / 256 * 210;
+    default: return 0;
+    }
+}
+
+}  // namespace yk
+
+struct yuuka_device {
+    int index = 0;
+    cudaDeviceProp prop{};
+    int sm_count = 0;
+};
+
+struct yuuka_buffer {
+    yuuka_device * dev = nullptr;
+    void * ptr = nullptr;
+    uint64_t bytes = 0;
+};
+
+struct yuuka_stream {
+    yuuka_device * dev = nullptr;
+    cudaStream_t s = nullptr;
+};
+
+struct yuuka_event {
+    yuuka_device * dev = nullptr;
+    cudaEvent_t e = nullptr;
+};
+
+namespace yk {
+inline void record_completion(yuuka_stream * stream, yuuka_event * completion) {
+    if (completion) YK_CUDA(cudaEventRecord(completion->e, stream->s));
+}
+inline void set_device(const yuuka_device * dev) { YK_CUDA(cudaSetDevice(dev->index)); }
+}  // namespace yk

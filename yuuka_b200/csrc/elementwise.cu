@@ -1,0 +1,225 @@
+// Row-wise kernels of the verify step: embedding gather, RMSNorm, SwiGLU
+// product, and the attention front end (per-head norm, RoPE, paged KV write).
+#include "layers.cuh"
+#include "quant.cuh"
+
+namespace yk {
+
+// ---------------------------------------------------------------------------
+// embedding (replaces embedding_batch_f32_kernel, kernels/hip/prefill/prefill.hip:146)
+
+__global__ void embedding_kernel(float * __restrict__ x, int ldx, const uint8_t * __restrict__ table, uint32_t dtype,
+                                 int64_t rb, int hidden, int vocab, const int32_t * __restrict__ tokens) {
+    const int r = blockIdx.x;
+    int tok = tokens[r];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // ids are validated on the host
+    const uint8_t * row = table + (int64_t)tok * rb;
+    for (int e8 = threadIdx.x; e8 < hidden / 8; e8 += blockDim.x) {
+        float w[8];
+        switch (dtype) {
+        case YUUKA_DTYPE_F32: decode8<YUUKA_DTYPE_F32>(row, e8, w); break;
+        case YUUKA_DTYPE_F16: decode8<YUUKA_DTYPE_F16>(row, e8, w); break;
+        case YUUKA_DTYPE_Q8_0: decode8<YUUKA_DTYPE_Q8_0>(row, e8, w); break;
+        case YUUKA_DTYPE_Q4_K: decode8<YUUKA_DTYPE_Q4_K>(row, e8, w); break;
+        case YUUKA_DTYPE_Q5_K: decode8<YUUKA_DTYPE_Q5_K>(row, e8, w); break;
+        default: decode8<YUUKA_DTYPE_Q6_K>(row, e8, w); break;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[(int64_t)r * ldx + e8 * 8 + i] = w[i];
+    }
+}
+
+void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
+                      const int32_t * tokens, int rows) {
+    embedding_kernel<<<rows, 128, 0, s>>>(x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens);
+    YK_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// block-wide double sum
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ double block_sum_d(double v, double * red) {
+    v = warp_sum_d(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double t = 0;
+    for (int i = 0; i < nw; i++) t += red[i];
+    __syncthreads();
+    return t;
+}
+
+// rmsNorm (model/qwen35/forward.go:460-470): f64 sum of squares, f32 mean,
+// scale = f32(1/sqrt(f64(mean + eps))), dst = src * scale * weight.
+__global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
+                               const float * __restrict__ weight, int cols, float eps) {
+    __shared__ double red[32];
+    const int r = blockIdx.x;
+    const float * x = src + (int64_t)r * lds;
+    double sum = 0;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) sum += (double)x[i] * (double)x[i];
+    sum = block_sum_d(sum, red);
+    float mean = (float)(sum / (double)cols);
+    float scale = (float)(1.0 / sqrt((double)(mean + eps)));
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) dst[(int64_t)r * ldd + i] = x[i] * scale * weight[i];
+}
+
+void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight, int cols,
+                    int rows, float eps) {
+    rmsnorm_kernel<<<rows, 256, 0, s>>>(dst, ldd, src, lds, weight, cols, eps);
+    YK_CUDA(cudaGetLastError());
+}
+
+// sigmoid / silu as the reference computes them: exp in f64 (forward.go:552-558)
+__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + (float)exp((double)-x)); }
+__device__ __forceinline__ float silu_ref(float x) { return x * sigmoid_ref(x); }
+
+__global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float * __restrict__ gate,
+                                const float * __restrict__ up, int ld, int cols) {
+    const int r = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < cols; i += gridDim.x * blockDim.x)
+        act[(int64_t)r * lda + i] = silu_ref(gate[(int64_t)r * ld + i]) * up[(int64_t)r * ld + i];
+}
+
+void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
+                     int rows) {
+    dim3 grid((cols + 255) / 256, rows);
+    silu_mul_kernel<<<grid, 256, 0, s>>>(act, lda, gate, up, ld, cols);
+    YK_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// attention front end
+
+struct PrepParams {
+    float * q; int ldq;
+    float * k; int ldk;
+    const float * v; int ldv;
+    const float * q_norm; const float * k_norm;
+    int heads, kv_heads, hd, rope_dim;
+    double rope_base;
+    float eps;
+    RowMeta rows;
+    KvPool pool;
+};
+
+// rmsNormInPlace (forward.go:472-482) on hd values handled by one warp, then
+// RoPE over the first rope_dim dims (forward.go:495-514).
+__device__ void norm_rope_head(float * x, const float * w, int hd, int rope_dim, double base, int pos, float eps) {
+    const int lane = threadIdx.x & 31;
+    double sum = 0;
+    for (int i = lane; i < hd; i += 32) sum += (double)x[i] * (double)x[i];
+    sum = warp_sum_d(sum);
+    float mean = (float)(sum / (double)hd);
+    float scale = (float)(1.0 / sqrt((double)(mean + eps)));
+    for (int i = lane; i < hd; i += 32) x[i] *= scale * w[i];
+    __syncwarp();
+    const int half = rope_dim / 2;
+    for (int i = lane; i < half; i += 32) {
+        double theta = (double)pos * pow(base, -2.0 * (double)i / (double)rope_dim);
+        float c = (float)cos(theta), s = (float)sin(theta);
+        float x0 = x[i], x1 = x[i + half];
+        x[i] = x0 * c - x1 * s;
+        x[i + half] = x0 * s + x1 * c;
+    }
+    __syncwarp();
+}
+
+__device__ __forceinline__ int64_t kv_row_offset(const KvPool & pool, int seq, int slot) {
+    int block = pool.tables[(int64_t)seq * pool.table_stride + slot / pool.block_size];
+    return ((int64_t)block * pool.block_size + slot % pool.block_size) * pool.row_bytes;
+}
+
+// KVFormat.EncodeRow (model/qwen35/kv_format.go:75-131)
+__device__ void kv_encode_row(uint8_t * dst, int format, const float * src, int n) {
+    if (format == YUUKA_KV_F32) {
+        float * d = reinterpret_cast<float *>(dst);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = src[i];
+    } else if (format == YUUKA_KV_F16) {
+        uint16_t * d = reinterpret_cast<uint16_t *>(dst);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = f32_to_f16_ref(src[i]);
+    } else {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        for (int blk = warp; blk < (n + 31) / 32; blk += nw) {
+            int i = blk * 32 + lane;
+            float v = i < n ? src[i] : 0.0f;
+            float amax = fabsf(v);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            float scale = amax / 127.0f;
+            uint8_t * o = dst + blk * 34;
+            if (lane == 0) *reinterpret_cast<uint16_t *>(o) = f32_to_f16_ref(scale);
+            int8_t q = 0;
+            if (i < n && scale != 0.0f) q = (int8_t)(int)round((double)(v / scale));
+            o[2 + lane] = (uint8_t)q;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
+    const int r = blockIdx.x;
+    const int seq = r / p.rows.nodes, node = r - seq * p.rows.nodes;
+    const int pos0 = p.rows.pos0[seq];
+    const int pos = pos0 + p.rows.depth[r];
+    const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = warp; h < p.heads + p.kv_heads; h += nw) {
+        if (h < p.heads)
+            norm_rope_head(p.q + (int64_t)r * p.ldq + (int64_t)h * 2 * p.hd, p.q_norm, p.hd, p.rope_dim, p.rope_base, pos,
+                           p.eps);
+        else
+            norm_rope_head(p.k + (int64_t)r * p.ldk + (int64_t)(h - p.heads) * p.hd, p.k_norm, p.hd, p.rope_dim,
+                           p.rope_base, pos, p.eps);
+    }
+    __syncthreads();
+    // every row is stored at slot pos0 + node; the commit moves accepted rows of
+    // a tree to their final positions
+    const int64_t off = kv_row_offset(p.pool, seq, pos0 + node);
+    kv_encode_row(p.pool.k + off, p.pool.format, p.k + (int64_t)r * p.ldk, p.pool.kv_dim);
+    kv_encode_row(p.pool.v + off, p.pool.format, p.v + (int64_t)r * p.ldv, p.pool.kv_dim);
+}
+
+void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, const float * v, int ldv,
+                      const float * q_norm, const float * k_norm, int heads, int kv_heads, int head_dim, int rope_dim,
+                      double rope_base, float eps, const RowMeta & rows, const KvPool & pool) {
+    PrepParams p{q, ldq, k, ldk, v, ldv, q_norm, k_norm, heads, kv_heads, head_dim, rope_dim, rope_base, eps, rows, pool};
+    attn_prep_kernel<<<rows.batch * rows.nodes, 256, 0, s>>>(p);
+    YK_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// gated RMSNorm of the delta-net output (model/qwen35/recurrent.go:39-50)
+
+__global__ void gdn_norm_gate_kernel(float * __restrict__ out, int ldo, const float * __restrict__ z, int ldz,
+                                     const float * __restrict__ norm, int rank, int S, float eps) {
+    const int r = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (h >= rank) return;
+    float * row = out + (int64_t)r * ldo + (int64_t)h * S;
+    const float * gate = z + (int64_t)r * ldz + (int64_t)h * S;
+    double sum = 0;
+    for (int i = lane; i < S; i += 32) sum += (double)row[i] * (double)row[i];
+    sum = warp_sum_d(sum);
+    float mean = (float)(sum / (double)S);
+    float scale = (float)(1.0 / sqrt((double)(mean + eps)));
+    for (int i = lane; i < S; i += 32) {
+        float v = row[i];
+        v *= scale * norm[i];
+        row[i] = v * silu_ref(gate[i]);
+    }
+}
+
+void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
+                          int S, int rows, float eps) {
+    dim3 grid((rank + 3) / 4, rows);
+    gdn_norm_gate_kernel<<<grid, 128, 0, s>>>(out, ldo, z, ldz, norm, rank, S, eps);
+    YK_CUDA(cudaGetLastError());
+}
+
+}  // namespace yk

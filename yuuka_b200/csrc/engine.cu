@@ -1,0 +1,931 @@
+// Model, session and the verify step: the host-side plan that the reference
+// builds in Go (engine/gpu/model.go, session.go, plan.go buildPrefillPlan with
+// prefillAllLogits) lives here behind the C ABI, so one call runs a whole
+// verify step: k+1 (or tree) rows through every layer, on-device acceptance,
+// KV / recurrent-state commit.
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "gemm_quant.cuh"
+#include "layers.cuh"
+
+using namespace yk;
+
+namespace {
+
+struct Tensor {
+    uint8_t * ptr = nullptr;
+    uint32_t dtype = 0;
+    uint64_t rows = 0, cols = 0, bytes = 0;
+    bool owned = false;
+    bool present() const { return ptr != nullptr; }
+};
+
+struct LayerW {
+    const float * attn_norm = nullptr;
+    const float * post_norm = nullptr;
+    // full attention
+    Tensor q, k, v, o;
+    const float * q_norm = nullptr;
+    const float * k_norm = nullptr;
+    // gated delta-net
+    Tensor qkv, gate, beta, alpha, out;
+    const float * conv = nullptr;
+    const float * dt = nullptr;
+    const float * a = nullptr;
+    const float * ssm_norm = nullptr;
+    // dense FFN
+    Tensor ffn_gate, ffn_up, ffn_down;
+    // fused row ranges (same dtype, adjacent in memory): one GEMM each
+    Tensor proj;     // qkv | gate | beta | alpha
+    Tensor qk;       // q | k (| v)
+    bool qk_has_v = false;
+    Tensor gate_up;  // ffn_gate | ffn_up
+};
+
+void free_tensor(Tensor & t) {
+    if (t.owned && t.ptr) cudaFree(t.ptr);
+    t = Tensor();
+}
+
+}  // namespace
+
+struct yuuka_model {
+    yuuka_device * dev = nullptr;
+    yuuka_model_config cfg{};
+    std::map<std::string, Tensor> tensors;
+    std::vector<LayerW> layers;
+    Tensor embedding, output;
+    const float * output_norm = nullptr;
+    std::vector<void *> extra_allocs;
+    bool finalized = false;
+    uint64_t weight_bytes = 0;
+
+    int conv_dim() const { return 2 * cfg.group_count * cfg.state_size + cfg.inner_size; }
+    int q_dim() const { return cfg.heads * cfg.head_dim * 2; }
+    int kv_dim() const { return cfg.kv_heads * cfg.head_dim; }
+    int o_dim() const { return cfg.heads * cfg.head_dim; }
+    bool recurrent(int layer) const { return (layer + 1) % cfg.full_attention_interval != 0; }
+};
+
+namespace {
+
+// model/qwen35/config.go:231-276
+void validate_config(const yuuka_model_config & c) {
+    YK_REQUIRE(c.block_count > 0 && c.hidden > 0 && c.head_dim > 0 && c.heads > 0, YUUKA_ERR_INVALID_ARGUMENT,
+               "invalid model size");
+    YK_REQUIRE(c.kv_heads > 0 && c.heads % c.kv_heads == 0, YUUKA_ERR_INVALID_ARGUMENT,
+               "head count %d is not a multiple of KV head count %d", c.heads, c.kv_heads);
+    YK_REQUIRE(c.rope_dim % 2 == 0 && c.rope_dim <= c.head_dim && c.rope_dim >= 0, YUUKA_ERR_INVALID_ARGUMENT,
+               "invalid RoPE dimension %d for head dim %d", c.rope_dim, c.head_dim);
+    YK_REQUIRE(c.full_attention_interval > 0, YUUKA_ERR_INVALID_ARGUMENT, "full attention interval must be positive");
+    YK_REQUIRE(c.inner_size == c.time_step_rank * c.state_size, YUUKA_ERR_INVALID_ARGUMENT,
+               "ssm inner size %d != time_step_rank %d * state_size %d", c.inner_size, c.time_step_rank, c.state_size);
+    YK_REQUIRE(c.conv_kernel >= 2, YUUKA_ERR_INVALID_ARGUMENT, "invalid ssm conv kernel %d", c.conv_kernel);
+    if (c.expert_count > 0) {
+        YK_REQUIRE(c.expert_used > 0 && c.expert_used <= c.expert_count, YUUKA_ERR_INVALID_ARGUMENT,
+                   "expert used count %d is outside 1..%d", c.expert_used, c.expert_count);
+        YK_REQUIRE(c.expert_ffn > 0, YUUKA_ERR_INVALID_ARGUMENT, "invalid expert feed-forward size %d", c.expert_ffn);
+        YK_REQUIRE(c.shared_ffn > 0, YUUKA_ERR_INVALID_ARGUMENT, "invalid shared expert feed-forward size %d",
+                   c.shared_ffn);
+    } else {
+        YK_REQUIRE(c.ffn > 0, YUUKA_ERR_INVALID_ARGUMENT, "invalid feed-forward size %d", c.ffn);
+    }
+    YK_REQUIRE(c.context_length > 0 && c.vocab > 0, YUUKA_ERR_INVALID_ARGUMENT, "invalid context or vocabulary size");
+    // limits of this backend's kernels
+    YK_REQUIRE(c.hidden % 8 == 0 && c.head_dim % 32 == 0, YUUKA_ERR_UNSUPPORTED, "hidden %% 8 and head_dim %% 32 must be 0");
+    YK_REQUIRE(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256, YUUKA_ERR_UNSUPPORTED,
+               "head_dim %d is not 64, 128 or 256", c.head_dim);
+    YK_REQUIRE(c.state_size == 64 || c.state_size == 128, YUUKA_ERR_UNSUPPORTED, "ssm state size %d is not 64 or 128",
+               c.state_size);
+    YK_REQUIRE(c.conv_kernel <= 8, YUUKA_ERR_UNSUPPORTED, "ssm conv kernel %d exceeds 8", c.conv_kernel);
+    YK_REQUIRE(c.group_count > 0 && c.time_step_rank % c.group_count == 0, YUUKA_ERR_UNSUPPORTED,
+               "time_step_rank %d is not a multiple of group_count %d", c.time_step_rank, c.group_count);
+}
+
+const Tensor & need(const yuuka_model * m, const std::string & name, uint64_t rows, uint64_t cols, bool f32_vector) {
+    auto it = m->tensors.find(name);
+    YK_REQUIRE(it != m->tensors.end(), YUUKA_ERR_INVALID_ARGUMENT, "missing required tensor \"%s\"", name.c_str());
+    const Tensor & t = it->second;
+    YK_REQUIRE(t.rows == rows && t.cols == cols, YUUKA_ERR_INVALID_ARGUMENT,
+               "tensor \"%s\" has shape [%llu,%llu], want [%llu,%llu]", name.c_str(), (unsigned long long)t.cols,
+               (unsigned long long)t.rows, (unsigned long long)cols, (unsigned long long)rows);
+    if (f32_vector)
+        YK_REQUIRE(t.dtype == YUUKA_DTYPE_F32, YUUKA_ERR_INVALID_ARGUMENT, "tensor \"%s\" uses dtype %u, want F32",
+                   name.c_str(), t.dtype);
+    return t;
+}
+
+const float * vec(const yuuka_model * m, const std::string & name, uint64_t n) {
+    return reinterpret_cast<const float *>(need(m, name, 1, n, true).ptr);
+}
+
+// Concatenates row ranges of equal dtype and width into one allocation.
+Tensor fuse(yuuka_model * m, std::vector<const Tensor *> parts) {
+    Tensor out;
+    for (const Tensor * t : parts) {
+        if (t->dtype != parts[0]->dtype || t->cols != parts[0]->cols) return out;
+    }
+    uint64_t total = 0, rows = 0;
+    for (const Tensor * t : parts) {
+        total += t->bytes;
+        rows += t->rows;
+    }
+    void * ptr = nullptr;
+    cudaError_t err = cudaMalloc(&ptr, total + 256);
+    YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "fused weight allocation of %llu bytes failed",
+               (unsigned long long)total);
+    m->extra_allocs.push_back(ptr);
+    uint64_t off = 0;
+    for (const Tensor * t : parts) {
+        YK_CUDA(cudaMemcpy((uint8_t *)ptr + off, t->ptr, t->bytes, cudaMemcpyDeviceToDevice));
+        off += t->bytes;
+    }
+    YK_CUDA(cudaMemset((uint8_t *)ptr + total, 0, 256));
+    out.ptr = (uint8_t *)ptr;
+    out.dtype = parts[0]->dtype;
+    out.rows = rows;
+    out.cols = parts[0]->cols;
+    out.bytes = total;
+    return out;
+}
+
+void drop(yuuka_model * m, const std::string & name) {
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) return;
+    free_tensor(it->second);
+    m->tensors.erase(it);
+}
+
+}  // namespace
+
+extern "C" {
+
+yuuka_status yuuka_model_create(yuuka_device * dev, const yuuka_model_config * cfg, yuuka_model ** out) {
+    return guard([&] {
+        YK_REQUIRE(dev && cfg && out, YUUKA_ERR_INVALID_ARGUMENT, "model_create: null argument");
+        *out = nullptr;
+        validate_config(*cfg);
+        auto * m = new yuuka_model();
+        m->dev = dev;
+        m->cfg = *cfg;
+        m->layers.resize(cfg->block_count);
+        *out = m;
+    });
+}
+
+void yuuka_model_destroy(yuuka_model * m) {
+    if (!m) return;
+    cudaSetDevice(m->dev->index);
+    for (auto & kv : m->tensors) free_tensor(kv.second);
+    for (void * p : m->extra_allocs) cudaFree(p);
+    delete m;
+}
+
+yuuka_status yuuka_model_set_tensor(yuuka_model * m, const char * name, uint32_t dtype, const void * data,
+                                    uint64_t rows, uint64_t cols) {
+    return guard([&] {
+        YK_REQUIRE(m && name && data, YUUKA_ERR_INVALID_ARGUMENT, "model_set_tensor: null argument");
+        YK_REQUIRE(!m->finalized, YUUKA_ERR_INVALID_ARGUMENT, "model_set_tensor: model is finalized");
+        uint64_t rb = row_bytes(dtype, cols);
+        YK_REQUIRE(rb > 0 && dtype != YUUKA_DTYPE_BF16, YUUKA_ERR_UNSUPPORTED,
+                   "tensor \"%s\": dtype %u does not fit a row of %llu columns", name, dtype, (unsigned long long)cols);
+        YK_REQUIRE(rows > 0, YUUKA_ERR_INVALID_ARGUMENT, "tensor \"%s\": invalid row count", name);
+        set_device(m->dev);
+        Tensor t;
+        t.dtype = dtype;
+        t.rows = rows;
+        t.cols = cols;
+        t.bytes = rows * rb;
+        t.owned = true;
+        void * ptr = nullptr;
+        cudaError_t err = cudaMalloc(&ptr, t.bytes + 256);  // slack: the GEMM ring copies whole 16-byte lines
+        YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "tensor \"%s\": allocation of %llu bytes failed", name,
+                   (unsigned long long)t.bytes);
+        t.ptr = (uint8_t *)ptr;
+        err = cudaMemcpy(ptr, data, t.bytes, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) err = cudaMemset(t.ptr + t.bytes, 0, 256);
+        if (err != cudaSuccess) {
+            cudaFree(ptr);
+            YK_CUDA(err);
+        }
+        drop(m, name);
+        m->tensors[name] = t;
+    });
+}
+
+yuuka_status yuuka_model_finalize(yuuka_model * m) {
+    return guard([&] {
+        YK_REQUIRE(m, YUUKA_ERR_INVALID_ARGUMENT, "model_finalize: null model");
+        if (m->finalized) return;
+        set_device(m->dev);
+        const yuuka_model_config & c = m->cfg;
+        YK_REQUIRE(c.expert_count == 0, YUUKA_ERR_UNSUPPORTED, "qwen35moe layers are not supported by this build yet");
+        const uint64_t H = c.hidden, V = c.vocab;
+        m->embedding = need(m, "token_embd.weight", V, H, false);
+        if (m->tensors.count("output.weight")) m->output = need(m, "output.weight", V, H, false);
+        else m->output = m->embedding;  // tied head (model/qwen35/load.go:88-97)
+        m->output_norm = vec(m, "output_norm.weight", H);
+        const uint64_t S = c.state_size, R = c.time_step_rank, inner = c.inner_size;
+        const uint64_t conv_dim = m->conv_dim(), q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim();
+        for (int i = 0; i < c.block_count; i++) {
+            LayerW & L = m->layers[i];
+            const std::string p = "blk." + std::to_string(i) + ".";
+            L.attn_norm = vec(m, p + "attn_norm.weight", H);
+            L.post_norm = vec(m, p + "post_attention_norm.weight", H);
+            if (m->recurrent(i)) {
+                L.qkv = need(m, p + "attn_qkv.weight", conv_dim, H, false);
+                L.gate = need(m, p + "attn_gate.weight", inner, H, false);
+                L.out = need(m, p + "ssm_out.weight", H, inner, false);
+                L.beta = need(m, p + "ssm_beta.weight", R, H, false);
+                L.alpha = need(m, p + "ssm_alpha.weight", R, H, false);
+                L.conv = reinterpret_cast<const float *>(need(m, p + "ssm_conv1d.weight", 1, c.conv_kernel * conv_dim, true).ptr);
+                L.dt = vec(m, p + "ssm_dt.bias", R);
+                L.a = vec(m, p + "ssm_a", R);
+                L.ssm_norm = vec(m, p + "ssm_norm.weight", S);
+                L.proj = fuse(m, {&L.qkv, &L.gate, &L.beta, &L.alpha});
+                if (L.proj.present()) {
+                    for (const char * n : {"attn_qkv.weight", "attn_gate.weight", "ssm_beta.weight", "ssm_alpha.weight"})
+                        drop(m, p + n);
+                    L.qkv = L.gate = L.beta = L.alpha = Tensor();
+                }
+            } else {
+                L.q = need(m, p + "attn_q.weight", q_dim, H, false);
+                L.k = need(m, p + "attn_k.weight", kv_dim, H, false);
+                L.v = need(m, p + "attn_v.weight", kv_dim, H, false);
+                L.o = need(m, p + "attn_output.weight", H, o_dim, false);
+                L.q_norm = vec(m, p + "attn_q_norm.weight", c.head_dim);
+                L.k_norm = vec(m, p + "attn_k_norm.weight", c.head_dim);
+                L.qk = fuse(m, {&L.q, &L.k, &L.v});
+                L.qk_has_v = L.qk.present();
+                if (!L.qk.present()) L.qk = fuse(m, {&L.q, &L.k});
+                if (L.qk.present()) {
+                    drop(m, p + "attn_q.weight");
+                    drop(m, p + "attn_k.weight");
+                    L.q = L.k = Tensor();
+                    if (L.qk_has_v) {
+                        drop(m, p + "attn_v.weight");
+                        L.v = Tensor();
+                    }
+                }
+            }
+            L.ffn_gate = need(m, p + "ffn_gate.weight", c.ffn, H, false);
+            L.ffn_up = need(m, p + "ffn_up.weight", c.ffn, H, false);
+            L.ffn_down = need(m, p + "ffn_down.weight", H, c.ffn, false);
+            L.gate_up = fuse(m, {&L.ffn_gate, &L.ffn_up});
+            if (L.gate_up.present()) {
+                drop(m, p + "ffn_gate.weight");
+                drop(m, p + "ffn_up.weight");
+                L.ffn_gate = L.ffn_up = Tensor();
+            }
+        }
+        // bytes one step streams: every matrix and vector except the embedding table
+        uint64_t total = 0;
+        for (auto & kv : m->tensors)
+            if (kv.first != "token_embd.weight") total += kv.second.bytes;
+        for (const LayerW & L : m->layers) total += L.proj.bytes + L.qk.bytes + L.gate_up.bytes;
+        m->weight_bytes = total;
+        m->finalized = true;
+    });
+}
+
+uint64_t yuuka_model_weight_bytes(const yuuka_model * m) { return m ? m->weight_bytes : 0; }
+
+}  // extern "C"
+
+// ===========================================================================
+// session
+
+namespace {
+
+template <typename T>
+T * dalloc(size_t count, std::vector<void *> & owned, bool zero = true) {
+    void * p = nullptr;
+    size_t bytes = (count > 0 ? count : 1) * sizeof(T);
+    cudaError_t err = cudaMalloc(&p, bytes);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        YK_REQUIRE(false, YUUKA_ERR_ALLOCATION, "session allocation of %llu bytes failed", (unsigned long long)bytes);
+    }
+    owned.push_back(p);
+    if (zero) YK_CUDA(cudaMemset(p, 0, bytes));
+    return (T *)p;
+}
+
+struct LayerState {
+    // attention layers
+    uint8_t * k = nullptr;
+    uint8_t * v = nullptr;
+    // recurrent layers
+    float * conv_state = nullptr;  // [batch][conv_dim][kernel-1]
+    float * state = nullptr;       // [batch][rank][S][S]
+    float * proj = nullptr;        // [rows][n_proj] kept until the commit
+    float * khat = nullptr;
+    float * dlog = nullptr;
+    float * decay = nullptr;
+};
+
+}  // namespace
+
+struct yuuka_session {
+    yuuka_model * model = nullptr;
+    yuuka_session_config cfg{};
+    yuuka_stream stream;
+    std::vector<void *> owned;
+    int table_stride = 0;
+    int kv_row_bytes = 0;
+    int64_t conv_count = 0, s_count = 0;
+    std::vector<LayerState> layers;
+    std::vector<int> gdn_layers, attn_layers;
+    GdnLayerCommit * d_gdn_commit = nullptr;
+    KvLayerCommit * d_kv_commit = nullptr;
+    // per sequence
+    int32_t * d_pos0 = nullptr;
+    int32_t * d_tables = nullptr;
+    std::vector<int> h_pos, h_pos_upper;
+    // per step
+    int32_t * d_tokens = nullptr;
+    int32_t * d_parent = nullptr;
+    int32_t * d_depth = nullptr;
+    uint64_t * d_anc = nullptr;
+    float *x = nullptr, *xn = nullptr, *qkv_attn = nullptr, *attn_out = nullptr, *gdn_out = nullptr;
+    float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
+    int n_proj = 0, n_qkv = 0;
+    ArgmaxScratch argmax{};
+    AcceptOut acc{};
+    float * attn_partial = nullptr;
+    size_t attn_partial_floats = 0;
+    GemmScratch gemm;
+    // staged step
+    int st_seq0 = 0, st_batch = 0, st_nodes = 0;
+    uint32_t st_mode = 0;
+    bool staged = false, launched = false;
+    uint32_t launches = 0;
+};
+
+namespace {
+
+void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, float * out, int ldo, int rows, uint32_t flags) {
+    GemmArgs a;
+    a.w = w.ptr;
+    a.w_readable = w.bytes + 256;
+    a.w_dtype = w.dtype;
+    a.x = x;
+    a.x_dtype = YUUKA_DTYPE_F32;
+    a.ldx = ldx;
+    a.out = out;
+    a.ldo = ldo;
+    a.rows = rows;
+    a.n_out = (int)w.rows;
+    a.n_in = (int)w.cols;
+    a.path = YUUKA_GEMM_PATH_AUTO;
+    a.flags = flags;
+    a.scratch = &s->gemm;
+    s->launches += launch_gemm_quant(s->model->dev, s->stream.s, a);
+}
+
+void reserve_gemm(yuuka_session * s, const Tensor & w, int rows) {
+    if (w.present()) gemm_scratch_reserve(s->model->dev, s->gemm, w.dtype, rows, (int)w.rows, (int)w.cols);
+}
+
+enum LogitRows { LOGITS_NONE, LOGITS_LAST, LOGITS_ALL };
+
+// Enqueues one step over sequences [seq0, seq0+batch) with `nodes` rows each.
+void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, LogitRows logit_rows, int max_total) {
+    yuuka_model * m = s->model;
+    const yuuka_model_config & c = m->cfg;
+    cudaStream_t st = s->stream.s;
+    const int R = batch * nodes, H = c.hidden;
+    RowMeta rows{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos0 + seq0, batch, nodes};
+    const int K1 = c.conv_kernel - 1;
+    const int conv_dim = m->conv_dim(), inner = c.inner_size, rank = c.time_step_rank, S = c.state_size;
+    const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
+
+    launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
+    s->launches++;
+    for (int i = 0; i < c.block_count; i++) {
+        const LayerW & L = m->layers[i];
+        LayerState & LS = s->layers[i];
+        launch_rmsnorm(st, s->xn, H, s->x, H, L.attn_norm, H, R, c.rms_eps);
+        s->launches++;
+        if (m->recurrent(i)) {
+            const int np = s->n_proj;
+            if (L.proj.present()) {
+                gemm(s, L.proj, s->xn, H, LS.proj, np, R, 0);
+            } else {
+                gemm(s, L.qkv, s->xn, H, LS.proj, np, R, 0);
+                gemm(s, L.gate, s->xn, H, LS.proj + conv_dim, np, R, 0);
+                gemm(s, L.beta, s->xn, H, LS.proj + conv_dim + inner, np, R, 0);
+                gemm(s, L.alpha, s->xn, H, LS.proj + conv_dim + inner + rank, np, R, 0);
+            }
+            GdnArgs g;
+            g.proj = LS.proj;
+            g.ldp = np;
+            g.conv_w = L.conv;
+            g.dt = L.dt;
+            g.a = L.a;
+            g.conv_state = LS.conv_state + (int64_t)seq0 * conv_dim * K1;
+            g.state = LS.state + (int64_t)seq0 * rank * S * S;
+            g.out = s->gdn_out;
+            g.khat = LS.khat;
+            g.dlog = LS.dlog;
+            g.decay = LS.decay;
+            g.groups = c.group_count;
+            g.rank = rank;
+            g.S = S;
+            g.kernel = c.conv_kernel;
+            g.eps = c.rms_eps;
+            launch_gdn_scan(st, g, rows);
+            launch_gdn_norm_gate(st, s->gdn_out, inner, LS.proj + conv_dim, np, L.ssm_norm, rank, S, R, c.rms_eps);
+            s->launches += 2;
+            gemm(s, L.out, s->gdn_out, inner, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+        } else {
+            const int nq = s->n_qkv;
+            float * qb = s->qkv_attn;
+            float * kb = qb + q_dim;
+            float * vb = kb + kv_dim;
+            if (L.qk.present()) {
+                gemm(s, L.qk, s->xn, H, qb, nq, R, 0);
+                if (!L.qk_has_v) gemm(s, L.v, s->xn, H, vb, nq, R, 0);
+            } else {
+                gemm(s, L.q, s->xn, H, qb, nq, R, 0);
+                gemm(s, L.k, s->xn, H, kb, nq, R, 0);
+                gemm(s, L.v, s->xn, H, vb, nq, R, 0);
+            }
+            KvPool pool;
+            pool.k = LS.k;
+            pool.v = LS.v;
+            pool.format = s->cfg.kv_format;
+            pool.block_size = s->cfg.block_size;
+            pool.pool_blocks = s->cfg.pool_blocks;
+            pool.kv_dim = kv_dim;
+            pool.row_bytes = s->kv_row_bytes;
+            pool.tables = s->d_tables + (int64_t)seq0 * s->table_stride;
+            pool.table_stride = s->table_stride;
+            launch_attn_prep(st, qb, nq, kb, nq, vb, nq, L.q_norm, L.k_norm, c.heads, c.kv_heads, c.head_dim, c.rope_dim,
+                             c.rope_freq_base, c.rms_eps, rows, pool);
+            s->launches++;
+            AttnScratch sc;
+            const int G = c.heads / c.kv_heads;
+            const int qtiles = (G * nodes + 39) / 40;
+            const int base = c.kv_heads * qtiles * batch;
+            int splits = (2 * m->dev->sm_count + base - 1) / base;
+            int max_splits = (max_total + 31) / 32;
+            if (splits > max_splits) splits = max_splits;
+            if (splits < 1) splits = 1;
+            sc.key_split = (((max_total + splits - 1) / splits + 31) / 32) * 32;
+            sc.splits = (max_total + sc.key_split - 1) / sc.key_split;
+            sc.partial = s->attn_partial;
+            YK_REQUIRE(attention_scratch_floats(R, c.heads, c.head_dim, sc.splits) <= s->attn_partial_floats,
+                       YUUKA_ERR_INTERNAL, "attention scratch is too small");
+            s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
+                                            max_total, sc);
+            gemm(s, L.o, s->attn_out, o_dim, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+        }
+        // forwardFFN (model/qwen35/forward.go:295-315)
+        launch_rmsnorm(st, s->xn, H, s->x, H, L.post_norm, H, R, c.rms_eps);
+        s->launches++;
+        if (L.gate_up.present()) {
+            gemm(s, L.gate_up, s->xn, H, s->gate_up, 2 * F, R, 0);
+        } else {
+            gemm(s, L.ffn_gate, s->xn, H, s->gate_up, 2 * F, R, 0);
+            gemm(s, L.ffn_up, s->xn, H, s->gate_up + F, 2 * F, R, 0);
+        }
+        launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R);
+        s->launches++;
+        gemm(s, L.ffn_down, s->act, F, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+    }
+    // tail: final norm + LM head over the wanted rows (forward.go:147-151)
+    if (logit_rows == LOGITS_ALL) {
+        launch_rmsnorm(st, s->xn, H, s->x, H, m->output_norm, H, R, c.rms_eps);
+        s->launches++;
+        gemm(s, m->output, s->xn, H, s->logits, c.vocab, R, 0);
+    } else if (logit_rows == LOGITS_LAST) {
+        // batch == 1: only the last row
+        launch_rmsnorm(st, s->xn, H, s->x + (int64_t)(R - 1) * H, H, m->output_norm, H, 1, c.rms_eps);
+        s->launches++;
+        gemm(s, m->output, s->xn, H, s->logits + (int64_t)(R - 1) * c.vocab, c.vocab, 1, 0);
+    }
+    // acceptance + commit
+    if (mode == YUUKA_ACCEPT_NONE) return;
+    if (mode == YUUKA_ACCEPT_GREEDY) {
+        s->launches += launch_accept_greedy(st, s->logits, c.vocab, rows, s->argmax, s->acc);
+    } else {
+        launch_accept_all(st, rows, s->acc);  // forced commit of a chain
+        s->launches++;
+    }
+    if (!s->gdn_layers.empty()) {
+        launch_gdn_commit(st, s->d_gdn_commit, (int)s->gdn_layers.size(), c.group_count, rank, S, c.conv_kernel, conv_dim,
+                          seq0, rows, s->acc);
+        s->launches++;
+    }
+    if (!s->attn_layers.empty()) {
+        KvPool geom{};
+        geom.block_size = s->cfg.block_size;
+        geom.row_bytes = s->kv_row_bytes;
+        geom.tables = s->d_tables + (int64_t)seq0 * s->table_stride;
+        geom.table_stride = s->table_stride;
+        launch_kv_commit(st, s->d_kv_commit, (int)s->attn_layers.size(), geom, rows, s->acc);
+        s->launches++;
+    }
+    launch_advance_positions(st, s->d_pos0 + seq0, s->acc, batch);
+    s->launches++;
+}
+
+}  // namespace
+
+// ===========================================================================
+// session ABI
+
+namespace {
+
+void check_seq(const yuuka_session * s, int seq) {
+    YK_REQUIRE(s, YUUKA_ERR_INVALID_ARGUMENT, "null session");
+    YK_REQUIRE(seq >= 0 && seq < s->cfg.max_batch, YUUKA_ERR_INVALID_ARGUMENT, "sequence %d is outside 0..%d", seq,
+               s->cfg.max_batch - 1);
+}
+
+void sync_and_check(yuuka_session * s) {
+    YK_CUDA(cudaStreamSynchronize(s->stream.s));
+    int err = read_device_error(s->model->dev);
+    YK_REQUIRE(err == 0, YUUKA_ERR_DEVICE, "a bounded wait inside a kernel expired (code %d); results are invalid", err);
+}
+
+// Uploads row metadata of a step: tokens, parents, depths, ancestor masks.
+void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t * tokens, const int32_t * parent) {
+    const int vocab = s->model->cfg.vocab;
+    const int R = batch * nodes;
+    std::vector<int32_t> par(R), dep(R);
+    std::vector<uint64_t> anc(R);
+    for (int b = 0; b < batch; b++) {
+        for (int i = 0; i < nodes; i++) {
+            const int r = b * nodes + i;
+            YK_REQUIRE(tokens[r] >= 0 && tokens[r] < vocab, YUUKA_ERR_INVALID_ARGUMENT, "token id %d is out of range",
+                       tokens[r]);
+            int p = parent ? parent[r] : i - 1;
+            YK_REQUIRE((i == 0 && p == -1) || (i > 0 && p >= 0 && p < i), YUUKA_ERR_INVALID_ARGUMENT,
+                       "parent[%d][%d] = %d is not a preceding row", b, i, p);
+            par[r] = p;
+            dep[r] = i == 0 ? 0 : dep[b * nodes + p] + 1;
+            anc[r] = (i == 0 ? 0ull : anc[b * nodes + p]) | (1ull << i);
+        }
+        YK_REQUIRE(s->h_pos_upper[seq0 + b] + nodes <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
+                   "token sequence of %d exceeds remaining context %d", nodes,
+                   s->cfg.capacity - s->h_pos_upper[seq0 + b]);
+    }
+    cudaStream_t st = s->stream.s;
+    YK_CUDA(cudaMemcpyAsync(s->d_tokens, tokens, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
+    YK_CUDA(cudaMemcpyAsync(s->d_parent, par.data(), sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
+    YK_CUDA(cudaMemcpyAsync(s->d_depth, dep.data(), sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
+    YK_CUDA(cudaMemcpyAsync(s->d_anc, anc.data(), sizeof(uint64_t) * R, cudaMemcpyHostToDevice, st));
+    YK_CUDA(cudaStreamSynchronize(st));  // the host vectors go out of scope
+}
+
+int max_total_keys(const yuuka_session * s, int seq0, int batch, int nodes) {
+    int mx = 0;
+    for (int b = 0; b < batch; b++) mx = s->h_pos_upper[seq0 + b] > mx ? s->h_pos_upper[seq0 + b] : mx;
+    return mx + nodes;
+}
+
+// Runs tokens of one sequence as committed chain chunks (Forward / PrefillLogits).
+void run_chain(yuuka_session * s, int seq, const int32_t * tokens, int n, float * all_logits, float * last_logits) {
+    check_seq(s, seq);
+    YK_REQUIRE(tokens && n > 0, YUUKA_ERR_INVALID_ARGUMENT, "empty token sequence");
+    YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "a launched verify step has not been fetched");
+    YK_REQUIRE(s->h_pos[seq] + n <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
+               "token sequence of %d exceeds remaining context %d", n, s->cfg.capacity - s->h_pos[seq]);
+    YK_REQUIRE(!(all_logits || last_logits) || s->logits, YUUKA_ERR_INVALID_ARGUMENT,
+               "the session was created without want_logits");
+    set_device(s->model->dev);
+    const int V = s->model->cfg.vocab;
+    for (int done = 0; done < n;) {
+        const int chunk = n - done < s->cfg.max_nodes ? n - done : s->cfg.max_nodes;
+        const bool last = done + chunk == n;
+        stage_rows(s, seq, 1, chunk, tokens + done, nullptr);
+        LogitRows lr = all_logits ? LOGITS_ALL : (last && last_logits ? LOGITS_LAST : LOGITS_NONE);
+        s->launches = 0;
+        run_step(s, seq, 1, chunk, 3u /* forced commit */, lr, s->h_pos[seq] + chunk);
+        sync_and_check(s);
+        if (all_logits)
+            YK_CUDA(cudaMemcpy(all_logits + (int64_t)done * V, s->logits, sizeof(float) * (size_t)chunk * V,
+                               cudaMemcpyDeviceToHost));
+        if (last && last_logits)
+            YK_CUDA(cudaMemcpy(last_logits, s->logits + (int64_t)(chunk - 1) * V, sizeof(float) * (size_t)V,
+                               cudaMemcpyDeviceToHost));
+        s->h_pos[seq] += chunk;
+        s->h_pos_upper[seq] = s->h_pos[seq];
+        done += chunk;
+    }
+}
+
+void validate_batch(const yuuka_session * s, const yuuka_verify_batch * b) {
+    YK_REQUIRE(s && b, YUUKA_ERR_INVALID_ARGUMENT, "verify: null argument");
+    YK_REQUIRE(b->batch > 0 && b->batch <= s->cfg.max_batch, YUUKA_ERR_INVALID_ARGUMENT,
+               "verify: batch %d is outside 1..%d", b->batch, s->cfg.max_batch);
+    YK_REQUIRE(b->nodes > 0 && b->nodes <= s->cfg.max_nodes, YUUKA_ERR_INVALID_ARGUMENT,
+               "verify: %d rows per sequence is outside 1..%d", b->nodes, s->cfg.max_nodes);
+    YK_REQUIRE(b->tokens, YUUKA_ERR_INVALID_ARGUMENT, "verify: tokens is null");
+    YK_REQUIRE(b->mode == YUUKA_ACCEPT_GREEDY || b->mode == YUUKA_ACCEPT_NONE || b->mode == YUUKA_ACCEPT_REJECTION,
+               YUUKA_ERR_INVALID_ARGUMENT, "verify: unknown acceptance mode %u", b->mode);
+    YK_REQUIRE(b->mode != YUUKA_ACCEPT_REJECTION, YUUKA_ERR_UNSUPPORTED,
+               "verify: rejection-sampling acceptance is not available in this build");
+    YK_REQUIRE(s->logits, YUUKA_ERR_INVALID_ARGUMENT, "verify: the session has no logits buffer");
+}
+
+}  // namespace
+
+extern "C" {
+
+yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_config * cfg, yuuka_session ** out) {
+    return guard([&] {
+        YK_REQUIRE(model && cfg && out, YUUKA_ERR_INVALID_ARGUMENT, "session_create: null argument");
+        *out = nullptr;
+        YK_REQUIRE(model->finalized, YUUKA_ERR_INVALID_ARGUMENT, "session_create: model is not finalized");
+        const yuuka_model_config & c = model->cfg;
+        yuuka_session_config sc = *cfg;
+        YK_REQUIRE(sc.max_batch > 0 && sc.max_batch <= 4096, YUUKA_ERR_INVALID_ARGUMENT, "invalid max_batch %d", sc.max_batch);
+        YK_REQUIRE(sc.max_nodes > 0 && sc.max_nodes <= 64, YUUKA_ERR_INVALID_ARGUMENT, "max_nodes %d is outside 1..64",
+                   sc.max_nodes);
+        YK_REQUIRE(sc.capacity > 0, YUUKA_ERR_INVALID_ARGUMENT, "context capacity must be positive");
+        YK_REQUIRE(sc.capacity <= c.context_length, YUUKA_ERR_INVALID_ARGUMENT,
+                   "context capacity %d exceeds model limit %d", sc.capacity, c.context_length);
+        if (sc.block_size <= 0) sc.block_size = sc.capacity < 16 ? sc.capacity : 16;  // state.go:68-72
+        const int per_seq = (sc.capacity + sc.block_size - 1) / sc.block_size;
+        if (sc.pool_blocks <= 0) sc.pool_blocks = per_seq * sc.max_batch;
+        YK_REQUIRE(sc.kv_format == YUUKA_KV_F32 || sc.kv_format == YUUKA_KV_F16 || sc.kv_format == YUUKA_KV_Q8_0,
+                   YUUKA_ERR_INVALID_ARGUMENT, "unknown KV format %d", sc.kv_format);
+        set_device(model->dev);
+        auto * s = new yuuka_session();
+        try {
+            s->model = model;
+            s->cfg = sc;
+            s->stream.dev = model->dev;
+            YK_CUDA(cudaStreamCreateWithFlags(&s->stream.s, cudaStreamNonBlocking));
+            const int kv_dim = model->kv_dim();
+            s->kv_row_bytes = sc.kv_format == YUUKA_KV_F32 ? kv_dim * 4 : (sc.kv_format == YUUKA_KV_F16 ? kv_dim * 2 : (kv_dim + 31) / 32 * 34);
+            s->table_stride = per_seq;
+            const int B = sc.max_batch, N = sc.max_nodes, R = B * N;
+            const int conv_dim = model->conv_dim(), K1 = c.conv_kernel - 1, S = c.state_size, rank = c.time_step_rank;
+            s->conv_count = (int64_t)conv_dim * K1;
+            s->s_count = (int64_t)rank * S * S;
+            s->n_proj = conv_dim + c.inner_size + 2 * rank;
+            s->n_qkv = model->q_dim() + 2 * kv_dim;
+            s->layers.resize(c.block_count);
+            const size_t pool_bytes = (size_t)sc.pool_blocks * sc.block_size * s->kv_row_bytes;
+            std::vector<GdnLayerCommit> gc;
+            std::vector<KvLayerCommit> kc;
+            for (int i = 0; i < c.block_count; i++) {
+                LayerState & LS = s->layers[i];
+                if (model->recurrent(i)) {
+                    LS.conv_state = dalloc<float>((size_t)B * s->conv_count, s->owned);
+                    LS.state = dalloc<float>((size_t)B * s->s_count, s->owned);
+                    LS.proj = dalloc<float>((size_t)R * s->n_proj, s->owned);
+                    LS.khat = dalloc<float>((size_t)R * c.group_count * S, s->owned);
+                    LS.dlog = dalloc<float>((size_t)R * c.inner_size, s->owned);
+                    LS.decay = dalloc<float>((size_t)R * rank, s->owned);
+                    s->gdn_layers.push_back(i);
+                    gc.push_back(GdnLayerCommit{LS.proj, s->n_proj, LS.khat, LS.dlog, LS.decay, LS.conv_state, LS.state});
+                } else {
+                    LS.k = dalloc<uint8_t>(pool_bytes, s->owned);
+                    LS.v = dalloc<uint8_t>(pool_bytes, s->owned);
+                    s->attn_layers.push_back(i);
+                    kc.push_back(KvLayerCommit{LS.k, LS.v});
+                }
+            }
+            s->d_gdn_commit = dalloc<GdnLayerCommit>(gc.size(), s->owned);
+            s->d_kv_commit = dalloc<KvLayerCommit>(kc.size(), s->owned);
+            if (!gc.empty()) YK_CUDA(cudaMemcpy(s->d_gdn_commit, gc.data(), gc.size() * sizeof(GdnLayerCommit), cudaMemcpyHostToDevice));
+            if (!kc.empty()) YK_CUDA(cudaMemcpy(s->d_kv_commit, kc.data(), kc.size() * sizeof(KvLayerCommit), cudaMemcpyHostToDevice));
+            s->d_pos0 = dalloc<int32_t>(B, s->owned);
+            s->d_tables = dalloc<int32_t>((size_t)B * per_seq, s->owned);
+            std::vector<int32_t> ident((size_t)B * per_seq);
+            for (int b = 0; b < B; b++)
+                for (int j = 0; j < per_seq; j++) ident[(size_t)b * per_seq + j] = (b * per_seq + j) % sc.pool_blocks;
+            YK_CUDA(cudaMemcpy(s->d_tables, ident.data(), ident.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+            s->h_pos.assign(B, 0);
+            s->h_pos_upper.assign(B, 0);
+            s->d_tokens = dalloc<int32_t>(R, s->owned);
+            s->d_parent = dalloc<int32_t>(R, s->owned);
+            s->d_depth = dalloc<int32_t>(R, s->owned);
+            s->d_anc = dalloc<uint64_t>(R, s->owned);
+            const int H = c.hidden;
+            s->x = dalloc<float>((size_t)R * H, s->owned);
+            s->xn = dalloc<float>((size_t)R * H, s->owned);
+            s->qkv_attn = dalloc<float>((size_t)R * s->n_qkv, s->owned);
+            s->attn_out = dalloc<float>((size_t)R * model->o_dim(), s->owned);
+            s->gdn_out = dalloc<float>((size_t)R * c.inner_size, s->owned);
+            s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
+            s->act = dalloc<float>((size_t)R * c.ffn, s->owned);
+            if (sc.want_logits) s->logits = dalloc<float>((size_t)R * c.vocab, s->owned);
+            s->argmax.chunks = argmax_chunks(c.vocab);
+            s->argmax.val = dalloc<float>((size_t)R * s->argmax.chunks, s->owned);
+            s->argmax.idx = dalloc<int32_t>((size_t)R * s->argmax.chunks, s->owned);
+            s->acc.accepted = dalloc<int32_t>(B, s->owned);
+            s->acc.path = dalloc<int32_t>(R, s->owned);
+            s->acc.emitted = dalloc<int32_t>(R, s->owned);
+            s->attn_partial_floats = (size_t)N * c.heads * (2 * model->dev->sm_count / c.kv_heads + 1 + B) * (c.head_dim + 2);
+            s->attn_partial = dalloc<float>(s->attn_partial_floats, s->owned, false);
+            // split-K scratch for every matrix shape of the step
+            for (int rows : {R < 32 ? R : 32, 1}) {
+                for (const LayerW & L : model->layers) {
+                    for (const Tensor * t : {&L.q, &L.k, &L.v, &L.o, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.ffn_gate,
+                                             &L.ffn_up, &L.ffn_down, &L.proj, &L.qk, &L.gate_up})
+                        reserve_gemm(s, *t, rows);
+                }
+                reserve_gemm(s, model->output, rows);
+            }
+            for (int r = 1; r < R && r < 32; r++) reserve_gemm(s, model->layers[0].ffn_down, r);
+        } catch (...) {
+            yuuka_session_destroy(s);
+            throw;
+        }
+        *out = s;
+    });
+}
+
+void yuuka_session_destroy(yuuka_session * s) {
+    if (!s) return;
+    cudaSetDevice(s->model->dev->index);
+    if (s->stream.s) {
+        cudaStreamSynchronize(s->stream.s);
+        cudaStreamDestroy(s->stream.s);
+    }
+    for (void * p : s->owned) cudaFree(p);
+    gemm_scratch_free(s->gemm);
+    delete s;
+}
+
+yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const int32_t * blocks, int32_t count) {
+    return guard([&] {
+        check_seq(s, seq);
+        YK_REQUIRE(blocks && count >= s->table_stride, YUUKA_ERR_INVALID_ARGUMENT,
+                   "block table maps %d positions, need %d", count * s->cfg.block_size, s->cfg.capacity);
+        for (int i = 0; i < s->table_stride; i++)
+            YK_REQUIRE(blocks[i] >= 0 && blocks[i] < s->cfg.pool_blocks, YUUKA_ERR_INVALID_ARGUMENT,
+                       "block %d is outside the KV pool", blocks[i]);
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        YK_CUDA(cudaMemcpy(s->d_tables + (int64_t)seq * s->table_stride, blocks, sizeof(int32_t) * s->table_stride,
+                           cudaMemcpyHostToDevice));
+    });
+}
+
+yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq) {
+    return guard([&] {
+        check_seq(s, seq);
+        set_device(s->model->dev);
+        cudaStream_t st = s->stream.s;
+        for (int i : s->gdn_layers) {
+            YK_CUDA(cudaMemsetAsync(s->layers[i].conv_state + (int64_t)seq * s->conv_count, 0, s->conv_count * 4, st));
+            YK_CUDA(cudaMemsetAsync(s->layers[i].state + (int64_t)seq * s->s_count, 0, s->s_count * 4, st));
+        }
+        YK_CUDA(cudaMemsetAsync(s->d_pos0 + seq, 0, sizeof(int32_t), st));
+        YK_CUDA(cudaStreamSynchronize(st));
+        s->h_pos[seq] = s->h_pos_upper[seq] = 0;
+    });
+}
+
+yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t position) {
+    return guard([&] {
+        check_seq(s, seq);
+        YK_REQUIRE(position >= 0 && position <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
+                   "position %d exceeds capacity %d", position, s->cfg.capacity);
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        YK_CUDA(cudaMemcpy(s->d_pos0 + seq, &position, sizeof(int32_t), cudaMemcpyHostToDevice));
+        s->h_pos[seq] = s->h_pos_upper[seq] = position;
+    });
+}
+
+yuuka_status yuuka_session_position(yuuka_session * s, int32_t seq, int32_t * position) {
+    return guard([&] {
+        check_seq(s, seq);
+        YK_REQUIRE(position, YUUKA_ERR_INVALID_ARGUMENT, "session_position: null output");
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        YK_CUDA(cudaMemcpy(position, s->d_pos0 + seq, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    });
+}
+
+uint64_t yuuka_session_snapshot_bytes(const yuuka_session * s) {
+    return s ? (uint64_t)s->gdn_layers.size() * (uint64_t)(s->conv_count + s->s_count) * 4 : 0;
+}
+
+yuuka_status yuuka_session_snapshot(yuuka_session * s, int32_t seq, void * dst, uint64_t bytes) {
+    return guard([&] {
+        check_seq(s, seq);
+        YK_REQUIRE(dst && bytes == yuuka_session_snapshot_bytes(s), YUUKA_ERR_INVALID_ARGUMENT,
+                   "state snapshot is %llu bytes, want %llu", (unsigned long long)bytes,
+                   (unsigned long long)yuuka_session_snapshot_bytes(s));
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        uint8_t * o = (uint8_t *)dst;
+        for (int i : s->gdn_layers) {
+            YK_CUDA(cudaMemcpy(o, s->layers[i].conv_state + (int64_t)seq * s->conv_count, s->conv_count * 4, cudaMemcpyDeviceToHost));
+            o += s->conv_count * 4;
+            YK_CUDA(cudaMemcpy(o, s->layers[i].state + (int64_t)seq * s->s_count, s->s_count * 4, cudaMemcpyDeviceToHost));
+            o += s->s_count * 4;
+        }
+    });
+}
+
+yuuka_status yuuka_session_restore(yuuka_session * s, int32_t seq, const void * src, uint64_t bytes) {
+    return guard([&] {
+        check_seq(s, seq);
+        YK_REQUIRE(src && bytes == yuuka_session_snapshot_bytes(s), YUUKA_ERR_INVALID_ARGUMENT,
+                   "state snapshot is %llu bytes, want %llu", (unsigned long long)bytes,
+                   (unsigned long long)yuuka_session_snapshot_bytes(s));
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        const uint8_t * o = (const uint8_t *)src;
+        for (int i : s->gdn_layers) {
+            YK_CUDA(cudaMemcpy(s->layers[i].conv_state + (int64_t)seq * s->conv_count, o, s->conv_count * 4, cudaMemcpyHostToDevice));
+            o += s->conv_count * 4;
+            YK_CUDA(cudaMemcpy(s->layers[i].state + (int64_t)seq * s->s_count, o, s->s_count * 4, cudaMemcpyHostToDevice));
+            o += s->s_count * 4;
+        }
+    });
+}
+
+yuuka_status yuuka_session_prefill_logits(yuuka_session * s, int32_t seq, const int32_t * tokens, int32_t n,
+                                          float * logits) {
+    return guard([&] { run_chain(s, seq, tokens, n, logits, nullptr); });
+}
+
+yuuka_status yuuka_session_forward(yuuka_session * s, int32_t seq, const int32_t * tokens, int32_t n,
+                                   float * last_logits) {
+    return guard([&] { run_chain(s, seq, tokens, n, nullptr, last_logits); });
+}
+
+yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b) {
+    return guard([&] {
+        validate_batch(s, b);
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_stage: the previous step has not been fetched");
+        set_device(s->model->dev);
+        stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent);
+        s->st_seq0 = 0;
+        s->st_batch = b->batch;
+        s->st_nodes = b->nodes;
+        s->st_mode = b->mode;
+        s->staged = true;
+    });
+}
+
+yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
+    return guard([&] {
+        YK_REQUIRE(s && s->staged, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: no staged step");
+        set_device(s->model->dev);
+        s->launches = 0;
+        run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL,
+                 max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes));
+        if (s->st_mode != YUUKA_ACCEPT_NONE)
+            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
+        s->launched = true;
+        if (completion) YK_CUDA(cudaEventRecord(completion->e, s->stream.s));
+    });
+}
+
+yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * b) {
+    return guard([&] {
+        YK_REQUIRE(s && b && s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_fetch: no launched step");
+        YK_REQUIRE(b->batch == s->st_batch && b->nodes == s->st_nodes, YUUKA_ERR_INVALID_ARGUMENT,
+                   "verify_fetch: batch shape differs from the staged step");
+        set_device(s->model->dev);
+        s->launched = false;
+        s->staged = false;
+        sync_and_check(s);
+        const int B = s->st_batch, N = s->st_nodes;
+        std::vector<int32_t> acc(B);
+        if (s->st_mode != YUUKA_ACCEPT_NONE) {
+            YK_CUDA(cudaMemcpy(acc.data(), s->acc.accepted, sizeof(int32_t) * B, cudaMemcpyDeviceToHost));
+            if (b->accepted) memcpy(b->accepted, acc.data(), sizeof(int32_t) * B);
+            if (b->emitted) YK_CUDA(cudaMemcpy(b->emitted, s->acc.emitted, sizeof(int32_t) * B * N, cudaMemcpyDeviceToHost));
+            if (b->path) YK_CUDA(cudaMemcpy(b->path, s->acc.path, sizeof(int32_t) * B * N, cudaMemcpyDeviceToHost));
+            for (int i = 0; i < B; i++) {
+                s->h_pos[s->st_seq0 + i] += acc[i] + 1;
+                s->h_pos_upper[s->st_seq0 + i] = s->h_pos[s->st_seq0 + i];
+            }
+        }
+        if (b->logits)
+            YK_CUDA(cudaMemcpy(b->logits, s->logits, sizeof(float) * (size_t)B * N * s->model->cfg.vocab, cudaMemcpyDeviceToHost));
+    });
+}
+
+yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_batch * b) {
+    yuuka_status st = yuuka_verify_stage(s, b);
+    if (st != YUUKA_OK) return st;
+    st = yuuka_verify_launch(s, nullptr);
+    if (st != YUUKA_OK) {
+        if (s) s->staged = false;
+        return st;
+    }
+    return yuuka_verify_fetch(s, b);
+}
+
+yuuka_stream * yuuka_session_stream(yuuka_session * s) { return s ? &s->stream : nullptr; }
+
+uint32_t yuuka_session_last_launch_count(const yuuka_session * s) { return s ? s->launches : 0; }
+
+}  // extern "C"

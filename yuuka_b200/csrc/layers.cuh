@@ -1,0 +1,116 @@
+// Host interface of the non-GEMM kernels of the verify step.
+#pragma once
+
+#include "common.cuh"
+
+namespace yk {
+
+// Per-step row metadata, all device pointers. Row r = seq * nodes + node.
+struct RowMeta {
+    const int32_t * tokens;    // [rows]
+    const int32_t * parent;    // [rows] node index of the preceding row within the sequence, -1 for node 0
+    const int32_t * depth;     // [rows] number of ancestors
+    const uint64_t * anc_mask; // [rows] bit j set iff node j is the row itself or one of its ancestors
+    const int32_t * pos0;      // [batch] committed positions of each sequence
+    int batch, nodes;
+};
+
+struct KvPool {
+    uint8_t * k;
+    uint8_t * v;
+    int format;        // yuuka_kv_format
+    int block_size;
+    int pool_blocks;
+    int kv_dim;
+    int row_bytes;
+    const int32_t * tables;  // [batch][table_stride]
+    int table_stride;
+};
+
+// x[r][:] = dequantized row tokens[r] of the embedding table (forward.go:120-129)
+void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden,
+                      int vocab, const int32_t * tokens, int rows);
+// dst[r][:] = src[r][:] * rsqrt(mean(src^2) + eps) * weight (forward.go:460-470)
+void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight,
+                    int cols, int rows, float eps);
+// act[r][i] = silu(gate[r][i]) * up[r][i] (forward.go:307-309)
+void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
+                     int rows);
+// Per-head RMSNorm of q and k, RoPE at pos0 + depth, and the paged KV write of
+// every row at slot pos0 + node (forward.go:172-186, kv_pool.go:117-134).
+void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, const float * v, int ldv,
+                      const float * q_norm, const float * k_norm, int heads, int kv_heads, int head_dim,
+                      int rope_dim, double rope_base, float eps, const RowMeta & rows, const KvPool & pool);
+// Paged attention of every row over the committed positions and the row's own
+// ancestors, split over key ranges, then merged and gated (forward.go:188-220).
+struct AttnScratch {
+    float * partial;   // [rows*heads][splits][head_dim + 2]
+    int splits;
+    int key_split;     // keys per split
+};
+int launch_attention(cudaStream_t s, float * out, int ldo, const float * q, int ldq, int heads, int kv_heads,
+                     int head_dim, const RowMeta & rows, const KvPool & pool, int max_total_keys,
+                     const AttnScratch & scratch);
+size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits);
+
+// Gated DeltaNet over the rows of a step (forward.go:245-287, recurrent.go:56-105).
+struct GdnArgs {
+    const float * proj;      // [rows][ldp]: qkv (conv_dim) | z (inner) | beta (rank) | alpha (rank)
+    int ldp;
+    const float * conv_w;    // [conv_dim][kernel]
+    const float * dt;        // [rank]
+    const float * a;         // [rank]
+    const float * conv_state;  // [batch][conv_dim][kernel-1]
+    const float * state;       // [batch][rank][S][S]
+    float * out;             // [rows][inner] raw per-head outputs
+    float * khat;            // [rows][groups*S] log: normalised keys
+    float * dlog;            // [rows][rank*S]   log: beta * (v - S^T k)
+    float * decay;           // [rows][rank]     log: exp(alpha)
+    int groups, rank, S, kernel;
+    float eps;
+};
+void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
+// out[r][h][:] = rmsnorm(out[r][h][:]) * norm * silu(z[r][h][:]) (recurrent.go:39-50)
+void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
+                          int S, int rows, float eps);
+
+// First-maximum argmax of every logits row (speculative.go:263-271) followed by
+// the greedy tree walk (speculative.go:193-202 generalised to a tree).
+struct AcceptOut {
+    int32_t * accepted;  // [batch]
+    int32_t * path;      // [batch][nodes]
+    int32_t * emitted;   // [batch][nodes]
+};
+struct ArgmaxScratch {
+    float * val;     // [rows][chunks]
+    int32_t * idx;   // [rows][chunks]
+    int chunks;
+};
+int launch_accept_greedy(cudaStream_t s, const float * logits, int vocab, const RowMeta & rows,
+                         const ArgmaxScratch & scratch, const AcceptOut & out);
+// Accept every row of a chain (prefill / forced commit): accepted = nodes-1.
+void launch_accept_all(cudaStream_t s, const RowMeta & rows, const AcceptOut & out);
+int argmax_chunks(int vocab);
+
+// Commit of the accepted path: recurrent state, conv history, KV row moves,
+// positions.
+struct GdnLayerCommit {
+    const float * proj;  // raw qkv rows of the step (first conv_dim columns of proj)
+    int ldp;
+    const float * khat;
+    const float * dlog;
+    const float * decay;
+    float * conv_state;
+    float * state;
+};
+void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_layers, int groups, int rank, int S,
+                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc);
+struct KvLayerCommit {
+    uint8_t * k;
+    uint8_t * v;
+};
+void launch_kv_commit(cudaStream_t s, const KvLayerCommit * layers_dev, int n_layers, const KvPool & geom,
+                      const RowMeta & rows, const AcceptOut & acc);
+void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch);
+
+}  // namespace yk

@@ -1,0 +1,414 @@
+"""ctypes mirror of include/yuuka_cuda.h: what the cgo binding does in Go
+(backend/hip/hip.go in the reference), for Python tests and the benchmark.
+
+Every call goes through libyuuka_cuda.so. There is no fallback: if the library
+is missing or no device answers, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_DEVICE, ERR_ALLOCATION, ERR_INTERNAL = range(6)
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
+KV_F32, KV_F16, KV_Q8_0 = 0, 1, 2
+PATH_AUTO, PATH_FP32, PATH_MMA = 0, 1, 2
+GEMM_ACCUMULATE = 1
+ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
+ABI_VERSION = 1
+
+
+class YuukaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class UnsupportedError(YuukaError):
+    """YUUKA_ERR_UNSUPPORTED, the counterpart of hip.ErrUnsupported."""
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 256), ("arch", C.c_char * 64), ("cuda_version", C.c_char * 64),
+                ("total_memory", C.c_uint64), ("multiprocessors", C.c_uint32), ("clock_mhz", C.c_uint32),
+                ("l2_bytes", C.c_uint32), ("smem_per_block_optin", C.c_uint32), ("pci_domain", C.c_int32),
+                ("pci_bus", C.c_int32), ("pci_device", C.c_int32)]
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [
+        ("block_count", C.c_int32), ("context_length", C.c_int32), ("hidden", C.c_int32),
+        ("ffn", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("rope_dim", C.c_int32), ("rope_freq_base", C.c_double),
+        ("rms_eps", C.c_float), ("vocab", C.c_int32), ("conv_kernel", C.c_int32),
+        ("state_size", C.c_int32), ("group_count", C.c_int32), ("time_step_rank", C.c_int32),
+        ("inner_size", C.c_int32), ("full_attention_interval", C.c_int32),
+        ("expert_count", C.c_int32), ("expert_used", C.c_int32), ("expert_ffn", C.c_int32),
+        ("shared_ffn", C.c_int32),
+    ]
+
+
+class SessionConfig(C.Structure):
+    _fields_ = [("max_batch", C.c_int32), ("max_nodes", C.c_int32), ("capacity", C.c_int32),
+                ("block_size", C.c_int32), ("pool_blocks", C.c_int32), ("kv_format", C.c_int32),
+                ("want_logits", C.c_int32)]
+
+
+class VerifyBatch(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("nodes", C.c_int32), ("tokens", C.c_void_p),
+                ("parent", C.c_void_p), ("mode", C.c_uint32), ("temperature", C.c_float),
+                ("draft_probs", C.c_void_p), ("uniforms", C.c_void_p), ("accepted", C.c_void_p),
+                ("emitted", C.c_void_p), ("path", C.c_void_p), ("logits", C.c_void_p)]
+
+
+# name -> (restype, argtypes); the exported symbol list the ABI test checks
+_vp, _i32, _u32, _u64, _f32 = C.c_void_p, C.c_int32, C.c_uint32, C.c_uint64, C.c_float
+SIGNATURES = {
+    "yuuka_abi_version": (_u32, []),
+    "yuuka_last_error": (C.c_char_p, []),
+    "yuuka_device_open": (_i32, [_i32, _vp]),
+    "yuuka_device_close": (None, [_vp]),
+    "yuuka_device_info_get": (_i32, [_vp, _vp]),
+    "yuuka_buffer_alloc": (_i32, [_vp, _u64, _vp]),
+    "yuuka_buffer_free": (None, [_vp]),
+    "yuuka_buffer_size": (_u64, [_vp]),
+    "yuuka_buffer_ptr": (_vp, [_vp]),
+    "yuuka_stream_create": (_i32, [_vp, _vp]),
+    "yuuka_stream_destroy": (None, [_vp]),
+    "yuuka_stream_synchronize": (_i32, [_vp]),
+    "yuuka_event_create": (_i32, [_vp, _vp]),
+    "yuuka_event_destroy": (None, [_vp]),
+    "yuuka_event_record": (_i32, [_vp, _vp]),
+    "yuuka_event_wait": (_i32, [_vp]),
+    "yuuka_event_elapsed_ms": (_i32, [_vp, _vp, _vp]),
+    "yuuka_memcpy_h2d": (_i32, [_vp, _vp, _u64]),
+    "yuuka_memcpy_h2d_at": (_i32, [_vp, _u64, _vp, _u64]),
+    "yuuka_memcpy_d2h": (_i32, [_vp, _vp, _u64]),
+    "yuuka_memcpy_d2h_at": (_i32, [_vp, _vp, _u64, _u64]),
+    "yuuka_memset": (_i32, [_vp, _vp, _i32, _u64]),
+    "yuuka_buffer_copy": (_i32, [_vp, _vp, _u64, _vp, _u64, _u64, _vp]),
+    "yuuka_gemm_quant": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
+                                _u32, _u32, _vp]),
+    "yuuka_model_create": (_i32, [_vp, _vp, _vp]),
+    "yuuka_model_destroy": (None, [_vp]),
+    "yuuka_model_set_tensor": (_i32, [_vp, C.c_char_p, _u32, _vp, _u64, _u64]),
+    "yuuka_model_finalize": (_i32, [_vp]),
+    "yuuka_model_weight_bytes": (_u64, [_vp]),
+    "yuuka_session_create": (_i32, [_vp, _vp, _vp]),
+    "yuuka_session_destroy": (None, [_vp]),
+    "yuuka_session_set_block_table": (_i32, [_vp, _i32, _vp, _i32]),
+    "yuuka_session_reset": (_i32, [_vp, _i32]),
+    "yuuka_session_set_position": (_i32, [_vp, _i32, _i32]),
+    "yuuka_session_position": (_i32, [_vp, _i32, _vp]),
+    "yuuka_session_snapshot_bytes": (_u64, [_vp]),
+    "yuuka_session_snapshot": (_i32, [_vp, _i32, _vp, _u64]),
+    "yuuka_session_restore": (_i32, [_vp, _i32, _vp, _u64]),
+    "yuuka_session_prefill_logits": (_i32, [_vp, _i32, _vp, _i32, _vp]),
+    "yuuka_session_forward": (_i32, [_vp, _i32, _vp, _i32, _vp]),
+    "yuuka_verify_step": (_i32, [_vp, _vp]),
+    "yuuka_verify_stage": (_i32, [_vp, _vp]),
+    "yuuka_verify_launch": (_i32, [_vp, _vp]),
+    "yuuka_verify_fetch": (_i32, [_vp, _vp]),
+    "yuuka_session_stream": (_vp, [_vp]),
+    "yuuka_session_last_launch_count": (_u32, [_vp]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.CUDA_LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            path = _build.build_cuda()
+        L = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        if L.yuuka_abi_version() != ABI_VERSION:
+            raise RuntimeError(f"libyuuka_cuda ABI {L.yuuka_abi_version()} != binding ABI {ABI_VERSION}")
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status == OK:
+        return
+    msg = lib().yuuka_last_error().decode(errors="replace")
+    if status == ERR_UNSUPPORTED:
+        raise UnsupportedError(status, msg)
+    raise YuukaError(status, msg)
+
+
+class Device:
+    def __init__(self, index: int = 0):
+        self.h = C.c_void_p()
+        check(lib().yuuka_device_open(index, C.byref(self.h)))
+        self.index = index
+
+    def info(self) -> DeviceInfo:
+        info = DeviceInfo()
+        check(lib().yuuka_device_info_get(self.h, C.byref(info)))
+        return info
+
+    def alloc(self, nbytes: int) -> "Buffer":
+        return Buffer(self, nbytes)
+
+    def upload(self, array) -> "Buffer":
+        a = np.ascontiguousarray(array)
+        buf = Buffer(self, max(a.nbytes, 16))
+        buf.write(a)
+        return buf
+
+    def stream(self) -> "Stream":
+        return Stream(self)
+
+    def event(self) -> "Event":
+        return Event(self)
+
+    def close(self):
+        if self.h:
+            lib().yuuka_device_close(self.h)
+            self.h = C.c_void_p()
+
+
+class Buffer:
+    def __init__(self, dev: Device, nbytes: int):
+        self.dev = dev
+        self.h = C.c_void_p()
+        check(lib().yuuka_buffer_alloc(dev.h, nbytes, C.byref(self.h)))
+        self.nbytes = nbytes
+
+    def write(self, array, offset: int = 0):
+        a = np.ascontiguousarray(array)
+        check(lib().yuuka_memcpy_h2d_at(self.h, offset, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def read(self, dtype, count: int, offset: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype)
+        check(lib().yuuka_memcpy_d2h_at(out.ctypes.data_as(C.c_void_p), self.h, offset, out.nbytes))
+        return out
+
+    def read_into(self, out: np.ndarray, offset: int = 0):
+        check(lib().yuuka_memcpy_d2h_at(out.ctypes.data_as(C.c_void_p), self.h, offset, out.nbytes))
+
+    def free(self):
+        if self.h:
+            lib().yuuka_buffer_free(self.h)
+            self.h = C.c_void_p()
+
+
+class Stream:
+    def __init__(self, dev: Device):
+        self.dev = dev
+        self.h = C.c_void_p()
+        check(lib().yuuka_stream_create(dev.h, C.byref(self.h)))
+
+    def synchronize(self):
+        check(lib().yuuka_stream_synchronize(self.h))
+
+    def record(self, event: "Event"):
+        check(lib().yuuka_event_record(self.h, event.h))
+
+    def destroy(self):
+        if self.h:
+            lib().yuuka_stream_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class Event:
+    def __init__(self, dev: Device):
+        self.h = C.c_void_p()
+        check(lib().yuuka_event_create(dev.h, C.byref(self.h)))
+
+    def wait(self):
+        check(lib().yuuka_event_wait(self.h))
+
+    def elapsed_ms(self, end: "Event") -> float:
+        ms = C.c_float()
+        check(lib().yuuka_event_elapsed_ms(self.h, end.h, C.byref(ms)))
+        return ms.value
+
+    def destroy(self):
+        if self.h:
+            lib().yuuka_event_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+def to_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bits (round to nearest even), as uint16."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+def from_bf16(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def gemm_quant(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_out: int, rows: int,
+               w_dtype: int, x_dtype: int = F32, path: int = PATH_AUTO, flags: int = 0,
+               out_offset: int = 0, x_offset: int = 0, w_offset: int = 0, completion: Event | None = None):
+    check(lib().yuuka_gemm_quant(stream.h, out.h, out_offset, x.h, x_offset, x_dtype, w.h, w_offset, w_dtype,
+                                 n_in, n_out, rows, path, flags, completion.h if completion else None))
+
+
+class Model:
+    """Device model: GGUF tensors uploaded verbatim (engine/gpu/model.go:288-301)."""
+
+    def __init__(self, dev: Device, cfg: dict, tensors: dict | None = None):
+        self.dev = dev
+        self.cfg = dict(cfg)
+        self.h = C.c_void_p()
+        c = ModelConfig(**cfg)
+        check(lib().yuuka_model_create(dev.h, C.byref(c), C.byref(self.h)))
+        if tensors is not None:
+            for name, (dtype, data, rows, cols) in tensors.items():
+                self.set_tensor(name, dtype, data, rows, cols)
+            self.finalize()
+
+    def set_tensor(self, name: str, dtype: int, data, rows: int, cols: int):
+        a = np.ascontiguousarray(data)
+        check(lib().yuuka_model_set_tensor(self.h, name.encode(), dtype, a.ctypes.data_as(C.c_void_p), rows, cols))
+
+    def finalize(self):
+        check(lib().yuuka_model_finalize(self.h))
+
+    @property
+    def weight_bytes(self) -> int:
+        return lib().yuuka_model_weight_bytes(self.h)
+
+    @property
+    def vocab(self) -> int:
+        return self.cfg["vocab"]
+
+    def close(self):
+        if self.h:
+            lib().yuuka_model_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class VerifyResult:
+    def __init__(self, accepted, emitted, path, logits):
+        self.accepted, self.emitted, self.path, self.logits = accepted, emitted, path, logits
+
+
+class Session:
+    """Paged KV pool, block tables, recurrent state and step buffers for up to
+    max_batch sequences (engine/gpu/session.go holds one sequence)."""
+
+    def __init__(self, model: Model, max_batch: int = 1, max_nodes: int = 16, capacity: int = 512,
+                 kv_format: int = KV_F16, block_size: int = 0, pool_blocks: int = 0, want_logits: bool = True):
+        self.model = model
+        self.max_batch, self.max_nodes, self.capacity = max_batch, max_nodes, capacity
+        cfg = SessionConfig(max_batch, max_nodes, capacity, block_size, pool_blocks, kv_format, int(want_logits))
+        self.h = C.c_void_p()
+        check(lib().yuuka_session_create(model.h, C.byref(cfg), C.byref(self.h)))
+        self._staged = None
+
+    def set_block_table(self, seq: int, blocks):
+        b = np.ascontiguousarray(blocks, np.int32)
+        check(lib().yuuka_session_set_block_table(self.h, seq, b.ctypes.data_as(C.c_void_p), b.size))
+
+    def reset(self, seq: int = 0):
+        check(lib().yuuka_session_reset(self.h, seq))
+
+    def set_position(self, seq: int, pos: int):
+        check(lib().yuuka_session_set_position(self.h, seq, pos))
+
+    def position(self, seq: int = 0) -> int:
+        v = C.c_int32()
+        check(lib().yuuka_session_position(self.h, seq, C.byref(v)))
+        return v.value
+
+    def snapshot(self, seq: int = 0) -> np.ndarray:
+        n = lib().yuuka_session_snapshot_bytes(self.h)
+        out = np.empty(n, np.uint8)
+        check(lib().yuuka_session_snapshot(self.h, seq, out.ctypes.data_as(C.c_void_p), n))
+        return out
+
+    def restore(self, data, seq: int = 0):
+        d = np.ascontiguousarray(data, np.uint8)
+        check(lib().yuuka_session_restore(self.h, seq, d.ctypes.data_as(C.c_void_p), d.size))
+
+    def prefill_logits(self, tokens, seq: int = 0) -> np.ndarray:
+        t = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty((t.size, self.model.vocab), np.float32)
+        check(lib().yuuka_session_prefill_logits(self.h, seq, t.ctypes.data_as(C.c_void_p), t.size,
+                                                 out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def forward(self, tokens, seq: int = 0, want_logits: bool = True):
+        t = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty(self.model.vocab, np.float32) if want_logits else None
+        check(lib().yuuka_session_forward(self.h, seq, t.ctypes.data_as(C.c_void_p), t.size,
+                                          out.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return out
+
+    def _batch(self, tokens, parent, mode, want_logits, temperature=1.0):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        if tokens.ndim == 1:
+            tokens = tokens[None, :]
+        B, N = tokens.shape
+        par = None
+        if parent is not None:
+            par = np.ascontiguousarray(np.broadcast_to(np.asarray(parent, np.int32), (B, N)))
+        keep = dict(tokens=tokens, parent=par, accepted=np.zeros(B, np.int32), emitted=np.full((B, N), -1, np.int32),
+                    path=np.full((B, N), -1, np.int32),
+                    logits=np.empty((B, N, self.model.vocab), np.float32) if want_logits else None)
+        vb = VerifyBatch()
+        vb.batch, vb.nodes = B, N
+        vb.tokens = tokens.ctypes.data
+        vb.parent = par.ctypes.data if par is not None else None
+        vb.mode, vb.temperature = mode, temperature
+        vb.accepted = keep["accepted"].ctypes.data
+        vb.emitted = keep["emitted"].ctypes.data
+        vb.path = keep["path"].ctypes.data
+        vb.logits = keep["logits"].ctypes.data if want_logits else None
+        return vb, keep
+
+    @staticmethod
+    def _result(keep) -> VerifyResult:
+        return VerifyResult(keep["accepted"], keep["emitted"], keep["path"], keep["logits"])
+
+    def verify(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False) -> VerifyResult:
+        """One verify step; tokens [batch, nodes] with the pending token in column 0."""
+        vb, keep = self._batch(tokens, parent, mode, want_logits)
+        check(lib().yuuka_verify_step(self.h, C.byref(vb)))
+        return self._result(keep)
+
+    def stage(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False):
+        vb, keep = self._batch(tokens, parent, mode, want_logits)
+        check(lib().yuuka_verify_stage(self.h, C.byref(vb)))
+        self._staged = (vb, keep)
+
+    def launch(self, completion: Event | None = None):
+        check(lib().yuuka_verify_launch(self.h, completion.h if completion else None))
+
+    def fetch(self) -> VerifyResult:
+        vb, keep = self._staged
+        check(lib().yuuka_verify_fetch(self.h, C.byref(vb)))
+        return self._result(keep)
+
+    def stream_handle(self):
+        return lib().yuuka_session_stream(self.h)
+
+    def record(self, event: Event):
+        check(lib().yuuka_event_record(self.stream_handle(), event.h))
+
+    @property
+    def last_launch_count(self) -> int:
+        return lib().yuuka_session_last_launch_count(self.h)
+
+    def close(self):
+        if self.h:
+            lib().yuuka_session_destroy(self.h)
+            self.h = C.c_void_p()
