@@ -251,6 +251,27 @@ YUUKA_API yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_b
 YUUKA_API yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * batch);
 YUUKA_API yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion);
 YUUKA_API yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * batch);
+
+/* Diagnostic launch: as yuuka_verify_launch, with an event pair around every
+ * operation and one synchronisation at the end; returns per-op codes and
+ * elapsed nanoseconds (yuuka_plan_execute_profiled, yuuka_hip.h:491-496). The
+ * step still has to be fetched. Not for the hot path. */
+typedef enum yuuka_op_code {
+    YUUKA_OP_GEMM = 16,          /* numbering follows yuuka_hip.h:104-149 where an op exists there */
+    YUUKA_OP_RMSNORM = 18,
+    YUUKA_OP_ATTN_PREP = 20,
+    YUUKA_OP_RECURRENT_CHUNK = 23,
+    YUUKA_OP_EMBEDDING = 24,
+    YUUKA_OP_ATTENTION = 29,
+    YUUKA_OP_LM_HEAD = 37,
+    YUUKA_OP_SILU_MUL = 9,
+    YUUKA_OP_GDN_SCAN = 100,
+    YUUKA_OP_GDN_NORM_GATE = 101,
+    YUUKA_OP_ACCEPT = 102,
+    YUUKA_OP_COMMIT = 103
+} yuuka_op_code;
+YUUKA_API yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes, uint64_t * op_times_ns,
+                                                    uint64_t capacity, uint64_t * op_count);
 YUUKA_API yuuka_stream * yuuka_session_stream(yuuka_session * s);
 /* Kernel launches enqueued by the last yuuka_verify_launch. */
 YUUKA_API uint32_t yuuka_session_last_launch_count(const yuuka_session * s);

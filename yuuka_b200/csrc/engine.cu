@@ -363,11 +363,24 @@ struct yuuka_session {
     uint32_t st_mode = 0;
     bool staged = false, launched = false;
     uint32_t launches = 0;
+    // per-op attribution (yuuka_verify_launch_profiled)
+    bool profiling = false;
+    std::vector<std::pair<uint32_t, cudaEvent_t>> prof;
 };
 
 namespace {
 
+// Records an event in front of the next op when a profiled launch is running.
+void mark(yuuka_session * s, uint32_t code) {
+    if (!s->profiling) return;
+    cudaEvent_t e;
+    YK_CUDA(cudaEventCreate(&e));
+    YK_CUDA(cudaEventRecord(e, s->stream.s));
+    s->prof.push_back({code, e});
+}
+
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, float * out, int ldo, int rows, uint32_t flags) {
+    mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     GemmArgs a;
     a.w = w.ptr;
     a.w_readable = w.bytes + 256;
@@ -403,11 +416,13 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     const int conv_dim = m->conv_dim(), inner = c.inner_size, rank = c.time_step_rank, S = c.state_size;
     const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
 
+    mark(s, YUUKA_OP_EMBEDDING);
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
     for (int i = 0; i < c.block_count; i++) {
         const LayerW & L = m->layers[i];
         LayerState & LS = s->layers[i];
+        mark(s, YUUKA_OP_RMSNORM);
         launch_rmsnorm(st, s->xn, H, s->x, H, L.attn_norm, H, R, c.rms_eps);
         s->launches++;
         if (m->recurrent(i)) {
@@ -437,7 +452,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.S = S;
             g.kernel = c.conv_kernel;
             g.eps = c.rms_eps;
+            mark(s, YUUKA_OP_GDN_SCAN);
             launch_gdn_scan(st, g, rows);
+            mark(s, YUUKA_OP_GDN_NORM_GATE);
             launch_gdn_norm_gate(st, s->gdn_out, inner, LS.proj + conv_dim, np, L.ssm_norm, rank, S, R, c.rms_eps);
             s->launches += 2;
             gemm(s, L.out, s->gdn_out, inner, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
@@ -464,6 +481,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             pool.row_bytes = s->kv_row_bytes;
             pool.tables = s->d_tables + (int64_t)seq0 * s->table_stride;
             pool.table_stride = s->table_stride;
+            mark(s, YUUKA_OP_ATTN_PREP);
             launch_attn_prep(st, qb, nq, kb, nq, vb, nq, L.q_norm, L.k_norm, c.heads, c.kv_heads, c.head_dim, c.rope_dim,
                              c.rope_freq_base, c.rms_eps, rows, pool);
             s->launches++;
@@ -480,11 +498,13 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             sc.partial = s->attn_partial;
             YK_REQUIRE(attention_scratch_floats(R, c.heads, c.head_dim, sc.splits) <= s->attn_partial_floats,
                        YUUKA_ERR_INTERNAL, "attention scratch is too small");
+            mark(s, YUUKA_OP_ATTENTION);
             s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
                                             max_total, sc);
             gemm(s, L.o, s->attn_out, o_dim, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
         }
         // forwardFFN (model/qwen35/forward.go:295-315)
+        mark(s, YUUKA_OP_RMSNORM);
         launch_rmsnorm(st, s->xn, H, s->x, H, L.post_norm, H, R, c.rms_eps);
         s->launches++;
         if (L.gate_up.present()) {
@@ -493,29 +513,34 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             gemm(s, L.ffn_gate, s->xn, H, s->gate_up, 2 * F, R, 0);
             gemm(s, L.ffn_up, s->xn, H, s->gate_up + F, 2 * F, R, 0);
         }
+        mark(s, YUUKA_OP_SILU_MUL);
         launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R);
         s->launches++;
         gemm(s, L.ffn_down, s->act, F, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
     }
     // tail: final norm + LM head over the wanted rows (forward.go:147-151)
     if (logit_rows == LOGITS_ALL) {
+        mark(s, YUUKA_OP_RMSNORM);
         launch_rmsnorm(st, s->xn, H, s->x, H, m->output_norm, H, R, c.rms_eps);
         s->launches++;
         gemm(s, m->output, s->xn, H, s->logits, c.vocab, R, 0);
     } else if (logit_rows == LOGITS_LAST) {
         // batch == 1: only the last row
+        mark(s, YUUKA_OP_RMSNORM);
         launch_rmsnorm(st, s->xn, H, s->x + (int64_t)(R - 1) * H, H, m->output_norm, H, 1, c.rms_eps);
         s->launches++;
         gemm(s, m->output, s->xn, H, s->logits + (int64_t)(R - 1) * c.vocab, c.vocab, 1, 0);
     }
     // acceptance + commit
     if (mode == YUUKA_ACCEPT_NONE) return;
+    mark(s, YUUKA_OP_ACCEPT);
     if (mode == YUUKA_ACCEPT_GREEDY) {
         s->launches += launch_accept_greedy(st, s->logits, c.vocab, rows, s->argmax, s->acc);
     } else {
         launch_accept_all(st, rows, s->acc);  // forced commit of a chain
         s->launches++;
     }
+    mark(s, YUUKA_OP_COMMIT);
     if (!s->gdn_layers.empty()) {
         launch_gdn_commit(st, s->d_gdn_commit, (int)s->gdn_layers.size(), c.group_count, rank, S, c.conv_kernel, conv_dim,
                           seq0, rows, s->acc);
@@ -884,6 +909,44 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
             for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
         s->launched = true;
         if (completion) YK_CUDA(cudaEventRecord(completion->e, s->stream.s));
+    });
+}
+
+yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes, uint64_t * op_times_ns,
+                                          uint64_t capacity, uint64_t * op_count) {
+    return guard([&] {
+        YK_REQUIRE(s && s->staged && op_codes && op_times_ns && op_count, YUUKA_ERR_INVALID_ARGUMENT,
+                   "verify_launch_profiled: null argument or no staged step");
+        set_device(s->model->dev);
+        s->launches = 0;
+        s->profiling = true;
+        s->prof.clear();
+        try {
+            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL,
+                     max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes));
+            mark(s, 0);
+        } catch (...) {
+            s->profiling = false;
+            for (auto & pe : s->prof) cudaEventDestroy(pe.second);
+            s->prof.clear();
+            throw;
+        }
+        s->profiling = false;
+        if (s->st_mode != YUUKA_ACCEPT_NONE)
+            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
+        s->launched = true;
+        cudaError_t err = cudaStreamSynchronize(s->stream.s);
+        uint64_t n = s->prof.empty() ? 0 : s->prof.size() - 1;
+        for (uint64_t i = 0; i < n && i < capacity && err == cudaSuccess; i++) {
+            float ms = 0;
+            err = cudaEventElapsedTime(&ms, s->prof[i].second, s->prof[i + 1].second);
+            op_codes[i] = s->prof[i].first;
+            op_times_ns[i] = (uint64_t)((double)ms * 1e6);
+        }
+        for (auto & pe : s->prof) cudaEventDestroy(pe.second);
+        s->prof.clear();
+        YK_CUDA(err);
+        *op_count = n;
     });
 }
 

@@ -19,6 +19,8 @@ KV_F32, KV_F16, KV_Q8_0 = 0, 1, 2
 PATH_AUTO, PATH_FP32, PATH_MMA = 0, 1, 2
 GEMM_ACCUMULATE = 1
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
+OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
+            100: "gdn_scan", 101: "gdn_norm_gate", 102: "accept", 103: "commit"}
 ABI_VERSION = 1
 
 
@@ -113,6 +115,7 @@ SIGNATURES = {
     "yuuka_verify_stage": (_i32, [_vp, _vp]),
     "yuuka_verify_launch": (_i32, [_vp, _vp]),
     "yuuka_verify_fetch": (_i32, [_vp, _vp]),
+    "yuuka_verify_launch_profiled": (_i32, [_vp, _vp, _vp, _u64, _vp]),
     "yuuka_session_stream": (_vp, [_vp]),
     "yuuka_session_last_launch_count": (_u32, [_vp]),
 }
@@ -392,6 +395,15 @@ class Session:
 
     def launch(self, completion: Event | None = None):
         check(lib().yuuka_verify_launch(self.h, completion.h if completion else None))
+
+    def launch_profiled(self, capacity: int = 4096):
+        """Runs the staged step with per-op events; returns [(op_code, nanoseconds)]."""
+        codes = np.zeros(capacity, np.uint32)
+        times = np.zeros(capacity, np.uint64)
+        n = C.c_uint64()
+        check(lib().yuuka_verify_launch_profiled(self.h, codes.ctypes.data_as(C.c_void_p),
+                                                 times.ctypes.data_as(C.c_void_p), capacity, C.byref(n)))
+        return list(zip(codes[:n.value].tolist(), times[:n.value].tolist()))
 
     def fetch(self) -> VerifyResult:
         vb, keep = self._staged
