@@ -126,12 +126,27 @@ YUUKA_API yuuka_status yuuka_buffer_copy(yuuka_stream * stream, yuuka_buffer * d
  * sub-ranges of the buffers. flags: bit 0 adds the product to out instead of
  * overwriting it (GEMV_RESIDUAL, yuuka_hip.h:398-401). */
 #define YUUKA_GEMM_ACCUMULATE 0x1u
+/* bit 1: w holds the tile-ordered copy made by yuuka_weights_tile (required by
+ * the mma route and by the fast fp32 route; GGUF-layout weights take a slower
+ * generic kernel). */
+#define YUUKA_GEMM_TILED 0x2u
 YUUKA_API yuuka_status yuuka_gemm_quant(yuuka_stream * stream,
                                         yuuka_buffer * out, uint64_t out_offset,
                                         const yuuka_buffer * x, uint64_t x_offset, uint32_t x_dtype,
                                         const yuuka_buffer * w, uint64_t w_offset, uint32_t w_dtype,
                                         uint64_t n_in, uint64_t n_out, uint64_t rows,
                                         uint32_t path, uint32_t flags, yuuka_event * completion);
+
+/* Tile-ordered weight copy: a byte permutation of a K-quant / Q8_0 GGUF matrix
+ * into 16-row x 256-column records laid out in the order a warp consumes them
+ * (the reference uploads GGUF bytes verbatim, engine/gpu/model.go:288-301; its
+ * docs list an offline re-layout as future work). Dequantized values are
+ * bit-identical. yuuka_weights_tiled_bytes returns 0 for dtypes / widths
+ * without a tiled form. */
+YUUKA_API uint64_t yuuka_weights_tiled_bytes(uint32_t dtype, uint64_t n_out, uint64_t n_in);
+YUUKA_API yuuka_status yuuka_weights_tile(yuuka_stream * stream, yuuka_buffer * dst, uint64_t dst_offset,
+                                          const yuuka_buffer * src, uint64_t src_offset, uint32_t dtype,
+                                          uint64_t n_out, uint64_t n_in, yuuka_event * completion);
 
 /* ------------------------------------------------------------------------
  * Model and verify session (what engine/gpu's Model/Session/plan builders do

@@ -15,17 +15,24 @@ def dev():
     d.close()
 
 
-def run_gemm(dev, w_packed, w_dtype, n_out, n_in, x, path, x_dtype=cuda.F32, accumulate=None):
+def run_gemm(dev, w_packed, w_dtype, n_out, n_in, x, path, x_dtype=cuda.F32, accumulate=None, tiled=True):
     stream = dev.stream()
-    wb = dev.alloc(w_packed.nbytes + 256)
-    wb.write(w_packed)
+    raw = dev.alloc(w_packed.nbytes + 256)
+    raw.write(w_packed)
+    if tiled:
+        wb = dev.alloc(cuda.tiled_bytes(w_dtype, n_out, n_in) + 256)
+        cuda.tile_weights(stream, wb, raw, w_dtype, n_out, n_in)
+        stream.synchronize()
+        raw.free()
+    else:
+        wb = raw
     xb = dev.upload(cuda.to_bf16(x) if x_dtype == cuda.BF16 else x.astype(np.float32))
     rows = x.shape[0]
     ob = dev.alloc(rows * n_out * 4)
-    flags = 0
+    flags = cuda.GEMM_TILED if tiled else 0
     if accumulate is not None:
         ob.write(accumulate.astype(np.float32))
-        flags = cuda.GEMM_ACCUMULATE
+        flags |= cuda.GEMM_ACCUMULATE
     cuda.gemm_quant(stream, ob, xb, wb, n_in, n_out, rows, w_dtype, x_dtype, path, flags)
     stream.synchronize()
     out = ob.read(np.float32, rows * n_out).reshape(rows, n_out)
@@ -108,6 +115,37 @@ def test_lm_head_shape_q6_k(dev):
     assert np.array_equal(np.argmax(got, -1), np.argmax(want, -1)) or err < 1e-3
 
 
+@pytest.mark.parametrize("dtype", [synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q5_K])
+def test_gguf_layout_route_matches_oracle(dev, dtype):
+    # weights left in GGUF row-major order take the generic fp32 kernel
+    n_out, n_in, rows = 300, 1280 if dtype != synth.Q8_0 else 96, 5
+    w = synth.normal_quant(n_out, n_in, dtype, 0.02, 300 + dtype)
+    x = synth.normal_f32(rows * n_in, 1.0, 31).reshape(rows, n_in)
+    want = yo.matmul(w, dtype, n_out, n_in, x)
+    got = run_gemm(dev, w, dtype, n_out, n_in, x, cuda.PATH_AUTO, tiled=False)
+    assert np.max(np.abs(got - want)) <= 2e-5 * (1 + np.max(np.abs(want)))
+    with pytest.raises(cuda.UnsupportedError):
+        run_gemm(dev, w, dtype, n_out, n_in, x, cuda.PATH_MMA, tiled=False)
+
+
+def test_tiling_is_a_permutation(dev):
+    # every GGUF byte appears exactly once in the tiled copy (rows padded with zeros)
+    for dtype, n_out, n_in in ((synth.Q4_K, 40, 512), (synth.Q6_K, 16, 256), (synth.Q8_0, 33, 256), (synth.Q5_K, 16, 512)):
+        rb = synth.row_bytes(dtype, n_in)
+        raw_h = np.random.default_rng(dtype).integers(1, 256, n_out * rb, dtype=np.uint8)
+        stream = dev.stream()
+        raw = dev.upload(raw_h)
+        nbytes = cuda.tiled_bytes(dtype, n_out, n_in)
+        assert nbytes == -(-n_out // 16) * 16 * rb
+        tb = dev.alloc(nbytes)
+        cuda.tile_weights(stream, tb, raw, dtype, n_out, n_in)
+        stream.synchronize()
+        t = tb.read(np.uint8, nbytes)
+        assert np.array_equal(np.sort(t[t != 0]), np.sort(raw_h))
+        assert int((t == 0).sum()) == nbytes - raw_h.size
+        raw.free(); tb.free(); stream.destroy()
+
+
 def test_accumulate_flag_adds_to_output(dev):
     n_out, n_in, rows = 2560, 4096, 9
     w = synth.normal_quant(n_out, n_in, synth.Q4_K, 0.02, 1)
@@ -124,6 +162,9 @@ def test_rejections(dev):
     b = dev.alloc(1 << 16)
     with pytest.raises(cuda.UnsupportedError):      # row width not a multiple of the block
         cuda.gemm_quant(stream, b, b, b, 100, 8, 1, cuda.Q4_K)
+    with pytest.raises(cuda.UnsupportedError):      # no tiled form for F32 weights
+        cuda.gemm_quant(stream, b, b, b, 256, 8, 1, cuda.F32, flags=cuda.GEMM_TILED)
+    assert cuda.tiled_bytes(cuda.F32, 8, 256) == 0
     with pytest.raises(cuda.YuukaError) as e:       # weight range exceeds the buffer
         cuda.gemm_quant(stream, b, b, b, 2560, 4096, 1, cuda.Q4_K)
     assert e.value.status == cuda.ERR_INVALID_ARGUMENT

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "gemm_quant.cuh"
+#include "gemm_tiled.cuh"
 #include "layers.cuh"
 
 using namespace yk;
@@ -20,6 +21,7 @@ struct Tensor {
     uint32_t dtype = 0;
     uint64_t rows = 0, cols = 0, bytes = 0;
     bool owned = false;
+    bool tiled = false;  // ptr holds the tile-ordered copy (gemm_tiled.cuh)
     bool present() const { return ptr != nullptr; }
 };
 
@@ -159,6 +161,34 @@ void drop(yuuka_model * m, const std::string & name) {
     m->tensors.erase(it);
 }
 
+// Replaces the GGUF-layout bytes of a matrix by their tile-ordered copy. name is
+// the tensor's key in m->tensors, or empty for a fused allocation.
+void tile_in_place(yuuka_model * m, Tensor & t, const std::string & name) {
+    if (!t.present() || t.tiled || !tiled_supported(t.dtype, t.cols)) return;
+    const uint64_t bytes = tiled_bytes(t.dtype, t.rows, t.cols);
+    void * ptr = nullptr;
+    cudaError_t err = cudaMalloc(&ptr, bytes + 256);
+    YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "tiled weight allocation of %llu bytes failed",
+               (unsigned long long)bytes);
+    m->extra_allocs.push_back(ptr);
+    launch_tile_weights(nullptr, (uint8_t *)ptr, t.ptr, t.dtype, (int)t.rows, (int)t.cols);
+    YK_CUDA(cudaDeviceSynchronize());
+    if (!name.empty()) {
+        drop(m, name);
+    } else {
+        for (auto it = m->extra_allocs.begin(); it != m->extra_allocs.end(); ++it)
+            if (*it == (void *)t.ptr) {
+                cudaFree(*it);
+                m->extra_allocs.erase(it);
+                break;
+            }
+    }
+    t.ptr = (uint8_t *)ptr;
+    t.bytes = bytes;
+    t.owned = false;
+    t.tiled = true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -287,6 +317,44 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
             if (kv.first != "token_embd.weight") total += kv.second.bytes;
         for (const LayerW & L : m->layers) total += L.proj.bytes + L.qk.bytes + L.gate_up.bytes;
         m->weight_bytes = total;
+        // tile-ordered copies for the GEMM kernels; the GGUF-layout bytes are released
+        const bool tied = !m->tensors.count("output.weight");
+        for (int i = 0; i < c.block_count; i++) {
+            LayerW & L = m->layers[i];
+            const std::string p = "blk." + std::to_string(i) + ".";
+            tile_in_place(m, L.proj, "");
+            tile_in_place(m, L.qk, "");
+            tile_in_place(m, L.gate_up, "");
+            tile_in_place(m, L.qkv, p + "attn_qkv.weight");
+            tile_in_place(m, L.gate, p + "attn_gate.weight");
+            tile_in_place(m, L.beta, p + "ssm_beta.weight");
+            tile_in_place(m, L.alpha, p + "ssm_alpha.weight");
+            tile_in_place(m, L.out, p + "ssm_out.weight");
+            tile_in_place(m, L.q, p + "attn_q.weight");
+            tile_in_place(m, L.k, p + "attn_k.weight");
+            tile_in_place(m, L.v, p + "attn_v.weight");
+            tile_in_place(m, L.o, p + "attn_output.weight");
+            tile_in_place(m, L.ffn_gate, p + "ffn_gate.weight");
+            tile_in_place(m, L.ffn_up, p + "ffn_up.weight");
+            tile_in_place(m, L.ffn_down, p + "ffn_down.weight");
+        }
+        if (!tied) tile_in_place(m, m->output, "output.weight");
+        else if (tiled_supported(m->output.dtype, m->output.cols)) {
+            // tied head: the embedding gather needs the GGUF rows, the head a tiled copy
+            Tensor head = m->output;
+            head.owned = false;
+            const uint64_t bytes = tiled_bytes(head.dtype, head.rows, head.cols);
+            void * ptr = nullptr;
+            cudaError_t err = cudaMalloc(&ptr, bytes + 256);
+            YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "tiled head allocation failed");
+            m->extra_allocs.push_back(ptr);
+            launch_tile_weights(nullptr, (uint8_t *)ptr, head.ptr, head.dtype, (int)head.rows, (int)head.cols);
+            YK_CUDA(cudaDeviceSynchronize());
+            head.ptr = (uint8_t *)ptr;
+            head.bytes = bytes;
+            head.tiled = true;
+            m->output = head;
+        }
         m->finalized = true;
     });
 }
@@ -381,6 +449,24 @@ void mark(yuuka_session * s, uint32_t code) {
 
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, float * out, int ldo, int rows, uint32_t flags) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
+    if (w.tiled) {
+        TiledGemmArgs t;
+        t.w = w.ptr;
+        t.w_dtype = w.dtype;
+        t.x = x;
+        t.x_dtype = YUUKA_DTYPE_F32;
+        t.ldx = ldx;
+        t.out = out;
+        t.ldo = ldo;
+        t.rows = rows;
+        t.n_out = (int)w.rows;
+        t.n_in = (int)w.cols;
+        t.path = YUUKA_GEMM_PATH_AUTO;
+        t.flags = flags;
+        t.scratch = &s->gemm;
+        s->launches += launch_gemm_tiled(s->model->dev, s->stream.s, t);
+        return;
+    }
     GemmArgs a;
     a.w = w.ptr;
     a.w_readable = w.bytes + 256;

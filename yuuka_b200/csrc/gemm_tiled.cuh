@@ -1,0 +1,54 @@
+// Tile-ordered weight layout and the GEMM kernels that read it.
+//
+// A GGUF matrix [n_out][row_bytes] is re-ordered once, byte for byte, into
+// records of 16 rows x 256 columns (one K-quant superblock per row): record
+// (rt, sb) holds rows 16*rt .. 16*rt+15, columns 256*sb .. 256*sb+255, with the
+// bytes placed in the order the 32 lanes of a warp consume them. A warp then
+// streams a 16-row tile along K with fully coalesced 512-byte loads, every
+// address 16-byte aligned whatever the GGUF row alignment was (Q6_K rows are
+// only 2-byte aligned). The re-ordering is a permutation: dequantized values
+// are bit-identical to the GGUF tensor's.
+#pragma once
+
+#include "gemm_quant.cuh"
+
+namespace yk {
+
+// Bytes of one 16-row x 256-column record; 0 if the dtype has no tiled form.
+inline int tiled_record_bytes(uint32_t dtype) {
+    switch (dtype) {
+    case YUUKA_DTYPE_Q4_K: return 16 * 144;
+    case YUUKA_DTYPE_Q5_K: return 16 * 176;
+    case YUUKA_DTYPE_Q6_K: return 16 * 210;
+    case YUUKA_DTYPE_Q8_0: return 16 * 272;
+    default: return 0;
+    }
+}
+inline bool tiled_supported(uint32_t dtype, uint64_t n_in) { return tiled_record_bytes(dtype) != 0 && n_in % 256 == 0; }
+inline uint64_t tiled_bytes(uint32_t dtype, uint64_t n_out, uint64_t n_in) {
+    return ((n_out + 15) / 16) * (n_in / 256) * (uint64_t)tiled_record_bytes(dtype);
+}
+
+// dst (tiled_bytes long) <- GGUF rows at src. Rows beyond n_out are zero.
+void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uint32_t dtype, int n_out, int n_in);
+
+struct TiledGemmArgs {
+    const uint8_t * w = nullptr;  // tiled layout
+    uint32_t w_dtype = 0;
+    const void * x = nullptr;
+    uint32_t x_dtype = YUUKA_DTYPE_F32;
+    int64_t ldx = 0;
+    float * out = nullptr;
+    int64_t ldo = 0;
+    int rows = 0, n_out = 0, n_in = 0;
+    uint32_t path = YUUKA_GEMM_PATH_AUTO;
+    uint32_t flags = 0;
+    GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
+};
+
+int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a);
+// Scratch the launch above needs for this shape (0 partial floats when K is not split across CTAs).
+void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int rows, int n_out, int n_in,
+                             uint64_t * partial_floats, int * counters);
+
+}  // namespace yk

@@ -18,6 +18,7 @@ F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
 KV_F32, KV_F16, KV_Q8_0 = 0, 1, 2
 PATH_AUTO, PATH_FP32, PATH_MMA = 0, 1, 2
 GEMM_ACCUMULATE = 1
+GEMM_TILED = 2
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
 OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
             100: "gdn_scan", 101: "gdn_norm_gate", 102: "accept", 103: "commit"}
@@ -95,6 +96,8 @@ SIGNATURES = {
     "yuuka_buffer_copy": (_i32, [_vp, _vp, _u64, _vp, _u64, _u64, _vp]),
     "yuuka_gemm_quant": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
                                 _u32, _u32, _vp]),
+    "yuuka_weights_tiled_bytes": (_u64, [_u32, _u64, _u64]),
+    "yuuka_weights_tile": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _u64, _u64, _vp]),
     "yuuka_model_create": (_i32, [_vp, _vp, _vp]),
     "yuuka_model_destroy": (None, [_vp]),
     "yuuka_model_set_tensor": (_i32, [_vp, C.c_char_p, _u32, _vp, _u64, _u64]),
@@ -255,6 +258,15 @@ def to_bf16(x: np.ndarray) -> np.ndarray:
 
 def from_bf16(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def tiled_bytes(dtype: int, n_out: int, n_in: int) -> int:
+    return lib().yuuka_weights_tiled_bytes(dtype, n_out, n_in)
+
+
+def tile_weights(stream: Stream, dst: Buffer, src: Buffer, dtype: int, n_out: int, n_in: int,
+                 dst_offset: int = 0, src_offset: int = 0):
+    check(lib().yuuka_weights_tile(stream.h, dst.h, dst_offset, src.h, src_offset, dtype, n_out, n_in, None))
 
 
 def gemm_quant(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_out: int, rows: int,

@@ -29,15 +29,21 @@ def bench_gemm(dev, n_out, n_in, dtype_name, rows, path, iters, warmup=3, l2_byt
     dtype = DTYPES[dtype_name]
     rb = synth.row_bytes(dtype, n_in)
     wbytes = n_out * rb
-    stride = (wbytes + 255) // 256 * 256
+    tbytes = cuda.tiled_bytes(dtype, n_out, n_in)
+    stride = (tbytes + 255) // 256 * 256
     copies = max(2, min(iters + warmup, -(-2 * l2_bytes // wbytes) + 1))
     # one generated matrix, replicated: the values do not matter for timing
     w = synth.normal_quant(min(n_out, 4096), n_in, dtype, 0.02, 1)
     reps = -(-n_out // min(n_out, 4096))
     w = np.tile(w, reps)[:wbytes]
     wb = dev.alloc(copies * stride + 256)
+    raw = dev.upload(w)
+    st0 = dev.stream()
     for c in range(copies):
-        wb.write(w, offset=c * stride)
+        cuda.tile_weights(st0, wb, raw, dtype, n_out, n_in, dst_offset=c * stride)
+    st0.synchronize()
+    st0.destroy()
+    raw.free()
     x = synth.normal_f32(rows * n_in, 1.0, 2)
     xb = dev.upload(cuda.to_bf16(x))
     ob = dev.alloc(rows * n_out * 4)
@@ -47,7 +53,8 @@ def bench_gemm(dev, n_out, n_in, dtype_name, rows, path, iters, warmup=3, l2_byt
     for it in range(warmup + iters):
         off = (it % copies) * stride
         stream.record(e0)
-        cuda.gemm_quant(stream, ob, xb, wb, n_in, n_out, rows, dtype, cuda.BF16, path, w_offset=off, completion=e1)
+        cuda.gemm_quant(stream, ob, xb, wb, n_in, n_out, rows, dtype, cuda.BF16, path, flags=cuda.GEMM_TILED,
+                        w_offset=off, completion=e1)
         e1.wait()
         if it >= warmup:
             times.append(e0.elapsed_ms(e1))
