@@ -68,7 +68,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -196,13 +196,18 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     logits = sess.forward(prompt)
     snap, pos = sess.snapshot(), sess.position()
     n_cont = total_steps * rows + rows
-    cont = np.empty(n_cont, np.int32)
-    tok = int(np.argmax(logits))
-    first = tok
-    for i in range(n_cont):
-        logits = sess.forward([tok])
-        tok = int(np.argmax(logits))
-        cont[i] = tok
+    # greedy continuation through the same 9-row kernels the timed steps use (row 0 of a step whose
+    # drafts are dummies), so that near-ties resolve the same way in both passes
+    cont_list: list[int] = []
+    first = int(np.argmax(logits))
+    pend = first
+    dummy = [0] * K_DRAFT
+    while len(cont_list) < n_cont:
+        r0 = sess.verify([[pend] + dummy])
+        a0 = int(r0.accepted[0])
+        cont_list.extend(int(t) for t in r0.emitted[0, :a0 + 1])
+        pend = cont_list[-1]
+    cont = np.array(cont_list[:n_cont], np.int32)
     sess.restore(snap)
     sess.set_position(0, pos)
     drafts = synth.corrupt_draft(cont, cfg["vocab"], P_CORRUPT, 7 + rank)
@@ -223,9 +228,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
 
     t_e2e = 0.0
     for step in range(total_steps):
+        if step == 0:
+            sampler.start()
         if step == args.warmup:
             barrier()
-            sampler.start()
             emitted_total = accepted_total = 0
             dev_ms = 0.0
             t_e2e = time.perf_counter()
@@ -316,7 +322,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32)

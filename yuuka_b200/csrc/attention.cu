@@ -10,6 +10,7 @@
 
 #include "layers.cuh"
 #include "quant.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -184,30 +185,48 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
     }
 }
 
-__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + (float)exp((double)-x)); }
+// float exp: the CPU reference evaluates exp in f64 and rounds; the difference is below 2e-7 relative
+__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+// one thread per 16 consecutive output dims of one (row, head)
 template <int HD>
 __global__ void attention_merge_kernel(float * __restrict__ out, int ldo, const float * __restrict__ partial,
-                                       const float * __restrict__ q, int ldq, int heads, int splits) {
-    const int r = blockIdx.x / heads, head = blockIdx.x % heads;
-    const float * base = partial + (int64_t)blockIdx.x * splits * (HD + 2);
+                                       const float * __restrict__ q, int ldq, int heads, int splits, XPrepOut prep) {
+    const int r = blockIdx.x;
+    const int gq = threadIdx.x;  // 16-group within the row: head * (HD/16) + part
+    if (gq >= heads * (HD / 16)) return;
+    const int head = gq / (HD / 16), part = gq - head * (HD / 16);
+    const float * base = partial + ((int64_t)r * heads + head) * splits * (HD + 2);
     float M = -INFINITY;
     for (int s = 0; s < splits; s++) M = fmaxf(M, base[s * (HD + 2) + HD]);
     float L = 0.0f;
+    float o[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i] = 0.0f;
     for (int s = 0; s < splits; s++) {
-        float ms = base[s * (HD + 2) + HD];
-        if (ms != -INFINITY) L += base[s * (HD + 2) + HD + 1] * expf(ms - M);
+        const float ms = base[s * (HD + 2) + HD];
+        if (ms == -INFINITY) continue;
+        const float w = expf(ms - M);
+        L += base[s * (HD + 2) + HD + 1] * w;
+        const float4 * src = reinterpret_cast<const float4 *>(base + s * (HD + 2) + part * 16);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 lo = reinterpret_cast<const float2 *>(src)[2 * i], hi = reinterpret_cast<const float2 *>(src)[2 * i + 1];
+            o[4 * i] = fmaf(lo.x, w, o[4 * i]);
+            o[4 * i + 1] = fmaf(lo.y, w, o[4 * i + 1]);
+            o[4 * i + 2] = fmaf(hi.x, w, o[4 * i + 2]);
+            o[4 * i + 3] = fmaf(hi.y, w, o[4 * i + 3]);
+        }
     }
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float o = 0.0f;
-        for (int s = 0; s < splits; s++) {
-            float ms = base[s * (HD + 2) + HD];
-            if (ms != -INFINITY) o = fmaf(base[s * (HD + 2) + d], expf(ms - M), o);
-        }
-        float gate = q[(int64_t)r * ldq + (int64_t)head * 2 * HD + HD + d];
-        out[(int64_t)r * ldo + head * HD + d] = o * inv * sigmoid_ref(gate);
-    }
+    const float * gate = q + (int64_t)r * ldq + (int64_t)head * 2 * HD + HD + part * 16;
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i] = o[i] * inv * sigmoid_ref(gate[i]);
+    float4 * d = reinterpret_cast<float4 *>(out + (int64_t)r * ldo + head * HD + part * 16);
+#pragma unroll
+    for (int i = 0; i < 4; i++) d[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    const int cols = heads * HD;
+    if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, o);
 }
 
 size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits) {
@@ -216,7 +235,7 @@ size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits) {
 
 template <int HD>
 static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float * q, int ldq, int heads, int kv_heads,
-                               const RowMeta & rows, const KvPool & pool, const AttnScratch & sc) {
+                               const RowMeta & rows, const KvPool & pool, const AttnScratch & sc, XPrepOut prep) {
     AttnParams p;
     p.partial = sc.partial;
     p.q = q;
@@ -235,22 +254,23 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
     dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
     kern<<<grid, ATT_WARPS * 32, smem, s>>>(p);
     YK_CUDA(cudaGetLastError());
-    attention_merge_kernel<HD><<<rows.batch * rows.nodes * heads, HD < 128 ? HD : 128, 0, s>>>(out, ldo, sc.partial, q, ldq,
-                                                                                             heads, sc.splits);
+    const int mthreads = ((heads * (HD / 16) + 31) / 32) * 32;
+    YK_REQUIRE(mthreads <= 1024, YUUKA_ERR_UNSUPPORTED, "attention: too many heads for the merge kernel");
+    attention_merge_kernel<HD><<<rows.batch * rows.nodes, mthreads, 0, s>>>(out, ldo, sc.partial, q, ldq, heads, sc.splits, prep);
     YK_CUDA(cudaGetLastError());
     return 2;
 }
 
 int launch_attention(cudaStream_t s, float * out, int ldo, const float * q, int ldq, int heads, int kv_heads,
                      int head_dim, const RowMeta & rows, const KvPool & pool, int max_total_keys,
-                     const AttnScratch & scratch) {
+                     const AttnScratch & scratch, XPrepOut prep) {
     YK_REQUIRE(rows.nodes <= 64, YUUKA_ERR_UNSUPPORTED, "attention: at most 64 rows per sequence");
     YK_REQUIRE((int64_t)scratch.splits * scratch.key_split >= max_total_keys, YUUKA_ERR_INTERNAL,
                "attention: key splits do not cover %d keys", max_total_keys);
     switch (head_dim) {
-    case 64: return launch_attention_hd<64>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch);
-    case 128: return launch_attention_hd<128>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch);
-    case 256: return launch_attention_hd<256>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch);
+    case 64: return launch_attention_hd<64>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch, prep);
+    case 128: return launch_attention_hd<128>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch, prep);
+    case 256: return launch_attention_hd<256>(s, out, ldo, q, ldq, heads, kv_heads, rows, pool, scratch, prep);
     default: YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "attention: head_dim %d is not 64, 128 or 256", head_dim);
     }
     return 0;

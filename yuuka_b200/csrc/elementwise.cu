@@ -2,6 +2,7 @@
 // product, and the attention front end (per-head norm, RoPE, paged KV write).
 #include "layers.cuh"
 #include "quant.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -56,9 +57,10 @@ __device__ __forceinline__ double block_sum_d(double v, double * red) {
 }
 
 // rmsNorm (model/qwen35/forward.go:460-470): f64 sum of squares, f32 mean,
-// scale = f32(1/sqrt(f64(mean + eps))), dst = src * scale * weight.
+// scale = f32(1/sqrt(f64(mean + eps))), dst = src * scale * weight. Also emits the
+// prepared (fp16 + group sums) form of dst for the GEMM that consumes it.
 __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
-                               const float * __restrict__ weight, int cols, float eps) {
+                               const float * __restrict__ weight, int cols, float eps, XPrepOut prep) {
     __shared__ double red[32];
     const int r = blockIdx.x;
     const float * x = src + (int64_t)r * lds;
@@ -67,30 +69,53 @@ __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * 
     sum = block_sum_d(sum, red);
     float mean = (float)(sum / (double)cols);
     float scale = (float)(1.0 / sqrt((double)(mean + eps)));
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) dst[(int64_t)r * ldd + i] = x[i] * scale * weight[i];
+    if ((cols & 15) == 0) {
+        for (int gq = threadIdx.x; gq < (cols >> 4); gq += blockDim.x) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = x[gq * 16 + i] * scale * weight[gq * 16 + i];
+            float4 * d = reinterpret_cast<float4 *>(dst + (int64_t)r * ldd + gq * 16);
+#pragma unroll
+            for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) dst[(int64_t)r * ldd + i] = x[i] * scale * weight[i];
+    }
 }
 
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight, int cols,
-                    int rows, float eps) {
-    rmsnorm_kernel<<<rows, 256, 0, s>>>(dst, ldd, src, lds, weight, cols, eps);
+                    int rows, float eps, XPrepOut prep) {
+    YK_REQUIRE(!prep.xh || ((cols & 15) == 0 && (ldd & 3) == 0), YUUKA_ERR_UNSUPPORTED,
+               "rmsnorm: prepared output needs a width that is a multiple of 16");
+    rmsnorm_kernel<<<rows, 256, 0, s>>>(dst, ldd, src, lds, weight, cols, eps, prep);
     YK_CUDA(cudaGetLastError());
 }
 
 // sigmoid / silu as the reference computes them: exp in f64 (forward.go:552-558)
-__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + (float)exp((double)-x)); }
+// float exp: the CPU reference evaluates exp in f64 and rounds; the difference is below 2e-7 relative
+__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_ref(float x) { return x * sigmoid_ref(x); }
 
 __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float * __restrict__ gate,
-                                const float * __restrict__ up, int ld, int cols) {
+                                const float * __restrict__ up, int ld, int cols, XPrepOut prep) {
     const int r = blockIdx.y;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < cols; i += gridDim.x * blockDim.x)
-        act[(int64_t)r * lda + i] = silu_ref(gate[(int64_t)r * ld + i]) * up[(int64_t)r * ld + i];
+    for (int gq = blockIdx.x * blockDim.x + threadIdx.x; gq < (cols >> 4); gq += gridDim.x * blockDim.x) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = silu_ref(gate[(int64_t)r * ld + gq * 16 + i]) * up[(int64_t)r * ld + gq * 16 + i];
+        float4 * d = reinterpret_cast<float4 *>(act + (int64_t)r * lda + gq * 16);
+#pragma unroll
+        for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+    }
 }
 
 void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
-                     int rows) {
-    dim3 grid((cols + 255) / 256, rows);
-    silu_mul_kernel<<<grid, 256, 0, s>>>(act, lda, gate, up, ld, cols);
+                     int rows, XPrepOut prep) {
+    YK_REQUIRE((cols & 15) == 0 && (lda & 3) == 0, YUUKA_ERR_UNSUPPORTED, "silu_mul: width must be a multiple of 16");
+    dim3 grid(((cols >> 4) + 127) / 128, rows);
+    silu_mul_kernel<<<grid, 128, 0, s>>>(act, lda, gate, up, ld, cols, prep);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -110,8 +135,9 @@ struct PrepParams {
 };
 
 // rmsNormInPlace (forward.go:472-482) on hd values handled by one warp, then
-// RoPE over the first rope_dim dims (forward.go:495-514).
-__device__ void norm_rope_head(float * x, const float * w, int hd, int rope_dim, double base, int pos, float eps) {
+// RoPE over the first rope_dim dims (forward.go:495-514) with the row's
+// (cos, sin) table.
+__device__ void norm_rope_head(float * x, const float * w, int hd, int rope_dim, const float2 * cs, float eps) {
     const int lane = threadIdx.x & 31;
     double sum = 0;
     for (int i = lane; i < hd; i += 32) sum += (double)x[i] * (double)x[i];
@@ -122,8 +148,7 @@ __device__ void norm_rope_head(float * x, const float * w, int hd, int rope_dim,
     __syncwarp();
     const int half = rope_dim / 2;
     for (int i = lane; i < half; i += 32) {
-        double theta = (double)pos * pow(base, -2.0 * (double)i / (double)rope_dim);
-        float c = (float)cos(theta), s = (float)sin(theta);
+        const float c = cs[i].x, s = cs[i].y;
         float x0 = x[i], x1 = x[i + half];
         x[i] = x0 * c - x1 * s;
         x[i + half] = x0 * s + x1 * c;
@@ -168,13 +193,18 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
     const int pos0 = p.rows.pos0[seq];
     const int pos = pos0 + p.rows.depth[r];
     const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    // angles in f64 as the reference computes them (forward.go:503-505), once per row
+    __shared__ float2 cs[128];
+    for (int i = threadIdx.x; i < p.rope_dim / 2; i += blockDim.x) {
+        double theta = (double)pos * pow(p.rope_base, -2.0 * (double)i / (double)p.rope_dim);
+        cs[i] = make_float2((float)cos(theta), (float)sin(theta));
+    }
+    __syncthreads();
     for (int h = warp; h < p.heads + p.kv_heads; h += nw) {
         if (h < p.heads)
-            norm_rope_head(p.q + (int64_t)r * p.ldq + (int64_t)h * 2 * p.hd, p.q_norm, p.hd, p.rope_dim, p.rope_base, pos,
-                           p.eps);
+            norm_rope_head(p.q + (int64_t)r * p.ldq + (int64_t)h * 2 * p.hd, p.q_norm, p.hd, p.rope_dim, cs, p.eps);
         else
-            norm_rope_head(p.k + (int64_t)r * p.ldk + (int64_t)(h - p.heads) * p.hd, p.k_norm, p.hd, p.rope_dim,
-                           p.rope_base, pos, p.eps);
+            norm_rope_head(p.k + (int64_t)r * p.ldk + (int64_t)(h - p.heads) * p.hd, p.k_norm, p.hd, p.rope_dim, cs, p.eps);
     }
     __syncthreads();
     // every row is stored at slot pos0 + node; the commit moves accepted rows of
@@ -195,30 +225,46 @@ void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, co
 // ---------------------------------------------------------------------------
 // gated RMSNorm of the delta-net output (model/qwen35/recurrent.go:39-50)
 
+// one thread per 16 consecutive values; a head (S values) is S/16 adjacent lanes
 __global__ void gdn_norm_gate_kernel(float * __restrict__ out, int ldo, const float * __restrict__ z, int ldz,
-                                     const float * __restrict__ norm, int rank, int S, float eps) {
+                                     const float * __restrict__ norm, int rank, int S, float eps, XPrepOut prep) {
     const int r = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (h >= rank) return;
-    float * row = out + (int64_t)r * ldo + (int64_t)h * S;
-    const float * gate = z + (int64_t)r * ldz + (int64_t)h * S;
+    const int lanes = S >> 4;                              // 8 (S = 128) or 4 (S = 64)
+    const int gq = blockIdx.x * blockDim.x + threadIdx.x;  // 16-group index within the row
+    const bool live = gq < rank * lanes;
+    const int h = live ? gq / lanes : 0, part = gq - h * lanes;
+    float * row = out + (int64_t)r * ldo + (int64_t)h * S + part * 16;
+    const float * gate = z + (int64_t)r * ldz + (int64_t)h * S + part * 16;
+    float v[16];
     double sum = 0;
-    for (int i = lane; i < S; i += 32) sum += (double)row[i] * (double)row[i];
-    sum = warp_sum_d(sum);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        v[i] = live ? row[i] : 0.0f;
+        sum += (double)v[i] * (double)v[i];
+    }
+    for (int o = 1; o < lanes; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (!live) return;
     float mean = (float)(sum / (double)S);
     float scale = (float)(1.0 / sqrt((double)(mean + eps)));
-    for (int i = lane; i < S; i += 32) {
-        float v = row[i];
-        v *= scale * norm[i];
-        row[i] = v * silu_ref(gate[i]);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        float t = v[i];
+        t *= scale * norm[part * 16 + i];
+        v[i] = t * silu_ref(gate[i]);
     }
+    float4 * d = reinterpret_cast<float4 *>(row);
+#pragma unroll
+    for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    const int cols = rank * S;
+    if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
 }
 
 void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
-                          int S, int rows, float eps) {
-    dim3 grid((rank + 3) / 4, rows);
-    gdn_norm_gate_kernel<<<grid, 128, 0, s>>>(out, ldo, z, ldz, norm, rank, S, eps);
+                          int S, int rows, float eps, XPrepOut prep) {
+    YK_REQUIRE(S == 64 || S == 128, YUUKA_ERR_UNSUPPORTED, "gdn_norm_gate: state size %d is not 64 or 128", S);
+    const int groups = rank * (S >> 4);
+    dim3 grid((groups + 127) / 128, rows);
+    gdn_norm_gate_kernel<<<grid, 128, 0, s>>>(out, ldo, z, ldz, norm, rank, S, eps, prep);
     YK_CUDA(cudaGetLastError());
 }
 

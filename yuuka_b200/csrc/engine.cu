@@ -3,6 +3,7 @@
 // prefillAllLogits) lives here behind the C ABI, so one call runs a whole
 // verify step: k+1 (or tree) rows through every layer, on-device acceptance,
 // KV / recurrent-state commit.
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -420,6 +421,7 @@ struct yuuka_session {
     uint64_t * d_anc = nullptr;
     float *x = nullptr, *xn = nullptr, *qkv_attn = nullptr, *attn_out = nullptr, *gdn_out = nullptr;
     float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
+    XPrepOut prep_xn, prep_attn, prep_gdn, prep_act;  // fp16 + group sums of the GEMM inputs
     int n_proj = 0, n_qkv = 0;
     ArgmaxScratch argmax{};
     AcceptOut acc{};
@@ -431,6 +433,15 @@ struct yuuka_session {
     uint32_t st_mode = 0;
     bool staged = false, launched = false;
     uint32_t launches = 0;
+    // captured steps, keyed by (seq0, batch, nodes, mode)
+    struct StepGraph {
+        int seq0, batch, nodes;
+        uint32_t mode;
+        cudaGraphExec_t exec;
+        uint32_t launches;
+    };
+    std::vector<StepGraph> graphs;
+    bool use_graphs = true;
     // per-op attribution (yuuka_verify_launch_profiled)
     bool profiling = false;
     std::vector<std::pair<uint32_t, cudaEvent_t>> prof;
@@ -447,13 +458,15 @@ void mark(yuuka_session * s, uint32_t code) {
     s->prof.push_back({code, e});
 }
 
-void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, float * out, int ldo, int rows, uint32_t flags) {
+void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOut prep, float * out, int ldo, int rows,
+          uint32_t flags) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     if (w.tiled) {
         TiledGemmArgs t;
         t.w = w.ptr;
         t.w_dtype = w.dtype;
         t.x = x;
+        t.xprep = prep;
         t.x_dtype = YUUKA_DTYPE_F32;
         t.ldx = ldx;
         t.out = out;
@@ -509,17 +522,17 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         const LayerW & L = m->layers[i];
         LayerState & LS = s->layers[i];
         mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, L.attn_norm, H, R, c.rms_eps);
+        launch_rmsnorm(st, s->xn, H, s->x, H, L.attn_norm, H, R, c.rms_eps, s->prep_xn);
         s->launches++;
         if (m->recurrent(i)) {
             const int np = s->n_proj;
             if (L.proj.present()) {
-                gemm(s, L.proj, s->xn, H, LS.proj, np, R, 0);
+                gemm(s, L.proj, s->xn, H, s->prep_xn, LS.proj, np, R, 0);
             } else {
-                gemm(s, L.qkv, s->xn, H, LS.proj, np, R, 0);
-                gemm(s, L.gate, s->xn, H, LS.proj + conv_dim, np, R, 0);
-                gemm(s, L.beta, s->xn, H, LS.proj + conv_dim + inner, np, R, 0);
-                gemm(s, L.alpha, s->xn, H, LS.proj + conv_dim + inner + rank, np, R, 0);
+                gemm(s, L.qkv, s->xn, H, s->prep_xn, LS.proj, np, R, 0);
+                gemm(s, L.gate, s->xn, H, s->prep_xn, LS.proj + conv_dim, np, R, 0);
+                gemm(s, L.beta, s->xn, H, s->prep_xn, LS.proj + conv_dim + inner, np, R, 0);
+                gemm(s, L.alpha, s->xn, H, s->prep_xn, LS.proj + conv_dim + inner + rank, np, R, 0);
             }
             GdnArgs g;
             g.proj = LS.proj;
@@ -541,21 +554,21 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             mark(s, YUUKA_OP_GDN_SCAN);
             launch_gdn_scan(st, g, rows);
             mark(s, YUUKA_OP_GDN_NORM_GATE);
-            launch_gdn_norm_gate(st, s->gdn_out, inner, LS.proj + conv_dim, np, L.ssm_norm, rank, S, R, c.rms_eps);
+            launch_gdn_norm_gate(st, s->gdn_out, inner, LS.proj + conv_dim, np, L.ssm_norm, rank, S, R, c.rms_eps, s->prep_gdn);
             s->launches += 2;
-            gemm(s, L.out, s->gdn_out, inner, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+            gemm(s, L.out, s->gdn_out, inner, s->prep_gdn, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
         } else {
             const int nq = s->n_qkv;
             float * qb = s->qkv_attn;
             float * kb = qb + q_dim;
             float * vb = kb + kv_dim;
             if (L.qk.present()) {
-                gemm(s, L.qk, s->xn, H, qb, nq, R, 0);
-                if (!L.qk_has_v) gemm(s, L.v, s->xn, H, vb, nq, R, 0);
+                gemm(s, L.qk, s->xn, H, s->prep_xn, qb, nq, R, 0);
+                if (!L.qk_has_v) gemm(s, L.v, s->xn, H, s->prep_xn, vb, nq, R, 0);
             } else {
-                gemm(s, L.q, s->xn, H, qb, nq, R, 0);
-                gemm(s, L.k, s->xn, H, kb, nq, R, 0);
-                gemm(s, L.v, s->xn, H, vb, nq, R, 0);
+                gemm(s, L.q, s->xn, H, s->prep_xn, qb, nq, R, 0);
+                gemm(s, L.k, s->xn, H, s->prep_xn, kb, nq, R, 0);
+                gemm(s, L.v, s->xn, H, s->prep_xn, vb, nq, R, 0);
             }
             KvPool pool;
             pool.k = LS.k;
@@ -586,36 +599,36 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
                        YUUKA_ERR_INTERNAL, "attention scratch is too small");
             mark(s, YUUKA_OP_ATTENTION);
             s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
-                                            max_total, sc);
-            gemm(s, L.o, s->attn_out, o_dim, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+                                            max_total, sc, s->prep_attn);
+            gemm(s, L.o, s->attn_out, o_dim, s->prep_attn, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
         }
         // forwardFFN (model/qwen35/forward.go:295-315)
         mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, L.post_norm, H, R, c.rms_eps);
+        launch_rmsnorm(st, s->xn, H, s->x, H, L.post_norm, H, R, c.rms_eps, s->prep_xn);
         s->launches++;
         if (L.gate_up.present()) {
-            gemm(s, L.gate_up, s->xn, H, s->gate_up, 2 * F, R, 0);
+            gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
         } else {
-            gemm(s, L.ffn_gate, s->xn, H, s->gate_up, 2 * F, R, 0);
-            gemm(s, L.ffn_up, s->xn, H, s->gate_up + F, 2 * F, R, 0);
+            gemm(s, L.ffn_gate, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
+            gemm(s, L.ffn_up, s->xn, H, s->prep_xn, s->gate_up + F, 2 * F, R, 0);
         }
         mark(s, YUUKA_OP_SILU_MUL);
-        launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R);
+        launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R, s->prep_act);
         s->launches++;
-        gemm(s, L.ffn_down, s->act, F, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+        gemm(s, L.ffn_down, s->act, F, s->prep_act, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
     }
     // tail: final norm + LM head over the wanted rows (forward.go:147-151)
     if (logit_rows == LOGITS_ALL) {
         mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, m->output_norm, H, R, c.rms_eps);
+        launch_rmsnorm(st, s->xn, H, s->x, H, m->output_norm, H, R, c.rms_eps, s->prep_xn);
         s->launches++;
-        gemm(s, m->output, s->xn, H, s->logits, c.vocab, R, 0);
+        gemm(s, m->output, s->xn, H, s->prep_xn, s->logits, c.vocab, R, 0);
     } else if (logit_rows == LOGITS_LAST) {
         // batch == 1: only the last row
         mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x + (int64_t)(R - 1) * H, H, m->output_norm, H, 1, c.rms_eps);
+        launch_rmsnorm(st, s->xn, H, s->x + (int64_t)(R - 1) * H, H, m->output_norm, H, 1, c.rms_eps, s->prep_xn);
         s->launches++;
-        gemm(s, m->output, s->xn, H, s->logits + (int64_t)(R - 1) * c.vocab, c.vocab, 1, 0);
+        gemm(s, m->output, s->xn, H, s->prep_xn, s->logits + (int64_t)(R - 1) * c.vocab, c.vocab, 1, 0);
     }
     // acceptance + commit
     if (mode == YUUKA_ACCEPT_NONE) return;
@@ -694,10 +707,12 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
     YK_CUDA(cudaStreamSynchronize(st));  // the host vectors go out of scope
 }
 
+// Key-range bound used to size the attention grid. It is the session capacity,
+// not the current positions, so that a captured step stays valid as sequences grow;
+// CTAs whose key range is empty return at once.
 int max_total_keys(const yuuka_session * s, int seq0, int batch, int nodes) {
-    int mx = 0;
-    for (int b = 0; b < batch; b++) mx = s->h_pos_upper[seq0 + b] > mx ? s->h_pos_upper[seq0 + b] : mx;
-    return mx + nodes;
+    (void)seq0; (void)batch; (void)nodes;
+    return s->cfg.capacity;
 }
 
 // Runs tokens of one sequence as committed chain chunks (Forward / PrefillLogits).
@@ -717,7 +732,7 @@ void run_chain(yuuka_session * s, int seq, const int32_t * tokens, int n, float 
         stage_rows(s, seq, 1, chunk, tokens + done, nullptr);
         LogitRows lr = all_logits ? LOGITS_ALL : (last && last_logits ? LOGITS_LAST : LOGITS_NONE);
         s->launches = 0;
-        run_step(s, seq, 1, chunk, 3u /* forced commit */, lr, s->h_pos[seq] + chunk);
+        run_step(s, seq, 1, chunk, 3u /* forced commit */, lr, s->cfg.capacity);
         sync_and_check(s);
         if (all_logits)
             YK_CUDA(cudaMemcpy(all_logits + (int64_t)done * V, s->logits, sizeof(float) * (size_t)chunk * V,
@@ -772,6 +787,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
         try {
             s->model = model;
             s->cfg = sc;
+            if (const char * e = getenv("YUUKA_CUDA_NO_GRAPH")) s->use_graphs = !(e[0] == '1');
             s->stream.dev = model->dev;
             YK_CUDA(cudaStreamCreateWithFlags(&s->stream.s, cudaStreamNonBlocking));
             const int kv_dim = model->kv_dim();
@@ -829,6 +845,18 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->gdn_out = dalloc<float>((size_t)R * c.inner_size, s->owned);
             s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
             s->act = dalloc<float>((size_t)R * c.ffn, s->owned);
+            auto prep_alloc = [&](int width) {
+                XPrepOut o;
+                if (width % 16 == 0) {
+                    o.xh = dalloc<__half>((size_t)R * width, s->owned);
+                    o.xs16 = dalloc<__half2>((size_t)R * (width / 16) + 4, s->owned);
+                }
+                return o;
+            };
+            s->prep_xn = prep_alloc(H);
+            s->prep_attn = prep_alloc(model->o_dim());
+            s->prep_gdn = prep_alloc(c.inner_size);
+            s->prep_act = prep_alloc(c.ffn);
             if (sc.want_logits) s->logits = dalloc<float>((size_t)R * c.vocab, s->owned);
             s->argmax.chunks = argmax_chunks(c.vocab);
             s->argmax.val = dalloc<float>((size_t)R * s->argmax.chunks, s->owned);
@@ -863,6 +891,7 @@ void yuuka_session_destroy(yuuka_session * s) {
         cudaStreamSynchronize(s->stream.s);
         cudaStreamDestroy(s->stream.s);
     }
+    for (auto & g : s->graphs) cudaGraphExecDestroy(g.exec);
     for (void * p : s->owned) cudaFree(p);
     gemm_scratch_free(s->gemm);
     delete s;
@@ -988,9 +1017,37 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
     return guard([&] {
         YK_REQUIRE(s && s->staged, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: no staged step");
         set_device(s->model->dev);
-        s->launches = 0;
-        run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL,
-                 max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes));
+        const int max_total = max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes);
+        if (!s->use_graphs) {
+            s->launches = 0;
+            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total);
+        } else {
+            yuuka_session::StepGraph * gr = nullptr;
+            for (auto & g : s->graphs)
+                if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.mode == s->st_mode) gr = &g;
+            if (!gr) {
+                // first step of this shape: capture the kernel sequence once, replay it afterwards
+                s->launches = 0;
+                YK_CUDA(cudaStreamBeginCapture(s->stream.s, cudaStreamCaptureModeThreadLocal));
+                cudaGraph_t graph = nullptr;
+                try {
+                    run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total);
+                } catch (...) {
+                    cudaStreamEndCapture(s->stream.s, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                YK_CUDA(cudaStreamEndCapture(s->stream.s, &graph));
+                cudaGraphExec_t exec = nullptr;
+                cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
+                cudaGraphDestroy(graph);
+                YK_CUDA(err);
+                s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, exec, s->launches});
+                gr = &s->graphs.back();
+            }
+            s->launches = gr->launches;
+            YK_CUDA(cudaGraphLaunch(gr->exec, s->stream.s));
+        }
         if (s->st_mode != YUUKA_ACCEPT_NONE)
             for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
         s->launched = true;

@@ -18,11 +18,12 @@ constexpr int GDN_COLS = 32;   // state columns per CTA (one per lane)
 constexpr int GDN_WARPS = 4;   // state rows are split over the warps
 constexpr int GDN_MAX_NODES = 64;
 
-__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + (float)exp((double)-x)); }
+// float exp: the CPU reference evaluates exp in f64 and rounds; the difference is below 2e-7 relative
+__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_ref(float x) { return x * sigmoid_ref(x); }
 __device__ __forceinline__ float softplus_ref(float x) {
     if (x > 20.0f) return x;
-    return (float)log1p(exp((double)x));
+    return log1pf(expf(x));
 }
 
 // One state update, the same expression in the scan and in the commit so both
@@ -36,39 +37,40 @@ struct ScanParams {
     RowMeta rows;
 };
 
-// Depthwise causal conv + SiLU for channel c of row (seq, node): taps run over
-// the row's ancestors, then into the stored conv history (forward.go:253-268).
-__device__ float conv_channel(const ScanParams & p, int seq, int node, int c) {
-    const GdnArgs & a = p.a;
-    const int N = p.rows.nodes, kernel = a.kernel;
-    const float * w = a.conv_w + (int64_t)c * kernel;
-    const float * hist = a.conv_state + ((int64_t)seq * (2 * a.groups * a.S + a.rank * a.S) + c) * (kernel - 1);
+// Depthwise causal conv + SiLU for local channel lc of row node, from the staged
+// raw inputs: taps run over the row's ancestors, then into the stored conv
+// history (forward.go:253-268). raw is [N + kernel-1][NCH]: rows 0..kernel-2
+// hold the history (oldest first), row kernel-1+i holds node i.
+template <int NCH>
+__device__ __forceinline__ float conv_channel(const float * raw, const float * w, const int * par, int kernel, int node,
+                                              int lc) {
     float taps[8];
-    // taps[kernel-1] = this row, taps[kernel-2] = parent, ...
-    int cur = node, t = kernel - 1, hidx = kernel - 2;
-    while (t >= 0) {
+    int cur = node, hidx = kernel - 2;
+    for (int t = kernel - 1; t >= 0; t--) {
         if (cur >= 0) {
-            taps[t] = a.proj[(int64_t)(seq * N + cur) * a.ldp + c];
-            cur = p.rows.parent[seq * N + cur];
+            taps[t] = raw[(kernel - 1 + cur) * NCH + lc];
+            cur = par[cur];
         } else {
-            taps[t] = hist[hidx--];
+            taps[t] = raw[hidx-- * NCH + lc];
         }
-        t--;
     }
     float sum = 0.0f;
-    for (int i = 0; i < kernel - 1; i++) sum += w[i] * taps[i];
-    sum += w[kernel - 1] * taps[kernel - 1];
+    for (int i = 0; i < kernel - 1; i++) sum += w[lc * kernel + i] * taps[i];
+    sum += w[lc * kernel + kernel - 1] * taps[kernel - 1];
     return silu_ref(sum);
 }
 
 template <int S>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
-    constexpr int RPW = S / GDN_WARPS;  // state rows per warp
+    constexpr int RPW = S / GDN_WARPS;        // state rows per warp
+    constexpr int NCH = 2 * S + GDN_COLS;     // channels this CTA needs: q[S] | k[S] | v[GDN_COLS]
     const GdnArgs & a = p.a;
     const int cb = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
     const int N = p.rows.nodes;
     const int kh = h % a.groups;
     const int key_dim = a.groups * S;
+    const int conv_dim = 2 * key_dim + a.rank * S;
+    const int K1 = a.kernel - 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = cb * GDN_COLS + lane;
 
@@ -80,26 +82,50 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     float * dec = dd + N * GDN_COLS;      // [N]
     float * bet = dec + N;                // [N]
     float * red = bet + N;                // [GDN_WARPS][GDN_COLS]
-    __shared__ double nrm[2 * GDN_MAX_NODES];
+    float * red2 = red + GDN_WARPS * GDN_COLS;
+    float * raw = red2 + GDN_WARPS * GDN_COLS;   // [K1 + N][NCH] raw inputs of this CTA's channels
+    float * wts = raw + (K1 + N) * NCH;           // [NCH][kernel]
+    int * par = reinterpret_cast<int *>(wts + NCH * a.kernel);  // [N]
+    __shared__ float nrm[2 * GDN_MAX_NODES];  // 1 / sqrt(sum of squares + eps) of q then k rows
 
-    // ---- front end: conv + SiLU, L2 norm of q and k, beta, decay ----
-    for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
-        int node = i / S, e = i - node * S;
-        qn[i] = conv_channel(p, seq, node, kh * S + e);
-        kn[i] = conv_channel(p, seq, node, key_dim + kh * S + e);
+    // The recurrent state does not depend on this step's projections: start its loads first.
+    const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + warp * RPW) * S + col;
+    float st[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
+
+    // ---- stage raw inputs, history, taps and parents with coalesced loads ----
+    auto channel = [&](int lc) {  // local channel -> channel of the conv row
+        return lc < S ? kh * S + lc : (lc < 2 * S ? key_dim + kh * S + (lc - S) : 2 * key_dim + h * S + cb * GDN_COLS + (lc - 2 * S));
+    };
+    for (int i = threadIdx.x; i < N * NCH; i += blockDim.x) {
+        const int node = i / NCH, lc = i - node * NCH;
+        raw[(K1 + node) * NCH + lc] = a.proj[(int64_t)(seq * N + node) * a.ldp + channel(lc)];
     }
-    for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
-        int node = i / GDN_COLS, e = i - node * GDN_COLS;
-        vv[i] = conv_channel(p, seq, node, 2 * key_dim + h * S + cb * GDN_COLS + e);
+    for (int i = threadIdx.x; i < NCH * K1; i += blockDim.x) {
+        const int lc = i / K1, t = i - lc * K1;
+        raw[t * NCH + lc] = a.conv_state[((int64_t)seq * conv_dim + channel(lc)) * K1 + t];
+    }
+    for (int i = threadIdx.x; i < NCH * a.kernel; i += blockDim.x) {
+        const int lc = i / a.kernel, t = i - lc * a.kernel;
+        wts[i] = a.conv_w[(int64_t)channel(lc) * a.kernel + t];
     }
     for (int node = threadIdx.x; node < N; node += blockDim.x) {
+        par[node] = p.rows.parent[seq * N + node];
         const float * row = a.proj + (int64_t)(seq * N + node) * a.ldp;
-        const int conv_dim = 2 * key_dim + a.rank * S;
-        float b = row[conv_dim + a.rank * S + h];
-        float al = row[conv_dim + a.rank * S + a.rank + h];
+        const float b = row[conv_dim + a.rank * S + h];
+        const float al = row[conv_dim + a.rank * S + a.rank + h];
         bet[node] = sigmoid_ref(b);
-        float log_decay = softplus_ref(al + a.dt[h]) * a.a[h];
-        dec[node] = (float)exp((double)log_decay);
+        dec[node] = expf(softplus_ref(al + a.dt[h]) * a.a[h]);
+    }
+    __syncthreads();
+    // ---- front end: conv + SiLU ----
+    for (int i = threadIdx.x; i < N * NCH; i += blockDim.x) {
+        const int node = i / NCH, lc = i - node * NCH;
+        const float v = conv_channel<NCH>(raw, wts, par, a.kernel, node, lc);
+        if (lc < S) qn[node * S + lc] = v;
+        else if (lc < 2 * S) kn[node * S + lc - S] = v;
+        else vv[node * GDN_COLS + lc - 2 * S] = v;
     }
     __syncthreads();
     // l2NormHead (forward.go:484-493): f64 sum, scale = f32(1/sqrt(sum + eps)) * extra
@@ -109,15 +135,15 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         for (int i = lane; i < S; i += 32) sum += (double)x[i] * (double)x[i];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) nrm[v] = sum;
+        if (lane == 0) nrm[v] = (float)(1.0 / sqrt(sum + (double)a.eps));
     }
     __syncthreads();
     {
         const float q_scale = (float)(1.0 / sqrt((double)S));
         for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
             int node = i / S;
-            qn[i] *= (float)(1.0 / sqrt(nrm[node] + (double)a.eps)) * q_scale;
-            kn[i] *= (float)(1.0 / sqrt(nrm[N + node] + (double)a.eps)) * 1.0f;
+            qn[i] *= nrm[node] * q_scale;
+            kn[i] *= nrm[N + node] * 1.0f;
         }
     }
     __syncthreads();
@@ -131,21 +157,17 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         for (int node = threadIdx.x; node < N; node += blockDim.x) a.decay[(int64_t)(seq * N + node) * a.rank + h] = dec[node];
 
     // ---- recurrence: this thread holds rows [warp*RPW, +RPW) of column col ----
-    const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + warp * RPW) * S + col;
-    float st[RPW];
     int cur = -1;  // node whose state st currently holds (-1: the stored state)
-#pragma unroll
-    for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
 
     for (int node = 0; node < N; node++) {
-        const int par = p.rows.parent[seq * N + node];
-        if (par != cur) {
+        const int pnode = par[node];
+        if (pnode != cur) {
             // a sibling branch: rebuild the parent's state from the stored one
             // by replaying the log of the parent's path
 #pragma unroll
             for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
             int path[GDN_MAX_NODES], len = 0;
-            for (int c = par; c >= 0; c = p.rows.parent[seq * N + c]) path[len++] = c;
+            for (int c = pnode; c >= 0; c = par[c]) path[len++] = c;
             for (int j = len - 1; j >= 0; j--) {
                 const int c = path[j];
                 const float dc = dec[c], dv = dd[c * GDN_COLS + lane];
@@ -172,18 +194,17 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
             st[i] = state_update(st[i], dc, kx[i], d);
             o = fmaf(st[i], qx[i], o);
         }
-        __syncthreads();
-        red[warp * GDN_COLS + lane] = o;
+        red2[warp * GDN_COLS + lane] = o;
         if (warp == 0) dd[node * GDN_COLS + lane] = d;
         __syncthreads();
+        // red is rewritten only after the next barrier, red2 only after the one after that
         if (warp == 0) {
             o = 0.0f;
 #pragma unroll
-            for (int w = 0; w < GDN_WARPS; w++) o += red[w * GDN_COLS + lane];
+            for (int w = 0; w < GDN_WARPS; w++) o += red2[w * GDN_COLS + lane];
             a.out[(int64_t)(seq * N + node) * (a.rank * S) + h * S + col] = o;
             a.dlog[(int64_t)(seq * N + node) * (a.rank * S) + h * S + col] = d;
         }
-        __syncthreads();
         cur = node;
     }
 }
@@ -193,7 +214,9 @@ void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
     ScanParams p{a, rows};
     const int N = rows.nodes;
-    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + GDN_WARPS * GDN_COLS);
+    const int nch = 2 * a.S + GDN_COLS;
+    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS +
+                                   (size_t)(a.kernel - 1 + N) * nch + (size_t)nch * a.kernel + N);
     dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

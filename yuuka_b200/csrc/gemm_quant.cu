@@ -17,7 +17,7 @@ int read_device_error(const yuuka_device * dev) {
     set_device(dev);
     int v = 0;
     YK_CUDA(cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)));
-    return v;
+    return v | read_gemm_wait_expired();
 }
 
 // ===========================================================================
@@ -134,6 +134,18 @@ void gemm_scratch_reserve(const yuuka_device * dev, GemmScratch & s, uint32_t w_
                    (unsigned long long)(want * 4));
         s.partial_floats = want;
     }
+    const uint64_t xneed = tiled_supported(w_dtype, n_in) ? (uint64_t)rows * n_in : 0;
+    if (xneed > s.xh_elems) {
+        if (s.xh) cudaFree(s.xh);
+        if (s.xs16) cudaFree(s.xs16);
+        s.xh = nullptr;
+        s.xs16 = nullptr;
+        s.xh_elems = 0;
+        cudaError_t err = cudaMalloc(&s.xh, xneed * sizeof(__half));
+        if (err == cudaSuccess) err = cudaMalloc(&s.xs16, xneed / 16 * sizeof(__half2) + 16);
+        YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "gemm activation scratch allocation failed");
+        s.xh_elems = xneed;
+    }
     if (tiles > s.counter_count) {
         if (s.counters) cudaFree(s.counters);
         s.counters = nullptr;
@@ -148,6 +160,8 @@ void gemm_scratch_reserve(const yuuka_device * dev, GemmScratch & s, uint32_t w_
 void gemm_scratch_free(GemmScratch & s) {
     if (s.partial) cudaFree(s.partial);
     if (s.counters) cudaFree(s.counters);
+    if (s.xh) cudaFree(s.xh);
+    if (s.xs16) cudaFree(s.xs16);
     s = GemmScratch();
 }
 

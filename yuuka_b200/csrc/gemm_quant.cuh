@@ -1,6 +1,8 @@
 // Host interface of the quantized GEMM kernels (gemm_quant.cu).
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace yk {
@@ -8,8 +10,11 @@ namespace yk {
 struct GemmScratch {
     float * partial = nullptr;   // split-K partial sums [parts][rows][n_out]
     uint64_t partial_floats = 0;
-    int * counters = nullptr;    // one arrival counter per 128-row tile, zero between launches
+    int * counters = nullptr;    // one arrival counter per tile group, zero between launches
     int counter_count = 0;
+    __half * xh = nullptr;       // prepared activations of a launch whose caller passed f32 / bf16
+    __half2 * xs16 = nullptr;
+    uint64_t xh_elems = 0;
 };
 
 struct GemmArgs {

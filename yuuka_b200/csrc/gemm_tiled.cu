@@ -21,6 +21,7 @@
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
 #include "gemm_tiled.cuh"
 #include "quant.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -33,6 +34,11 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 * p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void * p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// asks L2 for bytes [0, bytes) at base, one 128-byte line per lane and step
+__device__ __forceinline__ void prefetch_l2_range(const uint8_t * base, int bytes, int lane) {
+    for (int off = lane * 128; off < bytes; off += 32 * 128) prefetch_l2(base + off);
 }
 __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
@@ -72,33 +78,58 @@ __device__ __forceinline__ uint32_t bytes23_h2(uint32_t v) { return __byte_perm(
 __device__ __forceinline__ uint32_t bytes02_h2(uint32_t v) { return __byte_perm(v, 0x64646464u, 0x4240); }
 __device__ __forceinline__ uint32_t bytes13_h2(uint32_t v) { return __byte_perm(v, 0x64646464u, 0x4341); }
 
+template <typename XT> __device__ __forceinline__ float xf(XT v);
+template <> __device__ __forceinline__ float xf<float>(float v) { return v; }
+template <> __device__ __forceinline__ float xf<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// eight consecutive activations (16-byte aligned) as floats
+__device__ __forceinline__ void load8(const float * src, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 * src, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+}
+
 // ===========================================================================
-// Record layouts. map(p) gives, for byte p of a record, the source row (0..15)
-// and the byte offset inside that row's superblock.
+// Record layouts.
+//
+// Element order. Inside a superblock, sub-block k (32 elements) is split over
+// the four lanes t that share a weight row: lane t holds elements 32k + 8t + b,
+// b = 0..7, i.e. MMA (k, h) takes elements 32k + 8t + 4h + {0,1,2,3} from lane
+// t. Activations therefore stay in natural order: the B fragments of MMAs
+// (k,0) and (k,1) are the 16 bytes x[32k + 8t .. 32k + 8t + 7]. A 4-byte weight
+// word stores its four elements in byte order (0, 2, 1, 3) so that the masks
+// 0x000f000f / (>>8) give the (k-lo, k-hi) halves of an A fragment directly.
+//
+// map(p) gives, for byte p of a record, the source row (0..15) and the byte
+// offset inside that row's superblock in the GGUF layout.
 
 template <int DT> struct Codec;
 
-// weight slot q = i*32 + lane: row g + 8*(i / per_half), 16-byte chunk t + 4*(i % per_half)
-__device__ __forceinline__ void slot_row_chunk(int q, int per_half, int & r, int & c) {
-    int i = q >> 5, lane = q & 31;
-    r = (lane >> 2) + 8 * (i / per_half);
-    c = (lane & 3) + 4 * (i % per_half);
+__device__ __forceinline__ int elem_in_chunk8(int c8) {  // byte position 0..7 of an 8-byte piece -> element b
+    const int h = c8 >> 2, pos = c8 & 3;
+    return 4 * h + ((pos & 1) * 2 + (pos >> 1));  // pos 0,1,2,3 -> element 0,2,1,3
 }
 
 template <> struct Codec<YUUKA_DTYPE_Q4_K> {
-    static constexpr int SB = 144, REC = 16 * SB, NSUB = 8, TAB = 1024 + 512;
+    static constexpr int SB = 144, REC = 16 * SB;
+    static constexpr int SCL_STRIDE = 80, MN_STRIDE = 48, MN_OFF = 16 * SCL_STRIDE, TAB = MN_OFF + 16 * MN_STRIDE;
     struct Regs { uint4 q[4]; uint4 hdr; };
     __device__ static void map(int p, int & r, int & o) {
-        if (p < 2048) { int c; slot_row_chunk(p >> 4, 2, r, c); o = 16 + 16 * c + (p & 15); }
-        else { r = (p - 2048) >> 4; o = p & 15; }
+        if (p < 2048) {
+            const int q = p >> 4, c16 = p & 15, i = q >> 5, lane = q & 31, g = lane >> 2, t = lane & 3;
+            const int j = 2 * (i & 1) + (c16 >> 3);
+            r = g + 8 * (i >> 1);
+            o = 16 + 32 * j + 8 * t + elem_in_chunk8(c16 & 7);
+        } else { r = (p - 2048) >> 4; o = p & 15; }
     }
-    // element of the superblock that MMA (cc, n, w), lane t, slot s carries
-    __device__ static int pair_slot(int e8, int & t) {  // e8: element / 8 within the superblock
-        int e = e8 * 8, j = e >> 6, n = (e >> 5) & 1, tl = (e >> 4) & 1, wp = (e >> 3) & 1;
-        t = 2 * (j & 1) + tl;
-        return (j >> 1) * 4 + n * 2 + wp;
-    }
-    __device__ static int sub_of(int e) { return e >> 5; }
     __device__ static void load(const uint8_t * rec, int lane, Regs & r) {
         const uint4 * p = reinterpret_cast<const uint4 *>(rec);
 #pragma unroll
@@ -108,71 +139,69 @@ template <> struct Codec<YUUKA_DTYPE_Q4_K> {
 };
 
 template <> struct Codec<YUUKA_DTYPE_Q5_K> {
-    static constexpr int SB = 176, REC = 16 * SB, NSUB = 8, TAB = 1024 + 512;
-    struct Regs { uint4 q[4]; uint4 qh[2]; uint4 hdr; };
+    static constexpr int SB = 176, REC = 16 * SB;
+    static constexpr int SCL_STRIDE = 80, MN_STRIDE = 48, MN_OFF = 16 * SCL_STRIDE, TAB = MN_OFF + 16 * MN_STRIDE;
+    struct Regs { uint4 q[4]; uint4 qh; uint4 hdr; };
     __device__ static void map(int p, int & r, int & o) {
-        if (p < 2048) { int c; slot_row_chunk(p >> 4, 2, r, c); o = 48 + 16 * c + (p & 15); }
-        else if (p < 2560) { r = (p - 2048) >> 5; o = 16 + ((p - 2048) & 31); }
-        else { r = (p - 2560) >> 4; o = p & 15; }
+        if (p < 2048) {
+            const int q = p >> 4, c16 = p & 15, i = q >> 5, lane = q & 31, g = lane >> 2, t = lane & 3;
+            const int j = 2 * (i & 1) + (c16 >> 3);
+            r = g + 8 * (i >> 1);
+            o = 48 + 32 * j + 8 * t + elem_in_chunk8(c16 & 7);
+        } else if (p < 2560) {
+            const int lane = (p - 2048) >> 4, c16 = p & 15, g = lane >> 2, t = lane & 3;
+            r = g + 8 * (c16 >> 3);
+            o = 16 + 8 * t + elem_in_chunk8(c16 & 7);
+        } else { r = (p - 2560) >> 4; o = p & 15; }
     }
-    __device__ static int pair_slot(int e8, int & t) { return Codec<YUUKA_DTYPE_Q4_K>::pair_slot(e8, t); }
-    __device__ static int sub_of(int e) { return e >> 5; }
     __device__ static void load(const uint8_t * rec, int lane, Regs & r) {
         const uint4 * p = reinterpret_cast<const uint4 *>(rec);
-        const int g = lane >> 2, t = lane & 3;
 #pragma unroll
         for (int i = 0; i < 4; i++) r.q[i] = ldg_stream(p + i * 32 + lane);
-        r.qh[0] = ldg_stream(p + 128 + g * 2 + (t & 1));
-        r.qh[1] = ldg_stream(p + 128 + (g + 8) * 2 + (t & 1));
+        r.qh = ldg_stream(p + 128 + lane);
         r.hdr = ldg_stream(p + 160 + (lane & 15));
     }
 };
 
 template <> struct Codec<YUUKA_DTYPE_Q6_K> {
-    static constexpr int SB = 210, REC = 16 * SB, NSUB = 16, TAB = 2048 + 1024;
-    struct Regs { uint4 ql[4]; uint4 qh[4]; uint4 sc; uint32_t d; };
+    static constexpr int SB = 210, REC = 16 * SB;
+    static constexpr int SCL_STRIDE = 144, MN_STRIDE = 80, MN_OFF = 16 * SCL_STRIDE, TAB = MN_OFF + 16 * MN_STRIDE;
+    struct Regs { uint4 ql[4]; uint4 qh[2]; uint4 sc; uint32_t d; };
     __device__ static void map(int p, int & r, int & o) {
-        if (p < 2048) { int c; slot_row_chunk(p >> 4, 2, r, c); o = 16 * c + (p & 15); }
-        else if (p < 3072) {
-            int idx = (p - 2048) >> 4, h2 = idx & 1, g = (idx >> 1) & 7, i = idx >> 4;
+        if (p < 2048) {
+            const int q = p >> 4, c16 = p & 15, i = q >> 5, lane = q & 31, g = lane >> 2, t = lane & 3;
             r = g + 8 * (i >> 1);
-            o = 128 + 32 * (i & 1) + 16 * h2 + (p & 15);
+            o = 64 * (i & 1) + 32 * (c16 >> 3) + 8 * t + elem_in_chunk8(c16 & 7);
+        } else if (p < 3072) {
+            const int q = (p - 2048) >> 4, c16 = p & 15, lane = q & 31, g = lane >> 2, t = lane & 3;
+            r = g + 8 * (q >> 5);
+            o = 128 + 32 * (c16 >> 3) + 8 * t + elem_in_chunk8(c16 & 7);
         } else if (p < 3328) { r = (p - 3072) >> 4; o = 192 + (p & 15); }
         else { r = (p - 3328) >> 1; o = 208 + (p & 1); }
     }
-    __device__ static int pair_slot(int e8, int & t) {
-        int e = e8 * 8, cc = e >> 7, g4 = (e >> 5) & 3, tl = (e >> 4) & 1, wp = (e >> 3) & 1;
-        t = 2 * (g4 & 1) + tl;
-        return cc * 4 + (g4 >> 1) * 2 + wp;
-    }
-    __device__ static int sub_of(int e) { return e >> 4; }
     __device__ static void load(const uint8_t * rec, int lane, Regs & r) {
         const uint4 * p = reinterpret_cast<const uint4 *>(rec);
-        const int g = lane >> 2, t = lane & 3;
 #pragma unroll
         for (int i = 0; i < 4; i++) r.ql[i] = ldg_stream(p + i * 32 + lane);
-#pragma unroll
-        for (int i = 0; i < 4; i++) r.qh[i] = ldg_stream(p + 128 + (i * 8 + g) * 2 + (t & 1));
+        r.qh[0] = ldg_stream(p + 128 + lane);
+        r.qh[1] = ldg_stream(p + 160 + lane);
         r.sc = ldg_stream(p + 192 + (lane & 15));
         r.d = __ldg(reinterpret_cast<const uint16_t *>(rec + 3328) + (lane & 15));
     }
 };
 
 template <> struct Codec<YUUKA_DTYPE_Q8_0> {
-    static constexpr int SB = 272, REC = 16 * SB, NSUB = 8, TAB = 1024 + 512;
+    static constexpr int SB = 272, REC = 16 * SB;
+    static constexpr int SCL_STRIDE = 48, MN_OFF = 0, TAB = 16 * SCL_STRIDE;
     struct Regs { uint4 q[8]; uint4 d; };
     __device__ static void map(int p, int & r, int & o) {
         if (p < 4096) {
-            int c; slot_row_chunk(p >> 4, 4, r, c);
-            o = 34 * (c >> 1) + 2 + 16 * (c & 1) + (p & 15);
-        } else { r = (p - 4096) >> 4; int k = (p & 15) >> 1; o = 34 * k + (p & 1); }
+            const int q = p >> 4, c16 = p & 15, i = q >> 5, lane = q & 31, g = lane >> 2, t = lane & 3;
+            const int k = 2 * (i & 3) + (c16 >> 3);
+            r = g + 8 * (i >> 2);
+            o = 34 * k + 2 + 8 * t + elem_in_chunk8(c16 & 7);
+        } else { r = (p - 4096) >> 4; const int k = (p & 15) >> 1; o = 34 * k + (p & 1); }
     }
-    __device__ static int pair_slot(int e8, int & t) {
-        int e = e8 * 8, b = e >> 5, tl = (e >> 4) & 1, wp = (e >> 3) & 1;
-        t = 2 * (b & 1) + tl;
-        return (b >> 1) * 2 + wp;
-    }
-    __device__ static int sub_of(int e) { return e >> 5; }
     __device__ static void load(const uint8_t * rec, int lane, Regs & r) {
         const uint4 * p = reinterpret_cast<const uint4 *>(rec);
 #pragma unroll
@@ -222,18 +251,44 @@ void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uin
 }
 
 // ===========================================================================
+// Prepared activations: fp16 copy of x in natural order plus, per 16 elements,
+// the sum of the rounded values as a (hi, lo) half pair. The MMA kernels read
+// only this form; row-wise producer kernels can emit it directly.
+
+template <typename XT>
+__global__ void xprep_kernel(__half * __restrict__ xh, __half2 * __restrict__ xs16, const XT * __restrict__ x, int64_t ldx,
+                             int K, int M) {
+    const int groups = K >> 4;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * groups; i += gridDim.x * blockDim.x) {
+        const int m = i / groups, gq = i - m * groups;
+        float v[16];
+        load8(x + (int64_t)m * ldx + gq * 16, *reinterpret_cast<float(*)[8]>(v));
+        load8(x + (int64_t)m * ldx + gq * 16 + 8, *reinterpret_cast<float(*)[8]>(v + 8));
+        xprep_store16(xh + (int64_t)m * K + gq * 16, xs16 + (int64_t)m * groups + gq, v);
+    }
+}
+
+template <typename XT>
+static void launch_xprep(cudaStream_t s, __half * xh, __half2 * xs16, const XT * x, int64_t ldx, int K, int M) {
+    const int total = M * (K / 16);
+    xprep_kernel<XT><<<(total + 127) / 128, 128, 0, s>>>(xh, xs16, x, ldx, K, M);
+    YK_CUDA(cudaGetLastError());
+}
+
+// ===========================================================================
 // header decode -> per-warp tables, and the per-superblock MMA sequence
 
-// Q4_K / Q5_K header word layout: hdr.x = d | dmin << 16, hdr.y/z/w = 12 scale bytes.
-// Table: scl[row][pair j] = {s_lo, -1024 s_lo, s_hi/16, -64 s_hi} (half2 each, 16 B), mn2[row][sub] = (-min, -min).
+// Q4_K / Q5_K header: hdr.x = d | dmin << 16, hdr.y/z/w = 12 scale bytes.
+// scl[row][pair j] = {s_lo, -1024 s_lo, s_hi/16, -64 s_hi} (half2 each); mn2[row][sub] = (-min, -min).
+template <typename C>
 __device__ __forceinline__ void header_k4(const uint4 & hdr, int lane, uint8_t * tab) {
     const int r = lane & 15, hf = lane >> 4;  // hf: pairs 2hf, 2hf+1
     const uint32_t d2 = dup_lo(hdr.x), dm2 = dup_hi(hdr.x);
     const uint32_t w0 = hdr.y, w1 = hdr.z, w2 = hdr.w;
     const uint32_t sc4 = hf ? ((w2 & 0x0f0f0f0fu) | ((w0 >> 2) & 0x30303030u)) : (w0 & 0x3f3f3f3fu);
     const uint32_t mn4 = hf ? (((w2 >> 4) & 0x0f0f0f0fu) | ((w1 >> 2) & 0x30303030u)) : (w1 & 0x3f3f3f3fu);
-    uint4 * scl = reinterpret_cast<uint4 *>(tab) + r * 4 + hf * 2;
-    uint2 * mn2 = reinterpret_cast<uint2 *>(tab + 1024) + r * 4 + hf * 2;
+    uint4 * scl = reinterpret_cast<uint4 *>(tab + r * C::SCL_STRIDE) + hf * 2;
+    uint2 * mn2 = reinterpret_cast<uint2 *>(tab + C::MN_OFF + r * C::MN_STRIDE) + hf * 2;
 #pragma unroll
     for (int jl = 0; jl < 2; jl++) {
         const uint32_t sp = h2_mul(h2_sub(jl ? bytes23_h2(sc4) : bytes01_h2(sc4), H2_1024), d2);
@@ -244,15 +299,14 @@ __device__ __forceinline__ void header_k4(const uint4 & hdr, int lane, uint8_t *
     }
 }
 
+// One MMA adding  sum_s16 A[row][s16] * xsum[tok][s16]  for eight 16-element groups base..base+7.
+// a_* are the (value, value) pairs for groups base+t and base+t+4 of rows g and g+8.
 template <int NT>
-__device__ __forceinline__ void min_mma(const uint8_t * mn2, int stride_subs, int g, int t, int sub0,
-                                        const uint8_t * const (&xsrow)[NT], int xs_off, float (&acc)[NT][4]) {
-    const uint32_t * m = reinterpret_cast<const uint32_t *>(mn2);
-    const uint32_t a0 = m[g * stride_subs + sub0 + t], a1 = m[(g + 8) * stride_subs + sub0 + t];
-    const uint32_t a2 = m[g * stride_subs + sub0 + t + 4], a3 = m[(g + 8) * stride_subs + sub0 + t + 4];
+__device__ __forceinline__ void sum_mma(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int t, int s16_base,
+                                        const uint8_t * const (&xsrow)[NT], float (&acc)[NT][4]) {
 #pragma unroll
     for (int j = 0; j < NT; j++) {
-        const uint32_t * xs = reinterpret_cast<const uint32_t *>(xsrow[j]) + xs_off + sub0;
+        const uint32_t * xs = reinterpret_cast<const uint32_t *>(xsrow[j]) + s16_base;
         mma16816(acc[j], a0, a1, a2, a3, xs[t], xs[t + 4]);
     }
 }
@@ -261,109 +315,121 @@ template <int DT, int NT> struct Mma;
 
 template <int NT> struct Mma<YUUKA_DTYPE_Q4_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q4_K>;
-    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4(r.hdr, lane, tab); }
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4<C>(r.hdr, lane, tab); }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
                                const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint4 * scl = reinterpret_cast<const uint4 *>(tab);
+        const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const int j = (t >> 1) + 2 * cc;
-            const uint4 sg = scl[g * 4 + j], sh = scl[(g + 8) * 4 + j];
-            const uint32_t qg[4] = {r.q[cc].x, r.q[cc].y, r.q[cc].z, r.q[cc].w};
-            const uint32_t qh[4] = {r.q[2 + cc].x, r.q[2 + cc].y, r.q[2 + cc].z, r.q[2 + cc].w};
+        for (int jj = 0; jj < 2; jj++) {
+            const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+            const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
 #pragma unroll
-            for (int n = 0; n < 2; n++) {
-                const uint32_t mask = n ? 0x00f000f0u : 0x000f000fu;
-                const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+            for (int jl = 0; jl < 2; jl++) {
+                const int j = 2 * jj + jl;
+                const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
 #pragma unroll
-                for (int wp = 0; wp < 2; wp++) {
+                for (int n = 0; n < 2; n++) {
+                    const uint32_t mask = n ? 0x00f000f0u : 0x000f000fu;
+                    const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
                     uint32_t a[2][4];
 #pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        const uint32_t vg = qg[2 * wp + k], vh = qh[2 * wp + k];
-                        a[k][0] = h2_fma((vg & mask) | H2_1024, s_g, c_g);
-                        a[k][1] = h2_fma((vh & mask) | H2_1024, s_h, c_h);
-                        a[k][2] = h2_fma(((vg >> 8) & mask) | H2_1024, s_g, c_g);
-                        a[k][3] = h2_fma(((vh >> 8) & mask) | H2_1024, s_h, c_h);
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
+                        a[h][0] = h2_fma((vg & mask) | H2_1024, s_g, c_g);
+                        a[h][1] = h2_fma((vh & mask) | H2_1024, s_h, c_h);
+                        a[h][2] = h2_fma(((vg >> 8) & mask) | H2_1024, s_g, c_g);
+                        a[h][3] = h2_fma(((vh >> 8) & mask) | H2_1024, s_h, c_h);
                     }
-                    const int p = cc * 4 + n * 2 + wp;
+                    const int k = 2 * j + n;
 #pragma unroll
                     for (int jt = 0; jt < NT; jt++) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 8 + p) * 64);
+                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
                         mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                         mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
                     }
                 }
             }
         }
-        min_mma<NT>(tab + 1024, 8, g, t, 0, xsrow, sbl * 8, acc);
+        // - min * sum(x): 16-element groups s16 belong to sub-block s16 / 2
+        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
+        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int k0 = 4 * half + (t >> 1);
+            sum_mma<NT>(mg[k0], mh[k0], mg[k0 + 2], mh[k0 + 2], t, sbl * 16 + 8 * half, xsrow, acc);
+        }
     }
 };
 
 template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q5_K>;
-    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4(r.hdr, lane, tab); }
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4<C>(r.hdr, lane, tab); }
+    // bit k of every byte of hb -> bit `tgt` of bytes 0 and 2 (shift_bytes13: of bytes 1 and 3 moved down)
+    template <int K, int TGT, bool B13> __device__ static uint32_t hibit(uint32_t hb) {
+        constexpr int from = K + (B13 ? 8 : 0);
+        constexpr uint32_t mask = (1u << TGT) | (1u << (TGT + 16));
+        if constexpr (from >= TGT) return (hb >> (from - TGT)) & mask;
+        else return (hb << (TGT - from)) & mask;
+    }
+    template <int K> __device__ static void sub(uint32_t vg, uint32_t vh, uint32_t hg, uint32_t hh, uint32_t s_g, uint32_t c_g,
+                                                uint32_t s_h, uint32_t c_h, uint32_t (&a)[4]) {
+        constexpr bool hi = (K & 1) != 0;
+        constexpr uint32_t mask = hi ? 0x00f000f0u : 0x000f000fu;
+        constexpr int tgt = hi ? 8 : 4;
+        a[0] = h2_fma((vg & mask) | hibit<K, tgt, false>(hg) | H2_1024, s_g, c_g);
+        a[1] = h2_fma((vh & mask) | hibit<K, tgt, false>(hh) | H2_1024, s_h, c_h);
+        a[2] = h2_fma(((vg >> 8) & mask) | hibit<K, tgt, true>(hg) | H2_1024, s_g, c_g);
+        a[3] = h2_fma(((vh >> 8) & mask) | hibit<K, tgt, true>(hh) | H2_1024, s_h, c_h);
+    }
+    template <int K>
+    __device__ static void subblock(const typename C::Regs & r, const uint8_t * tg, const uint8_t * th,
+                                    const uint8_t * const (&xrow)[NT], int sbl, float (&acc)[NT][4]) {
+        constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
+        const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+        const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
+        const uint32_t hg[2] = {r.qh.x, r.qh.y}, hh[2] = {r.qh.z, r.qh.w};
+        const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
+        const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+        uint32_t a[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h]);
+#pragma unroll
+        for (int jt = 0; jt < NT; jt++) {
+            const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * K) * 2);
+            mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+            mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+        }
+    }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
                                const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint4 * scl = reinterpret_cast<const uint4 *>(tab);
-        const uint32_t hg[4] = {r.qh[0].x, r.qh[0].y, r.qh[0].z, r.qh[0].w};
-        const uint32_t hh[4] = {r.qh[1].x, r.qh[1].y, r.qh[1].z, r.qh[1].w};
+        const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
+        subblock<0>(r, tg, th, xrow, sbl, acc); subblock<1>(r, tg, th, xrow, sbl, acc);
+        subblock<2>(r, tg, th, xrow, sbl, acc); subblock<3>(r, tg, th, xrow, sbl, acc);
+        subblock<4>(r, tg, th, xrow, sbl, acc); subblock<5>(r, tg, th, xrow, sbl, acc);
+        subblock<6>(r, tg, th, xrow, sbl, acc); subblock<7>(r, tg, th, xrow, sbl, acc);
+        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
+        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const int j = (t >> 1) + 2 * cc;
-            const uint4 sg = scl[g * 4 + j], sh = scl[(g + 8) * 4 + j];
-            const uint32_t qg[4] = {r.q[cc].x, r.q[cc].y, r.q[cc].z, r.q[cc].w};
-            const uint32_t qh[4] = {r.q[2 + cc].x, r.q[2 + cc].y, r.q[2 + cc].z, r.q[2 + cc].w};
-#pragma unroll
-            for (int n = 0; n < 2; n++) {
-                const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
-#pragma unroll
-                for (int wp = 0; wp < 2; wp++) {
-                    uint32_t a[2][4];
-#pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        const int w = 2 * wp + k;
-                        const uint32_t vg = qg[w], vh = qh[w];
-                        const uint32_t bg = hg[w] >> (2 * j), bh = hh[w] >> (2 * j);  // bit 0: low nibble's fifth bit, bit 1: high nibble's
-                        if (n == 0) {
-                            a[k][0] = h2_fma((vg & 0x000f000fu) | ((bg << 4) & 0x00100010u) | H2_1024, s_g, c_g);
-                            a[k][1] = h2_fma((vh & 0x000f000fu) | ((bh << 4) & 0x00100010u) | H2_1024, s_h, c_h);
-                            a[k][2] = h2_fma(((vg >> 8) & 0x000f000fu) | ((bg >> 4) & 0x00100010u) | H2_1024, s_g, c_g);
-                            a[k][3] = h2_fma(((vh >> 8) & 0x000f000fu) | ((bh >> 4) & 0x00100010u) | H2_1024, s_h, c_h);
-                        } else {
-                            a[k][0] = h2_fma((vg & 0x00f000f0u) | ((bg << 7) & 0x01000100u) | H2_1024, s_g, c_g);
-                            a[k][1] = h2_fma((vh & 0x00f000f0u) | ((bh << 7) & 0x01000100u) | H2_1024, s_h, c_h);
-                            a[k][2] = h2_fma(((vg >> 8) & 0x00f000f0u) | ((bg >> 1) & 0x01000100u) | H2_1024, s_g, c_g);
-                            a[k][3] = h2_fma(((vh >> 8) & 0x00f000f0u) | ((bh >> 1) & 0x01000100u) | H2_1024, s_h, c_h);
-                        }
-                    }
-                    const int p = cc * 4 + n * 2 + wp;
-#pragma unroll
-                    for (int jt = 0; jt < NT; jt++) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 8 + p) * 64);
-                        mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                        mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-                    }
-                }
-            }
+        for (int half = 0; half < 2; half++) {
+            const int k0 = 4 * half + (t >> 1);
+            sum_mma<NT>(mg[k0], mh[k0], mg[k0 + 2], mh[k0 + 2], t, sbl * 16 + 8 * half, xsrow, acc);
         }
-        min_mma<NT>(tab + 1024, 8, g, t, 0, xsrow, sbl * 8, acc);
     }
 };
 
-// Q6_K table: scl[row][sub k] = {s', c'} with (s, -1024 s) for low-nibble subs (k%8 < 4) and
-// (s/16, -64 s) for high-nibble subs; mn2[row][k] = (-32 s, -32 s).
+// Q6_K: scl[row][s16] = {s', c'} with (s, -1024 s) where the value sits in a low nibble
+// (s16 % 8 < 4) and (s/16, -64 s) where it sits in a high nibble; mn2[row][s16] = (-32 s, -32 s).
 template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q6_K>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) {
-        const int row = lane & 15, hf = lane >> 4;  // hf: subs 8hf .. 8hf+7
+        const int row = lane & 15, hf = lane >> 4;  // hf: groups 8hf .. 8hf+7
         const uint32_t d2 = dup_lo(r.d);
-        const uint32_t wa = (hf ? r.sc.z : r.sc.x) ^ 0x80808080u;  // subs +0..3: low-nibble form
-        const uint32_t wb = (hf ? r.sc.w : r.sc.y) ^ 0x80808080u;  // subs +4..7: high-nibble form
-        uint2 * scl = reinterpret_cast<uint2 *>(tab) + row * 16 + hf * 8;
-        uint32_t * mn2 = reinterpret_cast<uint32_t *>(tab + 2048) + row * 16 + hf * 8;
+        const uint32_t wa = (hf ? r.sc.z : r.sc.x) ^ 0x80808080u;  // groups +0..3: low-nibble form
+        const uint32_t wb = (hf ? r.sc.w : r.sc.y) ^ 0x80808080u;  // groups +4..7: high-nibble form
+        uint2 * scl = reinterpret_cast<uint2 *>(tab + row * C::SCL_STRIDE) + hf * 8;
+        uint32_t * mn2 = reinterpret_cast<uint32_t *>(tab + C::MN_OFF + row * C::MN_STRIDE) + hf * 8;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const uint32_t w = q < 2 ? wa : wb;
@@ -383,55 +449,58 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
                                const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint2 * scl = reinterpret_cast<const uint2 *>(tab);
-        const int lsh = 4 - 2 * (t >> 1);  // brings this lane's two high bits to bit 4 (low nibble) / bit 8 (high nibble)
-        const int rsh = 8 - lsh;
+        const uint2 * tg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE) + (t >> 1);
+        const uint2 * th = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE) + (t >> 1);
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const uint32_t qg[4] = {r.ql[cc].x, r.ql[cc].y, r.ql[cc].z, r.ql[cc].w};
-            const uint32_t qh[4] = {r.ql[2 + cc].x, r.ql[2 + cc].y, r.ql[2 + cc].z, r.ql[2 + cc].w};
-            const uint32_t hg[4] = {r.qh[cc].x, r.qh[cc].y, r.qh[cc].z, r.qh[cc].w};
-            const uint32_t hh[4] = {r.qh[2 + cc].x, r.qh[2 + cc].y, r.qh[2 + cc].z, r.qh[2 + cc].w};
+        for (int n6 = 0; n6 < 2; n6++) {
+            const uint32_t lg[4] = {r.ql[n6].x, r.ql[n6].y, r.ql[n6].z, r.ql[n6].w};
+            const uint32_t lh[4] = {r.ql[2 + n6].x, r.ql[2 + n6].y, r.ql[2 + n6].z, r.ql[2 + n6].w};
+            const uint32_t hg[2] = {n6 ? r.qh[0].z : r.qh[0].x, n6 ? r.qh[0].w : r.qh[0].y};
+            const uint32_t hh[2] = {n6 ? r.qh[1].z : r.qh[1].x, n6 ? r.qh[1].w : r.qh[1].y};
 #pragma unroll
-            for (int n = 0; n < 2; n++) {
-                const int k = 8 * cc + 4 * n + t;
-                const uint2 eg = scl[g * 16 + k], eh = scl[(g + 8) * 16 + k];
-                const uint32_t qm = n ? 0x00f000f0u : 0x000f000fu, hm = n ? 0x03000300u : 0x00300030u;
+            for (int hsel = 0; hsel < 2; hsel++) {
+                const int lsh = 4 - 2 * hsel, rsh = 4 + 2 * hsel;
 #pragma unroll
-                for (int wp = 0; wp < 2; wp++) {
+                for (int nib = 0; nib < 2; nib++) {
+                    const int k = 4 * n6 + hsel + 2 * nib;
+                    const uint2 eg = tg[2 * k], eh = th[2 * k];
+                    const uint32_t qm = nib ? 0x00f000f0u : 0x000f000fu, hm = nib ? 0x03000300u : 0x00300030u;
                     uint32_t a[2][4];
 #pragma unroll
-                    for (int kk = 0; kk < 2; kk++) {
-                        const int w = 2 * wp + kk;
-                        // bytes 0,2 take the high bits shifted left; bytes 1,3 come down by 8 first
-                        a[kk][0] = h2_fma((qg[w] & qm) | ((hg[w] << lsh) & hm) | H2_1024, eg.x, eg.y);
-                        a[kk][1] = h2_fma((qh[w] & qm) | ((hh[w] << lsh) & hm) | H2_1024, eh.x, eh.y);
-                        a[kk][2] = h2_fma(((qg[w] >> 8) & qm) | ((hg[w] >> rsh) & hm) | H2_1024, eg.x, eg.y);
-                        a[kk][3] = h2_fma(((qh[w] >> 8) & qm) | ((hh[w] >> rsh) & hm) | H2_1024, eh.x, eh.y);
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
+                        a[h][0] = h2_fma((vg & qm) | ((hg[h] << lsh) & hm) | H2_1024, eg.x, eg.y);
+                        a[h][1] = h2_fma((vh & qm) | ((hh[h] << lsh) & hm) | H2_1024, eh.x, eh.y);
+                        a[h][2] = h2_fma(((vg >> 8) & qm) | ((hg[h] >> rsh) & hm) | H2_1024, eg.x, eg.y);
+                        a[h][3] = h2_fma(((vh >> 8) & qm) | ((hh[h] >> rsh) & hm) | H2_1024, eh.x, eh.y);
                     }
-                    const int p = cc * 4 + n * 2 + wp;
 #pragma unroll
                     for (int jt = 0; jt < NT; jt++) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 8 + p) * 64);
+                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
                         mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                         mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
                     }
                 }
             }
         }
-        min_mma<NT>(tab + 2048, 16, g, t, 0, xsrow, sbl * 16, acc);
-        min_mma<NT>(tab + 2048, 16, g, t, 8, xsrow, sbl * 16, acc);
+        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
+        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int s0 = 8 * half + t;
+            sum_mma<NT>(mg[s0], mh[s0], mg[s0 + 4], mh[s0 + 4], t, sbl * 16 + 8 * half, xsrow, acc);
+        }
     }
 };
 
-// Q8_0 table: scl[row][block] = (s, s). Bytes are biased by 128 to make them unsigned, converted
-// exactly (1024 + 128 + q), the bias subtracted exactly, then scaled: one rounding per weight.
+// Q8_0: scl[row][block] = (s, s). Bytes are biased by 128 to make them unsigned, converted exactly
+// (1024 + 128 + q), the bias subtracted exactly, then scaled: one rounding per weight.
 template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
     using C = Codec<YUUKA_DTYPE_Q8_0>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) {
         const int row = lane & 15, hf = lane >> 4;
         const uint32_t da = hf ? r.d.z : r.d.x, db = hf ? r.d.w : r.d.y;
-        uint32_t * scl = reinterpret_cast<uint32_t *>(tab) + row * 8 + hf * 4;
+        uint32_t * scl = reinterpret_cast<uint32_t *>(tab + row * C::SCL_STRIDE) + hf * 4;
         scl[0] = dup_lo(da);
         scl[1] = dup_hi(da);
         scl[2] = dup_lo(db);
@@ -440,31 +509,31 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
                                const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
         (void)xsrow;
-        const int g = lane >> 2, t = lane & 3;
-        const uint32_t * scl = reinterpret_cast<const uint32_t *>(tab);
+        const int g = lane >> 2;
+        const uint32_t * sgp = reinterpret_cast<const uint32_t *>(tab + g * C::SCL_STRIDE);
+        const uint32_t * shp = reinterpret_cast<const uint32_t *>(tab + (g + 8) * C::SCL_STRIDE);
 #pragma unroll
-        for (int cs = 0; cs < 4; cs++) {
-            const int b = 2 * cs + (t >> 1);
-            const uint32_t sg = scl[g * 8 + b], sh = scl[(g + 8) * 8 + b];
-            const uint32_t qg[4] = {r.q[cs].x, r.q[cs].y, r.q[cs].z, r.q[cs].w};
-            const uint32_t qh[4] = {r.q[4 + cs].x, r.q[4 + cs].y, r.q[4 + cs].z, r.q[4 + cs].w};
+        for (int kk = 0; kk < 4; kk++) {
+            const uint32_t qg[4] = {r.q[kk].x, r.q[kk].y, r.q[kk].z, r.q[kk].w};
+            const uint32_t qh[4] = {r.q[4 + kk].x, r.q[4 + kk].y, r.q[4 + kk].z, r.q[4 + kk].w};
 #pragma unroll
-            for (int wp = 0; wp < 2; wp++) {
+            for (int kl = 0; kl < 2; kl++) {
+                const int k = 2 * kk + kl;
+                const uint32_t sg = sgp[k], sh = shp[k];
                 uint32_t a[2][4];
 #pragma unroll
-                for (int kk = 0; kk < 2; kk++) {
-                    const uint32_t vg = qg[2 * wp + kk] ^ 0x80808080u, vh = qh[2 * wp + kk] ^ 0x80808080u;
-                    a[kk][0] = h2_mul(h2_sub(bytes02_h2(vg), H2_1152), sg);
-                    a[kk][1] = h2_mul(h2_sub(bytes02_h2(vh), H2_1152), sh);
-                    a[kk][2] = h2_mul(h2_sub(bytes13_h2(vg), H2_1152), sg);
-                    a[kk][3] = h2_mul(h2_sub(bytes13_h2(vh), H2_1152), sh);
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t vg = qg[2 * kl + h] ^ 0x80808080u, vh = qh[2 * kl + h] ^ 0x80808080u;
+                    a[h][0] = h2_mul(h2_sub(bytes02_h2(vg), H2_1152), sg);
+                    a[h][1] = h2_mul(h2_sub(bytes02_h2(vh), H2_1152), sh);
+                    a[h][2] = h2_mul(h2_sub(bytes13_h2(vg), H2_1152), sg);
+                    a[h][3] = h2_mul(h2_sub(bytes13_h2(vh), H2_1152), sh);
                 }
-                const int p = cs * 2 + wp;
 #pragma unroll
                 for (int jt = 0; jt < NT; jt++) {
-                    const uint4 bb = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 8 + p) * 64);
-                    mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], bb.x, bb.y);
-                    mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], bb.z, bb.w);
+                    const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
+                    mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                    mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
                 }
             }
         }
@@ -474,29 +543,14 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
 // ===========================================================================
 // mma kernel
 
-template <typename XT> __device__ __forceinline__ float xf(XT v);
-template <> __device__ __forceinline__ float xf<float>(float v) { return v; }
-template <> __device__ __forceinline__ float xf<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
-// eight consecutive activations (16-byte aligned) as floats
-__device__ __forceinline__ void load8(const float * src, float (&v)[8]) {
-    const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16 * src, float (&v)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4 *>(src);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        v[2 * k] = __uint_as_float(w[k] << 16);
-        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-    }
-}
+__device__ int g_gemm_wait_expired = 0;
 
 struct TParams {
     const uint8_t * w;
     int N, nsb;
-    const void * x;
+    const __half * xh;      // prepared activations [M][nsb * 256]
+    const __half2 * xs16;   // [M][nsb * 16]
+    const void * x;         // fp32 route only
     int64_t ldx;
     int M;
     float * out;
@@ -510,23 +564,24 @@ struct TParams {
     int * counters;
 };
 
-template <int DT, int NT, typename XT>
+template <int DT, int NT>
 __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParams p) {
     using C = Codec<DT>;
     using MM = Mma<DT, NT>;
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t xbar;
+    __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int c0 = blockIdx.y * p.nsb_chunk;
     const int c1 = min(p.nsb, c0 + p.nsb_chunk);
     const int cnt = c1 - c0;
-    const int xstride = p.nsb_chunk * 512 + 64;           // bytes of fp16 activations per row
-    const int xsum_stride = p.nsb_chunk * C::NSUB * 4;    // bytes of sub-block sums per row
+    const int xstride = p.nsb_chunk * 512 + 64;       // bytes of fp16 activations per row (+64: bank spread)
+    const int xsum_stride = p.nsb_chunk * 64 + 16;    // bytes of 16-element sums per row
     uint8_t * xs = smem;
     uint8_t * xsum = xs + (size_t)p.M * xstride;
     uint8_t * tabs = xsum + (((size_t)p.M * xsum_stride + 127) / 128) * 128;
     float * red = reinterpret_cast<float *>(tabs + TW * C::TAB);
-    __shared__ int last_flag;
 
     const int tile_in_group = warp / p.KS, kpart = warp - tile_in_group * p.KS;
     const int sb0 = c0 + (cnt * kpart) / p.KS, sb1 = c0 + (cnt * (kpart + 1)) / p.KS;
@@ -541,41 +596,43 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (sb0 < sb1) C::load(p.w + rt * rec_row + (size_t)sb0 * C::REC, lane, cur);
     }
 
-    // ---- stage activations of this K chunk: fp16 in fragment order, plus sub-block sums ----
-    {
-        const XT * X = reinterpret_cast<const XT *>(p.x);
-        const int groups_per_row = cnt * 32;  // 8-element groups
-        for (int i = threadIdx.x; i < p.M * groups_per_row; i += TW * 32) {
-            const int m = i / groups_per_row, q = i - m * groups_per_row;
-            const int sbl = q >> 5, e8 = q & 31;
-            const XT * src = X + (int64_t)m * p.ldx + (int64_t)(c0 + sbl) * 256 + e8 * 8;
-            float v[8];
-            load8(src, v);
-            const __half2 h0 = __floats2half2_rn(v[0], v[2]), h1 = __floats2half2_rn(v[1], v[3]);
-            const __half2 h2 = __floats2half2_rn(v[4], v[6]), h3 = __floats2half2_rn(v[5], v[7]);
-            int tt;
-            const int pslot = C::pair_slot(e8, tt);
-            uint4 pk;
-            pk.x = *reinterpret_cast<const uint32_t *>(&h0);
-            pk.y = *reinterpret_cast<const uint32_t *>(&h1);
-            pk.z = *reinterpret_cast<const uint32_t *>(&h2);
-            pk.w = *reinterpret_cast<const uint32_t *>(&h3);
-            *reinterpret_cast<uint4 *>(xs + (size_t)m * xstride + ((sbl * 8 + pslot) * 4 + tt) * 16) = pk;
-            // sums of the rounded values; groups of one sub-block sit in adjacent lanes
-            float s8 = (__low2float(h0) + __high2float(h0)) + (__low2float(h1) + __high2float(h1)) +
-                       (__low2float(h2) + __high2float(h2)) + (__low2float(h3) + __high2float(h3));
-            s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
-            if (C::NSUB == 8) s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
-            const int per_sub = C::NSUB == 8 ? 4 : 2;
-            if ((e8 & (per_sub - 1)) == 0) {
-                const __half hi = __float2half_rn(s8);
-                const __half lo = __float2half_rn(s8 - __half2float(hi));
-                const __half2 hl = __halves2half2(hi, lo);
-                *reinterpret_cast<__half2 *>(xsum + (size_t)m * xsum_stride + (sbl * C::NSUB + e8 / per_sub) * 4) = hl;
-            }
-        }
+    // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums ----
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&xbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
+        const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = (uint32_t)cnt * 64;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * p.M)
+                     : "memory");
+        for (int m = 0; m < p.M; m++) {
+            const __half * srcx = p.xh + ((size_t)m * p.nsb + c0) * 256;
+            const __half2 * srcs = p.xs16 + ((size_t)m * p.nsb + c0) * 16;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * xstride)),
+                         "l"(srcx), "r"(row_bytes_x), "r"(bar)
+                         : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(xsum + (size_t)m * xsum_stride)),
+                         "l"(srcs), "r"(row_bytes_s), "r"(bar)
+                         : "memory");
+        }
+    }
+    {
+        // bounded wait for the copies; on expiry the error word is set and the results are garbage
+        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
+        uint32_t ok = 0;
+        for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(bar)
+                : "memory");
+        }
+        if (!ok) atomicExch(&g_gemm_wait_expired, 1);
+    }
 
     uint8_t * tab = tabs + warp * C::TAB;
     const uint8_t * xrow[NT];
@@ -596,6 +653,9 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         for (int j = 0; j < NT; j++)
 #pragma unroll
             for (int c = 0; c < 4; c++) acc[j][c] = 0.0f;
+        // the rest of this warp's records: get them moving from DRAM to L2 now; the register
+        // double buffer below then only has to cover the L2 latency
+        if (sb0 + 1 < sb1) prefetch_l2_range(tile + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
 
         for (int sb = sb0; sb < sb1; sb++) {
             // prefetch the next record of this tile, or the first record of the next group's tile
@@ -679,46 +739,12 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
 
 constexpr int F32_MT = 4;
 
-template <int DT> struct F32Decode;
-
-// calls f(e, wg[4], wh[4]) for every 4 consecutive elements e..e+3 this lane holds, rows g and g+8
-template <> struct F32Decode<YUUKA_DTYPE_Q4_K> {
-    template <bool Q5, typename R, typename F> __device__ static void each(const R & r, int lane, const uint8_t * hdr_g,
-                                                                            const uint8_t * hdr_h, F f) {
-        const int t = lane & 3;
-        const float dg = ld_f16(hdr_g), mg = ld_f16(hdr_g + 2), dh = ld_f16(hdr_h), mh = ld_f16(hdr_h + 2);
-#pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const int j = (t >> 1) + 2 * cc;
-            const uint32_t qg[4] = {r.q[cc].x, r.q[cc].y, r.q[cc].z, r.q[cc].w};
-            const uint32_t qh[4] = {r.q[2 + cc].x, r.q[2 + cc].y, r.q[2 + cc].z, r.q[2 + cc].w};
-#pragma unroll
-            for (int n = 0; n < 2; n++) {
-                int sc, mn;
-                scale_min_k4(2 * j + n, hdr_g + 4, sc, mn);
-                const float d1g = dg * (float)sc, m1g = mg * (float)mn;
-                scale_min_k4(2 * j + n, hdr_h + 4, sc, mn);
-                const float d1h = dh * (float)sc, m1h = mh * (float)mn;
-#pragma unroll
-                for (int w = 0; w < 4; w++) {
-                    float wg[4], wh[4];
-#pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        int vg = (qg[w] >> (8 * b + 4 * n)) & 15, vh = (qh[w] >> (8 * b + 4 * n)) & 15;
-                        if constexpr (Q5) {
-                            const uint32_t bg = ((const uint32_t *)&r.qh[0])[w], bh = ((const uint32_t *)&r.qh[1])[w];
-                            vg += ((bg >> (8 * b + 2 * j + n)) & 1) << 4;
-                            vh += ((bh >> (8 * b + 2 * j + n)) & 1) << 4;
-                        }
-                        wg[b] = d1g * (float)vg - m1g;
-                        wh[b] = d1h * (float)vh - m1h;
-                    }
-                    f(64 * j + 32 * n + 16 * (t & 1) + 4 * w, wg, wh);
-                }
-            }
-        }
-    }
-};
+// value of element b (0..7) of an 8-byte piece stored as two shuffled words
+__device__ __forceinline__ uint32_t piece_byte(uint32_t w0, uint32_t w1, int b) {
+    const uint32_t w = (b & 4) ? w1 : w0;
+    const int e = b & 3, pos = (e & 1) * 2 + (e >> 1);  // element 0,1,2,3 -> byte 0,2,1,3
+    return (w >> (8 * pos)) & 0xffu;
+}
 
 template <int DT, typename XT>
 __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams p) {
@@ -745,27 +771,56 @@ __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams 
             const uint8_t * rec = p.w + ((size_t)rt * p.nsb + sb) * C::REC;
             C::load(rec, lane, r);
             const float * xb = xf32 + sb * 256;
-            auto fma4 = [&](int e, const float (&wg)[4], const float (&wh)[4]) {
+            // eight consecutive elements e..e+7 of rows g and g+8
+            auto fma8 = [&](int e, const float (&wg)[8], const float (&wh)[8]) {
 #pragma unroll
                 for (int m = 0; m < F32_MT; m++) {
                     if (m < p.M) {
-                        const float4 xv = *reinterpret_cast<const float4 *>(xb + m * K + e);
-                        ag[m] = fmaf(xv.x, wg[0], ag[m]); ag[m] = fmaf(xv.y, wg[1], ag[m]);
-                        ag[m] = fmaf(xv.z, wg[2], ag[m]); ag[m] = fmaf(xv.w, wg[3], ag[m]);
-                        ah[m] = fmaf(xv.x, wh[0], ah[m]); ah[m] = fmaf(xv.y, wh[1], ah[m]);
-                        ah[m] = fmaf(xv.z, wh[2], ah[m]); ah[m] = fmaf(xv.w, wh[3], ah[m]);
+                        const float4 x0 = *reinterpret_cast<const float4 *>(xb + m * K + e);
+                        const float4 x1 = *reinterpret_cast<const float4 *>(xb + m * K + e + 4);
+                        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int b = 0; b < 8; b++) {
+                            ag[m] = fmaf(xv[b], wg[b], ag[m]);
+                            ah[m] = fmaf(xv[b], wh[b], ah[m]);
+                        }
                     }
                 }
             };
+            __syncwarp();
             if constexpr (DT == YUUKA_DTYPE_Q4_K || DT == YUUKA_DTYPE_Q5_K) {
-                // headers through shared memory: lane r holds row r's 16 bytes
-                __syncwarp();
                 if (lane < 16) *reinterpret_cast<uint4 *>(hdrs[warp] + lane * 16) = r.hdr;
                 __syncwarp();
-                F32Decode<YUUKA_DTYPE_Q4_K>::template each<DT == YUUKA_DTYPE_Q5_K>(r, lane, hdrs[warp] + g * 16,
-                                                                          hdrs[warp] + (g + 8) * 16, fma4);
+                const uint8_t * hg = hdrs[warp] + g * 16, * hh = hdrs[warp] + (g + 8) * 16;
+                const float dg = ld_f16(hg), mg = ld_f16(hg + 2), dh = ld_f16(hh), mh = ld_f16(hh + 2);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint4 Qg = r.q[j >> 1], Qh = r.q[2 + (j >> 1)];
+                    const uint32_t g0 = (j & 1) ? Qg.z : Qg.x, g1 = (j & 1) ? Qg.w : Qg.y;
+                    const uint32_t h0 = (j & 1) ? Qh.z : Qh.x, h1 = (j & 1) ? Qh.w : Qh.y;
+#pragma unroll
+                    for (int n = 0; n < 2; n++) {
+                        const int k = 2 * j + n;
+                        int sc, mn;
+                        scale_min_k4(k, hg + 4, sc, mn);
+                        const float d1g = dg * (float)sc, m1g = mg * (float)mn;
+                        scale_min_k4(k, hh + 4, sc, mn);
+                        const float d1h = dh * (float)sc, m1h = mh * (float)mn;
+                        float wg[8], wh[8];
+#pragma unroll
+                        for (int b = 0; b < 8; b++) {
+                            int vg = (piece_byte(g0, g1, b) >> (4 * n)) & 15, vh = (piece_byte(h0, h1, b) >> (4 * n)) & 15;
+                            if constexpr (DT == YUUKA_DTYPE_Q5_K) {
+                                vg += ((piece_byte(r.qh.x, r.qh.y, b) >> k) & 1) << 4;
+                                vh += ((piece_byte(r.qh.z, r.qh.w, b) >> k) & 1) << 4;
+                            }
+                            wg[b] = d1g * (float)vg - m1g;
+                            wh[b] = d1h * (float)vh - m1h;
+                        }
+                        fma8(32 * k + 8 * t, wg, wh);
+                    }
+                }
             } else if constexpr (DT == YUUKA_DTYPE_Q6_K) {
-                __syncwarp();
                 if (lane < 16) {
                     *reinterpret_cast<uint4 *>(hdrs[warp] + lane * 32) = r.sc;
                     *reinterpret_cast<uint32_t *>(hdrs[warp] + lane * 32 + 16) = r.d;
@@ -775,49 +830,43 @@ __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams 
                 const int8_t * sch = reinterpret_cast<const int8_t *>(hdrs[warp] + (g + 8) * 32);
                 const float dg = ld_f16(hdrs[warp] + g * 32 + 16), dh = ld_f16(hdrs[warp] + (g + 8) * 32 + 16);
 #pragma unroll
-                for (int cc = 0; cc < 2; cc++) {
-                    const uint32_t qg[4] = {r.ql[cc].x, r.ql[cc].y, r.ql[cc].z, r.ql[cc].w};
-                    const uint32_t qh[4] = {r.ql[2 + cc].x, r.ql[2 + cc].y, r.ql[2 + cc].z, r.ql[2 + cc].w};
-                    const uint32_t hg[4] = {r.qh[cc].x, r.qh[cc].y, r.qh[cc].z, r.qh[cc].w};
-                    const uint32_t hh[4] = {r.qh[2 + cc].x, r.qh[2 + cc].y, r.qh[2 + cc].z, r.qh[2 + cc].w};
+                for (int n6 = 0; n6 < 2; n6++) {
+                    const uint4 Lg = r.ql[n6], Lh = r.ql[2 + n6];
+                    const uint32_t Hg0 = n6 ? r.qh[0].z : r.qh[0].x, Hg1 = n6 ? r.qh[0].w : r.qh[0].y;
+                    const uint32_t Hh0 = n6 ? r.qh[1].z : r.qh[1].x, Hh1 = n6 ? r.qh[1].w : r.qh[1].y;
 #pragma unroll
-                    for (int n = 0; n < 2; n++) {
-                        const int g4 = (t >> 1) + 2 * n, k = 8 * cc + 4 * n + t;
-                        const float sg = dg * (float)scg[k], sh = dh * (float)sch[k];
+                    for (int g4 = 0; g4 < 4; g4++) {
+                        const int hsel = g4 & 1, nib = g4 >> 1, k = 4 * n6 + g4, s16 = 2 * k + (t >> 1);
+                        const float sg = dg * (float)scg[s16], sh = dh * (float)sch[s16];
+                        const uint32_t g0 = hsel ? Lg.z : Lg.x, g1 = hsel ? Lg.w : Lg.y;
+                        const uint32_t h0 = hsel ? Lh.z : Lh.x, h1 = hsel ? Lh.w : Lh.y;
+                        float wg[8], wh[8];
 #pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            float wg[4], wh[4];
-#pragma unroll
-                            for (int b = 0; b < 4; b++) {
-                                const int vg = ((qg[w] >> (8 * b + 4 * n)) & 15) | (((hg[w] >> (8 * b + 2 * g4)) & 3) << 4);
-                                const int vh = ((qh[w] >> (8 * b + 4 * n)) & 15) | (((hh[w] >> (8 * b + 2 * g4)) & 3) << 4);
-                                wg[b] = sg * (float)(vg - 32);
-                                wh[b] = sh * (float)(vh - 32);
-                            }
-                            fma4(128 * cc + 32 * g4 + 16 * (t & 1) + 4 * w, wg, wh);
+                        for (int b = 0; b < 8; b++) {
+                            const int vg = ((piece_byte(g0, g1, b) >> (4 * nib)) & 15) | (((piece_byte(Hg0, Hg1, b) >> (2 * g4)) & 3) << 4);
+                            const int vh = ((piece_byte(h0, h1, b) >> (4 * nib)) & 15) | (((piece_byte(Hh0, Hh1, b) >> (2 * g4)) & 3) << 4);
+                            wg[b] = sg * (float)(vg - 32);
+                            wh[b] = sh * (float)(vh - 32);
                         }
+                        fma8(32 * k + 8 * t, wg, wh);
                     }
                 }
             } else {  // Q8_0
-                __syncwarp();
                 if (lane < 16) *reinterpret_cast<uint4 *>(hdrs[warp] + lane * 16) = r.d;
                 __syncwarp();
 #pragma unroll
-                for (int cs = 0; cs < 4; cs++) {
-                    const int b8 = 2 * cs + (t >> 1);
-                    const float dg = ld_f16(hdrs[warp] + g * 16 + 2 * b8), dh = ld_f16(hdrs[warp] + (g + 8) * 16 + 2 * b8);
-                    const uint32_t qg[4] = {r.q[cs].x, r.q[cs].y, r.q[cs].z, r.q[cs].w};
-                    const uint32_t qh[4] = {r.q[4 + cs].x, r.q[4 + cs].y, r.q[4 + cs].z, r.q[4 + cs].w};
+                for (int k = 0; k < 8; k++) {
+                    const float dg = ld_f16(hdrs[warp] + g * 16 + 2 * k), dh = ld_f16(hdrs[warp] + (g + 8) * 16 + 2 * k);
+                    const uint4 Qg = r.q[k >> 1], Qh = r.q[4 + (k >> 1)];
+                    const uint32_t g0 = (k & 1) ? Qg.z : Qg.x, g1 = (k & 1) ? Qg.w : Qg.y;
+                    const uint32_t h0 = (k & 1) ? Qh.z : Qh.x, h1 = (k & 1) ? Qh.w : Qh.y;
+                    float wg[8], wh[8];
 #pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        float wg[4], wh[4];
-#pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            wg[b] = dg * (float)(int8_t)(qg[w] >> (8 * b));
-                            wh[b] = dh * (float)(int8_t)(qh[w] >> (8 * b));
-                        }
-                        fma4(32 * b8 + 16 * (t & 1) + 4 * w, wg, wh);
+                    for (int b = 0; b < 8; b++) {
+                        wg[b] = dg * (float)(int8_t)piece_byte(g0, g1, b);
+                        wh[b] = dh * (float)(int8_t)piece_byte(h0, h1, b);
                     }
+                    fma8(32 * k + 8 * t, wg, wh);
                 }
             }
         }
@@ -843,12 +892,17 @@ struct TPlan {
     size_t smem;
 };
 
-static int nsub_of(uint32_t dtype) { return dtype == YUUKA_DTYPE_Q6_K ? 16 : 8; }
-static int tab_of(uint32_t dtype) { return dtype == YUUKA_DTYPE_Q6_K ? 3072 : 1536; }
+static int tab_of(uint32_t dtype) {
+    switch (dtype) {
+    case YUUKA_DTYPE_Q6_K: return Codec<YUUKA_DTYPE_Q6_K>::TAB;
+    case YUUKA_DTYPE_Q8_0: return Codec<YUUKA_DTYPE_Q8_0>::TAB;
+    default: return Codec<YUUKA_DTYPE_Q4_K>::TAB;
+    }
+}
 
 static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int nt, int ks) {
     size_t x = (size_t)m * (nsb_chunk * 512 + 64);
-    size_t xsum = (((size_t)m * nsb_chunk * nsub_of(dtype) * 4 + 127) / 128) * 128;
+    size_t xsum = (((size_t)m * (nsb_chunk * 64 + 16) + 127) / 128) * 128;
     size_t red = ks > 1 ? (size_t)TW * nt * 128 * 4 : 0;
     return x + xsum + (size_t)TW * tab_of(dtype) + red;
 }
@@ -865,9 +919,8 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     pl.n_groups = (n_tiles + pl.TG - 1) / pl.TG;
     // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
     int kchunks = 1;
-    const size_t budget = (dev->prop.sharedMemPerMultiprocessor - 2048) / 2 < dev->prop.sharedMemPerBlockOptin
-                              ? (dev->prop.sharedMemPerMultiprocessor - 2048) / 2
-                              : dev->prop.sharedMemPerBlockOptin;
+    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
+    const size_t budget = half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin;
     while (true) {
         int nsb_chunk = (nsb + kchunks - 1) / kchunks;
         bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks) <= budget;
@@ -890,7 +943,7 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     *counters = 0;
     if (!tiled_supported(w_dtype, n_in)) return;
     for (int m : {rows < 32 ? rows : 32, 32 < rows ? rows % 32 : 0}) {
-        if (m <= 0 || m <= 2) continue;
+        if (m <= 0) continue;
         TPlan pl;
         plan_tiled(dev, w_dtype, m, n_out, n_in, pl);
         if (pl.kchunks > 1) {
@@ -901,16 +954,17 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     }
 }
 
-template <int DT, int NT, typename XT>
-static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, int m0, int m, const TPlan & pl) {
-    auto kern = gemm_tiled_mma_kernel<DT, NT, XT>;
+template <int DT, int NT>
+static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
+                            const TPlan & pl) {
+    auto kern = gemm_tiled_mma_kernel<DT, NT>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-    TParams p;
+    TParams p{};
     p.w = a.w;
     p.N = a.n_out;
     p.nsb = a.n_in / 256;
-    p.x = (const XT *)a.x + (int64_t)m0 * a.ldx;
-    p.ldx = a.ldx;
+    p.xh = xh + (int64_t)m0 * a.n_in;
+    p.xs16 = xs16 + (int64_t)m0 * (a.n_in / 16);
     p.M = m;
     p.out = a.out + (int64_t)m0 * a.ldo;
     p.ldo = a.ldo;
@@ -927,9 +981,23 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, int m0, int
     YK_CUDA(cudaGetLastError());
 }
 
-template <int DT, typename XT>
+template <int DT>
 static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a) {
     int launches = 0;
+    const __half * xh = a.xprep.xh;
+    const __half2 * xs16 = a.xprep.xs16;
+    if (!xh) {
+        // activations arrive as f32 / bf16: convert once into the scratch
+        YK_REQUIRE(a.x && a.scratch && a.scratch->xh && a.scratch->xh_elems >= (uint64_t)a.rows * a.n_in,
+                   YUUKA_ERR_INTERNAL, "gemm: no prepared activations and no scratch to prepare them in");
+        if (a.x_dtype == YUUKA_DTYPE_F32)
+            launch_xprep<float>(s, a.scratch->xh, a.scratch->xs16, (const float *)a.x, a.ldx, a.n_in, a.rows);
+        else
+            launch_xprep<__nv_bfloat16>(s, a.scratch->xh, a.scratch->xs16, (const __nv_bfloat16 *)a.x, a.ldx, a.n_in, a.rows);
+        xh = a.scratch->xh;
+        xs16 = a.scratch->xs16;
+        launches++;
+    }
     for (int m0 = 0; m0 < a.rows; m0 += 32) {
         const int m = a.rows - m0 < 32 ? a.rows - m0 : 32;
         TPlan pl;
@@ -940,9 +1008,9 @@ static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGe
             YK_REQUIRE(a.scratch && a.scratch->partial_floats >= (uint64_t)pl.kchunks * m * a.n_out &&
                            a.scratch->counter_count >= pl.n_groups,
                        YUUKA_ERR_INTERNAL, "gemm: split-K scratch is too small");
-        if (m <= 8) launch_mma_inst<DT, 1, XT>(s, a, m0, m, pl);
-        else if (m <= 16) launch_mma_inst<DT, 2, XT>(s, a, m0, m, pl);
-        else launch_mma_inst<DT, 4, XT>(s, a, m0, m, pl);
+        if (m <= 8) launch_mma_inst<DT, 1>(s, a, xh, xs16, m0, m, pl);
+        else if (m <= 16) launch_mma_inst<DT, 2>(s, a, xh, xs16, m0, m, pl);
+        else launch_mma_inst<DT, 4>(s, a, xh, xs16, m0, m, pl);
         launches++;
     }
     return launches;
@@ -978,33 +1046,40 @@ static int launch_fp32_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
     return launches;
 }
 
-template <typename XT>
-static int launch_tiled_x(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, bool mma) {
-    switch (a.w_dtype) {
-    case YUUKA_DTYPE_Q4_K: return mma ? launch_mma_dt<YUUKA_DTYPE_Q4_K, XT>(dev, s, a) : launch_fp32_dt<YUUKA_DTYPE_Q4_K, XT>(dev, s, a);
-    case YUUKA_DTYPE_Q5_K: return mma ? launch_mma_dt<YUUKA_DTYPE_Q5_K, XT>(dev, s, a) : launch_fp32_dt<YUUKA_DTYPE_Q5_K, XT>(dev, s, a);
-    case YUUKA_DTYPE_Q6_K: return mma ? launch_mma_dt<YUUKA_DTYPE_Q6_K, XT>(dev, s, a) : launch_fp32_dt<YUUKA_DTYPE_Q6_K, XT>(dev, s, a);
-    case YUUKA_DTYPE_Q8_0: return mma ? launch_mma_dt<YUUKA_DTYPE_Q8_0, XT>(dev, s, a) : launch_fp32_dt<YUUKA_DTYPE_Q8_0, XT>(dev, s, a);
-    default: YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u has no tiled kernels", a.w_dtype);
-    }
-    return 0;
+template <int DT>
+static int launch_tiled_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, bool mma) {
+    if (mma) return launch_mma_dt<DT>(dev, s, a);
+    YK_REQUIRE(a.x, YUUKA_ERR_INVALID_ARGUMENT, "gemm fp32 route: needs the f32 / bf16 activations");
+    return a.x_dtype == YUUKA_DTYPE_F32 ? launch_fp32_dt<DT, float>(dev, s, a) : launch_fp32_dt<DT, __nv_bfloat16>(dev, s, a);
 }
 
 int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a) {
-    YK_REQUIRE(a.w && a.x && a.out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: null operand");
+    YK_REQUIRE(a.w && (a.x || a.xprep.xh) && a.out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: null operand");
     YK_REQUIRE(a.rows > 0 && a.n_out > 0 && a.n_in > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: invalid shape");
     YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u / width %d has no tiled layout",
                a.w_dtype, a.n_in);
     YK_REQUIRE(a.x_dtype == YUUKA_DTYPE_F32 || a.x_dtype == YUUKA_DTYPE_BF16, YUUKA_ERR_UNSUPPORTED,
                "gemm: activation dtype %u is not F32 or BF16", a.x_dtype);
-    YK_REQUIRE(a.ldx >= a.n_in && a.ldo >= a.n_out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: leading dimension too small");
+    YK_REQUIRE((!a.x || a.ldx >= a.n_in) && a.ldo >= a.n_out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: leading dimension too small");
     uint32_t path = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
     YK_REQUIRE(path == YUUKA_GEMM_PATH_FP32 || path == YUUKA_GEMM_PATH_MMA, YUUKA_ERR_INVALID_ARGUMENT,
                "gemm: unknown path %u", path);
     set_device(dev);
     const bool mma = path == YUUKA_GEMM_PATH_MMA;
-    return a.x_dtype == YUUKA_DTYPE_F32 ? launch_tiled_x<float>(dev, stream, a, mma)
-                                        : launch_tiled_x<__nv_bfloat16>(dev, stream, a, mma);
+    switch (a.w_dtype) {
+    case YUUKA_DTYPE_Q4_K: return launch_tiled_dt<YUUKA_DTYPE_Q4_K>(dev, stream, a, mma);
+    case YUUKA_DTYPE_Q5_K: return launch_tiled_dt<YUUKA_DTYPE_Q5_K>(dev, stream, a, mma);
+    case YUUKA_DTYPE_Q6_K: return launch_tiled_dt<YUUKA_DTYPE_Q6_K>(dev, stream, a, mma);
+    case YUUKA_DTYPE_Q8_0: return launch_tiled_dt<YUUKA_DTYPE_Q8_0>(dev, stream, a, mma);
+    default: YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u has no tiled kernels", a.w_dtype);
+    }
+    return 0;
+}
+
+int read_gemm_wait_expired() {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_gemm_wait_expired, sizeof(int));
+    return v;
 }
 
 }  // namespace yk

@@ -11,6 +11,7 @@
 #pragma once
 
 #include "gemm_quant.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -35,7 +36,8 @@ void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uin
 struct TiledGemmArgs {
     const uint8_t * w = nullptr;  // tiled layout
     uint32_t w_dtype = 0;
-    const void * x = nullptr;
+    const void * x = nullptr;     // f32 / bf16 activations (fp32 route, or to be prepared into the scratch)
+    XPrepOut xprep;               // prepared activations [rows][n_in], if a producer already made them
     uint32_t x_dtype = YUUKA_DTYPE_F32;
     int64_t ldx = 0;
     float * out = nullptr;
@@ -50,5 +52,8 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
 // Scratch the launch above needs for this shape (0 partial floats when K is not split across CTAs).
 void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int rows, int n_out, int n_in,
                              uint64_t * partial_floats, int * counters);
+
+// Non-zero once a bounded wait inside a GEMM kernel has expired (sticky).
+int read_gemm_wait_expired();
 
 }  // namespace yk

@@ -2,6 +2,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -32,10 +33,10 @@ void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table,
                       int vocab, const int32_t * tokens, int rows);
 // dst[r][:] = src[r][:] * rsqrt(mean(src^2) + eps) * weight (forward.go:460-470)
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight,
-                    int cols, int rows, float eps);
+                    int cols, int rows, float eps, XPrepOut prep = XPrepOut());
 // act[r][i] = silu(gate[r][i]) * up[r][i] (forward.go:307-309)
 void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
-                     int rows);
+                     int rows, XPrepOut prep = XPrepOut());
 // Per-head RMSNorm of q and k, RoPE at pos0 + depth, and the paged KV write of
 // every row at slot pos0 + node (forward.go:172-186, kv_pool.go:117-134).
 void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, const float * v, int ldv,
@@ -50,7 +51,7 @@ struct AttnScratch {
 };
 int launch_attention(cudaStream_t s, float * out, int ldo, const float * q, int ldq, int heads, int kv_heads,
                      int head_dim, const RowMeta & rows, const KvPool & pool, int max_total_keys,
-                     const AttnScratch & scratch);
+                     const AttnScratch & scratch, XPrepOut prep = XPrepOut());
 size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits);
 
 // Gated DeltaNet over the rows of a step (forward.go:245-287, recurrent.go:56-105).
@@ -72,7 +73,7 @@ struct GdnArgs {
 void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
 // out[r][h][:] = rmsnorm(out[r][h][:]) * norm * silu(z[r][h][:]) (recurrent.go:39-50)
 void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
-                          int S, int rows, float eps);
+                          int S, int rows, float eps, XPrepOut prep = XPrepOut());
 
 // First-maximum argmax of every logits row (speculative.go:263-271) followed by
 // the greedy tree walk (speculative.go:193-202 generalised to a tree).
