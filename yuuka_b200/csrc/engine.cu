@@ -422,6 +422,10 @@ struct yuuka_session {
     float *x = nullptr, *xn = nullptr, *qkv_attn = nullptr, *attn_out = nullptr, *gdn_out = nullptr;
     float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
     XPrepOut prep_xn, prep_attn, prep_gdn, prep_act;  // fp16 + group sums of the GEMM inputs
+    float *gdn_qn = nullptr, *gdn_vconv = nullptr, *gdn_beta = nullptr;
+    int * gdn_counters = nullptr;
+    int * post_counter = nullptr;
+    bool fuse_post_norm = false;
     int n_proj = 0, n_qkv = 0;
     ArgmaxScratch argmax{};
     AcceptOut acc{};
@@ -459,7 +463,7 @@ void mark(yuuka_session * s, uint32_t code) {
 }
 
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOut prep, float * out, int ldo, int rows,
-          uint32_t flags) {
+          uint32_t flags, const GemmPostNorm * post = nullptr) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     if (w.tiled) {
         TiledGemmArgs t;
@@ -477,6 +481,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.path = YUUKA_GEMM_PATH_AUTO;
         t.flags = flags;
         t.scratch = &s->gemm;
+        if (post) t.post = *post;
         s->launches += launch_gemm_tiled(s->model->dev, s->stream.s, t);
         return;
     }
@@ -496,6 +501,34 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
     a.flags = flags;
     a.scratch = &s->gemm;
     s->launches += launch_gemm_quant(s->model->dev, s->stream.s, a);
+}
+
+// x += W * in, then xn = rmsnorm(x) * norm_w (skipped when norm_w is null). On the mma route the
+// norm runs inside the GEMM launch; otherwise as its own kernel.
+void gemm_residual_norm(yuuka_session * s, const Tensor & w, const float * in, int ld_in, XPrepOut prep_in, int rows,
+                        const float * norm_w) {
+    const yuuka_model_config & c = s->model->cfg;
+    const int H = c.hidden;
+    // Measured on the 4B shape: the in-launch norm (last CTA, 9 rows) costs more than the 9-CTA kernel
+    // it replaces, because every other SM idles behind it. Kept behind a switch.
+    const bool fuse = s->fuse_post_norm && norm_w && w.tiled && rows > 2 && H % 16 == 0;
+    if (fuse) {
+        GemmPostNorm post;
+        post.norm_w = norm_w;
+        post.eps = c.rms_eps;
+        post.dst = s->xn;
+        post.ld = H;
+        post.prep = s->prep_xn;
+        post.counter = s->post_counter;
+        gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, &post);
+        return;
+    }
+    gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE);
+    if (norm_w) {
+        mark(s, YUUKA_OP_RMSNORM);
+        launch_rmsnorm(s->stream.s, s->xn, H, s->x, H, norm_w, H, rows, c.rms_eps, s->prep_xn);
+        s->launches++;
+    }
 }
 
 void reserve_gemm(yuuka_session * s, const Tensor & w, int rows) {
@@ -518,12 +551,15 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     mark(s, YUUKA_OP_EMBEDDING);
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
+    // the first layer's input norm; every later norm rides on the GEMM that finishes the residual stream
+    mark(s, YUUKA_OP_RMSNORM);
+    launch_rmsnorm(st, s->xn, H, s->x, H, m->layers[0].attn_norm, H, R, c.rms_eps, s->prep_xn);
+    s->launches++;
     for (int i = 0; i < c.block_count; i++) {
         const LayerW & L = m->layers[i];
         LayerState & LS = s->layers[i];
-        mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, L.attn_norm, H, R, c.rms_eps, s->prep_xn);
-        s->launches++;
+        const float * next_norm = i + 1 < c.block_count ? m->layers[i + 1].attn_norm
+                                                         : (logit_rows == LOGITS_ALL ? m->output_norm : nullptr);
         if (m->recurrent(i)) {
             const int np = s->n_proj;
             if (L.proj.present()) {
@@ -543,6 +579,14 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.conv_state = LS.conv_state + (int64_t)seq0 * conv_dim * K1;
             g.state = LS.state + (int64_t)seq0 * rank * S * S;
             g.out = s->gdn_out;
+            g.prep = s->prep_gdn;
+            g.z = LS.proj + conv_dim;
+            g.ldz = np;
+            g.norm = L.ssm_norm;
+            g.qn = s->gdn_qn;
+            g.vconv = s->gdn_vconv;
+            g.beta = s->gdn_beta;
+            g.counters = s->gdn_counters;
             g.khat = LS.khat;
             g.dlog = LS.dlog;
             g.decay = LS.decay;
@@ -553,10 +597,8 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.eps = c.rms_eps;
             mark(s, YUUKA_OP_GDN_SCAN);
             launch_gdn_scan(st, g, rows);
-            mark(s, YUUKA_OP_GDN_NORM_GATE);
-            launch_gdn_norm_gate(st, s->gdn_out, inner, LS.proj + conv_dim, np, L.ssm_norm, rank, S, R, c.rms_eps, s->prep_gdn);
             s->launches += 2;
-            gemm(s, L.out, s->gdn_out, inner, s->prep_gdn, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+            gemm_residual_norm(s, L.out, s->gdn_out, inner, s->prep_gdn, R, L.post_norm);
         } else {
             const int nq = s->n_qkv;
             float * qb = s->qkv_attn;
@@ -600,12 +642,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             mark(s, YUUKA_OP_ATTENTION);
             s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
                                             max_total, sc, s->prep_attn);
-            gemm(s, L.o, s->attn_out, o_dim, s->prep_attn, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+            gemm_residual_norm(s, L.o, s->attn_out, o_dim, s->prep_attn, R, L.post_norm);
         }
-        // forwardFFN (model/qwen35/forward.go:295-315)
-        mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, L.post_norm, H, R, c.rms_eps, s->prep_xn);
-        s->launches++;
+        // forwardFFN (model/qwen35/forward.go:295-315); its input norm came with the mixer's output GEMM
         if (L.gate_up.present()) {
             gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
         } else {
@@ -615,13 +654,10 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         mark(s, YUUKA_OP_SILU_MUL);
         launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R, s->prep_act);
         s->launches++;
-        gemm(s, L.ffn_down, s->act, F, s->prep_act, s->x, H, R, YUUKA_GEMM_ACCUMULATE);
+        gemm_residual_norm(s, L.ffn_down, s->act, F, s->prep_act, R, next_norm);
     }
     // tail: final norm + LM head over the wanted rows (forward.go:147-151)
     if (logit_rows == LOGITS_ALL) {
-        mark(s, YUUKA_OP_RMSNORM);
-        launch_rmsnorm(st, s->xn, H, s->x, H, m->output_norm, H, R, c.rms_eps, s->prep_xn);
-        s->launches++;
         gemm(s, m->output, s->xn, H, s->prep_xn, s->logits, c.vocab, R, 0);
     } else if (logit_rows == LOGITS_LAST) {
         // batch == 1: only the last row
@@ -788,6 +824,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->model = model;
             s->cfg = sc;
             if (const char * e = getenv("YUUKA_CUDA_NO_GRAPH")) s->use_graphs = !(e[0] == '1');
+            if (const char * e = getenv("YUUKA_CUDA_FUSE_NORM")) s->fuse_post_norm = e[0] == '1';
             s->stream.dev = model->dev;
             YK_CUDA(cudaStreamCreateWithFlags(&s->stream.s, cudaStreamNonBlocking));
             const int kv_dim = model->kv_dim();
@@ -843,6 +880,11 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->qkv_attn = dalloc<float>((size_t)R * s->n_qkv, s->owned);
             s->attn_out = dalloc<float>((size_t)R * model->o_dim(), s->owned);
             s->gdn_out = dalloc<float>((size_t)R * c.inner_size, s->owned);
+            s->gdn_qn = dalloc<float>((size_t)R * c.group_count * S, s->owned);
+            s->gdn_vconv = dalloc<float>((size_t)R * c.inner_size, s->owned);
+            s->gdn_beta = dalloc<float>((size_t)R * rank, s->owned);
+            s->gdn_counters = dalloc<int>((size_t)B * rank, s->owned);
+            s->post_counter = dalloc<int>(4, s->owned);
             s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
             s->act = dalloc<float>((size_t)R * c.ffn, s->owned);
             auto prep_alloc = [&](int width) {

@@ -11,6 +11,7 @@
 // conv1d_chunk / gdn_prepare_splitreg / gdn_chunk_prepared of the reference
 // (kernels/hip/prefill/prefill.hip:274-521).
 #include "layers.cuh"
+#include "xprep.cuh"
 
 namespace yk {
 
@@ -37,40 +38,81 @@ struct ScanParams {
     RowMeta rows;
 };
 
-// Depthwise causal conv + SiLU for local channel lc of row node, from the staged
-// raw inputs: taps run over the row's ancestors, then into the stored conv
-// history (forward.go:253-268). raw is [N + kernel-1][NCH]: rows 0..kernel-2
-// hold the history (oldest first), row kernel-1+i holds node i.
-template <int NCH>
-__device__ __forceinline__ float conv_channel(const float * raw, const float * w, const int * par, int kernel, int node,
-                                              int lc) {
+// ---------------------------------------------------------------------------
+// Front end, fully parallel over (row, 128-channel unit): depthwise causal conv
+// over the row's ancestors and the stored history + SiLU (forward.go:253-268),
+// L2 norm of the q and k units (forward.go:275-279, 484-493), beta = sigmoid,
+// decay = exp(softplus(alpha + dt) * a) (forward.go:245-248).
+// grid (2*groups + rank, nodes, batch), S threads.
+__global__ void gdn_front_kernel(const ScanParams p) {
+    const GdnArgs & a = p.a;
+    const int S = a.S, N = p.rows.nodes;
+    const int u = blockIdx.x, node = blockIdx.y, seq = blockIdx.z;
+    const int key_dim = a.groups * S, conv_dim = 2 * key_dim + a.rank * S, K1 = a.kernel - 1;
+    const int r = seq * N + node;
+    __shared__ int par[GDN_MAX_NODES];
+    __shared__ double red[4];
+    for (int i = threadIdx.x; i < N; i += blockDim.x) par[i] = p.rows.parent[seq * N + i];
+    __syncthreads();
+    const int e = threadIdx.x;
+    const int c = u * S + e;  // q units, then k units, then v units: exactly the conv row order
     float taps[8];
-    int cur = node, hidx = kernel - 2;
-    for (int t = kernel - 1; t >= 0; t--) {
-        if (cur >= 0) {
-            taps[t] = raw[(kernel - 1 + cur) * NCH + lc];
-            cur = par[cur];
-        } else {
-            taps[t] = raw[hidx-- * NCH + lc];
+    {
+        const float * hist = a.conv_state + ((int64_t)seq * conv_dim + c) * K1;
+        int cur = node, hidx = K1 - 1;
+#pragma unroll
+        for (int t = 7; t >= 0; t--) {
+            if (t >= a.kernel) { taps[t] = 0.0f; continue; }
+            if (cur >= 0) {
+                taps[t] = a.proj[(int64_t)(seq * N + cur) * a.ldp + c];
+                cur = par[cur];
+            } else {
+                taps[t] = hist[hidx--];
+            }
         }
     }
     float sum = 0.0f;
-    for (int i = 0; i < kernel - 1; i++) sum += w[lc * kernel + i] * taps[i];
-    sum += w[lc * kernel + kernel - 1] * taps[kernel - 1];
-    return silu_ref(sum);
+    const float * w = a.conv_w + (int64_t)c * a.kernel;
+#pragma unroll
+    for (int t = 0; t < 8; t++)
+        if (t < a.kernel) sum += w[t] * taps[t];
+    float v = silu_ref(sum);
+    if (u < 2 * a.groups) {
+        double sq = (double)v * (double)v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        double tot = 0;
+        for (int i = 0; i < (S >> 5); i++) tot += red[i];
+        const float scale = (float)(1.0 / sqrt(tot + (double)a.eps));
+        if (u < a.groups) a.qn[(int64_t)r * key_dim + u * S + e] = v * (scale * (float)(1.0 / sqrt((double)S)));
+        else a.khat[(int64_t)r * key_dim + (u - a.groups) * S + e] = v * (scale * 1.0f);
+    } else {
+        const int h = u - 2 * a.groups;
+        a.vconv[(int64_t)r * (a.rank * S) + h * S + e] = v;
+        if (e == 0) {
+            const float * row = a.proj + (int64_t)r * a.ldp;
+            a.beta[(int64_t)r * a.rank + h] = sigmoid_ref(row[conv_dim + a.rank * S + h]);
+            a.decay[(int64_t)r * a.rank + h] = expf(softplus_ref(row[conv_dim + a.rank * S + a.rank + h] + a.dt[h]) * a.a[h]);
+        }
+    }
 }
 
+// ---------------------------------------------------------------------------
+// Recurrence (recurrent.go:56-105) + gated RMSNorm (recurrent.go:39-50).
+// grid (S/32 column blocks, rank, batch), 4 warps: warp w holds state rows
+// [w*S/4, (w+1)*S/4) of 32 columns in registers. The last column block of a
+// head to finish applies the gated norm to the head's outputs and emits them as
+// f32 and in the prepared form the out-projection GEMM reads.
 template <int S>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
-    constexpr int RPW = S / GDN_WARPS;        // state rows per warp
-    constexpr int NCH = 2 * S + GDN_COLS;     // channels this CTA needs: q[S] | k[S] | v[GDN_COLS]
+    constexpr int RPW = S / GDN_WARPS;
     const GdnArgs & a = p.a;
     const int cb = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
     const int N = p.rows.nodes;
     const int kh = h % a.groups;
-    const int key_dim = a.groups * S;
-    const int conv_dim = 2 * key_dim + a.rank * S;
-    const int K1 = a.kernel - 1;
+    const int key_dim = a.groups * S, inner = a.rank * S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = cb * GDN_COLS + lane;
 
@@ -83,82 +125,34 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     float * bet = dec + N;                // [N]
     float * red = bet + N;                // [GDN_WARPS][GDN_COLS]
     float * red2 = red + GDN_WARPS * GDN_COLS;
-    float * raw = red2 + GDN_WARPS * GDN_COLS;   // [K1 + N][NCH] raw inputs of this CTA's channels
-    float * wts = raw + (K1 + N) * NCH;           // [NCH][kernel]
-    int * par = reinterpret_cast<int *>(wts + NCH * a.kernel);  // [N]
-    __shared__ float nrm[2 * GDN_MAX_NODES];  // 1 / sqrt(sum of squares + eps) of q then k rows
+    int * par = reinterpret_cast<int *>(red2 + GDN_WARPS * GDN_COLS);  // [N]
+    __shared__ int last_flag;
+    __shared__ double nred[8 * GDN_WARPS];
+    __shared__ float gbuf[8 * S];  // gated outputs of a chunk of rows
 
-    // The recurrent state does not depend on this step's projections: start its loads first.
+    // stored state first: it does not depend on this step
     const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + warp * RPW) * S + col;
     float st[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
 
-    // ---- stage raw inputs, history, taps and parents with coalesced loads ----
-    auto channel = [&](int lc) {  // local channel -> channel of the conv row
-        return lc < S ? kh * S + lc : (lc < 2 * S ? key_dim + kh * S + (lc - S) : 2 * key_dim + h * S + cb * GDN_COLS + (lc - 2 * S));
-    };
-    for (int i = threadIdx.x; i < N * NCH; i += blockDim.x) {
-        const int node = i / NCH, lc = i - node * NCH;
-        raw[(K1 + node) * NCH + lc] = a.proj[(int64_t)(seq * N + node) * a.ldp + channel(lc)];
+    for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
+        const int node = i / S, e = i - node * S;
+        qn[i] = a.qn[(int64_t)(seq * N + node) * key_dim + kh * S + e];
+        kn[i] = a.khat[(int64_t)(seq * N + node) * key_dim + kh * S + e];
     }
-    for (int i = threadIdx.x; i < NCH * K1; i += blockDim.x) {
-        const int lc = i / K1, t = i - lc * K1;
-        raw[t * NCH + lc] = a.conv_state[((int64_t)seq * conv_dim + channel(lc)) * K1 + t];
-    }
-    for (int i = threadIdx.x; i < NCH * a.kernel; i += blockDim.x) {
-        const int lc = i / a.kernel, t = i - lc * a.kernel;
-        wts[i] = a.conv_w[(int64_t)channel(lc) * a.kernel + t];
+    for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
+        const int node = i / GDN_COLS, e = i - node * GDN_COLS;
+        vv[i] = a.vconv[(int64_t)(seq * N + node) * inner + h * S + cb * GDN_COLS + e];
     }
     for (int node = threadIdx.x; node < N; node += blockDim.x) {
         par[node] = p.rows.parent[seq * N + node];
-        const float * row = a.proj + (int64_t)(seq * N + node) * a.ldp;
-        const float b = row[conv_dim + a.rank * S + h];
-        const float al = row[conv_dim + a.rank * S + a.rank + h];
-        bet[node] = sigmoid_ref(b);
-        dec[node] = expf(softplus_ref(al + a.dt[h]) * a.a[h]);
+        bet[node] = a.beta[(int64_t)(seq * N + node) * a.rank + h];
+        dec[node] = a.decay[(int64_t)(seq * N + node) * a.rank + h];
     }
     __syncthreads();
-    // ---- front end: conv + SiLU ----
-    for (int i = threadIdx.x; i < N * NCH; i += blockDim.x) {
-        const int node = i / NCH, lc = i - node * NCH;
-        const float v = conv_channel<NCH>(raw, wts, par, a.kernel, node, lc);
-        if (lc < S) qn[node * S + lc] = v;
-        else if (lc < 2 * S) kn[node * S + lc - S] = v;
-        else vv[node * GDN_COLS + lc - 2 * S] = v;
-    }
-    __syncthreads();
-    // l2NormHead (forward.go:484-493): f64 sum, scale = f32(1/sqrt(sum + eps)) * extra
-    for (int v = warp; v < 2 * N; v += GDN_WARPS) {
-        const float * x = (v < N ? qn : kn) + (v % N) * S;
-        double sum = 0;
-        for (int i = lane; i < S; i += 32) sum += (double)x[i] * (double)x[i];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) nrm[v] = (float)(1.0 / sqrt(sum + (double)a.eps));
-    }
-    __syncthreads();
-    {
-        const float q_scale = (float)(1.0 / sqrt((double)S));
-        for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
-            int node = i / S;
-            qn[i] *= nrm[node] * q_scale;
-            kn[i] *= nrm[N + node] * 1.0f;
-        }
-    }
-    __syncthreads();
-    if (cb == 0 && h < a.groups) {
-        for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
-            int node = i / S, e = i - node * S;
-            a.khat[(int64_t)(seq * N + node) * key_dim + h * S + e] = kn[i];
-        }
-    }
-    if (cb == 0)
-        for (int node = threadIdx.x; node < N; node += blockDim.x) a.decay[(int64_t)(seq * N + node) * a.rank + h] = dec[node];
 
-    // ---- recurrence: this thread holds rows [warp*RPW, +RPW) of column col ----
     int cur = -1;  // node whose state st currently holds (-1: the stored state)
-
     for (int node = 0; node < N; node++) {
         const int pnode = par[node];
         if (pnode != cur) {
@@ -202,30 +196,87 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
             o = 0.0f;
 #pragma unroll
             for (int w = 0; w < GDN_WARPS; w++) o += red2[w * GDN_COLS + lane];
-            a.out[(int64_t)(seq * N + node) * (a.rank * S) + h * S + col] = o;
-            a.dlog[(int64_t)(seq * N + node) * (a.rank * S) + h * S + col] = d;
+            __stcg(a.out + (int64_t)(seq * N + node) * inner + h * S + col, o);
+            a.dlog[(int64_t)(seq * N + node) * inner + h * S + col] = d;
         }
         cur = node;
     }
+
+    // ---- gated RMSNorm of the head, by the last column block to arrive ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_flag = atomicAdd(&a.counters[seq * a.rank + h], 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    // eight rows at a time so that the loads of a chunk are all in flight together
+    constexpr int NB = 8;
+    for (int n0 = 0; n0 < N; n0 += NB) {
+        const int nb = min(NB, N - n0);
+        const int j = threadIdx.x;
+        float v[NB], zz[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int64_t r = seq * N + n0 + b;
+            const bool live = b < nb && j < S;
+            v[b] = live ? __ldcg(a.out + r * inner + h * S + j) : 0.0f;
+            zz[b] = live ? a.z[r * a.ldz + h * S + j] : 0.0f;
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            double sq = (double)v[b] * (double)v[b];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) nred[b * GDN_WARPS + warp] = sq;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            double tot = 0;
+            for (int w = 0; w < GDN_WARPS; w++) tot += nred[b * GDN_WARPS + w];
+            const float mean = (float)(tot / (double)S);
+            const float scale = (float)(1.0 / sqrt((double)(mean + a.eps)));
+            if (b < nb && j < S) {
+                float t = v[b];
+                t *= scale * a.norm[j];
+                gbuf[b * S + j] = t * silu_ref(zz[b]);
+            }
+        }
+        __syncthreads();
+        for (int gi = threadIdx.x; gi < nb * (S >> 4); gi += blockDim.x) {
+            const int b = gi / (S >> 4), part = gi - b * (S >> 4);
+            const int64_t r = seq * N + n0 + b;
+            float g16[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) g16[i] = gbuf[b * S + part * 16 + i];
+            float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + h * S + part * 16);
+#pragma unroll
+            for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
+            if (a.prep.xh)
+                xprep_store16(a.prep.xh + r * inner + h * S + part * 16, a.prep.xs16 + r * (inner >> 4) + ((h * S) >> 4) + part, g16);
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) a.counters[seq * a.rank + h] = 0;
 }
 
 void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per sequence", GDN_MAX_NODES);
     YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
+    YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
     ScanParams p{a, rows};
     const int N = rows.nodes;
-    const int nch = 2 * a.S + GDN_COLS;
-    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS +
-                                   (size_t)(a.kernel - 1 + N) * nch + (size_t)nch * a.kernel + N);
+    dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
+    gdn_front_kernel<<<fgrid, a.S, 0, s>>>(p);
+    YK_CUDA(cudaGetLastError());
+    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS + N);
     dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         gdn_scan_kernel<128><<<grid, GDN_WARPS * 32, smem, s>>>(p);
-    } else if (a.S == 64) {
+    } else {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         gdn_scan_kernel<64><<<grid, GDN_WARPS * 32, smem, s>>>(p);
-    } else {
-        YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
     }
     YK_CUDA(cudaGetLastError());
 }

@@ -562,7 +562,49 @@ struct TParams {
     int n_groups;
     float * partial;
     int * counters;
+    // optional: RMSNorm of the finished output rows by the last CTA to arrive
+    const float * post_norm_w;
+    float post_eps;
+    float * post_dst;
+    int64_t post_ld;
+    XPrepOut post_prep;
+    int * post_counter;
 };
+
+// rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
+// one warp per row, emitting f32 and the prepared form.
+__device__ void post_rmsnorm_rows(const TParams & p, int warp, int lane) {
+    const int cols = p.N;
+    for (int m = warp; m < p.M; m += TW) {
+        const float * x = p.out + (int64_t)m * p.ldo;
+        double sum = 0;
+        for (int i = lane; i < cols; i += 32) {
+            const float v = __ldcg(x + i);
+            sum += (double)v * (double)v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = (float)(sum / (double)cols);
+        const float scale = (float)(1.0 / sqrt((double)(mean + p.post_eps)));
+        for (int gq = lane; gq < (cols >> 4); gq += 32) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float4 xv = __ldcg(reinterpret_cast<const float4 *>(x + gq * 16) + i);
+                const float4 wv = reinterpret_cast<const float4 *>(p.post_norm_w + gq * 16)[i];
+                v[4 * i] = xv.x * scale * wv.x;
+                v[4 * i + 1] = xv.y * scale * wv.y;
+                v[4 * i + 2] = xv.z * scale * wv.z;
+                v[4 * i + 3] = xv.w * scale * wv.w;
+            }
+            float4 * d = reinterpret_cast<float4 *>(p.post_dst + (int64_t)m * p.post_ld + gq * 16);
+#pragma unroll
+            for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            if (p.post_prep.xh)
+                xprep_store16(p.post_prep.xh + (int64_t)m * cols + gq * 16, p.post_prep.xs16 + (int64_t)m * (cols >> 4) + gq, v);
+        }
+    }
+}
 
 template <int DT, int NT>
 __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParams p) {
@@ -728,6 +770,19 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             }
         } else if (p.KS > 1) {
             __syncthreads();  // red is reused by the next group
+        }
+    }
+
+    if (p.post_norm_w) {
+        // every CTA has written (and, with a K split across CTAs, finalised) its rows before it arrives here
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last_flag = atomicAdd(p.post_counter, 1) == (int)(gridDim.x * gridDim.y) - 1;
+        __syncthreads();
+        if (last_flag) {
+            __threadfence();
+            post_rmsnorm_rows(p, warp, lane);
+            if (threadIdx.x == 0) *p.post_counter = 0;
         }
     }
 }
@@ -976,6 +1031,18 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     p.n_groups = pl.n_groups;
     p.partial = a.scratch ? a.scratch->partial : nullptr;
     p.counters = a.scratch ? a.scratch->counters : nullptr;
+    if (a.post.norm_w) {
+        p.post_norm_w = a.post.norm_w;
+        p.post_eps = a.post.eps;
+        p.post_dst = a.post.dst + (int64_t)m0 * a.post.ld;
+        p.post_ld = a.post.ld;
+        p.post_prep = a.post.prep;
+        if (p.post_prep.xh) {
+            p.post_prep.xh += (int64_t)m0 * a.n_out;
+            p.post_prep.xs16 += (int64_t)m0 * (a.n_out / 16);
+        }
+        p.post_counter = a.post.counter;
+    }
     dim3 grid(pl.grid_x, pl.kchunks);
     kern<<<grid, TW * 32, pl.smem, s>>>(p);
     YK_CUDA(cudaGetLastError());
@@ -1055,6 +1122,8 @@ static int launch_tiled_dt(const yuuka_device * dev, cudaStream_t s, const Tiled
 
 int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a) {
     YK_REQUIRE(a.w && (a.x || a.xprep.xh) && a.out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: null operand");
+    YK_REQUIRE(!a.post.norm_w || (a.post.dst && a.post.counter && a.n_out % 16 == 0 && a.ldo % 4 == 0 && a.post.ld % 4 == 0),
+               YUUKA_ERR_INVALID_ARGUMENT, "gemm: the fused RMSNorm needs a destination, a counter and a width that is a multiple of 16");
     YK_REQUIRE(a.rows > 0 && a.n_out > 0 && a.n_in > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: invalid shape");
     YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u / width %d has no tiled layout",
                a.w_dtype, a.n_in);

@@ -33,6 +33,17 @@ inline uint64_t tiled_bytes(uint32_t dtype, uint64_t n_out, uint64_t n_in) {
 // dst (tiled_bytes long) <- GGUF rows at src. Rows beyond n_out are zero.
 void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uint32_t dtype, int n_out, int n_in);
 
+// RMSNorm of the GEMM's finished output rows, done inside the same launch by the
+// last CTA to finish (mma route only): dst = rmsnorm(out) * norm_w.
+struct GemmPostNorm {
+    const float * norm_w = nullptr;
+    float eps = 0.0f;
+    float * dst = nullptr;
+    int64_t ld = 0;
+    XPrepOut prep;
+    int * counter = nullptr;  // one int, zero between launches
+};
+
 struct TiledGemmArgs {
     const uint8_t * w = nullptr;  // tiled layout
     uint32_t w_dtype = 0;
@@ -46,6 +57,7 @@ struct TiledGemmArgs {
     uint32_t path = YUUKA_GEMM_PATH_AUTO;
     uint32_t flags = 0;
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
+    GemmPostNorm post;
 };
 
 int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a);

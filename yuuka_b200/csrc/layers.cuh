@@ -63,13 +63,22 @@ struct GdnArgs {
     const float * a;         // [rank]
     const float * conv_state;  // [batch][conv_dim][kernel-1]
     const float * state;       // [batch][rank][S][S]
-    float * out;             // [rows][inner] raw per-head outputs
+    const float * z;         // gate projection rows (= proj + conv_dim), leading dimension ldz
+    int ldz;
+    const float * norm;      // [S] gated-norm weight
+    float * out;             // [rows][inner] gated head outputs (f32)
+    XPrepOut prep;           // same, prepared for the out-projection GEMM
+    float * qn;              // [rows][groups*S] scratch: normalised queries
+    float * vconv;           // [rows][inner] scratch: conv output of v
+    float * beta;            // [rows][rank] scratch
     float * khat;            // [rows][groups*S] log: normalised keys
     float * dlog;            // [rows][rank*S]   log: beta * (v - S^T k)
     float * decay;           // [rows][rank]     log: exp(alpha)
+    int * counters;          // [batch][rank] arrival counters, zero between launches
     int groups, rank, S, kernel;
     float eps;
 };
+// conv + norms (one kernel), then the recurrence with the gated RMSNorm folded in (one kernel)
 void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
 // out[r][h][:] = rmsnorm(out[r][h][:]) * norm * silu(z[r][h][:]) (recurrent.go:39-50)
 void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
