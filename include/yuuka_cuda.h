@@ -137,6 +137,34 @@ YUUKA_API yuuka_status yuuka_gemm_quant(yuuka_stream * stream,
                                         uint64_t n_in, uint64_t n_out, uint64_t rows,
                                         uint32_t path, uint32_t flags, yuuka_event * completion);
 
+/* The tiled GEMM above with its scratch memory in a fixed device array of this
+ * library instead of the per-device scratch that yuuka_gemm_quant grows with
+ * cudaMalloc when a larger shape arrives. No counterpart in the reference. It is
+ * for hosts that may not cause a device allocation once serving has started:
+ * an engine that hands all free HBM to its weight and KV pools at start-up
+ * (a later cudaMalloc can fail there, and it stalls every stream of the device
+ * while it runs), or a real-time loop that must not take the allocator's lock.
+ * This call allocates and frees nothing, on the device or through a library.
+ *  - Same arguments, routes and bit-identical results as yuuka_gemm_quant with
+ *    YUUKA_GEMM_TILED, which flags must carry.
+ *  - The scratch holds the prepared fp16 activations (rows * n_in * 2.25 bytes),
+ *    the split-K partial sums and 4096 arrival counters. A shape that needs more
+ *    than YUUKA_GEMM_STATIC_SCRATCH_BYTES returns YUUKA_ERR_UNSUPPORTED and
+ *    launches nothing; yuuka_last_error() names the bytes needed.
+ *  - The first call on each device does the set-up (it looks up the array's
+ *    device address, zeroes the counters and synchronizes the device): make
+ *    that call before any stream capture begins. Later calls only launch.
+ *  - One scratch per device: two calls whose kernels can overlap (different
+ *    streams, or two host threads) race on it. Keep calls on one stream, or
+ *    order them with events. */
+#define YUUKA_GEMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+YUUKA_API yuuka_status yuuka_gemm_quant_static(yuuka_stream * stream,
+                                               yuuka_buffer * out, uint64_t out_offset,
+                                               const yuuka_buffer * x, uint64_t x_offset, uint32_t x_dtype,
+                                               const yuuka_buffer * w, uint64_t w_offset, uint32_t w_dtype,
+                                               uint64_t n_in, uint64_t n_out, uint64_t rows,
+                                               uint32_t path, uint32_t flags, yuuka_event * completion);
+
 /* Tile-ordered weight copy: a byte permutation of a K-quant / Q8_0 GGUF matrix
  * into 16-row x 256-column records laid out in the order a warp consumes them
  * (the reference uploads GGUF bytes verbatim, engine/gpu/model.go:288-301; its

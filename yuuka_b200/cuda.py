@@ -96,6 +96,8 @@ SIGNATURES = {
     "yuuka_buffer_copy": (_i32, [_vp, _vp, _u64, _vp, _u64, _u64, _vp]),
     "yuuka_gemm_quant": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
                                 _u32, _u32, _vp]),
+    "yuuka_gemm_quant_static": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
+                                _u32, _u32, _vp]),
     "yuuka_weights_tiled_bytes": (_u64, [_u32, _u64, _u64]),
     "yuuka_weights_tile": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _u64, _u64, _vp]),
     "yuuka_model_create": (_i32, [_vp, _vp, _vp]),
@@ -274,6 +276,17 @@ def gemm_quant(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_o
                out_offset: int = 0, x_offset: int = 0, w_offset: int = 0, completion: Event | None = None):
     check(lib().yuuka_gemm_quant(stream.h, out.h, out_offset, x.h, x_offset, x_dtype, w.h, w_offset, w_dtype,
                                  n_in, n_out, rows, path, flags, completion.h if completion else None))
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def gemm_quant_static(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_out: int, rows: int,
+                      w_dtype: int, x_dtype: int = F32, path: int = PATH_AUTO, flags: int = GEMM_TILED,
+                      out_offset: int = 0, x_offset: int = 0, w_offset: int = 0, completion: Event | None = None):
+    """yuuka_gemm_quant with its scratch in a fixed device array (allocates nothing)."""
+    check(lib().yuuka_gemm_quant_static(stream.h, out.h, out_offset, x.h, x_offset, x_dtype, w.h, w_offset, w_dtype,
+                                        n_in, n_out, rows, path, flags, completion.h if completion else None))
 
 
 class Model:
