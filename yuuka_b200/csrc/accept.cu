@@ -24,6 +24,7 @@ __device__ __forceinline__ void best_of(float & v, int & i, float ov, int oi) {
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __restrict__ logits, int vocab,
                                                              float * __restrict__ val, int32_t * __restrict__ idx,
                                                              int chunks) {
+    pdl_entry();
     const int r = blockIdx.y, c = blockIdx.x;
     const float * row = logits + (int64_t)r * vocab;
     const int begin = c * ARGMAX_CHUNK, end = min(vocab, begin + ARGMAX_CHUNK);
@@ -60,6 +61,7 @@ struct WalkParams {
 
 // one CTA per sequence: finish the argmax of each of its rows, then walk
 __global__ void __launch_bounds__(64) greedy_walk_kernel(const WalkParams p) {
+    pdl_entry();
     __shared__ int want[64];
     const int seq = blockIdx.x, N = p.rows.nodes;
     for (int node = threadIdx.x; node < N; node += blockDim.x) {
@@ -99,15 +101,16 @@ int launch_accept_greedy(cudaStream_t s, const float * logits, int vocab, const 
     const int chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
     YK_REQUIRE(chunks <= scratch.chunks, YUUKA_ERR_INTERNAL, "argmax scratch is too small");
     dim3 grid(chunks, R);
-    argmax_partial_kernel<<<grid, 256, 0, s>>>(logits, vocab, scratch.val, scratch.idx, scratch.chunks);
+    launch_k(argmax_partial_kernel, grid, 256, 0, s, logits, vocab, scratch.val, scratch.idx, scratch.chunks);
     YK_CUDA(cudaGetLastError());
     WalkParams p{scratch.val, scratch.idx, scratch.chunks, rows, out};
-    greedy_walk_kernel<<<rows.batch, 64, 0, s>>>(p);
+    launch_k(greedy_walk_kernel, rows.batch, 64, 0, s, p);
     YK_CUDA(cudaGetLastError());
     return 2;
 }
 
 __global__ void accept_all_kernel(RowMeta rows, AcceptOut out) {
+    pdl_entry();
     const int seq = blockIdx.x, N = rows.nodes;
     if (threadIdx.x == 0) out.accepted[seq] = N - 1;
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
@@ -117,7 +120,7 @@ __global__ void accept_all_kernel(RowMeta rows, AcceptOut out) {
 }
 
 void launch_accept_all(cudaStream_t s, const RowMeta & rows, const AcceptOut & out) {
-    accept_all_kernel<<<rows.batch, 64, 0, s>>>(rows, out);
+    launch_k(accept_all_kernel, rows.batch, 64, 0, s, rows, out);
     YK_CUDA(cudaGetLastError());
 }
 

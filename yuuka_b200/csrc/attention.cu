@@ -49,6 +49,7 @@ __device__ __forceinline__ void kv_decode8(const uint8_t * row, int format, int 
 
 template <int HD>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const AttnParams p) {
+    pdl_entry();
     constexpr int KSTR = HD + 4;
     extern __shared__ __align__(16) float sm[];
     float * qs = sm;                       // [ATT_QT][HD]
@@ -192,6 +193,7 @@ __device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + ex
 template <int HD>
 __global__ void attention_merge_kernel(float * __restrict__ out, int ldo, const float * __restrict__ partial,
                                        const float * __restrict__ q, int ldq, int heads, int splits, XPrepOut prep) {
+    pdl_entry();
     const int r = blockIdx.x;
     const int gq = threadIdx.x;  // 16-group within the row: head * (HD/16) + part
     if (gq >= heads * (HD / 16)) return;
@@ -252,11 +254,11 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
     auto kern = attention_partial_kernel<HD>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
-    kern<<<grid, ATT_WARPS * 32, smem, s>>>(p);
+    launch_k(kern, grid, ATT_WARPS * 32, smem, s, p);
     YK_CUDA(cudaGetLastError());
     const int mthreads = ((heads * (HD / 16) + 31) / 32) * 32;
     YK_REQUIRE(mthreads <= 1024, YUUKA_ERR_UNSUPPORTED, "attention: too many heads for the merge kernel");
-    attention_merge_kernel<HD><<<rows.batch * rows.nodes, mthreads, 0, s>>>(out, ldo, sc.partial, q, ldq, heads, sc.splits, prep);
+    launch_k(attention_merge_kernel<HD>, rows.batch * rows.nodes, mthreads, 0, s, out, ldo, sc.partial, q, ldq, heads, sc.splits, prep);
     YK_CUDA(cudaGetLastError());
     return 2;
 }

@@ -2,6 +2,8 @@
 // Mirrors the handle and error conventions of backend/hip/bridge/bridge.cpp.
 #include <cstring>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace yk {
@@ -24,6 +26,16 @@ yuuka_status fail(yuuka_status code, const char * fmt, ...) {
 }  // namespace yk
 
 using namespace yk;
+
+namespace yk {
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char * e = getenv("YUUKA_CUDA_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+}  // namespace yk
 
 extern "C" {
 

@@ -11,6 +11,7 @@ namespace yk {
 
 __global__ void embedding_kernel(float * __restrict__ x, int ldx, const uint8_t * __restrict__ table, uint32_t dtype,
                                  int64_t rb, int hidden, int vocab, const int32_t * __restrict__ tokens) {
+    pdl_entry();
     const int r = blockIdx.x;
     int tok = tokens[r];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // ids are validated on the host
@@ -32,7 +33,7 @@ __global__ void embedding_kernel(float * __restrict__ x, int ldx, const uint8_t 
 
 void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
                       const int32_t * tokens, int rows) {
-    embedding_kernel<<<rows, 128, 0, s>>>(x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens);
+    launch_k(embedding_kernel, rows, 128, 0, s, x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -61,6 +62,7 @@ __device__ __forceinline__ double block_sum_d(double v, double * red) {
 // prepared (fp16 + group sums) form of dst for the GEMM that consumes it.
 __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
                                const float * __restrict__ weight, int cols, float eps, XPrepOut prep) {
+    pdl_entry();
     __shared__ double red[32];
     const int r = blockIdx.x;
     const float * x = src + (int64_t)r * lds;
@@ -88,7 +90,7 @@ void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int
                     int rows, float eps, XPrepOut prep) {
     YK_REQUIRE(!prep.xh || ((cols & 15) == 0 && (ldd & 3) == 0), YUUKA_ERR_UNSUPPORTED,
                "rmsnorm: prepared output needs a width that is a multiple of 16");
-    rmsnorm_kernel<<<rows, 256, 0, s>>>(dst, ldd, src, lds, weight, cols, eps, prep);
+    launch_k(rmsnorm_kernel, rows, 256, 0, s, dst, ldd, src, lds, weight, cols, eps, prep);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -99,6 +101,7 @@ __device__ __forceinline__ float silu_ref(float x) { return x * sigmoid_ref(x); 
 
 __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float * __restrict__ gate,
                                 const float * __restrict__ up, int ld, int cols, XPrepOut prep) {
+    pdl_entry();
     const int r = blockIdx.y;
     for (int gq = blockIdx.x * blockDim.x + threadIdx.x; gq < (cols >> 4); gq += gridDim.x * blockDim.x) {
         float v[16];
@@ -115,7 +118,7 @@ void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, c
                      int rows, XPrepOut prep) {
     YK_REQUIRE((cols & 15) == 0 && (lda & 3) == 0, YUUKA_ERR_UNSUPPORTED, "silu_mul: width must be a multiple of 16");
     dim3 grid(((cols >> 4) + 127) / 128, rows);
-    silu_mul_kernel<<<grid, 128, 0, s>>>(act, lda, gate, up, ld, cols, prep);
+    launch_k(silu_mul_kernel, grid, 128, 0, s, act, lda, gate, up, ld, cols, prep);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -188,6 +191,7 @@ __device__ void kv_encode_row(uint8_t * dst, int format, const float * src, int 
 }
 
 __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
+    pdl_entry();
     const int r = blockIdx.x;
     const int seq = r / p.rows.nodes, node = r - seq * p.rows.nodes;
     const int pos0 = p.rows.pos0[seq];
@@ -218,7 +222,7 @@ void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, co
                       const float * q_norm, const float * k_norm, int heads, int kv_heads, int head_dim, int rope_dim,
                       double rope_base, float eps, const RowMeta & rows, const KvPool & pool) {
     PrepParams p{q, ldq, k, ldk, v, ldv, q_norm, k_norm, heads, kv_heads, head_dim, rope_dim, rope_base, eps, rows, pool};
-    attn_prep_kernel<<<rows.batch * rows.nodes, 256, 0, s>>>(p);
+    launch_k(attn_prep_kernel, rows.batch * rows.nodes, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -228,6 +232,7 @@ void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, co
 // one thread per 16 consecutive values; a head (S values) is S/16 adjacent lanes
 __global__ void gdn_norm_gate_kernel(float * __restrict__ out, int ldo, const float * __restrict__ z, int ldz,
                                      const float * __restrict__ norm, int rank, int S, float eps, XPrepOut prep) {
+    pdl_entry();
     const int r = blockIdx.y;
     const int lanes = S >> 4;                              // 8 (S = 128) or 4 (S = 64)
     const int gq = blockIdx.x * blockDim.x + threadIdx.x;  // 16-group index within the row
@@ -264,7 +269,7 @@ void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z,
     YK_REQUIRE(S == 64 || S == 128, YUUKA_ERR_UNSUPPORTED, "gdn_norm_gate: state size %d is not 64 or 128", S);
     const int groups = rank * (S >> 4);
     dim3 grid((groups + 127) / 128, rows);
-    gdn_norm_gate_kernel<<<grid, 128, 0, s>>>(out, ldo, z, ldz, norm, rank, S, eps, prep);
+    launch_k(gdn_norm_gate_kernel, grid, 128, 0, s, out, ldo, z, ldz, norm, rank, S, eps, prep);
     YK_CUDA(cudaGetLastError());
 }
 

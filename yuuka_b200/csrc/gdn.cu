@@ -45,6 +45,7 @@ struct ScanParams {
 // decay = exp(softplus(alpha + dt) * a) (forward.go:245-248).
 // grid (2*groups + rank, nodes, batch), S threads.
 __global__ void gdn_front_kernel(const ScanParams p) {
+    pdl_entry();
     const GdnArgs & a = p.a;
     const int S = a.S, N = p.rows.nodes;
     const int u = blockIdx.x, node = blockIdx.y, seq = blockIdx.z;
@@ -107,6 +108,7 @@ __global__ void gdn_front_kernel(const ScanParams p) {
 // f32 and in the prepared form the out-projection GEMM reads.
 template <int S>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
+    pdl_entry();
     constexpr int RPW = S / GDN_WARPS;
     const GdnArgs & a = p.a;
     const int cb = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
@@ -267,16 +269,16 @@ void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     ScanParams p{a, rows};
     const int N = rows.nodes;
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
-    gdn_front_kernel<<<fgrid, a.S, 0, s>>>(p);
+    launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
     size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS + N);
     dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        gdn_scan_kernel<128><<<grid, GDN_WARPS * 32, smem, s>>>(p);
+        launch_k(gdn_scan_kernel<128>, grid, GDN_WARPS * 32, smem, s, p);
     } else {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        gdn_scan_kernel<64><<<grid, GDN_WARPS * 32, smem, s>>>(p);
+        launch_k(gdn_scan_kernel<64>, grid, GDN_WARPS * 32, smem, s, p);
     }
     YK_CUDA(cudaGetLastError());
 }
@@ -295,6 +297,7 @@ struct CommitParams {
 // grid (rank + 1, batch, layers): blocks 0..rank-1 update one head's state,
 // block `rank` rewrites the conv history.
 __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
+    pdl_entry();
     const GdnLayerCommit L = p.layers[blockIdx.z];
     const int seq = blockIdx.y, N = p.rows.nodes, S = p.S;
     const int a = p.acc.accepted[seq];
@@ -336,7 +339,7 @@ void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_
     if (n_layers == 0) return;
     CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, rows, acc};
     dim3 grid(rank + 1, rows.batch, n_layers);
-    gdn_commit_kernel<<<grid, 256, 0, s>>>(p);
+    launch_k(gdn_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -352,6 +355,7 @@ struct KvCommitParams {
 };
 
 __global__ void kv_commit_kernel(const KvCommitParams p) {
+    pdl_entry();
     const KvLayerCommit L = p.layers[blockIdx.y];
     const int seq = blockIdx.x, N = p.rows.nodes;
     const int a = p.acc.accepted[seq];
@@ -384,17 +388,18 @@ void launch_kv_commit(cudaStream_t s, const KvLayerCommit * layers_dev, int n_la
     if (n_layers == 0) return;
     KvCommitParams p{layers_dev, geom, rows, acc};
     dim3 grid(rows.batch, n_layers);
-    kv_commit_kernel<<<grid, 256, 0, s>>>(p);
+    launch_k(kv_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
 __global__ void advance_positions_kernel(int32_t * pos0, const int32_t * accepted, int batch) {
+    pdl_entry();
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch) pos0[b] += accepted[b] + 1;
 }
 
 void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch) {
-    advance_positions_kernel<<<(batch + 127) / 128, 128, 0, s>>>(pos0, acc.accepted, batch);
+    launch_k(advance_positions_kernel, (batch + 127) / 128, 128, 0, s, pos0, acc.accepted, batch);
     YK_CUDA(cudaGetLastError());
 }
 

@@ -630,13 +630,17 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     const int n_tiles = (p.N + 15) >> 4;
     const size_t rec_row = (size_t)p.nsb * C::REC;
 
-    // Weights do not depend on the previous kernel: start the first loads before touching x.
+    // Weights do not depend on the previous kernel: start the first loads, and pull the rest of the
+    // first group's records towards L2, before waiting for the kernel that produces x.
+    pdl_trigger();
     int grp = blockIdx.x;
     typename C::Regs cur, nxt;
     {
         const int rt = min(grp * p.TG + tile_in_group, n_tiles - 1);
         if (sb0 < sb1) C::load(p.w + rt * rec_row + (size_t)sb0 * C::REC, lane, cur);
+        if (sb0 + 1 < sb1) prefetch_l2_range(p.w + rt * rec_row + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
     }
+    pdl_wait();
 
     // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums ----
     if (threadIdx.x == 0) {
@@ -697,7 +701,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             for (int c = 0; c < 4; c++) acc[j][c] = 0.0f;
         // the rest of this warp's records: get them moving from DRAM to L2 now; the register
         // double buffer below then only has to cover the L2 latency
-        if (sb0 + 1 < sb1) prefetch_l2_range(tile + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
+        if (grp != (int)blockIdx.x && sb0 + 1 < sb1)
+            prefetch_l2_range(tile + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
 
         for (int sb = sb0; sb < sb1; sb++) {
             // prefetch the next record of this tile, or the first record of the next group's tile
@@ -803,6 +808,7 @@ __device__ __forceinline__ uint32_t piece_byte(uint32_t w0, uint32_t w1, int b) 
 
 template <int DT, typename XT>
 __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams p) {
+    pdl_entry();
     using C = Codec<DT>;
     extern __shared__ __align__(16) float xf32[];  // [M][K]
     const int K = p.nsb * 256;
@@ -1044,7 +1050,7 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
         p.post_counter = a.post.counter;
     }
     dim3 grid(pl.grid_x, pl.kchunks);
-    kern<<<grid, TW * 32, pl.smem, s>>>(p);
+    launch_k(kern, grid, TW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -1106,7 +1112,7 @@ static int launch_fp32_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         p.out = a.out + (int64_t)m0 * a.ldo;
         p.ldo = a.ldo;
         p.accumulate = (a.flags & YUUKA_GEMM_ACCUMULATE) ? 1 : 0;
-        kern<<<grid, TW * 32, (size_t)m * a.n_in * sizeof(float), s>>>(p);
+        launch_k(kern, grid, TW * 32, (size_t)m * a.n_in * sizeof(float), s, p);
         YK_CUDA(cudaGetLastError());
         launches++;
     }
