@@ -296,7 +296,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
                     "h2d_bytes_per_step": rows * (4 + 4 + 4 + 8), "d2h_bytes_per_step": 4 + 2 * rows * 4},
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gemm_q_mma_kernel (all quantized GEMMs of a step)",
+            "roofline": {"bound": "hbm", "kernel": "gemm_tiled_mma_kernel (every quantized GEMM launch of a step, LM head included)",
                          "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak,
                          "peak_source": peak_kind, "bytes_per_step": weight_bytes, "ms_per_step": gemm_ms,
                          "traffic": None},

@@ -319,6 +319,55 @@ YUUKA_API yuuka_stream * yuuka_session_stream(yuuka_session * s);
 /* Kernel launches enqueued by the last yuuka_verify_launch. */
 YUUKA_API uint32_t yuuka_session_last_launch_count(const yuuka_session * s);
 
+/* Geometry of a session, for callers that drive it generically. */
+typedef struct yuuka_session_info {
+    int32_t max_batch, max_nodes, capacity, block_size, pool_blocks, kv_format;
+    int32_t vocab;
+} yuuka_session_info;
+YUUKA_API yuuka_status yuuka_session_info_get(const yuuka_session * s, yuuka_session_info * out);
+
+/* ------------------------------------------------------------------------
+ * Exact greedy speculative decoding with prompt-lookup drafts: the host loop
+ * of engine/speculative.go over the verify step above.
+ * ---------------------------------------------------------------------- */
+
+/* engine/speculative.go:13-19 */
+typedef struct yuuka_spec_options {
+    int32_t max_draft; /* <= 0: 4; capped at 16 */
+    int32_t min_match; /* <= 0: 2; capped at 8 */
+} yuuka_spec_options;
+/* SpeculativeOptions.normalize, engine/speculative.go:21-34 */
+YUUKA_API void yuuka_spec_options_normalize(yuuka_spec_options * options);
+/* lookupDraft, engine/speculative.go:39-66. out must hold max_draft ids; returns
+ * the number of draft tokens (0: none). */
+YUUKA_API int32_t yuuka_spec_lookup_draft(const int32_t * history, int32_t n, int32_t max_draft, int32_t min_match,
+                                          int32_t * out);
+
+#define YUUKA_FINISH_LENGTH 0 /* "length" */
+#define YUUKA_FINISH_STOP 1   /* "stop" */
+typedef struct yuuka_spec_request {
+    int32_t max_tokens;          /* GenerateOptions.MaxTokens; clipped to the free context */
+    yuuka_spec_options options;
+    const int32_t * stop_tokens; /* StopTokens plus the EOS id if it applies; may be NULL with n_stop 0 */
+    int32_t n_stop;
+} yuuka_spec_request;
+/* The counters of engine.GenerateResult that the loop maintains (engine/speculative.go:186-203). */
+typedef struct yuuka_spec_result {
+    int32_t prompt_tokens, output_tokens, finish_reason;
+    int32_t steps;          /* verify steps run */
+    int32_t draft_tokens;   /* DraftTokens */
+    int32_t accepted_draft; /* AcceptedDraft */
+} yuuka_spec_result;
+/* generateSpeculative, engine/speculative.go:68-251, for sequence 0 of the
+ * session: resets it, runs the prompt, then verify steps of [pending token,
+ * prompt-lookup drafts] until max_tokens, a stop token (not emitted) or the
+ * context capacity. tokens must hold max_tokens ids. The emitted stream equals
+ * plain greedy decoding. The session needs max_nodes >= 2 to draft at all
+ * (drafts per step are capped at max_nodes - 1). Synchronous. */
+YUUKA_API yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
+                                           const yuuka_spec_request * request, int32_t * tokens,
+                                           yuuka_spec_result * result);
+
 #ifdef __cplusplus
 }
 #endif

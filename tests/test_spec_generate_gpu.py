@@ -1,0 +1,121 @@
+"""yuuka_spec_generate (host loop of engine/speculative.go over the k+1-row verify
+step) on the tiny model: the emitted stream must equal plain greedy decoding by
+the CPU oracle, which is the property the reference's own
+TestSpeculative*MatchesGreedy tests assert (engine/speculative_test.go:103-137)."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as yo
+from yuuka_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    cfg = synth.tiny_config()
+    tensors = synth.make_model(cfg, "q8_0", seed=7, unit_norms=False)
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, tensors)
+    om = yo.Model(cfg, tensors)
+    yield cfg, gm, om
+    gm.close()
+    dev.close()
+
+
+def oracle_greedy(om, prompt, n, capacity=256):
+    st = yo.State(om, capacity, yo.KV_F32)
+    logits = st.forward(prompt)
+    out, gaps = [], []
+    for _ in range(n):
+        top2 = np.partition(logits, -2)[-2:]
+        gaps.append(float(top2[1] - top2[0]))
+        t = yo.argmax(logits)
+        out.append(t)
+        if len(out) < n:
+            logits = st.step(t)
+    st.close()
+    return out, gaps
+
+
+def agree(got, want, gaps):
+    """Identical tokens, except that a near-tie (top-2 gap < 1e-3) may legitimately fork the stream."""
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert gaps[i] < 1e-3, f"token {i}: got {g}, want {w}, top-2 gap {gaps[i]}"
+            return i
+    return len(want)
+
+
+def damped_model(cfg, dev, scale):
+    """The tiny model with its mixer output projections scaled down: at 0 the next token depends on
+    the current token only, so greedy decoding falls into a cycle that prompt lookup predicts; at
+    0.1 the cycle is broken often enough that most drafts are wrong."""
+    tensors = synth.make_model(cfg, "q8_0", seed=7, unit_norms=False)
+    for name, (d, arr, r, c) in list(tensors.items()):
+        if name.endswith("ssm_out.weight") or name.endswith("attn_output.weight"):
+            tensors[name] = (d, synth.normal_quant(r, c, d, 0.02 * scale, 999 + r), r, c)
+    return cuda.Model(dev, cfg, tensors), yo.Model(cfg, tensors)
+
+
+@pytest.mark.parametrize("scale,min_match", [(0.0, 2), (0.1, 1)])
+def test_generate_matches_greedy_decoding(tiny, scale, min_match):
+    cfg, gm0, om0 = tiny
+    gm, om = damped_model(cfg, gm0.dev, scale)
+    V = cfg["vocab"]
+    prompt = synth.uniform_i32(12, 0, V, 70).tolist()
+    n = 300
+    want, gaps = oracle_greedy(om, prompt, n, capacity=512)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=9, capacity=512, kv_format=cuda.KV_F32)
+    got, res = cuda.spec_generate(sess, prompt, n, max_draft=8, min_match=min_match)
+    same = agree(got, want, gaps)
+    assert same >= 150, f"stream forked at a near-tie after {same} tokens; pick another seed"
+    assert len(got) == n and res.output_tokens == n and res.prompt_tokens == len(prompt)
+    assert res.finish_reason == cuda.FINISH_LENGTH
+    assert res.draft_tokens > 50 and 0 <= res.accepted_draft <= res.draft_tokens
+    if scale == 0.0:
+        assert res.accepted_draft > res.draft_tokens // 2 and res.steps < n // 2   # the cycle is predicted
+    else:
+        assert res.accepted_draft < res.draft_tokens // 2                          # mostly corrections
+    assert res.steps + res.accepted_draft == n - 1  # every step emits its accepted drafts plus one token
+    assert sess.position() == len(prompt) + n - 1   # the last emitted token is pending, not run
+    # the same request again (the call resets the sequence) gives the same stream
+    again, res2 = cuda.spec_generate(sess, prompt, n, max_draft=8, min_match=min_match)
+    assert again == got and (res2.steps, res2.draft_tokens, res2.accepted_draft) == (res.steps, res.draft_tokens, res.accepted_draft)
+    sess.close()
+    gm.close()
+
+
+def test_generate_stops_on_stop_token_and_on_capacity(tiny):
+    cfg, gm, om = tiny
+    V = cfg["vocab"]
+    base = synth.uniform_i32(10, 0, V, 71).tolist()
+    prompt = base + base
+    want, gaps = oracle_greedy(om, prompt, 24)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=64, kv_format=cuda.KV_F16)
+    stop = want[9]
+    first = want.index(stop)
+    got, res = cuda.spec_generate(sess, prompt, 24, max_draft=4, stop_tokens=[stop, V - 1])
+    assert res.finish_reason == cuda.FINISH_STOP and got == want[:first]
+    # max_tokens is clipped to the free context: capacity 64 - 20 prompt tokens = 44
+    got, res = cuda.spec_generate(sess, prompt, 1000, max_draft=16)
+    assert res.finish_reason == cuda.FINISH_LENGTH and len(got) == 44
+    assert sess.position() <= 64
+    want44, gaps44 = oracle_greedy(om, prompt, 44, capacity=64)
+    assert agree(got, want44, gaps44) >= 24
+    # a session of one row per step cannot draft and still decodes
+    one = cuda.Session(gm, max_batch=1, max_nodes=1, capacity=64, kv_format=cuda.KV_F32)
+    got1, res1 = cuda.spec_generate(one, prompt, 12)
+    assert agree(got1, want[:12], gaps[:12]) == 12 and res1.draft_tokens == 0 and res1.steps == 11
+    one.close()
+    sess.close()
+
+
+def test_generate_argument_errors(tiny):
+    cfg, gm, om = tiny
+    sess = cuda.Session(gm, max_batch=1, max_nodes=4, capacity=32, kv_format=cuda.KV_F32)
+    for prompt, n in (([], 4), ([1, 2, 3], 0), (list(range(33)), 4), (list(range(32)), 4)):
+        with pytest.raises(cuda.YuukaError) as e:
+            cuda.spec_generate(sess, prompt, n)
+        assert e.value.status == 1
+    sess.close()

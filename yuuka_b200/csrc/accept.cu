@@ -109,6 +109,190 @@ int launch_accept_greedy(cudaStream_t s, const float * logits, int vocab, const 
     return 2;
 }
 
+// ---------------------------------------------------------------------------
+// Rejection-sampling acceptance over a draft tree (not in the reference, which
+// verifies greedily only: engine/speculative.go:73-75). The rule is written so
+// that every deciding quantity is an elementwise IEEE operation or an integer
+// sum; the result does not depend on the order of the parallel reductions.
+//
+// At node cur (start: the root), with children in row order:
+//   mx  = max_i L[cur][i];  e_i = exp_det((L[cur][i] - mx) / T);  w_i = (uint64)(e_i * 2^40)
+//   r = w, R = sum w
+//   child c (token x, draft distribution Q[c], uniform u = U[2c]):
+//     accept iff (double)(u * Q[c][x]) * (double)R <= (double)r_x      -> cur = c, start over at c
+//     else r_i = max(0, r_i - (uint64)((double)Q[c][i] * (double)R)), R = sum r  (R == 0: r = w again)
+//   no child accepted: t = min((uint64)((double)U[2 cur + 1] * (double)R), R - 1);
+//     emit the smallest j with sum_{i <= j} r_i > t.
+
+__device__ __forceinline__ float exp_det(float x) {
+    if (x < -87.0f) return 0.0f;
+    if (x > 88.0f) x = 88.0f;
+    const float n = rintf(x * 1.44269504f);
+    float r = fmaf(n, -0.693359375f, x);
+    r = fmaf(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    const float r2 = __fmul_rn(r, r);
+    const float e = __fadd_rn(fmaf(p, r2, r), 1.0f);
+    const float scale = __uint_as_float((uint32_t)((int)n + 127) << 23);
+    return __fmul_rn(e, scale);
+}
+
+__device__ __forceinline__ unsigned long long target_weight(float logit, float mx, float inv_t) {
+    const float e = exp_det(__fmul_rn(__fsub_rn(logit, mx), inv_t));
+    return (unsigned long long)__fmul_rn(e, 1099511627776.0f);
+}
+
+constexpr int REJ_THREADS = 1024;
+
+struct RejectParams {
+    const float * logits;   // [batch][nodes][vocab]
+    const float * q;        // [batch][nodes][vocab]
+    const float * u;        // [batch][nodes][2]
+    unsigned long long * r; // [batch][vocab]
+    int vocab;
+    float inv_t;
+    RowMeta rows;
+    AcceptOut out;
+};
+
+__device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long * red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();  // red may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    unsigned long long t = 0;
+    for (int w = 0; w < REJ_THREADS / 32; w++) t += red[w];
+    return t;
+}
+
+__global__ void __launch_bounds__(REJ_THREADS) rejection_walk_kernel(const RejectParams p) {
+    pdl_entry();
+    __shared__ unsigned long long red[REJ_THREADS / 32];
+    __shared__ float redf[REJ_THREADS / 32];
+    __shared__ int flag;
+    __shared__ int found;
+    const int seq = blockIdx.x, N = p.rows.nodes, V = p.vocab, tid = threadIdx.x;
+    const int32_t * tokens = p.rows.tokens + (int64_t)seq * N;
+    const int32_t * parent = p.rows.parent + (int64_t)seq * N;
+    const float * U = p.u + (int64_t)seq * N * 2;
+    unsigned long long * r = p.r + (int64_t)seq * V;
+    int32_t * path = p.out.path + (int64_t)seq * N;
+    int32_t * emitted = p.out.emitted + (int64_t)seq * N;
+    int cur = 0, a = 0;
+    for (;;) {
+        const float * L = p.logits + ((int64_t)seq * N + cur) * V;
+        // max of the row (order-independent)
+        float mx = -INFINITY;
+        for (int i = tid; i < V; i += REJ_THREADS) mx = fmaxf(mx, L[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        __syncthreads();
+        if ((tid & 31) == 0) redf[tid >> 5] = mx;
+        __syncthreads();
+        for (int w = 0; w < REJ_THREADS / 32; w++) mx = fmaxf(mx, redf[w]);
+        // target weights
+        unsigned long long z = 0;
+        for (int i = tid; i < V; i += REJ_THREADS) {
+            const unsigned long long w = target_weight(L[i], mx, p.inv_t);
+            r[i] = w;
+            z += w;
+        }
+        const unsigned long long Z = block_sum_u64(z, red);
+        unsigned long long R = Z;
+        int next = -1;
+        for (int c = cur + 1; c < N && next < 0; c++) {
+            if (parent[c] != cur) continue;
+            const float * q = p.q + ((int64_t)seq * N + c) * V;
+            __syncthreads();  // r of the previous pass is complete
+            if (tid == 0) {
+                const int32_t x = tokens[c];
+                const float lhs = __fmul_rn(U[2 * c], q[x]);
+                flag = __dmul_rn((double)lhs, (double)R) <= (double)r[x];
+            }
+            __syncthreads();
+            if (flag) {
+                next = c;
+                break;
+            }
+            unsigned long long sum = 0;
+            for (int i = tid; i < V; i += REJ_THREADS) {
+                const unsigned long long qr = (unsigned long long)__dmul_rn((double)q[i], (double)R);
+                const unsigned long long ri = r[i];
+                const unsigned long long nr = ri > qr ? ri - qr : 0ull;
+                r[i] = nr;
+                sum += nr;
+            }
+            R = block_sum_u64(sum, red);
+            if (R == 0) {
+                for (int i = tid; i < V; i += REJ_THREADS) r[i] = target_weight(L[i], mx, p.inv_t);
+                R = Z;
+            }
+        }
+        if (next >= 0) {
+            if (tid == 0) {
+                emitted[a] = tokens[next];
+                path[a] = next;
+            }
+            a++;
+            cur = next;
+            continue;
+        }
+        // residual draw: thread tid owns the contiguous range [lo, hi)
+        __syncthreads();
+        unsigned long long t = (unsigned long long)__dmul_rn((double)U[2 * cur + 1], (double)R);
+        if (t >= R) t = R - 1;
+        const int per = (V + REJ_THREADS - 1) / REJ_THREADS;
+        const int lo = min(V, tid * per), hi = min(V, lo + per);
+        unsigned long long mine = 0;
+        for (int i = lo; i < hi; i++) mine += r[i];
+        // exclusive prefix of the per-thread sums: inside the warp, then across warps
+        unsigned long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long v = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((tid & 31) >= o) incl += v;
+        }
+        if (tid == 0) found = V - 1;
+        __syncthreads();
+        if ((tid & 31) == 31) red[tid >> 5] = incl;
+        __syncthreads();
+        unsigned long long before = incl - mine;
+        for (int w = 0; w < (tid >> 5); w++) before += red[w];
+        if (before <= t && t < before + mine) {
+            unsigned long long acc = before;
+            for (int i = lo; i < hi; i++) {
+                acc += r[i];
+                if (acc > t) {
+                    found = i;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) emitted[a] = found;
+        break;
+    }
+    for (int i = a + tid; i < N; i += REJ_THREADS) path[i] = -1;
+    for (int i = a + 1 + tid; i < N; i += REJ_THREADS) emitted[i] = -1;
+    if (tid == 0) p.out.accepted[seq] = a;
+}
+
+int launch_accept_rejection(cudaStream_t s, const float * logits, const float * draft_probs, const float * uniforms,
+                            unsigned long long * residual, int vocab, float temperature, const RowMeta & rows,
+                            const AcceptOut & out) {
+    YK_REQUIRE(temperature > 0.0f, YUUKA_ERR_INVALID_ARGUMENT, "rejection sampling needs a temperature above zero");
+    RejectParams p{logits, draft_probs, uniforms, residual, vocab, 1.0f / temperature, rows, out};
+    launch_k(rejection_walk_kernel, rows.batch, REJ_THREADS, 0, s, p);
+    YK_CUDA(cudaGetLastError());
+    return 1;
+}
+
 __global__ void accept_all_kernel(RowMeta rows, AcceptOut out) {
     pdl_entry();
     const int seq = blockIdx.x, N = rows.nodes;

@@ -435,6 +435,10 @@ struct yuuka_session {
     // staged step
     int st_seq0 = 0, st_batch = 0, st_nodes = 0;
     uint32_t st_mode = 0;
+    float st_temperature = 0.0f;
+    const float * st_draft_probs = nullptr;   // device, rejection mode
+    float * d_uniforms = nullptr;             // [max_batch * max_nodes * 2]
+    unsigned long long * reject_residual = nullptr;  // [max_batch][vocab], allocated by the first rejection step
     bool staged = false, launched = false;
     uint32_t launches = 0;
     // captured steps, keyed by (seq0, batch, nodes, mode)
@@ -630,7 +634,8 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             const int G = c.heads / c.kv_heads;
             const int qtiles = (G * nodes + 39) / 40;
             const int base = c.kv_heads * qtiles * batch;
-            int splits = (2 * m->dev->sm_count + base - 1) / base;
+            // one 32-key tile per CTA while the sequences are short enough: about four CTAs per SM at capacity
+            int splits = (4 * m->dev->sm_count + base - 1) / base;
             int max_splits = (max_total + 31) / 32;
             if (splits > max_splits) splits = max_splits;
             if (splits < 1) splits = 1;
@@ -671,6 +676,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     mark(s, YUUKA_OP_ACCEPT);
     if (mode == YUUKA_ACCEPT_GREEDY) {
         s->launches += launch_accept_greedy(st, s->logits, c.vocab, rows, s->argmax, s->acc);
+    } else if (mode == YUUKA_ACCEPT_REJECTION) {
+        s->launches += launch_accept_rejection(st, s->logits, s->st_draft_probs, s->d_uniforms, s->reject_residual, c.vocab,
+                                               s->st_temperature, rows, s->acc);
     } else {
         launch_accept_all(st, rows, s->acc);  // forced commit of a chain
         s->launches++;
@@ -791,8 +799,16 @@ void validate_batch(const yuuka_session * s, const yuuka_verify_batch * b) {
     YK_REQUIRE(b->tokens, YUUKA_ERR_INVALID_ARGUMENT, "verify: tokens is null");
     YK_REQUIRE(b->mode == YUUKA_ACCEPT_GREEDY || b->mode == YUUKA_ACCEPT_NONE || b->mode == YUUKA_ACCEPT_REJECTION,
                YUUKA_ERR_INVALID_ARGUMENT, "verify: unknown acceptance mode %u", b->mode);
-    YK_REQUIRE(b->mode != YUUKA_ACCEPT_REJECTION, YUUKA_ERR_UNSUPPORTED,
-               "verify: rejection-sampling acceptance is not available in this build");
+    if (b->mode == YUUKA_ACCEPT_REJECTION) {
+        const uint64_t need = (uint64_t)b->batch * b->nodes * s->model->cfg.vocab * sizeof(float);
+        YK_REQUIRE(b->temperature > 0.0f && b->temperature == b->temperature, YUUKA_ERR_INVALID_ARGUMENT,
+                   "verify: rejection sampling needs a temperature above zero");
+        YK_REQUIRE(b->uniforms, YUUKA_ERR_INVALID_ARGUMENT, "verify: rejection sampling needs the uniform draws");
+        YK_REQUIRE(b->draft_probs && b->draft_probs->ptr && b->draft_probs->bytes >= need, YUUKA_ERR_INVALID_ARGUMENT,
+                   "verify: draft_probs must be a device buffer of at least %llu bytes", (unsigned long long)need);
+        YK_REQUIRE(b->draft_probs->dev == s->model->dev, YUUKA_ERR_INVALID_ARGUMENT,
+                   "verify: draft_probs lives on another device");
+    }
     YK_REQUIRE(s->logits, YUUKA_ERR_INVALID_ARGUMENT, "verify: the session has no logits buffer");
 }
 
@@ -904,9 +920,10 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->argmax.val = dalloc<float>((size_t)R * s->argmax.chunks, s->owned);
             s->argmax.idx = dalloc<int32_t>((size_t)R * s->argmax.chunks, s->owned);
             s->acc.accepted = dalloc<int32_t>(B, s->owned);
+            s->d_uniforms = dalloc<float>((size_t)R * 2, s->owned);
             s->acc.path = dalloc<int32_t>(R, s->owned);
             s->acc.emitted = dalloc<int32_t>(R, s->owned);
-            s->attn_partial_floats = (size_t)N * c.heads * (2 * model->dev->sm_count / c.kv_heads + 1 + B) * (c.head_dim + 2);
+            s->attn_partial_floats = (size_t)N * c.heads * (4 * model->dev->sm_count / c.kv_heads + 1 + B) * (c.head_dim + 2);
             s->attn_partial = dalloc<float>(s->attn_partial_floats, s->owned, false);
             // split-K scratch for every matrix shape of the step
             for (int rows : {R < 32 ? R : 32, 1}) {
@@ -981,6 +998,19 @@ yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t 
     });
 }
 
+yuuka_status yuuka_session_info_get(const yuuka_session * s, yuuka_session_info * out) {
+    return guard([&] {
+        YK_REQUIRE(s && out, YUUKA_ERR_INVALID_ARGUMENT, "session_info_get: null argument");
+        out->max_batch = s->cfg.max_batch;
+        out->max_nodes = s->cfg.max_nodes;
+        out->capacity = s->cfg.capacity;
+        out->block_size = s->cfg.block_size;
+        out->pool_blocks = s->cfg.pool_blocks;
+        out->kv_format = s->cfg.kv_format;
+        out->vocab = s->model->cfg.vocab;
+    });
+}
+
 yuuka_status yuuka_session_position(yuuka_session * s, int32_t seq, int32_t * position) {
     return guard([&] {
         check_seq(s, seq);
@@ -1047,6 +1077,18 @@ yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b)
         YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_stage: the previous step has not been fetched");
         set_device(s->model->dev);
         stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent);
+        if (b->mode == YUUKA_ACCEPT_REJECTION) {
+            const int V = s->model->cfg.vocab;
+            if (!s->reject_residual) s->reject_residual = dalloc<unsigned long long>((size_t)s->cfg.max_batch * V, s->owned, false);
+            for (int i = 0; i < b->batch * b->nodes * 2; i++)
+                YK_REQUIRE(b->uniforms[i] >= 0.0f && b->uniforms[i] < 1.0f, YUUKA_ERR_INVALID_ARGUMENT,
+                           "verify: uniform draw %d is outside [0, 1)", i);
+            YK_CUDA(cudaMemcpyAsync(s->d_uniforms, b->uniforms, sizeof(float) * (size_t)b->batch * b->nodes * 2,
+                                    cudaMemcpyHostToDevice, s->stream.s));
+            YK_CUDA(cudaStreamSynchronize(s->stream.s));  // the host array may go away after this call
+            s->st_draft_probs = (const float *)b->draft_probs->ptr;
+            s->st_temperature = b->temperature;
+        }
         s->st_seq0 = 0;
         s->st_batch = b->batch;
         s->st_nodes = b->nodes;
@@ -1060,7 +1102,8 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
         YK_REQUIRE(s && s->staged, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: no staged step");
         set_device(s->model->dev);
         const int max_total = max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes);
-        if (!s->use_graphs) {
+        if (!s->use_graphs || s->st_mode == YUUKA_ACCEPT_REJECTION) {
+            // (a rejection step carries a temperature and a buffer address that a replayed graph would freeze)
             s->launches = 0;
             run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total);
         } else {

@@ -98,6 +98,11 @@ struct ArgmaxScratch {
 };
 int launch_accept_greedy(cudaStream_t s, const float * logits, int vocab, const RowMeta & rows,
                          const ArgmaxScratch & scratch, const AcceptOut & out);
+// Rejection-sampling walk (rule in accept.cu). residual is scratch of batch * vocab 64-bit words;
+// draft_probs [batch][nodes][vocab] and uniforms [batch][nodes][2] are device arrays.
+int launch_accept_rejection(cudaStream_t s, const float * logits, const float * draft_probs, const float * uniforms,
+                            unsigned long long * residual, int vocab, float temperature, const RowMeta & rows,
+                            const AcceptOut & out);
 // Accept every row of a chain (prefill / forced commit): accepted = nodes-1.
 void launch_accept_all(cudaStream_t s, const RowMeta & rows, const AcceptOut & out);
 int argmax_chunks(int vocab);

@@ -61,6 +61,24 @@ class SessionConfig(C.Structure):
                 ("want_logits", C.c_int32)]
 
 
+class SessionInfo(C.Structure):
+    _fields_ = [("max_batch", C.c_int32), ("max_nodes", C.c_int32), ("capacity", C.c_int32), ("block_size", C.c_int32),
+                ("pool_blocks", C.c_int32), ("kv_format", C.c_int32), ("vocab", C.c_int32)]
+
+
+class SpecOptions(C.Structure):
+    _fields_ = [("max_draft", C.c_int32), ("min_match", C.c_int32)]
+
+
+class SpecRequest(C.Structure):
+    _fields_ = [("max_tokens", C.c_int32), ("options", SpecOptions), ("stop_tokens", C.c_void_p), ("n_stop", C.c_int32)]
+
+
+class SpecResult(C.Structure):
+    _fields_ = [("prompt_tokens", C.c_int32), ("output_tokens", C.c_int32), ("finish_reason", C.c_int32),
+                ("steps", C.c_int32), ("draft_tokens", C.c_int32), ("accepted_draft", C.c_int32)]
+
+
 class VerifyBatch(C.Structure):
     _fields_ = [("batch", C.c_int32), ("nodes", C.c_int32), ("tokens", C.c_void_p),
                 ("parent", C.c_void_p), ("mode", C.c_uint32), ("temperature", C.c_float),
@@ -98,6 +116,10 @@ SIGNATURES = {
                                 _u32, _u32, _vp]),
     "yuuka_gemm_quant_static": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
                                 _u32, _u32, _vp]),
+    "yuuka_session_info_get": (_i32, [_vp, _vp]),
+    "yuuka_spec_options_normalize": (None, [_vp]),
+    "yuuka_spec_lookup_draft": (_i32, [_vp, _i32, _i32, _i32, _vp]),
+    "yuuka_spec_generate": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp]),
     "yuuka_weights_tiled_bytes": (_u64, [_u32, _u64, _u64]),
     "yuuka_weights_tile": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _u64, _u64, _vp]),
     "yuuka_model_create": (_i32, [_vp, _vp, _vp]),
@@ -278,6 +300,35 @@ def gemm_quant(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_o
                                  n_in, n_out, rows, path, flags, completion.h if completion else None))
 
 
+FINISH_LENGTH, FINISH_STOP = 0, 1
+
+
+def spec_options_normalize(max_draft: int, min_match: int) -> tuple[int, int]:
+    """SpeculativeOptions.normalize (engine/speculative.go:21-34)."""
+    o = SpecOptions(max_draft, min_match)
+    lib().yuuka_spec_options_normalize(C.byref(o))
+    return o.max_draft, o.min_match
+
+
+def spec_lookup_draft(history, max_draft: int, min_match: int) -> list[int]:
+    """lookupDraft (engine/speculative.go:39-66)."""
+    h = np.ascontiguousarray(history, np.int32)
+    out = np.zeros(max(max_draft, 1), np.int32)
+    n = lib().yuuka_spec_lookup_draft(h.ctypes.data, h.size, max_draft, min_match, out.ctypes.data)
+    return out[:n].tolist()
+
+
+def spec_generate(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, min_match: int = 0, stop_tokens=()):
+    """generateSpeculative (engine/speculative.go:68-251) on sequence 0 of sess; returns (tokens, SpecResult)."""
+    p = np.ascontiguousarray(prompt, np.int32)
+    stops = np.ascontiguousarray(list(stop_tokens), np.int32)
+    req = SpecRequest(max_tokens, SpecOptions(max_draft, min_match), stops.ctypes.data if stops.size else None, stops.size)
+    out = np.zeros(max(max_tokens, 1), np.int32)
+    res = SpecResult()
+    check(lib().yuuka_spec_generate(sess.h, 0, p.ctypes.data, p.size, C.byref(req), out.ctypes.data, C.byref(res)))
+    return out[:res.output_tokens].tolist(), res
+
+
 STATIC_SCRATCH_BYTES = 8 << 20
 
 
@@ -381,7 +432,7 @@ class Session:
                                           out.ctypes.data_as(C.c_void_p) if want_logits else None))
         return out
 
-    def _batch(self, tokens, parent, mode, want_logits, temperature=1.0):
+    def _batch(self, tokens, parent, mode, want_logits, temperature=1.0, draft_probs=None, uniforms=None):
         tokens = np.ascontiguousarray(tokens, np.int32)
         if tokens.ndim == 1:
             tokens = tokens[None, :]
@@ -397,6 +448,12 @@ class Session:
         vb.tokens = tokens.ctypes.data
         vb.parent = par.ctypes.data if par is not None else None
         vb.mode, vb.temperature = mode, temperature
+        if draft_probs is not None:
+            vb.draft_probs = draft_probs.h  # Buffer: f32 [batch, nodes, vocab] on the device
+        if uniforms is not None:
+            keep["uniforms"] = np.ascontiguousarray(uniforms, np.float32)
+            assert keep["uniforms"].size == B * N * 2
+            vb.uniforms = keep["uniforms"].ctypes.data
         vb.accepted = keep["accepted"].ctypes.data
         vb.emitted = keep["emitted"].ctypes.data
         vb.path = keep["path"].ctypes.data
@@ -407,9 +464,14 @@ class Session:
     def _result(keep) -> VerifyResult:
         return VerifyResult(keep["accepted"], keep["emitted"], keep["path"], keep["logits"])
 
-    def verify(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False) -> VerifyResult:
-        """One verify step; tokens [batch, nodes] with the pending token in column 0."""
-        vb, keep = self._batch(tokens, parent, mode, want_logits)
+    def verify(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False,
+               temperature: float = 1.0, draft_probs: "Buffer | None" = None, uniforms=None) -> VerifyResult:
+        """One verify step; tokens [batch, nodes] with the pending token in column 0.
+
+        mode ACCEPT_REJECTION needs temperature, draft_probs (device Buffer, f32 [batch, nodes, vocab])
+        and uniforms (f32 [batch, nodes, 2] in [0, 1)).
+        """
+        vb, keep = self._batch(tokens, parent, mode, want_logits, temperature, draft_probs, uniforms)
         check(lib().yuuka_verify_step(self.h, C.byref(vb)))
         return self._result(keep)
 
