@@ -268,16 +268,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     ctx_mid = PROMPT_LEN + (idx // 2)
 
     # max over ranks of the timed region, sum of tokens
-    if dist is not None:
-        import torch
-        t = torch.tensor([dev_ms, t_e2e], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        n = torch.tensor([float(emitted_total)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(n, op=dist.ReduceOp.SUM)
-        dev_ms, t_e2e = float(t[0]), float(t[1])
-        emitted_all = float(n[0])
-    else:
-        emitted_all = float(emitted_total)
+    from yuuka_b200 import replicas
+    tot = replicas.reduce_totals(dist, "cuda", dev_ms, t_e2e, float(emitted_total), float(accepted_total))
+    dev_ms, t_e2e, emitted_all = tot.device_ms, tot.wall_s, tot.emitted
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
