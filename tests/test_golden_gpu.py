@@ -1,0 +1,62 @@
+"""The CUDA path against the committed C0 vectors (tests/golden/c0_tiny.npz), without the oracle in
+the loop: integers exact, sampled logits within the all-logits bound of the reference's own GPU
+fixture test (5e-3, engine/gpu/spec_fixture_test.go:70; 2e-2 with a Q8_0 KV pool)."""
+import os
+
+import numpy as np
+import pytest
+
+from yuuka_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "c0_tiny.npz"))
+
+
+@pytest.fixture(scope="module")
+def model():
+    cfg = synth.tiny_config()
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, synth.make_model(cfg, "q8_0", seed=7, unit_norms=False))
+    yield gm
+    gm.close()
+    dev.close()
+
+
+@pytest.mark.parametrize("name,kv,tol", [("f32", cuda.KV_F32, 5e-3), ("f16", cuda.KV_F16, 5e-3), ("q8_0", cuda.KV_Q8_0, 2e-2)])
+def test_prefill_rows(model, name, kv, tol):
+    cols = GOLD["sample_cols"]
+    sess = cuda.Session(model, max_batch=1, max_nodes=16, capacity=128, kv_format=kv)
+    rows = sess.prefill_logits(GOLD["prompt"])
+    assert float(np.max(np.abs(rows[:, cols] - GOLD[f"prefill_logits_{name}"]))) <= tol
+    got = rows.argmax(axis=1)
+    want = GOLD[f"prefill_argmax_{name}"]
+    for r in np.nonzero(got != want)[0]:  # only a near-tie may differ
+        top = np.sort(rows[r])[-2:]
+        assert top[1] - top[0] < 1e-3, r
+    sess.close()
+
+
+def test_chain_and_tree_steps(model):
+    cols = GOLD["sample_cols"]
+    greedy = GOLD["greedy"]
+    sess = cuda.Session(model, max_batch=1, max_nodes=17, capacity=128, kv_format=cuda.KV_F32)
+    sess.forward(GOLD["prompt"], want_logits=False)
+    res = sess.verify([np.concatenate(([greedy[0]], GOLD["chain_draft"]))], want_logits=True)
+    a = int(GOLD["chain_accepted"][0])
+    assert int(res.accepted[0]) == a
+    assert res.emitted[0, :a + 1].tolist() == GOLD["chain_emitted"].tolist()
+    assert float(np.max(np.abs(res.logits[0][:, cols] - GOLD["chain_logits"]))) <= 5e-3
+    assert sess.position() == int(GOLD["chain_position"][0])
+    state_sum = np.abs(sess.snapshot().view(np.float32)).astype(np.float64).sum()
+    assert abs(state_sum - float(GOLD["chain_state_sum"][0])) <= 1e-4 * float(GOLD["chain_state_sum"][0])
+    sess.close()
+
+    sess = cuda.Session(model, max_batch=1, max_nodes=17, capacity=128, kv_format=cuda.KV_F16)
+    sess.forward(GOLD["prompt"], want_logits=False)
+    res = sess.verify([GOLD["tree_tokens"]], parent=GOLD["tree_parent"], want_logits=True)
+    a = int(GOLD["tree_accepted"][0])
+    assert int(res.accepted[0]) == a and res.path[0, :a].tolist() == GOLD["tree_path"].tolist()
+    assert res.emitted[0, :a + 1].tolist() == GOLD["tree_emitted"].tolist()
+    assert float(np.max(np.abs(res.logits[0][:, cols] - GOLD["tree_logits"]))) <= 5e-3
+    sess.close()
+    assert cuda.spec_lookup_draft(GOLD["lookup_history"], 4, 2) == GOLD["lookup_draft"].tolist()
