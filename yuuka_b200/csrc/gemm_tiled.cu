@@ -311,13 +311,39 @@ __device__ __forceinline__ void sum_mma(uint32_t a0, uint32_t a1, uint32_t a2, u
     }
 }
 
+// Bit masks and the fp16 "1024" pattern as run-time values (kernel parameters). A LOP3 takes one
+// immediate only; with two compile-time constants in (v & mask) | 0x6400'6400 the compiler emits two
+// instructions per weight pair, with values it cannot see through it emits one.
+struct DecodeConsts {
+    uint32_t m0f;    // 0x000f000f
+    uint32_t mf0;    // 0x00f000f0
+    uint32_t magic;  // 0x64006400
+    uint32_t h4;     // 0x00300030 (Q6_K high bits, low-nibble form); Q5_K: 0x00100010
+    uint32_t h8;     // 0x03000300 (Q6_K high bits, high-nibble form); Q5_K: 0x01000100
+};
+inline DecodeConsts decode_consts(uint32_t dtype) {
+    DecodeConsts c{0x000f000fu, 0x00f000f0u, 0x64006400u, 0x00300030u, 0x03000300u};
+    if (dtype == YUUKA_DTYPE_Q5_K) {
+        c.h4 = 0x00100010u;
+        c.h8 = 0x01000100u;
+    }
+    return c;
+}
+
+#ifndef YK_GEMM_PINGPONG
+#define YK_GEMM_PINGPONG 0
+#endif
+#ifndef YK_GEMM_RUNTIME_CONSTS
+#define YK_GEMM_RUNTIME_CONSTS 1
+#endif
+
 template <int DT, int NT> struct Mma;
 
 template <int NT> struct Mma<YUUKA_DTYPE_Q4_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q4_K>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4<C>(r.hdr, lane, tab); }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
+                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
         const int g = lane >> 2, t = lane & 3;
         const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
 #pragma unroll
@@ -330,16 +356,16 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q4_K, NT> {
                 const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
 #pragma unroll
                 for (int n = 0; n < 2; n++) {
-                    const uint32_t mask = n ? 0x00f000f0u : 0x000f000fu;
+                    const uint32_t mask = n ? kc.mf0 : kc.m0f;
                     const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
                     uint32_t a[2][4];
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
-                        a[h][0] = h2_fma((vg & mask) | H2_1024, s_g, c_g);
-                        a[h][1] = h2_fma((vh & mask) | H2_1024, s_h, c_h);
-                        a[h][2] = h2_fma(((vg >> 8) & mask) | H2_1024, s_g, c_g);
-                        a[h][3] = h2_fma(((vh >> 8) & mask) | H2_1024, s_h, c_h);
+                        a[h][0] = h2_fma((vg & mask) | kc.magic, s_g, c_g);
+                        a[h][1] = h2_fma((vh & mask) | kc.magic, s_h, c_h);
+                        a[h][2] = h2_fma(((vg >> 8) & mask) | kc.magic, s_g, c_g);
+                        a[h][3] = h2_fma(((vh >> 8) & mask) | kc.magic, s_h, c_h);
                     }
                     const int k = 2 * j + n;
 #pragma unroll
@@ -366,25 +392,25 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q5_K>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4<C>(r.hdr, lane, tab); }
     // bit k of every byte of hb -> bit `tgt` of bytes 0 and 2 (shift_bytes13: of bytes 1 and 3 moved down)
-    template <int K, int TGT, bool B13> __device__ static uint32_t hibit(uint32_t hb) {
+    // ... merged with the fp16 1024 pattern: ((hb shifted) & bit) | magic is one LOP3
+    template <int K, int TGT, bool B13> __device__ static uint32_t hibit(uint32_t hb, uint32_t bit, uint32_t magic) {
         constexpr int from = K + (B13 ? 8 : 0);
-        constexpr uint32_t mask = (1u << TGT) | (1u << (TGT + 16));
-        if constexpr (from >= TGT) return (hb >> (from - TGT)) & mask;
-        else return (hb << (TGT - from)) & mask;
+        if constexpr (from >= TGT) return ((hb >> (from - TGT)) & bit) | magic;
+        else return ((hb << (TGT - from)) & bit) | magic;
     }
     template <int K> __device__ static void sub(uint32_t vg, uint32_t vh, uint32_t hg, uint32_t hh, uint32_t s_g, uint32_t c_g,
-                                                uint32_t s_h, uint32_t c_h, uint32_t (&a)[4]) {
+                                                uint32_t s_h, uint32_t c_h, uint32_t (&a)[4], const DecodeConsts & kc) {
         constexpr bool hi = (K & 1) != 0;
-        constexpr uint32_t mask = hi ? 0x00f000f0u : 0x000f000fu;
         constexpr int tgt = hi ? 8 : 4;
-        a[0] = h2_fma((vg & mask) | hibit<K, tgt, false>(hg) | H2_1024, s_g, c_g);
-        a[1] = h2_fma((vh & mask) | hibit<K, tgt, false>(hh) | H2_1024, s_h, c_h);
-        a[2] = h2_fma(((vg >> 8) & mask) | hibit<K, tgt, true>(hg) | H2_1024, s_g, c_g);
-        a[3] = h2_fma(((vh >> 8) & mask) | hibit<K, tgt, true>(hh) | H2_1024, s_h, c_h);
+        const uint32_t mask = hi ? kc.mf0 : kc.m0f, bit = hi ? kc.h8 : kc.h4;
+        a[0] = h2_fma((vg & mask) | hibit<K, tgt, false>(hg, bit, kc.magic), s_g, c_g);
+        a[1] = h2_fma((vh & mask) | hibit<K, tgt, false>(hh, bit, kc.magic), s_h, c_h);
+        a[2] = h2_fma(((vg >> 8) & mask) | hibit<K, tgt, true>(hg, bit, kc.magic), s_g, c_g);
+        a[3] = h2_fma(((vh >> 8) & mask) | hibit<K, tgt, true>(hh, bit, kc.magic), s_h, c_h);
     }
     template <int K>
     __device__ static void subblock(const typename C::Regs & r, const uint8_t * tg, const uint8_t * th,
-                                    const uint8_t * const (&xrow)[NT], int sbl, float (&acc)[NT][4]) {
+                                    const uint8_t * const (&xrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
         constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
         const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
         const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
@@ -393,7 +419,7 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
         const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
         uint32_t a[2][4];
 #pragma unroll
-        for (int h = 0; h < 2; h++) sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h]);
+        for (int h = 0; h < 2; h++) sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h], kc);
 #pragma unroll
         for (int jt = 0; jt < NT; jt++) {
             const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * K) * 2);
@@ -402,13 +428,13 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
         }
     }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
+                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
         const int g = lane >> 2, t = lane & 3;
         const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
-        subblock<0>(r, tg, th, xrow, sbl, acc); subblock<1>(r, tg, th, xrow, sbl, acc);
-        subblock<2>(r, tg, th, xrow, sbl, acc); subblock<3>(r, tg, th, xrow, sbl, acc);
-        subblock<4>(r, tg, th, xrow, sbl, acc); subblock<5>(r, tg, th, xrow, sbl, acc);
-        subblock<6>(r, tg, th, xrow, sbl, acc); subblock<7>(r, tg, th, xrow, sbl, acc);
+        subblock<0>(r, tg, th, xrow, sbl, acc, kc); subblock<1>(r, tg, th, xrow, sbl, acc, kc);
+        subblock<2>(r, tg, th, xrow, sbl, acc, kc); subblock<3>(r, tg, th, xrow, sbl, acc, kc);
+        subblock<4>(r, tg, th, xrow, sbl, acc, kc); subblock<5>(r, tg, th, xrow, sbl, acc, kc);
+        subblock<6>(r, tg, th, xrow, sbl, acc, kc); subblock<7>(r, tg, th, xrow, sbl, acc, kc);
         const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
         const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
 #pragma unroll
@@ -447,7 +473,7 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
         }
     }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
+                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
         const int g = lane >> 2, t = lane & 3;
         const uint2 * tg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE) + (t >> 1);
         const uint2 * th = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE) + (t >> 1);
@@ -464,15 +490,15 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
                 for (int nib = 0; nib < 2; nib++) {
                     const int k = 4 * n6 + hsel + 2 * nib;
                     const uint2 eg = tg[2 * k], eh = th[2 * k];
-                    const uint32_t qm = nib ? 0x00f000f0u : 0x000f000fu, hm = nib ? 0x03000300u : 0x00300030u;
+                    const uint32_t qm = nib ? kc.mf0 : kc.m0f, hm = nib ? kc.h8 : kc.h4;
                     uint32_t a[2][4];
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
-                        a[h][0] = h2_fma((vg & qm) | ((hg[h] << lsh) & hm) | H2_1024, eg.x, eg.y);
-                        a[h][1] = h2_fma((vh & qm) | ((hh[h] << lsh) & hm) | H2_1024, eh.x, eh.y);
-                        a[h][2] = h2_fma(((vg >> 8) & qm) | ((hg[h] >> rsh) & hm) | H2_1024, eg.x, eg.y);
-                        a[h][3] = h2_fma(((vh >> 8) & qm) | ((hh[h] >> rsh) & hm) | H2_1024, eh.x, eh.y);
+                        a[h][0] = h2_fma((vg & qm) | (((hg[h] << lsh) & hm) | kc.magic), eg.x, eg.y);
+                        a[h][1] = h2_fma((vh & qm) | (((hh[h] << lsh) & hm) | kc.magic), eh.x, eh.y);
+                        a[h][2] = h2_fma(((vg >> 8) & qm) | (((hg[h] >> rsh) & hm) | kc.magic), eg.x, eg.y);
+                        a[h][3] = h2_fma(((vh >> 8) & qm) | (((hh[h] >> rsh) & hm) | kc.magic), eh.x, eh.y);
                     }
 #pragma unroll
                     for (int jt = 0; jt < NT; jt++) {
@@ -507,8 +533,9 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
         scl[3] = dup_hi(db);
     }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4]) {
+                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
         (void)xsrow;
+        (void)kc;
         const int g = lane >> 2;
         const uint32_t * sgp = reinterpret_cast<const uint32_t *>(tab + g * C::SCL_STRIDE);
         const uint32_t * shp = reinterpret_cast<const uint32_t *>(tab + (g + 8) * C::SCL_STRIDE);
@@ -546,6 +573,7 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
 __device__ int g_gemm_wait_expired = 0;
 
 struct TParams {
+    DecodeConsts kc;
     const uint8_t * w;
     int N, nsb;
     const __half * xh;      // prepared activations [M][nsb * 256]
@@ -690,6 +718,12 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         xsrow[j] = xsum + (size_t)tok * xsum_stride;
     }
 
+#if YK_GEMM_RUNTIME_CONSTS
+    const DecodeConsts kc = p.kc;
+#else
+    const DecodeConsts kc = DT == YUUKA_DTYPE_Q5_K ? DecodeConsts{0x000f000fu, 0x00f000f0u, 0x64006400u, 0x00100010u, 0x01000100u}
+                                                   : DecodeConsts{0x000f000fu, 0x00f000f0u, 0x64006400u, 0x00300030u, 0x03000300u};
+#endif
     for (; grp < p.n_groups; grp += gridDim.x) {
         const int rt = grp * p.TG + tile_in_group;
         const int rtc = min(rt, n_tiles - 1);
@@ -704,6 +738,33 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (grp != (int)blockIdx.x && sb0 + 1 < sb1)
             prefetch_l2_range(tile + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
 
+#if YK_GEMM_PINGPONG
+        // Two records per trip, the register buffers swapping roles: while one is consumed the other
+        // is in flight. At the end of the group `cur` holds the first record of the next group's tile.
+        const uint8_t * next_first = nullptr;
+        if (grp + (int)gridDim.x < p.n_groups) {
+            const int rtn = min((grp + (int)gridDim.x) * p.TG + tile_in_group, n_tiles - 1);
+            next_first = p.w + rtn * rec_row + (size_t)sb0 * C::REC;
+        }
+        for (int sb = sb0; sb < sb1; sb += 2) {
+            if (sb + 1 < sb1) C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
+            else if (next_first) C::load(next_first, lane, nxt);
+            MM::header(cur, lane, tab);
+            __syncwarp();
+            MM::run(cur, lane, tab, xrow, xsrow, sb - c0, acc, kc);
+            __syncwarp();
+            if (sb + 1 >= sb1) {
+                cur = nxt;
+                break;
+            }
+            if (sb + 2 < sb1) C::load(tile + (size_t)(sb + 2) * C::REC, lane, cur);
+            else if (next_first) C::load(next_first, lane, cur);
+            MM::header(nxt, lane, tab);
+            __syncwarp();
+            MM::run(nxt, lane, tab, xrow, xsrow, sb + 1 - c0, acc, kc);
+            __syncwarp();
+        }
+#else
         for (int sb = sb0; sb < sb1; sb++) {
             // prefetch the next record of this tile, or the first record of the next group's tile
             if (sb + 1 < sb1) {
@@ -714,10 +775,11 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             }
             MM::header(cur, lane, tab);
             __syncwarp();
-            MM::run(cur, lane, tab, xrow, xsrow, sb - c0, acc);
+            MM::run(cur, lane, tab, xrow, xsrow, sb - c0, acc, kc);
             __syncwarp();
             cur = nxt;
         }
+#endif
 
         // ---- reduce the K parts of a row tile inside the CTA ----
         if (p.KS > 1) {
@@ -1021,6 +1083,7 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     auto kern = gemm_tiled_mma_kernel<DT, NT>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
+    p.kc = decode_consts(DT);
     p.w = a.w;
     p.N = a.n_out;
     p.nsb = a.n_in / 256;
