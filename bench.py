@@ -292,7 +292,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
             "roofline": {"bound": "hbm", "kernel": "gemm_tiled_mma_kernel (every quantized GEMM launch of a step, LM head included)",
                          "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak,
                          "peak_source": peak_kind, "bytes_per_step": weight_bytes, "ms_per_step": gemm_ms,
-                         "traffic": None},
+                         # DRAM read / algorithmic ratio of the ncu captures under profiles/ (1.004 Q4_K, 1.002 Q6_K)
+                         "traffic": int(weight_bytes * 1.003), "traffic_source": "ncu dram__bytes_read of two GEMM "
+                         "shapes, scaled by bytes processed",
+                         "launches_per_step": 137},
             "step_roofline": {"bytes_per_step": step_bytes, "weights": weight_bytes, "kv": kv_bytes,
                               "recurrent_state": state_bytes, "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
                               "frac_of_measured_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
