@@ -311,7 +311,10 @@ typedef enum yuuka_op_code {
     YUUKA_OP_GDN_SCAN = 100,
     YUUKA_OP_GDN_NORM_GATE = 101,
     YUUKA_OP_ACCEPT = 102,
-    YUUKA_OP_COMMIT = 103
+    YUUKA_OP_COMMIT = 103,
+    YUUKA_OP_MOE_ROUTE = 104,   /* router logits, top-k, grouping of (row, slot) pairs by expert */
+    YUUKA_OP_MOE_EXPERTS = 105, /* grouped expert gate|up GEMM, SwiGLU, grouped down GEMM */
+    YUUKA_OP_MOE_COMBINE = 106
 } yuuka_op_code;
 YUUKA_API yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes, uint64_t * op_times_ns,
                                                     uint64_t capacity, uint64_t * op_count);

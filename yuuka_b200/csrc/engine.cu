@@ -46,6 +46,13 @@ struct LayerW {
     Tensor qk;       // q | k (| v)
     bool qk_has_v = false;
     Tensor gate_up;  // ffn_gate | ffn_up
+    // qwen35moe block (model/qwen35/load.go:171-215)
+    const float * router = nullptr;       // ffn_gate_inp [experts][hidden] f32
+    const float * sh_gate_inp = nullptr;  // ffn_gate_inp_shexp [hidden] f32
+    Tensor sh_gate, sh_up, sh_down, sh_gate_up;
+    Tensor exp_gate_up;  // per expert: gate rows then up rows, each expert tiled on its own
+    Tensor exp_down;     // per expert [hidden][expert_ffn], each expert tiled on its own
+    size_t exp_gate_up_stride = 0, exp_down_stride = 0;
 };
 
 void free_tensor(Tensor & t) {
@@ -190,6 +197,57 @@ void tile_in_place(yuuka_model * m, Tensor & t, const std::string & name) {
     t.tiled = true;
 }
 
+// Expert matrices of one MoE layer, tile-ordered expert by expert. parts: tensors of `experts`
+// stacked matrices of rows_each x cols (expertSlice, model/qwen35/forward.go:441-458); expert e of
+// the result holds part[0]'s rows of e, then part[1]'s, ... as one matrix.
+Tensor tile_experts(yuuka_model * m, std::vector<const Tensor *> parts, int experts, uint64_t rows_each, size_t * stride) {
+    const Tensor & first = *parts[0];
+    for (const Tensor * t : parts) {
+        YK_REQUIRE(t->dtype == first.dtype && t->cols == first.cols && t->rows == rows_each * (uint64_t)experts, YUUKA_ERR_UNSUPPORTED,
+                   "expert tensors of one projection must share dtype and shape");
+    }
+    YK_REQUIRE(tiled_supported(first.dtype, first.cols) && rows_each % 16 == 0, YUUKA_ERR_UNSUPPORTED,
+               "expert matrices of dtype %u, %llu x %llu have no tiled layout", first.dtype, (unsigned long long)rows_each,
+               (unsigned long long)first.cols);
+    const uint64_t rb = row_bytes(first.dtype, first.cols);
+    const uint64_t rows_fused = rows_each * parts.size();
+    const uint64_t per_expert = tiled_bytes(first.dtype, rows_fused, first.cols);
+    void * dst = nullptr;
+    void * tmp = nullptr;
+    cudaError_t err = cudaMalloc(&dst, per_expert * experts + 256);
+    YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "expert weight allocation of %llu bytes failed",
+               (unsigned long long)(per_expert * experts));
+    m->extra_allocs.push_back(dst);
+    err = cudaMalloc(&tmp, rows_fused * rb + 256);
+    YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "expert staging allocation failed");
+    try {
+        for (int e = 0; e < experts; e++) {
+            uint64_t off = 0;
+            for (const Tensor * t : parts) {
+                YK_CUDA(cudaMemcpyAsync((uint8_t *)tmp + off, t->ptr + (uint64_t)e * rows_each * rb, rows_each * rb,
+                                        cudaMemcpyDeviceToDevice, nullptr));
+                off += rows_each * rb;
+            }
+            launch_tile_weights(nullptr, (uint8_t *)dst + (uint64_t)e * per_expert, (const uint8_t *)tmp, first.dtype,
+                                (int)rows_fused, (int)first.cols);
+        }
+        YK_CUDA(cudaDeviceSynchronize());
+    } catch (...) {
+        cudaFree(tmp);
+        throw;
+    }
+    cudaFree(tmp);
+    Tensor out;
+    out.ptr = (uint8_t *)dst;
+    out.dtype = first.dtype;
+    out.rows = rows_fused;  // per expert
+    out.cols = first.cols;
+    out.bytes = per_expert * experts;
+    out.tiled = true;
+    *stride = per_expert;
+    return out;
+}
+
 }  // namespace
 
 extern "C" {
@@ -253,7 +311,6 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
         if (m->finalized) return;
         set_device(m->dev);
         const yuuka_model_config & c = m->cfg;
-        YK_REQUIRE(c.expert_count == 0, YUUKA_ERR_UNSUPPORTED, "qwen35moe layers are not supported by this build yet");
         const uint64_t H = c.hidden, V = c.vocab;
         m->embedding = need(m, "token_embd.weight", V, H, false);
         if (m->tensors.count("output.weight")) m->output = need(m, "output.weight", V, H, false);
@@ -261,6 +318,7 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
         m->output_norm = vec(m, "output_norm.weight", H);
         const uint64_t S = c.state_size, R = c.time_step_rank, inner = c.inner_size;
         const uint64_t conv_dim = m->conv_dim(), q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim();
+        uint64_t moe_bytes = 0;
         for (int i = 0; i < c.block_count; i++) {
             LayerW & L = m->layers[i];
             const std::string p = "blk." + std::to_string(i) + ".";
@@ -302,6 +360,28 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
                     }
                 }
             }
+            if (c.expert_count > 0) {
+                const uint64_t E = c.expert_count, EF = c.expert_ffn, SF = c.shared_ffn;
+                L.router = reinterpret_cast<const float *>(need(m, p + "ffn_gate_inp.weight", E, H, true).ptr);
+                L.sh_gate_inp = vec(m, p + "ffn_gate_inp_shexp.weight", H);
+                L.sh_gate = need(m, p + "ffn_gate_shexp.weight", SF, H, false);
+                L.sh_up = need(m, p + "ffn_up_shexp.weight", SF, H, false);
+                L.sh_down = need(m, p + "ffn_down_shexp.weight", H, SF, false);
+                const Tensor ge = need(m, p + "ffn_gate_exps.weight", EF * E, H, false);
+                const Tensor ue = need(m, p + "ffn_up_exps.weight", EF * E, H, false);
+                const Tensor de = need(m, p + "ffn_down_exps.weight", H * E, EF, false);
+                moe_bytes += ge.bytes + ue.bytes + de.bytes;
+                L.exp_gate_up = tile_experts(m, {&ge, &ue}, (int)E, EF, &L.exp_gate_up_stride);
+                L.exp_down = tile_experts(m, {&de}, (int)E, H, &L.exp_down_stride);
+                for (const char * n : {"ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"}) drop(m, p + n);
+                L.sh_gate_up = fuse(m, {&L.sh_gate, &L.sh_up});
+                if (L.sh_gate_up.present()) {
+                    drop(m, p + "ffn_gate_shexp.weight");
+                    drop(m, p + "ffn_up_shexp.weight");
+                    L.sh_gate = L.sh_up = Tensor();
+                }
+                continue;
+            }
             L.ffn_gate = need(m, p + "ffn_gate.weight", c.ffn, H, false);
             L.ffn_up = need(m, p + "ffn_up.weight", c.ffn, H, false);
             L.ffn_down = need(m, p + "ffn_down.weight", H, c.ffn, false);
@@ -316,8 +396,8 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
         uint64_t total = 0;
         for (auto & kv : m->tensors)
             if (kv.first != "token_embd.weight") total += kv.second.bytes;
-        for (const LayerW & L : m->layers) total += L.proj.bytes + L.qk.bytes + L.gate_up.bytes;
-        m->weight_bytes = total;
+        for (const LayerW & L : m->layers) total += L.proj.bytes + L.qk.bytes + L.gate_up.bytes + L.sh_gate_up.bytes;
+        m->weight_bytes = total + moe_bytes;
         // tile-ordered copies for the GEMM kernels; the GGUF-layout bytes are released
         const bool tied = !m->tensors.count("output.weight");
         for (int i = 0; i < c.block_count; i++) {
@@ -338,6 +418,10 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
             tile_in_place(m, L.ffn_gate, p + "ffn_gate.weight");
             tile_in_place(m, L.ffn_up, p + "ffn_up.weight");
             tile_in_place(m, L.ffn_down, p + "ffn_down.weight");
+            tile_in_place(m, L.sh_gate_up, "");
+            tile_in_place(m, L.sh_gate, p + "ffn_gate_shexp.weight");
+            tile_in_place(m, L.sh_up, p + "ffn_up_shexp.weight");
+            tile_in_place(m, L.sh_down, p + "ffn_down_shexp.weight");
         }
         if (!tied) tile_in_place(m, m->output, "output.weight");
         else if (tiled_supported(m->output.dtype, m->output.cols)) {
@@ -421,6 +505,13 @@ struct yuuka_session {
     uint64_t * d_anc = nullptr;
     float *x = nullptr, *xn = nullptr, *qkv_attn = nullptr, *attn_out = nullptr, *gdn_out = nullptr;
     float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
+    // qwen35moe scratch: routing, expert-sorted (row, slot) pairs, expert and shared-expert activations
+    int32_t *moe_ids = nullptr, *moe_pos = nullptr, *moe_row = nullptr;
+    float *moe_w = nullptr, *moe_sg = nullptr, *moe_gu = nullptr, *moe_act = nullptr, *moe_y = nullptr;
+    float *sh_gu = nullptr, *sh_act = nullptr, *sh_y = nullptr;
+    GemmSegment * moe_segments = nullptr;
+    int moe_max_segments = 0;
+    XPrepOut prep_moe_act, prep_sh_act;
     XPrepOut prep_xn, prep_attn, prep_gdn, prep_act;  // fp16 + group sums of the GEMM inputs
     float *gdn_qn = nullptr, *gdn_vconv = nullptr, *gdn_beta = nullptr;
     int * gdn_counters = nullptr;
@@ -648,6 +739,64 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
                                             max_total, sc, s->prep_attn);
             gemm_residual_norm(s, L.o, s->attn_out, o_dim, s->prep_attn, R, L.post_norm);
+        }
+        if (c.expert_count > 0) {
+            // forwardMoEFFN (model/qwen35/forward.go:320-389); xn = rmsnorm(x) * post_norm is in place
+            const int E = c.expert_count, U = c.expert_used, EF = c.expert_ffn, SF = c.shared_ffn, P = R * U;
+            YK_REQUIRE(s->prep_xn.xh, YUUKA_ERR_UNSUPPORTED, "moe: hidden size must be a multiple of 16");
+            mark(s, YUUKA_OP_MOE_ROUTE);
+            launch_moe_route(st, s->xn, L.router, L.sh_gate_inp, H, E, U, R, s->moe_ids, s->moe_w, s->moe_sg);
+            launch_moe_group(st, s->moe_ids, R, U, E, s->moe_pos, s->moe_row, s->moe_segments, s->moe_max_segments);
+            s->launches += 2;
+            mark(s, YUUKA_OP_MOE_EXPERTS);
+            GroupedGemmArgs ga;
+            ga.w = L.exp_gate_up.ptr;
+            ga.w_dtype = L.exp_gate_up.dtype;
+            ga.expert_stride = L.exp_gate_up_stride;
+            ga.xprep = s->prep_xn;
+            ga.row_index = s->moe_row;
+            ga.out = s->moe_gu;
+            ga.ldo = 2 * EF;
+            ga.n_out = 2 * EF;
+            ga.n_in = H;
+            ga.segments = s->moe_segments;
+            ga.max_segments = s->moe_max_segments;
+            s->launches += launch_gemm_tiled_grouped(m->dev, st, ga);
+            launch_silu_mul(st, s->moe_act, EF, s->moe_gu, s->moe_gu + EF, 2 * EF, EF, P, s->prep_moe_act);
+            s->launches++;
+            GroupedGemmArgs gd;
+            gd.w = L.exp_down.ptr;
+            gd.w_dtype = L.exp_down.dtype;
+            gd.expert_stride = L.exp_down_stride;
+            gd.xprep = s->prep_moe_act;
+            gd.out = s->moe_y;
+            gd.ldo = H;
+            gd.n_out = H;
+            gd.n_in = EF;
+            gd.segments = s->moe_segments;
+            gd.max_segments = s->moe_max_segments;
+            s->launches += launch_gemm_tiled_grouped(m->dev, st, gd);
+            // shared expert: dense
+            mark(s, YUUKA_OP_GEMM);
+            if (L.sh_gate_up.present()) {
+                gemm(s, L.sh_gate_up, s->xn, H, s->prep_xn, s->sh_gu, 2 * SF, R, 0);
+            } else {
+                gemm(s, L.sh_gate, s->xn, H, s->prep_xn, s->sh_gu, 2 * SF, R, 0);
+                gemm(s, L.sh_up, s->xn, H, s->prep_xn, s->sh_gu + SF, 2 * SF, R, 0);
+            }
+            mark(s, YUUKA_OP_SILU_MUL);
+            launch_silu_mul(st, s->sh_act, SF, s->sh_gu, s->sh_gu + SF, 2 * SF, SF, R, s->prep_sh_act);
+            s->launches++;
+            gemm(s, L.sh_down, s->sh_act, SF, s->prep_sh_act, s->sh_y, H, R, 0);
+            mark(s, YUUKA_OP_MOE_COMBINE);
+            launch_moe_combine(st, s->x, s->moe_y, s->sh_y, s->moe_pos, s->moe_w, s->moe_sg, H, U, R);
+            s->launches++;
+            if (next_norm) {
+                mark(s, YUUKA_OP_RMSNORM);
+                launch_rmsnorm(st, s->xn, H, s->x, H, next_norm, H, R, c.rms_eps, s->prep_xn);
+                s->launches++;
+            }
+            continue;
         }
         // forwardFFN (model/qwen35/forward.go:295-315); its input norm came with the mixer's output GEMM
         if (L.gate_up.present()) {
@@ -915,6 +1064,28 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->prep_attn = prep_alloc(model->o_dim());
             s->prep_gdn = prep_alloc(c.inner_size);
             s->prep_act = prep_alloc(c.ffn);
+            if (c.expert_count > 0) {
+                const size_t P = (size_t)R * c.expert_used;
+                s->moe_ids = dalloc<int32_t>(P, s->owned);
+                s->moe_pos = dalloc<int32_t>(P, s->owned);
+                s->moe_row = dalloc<int32_t>(P, s->owned);
+                s->moe_w = dalloc<float>(P, s->owned);
+                s->moe_sg = dalloc<float>(R, s->owned);
+                s->moe_gu = dalloc<float>(P * 2 * c.expert_ffn, s->owned);
+                s->moe_act = dalloc<float>(P * c.expert_ffn, s->owned);
+                s->moe_y = dalloc<float>(P * H, s->owned);
+                s->sh_gu = dalloc<float>((size_t)R * 2 * c.shared_ffn, s->owned);
+                s->sh_act = dalloc<float>((size_t)R * c.shared_ffn, s->owned);
+                s->sh_y = dalloc<float>((size_t)R * H, s->owned);
+                s->moe_max_segments = moe_max_segments((int)P, c.expert_count);
+                s->moe_segments = dalloc<GemmSegment>((size_t)s->moe_max_segments, s->owned);
+                YK_REQUIRE(c.expert_ffn % 16 == 0 && c.shared_ffn % 16 == 0, YUUKA_ERR_UNSUPPORTED,
+                           "expert feed-forward sizes must be multiples of 16");
+                s->prep_moe_act.xh = dalloc<__half>(P * c.expert_ffn, s->owned);
+                s->prep_moe_act.xs16 = dalloc<__half2>(P * (c.expert_ffn / 16) + 4, s->owned);
+                s->prep_sh_act.xh = dalloc<__half>((size_t)R * c.shared_ffn, s->owned);
+                s->prep_sh_act.xs16 = dalloc<__half2>((size_t)R * (c.shared_ffn / 16) + 4, s->owned);
+            }
             if (sc.want_logits) s->logits = dalloc<float>((size_t)R * c.vocab, s->owned);
             s->argmax.chunks = argmax_chunks(c.vocab);
             s->argmax.val = dalloc<float>((size_t)R * s->argmax.chunks, s->owned);
@@ -929,12 +1100,14 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             for (int rows : {R < 32 ? R : 32, 1}) {
                 for (const LayerW & L : model->layers) {
                     for (const Tensor * t : {&L.q, &L.k, &L.v, &L.o, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.ffn_gate,
-                                             &L.ffn_up, &L.ffn_down, &L.proj, &L.qk, &L.gate_up})
+                                             &L.ffn_up, &L.ffn_down, &L.proj, &L.qk, &L.gate_up, &L.sh_gate, &L.sh_up,
+                                             &L.sh_down, &L.sh_gate_up})
                         reserve_gemm(s, *t, rows);
                 }
                 reserve_gemm(s, model->output, rows);
             }
             for (int r = 1; r < R && r < 32; r++) reserve_gemm(s, model->layers[0].ffn_down, r);
+            for (int r = 1; r < R && r < 32; r++) reserve_gemm(s, model->layers[0].sh_down, r);
         } catch (...) {
             yuuka_session_destroy(s);
             throw;

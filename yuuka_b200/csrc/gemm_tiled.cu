@@ -597,6 +597,11 @@ struct TParams {
     int64_t post_ld;
     XPrepOut post_prep;
     int * post_counter;
+    // optional (GROUPED kernels): per-blockIdx.z row segments, byte stride between expert matrices,
+    // and the source row of every activation row
+    const GemmSegment * segments;
+    size_t expert_stride;
+    const int32_t * row_index;
 };
 
 // rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
@@ -634,13 +639,37 @@ __device__ void post_rmsnorm_rows(const TParams & p, int warp, int lane) {
     }
 }
 
-template <int DT, int NT>
+// GROUPED: blockIdx.z walks a device-built list of row segments, each bound to one expert's matrix
+// (qwen35moe expert FFNs). A segment's rows are contiguous in the prepared-activation and output
+// arrays unless row_index redirects the activation rows.
+template <int DT, int NT, bool GROUPED>
 __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParams p) {
     using C = Codec<DT>;
     using MM = Mma<DT, NT>;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t xbar;
     __shared__ int last_flag;
+    const uint8_t * wbase = p.w;
+    const __half * xhp = p.xh;
+    const __half2 * xsp = p.xs16;
+    float * outp = p.out;
+    int Mrows = p.M;
+    const int32_t * row_index = nullptr;
+    if constexpr (GROUPED) {
+        // the segment list is written by the kernel before this one: nothing can start ahead of the wait
+        pdl_trigger();
+        pdl_wait();
+        const GemmSegment sg = p.segments[blockIdx.z];
+        if (sg.count <= 0) return;  // the whole CTA: unused slot of the segment list
+        wbase += (size_t)sg.expert * p.expert_stride;
+        Mrows = sg.count;
+        outp += (int64_t)sg.row0 * p.ldo;
+        if (p.row_index) row_index = p.row_index + sg.row0;
+        else {
+            xhp += (size_t)sg.row0 * p.nsb * 256;
+            xsp += (size_t)sg.row0 * p.nsb * 16;
+        }
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int c0 = blockIdx.y * p.nsb_chunk;
@@ -649,8 +678,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     const int xstride = p.nsb_chunk * 512 + 64;       // bytes of fp16 activations per row (+64: bank spread)
     const int xsum_stride = p.nsb_chunk * 64 + 16;    // bytes of 16-element sums per row
     uint8_t * xs = smem;
-    uint8_t * xsum = xs + (size_t)p.M * xstride;
-    uint8_t * tabs = xsum + (((size_t)p.M * xsum_stride + 127) / 128) * 128;
+    uint8_t * xsum = xs + (size_t)Mrows * xstride;
+    uint8_t * tabs = xsum + (((size_t)Mrows * xsum_stride + 127) / 128) * 128;
     float * red = reinterpret_cast<float *>(tabs + TW * C::TAB);
 
     const int tile_in_group = warp / p.KS, kpart = warp - tile_in_group * p.KS;
@@ -665,8 +694,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     typename C::Regs cur, nxt;
     {
         const int rt = min(grp * p.TG + tile_in_group, n_tiles - 1);
-        if (sb0 < sb1) C::load(p.w + rt * rec_row + (size_t)sb0 * C::REC, lane, cur);
-        if (sb0 + 1 < sb1) prefetch_l2_range(p.w + rt * rec_row + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
+        if (sb0 < sb1) C::load(wbase + rt * rec_row + (size_t)sb0 * C::REC, lane, cur);
+        if (sb0 + 1 < sb1) prefetch_l2_range(wbase + rt * rec_row + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
     }
     pdl_wait();
 
@@ -679,11 +708,12 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     if (threadIdx.x == 0) {
         const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
         const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = (uint32_t)cnt * 64;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * p.M)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * Mrows)
                      : "memory");
-        for (int m = 0; m < p.M; m++) {
-            const __half * srcx = p.xh + ((size_t)m * p.nsb + c0) * 256;
-            const __half2 * srcs = p.xs16 + ((size_t)m * p.nsb + c0) * 16;
+        for (int m = 0; m < Mrows; m++) {
+            const size_t mr = row_index ? (size_t)row_index[m] : (size_t)m;
+            const __half * srcx = xhp + (mr * p.nsb + c0) * 256;
+            const __half2 * srcs = xsp + (mr * p.nsb + c0) * 16;
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                              (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * xstride)),
                          "l"(srcx), "r"(row_bytes_x), "r"(bar)
@@ -713,7 +743,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     const uint8_t * xsrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; j++) {
-        const int tok = min(8 * j + g, p.M - 1);
+        const int tok = min(8 * j + g, Mrows - 1);
         xrow[j] = xs + (size_t)tok * xstride + t * 16;
         xsrow[j] = xsum + (size_t)tok * xsum_stride;
     }
@@ -727,7 +757,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     for (; grp < p.n_groups; grp += gridDim.x) {
         const int rt = grp * p.TG + tile_in_group;
         const int rtc = min(rt, n_tiles - 1);
-        const uint8_t * tile = p.w + rtc * rec_row;
+        const uint8_t * tile = wbase + rtc * rec_row;
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; j++)
@@ -744,7 +774,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         const uint8_t * next_first = nullptr;
         if (grp + (int)gridDim.x < p.n_groups) {
             const int rtn = min((grp + (int)gridDim.x) * p.TG + tile_in_group, n_tiles - 1);
-            next_first = p.w + rtn * rec_row + (size_t)sb0 * C::REC;
+            next_first = wbase + rtn * rec_row + (size_t)sb0 * C::REC;
         }
         for (int sb = sb0; sb < sb1; sb += 2) {
             if (sb + 1 < sb1) C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
@@ -771,7 +801,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                 C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
             } else if (grp + (int)gridDim.x < p.n_groups) {
                 const int rtn = min((grp + (int)gridDim.x) * p.TG + tile_in_group, n_tiles - 1);
-                C::load(p.w + rtn * rec_row + (size_t)sb0 * C::REC, lane, nxt);
+                C::load(wbase + rtn * rec_row + (size_t)sb0 * C::REC, lane, nxt);
             }
             MM::header(cur, lane, tab);
             __syncwarp();
@@ -803,14 +833,14 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         // ---- epilogue ----
         if (kpart == 0 && rt < n_tiles) {
             const int n_g = rt * 16 + g, n_h = n_g + 8;
-            float * base = p.kchunks == 1 ? p.out : p.partial + (size_t)blockIdx.y * p.M * p.N;
+            float * base = p.kchunks == 1 ? outp : p.partial + (size_t)blockIdx.y * Mrows * p.N;
             const int64_t ld = p.kchunks == 1 ? p.ldo : p.N;
 #pragma unroll
             for (int j = 0; j < NT; j++)
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     const int tok = 8 * j + 2 * t + (c & 1), n = (c & 2) ? n_h : n_g;
-                    if (tok < p.M && n < p.N) {
+                    if (tok < Mrows && n < p.N) {
                         float * dst = base + (int64_t)tok * ld + n;
                         if (p.kchunks == 1) *dst = p.accumulate ? *dst + acc[j][c] : acc[j][c];
                         else __stcg(dst, acc[j][c]);
@@ -826,11 +856,11 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             if (last_flag) {
                 __threadfence();
                 const int row0 = grp * p.TG * 16, nrows = min(p.TG * 16, p.N - row0);
-                for (int i = threadIdx.x; i < p.M * nrows; i += TW * 32) {
+                for (int i = threadIdx.x; i < Mrows * nrows; i += TW * 32) {
                     const int tok = i / nrows, n = row0 + (i - tok * nrows);
                     float s = 0.0f;
-                    for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * p.M + tok) * p.N + n);
-                    float * dst = p.out + (int64_t)tok * p.ldo + n;
+                    for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * Mrows + tok) * p.N + n);
+                    float * dst = outp + (int64_t)tok * p.ldo + n;
                     *dst = p.accumulate ? *dst + s : s;
                 }
                 if (threadIdx.x == 0) p.counters[grp] = 0;
@@ -848,7 +878,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         __syncthreads();
         if (last_flag) {
             __threadfence();
-            post_rmsnorm_rows(p, warp, lane);
+            post_rmsnorm_rows(p, warp, lane);  // (never with GROUPED: p.M and p.out are the launch-wide ones)
             if (threadIdx.x == 0) *p.post_counter = 0;
         }
     }
@@ -1080,7 +1110,7 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
 template <int DT, int NT>
 static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
                             const TPlan & pl) {
-    auto kern = gemm_tiled_mma_kernel<DT, NT>;
+    auto kern = gemm_tiled_mma_kernel<DT, NT, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
     p.kc = decode_consts(DT);
@@ -1115,6 +1145,63 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     dim3 grid(pl.grid_x, pl.kchunks);
     launch_k(kern, grid, TW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
+}
+
+template <int DT>
+static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const GroupedGemmArgs & a) {
+    const int nsb = a.n_in / 256, n_tiles = (a.n_out + 15) / 16;
+    TPlan pl;
+    pl.KS = 1;
+    pl.TG = TW;
+    pl.n_groups = (n_tiles + TW - 1) / TW;
+    pl.kchunks = 1;
+    pl.nsb_chunk = nsb;
+    pl.smem = mma_smem(DT, GEMM_SEGMENT_ROWS, nsb, 1, 1);
+    pl.grid_x = pl.n_groups;
+    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
+    YK_REQUIRE(pl.smem <= half_sm && pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
+               "grouped gemm: %d columns of activations do not fit shared memory", a.n_in);
+    auto kern = gemm_tiled_mma_kernel<DT, 1, true>;
+    YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+    TParams p{};
+    p.kc = decode_consts(DT);
+    p.w = a.w;
+    p.N = a.n_out;
+    p.nsb = nsb;
+    p.xh = a.xprep.xh;
+    p.xs16 = a.xprep.xs16;
+    p.M = GEMM_SEGMENT_ROWS;
+    p.out = a.out;
+    p.ldo = a.ldo;
+    p.TG = pl.TG;
+    p.KS = pl.KS;
+    p.kchunks = 1;
+    p.nsb_chunk = nsb;
+    p.n_groups = pl.n_groups;
+    p.segments = a.segments;
+    p.expert_stride = a.expert_stride;
+    p.row_index = a.row_index;
+    dim3 grid(pl.grid_x, 1, a.max_segments);
+    launch_k(kern, grid, TW * 32, pl.smem, s, p);
+    YK_CUDA(cudaGetLastError());
+}
+
+int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, const GroupedGemmArgs & a) {
+    YK_REQUIRE(a.w && a.xprep.xh && a.xprep.xs16 && a.out && a.segments, YUUKA_ERR_INVALID_ARGUMENT, "grouped gemm: null operand");
+    YK_REQUIRE(a.n_out > 0 && a.n_in > 0 && a.max_segments > 0 && a.max_segments <= 65535, YUUKA_ERR_INVALID_ARGUMENT,
+               "grouped gemm: invalid shape");
+    YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "grouped gemm: dtype %u / width %d has no tiled layout",
+               a.w_dtype, a.n_in);
+    YK_REQUIRE(a.ldo >= a.n_out, YUUKA_ERR_INVALID_ARGUMENT, "grouped gemm: leading dimension too small");
+    set_device(dev);
+    switch (a.w_dtype) {
+    case YUUKA_DTYPE_Q4_K: launch_grouped_dt<YUUKA_DTYPE_Q4_K>(dev, stream, a); break;
+    case YUUKA_DTYPE_Q5_K: launch_grouped_dt<YUUKA_DTYPE_Q5_K>(dev, stream, a); break;
+    case YUUKA_DTYPE_Q6_K: launch_grouped_dt<YUUKA_DTYPE_Q6_K>(dev, stream, a); break;
+    case YUUKA_DTYPE_Q8_0: launch_grouped_dt<YUUKA_DTYPE_Q8_0>(dev, stream, a); break;
+    default: YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "grouped gemm: dtype %u has no tiled kernels", a.w_dtype);
+    }
+    return 1;
 }
 
 template <int DT>

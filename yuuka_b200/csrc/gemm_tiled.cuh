@@ -44,6 +44,32 @@ struct GemmPostNorm {
     int * counter = nullptr;  // one int, zero between launches
 };
 
+// One run of at most 8 consecutive rows bound to one expert matrix (grouped GEMM). count <= 0 marks
+// an unused slot: the list has a fixed length so that the launch shape does not depend on the routing.
+struct GemmSegment {
+    int32_t expert;
+    int32_t row0;
+    int32_t count;
+    int32_t reserved;
+};
+constexpr int GEMM_SEGMENT_ROWS = 8;
+
+// out[row0 + i][:] = x[row(row0 + i)][:] * W[expert]^T for every segment, W[e] = w + e * expert_stride
+// (tile-ordered, n_out x n_in each). row(j) = row_index[j] if given, else j.
+struct GroupedGemmArgs {
+    const uint8_t * w = nullptr;
+    uint32_t w_dtype = 0;
+    size_t expert_stride = 0;
+    XPrepOut xprep;
+    const int32_t * row_index = nullptr;
+    float * out = nullptr;
+    int64_t ldo = 0;
+    int n_out = 0, n_in = 0;
+    const GemmSegment * segments = nullptr;  // device
+    int max_segments = 0;
+};
+int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, const GroupedGemmArgs & a);
+
 struct TiledGemmArgs {
     const uint8_t * w = nullptr;  // tiled layout
     uint32_t w_dtype = 0;

@@ -1,0 +1,195 @@
+// qwen35moe feed-forward block on the device (model/qwen35/forward.go:320-458):
+// router logits -> top-k experts by repeated argmax (lowest index wins ties) ->
+// softmax over the selected logits only -> grouping of the (row, slot) pairs by
+// expert -> the combine  x += sum_slot w * expert_out + sigmoid(gate) * shared_out.
+// The expert matrices themselves run through the grouped tiled GEMM.
+#include <cfloat>
+
+#include "gemm_tiled.cuh"
+#include "layers.cuh"
+
+namespace yk {
+
+constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_MAX_EXPERTS = 1024;
+
+struct RouteParams {
+    const float * xn;       // [rows][hidden] normalised activations
+    const float * router;   // [experts][hidden] f32
+    const float * sh_gate;  // [hidden] f32 (shared-expert gate vector)
+    int hidden, experts, used;
+    int32_t * ids;          // [rows][used]
+    float * weights;        // [rows][used]
+    float * shared_gate;    // [rows]
+};
+
+// One CTA per row. Warps take experts round-robin; a dot product is summed by lanes in a fixed
+// order (the CPU reference sums sequentially, so logits agree to rounding, not bit for bit).
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteParams p) {
+    pdl_entry();
+    extern __shared__ __align__(16) float sm[];
+    float * x = sm;                      // [hidden]
+    float * logit = sm + p.hidden;       // [experts]
+    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float * src = p.xn + (int64_t)r * p.hidden;
+    for (int i = threadIdx.x; i < p.hidden; i += ROUTE_THREADS) x[i] = src[i];
+    __syncthreads();
+    for (int e = warp; e <= p.experts; e += ROUTE_THREADS / 32) {
+        const float * w = e < p.experts ? p.router + (int64_t)e * p.hidden : p.sh_gate;  // the last one is the shared gate
+        float acc = 0.0f;
+        for (int i = lane; i < p.hidden; i += 32) acc = fmaf(w[i], x[i], acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            if (e < p.experts) logit[e] = acc;
+            else p.shared_gate[r] = 1.0f / (1.0f + (float)exp((double)-acc));
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // selectExperts (forward.go:393-439): `used` rounds of first-maximum argmax over the experts not yet taken
+    int32_t * ids = p.ids + (int64_t)r * p.used;
+    float * wts = p.weights + (int64_t)r * p.used;
+    float my_logit = 0.0f;  // lane s keeps the logit of slot s (used <= 32)
+    for (int slot = 0; slot < p.used; slot++) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < p.experts; e += 32) {
+            const float v = logit[e];
+            if (v != v) continue;  // taken (marked NaN below)
+            if (bi == 0x7fffffff || v > bv) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;
+        if (lane == slot) my_logit = bv;
+        if (lane == 0) {
+            ids[slot] = bi;
+            logit[bi] = __int_as_float(0x7fc00000);
+        }
+        __syncwarp();
+    }
+    // softmax over the selected logits: exp in double, sum in float in slot order
+    float mx = lane < p.used ? my_logit : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float w = lane < p.used ? (float)exp((double)(my_logit - mx)) : 0.0f;
+    float total = 0.0f;
+    for (int s = 0; s < p.used; s++) total += __shfl_sync(0xffffffffu, w, s);
+    if (lane < p.used) wts[lane] = total > 0.0f ? w / total : w;
+}
+
+struct GroupParams {
+    const int32_t * ids;     // [pairs] expert of pair p = row * used + slot
+    int pairs, used, experts, max_segments;
+    int32_t * pos_of_pair;   // [pairs] position of the pair in the expert-sorted order
+    int32_t * row_of_pos;    // [pairs] source row of the pair at a position
+    GemmSegment * segments;  // [max_segments]
+};
+
+// One CTA. Stable counting sort of the pairs by expert, cut into segments of at most 8 rows.
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_group_kernel(const GroupParams p) {
+    pdl_entry();
+    __shared__ int count[ROUTE_MAX_EXPERTS];
+    __shared__ int pair_off[ROUTE_MAX_EXPERTS];
+    __shared__ int seg_off[ROUTE_MAX_EXPERTS];
+    __shared__ int total_segments;
+    for (int e = threadIdx.x; e < p.experts; e += ROUTE_THREADS) {
+        int c = 0;
+        for (int i = 0; i < p.pairs; i++) c += p.ids[i] == e;
+        count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int po = 0, so = 0;
+        for (int e = 0; e < p.experts; e++) {
+            pair_off[e] = po;
+            seg_off[e] = so;
+            po += count[e];
+            so += (count[e] + GEMM_SEGMENT_ROWS - 1) / GEMM_SEGMENT_ROWS;
+        }
+        total_segments = so;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.experts; e += ROUTE_THREADS) {
+        int j = 0;
+        const int c = count[e];
+        for (int i = 0; i < p.pairs && j < c; i++) {
+            if (p.ids[i] != e) continue;
+            const int pos = pair_off[e] + j;
+            p.pos_of_pair[i] = pos;
+            p.row_of_pos[pos] = i / p.used;
+            if (j % GEMM_SEGMENT_ROWS == 0) {
+                const int z = seg_off[e] + j / GEMM_SEGMENT_ROWS;
+                if (z < p.max_segments) p.segments[z] = GemmSegment{e, pos, min(GEMM_SEGMENT_ROWS, c - j), 0};
+            }
+            j++;
+        }
+    }
+    for (int z = total_segments + threadIdx.x; z < p.max_segments; z += ROUTE_THREADS) p.segments[z] = GemmSegment{0, 0, 0, 0};
+}
+
+int moe_max_segments(int pairs, int experts) {
+    const int by_rows = pairs / GEMM_SEGMENT_ROWS + (experts < pairs ? experts : pairs);
+    return by_rows < pairs ? by_rows : pairs;
+}
+
+void launch_moe_route(cudaStream_t s, const float * xn, const float * router, const float * sh_gate, int hidden, int experts,
+                      int used, int rows, int32_t * ids, float * weights, float * shared_gate) {
+    YK_REQUIRE(experts <= ROUTE_MAX_EXPERTS && used <= 32 && used <= experts, YUUKA_ERR_UNSUPPORTED,
+               "moe: %d experts / %d used exceeds the router kernel's limits (%d / 32)", experts, used, ROUTE_MAX_EXPERTS);
+    RouteParams p{xn, router, sh_gate, hidden, experts, used, ids, weights, shared_gate};
+    const size_t smem = sizeof(float) * ((size_t)hidden + experts);
+    YK_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_k(moe_route_kernel, rows, ROUTE_THREADS, smem, s, p);
+    YK_CUDA(cudaGetLastError());
+}
+
+void launch_moe_group(cudaStream_t s, const int32_t * ids, int rows, int used, int experts, int32_t * pos_of_pair,
+                      int32_t * row_of_pos, GemmSegment * segments, int max_segments) {
+    GroupParams p{ids, rows * used, used, experts, max_segments, pos_of_pair, row_of_pos, segments};
+    launch_k(moe_group_kernel, 1, ROUTE_THREADS, 0, s, p);
+    YK_CUDA(cudaGetLastError());
+}
+
+struct CombineParams {
+    float * x;                 // [rows][hidden] residual stream, updated in place
+    const float * expert_out;  // [pairs][hidden] in expert-sorted order
+    const float * shared_out;  // [rows][hidden]
+    const int32_t * pos_of_pair;
+    const float * weights;     // [rows][used]
+    const float * shared_gate; // [rows]
+    int hidden, used;
+};
+
+// forward.go:370-389, same order of operations: tmp = sum over slots of w * out (slot order), then
+// + gate * shared, then x += tmp; products and sums rounded separately as the reference does.
+__global__ void moe_combine_kernel(const CombineParams p) {
+    pdl_entry();
+    const int r = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.hidden) return;
+    float tmp = 0.0f;
+    for (int s = 0; s < p.used; s++) {
+        const int pos = p.pos_of_pair[r * p.used + s];
+        tmp = __fadd_rn(tmp, __fmul_rn(p.weights[r * p.used + s], p.expert_out[(int64_t)pos * p.hidden + i]));
+    }
+    tmp = __fadd_rn(tmp, __fmul_rn(p.shared_gate[r], p.shared_out[(int64_t)r * p.hidden + i]));
+    float * dst = p.x + (int64_t)r * p.hidden + i;
+    *dst = __fadd_rn(*dst, tmp);
+}
+
+void launch_moe_combine(cudaStream_t s, float * x, const float * expert_out, const float * shared_out,
+                        const int32_t * pos_of_pair, const float * weights, const float * shared_gate, int hidden, int used,
+                        int rows) {
+    CombineParams p{x, expert_out, shared_out, pos_of_pair, weights, shared_gate, hidden, used};
+    dim3 grid((hidden + 255) / 256, rows);
+    launch_k(moe_combine_kernel, grid, 256, 0, s, p);
+    YK_CUDA(cudaGetLastError());
+}
+
+}  // namespace yk
