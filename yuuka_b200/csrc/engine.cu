@@ -517,6 +517,11 @@ struct yuuka_session {
     int * gdn_counters = nullptr;
     int * post_counter = nullptr;
     bool fuse_post_norm = false;
+    // L2 prefetch of the next GEMM's weights: matrices in the order a step streams them
+    bool prefetch_next = true;
+    uint64_t prefetch_bytes = 16ull << 20;  // measured: 16 MB ahead 3.09 ms/step, none 3.12, 48 MB 3.13
+    std::vector<std::pair<const uint8_t *, uint64_t>> gemm_order;
+    size_t order_pos = 0;
     int n_proj = 0, n_qkv = 0;
     ArgmaxScratch argmax{};
     AcceptOut acc{};
@@ -577,6 +582,19 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.flags = flags;
         t.scratch = &s->gemm;
         if (post) t.post = *post;
+        if (s->prefetch_next) {
+            // where this matrix sits in the step's order, and what follows it
+            const auto & order = s->gemm_order;
+            for (size_t k = s->order_pos; k < order.size(); k++)
+                if (order[k].first == w.ptr) {
+                    s->order_pos = k + 1;
+                    if (k + 1 < order.size()) {
+                        t.next_w = order[k + 1].first;
+                        t.next_bytes = order[k + 1].second < s->prefetch_bytes ? order[k + 1].second : s->prefetch_bytes;
+                    }
+                    break;
+                }
+        }
         s->launches += launch_gemm_tiled(s->model->dev, s->stream.s, t);
         return;
     }
@@ -643,6 +661,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     const int conv_dim = m->conv_dim(), inner = c.inner_size, rank = c.time_step_rank, S = c.state_size;
     const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
 
+    s->order_pos = 0;
     mark(s, YUUKA_OP_EMBEDDING);
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
@@ -990,6 +1009,14 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->cfg = sc;
             if (const char * e = getenv("YUUKA_CUDA_NO_GRAPH")) s->use_graphs = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_FUSE_NORM")) s->fuse_post_norm = e[0] == '1';
+            if (const char * e = getenv("YUUKA_CUDA_NO_PREFETCH")) s->prefetch_next = !(e[0] == '1');
+            if (const char * e = getenv("YUUKA_CUDA_PREFETCH_MB")) s->prefetch_bytes = (uint64_t)atoi(e) << 20;
+            for (const LayerW & L : model->layers) {
+                for (const Tensor * t : {&L.proj, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.qk, &L.q, &L.k, &L.v, &L.o,
+                                         &L.gate_up, &L.ffn_gate, &L.ffn_up, &L.ffn_down})
+                    if (t->present() && t->tiled) s->gemm_order.push_back({t->ptr, t->bytes});
+            }
+            if (model->output.tiled) s->gemm_order.push_back({model->output.ptr, model->output.bytes});
             s->stream.dev = model->dev;
             YK_CUDA(cudaStreamCreateWithFlags(&s->stream.s, cudaStreamNonBlocking));
             const int kv_dim = model->kv_dim();

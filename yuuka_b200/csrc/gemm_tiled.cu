@@ -40,6 +40,12 @@ __device__ __forceinline__ void prefetch_l2(const void * p) { asm volatile("pref
 __device__ __forceinline__ void prefetch_l2_range(const uint8_t * base, int bytes, int lane) {
     for (int off = lane * 128; off < bytes; off += 32 * 128) prefetch_l2(base + off);
 }
+// (a & b) | c as one three-input logic instruction
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -362,10 +368,10 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q4_K, NT> {
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
-                        a[h][0] = h2_fma((vg & mask) | kc.magic, s_g, c_g);
-                        a[h][1] = h2_fma((vh & mask) | kc.magic, s_h, c_h);
-                        a[h][2] = h2_fma(((vg >> 8) & mask) | kc.magic, s_g, c_g);
-                        a[h][3] = h2_fma(((vh >> 8) & mask) | kc.magic, s_h, c_h);
+                        a[h][0] = h2_fma(and_or(vg, mask, kc.magic), s_g, c_g);
+                        a[h][1] = h2_fma(and_or(vh, mask, kc.magic), s_h, c_h);
+                        a[h][2] = h2_fma(and_or(vg >> 8, mask, kc.magic), s_g, c_g);
+                        a[h][3] = h2_fma(and_or(vh >> 8, mask, kc.magic), s_h, c_h);
                     }
                     const int k = 2 * j + n;
 #pragma unroll
@@ -395,18 +401,18 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
     // ... merged with the fp16 1024 pattern: ((hb shifted) & bit) | magic is one LOP3
     template <int K, int TGT, bool B13> __device__ static uint32_t hibit(uint32_t hb, uint32_t bit, uint32_t magic) {
         constexpr int from = K + (B13 ? 8 : 0);
-        if constexpr (from >= TGT) return ((hb >> (from - TGT)) & bit) | magic;
-        else return ((hb << (TGT - from)) & bit) | magic;
+        if constexpr (from >= TGT) return and_or(hb >> (from - TGT), bit, magic);
+        else return and_or(hb << (TGT - from), bit, magic);
     }
     template <int K> __device__ static void sub(uint32_t vg, uint32_t vh, uint32_t hg, uint32_t hh, uint32_t s_g, uint32_t c_g,
                                                 uint32_t s_h, uint32_t c_h, uint32_t (&a)[4], const DecodeConsts & kc) {
         constexpr bool hi = (K & 1) != 0;
         constexpr int tgt = hi ? 8 : 4;
         const uint32_t mask = hi ? kc.mf0 : kc.m0f, bit = hi ? kc.h8 : kc.h4;
-        a[0] = h2_fma((vg & mask) | hibit<K, tgt, false>(hg, bit, kc.magic), s_g, c_g);
-        a[1] = h2_fma((vh & mask) | hibit<K, tgt, false>(hh, bit, kc.magic), s_h, c_h);
-        a[2] = h2_fma(((vg >> 8) & mask) | hibit<K, tgt, true>(hg, bit, kc.magic), s_g, c_g);
-        a[3] = h2_fma(((vh >> 8) & mask) | hibit<K, tgt, true>(hh, bit, kc.magic), s_h, c_h);
+        a[0] = h2_fma(and_or(vg, mask, hibit<K, tgt, false>(hg, bit, kc.magic)), s_g, c_g);
+        a[1] = h2_fma(and_or(vh, mask, hibit<K, tgt, false>(hh, bit, kc.magic)), s_h, c_h);
+        a[2] = h2_fma(and_or(vg >> 8, mask, hibit<K, tgt, true>(hg, bit, kc.magic)), s_g, c_g);
+        a[3] = h2_fma(and_or(vh >> 8, mask, hibit<K, tgt, true>(hh, bit, kc.magic)), s_h, c_h);
     }
     template <int K>
     __device__ static void subblock(const typename C::Regs & r, const uint8_t * tg, const uint8_t * th,
@@ -495,10 +501,10 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
-                        a[h][0] = h2_fma((vg & qm) | (((hg[h] << lsh) & hm) | kc.magic), eg.x, eg.y);
-                        a[h][1] = h2_fma((vh & qm) | (((hh[h] << lsh) & hm) | kc.magic), eh.x, eh.y);
-                        a[h][2] = h2_fma(((vg >> 8) & qm) | (((hg[h] >> rsh) & hm) | kc.magic), eg.x, eg.y);
-                        a[h][3] = h2_fma(((vh >> 8) & qm) | (((hh[h] >> rsh) & hm) | kc.magic), eh.x, eh.y);
+                        a[h][0] = h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), eg.x, eg.y);
+                        a[h][1] = h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), eh.x, eh.y);
+                        a[h][2] = h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), eg.x, eg.y);
+                        a[h][3] = h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), eh.x, eh.y);
                     }
 #pragma unroll
                     for (int jt = 0; jt < NT; jt++) {
@@ -602,6 +608,10 @@ struct TParams {
     const GemmSegment * segments;
     size_t expert_stride;
     const int32_t * row_index;
+    // optional: the matrix the next GEMM of the step will stream; its first bytes are asked into L2
+    // while this kernel drains and the small kernels in between run
+    const uint8_t * next_w;
+    uint32_t next_lines;  // 128-byte lines
 };
 
 // rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
@@ -870,6 +880,12 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         }
     }
 
+    if (p.next_w) {
+        const uint32_t first = ((blockIdx.y * gridDim.x + blockIdx.x) * (TW * 32) + threadIdx.x);
+        const uint32_t step = gridDim.x * gridDim.y * (TW * 32);
+        for (uint32_t line = first; line < p.next_lines; line += step) prefetch_l2(p.next_w + (size_t)line * 128);
+    }
+
     if (p.post_norm_w) {
         // every CTA has written (and, with a K split across CTAs, finalised) its rows before it arrives here
         __threadfence();
@@ -1130,6 +1146,10 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     p.n_groups = pl.n_groups;
     p.partial = a.scratch ? a.scratch->partial : nullptr;
     p.counters = a.scratch ? a.scratch->counters : nullptr;
+    if (a.next_w && m0 + 32 >= a.rows) {
+        p.next_w = a.next_w;
+        p.next_lines = (uint32_t)(a.next_bytes / 128);
+    }
     if (a.post.norm_w) {
         p.post_norm_w = a.post.norm_w;
         p.post_eps = a.post.eps;

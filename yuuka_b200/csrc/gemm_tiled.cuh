@@ -84,6 +84,8 @@ struct TiledGemmArgs {
     uint32_t flags = 0;
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     GemmPostNorm post;
+    const uint8_t * next_w = nullptr;  // optional L2 prefetch hint: the next matrix to be streamed (mma route)
+    uint64_t next_bytes = 0;
 };
 
 int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a);

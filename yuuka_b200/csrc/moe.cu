@@ -34,15 +34,38 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RoutePar
     const float * src = p.xn + (int64_t)r * p.hidden;
     for (int i = threadIdx.x; i < p.hidden; i += ROUTE_THREADS) x[i] = src[i];
     __syncthreads();
-    for (int e = warp; e <= p.experts; e += ROUTE_THREADS / 32) {
-        const float * w = e < p.experts ? p.router + (int64_t)e * p.hidden : p.sh_gate;  // the last one is the shared gate
-        float acc = 0.0f;
-        for (int i = lane; i < p.hidden; i += 32) acc = fmaf(w[i], x[i], acc);
+    // four experts per warp pass, 16 bytes per lane and load: enough independent loads in flight to
+    // cover the L2 latency (index `experts` is the shared-expert gate vector)
+    const int n_vec = p.experts + 1;
+    for (int e0 = warp * 4; e0 < n_vec; e0 += (ROUTE_THREADS / 32) * 4) {
+        const float * w[4];
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) {
-            if (e < p.experts) logit[e] = acc;
-            else p.shared_gate[r] = 1.0f / (1.0f + (float)exp((double)-acc));
+        for (int q = 0; q < 4; q++) {
+            const int e = min(e0 + q, n_vec - 1);
+            w[q] = e < p.experts ? p.router + (int64_t)e * p.hidden : p.sh_gate;
+        }
+#pragma unroll 2
+        for (int i = lane * 4; i < p.hidden; i += 128) {
+            const float4 xv = *reinterpret_cast<const float4 *>(x + i);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 wv = __ldg(reinterpret_cast<const float4 *>(w[q] + i));
+                acc[q] = fmaf(wv.x, xv.x, acc[q]);
+                acc[q] = fmaf(wv.y, xv.y, acc[q]);
+                acc[q] = fmaf(wv.z, xv.z, acc[q]);
+                acc[q] = fmaf(wv.w, xv.w, acc[q]);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], o);
+            const int e = e0 + q;
+            if (lane == 0 && e < n_vec) {
+                if (e < p.experts) logit[e] = acc[q];
+                else p.shared_gate[r] = 1.0f / (1.0f + (float)exp((double)-acc[q]));
+            }
         }
     }
     __syncthreads();
@@ -91,16 +114,27 @@ struct GroupParams {
     GemmSegment * segments;  // [max_segments]
 };
 
-// One CTA. Stable counting sort of the pairs by expert, cut into segments of at most 8 rows.
+// One CTA. Stable counting sort of the pairs by expert, cut into segments of at most 8 rows. The
+// expert ids are staged in shared memory first (when they fit): the scans below would otherwise
+// wait out a global-memory round trip per pair, because the stores in the loop keep the compiler
+// from batching the loads.
+constexpr int GROUP_SMEM_PAIRS = 8192;
+
 __global__ void __launch_bounds__(ROUTE_THREADS) moe_group_kernel(const GroupParams p) {
     pdl_entry();
     __shared__ int count[ROUTE_MAX_EXPERTS];
     __shared__ int pair_off[ROUTE_MAX_EXPERTS];
     __shared__ int seg_off[ROUTE_MAX_EXPERTS];
+    __shared__ int32_t ids_s[GROUP_SMEM_PAIRS];
     __shared__ int total_segments;
+    const bool staged = p.pairs <= GROUP_SMEM_PAIRS;
+    if (staged)
+        for (int i = threadIdx.x; i < p.pairs; i += ROUTE_THREADS) ids_s[i] = p.ids[i];
+    __syncthreads();
+    const int32_t * ids = staged ? ids_s : p.ids;
     for (int e = threadIdx.x; e < p.experts; e += ROUTE_THREADS) {
         int c = 0;
-        for (int i = 0; i < p.pairs; i++) c += p.ids[i] == e;
+        for (int i = 0; i < p.pairs; i++) c += ids[i] == e;
         count[e] = c;
     }
     __syncthreads();
@@ -119,7 +153,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_group_kernel(const GroupPar
         int j = 0;
         const int c = count[e];
         for (int i = 0; i < p.pairs && j < c; i++) {
-            if (p.ids[i] != e) continue;
+            if (ids[i] != e) continue;
             const int pos = pair_off[e] + j;
             p.pos_of_pair[i] = pos;
             p.row_of_pos[pos] = i / p.used;
@@ -140,6 +174,7 @@ int moe_max_segments(int pairs, int experts) {
 
 void launch_moe_route(cudaStream_t s, const float * xn, const float * router, const float * sh_gate, int hidden, int experts,
                       int used, int rows, int32_t * ids, float * weights, float * shared_gate) {
+    YK_REQUIRE(hidden % 4 == 0, YUUKA_ERR_UNSUPPORTED, "moe: hidden size %d is not a multiple of 4", hidden);
     YK_REQUIRE(experts <= ROUTE_MAX_EXPERTS && used <= 32 && used <= experts, YUUKA_ERR_UNSUPPORTED,
                "moe: %d experts / %d used exceeds the router kernel's limits (%d / 32)", experts, used, ROUTE_MAX_EXPERTS);
     RouteParams p{xn, router, sh_gate, hidden, experts, used, ids, weights, shared_gate};
