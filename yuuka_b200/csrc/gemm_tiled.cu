@@ -19,6 +19,8 @@
 //
 // fp32 route (1-2 rows, tight-tolerance checks): same loads, the reference's
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
+#include <cstdlib>
+
 #include "gemm_tiled.cuh"
 #include "quant.cuh"
 #include "xprep.cuh"
@@ -577,6 +579,10 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
 // mma kernel
 
 __device__ int g_gemm_wait_expired = 0;
+
+}  // namespace yk
+#include "gemm_umma.cuh"
+namespace yk {
 
 struct TParams {
     DecodeConsts kc;
@@ -1224,6 +1230,50 @@ int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, con
     return 1;
 }
 
+// Rows from which the tensor-memory route takes over from 32-row passes of the register-fed kernel.
+constexpr int UMMA_MIN_ROWS = 48;
+
+static bool umma_enabled() {
+    static const bool on = [] {
+        const char * e = getenv("YUUKA_CUDA_NO_UMMA");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+template <int DT>
+static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, const __half * xh) {
+    auto kern = gemm_umma_kernel<DT>;
+    int launches = 0;
+    for (int m0 = 0; m0 < a.rows; m0 += UM_MAX_N) {
+        const int m = a.rows - m0 < UM_MAX_N ? a.rows - m0 : UM_MAX_N;
+        UParams p{};
+        p.kc = decode_consts(DT);
+        p.w = a.w;
+        p.N = a.n_out;
+        p.nsb = a.n_in / 256;
+        p.xh = xh + (int64_t)m0 * a.n_in;
+        p.M = m;
+        p.npad = (m + 15) / 16 * 16;
+        p.out = a.out + (int64_t)m0 * a.ldo;
+        p.ldo = a.ldo;
+        p.accumulate = (a.flags & YUUKA_GEMM_ACCUMULATE) ? 1 : 0;
+        p.tmem_cols = 32;
+        while ((int)p.tmem_cols < p.npad) p.tmem_cols *= 2;
+        // instruction descriptor: D f32, A and B f16, both K-major, N = npad, M = 128
+        p.idesc = (1u << 4) | ((uint32_t)(p.npad >> 3) << 17) | ((uint32_t)(UM_ROWS >> 4) << 24);
+        const size_t smem = (size_t)UM_STAGES * (UM_A_BYTES + (size_t)p.npad * UM_KC * 2) + (size_t)TW * Codec<DT>::TAB;
+        YK_REQUIRE(smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_INTERNAL, "umma gemm: stage buffers do not fit shared memory");
+        YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int n_blocks = (a.n_out + UM_ROWS - 1) / UM_ROWS;
+        const int grid = n_blocks < dev->sm_count ? n_blocks : dev->sm_count;
+        launch_k(kern, grid, TW * 32, smem, s, p);
+        YK_CUDA(cudaGetLastError());
+        launches++;
+    }
+    return launches;
+}
+
 template <int DT>
 static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a) {
     int launches = 0;
@@ -1241,6 +1291,7 @@ static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGe
         xs16 = a.scratch->xs16;
         launches++;
     }
+    if (a.rows >= UMMA_MIN_ROWS && umma_enabled() && !a.post.norm_w) return launches + launch_umma_dt<DT>(dev, s, a, xh);
     for (int m0 = 0; m0 < a.rows; m0 += 32) {
         const int m = a.rows - m0 < 32 ? a.rows - m0 : 32;
         TPlan pl;

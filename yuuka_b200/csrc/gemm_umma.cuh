@@ -1,0 +1,361 @@
+// Large-M route of the tiled quantized GEMM: tcgen05 tensor cores with the
+// accumulator in tensor memory. Included by gemm_tiled.cu (it uses that file's
+// record codecs and header decoders).
+//
+// From about 48 rows on, re-decoding the packed weights for every 32-row pass of
+// the register-fed MMA kernel costs more than the arithmetic. Here a CTA owns
+// 128 weight rows and up to 256 activation rows: eight warps decode one 16-row
+// tile each into fp16 (s * q - min), 64 columns at a time, and store it into a
+// shared-memory stage in the K-major core-matrix layout (8 rows x 16 bytes,
+// no swizzle); the matching 64 columns of the prepared activations arrive in the
+// same stage by cp.async. One thread then issues four tcgen05.mma (M = 128,
+// N = rows padded to 16, K = 16 each) that accumulate D[weight row][activation
+// row] in tensor memory, and tcgen05.commit releases the stage through an
+// mbarrier when they have read it. Three stages let decoding run ahead of the
+// tensor pipe. The epilogue reads the accumulator with tcgen05.ld (lane = weight
+// row, column = activation row) and writes out[row][n], 128 bytes per warp store.
+//
+// Every mbarrier wait is bounded; on expiry the device error word is set, the
+// kernel carries on (results are then garbage), frees its tensor memory and
+// returns.
+#pragma once
+
+namespace yk {
+
+constexpr int UM_ROWS = 128;   // weight rows per CTA = UMMA M
+constexpr int UM_KC = 64;      // columns per stage
+constexpr int UM_STAGES = 3;
+constexpr int UM_MAX_N = 256;  // activation rows per launch = UMMA N
+constexpr int UM_A_BYTES = UM_ROWS * UM_KC * 2;  // 16 KB
+
+struct UParams {
+    DecodeConsts kc;
+    const uint8_t * w;
+    int N, nsb;           // weight rows, superblocks per row
+    const __half * xh;    // prepared activations [M][nsb * 256]
+    int M, npad;          // activation rows, padded to a multiple of 16
+    float * out;
+    int64_t ldo;
+    int accumulate;
+    uint32_t tmem_cols;   // power of two >= npad, >= 32
+    uint32_t idesc;
+};
+
+// ---- scaled fragments of one 32-column sub-block K of a record, as the register-fed kernel forms
+// them: a[h][0], a[h][2] = row g, elements 8t + 4h + {0,1}, {2,3}; a[h][1], a[h][3] = row g + 8.
+// `mg`, `mh` receive the half2 that still has to be added (-min, or -32 * scale for Q6_K).
+template <int DT> struct SubBlock;
+
+template <> struct SubBlock<YUUKA_DTYPE_Q4_K> {
+    using C = Codec<YUUKA_DTYPE_Q4_K>;
+    template <int K>
+    __device__ static void frag(const typename C::Regs & r, int lane, const uint8_t * tab, const DecodeConsts & kc,
+                                uint32_t (&a)[2][4], uint32_t & mg, uint32_t & mh) {
+        constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
+        const int g = lane >> 2;
+        const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+        const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
+        const uint4 sg = reinterpret_cast<const uint4 *>(tab + g * C::SCL_STRIDE)[j];
+        const uint4 sh = reinterpret_cast<const uint4 *>(tab + (g + 8) * C::SCL_STRIDE)[j];
+        const uint32_t mask = n ? kc.mf0 : kc.m0f;
+        const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
+            a[h][0] = h2_fma(and_or(vg, mask, kc.magic), s_g, c_g);
+            a[h][1] = h2_fma(and_or(vh, mask, kc.magic), s_h, c_h);
+            a[h][2] = h2_fma(and_or(vg >> 8, mask, kc.magic), s_g, c_g);
+            a[h][3] = h2_fma(and_or(vh >> 8, mask, kc.magic), s_h, c_h);
+        }
+        mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE)[K];
+        mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE)[K];
+    }
+};
+
+template <> struct SubBlock<YUUKA_DTYPE_Q5_K> {
+    using C = Codec<YUUKA_DTYPE_Q5_K>;
+    template <int K>
+    __device__ static void frag(const typename C::Regs & r, int lane, const uint8_t * tab, const DecodeConsts & kc,
+                                uint32_t (&a)[2][4], uint32_t & mg, uint32_t & mh) {
+        constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
+        const int g = lane >> 2;
+        const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+        const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
+        const uint32_t hg[2] = {r.qh.x, r.qh.y}, hh[2] = {r.qh.z, r.qh.w};
+        const uint4 sg = reinterpret_cast<const uint4 *>(tab + g * C::SCL_STRIDE)[j];
+        const uint4 sh = reinterpret_cast<const uint4 *>(tab + (g + 8) * C::SCL_STRIDE)[j];
+        const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            Mma<YUUKA_DTYPE_Q5_K, 1>::template sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h], kc);
+        mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE)[K];
+        mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE)[K];
+    }
+};
+
+template <> struct SubBlock<YUUKA_DTYPE_Q6_K> {
+    using C = Codec<YUUKA_DTYPE_Q6_K>;
+    template <int K>
+    __device__ static void frag(const typename C::Regs & r, int lane, const uint8_t * tab, const DecodeConsts & kc,
+                                uint32_t (&a)[2][4], uint32_t & mg, uint32_t & mh) {
+        constexpr int n6 = K >> 2, nib = (K >> 1) & 1, hsel = K & 1;
+        constexpr int lsh = 4 - 2 * hsel, rsh = 4 + 2 * hsel;
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t lg[4] = {r.ql[n6].x, r.ql[n6].y, r.ql[n6].z, r.ql[n6].w};
+        const uint32_t lh[4] = {r.ql[2 + n6].x, r.ql[2 + n6].y, r.ql[2 + n6].z, r.ql[2 + n6].w};
+        const uint32_t hg[2] = {n6 ? r.qh[0].z : r.qh[0].x, n6 ? r.qh[0].w : r.qh[0].y};
+        const uint32_t hh[2] = {n6 ? r.qh[1].z : r.qh[1].x, n6 ? r.qh[1].w : r.qh[1].y};
+        const int s16 = 2 * K + (t >> 1);  // the 16-element group this lane's eight elements belong to
+        const uint2 eg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE)[s16];
+        const uint2 eh = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE)[s16];
+        const uint32_t qm = nib ? kc.mf0 : kc.m0f, hm = nib ? kc.h8 : kc.h4;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
+            a[h][0] = h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), eg.x, eg.y);
+            a[h][1] = h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), eh.x, eh.y);
+            a[h][2] = h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), eg.x, eg.y);
+            a[h][3] = h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), eh.x, eh.y);
+        }
+        mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE)[s16];
+        mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE)[s16];
+    }
+};
+
+template <> struct SubBlock<YUUKA_DTYPE_Q8_0> {
+    using C = Codec<YUUKA_DTYPE_Q8_0>;
+    template <int K>
+    __device__ static void frag(const typename C::Regs & r, int lane, const uint8_t * tab, const DecodeConsts & kc,
+                                uint32_t (&a)[2][4], uint32_t & mg, uint32_t & mh) {
+        (void)kc;
+        constexpr int kk = K >> 1, kl = K & 1;
+        const int g = lane >> 2;
+        const uint32_t qg[4] = {r.q[kk].x, r.q[kk].y, r.q[kk].z, r.q[kk].w};
+        const uint32_t qh[4] = {r.q[4 + kk].x, r.q[4 + kk].y, r.q[4 + kk].z, r.q[4 + kk].w};
+        const uint32_t sg = reinterpret_cast<const uint32_t *>(tab + g * C::SCL_STRIDE)[K];
+        const uint32_t sh = reinterpret_cast<const uint32_t *>(tab + (g + 8) * C::SCL_STRIDE)[K];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t vg = qg[2 * kl + h] ^ 0x80808080u, vh = qh[2 * kl + h] ^ 0x80808080u;
+            a[h][0] = h2_mul(h2_sub(bytes02_h2(vg), H2_1152), sg);
+            a[h][1] = h2_mul(h2_sub(bytes02_h2(vh), H2_1152), sh);
+            a[h][2] = h2_mul(h2_sub(bytes13_h2(vg), H2_1152), sg);
+            a[h][3] = h2_mul(h2_sub(bytes13_h2(vh), H2_1152), sh);
+        }
+        mg = 0u;
+        mh = 0u;
+    }
+};
+
+__device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// K-major, no swizzle: core matrix (8 rows x 16 bytes) at rowgroup * 1024 + kchunk * 128 inside a stage
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) |
+           (1ull << 46);
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    }
+    return ok != 0;
+}
+
+template <int DT, int K>
+__device__ __forceinline__ void umma_store_subblock(const typename Codec<DT>::Regs & r, int lane, const uint8_t * tab,
+                                                    const DecodeConsts & kc, uint8_t * a_stage, int warp, int kblk_in_stage) {
+    uint32_t a[2][4], mg, mh;
+    SubBlock<DT>::template frag<K>(r, lane, tab, kc, a, mg, mh);
+    const int g = lane >> 2, t = lane & 3;
+    const int kchunk = 4 * kblk_in_stage + t;  // eight columns each
+    uint4 vg = make_uint4(a[0][0], a[0][2], a[1][0], a[1][2]);
+    uint4 vh = make_uint4(a[0][1], a[0][3], a[1][1], a[1][3]);
+    if (DT != YUUKA_DTYPE_Q8_0) {
+        vg = make_uint4(h2_add(vg.x, mg), h2_add(vg.y, mg), h2_add(vg.z, mg), h2_add(vg.w, mg));
+        vh = make_uint4(h2_add(vh.x, mh), h2_add(vh.y, mh), h2_add(vh.z, mh), h2_add(vh.w, mh));
+    }
+    *reinterpret_cast<uint4 *>(a_stage + (2 * warp) * 1024 + kchunk * 128 + g * 16) = vg;
+    *reinterpret_cast<uint4 *>(a_stage + (2 * warp + 1) * 1024 + kchunk * 128 + g * 16) = vh;
+}
+
+template <int DT, int Q>
+__device__ __forceinline__ void umma_store_chunk(const typename Codec<DT>::Regs & r, int lane, const uint8_t * tab,
+                                                 const DecodeConsts & kc, uint8_t * a_stage, int warp) {
+    umma_store_subblock<DT, 2 * Q>(r, lane, tab, kc, a_stage, warp, 0);
+    umma_store_subblock<DT, 2 * Q + 1>(r, lane, tab, kc, a_stage, warp, 1);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) {
+    using C = Codec<DT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t empty_bar[UM_STAGES];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t b_bytes = (uint32_t)p.npad * (UM_KC * 2);
+    const uint32_t stage_bytes = UM_A_BYTES + b_bytes;
+    uint8_t * tabs = smem + (size_t)UM_STAGES * stage_bytes;
+    uint8_t * tab = tabs + warp * C::TAB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < UM_STAGES; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&empty_bar[s])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&done_bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         (uint32_t)__cvta_generic_to_shared(&tmem_slot)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t taddr = tmem_slot;
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    const DecodeConsts kc = p.kc;
+
+    const int n_tiles = (p.N + 15) >> 4;
+    const int n_blocks = (p.N + UM_ROWS - 1) / UM_ROWS;
+    const size_t rec_row = (size_t)p.nsb * C::REC;
+    const int K = p.nsb * 256;
+    bool expired = false;
+
+    pdl_trigger();
+    typename C::Regs cur, nxt;
+    {
+        const int rt = min(blockIdx.x * (UM_ROWS / 16) + warp, n_tiles - 1);
+        C::load(p.w + rt * rec_row, lane, cur);
+    }
+    pdl_wait();
+
+    uint32_t chunk = 0;  // chunks issued by this CTA so far (stage = chunk % UM_STAGES)
+    uint32_t block_iter = 0;
+    for (int rb = blockIdx.x; rb < n_blocks; rb += gridDim.x, block_iter++) {
+        const int rt = min(rb * (UM_ROWS / 16) + warp, n_tiles - 1);
+        const uint8_t * tile = p.w + rt * rec_row;
+        for (int sb = 0; sb < p.nsb; sb++) {
+            if (sb + 1 < p.nsb) {
+                C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
+            } else if (rb + (int)gridDim.x < n_blocks) {
+                const int rtn = min((rb + (int)gridDim.x) * (UM_ROWS / 16) + warp, n_tiles - 1);
+                C::load(p.w + rtn * rec_row, lane, nxt);
+            }
+            Mma<DT, 1>::header(cur, lane, tab);
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint32_t stage = chunk % UM_STAGES, use = chunk / UM_STAGES;
+                uint8_t * a_stage = smem + (size_t)stage * stage_bytes;
+                uint8_t * b_stage = a_stage + UM_A_BYTES;
+                // the tensor pipe must have finished reading this stage's previous contents
+                if (use > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[stage]), (use - 1) & 1)) expired = true;
+                // activations: columns [sb * 256 + q * 64, + 64) of every row, 16 bytes per copy
+                const int col0 = sb * 256 + q * UM_KC;
+                for (int i = threadIdx.x; i < p.npad * 8; i += TW * 32) {
+                    const int kch = i / p.npad, tok = i - kch * p.npad;
+                    const __half * src = p.xh + (size_t)min(tok, p.M - 1) * K + col0 + kch * 8;
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(b_stage + (tok >> 3) * 1024 + kch * 128 + (tok & 7) * 16);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                // weights: this warp's 16 rows x 64 columns
+                if (q == 0) umma_store_chunk<DT, 0>(cur, lane, tab, kc, a_stage, warp);
+                else if (q == 1) umma_store_chunk<DT, 1>(cur, lane, tab, kc, a_stage, warp);
+                else if (q == 2) umma_store_chunk<DT, 2>(cur, lane, tab, kc, a_stage, warp);
+                else umma_store_chunk<DT, 3>(cur, lane, tab, kc, a_stage, warp);
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc(smem_base + stage * stage_bytes);
+                    const uint64_t db = umma_desc(smem_base + stage * stage_bytes + UM_A_BYTES);
+#pragma unroll
+                    for (int j = 0; j < UM_KC / 16; j++) {
+                        const uint32_t accumulate = (sb > 0 || q > 0 || j > 0) ? 1u : 0u;
+                        // 16 columns = two core matrices = 256 bytes further along K
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                            :
+                            : "r"(taddr), "l"(da + (uint64_t)(j * 16)), "l"(db + (uint64_t)(j * 16)), "r"(p.idesc), "r"(accumulate),
+                              "r"(0u)
+                            : "memory");
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                     (uint32_t)__cvta_generic_to_shared(&empty_bar[stage]))
+                                 : "memory");
+                }
+                chunk++;
+            }
+            __syncwarp();
+            cur = nxt;
+        }
+        // ---- epilogue of this block of 128 weight rows ----
+        if (threadIdx.x == 0)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(&done_bar))
+                         : "memory");
+        if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&done_bar), block_iter & 1)) expired = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
+            // warp w reads TMEM lanes 32 * (w % 4) ..; warps 0-3 take the even 32-column groups, 4-7 the odd ones
+            const int quad = warp & 3;
+            const int n = rb * UM_ROWS + quad * 32 + lane;
+            for (int c0 = (warp >> 2) * 32; c0 < p.npad; c0 += 64) {
+                uint32_t v[32];
+                const uint32_t src = taddr + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(src)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int tok = c0 + i;
+                        if (tok < p.M) {
+                            float * dst = p.out + (int64_t)tok * p.ldo + n;
+                            const float val = __uint_as_float(v[i]);
+                            *dst = p.accumulate ? *dst + val : val;
+                        }
+                    }
+                }
+            }
+        }
+        // the next block overwrites the accumulator: everybody must have read it
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    if (expired) atomicExch(&g_gemm_wait_expired, 2);
+    // every MMA this CTA issued has completed (the last done_bar wait), nothing reads TMEM any more
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(p.tmem_cols) : "memory");
+}
+
+}  // namespace yk
