@@ -254,7 +254,7 @@ YUUKA_API yuuka_status yuuka_session_forward(yuuka_session * s, int32_t seq, con
 
 /* Acceptance modes of a verify step. */
 #define YUUKA_ACCEPT_GREEDY 0u    /* engine/speculative.go:193-202 with argmaxLogit :263-271 */
-#define YUUKA_ACCEPT_REJECTION 1u /* not in the reference; rule documented in DESIGN.md */
+#define YUUKA_ACCEPT_REJECTION 1u /* not in the reference; the rule is stated above rejection_walk_kernel (accept.cu) */
 #define YUUKA_ACCEPT_NONE 2u      /* run and commit nothing: logits only */
 
 /* One verify step over `batch` sequences (seq ids 0..batch-1 of the session).

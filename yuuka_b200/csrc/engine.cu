@@ -1124,7 +1124,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->attn_partial_floats = (size_t)N * c.heads * (4 * model->dev->sm_count / c.kv_heads + 1 + B) * (c.head_dim + 2);
             s->attn_partial = dalloc<float>(s->attn_partial_floats, s->owned, false);
             // split-K scratch for every matrix shape of the step
-            for (int rows : {R < 32 ? R : 32, 1}) {
+            for (int rows : {R < 32 ? R : 32, 1, R < 256 ? R : 256}) {
                 for (const LayerW & L : model->layers) {
                     for (const Tensor * t : {&L.q, &L.k, &L.v, &L.o, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.ffn_gate,
                                              &L.ffn_up, &L.ffn_down, &L.proj, &L.qk, &L.gate_up, &L.sh_gate, &L.sh_up,

@@ -19,7 +19,10 @@
 //
 // fp32 route (1-2 rows, tight-tolerance checks): same loads, the reference's
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
+#include <cuda.h>
+
 #include <cstdlib>
+#include <cstring>
 
 #include "gemm_tiled.cuh"
 #include "quant.cuh"
@@ -1095,7 +1098,9 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
     int kchunks = 1;
     const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
-    const size_t budget = half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin;
+    static const bool full_smem = [] { const char * e = getenv("YUUKA_GEMM_FULL_SMEM"); return e && e[0] == '1'; }();
+    const size_t budget = full_smem ? dev->prop.sharedMemPerBlockOptin - 1024
+                                    : (half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin);
     while (true) {
         int nsb_chunk = (nsb + kchunks - 1) / kchunks;
         bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks) <= budget;
@@ -1112,11 +1117,39 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     pl.grid_x = pl.n_groups < per ? pl.n_groups : per;
 }
 
+// Rows from which the tensor-memory route takes over from 32-row passes of the register-fed kernel.
+constexpr int UMMA_MIN_ROWS = 48;
+
+static bool umma_enabled() {
+    static const bool on = [] {
+        const char * e = getenv("YUUKA_CUDA_NO_UMMA");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+// K splits of the tensor-memory route: enough CTAs to fill the machine when the matrix has few
+// 128-row blocks, at least two superblocks each.
+static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in) {
+    const int n_blocks = (n_out + UM_ROWS - 1) / UM_ROWS, nsb = n_in / 256;
+    int ks = dev->sm_count / n_blocks;
+    if (ks > nsb / 2) ks = nsb / 2;
+    if (ks > 16) ks = 16;
+    return ks < 1 ? 1 : ks;
+}
+
 void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int rows, int n_out, int n_in,
                              uint64_t * partial_floats, int * counters) {
     *partial_floats = 0;
     *counters = 0;
     if (!tiled_supported(w_dtype, n_in)) return;
+    if (rows >= UMMA_MIN_ROWS) {
+        const int ks = umma_ksplit(dev, n_out, n_in);
+        if (ks > 1) {
+            *partial_floats = (uint64_t)ks * (rows < UM_MAX_N ? rows : UM_MAX_N) * n_out;
+            *counters = (n_out + UM_ROWS - 1) / UM_ROWS;
+        }
+    }
     for (int m : {rows < 32 ? rows : 32, 32 < rows ? rows % 32 : 0}) {
         if (m <= 0) continue;
         TPlan pl;
@@ -1230,23 +1263,52 @@ int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, con
     return 1;
 }
 
-// Rows from which the tensor-memory route takes over from 32-row passes of the register-fed kernel.
-constexpr int UMMA_MIN_ROWS = 48;
-
-static bool umma_enabled() {
-    static const bool on = [] {
-        const char * e = getenv("YUUKA_CUDA_NO_UMMA");
-        return !(e && e[0] == '1');
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                      const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static const TensorMapEncodeFn fn = [] {
+        const char * e = getenv("YUUKA_CUDA_NO_TMA");
+        if (e && e[0] == '1') return (TensorMapEncodeFn) nullptr;
+        void * f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return (TensorMapEncodeFn) nullptr;
+        }
+        return (TensorMapEncodeFn)f;
     }();
-    return on;
+    return fn;
+}
+
+// 2-D map over prepared activations [m][k] (fp16, row-major): boxes of 64 columns x npad rows, 128-byte swizzle.
+static bool make_x_map(CUtensorMap * map, const __half * xh, int m, int k, int npad) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc || ((uintptr_t)xh & 15) != 0) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
+    const cuuint64_t gstride[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)UM_KC, (cuuint32_t)npad};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)xh, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int DT>
 static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, const __half * xh) {
-    auto kern = gemm_umma_kernel<DT>;
     int launches = 0;
-    for (int m0 = 0; m0 < a.rows; m0 += UM_MAX_N) {
-        const int m = a.rows - m0 < UM_MAX_N ? a.rows - m0 : UM_MAX_N;
+    const int n_blocks = (a.n_out + UM_ROWS - 1) / UM_ROWS;
+    const int ksplit = umma_ksplit(dev, a.n_out, a.n_in);
+    // rows per launch: 256 with tensor-map copies; the padded cp.async stages are larger, so fewer fit
+    const bool want_tma = tensor_map_encoder() != nullptr;
+    int max_n = UM_MAX_N;
+    while (!want_tma && max_n > 16 &&
+           (size_t)UM_STAGES * (UM_A_BYTES + (size_t)(max_n / 8) * UM_B_SBO) + (size_t)TW * Codec<DT>::TAB + 1024 >
+               dev->prop.sharedMemPerBlockOptin)
+        max_n -= 16;
+    for (int m0 = 0; m0 < a.rows; m0 += max_n) {
+        const int m = a.rows - m0 < max_n ? a.rows - m0 : max_n;
         UParams p{};
         p.kc = decode_consts(DT);
         p.w = a.w;
@@ -1262,12 +1324,25 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         while ((int)p.tmem_cols < p.npad) p.tmem_cols *= 2;
         // instruction descriptor: D f32, A and B f16, both K-major, N = npad, M = 128
         p.idesc = (1u << 4) | ((uint32_t)(p.npad >> 3) << 17) | ((uint32_t)(UM_ROWS >> 4) << 24);
-        const size_t smem = (size_t)UM_STAGES * (UM_A_BYTES + (size_t)p.npad * UM_KC * 2) + (size_t)TW * Codec<DT>::TAB;
+        if (ksplit > 1) {
+            YK_REQUIRE(a.scratch && a.scratch->partial_floats >= (uint64_t)ksplit * m * a.n_out &&
+                           a.scratch->counter_count >= n_blocks,
+                       YUUKA_ERR_INTERNAL, "umma gemm: split-K scratch is too small");
+            p.partial = a.scratch->partial;
+            p.counters = a.scratch->counters;
+        }
+        alignas(64) CUtensorMap xmap;
+        memset(&xmap, 0, sizeof(xmap));
+        const bool tma = want_tma && make_x_map(&xmap, p.xh, m, a.n_in, p.npad);
+        YK_REQUIRE(tma || !want_tma, YUUKA_ERR_INTERNAL, "umma gemm: the tensor map of the activations could not be encoded");
+        const size_t b_bytes = tma ? (size_t)p.npad * 128 : (size_t)(p.npad / 8) * UM_B_SBO;
+        const size_t smem = (size_t)UM_STAGES * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
         YK_REQUIRE(smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_INTERNAL, "umma gemm: stage buffers do not fit shared memory");
+        auto kern = tma ? gemm_umma_kernel<DT, true> : gemm_umma_kernel<DT, false>;
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        const int n_blocks = (a.n_out + UM_ROWS - 1) / UM_ROWS;
-        const int grid = n_blocks < dev->sm_count ? n_blocks : dev->sm_count;
-        launch_k(kern, grid, TW * 32, smem, s, p);
+        const int per_split = dev->sm_count / ksplit > 0 ? dev->sm_count / ksplit : 1;
+        dim3 grid(n_blocks < per_split ? n_blocks : per_split, ksplit);
+        launch_k(kern, grid, TW * 32, smem, s, p, xmap);
         YK_CUDA(cudaGetLastError());
         launches++;
     }

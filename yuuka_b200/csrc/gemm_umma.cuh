@@ -24,9 +24,15 @@ namespace yk {
 
 constexpr int UM_ROWS = 128;   // weight rows per CTA = UMMA M
 constexpr int UM_KC = 64;      // columns per stage
-constexpr int UM_STAGES = 3;
+constexpr int UM_STAGES = 4;
+constexpr int UM_AHEAD = 2;    // chunks of activations in flight ahead of the decode
 constexpr int UM_MAX_N = 256;  // activation rows per launch = UMMA N
 constexpr int UM_A_BYTES = UM_ROWS * UM_KC * 2;  // 16 KB
+// Activation stage: core matrices 144 bytes apart along K (16 bytes of padding each), so that the eight
+// 16-byte pieces of one row, copied by eight neighbouring lanes from 128 contiguous global bytes,
+// land in different banks.
+constexpr int UM_B_LBO = 144;
+constexpr int UM_B_SBO = 8 * UM_B_LBO;  // one group of eight rows
 
 struct UParams {
     DecodeConsts kc;
@@ -39,7 +45,16 @@ struct UParams {
     int accumulate;
     uint32_t tmem_cols;   // power of two >= npad, >= 32
     uint32_t idesc;
+    float * partial;      // [gridDim.y][M][N] when K is split across CTAs
+    int * counters;       // one per block of 128 weight rows, zero between launches
 };
+
+// K-major, 128-byte swizzle: rows of 64 halves (128 bytes), eight rows per 1024-byte atom, as a tensor-map
+// copy with CU_TENSOR_MAP_SWIZZLE_128B lays them out. 16 columns further along K = 32 bytes.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)1u << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
 
 // ---- scaled fragments of one 32-column sub-block K of a record, as the register-fed kernel forms
 // them: a[h][0], a[h][2] = row g, elements 8t + 4h + {0,1}, {2,3}; a[h][1], a[h][3] = row g + 8.
@@ -154,9 +169,8 @@ __device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b) {
 }
 
 // K-major, no swizzle: core matrix (8 rows x 16 bytes) at rowgroup * 1024 + kchunk * 128 inside a stage
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) |
-           (1ull << 46);
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo = 128u, uint32_t sbo = 1024u) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -195,22 +209,31 @@ __device__ __forceinline__ void umma_store_chunk(const typename Codec<DT>::Regs 
     umma_store_subblock<DT, 2 * Q + 1>(r, lane, tab, kc, a_stage, warp, 1);
 }
 
-template <int DT>
-__global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) {
+// TMA: the activation stage is filled by one cp.async.bulk.tensor per chunk (2-D map over the prepared
+// activations, box 64 columns x npad rows, 128-byte swizzle, rows beyond M zero-filled) that completes on
+// full_bar; otherwise by 16-byte cp.async copies into padded core matrices.
+template <int DT, bool TMA>
+__global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, const __grid_constant__ CUtensorMap xmap) {
     using C = Codec<DT>;
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    // the swizzled stage needs 1024-byte alignment
+    uint8_t * smem = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t empty_bar[UM_STAGES];
+    __shared__ __align__(8) uint64_t full_bar[UM_STAGES];
     __shared__ __align__(8) uint64_t done_bar;
     __shared__ uint32_t tmem_slot;
+    __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t b_bytes = (uint32_t)p.npad * (UM_KC * 2);
+    const uint32_t b_bytes = TMA ? (uint32_t)p.npad * 128u : (uint32_t)(p.npad >> 3) * UM_B_SBO;
     const uint32_t stage_bytes = UM_A_BYTES + b_bytes;
     uint8_t * tabs = smem + (size_t)UM_STAGES * stage_bytes;
     uint8_t * tab = tabs + warp * C::TAB;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < UM_STAGES; s++)
+        for (int s = 0; s < UM_STAGES; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&empty_bar[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&full_bar[s])) : "memory");
+        }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&done_bar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -226,75 +249,121 @@ __global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t taddr = tmem_slot;
-    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);  // (1024-byte aligned)
     const DecodeConsts kc = p.kc;
 
     const int n_tiles = (p.N + 15) >> 4;
     const int n_blocks = (p.N + UM_ROWS - 1) / UM_ROWS;
     const size_t rec_row = (size_t)p.nsb * C::REC;
     const int K = p.nsb * 256;
+    // this CTA's share of K (superblocks), when K is split across gridDim.y
+    const int sb_begin = (int)(((long long)p.nsb * blockIdx.y) / gridDim.y);
+    const int sb_end = (int)(((long long)p.nsb * (blockIdx.y + 1)) / gridDim.y);
+    const int chunks_per_block = (sb_end - sb_begin) * 4;
     bool expired = false;
+
+    // activations of one chunk: columns [col0, col0 + 64) of every row into the stage
+    auto issue_x = [&](uint32_t stage, int col0) {
+        uint8_t * b_stage = smem + (size_t)stage * stage_bytes + UM_A_BYTES;
+        if constexpr (TMA) {
+            if (threadIdx.x == 0) {
+                const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[stage]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    :
+                    : "r"((uint32_t)__cvta_generic_to_shared(b_stage)), "l"(&xmap), "r"(col0), "r"(0), "r"(bar)
+                    : "memory");
+            }
+        } else {
+            for (int i = threadIdx.x; i < p.npad * 8; i += TW * 32) {
+                const int tok = i >> 3, kch = i & 7;
+                const __half * src = p.xh + (size_t)min(tok, p.M - 1) * K + col0 + kch * 8;
+                const uint32_t dst =
+                    (uint32_t)__cvta_generic_to_shared(b_stage + (tok >> 3) * UM_B_SBO + kch * UM_B_LBO + (tok & 7) * 16);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+        }
+    };
+    // column offset of chunk number `ci` counted from this CTA's first chunk (blocks repeat the same columns)
+    auto chunk_col = [&](uint32_t ci) { return sb_begin * 256 + (int)(ci % (uint32_t)chunks_per_block) * UM_KC; };
 
     pdl_trigger();
     typename C::Regs cur, nxt;
     {
         const int rt = min(blockIdx.x * (UM_ROWS / 16) + warp, n_tiles - 1);
-        C::load(p.w + rt * rec_row, lane, cur);
+        if (sb_begin < sb_end) C::load(p.w + rt * rec_row + (size_t)sb_begin * C::REC, lane, cur);
     }
     pdl_wait();
 
-    uint32_t chunk = 0;  // chunks issued by this CTA so far (stage = chunk % UM_STAGES)
+    uint32_t chunk = 0;  // chunks started by this CTA so far (stage = chunk % UM_STAGES)
     uint32_t block_iter = 0;
-    for (int rb = blockIdx.x; rb < n_blocks; rb += gridDim.x, block_iter++) {
+    // chunks this CTA will run in total, and the first UM_AHEAD activation copies
+    uint32_t total_chunks = 0;
+    if (chunks_per_block > 0 && (int)blockIdx.x < n_blocks)
+        total_chunks = (uint32_t)((n_blocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1) * (uint32_t)chunks_per_block;
+    for (uint32_t ci = 0; ci < UM_AHEAD; ci++) {
+        if (ci < total_chunks) issue_x(ci % UM_STAGES, chunk_col(ci));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int rb = blockIdx.x; rb < n_blocks && chunks_per_block > 0; rb += gridDim.x, block_iter++) {
         const int rt = min(rb * (UM_ROWS / 16) + warp, n_tiles - 1);
         const uint8_t * tile = p.w + rt * rec_row;
-        for (int sb = 0; sb < p.nsb; sb++) {
-            if (sb + 1 < p.nsb) {
+        const bool more_blocks = rb + (int)gridDim.x < n_blocks;
+        for (int sb = sb_begin; sb < sb_end; sb++) {
+            if (sb + 1 < sb_end) {
                 C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
-            } else if (rb + (int)gridDim.x < n_blocks) {
+            } else if (more_blocks) {
                 const int rtn = min((rb + (int)gridDim.x) * (UM_ROWS / 16) + warp, n_tiles - 1);
-                C::load(p.w + rtn * rec_row, lane, nxt);
+                C::load(p.w + rtn * rec_row + (size_t)sb_begin * C::REC, lane, nxt);
             }
             Mma<DT, 1>::header(cur, lane, tab);
             __syncwarp();
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const uint32_t stage = chunk % UM_STAGES, use = chunk / UM_STAGES;
+                const uint32_t stage = chunk % UM_STAGES;
                 uint8_t * a_stage = smem + (size_t)stage * stage_bytes;
-                uint8_t * b_stage = a_stage + UM_A_BYTES;
-                // the tensor pipe must have finished reading this stage's previous contents
-                if (use > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[stage]), (use - 1) & 1)) expired = true;
-                // activations: columns [sb * 256 + q * 64, + 64) of every row, 16 bytes per copy
-                const int col0 = sb * 256 + q * UM_KC;
-                for (int i = threadIdx.x; i < p.npad * 8; i += TW * 32) {
-                    const int kch = i / p.npad, tok = i - kch * p.npad;
-                    const __half * src = p.xh + (size_t)min(tok, p.M - 1) * K + col0 + kch * 8;
-                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(b_stage + (tok >> 3) * 1024 + kch * 128 + (tok & 7) * 16);
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                // start the activations of chunk + UM_AHEAD: the tensor pipe must have read that stage's previous contents
+                {
+                    const uint32_t nchunk = chunk + UM_AHEAD;
+                    if (nchunk < total_chunks) {
+                        const uint32_t nstage = nchunk % UM_STAGES, nuse = nchunk / UM_STAGES;
+                        if (nuse > 0 && !expired &&
+                            !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[nstage]), (nuse - 1) & 1))
+                            expired = true;
+                        issue_x(nstage, chunk_col(nchunk));
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                // weights: this warp's 16 rows x 64 columns
+                // this chunk's stage: free since the wait made when its activations were started (UM_AHEAD chunks ago)
+                // weights: this warp's 16 rows x 64 columns (the stage was waited for when its activations were started)
                 if (q == 0) umma_store_chunk<DT, 0>(cur, lane, tab, kc, a_stage, warp);
                 else if (q == 1) umma_store_chunk<DT, 1>(cur, lane, tab, kc, a_stage, warp);
                 else if (q == 2) umma_store_chunk<DT, 2>(cur, lane, tab, kc, a_stage, warp);
                 else umma_store_chunk<DT, 3>(cur, lane, tab, kc, a_stage, warp);
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                if constexpr (!TMA) asm volatile("cp.async.wait_group %0;" ::"n"(UM_AHEAD) : "memory");  // this chunk's have landed
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncthreads();
                 if (threadIdx.x == 0) {
+                    if constexpr (TMA) {
+                        if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&full_bar[stage]), (chunk / UM_STAGES) & 1))
+                            expired = true;
+                    }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t da = umma_desc(smem_base + stage * stage_bytes);
-                    const uint64_t db = umma_desc(smem_base + stage * stage_bytes + UM_A_BYTES);
+                    const uint64_t db = TMA ? umma_desc_sw128(smem_base + stage * stage_bytes + UM_A_BYTES)
+                                            : umma_desc(smem_base + stage * stage_bytes + UM_A_BYTES, UM_B_LBO, UM_B_SBO);
+                    const uint32_t b_step = TMA ? 2u : (uint32_t)(2 * UM_B_LBO / 16);
 #pragma unroll
                     for (int j = 0; j < UM_KC / 16; j++) {
-                        const uint32_t accumulate = (sb > 0 || q > 0 || j > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (sb > sb_begin || q > 0 || j > 0) ? 1u : 0u;
                         // 16 columns = two core matrices = 256 bytes further along K
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                             :
-                            : "r"(taddr), "l"(da + (uint64_t)(j * 16)), "l"(db + (uint64_t)(j * 16)), "r"(p.idesc), "r"(accumulate),
+                            : "r"(taddr), "l"(da + (uint64_t)(j * 16)), "l"(db + (uint64_t)(j * b_step)), "r"(p.idesc), "r"(accumulate),
                               "r"(0u)
                             : "memory");
                     }
@@ -318,6 +387,9 @@ __global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) 
             // warp w reads TMEM lanes 32 * (w % 4) ..; warps 0-3 take the even 32-column groups, 4-7 the odd ones
             const int quad = warp & 3;
             const int n = rb * UM_ROWS + quad * 32 + lane;
+            const bool split = gridDim.y > 1;
+            float * base = split ? p.partial + (size_t)blockIdx.y * p.M * p.N : p.out;
+            const int64_t ld = split ? p.N : p.ldo;
             for (int c0 = (warp >> 2) * 32; c0 < p.npad; c0 += 64) {
                 uint32_t v[32];
                 const uint32_t src = taddr + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
@@ -337,12 +409,52 @@ __global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) 
                     for (int i = 0; i < 32; i++) {
                         const int tok = c0 + i;
                         if (tok < p.M) {
-                            float * dst = p.out + (int64_t)tok * p.ldo + n;
+                            float * dst = base + (int64_t)tok * ld + n;
                             const float val = __uint_as_float(v[i]);
-                            *dst = p.accumulate ? *dst + val : val;
+                            if (split) __stcg(dst, val);
+                            else *dst = p.accumulate ? *dst + val : val;
                         }
                     }
                 }
+            }
+        }
+        if (gridDim.y > 1) {
+            // K is split across CTAs: the last one to finish this block of rows sums the parts in a fixed order
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) last_flag = atomicAdd(&p.counters[rb], 1) == (int)gridDim.y - 1;
+            __syncthreads();
+            if (last_flag) {
+                __threadfence();
+                const int n0 = rb * UM_ROWS, nrows = min(UM_ROWS, p.N - n0);
+                // four outputs per thread and trip: all their loads are issued before the first sum is formed
+                const int total = p.M * nrows;
+                for (int i0 = threadIdx.x; i0 < total; i0 += 4 * TW * 32) {
+                    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f}, old[4];
+                    float * dst[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int i = min(i0 + u * TW * 32, total - 1);
+                        const int tok = i / nrows, n = n0 + i - tok * nrows;
+                        dst[u] = p.out + (int64_t)tok * p.ldo + n;
+                        old[u] = p.accumulate ? *dst[u] : 0.0f;
+                    }
+                    for (int part = 0; part < (int)gridDim.y; part++) {
+                        float v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int i = min(i0 + u * TW * 32, total - 1);
+                            const int tok = i / nrows, n = n0 + i - tok * nrows;
+                            v[u] = __ldcg(p.partial + ((size_t)part * p.M + tok) * p.N + n);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) sum[u] += v[u];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (i0 + u * TW * 32 < total) *dst[u] = old[u] + sum[u];
+                }
+                if (threadIdx.x == 0) p.counters[rb] = 0;
             }
         }
         // the next block overwrites the accumulator: everybody must have read it
@@ -350,6 +462,7 @@ __global__ void __launch_bounds__(TW * 32, 1) gemm_umma_kernel(const UParams p) 
         __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (expired) atomicExch(&g_gemm_wait_expired, 2);
     // every MMA this CTA issued has completed (the last done_bar wait), nothing reads TMEM any more
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
