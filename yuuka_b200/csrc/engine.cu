@@ -517,6 +517,7 @@ struct yuuka_session {
     int * gdn_counters = nullptr;
     int * post_counter = nullptr;
     bool fuse_post_norm = false;
+    int chain_rows = 0;  // rows per prompt chunk (prefill_logits / forward)
     // L2 prefetch of the next GEMM's weights: matrices in the order a step streams them
     bool prefetch_next = true;
     uint64_t prefetch_bytes = 16ull << 20;  // measured: 16 MB ahead 3.09 ms/step, none 3.12, 48 MB 3.13
@@ -649,6 +650,10 @@ void reserve_gemm(yuuka_session * s, const Tensor & w, int rows) {
 }
 
 enum LogitRows { LOGITS_NONE, LOGITS_LAST, LOGITS_ALL };
+
+// Prompt tokens run through the step kernels in chains of up to this many rows (the row masks are 64 bits
+// wide); from 48 rows on the GEMMs take the tensor-memory route.
+constexpr int CHAIN_ROWS = 64;
 
 // Enqueues one step over sequences [seq0, seq0+batch) with `nodes` rows each.
 void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, LogitRows logit_rows, int max_total) {
@@ -939,7 +944,7 @@ void run_chain(yuuka_session * s, int seq, const int32_t * tokens, int n, float 
     set_device(s->model->dev);
     const int V = s->model->cfg.vocab;
     for (int done = 0; done < n;) {
-        const int chunk = n - done < s->cfg.max_nodes ? n - done : s->cfg.max_nodes;
+        const int chunk = n - done < s->chain_rows ? n - done : s->chain_rows;
         const bool last = done + chunk == n;
         stage_rows(s, seq, 1, chunk, tokens + done, nullptr);
         LogitRows lr = all_logits ? LOGITS_ALL : (last && last_logits ? LOGITS_LAST : LOGITS_NONE);
@@ -1022,7 +1027,11 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             const int kv_dim = model->kv_dim();
             s->kv_row_bytes = sc.kv_format == YUUKA_KV_F32 ? kv_dim * 4 : (sc.kv_format == YUUKA_KV_F16 ? kv_dim * 2 : (kv_dim + 31) / 32 * 34);
             s->table_stride = per_seq;
-            const int B = sc.max_batch, N = sc.max_nodes, R = B * N;
+            // row buffers hold a verify step (max_batch x max_nodes rows) or one prompt chunk of chain_rows rows
+            const int B = sc.max_batch, N = sc.max_nodes;
+            s->chain_rows = CHAIN_ROWS < sc.capacity ? CHAIN_ROWS : sc.capacity;
+            if (s->chain_rows < N) s->chain_rows = N;
+            const int R = B * N > s->chain_rows ? B * N : s->chain_rows;
             const int conv_dim = model->conv_dim(), K1 = c.conv_kernel - 1, S = c.state_size, rank = c.time_step_rank;
             s->conv_count = (int64_t)conv_dim * K1;
             s->s_count = (int64_t)rank * S * S;
@@ -1121,7 +1130,16 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->d_uniforms = dalloc<float>((size_t)R * 2, s->owned);
             s->acc.path = dalloc<int32_t>(R, s->owned);
             s->acc.emitted = dalloc<int32_t>(R, s->owned);
-            s->attn_partial_floats = (size_t)N * c.heads * (4 * model->dev->sm_count / c.kv_heads + 1 + B) * (c.head_dim + 2);
+            {
+                // rows x splits of the flash-decoding partials, for the verify shape and for a prompt chunk
+                auto need = [&](int bx, int nx) {
+                    const int G = c.heads / c.kv_heads, qt = (G * nx + 39) / 40;
+                    return (size_t)bx * nx * c.heads * (size_t)(4 * model->dev->sm_count / (c.kv_heads * qt * bx) + 2) *
+                           (size_t)(c.head_dim + 2);
+                };
+                const size_t a = need(B, N), b = need(1, s->chain_rows);
+                s->attn_partial_floats = a > b ? a : b;
+            }
             s->attn_partial = dalloc<float>(s->attn_partial_floats, s->owned, false);
             // split-K scratch for every matrix shape of the step
             for (int rows : {R < 32 ? R : 32, 1, R < 256 ? R : 256}) {
