@@ -1304,7 +1304,7 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
     const bool want_tma = tensor_map_encoder() != nullptr;
     int max_n = UM_MAX_N;
     while (!want_tma && max_n > 16 &&
-           (size_t)UM_STAGES * (UM_A_BYTES + (size_t)(max_n / 8) * UM_B_SBO) + (size_t)TW * Codec<DT>::TAB + 1024 >
+           (size_t)(UM_STAGES - 1) * (UM_A_BYTES + (size_t)(max_n / 8) * UM_B_SBO) + (size_t)TW * Codec<DT>::TAB + 1024 >
                dev->prop.sharedMemPerBlockOptin)
         max_n -= 16;
     for (int m0 = 0; m0 < a.rows; m0 += max_n) {
@@ -1336,13 +1336,20 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         const bool tma = want_tma && make_x_map(&xmap, p.xh, m, a.n_in, p.npad);
         YK_REQUIRE(tma || !want_tma, YUUKA_ERR_INTERNAL, "umma gemm: the tensor map of the activations could not be encoded");
         const size_t b_bytes = tma ? (size_t)p.npad * 128 : (size_t)(p.npad / 8) * UM_B_SBO;
-        const size_t smem = (size_t)UM_STAGES * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
+        p.stages = UM_STAGES;
+        size_t smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
+        if (smem > dev->prop.sharedMemPerBlockOptin) {
+            p.stages = UM_STAGES - 1;
+            smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
+        }
         YK_REQUIRE(smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_INTERNAL, "umma gemm: stage buffers do not fit shared memory");
-        auto kern = tma ? gemm_umma_kernel<DT, true> : gemm_umma_kernel<DT, false>;
+        static const bool specialised = [] { const char * e = getenv("YUUKA_CUDA_UMMA_WS"); return !(e && e[0] == '0'); }();
+        const bool ws = tma && specialised;
+        auto kern = ws ? gemm_umma_ws_kernel<DT> : (tma ? gemm_umma_kernel<DT, true> : gemm_umma_kernel<DT, false>);
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int per_split = dev->sm_count / ksplit > 0 ? dev->sm_count / ksplit : 1;
         dim3 grid(n_blocks < per_split ? n_blocks : per_split, ksplit);
-        launch_k(kern, grid, TW * 32, smem, s, p, xmap);
+        launch_k(kern, grid, ws ? UM_WS_THREADS : TW * 32, smem, s, p, xmap);
         YK_CUDA(cudaGetLastError());
         launches++;
     }

@@ -27,7 +27,15 @@ constexpr int UM_KC = 64;      // columns per stage
 constexpr int UM_STAGES = 4;
 constexpr int UM_AHEAD = 2;    // chunks of activations in flight ahead of the decode
 constexpr int UM_MAX_N = 256;  // activation rows per launch = UMMA N
-constexpr int UM_A_BYTES = UM_ROWS * UM_KC * 2;  // 16 KB
+// Weight stage: dense core matrices. Padding them to 160 bytes removes the four-way bank conflicts of the
+// decode warps' 16-byte stores and measured the same overall (56.3 vs 55.8 us on 18432 x 2560 at 256 rows),
+// so the smaller stage is kept; -DYK_UMMA_A_LBO=160 builds the padded form.
+#ifndef YK_UMMA_A_LBO
+#define YK_UMMA_A_LBO 128
+#endif
+constexpr int UM_A_LBO = YK_UMMA_A_LBO;
+constexpr int UM_A_SBO = 8 * UM_A_LBO;                // one group of eight rows
+constexpr int UM_A_BYTES = (UM_ROWS / 8) * UM_A_SBO;  // 16 KB
 // Activation stage: core matrices 144 bytes apart along K (16 bytes of padding each), so that the eight
 // 16-byte pieces of one row, copied by eight neighbouring lanes from 128 contiguous global bytes,
 // land in different banks.
@@ -45,6 +53,7 @@ struct UParams {
     int accumulate;
     uint32_t tmem_cols;   // power of two >= npad, >= 32
     uint32_t idesc;
+    uint32_t stages;      // ring depth: UM_STAGES, or one less when four stages do not fit shared memory
     float * partial;      // [gridDim.y][M][N] when K is split across CTAs
     int * counters;       // one per block of 128 weight rows, zero between launches
 };
@@ -198,8 +207,8 @@ __device__ __forceinline__ void umma_store_subblock(const typename Codec<DT>::Re
         vg = make_uint4(h2_add(vg.x, mg), h2_add(vg.y, mg), h2_add(vg.z, mg), h2_add(vg.w, mg));
         vh = make_uint4(h2_add(vh.x, mh), h2_add(vh.y, mh), h2_add(vh.z, mh), h2_add(vh.w, mh));
     }
-    *reinterpret_cast<uint4 *>(a_stage + (2 * warp) * 1024 + kchunk * 128 + g * 16) = vg;
-    *reinterpret_cast<uint4 *>(a_stage + (2 * warp + 1) * 1024 + kchunk * 128 + g * 16) = vh;
+    *reinterpret_cast<uint4 *>(a_stage + (2 * warp) * UM_A_SBO + kchunk * UM_A_LBO + g * 16) = vg;
+    *reinterpret_cast<uint4 *>(a_stage + (2 * warp + 1) * UM_A_SBO + kchunk * UM_A_LBO + g * 16) = vh;
 }
 
 template <int DT, int Q>
@@ -226,7 +235,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t b_bytes = TMA ? (uint32_t)p.npad * 128u : (uint32_t)(p.npad >> 3) * UM_B_SBO;
     const uint32_t stage_bytes = UM_A_BYTES + b_bytes;
-    uint8_t * tabs = smem + (size_t)UM_STAGES * stage_bytes;
+    uint8_t * tabs = smem + (size_t)p.stages * stage_bytes;
     uint8_t * tab = tabs + warp * C::TAB;
 
     if (threadIdx.x == 0) {
@@ -296,14 +305,14 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
     }
     pdl_wait();
 
-    uint32_t chunk = 0;  // chunks started by this CTA so far (stage = chunk % UM_STAGES)
+    uint32_t chunk = 0;  // chunks started by this CTA so far (stage = chunk % p.stages)
     uint32_t block_iter = 0;
     // chunks this CTA will run in total, and the first UM_AHEAD activation copies
     uint32_t total_chunks = 0;
     if (chunks_per_block > 0 && (int)blockIdx.x < n_blocks)
         total_chunks = (uint32_t)((n_blocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1) * (uint32_t)chunks_per_block;
     for (uint32_t ci = 0; ci < UM_AHEAD; ci++) {
-        if (ci < total_chunks) issue_x(ci % UM_STAGES, chunk_col(ci));
+        if (ci < total_chunks) issue_x(ci % p.stages, chunk_col(ci));
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     for (int rb = blockIdx.x; rb < n_blocks && chunks_per_block > 0; rb += gridDim.x, block_iter++) {
@@ -321,13 +330,13 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
             __syncwarp();
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const uint32_t stage = chunk % UM_STAGES;
+                const uint32_t stage = chunk % p.stages;
                 uint8_t * a_stage = smem + (size_t)stage * stage_bytes;
                 // start the activations of chunk + UM_AHEAD: the tensor pipe must have read that stage's previous contents
                 {
                     const uint32_t nchunk = chunk + UM_AHEAD;
                     if (nchunk < total_chunks) {
-                        const uint32_t nstage = nchunk % UM_STAGES, nuse = nchunk / UM_STAGES;
+                        const uint32_t nstage = nchunk % p.stages, nuse = nchunk / p.stages;
                         if (nuse > 0 && !expired &&
                             !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[nstage]), (nuse - 1) & 1))
                             expired = true;
@@ -347,11 +356,11 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
                 __syncthreads();
                 if (threadIdx.x == 0) {
                     if constexpr (TMA) {
-                        if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&full_bar[stage]), (chunk / UM_STAGES) & 1))
+                        if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&full_bar[stage]), (chunk / p.stages) & 1))
                             expired = true;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = umma_desc(smem_base + stage * stage_bytes);
+                    const uint64_t da = umma_desc(smem_base + stage * stage_bytes, UM_A_LBO, UM_A_SBO);
                     const uint64_t db = TMA ? umma_desc_sw128(smem_base + stage * stage_bytes + UM_A_BYTES)
                                             : umma_desc(smem_base + stage * stage_bytes + UM_A_BYTES, UM_B_LBO, UM_B_SBO);
                     const uint32_t b_step = TMA ? 2u : (uint32_t)(2 * UM_B_LBO / 16);
@@ -363,7 +372,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                             :
-                            : "r"(taddr), "l"(da + (uint64_t)(j * 16)), "l"(db + (uint64_t)(j * b_step)), "r"(p.idesc), "r"(accumulate),
+                            : "r"(taddr), "l"(da + (uint64_t)(j * (2 * UM_A_LBO / 16))), "l"(db + (uint64_t)(j * b_step)), "r"(p.idesc), "r"(accumulate),
                               "r"(0u)
                             : "memory");
                     }
@@ -465,6 +474,271 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (expired) atomicExch(&g_gemm_wait_expired, 2);
     // every MMA this CTA issued has completed (the last done_bar wait), nothing reads TMEM any more
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(p.tmem_cols) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Warp-specialised variant (tensor-map activations only): eight decode warps and one control warp.
+// The decode warps never meet at a CTA-wide barrier inside a block of rows: each announces its
+// share of a stage on afull_bar (eight arrivals) and moves on to the next stage as soon as
+// empty_bar says the tensor pipe has drained it. Lane 0 of the control warp keeps the activation
+// copies UM_AHEAD chunks ahead, waits for (activations landed, weights decoded), issues the MMAs
+// and commits the stage back. tmem_free_bar (eight arrivals) tells it that the epilogue has read
+// the accumulator before the next block of rows overwrites it.
+constexpr int UM_WS_THREADS = (TW + 1) * 32;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UParams p, const __grid_constant__ CUtensorMap xmap) {
+    using C = Codec<DT>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t * smem = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
+    __shared__ __align__(8) uint64_t empty_bar[UM_STAGES];
+    __shared__ __align__(8) uint64_t xfull_bar[UM_STAGES];
+    __shared__ __align__(8) uint64_t afull_bar[UM_STAGES];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ __align__(8) uint64_t tmem_free_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int last_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t b_bytes = (uint32_t)p.npad * 128u;
+    const uint32_t stage_bytes = UM_A_BYTES + b_bytes;
+    uint8_t * tabs = smem + (size_t)p.stages * stage_bytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < UM_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&empty_bar[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&xfull_bar[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&afull_bar[s])), "r"(TW)
+                         : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&done_bar)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_free_bar)), "r"(TW)
+                     : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         (uint32_t)__cvta_generic_to_shared(&tmem_slot)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t taddr = tmem_slot;
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+
+    const int n_tiles = (p.N + 15) >> 4;
+    const int n_blocks = (p.N + UM_ROWS - 1) / UM_ROWS;
+    const size_t rec_row = (size_t)p.nsb * C::REC;
+    const int sb_begin = (int)(((long long)p.nsb * blockIdx.y) / gridDim.y);
+    const int sb_end = (int)(((long long)p.nsb * (blockIdx.y + 1)) / gridDim.y);
+    const int chunks_per_block = (sb_end - sb_begin) * 4;
+    uint32_t my_blocks = 0;
+    if (chunks_per_block > 0 && (int)blockIdx.x < n_blocks) my_blocks = (uint32_t)((n_blocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1);
+    const uint32_t total_chunks = my_blocks * (uint32_t)chunks_per_block;
+    bool expired = false;
+
+    pdl_trigger();
+    if (warp == TW) {
+        // ---------------- control warp ----------------
+        pdl_wait();
+        if (lane == 0) {
+            // ring positions are advanced by hand: the ring depth is a run-time value and a division per
+            // chunk on this thread's critical path would cost more than the MMAs it issues
+            auto issue_x = [&](uint32_t stage, uint32_t in_block) {
+                const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xfull_bar[stage]);
+                const int col0 = sb_begin * 256 + (int)in_block * UM_KC;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    :
+                    : "r"(smem_base + stage * stage_bytes + UM_A_BYTES), "l"(&xmap), "r"(col0), "r"(0), "r"(bar)
+                    : "memory");
+            };
+            uint32_t nstage = 0, nuse = 0, n_in_block = 0;  // chunk n = c + UM_AHEAD
+            auto advance_n = [&]() {
+                if (++nstage == p.stages) { nstage = 0; nuse++; }
+                if (++n_in_block == (uint32_t)chunks_per_block) n_in_block = 0;
+            };
+            for (uint32_t ci = 0; ci < UM_AHEAD && ci < total_chunks; ci++) {
+                issue_x(nstage, n_in_block);
+                advance_n();
+            }
+            uint32_t stage = 0, use = 0, in_block = 0, blk = 0;
+            for (uint32_t c = 0; c < total_chunks; c++) {
+                if (c + UM_AHEAD < total_chunks) {
+                    if (nuse > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[nstage]), (nuse - 1) & 1))
+                        expired = true;
+                    issue_x(nstage, n_in_block);
+                    advance_n();
+                }
+                // the epilogue of the previous block must have read the accumulator
+                if (in_block == 0 && blk > 0 && !expired &&
+                    !mbar_wait((uint32_t)__cvta_generic_to_shared(&tmem_free_bar), (blk - 1) & 1))
+                    expired = true;
+                if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&xfull_bar[stage]), use & 1)) expired = true;
+                if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&afull_bar[stage]), use & 1)) expired = true;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = umma_desc(smem_base + stage * stage_bytes, UM_A_LBO, UM_A_SBO);
+                const uint64_t db = umma_desc_sw128(smem_base + stage * stage_bytes + UM_A_BYTES);
+#pragma unroll
+                for (int j = 0; j < UM_KC / 16; j++) {
+                    const uint32_t accumulate = (in_block > 0 || j > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                        :
+                        : "r"(taddr), "l"(da + (uint64_t)(j * (2 * UM_A_LBO / 16))), "l"(db + (uint64_t)(j * 2)), "r"(p.idesc),
+                          "r"(accumulate), "r"(0u)
+                        : "memory");
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 (uint32_t)__cvta_generic_to_shared(&empty_bar[stage]))
+                             : "memory");
+                if (in_block == (uint32_t)chunks_per_block - 1)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                     (uint32_t)__cvta_generic_to_shared(&done_bar))
+                                 : "memory");
+                if (++stage == p.stages) { stage = 0; use++; }
+                if (++in_block == (uint32_t)chunks_per_block) { in_block = 0; blk++; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- decode warps ----------------
+        uint8_t * tab = tabs + warp * C::TAB;
+        const DecodeConsts kc = p.kc;
+        typename C::Regs cur, nxt;
+        if (my_blocks > 0) {
+            const int rt = min(blockIdx.x * (UM_ROWS / 16) + warp, n_tiles - 1);
+            C::load(p.w + rt * rec_row + (size_t)sb_begin * C::REC, lane, cur);
+        }
+        pdl_wait();
+        uint32_t stage = 0, use = 0, block_iter = 0;
+        for (int rb = blockIdx.x; rb < n_blocks && chunks_per_block > 0; rb += gridDim.x, block_iter++) {
+            const int rt = min(rb * (UM_ROWS / 16) + warp, n_tiles - 1);
+            const uint8_t * tile = p.w + rt * rec_row;
+            const bool more_blocks = rb + (int)gridDim.x < n_blocks;
+            for (int sb = sb_begin; sb < sb_end; sb++) {
+                if (sb + 1 < sb_end) {
+                    C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
+                } else if (more_blocks) {
+                    const int rtn = min((rb + (int)gridDim.x) * (UM_ROWS / 16) + warp, n_tiles - 1);
+                    C::load(p.w + rtn * rec_row + (size_t)sb_begin * C::REC, lane, nxt);
+                }
+                Mma<DT, 1>::header(cur, lane, tab);
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    uint8_t * a_stage = smem + (size_t)stage * stage_bytes;
+                    if (use > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[stage]), (use - 1) & 1))
+                        expired = true;
+                    if (q == 0) umma_store_chunk<DT, 0>(cur, lane, tab, kc, a_stage, warp);
+                    else if (q == 1) umma_store_chunk<DT, 1>(cur, lane, tab, kc, a_stage, warp);
+                    else if (q == 2) umma_store_chunk<DT, 2>(cur, lane, tab, kc, a_stage, warp);
+                    else umma_store_chunk<DT, 3>(cur, lane, tab, kc, a_stage, warp);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive((uint32_t)__cvta_generic_to_shared(&afull_bar[stage]));
+                    if (++stage == p.stages) { stage = 0; use++; }
+                }
+                __syncwarp();
+                cur = nxt;
+            }
+            // ---- epilogue of this block of 128 weight rows ----
+            if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&done_bar), block_iter & 1)) expired = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool split = gridDim.y > 1;
+            {
+                const int quad = warp & 3;
+                const int n = rb * UM_ROWS + quad * 32 + lane;
+                float * base = split ? p.partial + (size_t)blockIdx.y * p.M * p.N : p.out;
+                const int64_t ld = split ? p.N : p.ldo;
+                for (int c0 = (warp >> 2) * 32; c0 < p.npad; c0 += 64) {
+                    uint32_t v[32];
+                    const uint32_t src = taddr + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(src)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < p.N) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int tok = c0 + i;
+                            if (tok < p.M) {
+                                float * dst = base + (int64_t)tok * ld + n;
+                                const float val = __uint_as_float(v[i]);
+                                if (split) __stcg(dst, val);
+                                else *dst = p.accumulate ? *dst + val : val;
+                            }
+                        }
+                    }
+                }
+            }
+            // the accumulator has been read: the control warp may start the next block of rows
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive((uint32_t)__cvta_generic_to_shared(&tmem_free_bar));
+            if (split) {
+                // K is split across CTAs: the last one to finish this block of rows sums the parts in a fixed order
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");
+                if (threadIdx.x == 0) last_flag = atomicAdd(&p.counters[rb], 1) == (int)gridDim.y - 1;
+                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");
+                if (last_flag) {
+                    __threadfence();
+                    const int n0 = rb * UM_ROWS, nrows = min(UM_ROWS, p.N - n0);
+                    const int total = p.M * nrows;
+                    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * TW * 32) {
+                        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f}, old[4];
+                        float * dst[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int i = min(i0 + u * TW * 32, total - 1);
+                            const int tok = i / nrows, n = n0 + i - tok * nrows;
+                            dst[u] = p.out + (int64_t)tok * p.ldo + n;
+                            old[u] = p.accumulate ? *dst[u] : 0.0f;
+                        }
+                        for (int part = 0; part < (int)gridDim.y; part++) {
+                            float v[4];
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int i = min(i0 + u * TW * 32, total - 1);
+                                const int tok = i / nrows, n = n0 + i - tok * nrows;
+                                v[u] = __ldcg(p.partial + ((size_t)part * p.M + tok) * p.N + n);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; u++) sum[u] += v[u];
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (i0 + u * TW * 32 < total) *dst[u] = old[u] + sum[u];
+                    }
+                    if (threadIdx.x == 0) p.counters[rb] = 0;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");  // last_flag is reused by the next block
+            }
+        }
+    }
+    if (expired) atomicExch(&g_gemm_wait_expired, 3);
+    // all MMAs have completed (every block's done_bar was waited for) and all epilogue loads are done
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
