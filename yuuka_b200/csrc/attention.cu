@@ -6,7 +6,10 @@
 // attention_prefill_paged_f32_kernel, kernels/hip/prefill/prefill.hip:683).
 //
 // fp32 arithmetic on CUDA cores; K and V rows are decoded from the pool format.
+#include <cuda_fp16.h>
+
 #include <cfloat>
+#include <cstdlib>
 
 #include "layers.cuh"
 #include "quant.cuh"
@@ -186,49 +189,313 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core form of the partial kernel (mma.sync m16n8k16, fp16 operands, fp32 accumulate).
+// A CTA of twelve warps covers up to 48 query rows (three blocks of 16) of one KV head and one key
+// range; warp (rb, dq) owns row block rb and a quarter dq of the head dimension. Every warp of a
+// row block computes the same 16 x 32 score tile (queries as an fp16 hi + lo pair, so scores keep
+// fp32-level accuracy; keys are exact when the pool stores F16 rows, otherwise they are split the
+// same way), hence the same softmax statistics with no exchange between warps, and multiplies the
+// probabilities (fp16) with its own 16 x 32 x HD/4 slice of V, fetched with ldmatrix.trans.
+constexpr int AM_KT = 32;
+constexpr int AM_ROWS = 48;
+constexpr int AM_WARPS = 12;
+
+__device__ __forceinline__ void mma16816h(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+// v as fp16 hi (returned) and the fp16 of the remainder
+__device__ __forceinline__ __half split_half(float v, __half & lo) {
+    const __half hi = __float2half_rn(v);
+    lo = __float2half_rn(v - __half2float(hi));
+    return hi;
+}
+
+template <int HD, bool KSPLIT>
+__global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const AttnParams p) {
+    pdl_entry();
+    constexpr int STR = HD + 8;   // halves per shared-memory row: 16 bytes of padding spread the banks
+    constexpr int DW = HD / 4;    // head dimensions per warp
+    constexpr int NT_O = DW / 8;  // 8-column output tiles per warp
+    extern __shared__ __align__(16) uint8_t smraw[];
+    __half * qhi = reinterpret_cast<__half *>(smraw);
+    __half * qlo = qhi + AM_ROWS * STR;
+    __half * ks = qlo + AM_ROWS * STR;
+    __half * kl = ks + AM_KT * STR;  // low parts of K (KSPLIT only)
+    __half * vs = KSPLIT ? kl + AM_KT * STR : kl;
+
+    const int seq = blockIdx.z;
+    const int kvh = blockIdx.y % p.kv_heads, qt = blockIdx.y / p.kv_heads;
+    const int split = blockIdx.x;
+    const int G = p.heads / p.kv_heads, N = p.rows.nodes;
+    const int pos0 = p.rows.pos0[seq];
+    const int total = pos0 + N;
+    const int k_begin = split * p.key_split;
+    const int k_end = min(total, k_begin + p.key_split);
+    const int nq = min(AM_ROWS, G * N - qt * AM_ROWS);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rb = warp >> 2, dq = warp & 3;
+    const float scale = (float)(1.0 / sqrt((double)HD));
+
+    // queries of this tile as fp16 hi / lo; rows beyond nq are zero
+    for (int i = threadIdx.x; i < AM_ROWS * (HD / 4); i += AM_WARPS * 32) {
+        const int qi = i / (HD / 4), c = i - qi * (HD / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (qi < nq) {
+            const int gq = qt * AM_ROWS + qi, node = gq / G, head = kvh * G + gq % G;
+            v = reinterpret_cast<const float4 *>(p.q + (int64_t)(seq * N + node) * p.ldq + (int64_t)head * 2 * HD)[c];
+        }
+        __half l0, l1, l2, l3;
+        const __half h0 = split_half(v.x, l0), h1 = split_half(v.y, l1), h2 = split_half(v.z, l2), h3 = split_half(v.w, l3);
+        __half2 * dh = reinterpret_cast<__half2 *>(qhi + qi * STR + c * 4);
+        __half2 * dl = reinterpret_cast<__half2 *>(qlo + qi * STR + c * 4);
+        dh[0] = __halves2half2(h0, h1);
+        dh[1] = __halves2half2(h2, h3);
+        dl[0] = __halves2half2(l0, l1);
+        dl[1] = __halves2half2(l2, l3);
+    }
+
+    // the two query rows this lane holds in the accumulator layout: local rows rb*16 + g and + 8
+    uint64_t mask[2];
+    int row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int qi = rb * 16 + g + 8 * h;
+        row_ok[h] = qi < nq;
+        const int node = row_ok[h] ? (qt * AM_ROWS + qi) / G : 0;
+        mask[h] = row_ok[h] ? p.rows.anc_mask[seq * N + node] : 0ull;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int nt = 0; nt < NT_O; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) o[nt][c] = 0.0f;
+
+    for (int k0 = k_begin; k0 < k_end; k0 += AM_KT) {
+        __syncthreads();  // the previous tile has been consumed (and, first time, the queries are in place)
+        for (int i = threadIdx.x; i < AM_KT * (HD / 8); i += AM_WARPS * 32) {
+            const int j = i / (HD / 8), c8 = i - j * (HD / 8);
+            const int pos = k0 + j;
+            uint4 kh4 = make_uint4(0, 0, 0, 0), kl4 = kh4, vh4 = kh4;
+            if (pos < k_end) {
+                const int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
+                const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
+                if (!KSPLIT) {
+                    kh4 = *reinterpret_cast<const uint4 *>(p.pool.k + off + (size_t)(kvh * HD + c8 * 8) * 2);
+                    vh4 = *reinterpret_cast<const uint4 *>(p.pool.v + off + (size_t)(kvh * HD + c8 * 8) * 2);
+                } else {
+                    float kw[8], vw[8];
+                    kv_decode8(p.pool.k + off, p.pool.format, kvh * (HD / 8) + c8, kw);
+                    kv_decode8(p.pool.v + off, p.pool.format, kvh * (HD / 8) + c8, vw);
+                    __half hh[8], ll[8], vv[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        hh[e] = split_half(kw[e], ll[e]);
+                        vv[e] = __float2half_rn(vw[e]);
+                    }
+                    kh4 = *reinterpret_cast<const uint4 *>(hh);
+                    kl4 = *reinterpret_cast<const uint4 *>(ll);
+                    vh4 = *reinterpret_cast<const uint4 *>(vv);
+                }
+            }
+            *reinterpret_cast<uint4 *>(ks + j * STR + c8 * 8) = kh4;
+            if (KSPLIT) *reinterpret_cast<uint4 *>(kl + j * STR + c8 * 8) = kl4;
+            *reinterpret_cast<uint4 *>(vs + j * STR + c8 * 8) = vh4;
+        }
+        __syncthreads();
+
+        // scores of this warp's 16 rows against the 32 keys
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) s[nt][c] = 0.0f;
+        const __half * qh_row = qhi + (rb * 16 + g) * STR + 2 * t;
+        const __half * ql_row = qlo + (rb * 16 + g) * STR + 2 * t;
+#pragma unroll 4
+        for (int kk = 0; kk < HD / 16; kk++) {
+            uint32_t ah[4], al[4];
+            ah[0] = *reinterpret_cast<const uint32_t *>(qh_row + 16 * kk);
+            ah[1] = *reinterpret_cast<const uint32_t *>(qh_row + 8 * STR + 16 * kk);
+            ah[2] = *reinterpret_cast<const uint32_t *>(qh_row + 16 * kk + 8);
+            ah[3] = *reinterpret_cast<const uint32_t *>(qh_row + 8 * STR + 16 * kk + 8);
+            al[0] = *reinterpret_cast<const uint32_t *>(ql_row + 16 * kk);
+            al[1] = *reinterpret_cast<const uint32_t *>(ql_row + 8 * STR + 16 * kk);
+            al[2] = *reinterpret_cast<const uint32_t *>(ql_row + 16 * kk + 8);
+            al[3] = *reinterpret_cast<const uint32_t *>(ql_row + 8 * STR + 16 * kk + 8);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const __half * kr = ks + (8 * nt + g) * STR + 16 * kk + 2 * t;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kr), b1 = *reinterpret_cast<const uint32_t *>(kr + 8);
+                mma16816h(s[nt], ah, b0, b1);
+                mma16816h(s[nt], al, b0, b1);
+                if (KSPLIT) {
+                    const __half * lr = kl + (8 * nt + g) * STR + 16 * kk + 2 * t;
+                    mma16816h(s[nt], ah, *reinterpret_cast<const uint32_t *>(lr), *reinterpret_cast<const uint32_t *>(lr + 8));
+                }
+            }
+        }
+        // mask, online softmax; s[nt][0,1] -> row g, keys 8 nt + 2 t + {0,1}; s[nt][2,3] -> row g + 8
+        uint32_t pa[2][4];  // probabilities as A fragments of the two 16-key steps
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float sv[4][2];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int pos = k0 + 8 * nt + 2 * t + e;
+                    const bool vis = pos < k_end && row_ok[h] && (pos < pos0 || ((mask[h] >> (pos - pos0)) & 1ull));
+                    sv[nt][e] = vis ? s[nt][2 * h + e] * scale : -INFINITY;
+                    mx = fmaxf(mx, sv[nt][e]);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[h], mx);
+            float corr = 1.0f, sum = 0.0f;
+            float pr[4][2];
+            if (m_new != -INFINITY) corr = expf(m[h] - m_new);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float pv = (m_new != -INFINITY && sv[nt][e] != -INFINITY) ? expf(sv[nt][e] - m_new) : 0.0f;
+                    pr[nt][e] = __half2float(__float2half_rn(pv));  // the value the tensor core will see
+                    sum += pr[nt][e];
+                }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l[h] = l[h] * corr + sum;
+            m[h] = m_new;
+#pragma unroll
+            for (int nt = 0; nt < NT_O; nt++) {
+                o[nt][2 * h] *= corr;
+                o[nt][2 * h + 1] *= corr;
+            }
+            // A fragment registers: [0] row g / [1] row g+8 for keys 2t..; [2], [3] the same rows, keys 2t+8..
+            pa[0][h] = pack_h2(pr[0][0], pr[0][1]);
+            pa[0][2 + h] = pack_h2(pr[1][0], pr[1][1]);
+            pa[1][h] = pack_h2(pr[2][0], pr[2][1]);
+            pa[1][2 + h] = pack_h2(pr[3][0], pr[3][1]);
+        }
+        // O += P V on this warp's DW dimensions
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const __half * vrow = vs + (16 * kk + (lane & 15)) * STR + dq * DW;
+#pragma unroll
+            for (int nt = 0; nt < NT_O; nt++) {
+                uint32_t b0, b1;
+                const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vrow + 8 * nt);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+                mma16816h(o[nt], pa[kk], b0, b1);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        if (!row_ok[h]) continue;
+        const int gq = qt * AM_ROWS + rb * 16 + g + 8 * h, node = gq / G, head = kvh * G + gq % G;
+        float * dst = p.partial + (((int64_t)(seq * N + node) * p.heads + head) * p.splits + split) * (HD + 2);
+#pragma unroll
+        for (int nt = 0; nt < NT_O; nt++) {
+            float2 v = make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+            *reinterpret_cast<float2 *>(dst + dq * DW + 8 * nt + 2 * t) = v;
+        }
+        if (dq == 0 && t == 0) {
+            dst[HD] = m[h];
+            dst[HD + 1] = l[h];
+        }
+    }
+}
+
 // float exp: the CPU reference evaluates exp in f64 and rounds; the difference is below 2e-7 relative
 __device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// one thread per 16 consecutive output dims of one (row, head)
+// One CTA per (row, head): the split statistics are combined once in shared memory, then every thread
+// sums its four output dims over the splits that saw a key (independent, coalesced loads), applies the
+// sigmoid gate, and a 16-dim group leader writes the prepared form.
+constexpr int MERGE_MAX_SPLITS = 1024;
+
 template <int HD>
-__global__ void attention_merge_kernel(float * __restrict__ out, int ldo, const float * __restrict__ partial,
-                                       const float * __restrict__ q, int ldq, int heads, int splits, XPrepOut prep) {
+__global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) attention_merge_kernel(float * __restrict__ out, int ldo, const float * __restrict__ partial,
+                                                                 const float * __restrict__ q, int ldq, int heads, int splits,
+                                                                 XPrepOut prep) {
     pdl_entry();
-    const int r = blockIdx.x;
-    const int gq = threadIdx.x;  // 16-group within the row: head * (HD/16) + part
-    if (gq >= heads * (HD / 16)) return;
-    const int head = gq / (HD / 16), part = gq - head * (HD / 16);
+    __shared__ float w_s[MERGE_MAX_SPLITS];
+    __shared__ float inv_l;
+    const int r = blockIdx.x / heads, head = blockIdx.x - r * heads;
+    const int tid = threadIdx.x;
     const float * base = partial + ((int64_t)r * heads + head) * splits * (HD + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; s++) M = fmaxf(M, base[s * (HD + 2) + HD]);
-    float L = 0.0f;
-    float o[16];
+    constexpr int THREADS = HD / 4 < 32 ? 32 : HD / 4;  // whole warps; threads beyond HD / 4 only help with the statistics
+    const bool has_dims = tid < HD / 4;
+    for (int s = tid; s < splits; s += THREADS) w_s[s] = base[s * (HD + 2) + HD];  // the split's running maximum
+    __syncthreads();
+    if (tid < 32) {
+        float M = -INFINITY;
+        for (int s = tid; s < splits; s += 32) M = fmaxf(M, w_s[s]);
 #pragma unroll
-    for (int i = 0; i < 16; i++) o[i] = 0.0f;
-    for (int s = 0; s < splits; s++) {
-        const float ms = base[s * (HD + 2) + HD];
-        if (ms == -INFINITY) continue;
-        const float w = expf(ms - M);
-        L += base[s * (HD + 2) + HD + 1] * w;
-        const float4 * src = reinterpret_cast<const float4 *>(base + s * (HD + 2) + part * 16);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float2 lo = reinterpret_cast<const float2 *>(src)[2 * i], hi = reinterpret_cast<const float2 *>(src)[2 * i + 1];
-            o[4 * i] = fmaf(lo.x, w, o[4 * i]);
-            o[4 * i + 1] = fmaf(lo.y, w, o[4 * i + 1]);
-            o[4 * i + 2] = fmaf(hi.x, w, o[4 * i + 2]);
-            o[4 * i + 3] = fmaf(hi.y, w, o[4 * i + 3]);
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        // weights exp(m_s - M); the normaliser is summed in split order by one lane, as the serial form did
+        for (int s = tid; s < splits; s += 32) {
+            const float ms = w_s[s];
+            w_s[s] = ms == -INFINITY ? 0.0f : expf(ms - M);
+        }
+        __syncwarp();
+        if (tid == 0) {
+            float L = 0.0f;
+            for (int s = 0; s < splits; s++)
+                if (w_s[s] != 0.0f) L += base[s * (HD + 2) + HD + 1] * w_s[s];
+            inv_l = L > 0.0f ? 1.0f / L : 0.0f;
         }
     }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    const float * gate = q + (int64_t)r * ldq + (int64_t)head * 2 * HD + HD + part * 16;
+    __syncthreads();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float * col = base + (has_dims ? tid : 0) * 4;
+#pragma unroll 8
+    for (int s = 0; s < splits; s++) {
+        const float w = w_s[s];
+        if (w == 0.0f) continue;
+        const float2 lo = *reinterpret_cast<const float2 *>(col + (size_t)s * (HD + 2));
+        const float2 hi = *reinterpret_cast<const float2 *>(col + (size_t)s * (HD + 2) + 2);
+        acc.x = fmaf(lo.x, w, acc.x);
+        acc.y = fmaf(lo.y, w, acc.y);
+        acc.z = fmaf(hi.x, w, acc.z);
+        acc.w = fmaf(hi.y, w, acc.w);
+    }
+    const float inv = inv_l;
+    const float4 gate =
+        *reinterpret_cast<const float4 *>(q + (int64_t)r * ldq + (int64_t)head * 2 * HD + HD + (has_dims ? tid : 0) * 4);
+    float4 o;
+    o.x = acc.x * inv * sigmoid_ref(gate.x);
+    o.y = acc.y * inv * sigmoid_ref(gate.y);
+    o.z = acc.z * inv * sigmoid_ref(gate.z);
+    o.w = acc.w * inv * sigmoid_ref(gate.w);
+    if (has_dims) *reinterpret_cast<float4 *>(out + (int64_t)r * ldo + head * HD + tid * 4) = o;
+    if (prep.xh) {
+        // gather the 16-dim group in its first lane (four neighbouring threads hold it)
+        float v[16];
 #pragma unroll
-    for (int i = 0; i < 16; i++) o[i] = o[i] * inv * sigmoid_ref(gate[i]);
-    float4 * d = reinterpret_cast<float4 *>(out + (int64_t)r * ldo + head * HD + part * 16);
-#pragma unroll
-    for (int i = 0; i < 4; i++) d[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-    const int cols = heads * HD;
-    if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, o);
+        for (int k = 0; k < 4; k++) {
+            v[4 * k] = __shfl_sync(0xffffffffu, o.x, (tid & 28) + k);
+            v[4 * k + 1] = __shfl_sync(0xffffffffu, o.y, (tid & 28) + k);
+            v[4 * k + 2] = __shfl_sync(0xffffffffu, o.z, (tid & 28) + k);
+            v[4 * k + 3] = __shfl_sync(0xffffffffu, o.w, (tid & 28) + k);
+        }
+        if ((tid & 3) == 0 && has_dims) {
+            const int cols = heads * HD, gq = head * (HD / 16) + (tid >> 2);
+            xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+        }
+    }
 }
 
 size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits) {
@@ -249,16 +516,30 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
     p.rows = rows;
     p.pool = pool;
     const int G = heads / kv_heads;
-    const int qtiles = (G * rows.nodes + ATT_QT - 1) / ATT_QT;
-    size_t smem = sizeof(float) * ((size_t)ATT_QT * HD + ATT_KT * (HD + 4) + ATT_KT * HD + ATT_QT * ATT_KT);
-    auto kern = attention_partial_kernel<HD>;
-    YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
-    launch_k(kern, grid, ATT_WARPS * 32, smem, s, p);
-    YK_CUDA(cudaGetLastError());
-    const int mthreads = ((heads * (HD / 16) + 31) / 32) * 32;
-    YK_REQUIRE(mthreads <= 1024, YUUKA_ERR_UNSUPPORTED, "attention: too many heads for the merge kernel");
-    launch_k(attention_merge_kernel<HD>, rows.batch * rows.nodes, mthreads, 0, s, out, ldo, sc.partial, q, ldq, heads, sc.splits, prep);
+    static const bool use_mma = [] { const char * e = getenv("YUUKA_CUDA_ATTN_FP32"); return !(e && e[0] == '1'); }();
+    if (use_mma) {
+        // tensor-core partials; keys are taken as they are from an F16 pool and split into hi + lo otherwise
+        const bool ksplit = pool.format != YUUKA_KV_F16;
+        const int qtiles = (G * rows.nodes + AM_ROWS - 1) / AM_ROWS;
+        const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * AM_ROWS + (ksplit ? 3 : 2) * AM_KT);
+        auto kern = ksplit ? attention_mma_kernel<HD, true> : attention_mma_kernel<HD, false>;
+        YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
+        launch_k(kern, grid, AM_WARPS * 32, smem, s, p);
+        YK_CUDA(cudaGetLastError());
+    } else {
+        const int qtiles = (G * rows.nodes + ATT_QT - 1) / ATT_QT;
+        size_t smem = sizeof(float) * ((size_t)ATT_QT * HD + ATT_KT * (HD + 4) + ATT_KT * HD + ATT_QT * ATT_KT);
+        auto kern = attention_partial_kernel<HD>;
+        YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
+        launch_k(kern, grid, ATT_WARPS * 32, smem, s, p);
+        YK_CUDA(cudaGetLastError());
+    }
+    YK_REQUIRE(sc.splits <= MERGE_MAX_SPLITS, YUUKA_ERR_UNSUPPORTED, "attention: %d key splits exceed the merge kernel's %d",
+               sc.splits, MERGE_MAX_SPLITS);
+    launch_k(attention_merge_kernel<HD>, rows.batch * rows.nodes * heads, HD / 4 < 32 ? 32 : HD / 4, 0, s, out, ldo, sc.partial, q, ldq, heads,
+             sc.splits, prep);
     YK_CUDA(cudaGetLastError());
     return 2;
 }

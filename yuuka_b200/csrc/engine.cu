@@ -749,8 +749,14 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             const int G = c.heads / c.kv_heads;
             const int qtiles = (G * nodes + 39) / 40;
             const int base = c.kv_heads * qtiles * batch;
-            // one 32-key tile per CTA while the sequences are short enough: about four CTAs per SM at capacity
-            int splits = (4 * m->dev->sm_count + base - 1) / base;
+            // about one CTA per SM at capacity (measured at a 1500-token context: 3.11 ms per step, against 3.16 with
+            // two or four per SM: fewer partials for the merge kernel outweigh the shorter key ranges)
+            static const int split_mult = [] {
+                const char * e = getenv("YUUKA_CUDA_ATTN_SPLIT_MULT");
+                const int v = e ? atoi(e) : 1;
+                return v < 1 ? 1 : (v > 4 ? 4 : v);
+            }();
+            int splits = (split_mult * m->dev->sm_count + base - 1) / base;
             int max_splits = (max_total + 31) / 32;
             if (splits > max_splits) splits = max_splits;
             if (splits < 1) splits = 1;
