@@ -112,7 +112,8 @@ def cpu_reference_sample(steps: int, warmup: int, threads: int = 0) -> dict:
     from oracle import pyoracle as yo
     from yuuka_b200 import synth
 
-    yo.lib().yo_set_threads(threads)
+    # all host cores, whatever OMP_NUM_THREADS says (torch.distributed.run sets it to 1)
+    yo.lib().yo_set_threads(threads if threads > 0 else (os.cpu_count() or 1))
     cores = yo.lib().yo_get_threads()
     cfg = synth.dense4b_config(layers=4, context=64)
     tensors = synth.make_model(cfg, "q4_k_m", seed=1)
