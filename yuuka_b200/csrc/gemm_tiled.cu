@@ -1130,11 +1130,15 @@ static bool umma_enabled() {
 
 // K splits of the tensor-memory route: enough CTAs to fill the machine when the matrix has few
 // 128-row blocks, at least two superblocks each.
-static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in) {
+static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in, int rows) {
     const int n_blocks = (n_out + UM_ROWS - 1) / UM_ROWS, nsb = n_in / 256;
     int ks = dev->sm_count / n_blocks;
     if (ks > nsb / 2) ks = nsb / 2;
-    if (ks > 16) ks = 16;
+    // the last CTA of a block sums the parts alone: measured on 2560-row matrices, four parts pay up to
+    // about 96 activation rows and two beyond (the sum grows with rows x parts, the decode it hides does not)
+    static const int forced = [] { const char * e = getenv("YUUKA_CUDA_UMMA_KSPLIT"); return e ? atoi(e) : 0; }();
+    const int cap = forced > 0 ? forced : (rows <= 96 ? 4 : 2);
+    if (ks > cap) ks = cap;
     return ks < 1 ? 1 : ks;
 }
 
@@ -1144,9 +1148,21 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     *counters = 0;
     if (!tiled_supported(w_dtype, n_in)) return;
     if (rows >= UMMA_MIN_ROWS) {
-        const int ks = umma_ksplit(dev, n_out, n_in);
+        const int per_launch = rows < UM_MAX_N ? rows : UM_MAX_N;
+        // enough for this row count and for every smaller one (fewer rows may split K further)
+        int ks = 1, worst = 0;
+        for (int m = UMMA_MIN_ROWS; m <= per_launch; m += 16) {
+            const int k = umma_ksplit(dev, n_out, n_in, m);
+            if (k > ks) ks = k;
+            if (k * m > worst) worst = k * m;
+        }
+        {
+            const int k = umma_ksplit(dev, n_out, n_in, per_launch);
+            if (k > ks) ks = k;
+            if (k * per_launch > worst) worst = k * per_launch;
+        }
         if (ks > 1) {
-            *partial_floats = (uint64_t)ks * (rows < UM_MAX_N ? rows : UM_MAX_N) * n_out;
+            *partial_floats = (uint64_t)worst * n_out;
             *counters = (n_out + UM_ROWS - 1) / UM_ROWS;
         }
     }
@@ -1299,7 +1315,6 @@ template <int DT>
 static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, const __half * xh) {
     int launches = 0;
     const int n_blocks = (a.n_out + UM_ROWS - 1) / UM_ROWS;
-    const int ksplit = umma_ksplit(dev, a.n_out, a.n_in);
     // rows per launch: 256 with tensor-map copies; the padded cp.async stages are larger, so fewer fit
     const bool want_tma = tensor_map_encoder() != nullptr;
     int max_n = UM_MAX_N;
@@ -1309,6 +1324,7 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         max_n -= 16;
     for (int m0 = 0; m0 < a.rows; m0 += max_n) {
         const int m = a.rows - m0 < max_n ? a.rows - m0 : max_n;
+        const int ksplit = umma_ksplit(dev, a.n_out, a.n_in, m);
         UParams p{};
         p.kc = decode_consts(DT);
         p.w = a.w;
