@@ -507,6 +507,8 @@ struct yuuka_session {
     float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
     // qwen35moe scratch: routing, expert-sorted (row, slot) pairs, expert and shared-expert activations
     int32_t *moe_ids = nullptr, *moe_pos = nullptr, *moe_row = nullptr;
+    float * moe_logits = nullptr;  // [rows][experts] router logits
+    int * moe_counters = nullptr;  // one per group of eight rows, zero between launches
     float *moe_w = nullptr, *moe_sg = nullptr, *moe_gu = nullptr, *moe_act = nullptr, *moe_y = nullptr;
     float *sh_gu = nullptr, *sh_act = nullptr, *sh_y = nullptr;
     GemmSegment * moe_segments = nullptr;
@@ -775,7 +777,8 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             const int E = c.expert_count, U = c.expert_used, EF = c.expert_ffn, SF = c.shared_ffn, P = R * U;
             YK_REQUIRE(s->prep_xn.xh, YUUKA_ERR_UNSUPPORTED, "moe: hidden size must be a multiple of 16");
             mark(s, YUUKA_OP_MOE_ROUTE);
-            launch_moe_route(st, s->xn, L.router, L.sh_gate_inp, H, E, U, R, s->moe_ids, s->moe_w, s->moe_sg);
+            launch_moe_route(st, s->xn, L.router, L.sh_gate_inp, H, E, U, R, s->moe_ids, s->moe_w, s->moe_sg, s->moe_logits,
+                             s->moe_counters);
             launch_moe_group(st, s->moe_ids, R, U, E, s->moe_pos, s->moe_row, s->moe_segments, s->moe_max_segments);
             s->launches += 2;
             mark(s, YUUKA_OP_MOE_EXPERTS);
@@ -1113,6 +1116,8 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 s->moe_row = dalloc<int32_t>(P, s->owned);
                 s->moe_w = dalloc<float>(P, s->owned);
                 s->moe_sg = dalloc<float>(R, s->owned);
+                s->moe_logits = dalloc<float>((size_t)R * c.expert_count, s->owned);
+                s->moe_counters = dalloc<int>((size_t)R / 8 + 1, s->owned);
                 s->moe_gu = dalloc<float>(P * 2 * c.expert_ffn, s->owned);
                 s->moe_act = dalloc<float>(P * c.expert_ffn, s->owned);
                 s->moe_y = dalloc<float>(P * H, s->owned);

@@ -132,7 +132,7 @@ void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & 
 struct GemmSegment;
 int moe_max_segments(int pairs, int experts);
 void launch_moe_route(cudaStream_t s, const float * xn, const float * router, const float * sh_gate, int hidden, int experts,
-                      int used, int rows, int32_t * ids, float * weights, float * shared_gate);
+                      int used, int rows, int32_t * ids, float * weights, float * shared_gate, float * logits, int * counters);
 void launch_moe_group(cudaStream_t s, const int32_t * ids, int rows, int used, int experts, int32_t * pos_of_pair,
                       int32_t * row_of_pos, GemmSegment * segments, int max_segments);
 void launch_moe_combine(cudaStream_t s, float * x, const float * expert_out, const float * shared_out,

@@ -23,53 +23,85 @@ struct RouteParams {
     float * shared_gate;    // [rows]
 };
 
-// One CTA per row. Warps take experts round-robin; a dot product is summed by lanes in a fixed
-// order (the CPU reference sums sequentially, so logits agree to rounding, not bit for bit).
-__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteParams p) {
+constexpr int ROUTE_ROWS = 8;      // rows per CTA: a router row is read once per eight activation rows
+constexpr int ROUTE_EXPERTS = 32;  // router rows per CTA: four per warp
+
+// grid (row groups, expert groups). A warp takes four router rows and all eight activation rows: 16-byte
+// weight loads shared by the rows, 32 accumulators per lane; a dot product is summed by lanes in a fixed
+// order (the CPU reference sums sequentially, so logits agree to rounding, not bit for bit). Logits go to
+// global memory; the last CTA of a row group to arrive (atomic counter, no waiting) selects the experts
+// of its eight rows, one warp per row.
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteParams p, int rows, float * logits, int * counters) {
     pdl_entry();
     extern __shared__ __align__(16) float sm[];
-    float * x = sm;                      // [hidden]
-    float * logit = sm + p.hidden;       // [experts]
-    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float * src = p.xn + (int64_t)r * p.hidden;
-    for (int i = threadIdx.x; i < p.hidden; i += ROUTE_THREADS) x[i] = src[i];
+    float * x = sm;  // [ROUTE_ROWS][hidden]
+    __shared__ int last_flag;
+    const int r0 = blockIdx.x * ROUTE_ROWS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nr = min(ROUTE_ROWS, rows - r0);
+    const int n_vec = p.experts + 1;  // index `experts` is the shared-expert gate vector
+    for (int i = threadIdx.x; i < ROUTE_ROWS * (p.hidden / 4); i += ROUTE_THREADS) {
+        const int rr = i / (p.hidden / 4), c = i - rr * (p.hidden / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rr < nr) v = reinterpret_cast<const float4 *>(p.xn + (int64_t)(r0 + rr) * p.hidden)[c];
+        reinterpret_cast<float4 *>(x + rr * p.hidden)[c] = v;
+    }
     __syncthreads();
-    // four experts per warp pass, 16 bytes per lane and load: enough independent loads in flight to
-    // cover the L2 latency (index `experts` is the shared-expert gate vector)
-    const int n_vec = p.experts + 1;
-    for (int e0 = warp * 4; e0 < n_vec; e0 += (ROUTE_THREADS / 32) * 4) {
+    const int e0 = blockIdx.y * ROUTE_EXPERTS + warp * 4;
+    if (e0 < n_vec) {
         const float * w[4];
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float acc[4][ROUTE_ROWS];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const int e = min(e0 + q, n_vec - 1);
             w[q] = e < p.experts ? p.router + (int64_t)e * p.hidden : p.sh_gate;
+#pragma unroll
+            for (int rr = 0; rr < ROUTE_ROWS; rr++) acc[q][rr] = 0.0f;
         }
 #pragma unroll 2
         for (int i = lane * 4; i < p.hidden; i += 128) {
-            const float4 xv = *reinterpret_cast<const float4 *>(x + i);
+            float4 wv[4];
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const float4 wv = __ldg(reinterpret_cast<const float4 *>(w[q] + i));
-                acc[q] = fmaf(wv.x, xv.x, acc[q]);
-                acc[q] = fmaf(wv.y, xv.y, acc[q]);
-                acc[q] = fmaf(wv.z, xv.z, acc[q]);
-                acc[q] = fmaf(wv.w, xv.w, acc[q]);
+            for (int q = 0; q < 4; q++) wv[q] = __ldg(reinterpret_cast<const float4 *>(w[q] + i));
+#pragma unroll
+            for (int rr = 0; rr < ROUTE_ROWS; rr++) {
+                const float4 xv = *reinterpret_cast<const float4 *>(x + rr * p.hidden + i);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    acc[q][rr] = fmaf(wv[q].x, xv.x, acc[q][rr]);
+                    acc[q][rr] = fmaf(wv[q].y, xv.y, acc[q][rr]);
+                    acc[q][rr] = fmaf(wv[q].z, xv.z, acc[q][rr]);
+                    acc[q][rr] = fmaf(wv[q].w, xv.w, acc[q][rr]);
+                }
             }
         }
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], o);
             const int e = e0 + q;
-            if (lane == 0 && e < n_vec) {
-                if (e < p.experts) logit[e] = acc[q];
-                else p.shared_gate[r] = 1.0f / (1.0f + (float)exp((double)-acc[q]));
+#pragma unroll
+            for (int rr = 0; rr < ROUTE_ROWS; rr++) {
+                float v = acc[q][rr];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && e < n_vec && rr < nr) {
+                    if (e < p.experts) __stcg(logits + (int64_t)(r0 + rr) * p.experts + e, v);
+                    else p.shared_gate[r0 + rr] = 1.0f / (1.0f + (float)exp((double)-v));
+                }
             }
         }
     }
+    __threadfence();
     __syncthreads();
-    if (warp != 0) return;
+    if (threadIdx.x == 0) last_flag = atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0;
+    if (warp >= nr) return;
+    const int r = r0 + warp;
+    float * logit = sm + warp * p.experts;  // (the activation rows in shared memory are no longer needed)
+    __syncwarp();
+    for (int e = lane; e < p.experts; e += 32) logit[e] = __ldcg(logits + (int64_t)r * p.experts + e);
+    __syncwarp();
     // selectExperts (forward.go:393-439): `used` rounds of first-maximum argmax over the experts not yet taken
     int32_t * ids = p.ids + (int64_t)r * p.used;
     float * wts = p.weights + (int64_t)r * p.used;
@@ -173,14 +205,17 @@ int moe_max_segments(int pairs, int experts) {
 }
 
 void launch_moe_route(cudaStream_t s, const float * xn, const float * router, const float * sh_gate, int hidden, int experts,
-                      int used, int rows, int32_t * ids, float * weights, float * shared_gate) {
+                      int used, int rows, int32_t * ids, float * weights, float * shared_gate, float * logits, int * counters) {
     YK_REQUIRE(hidden % 4 == 0, YUUKA_ERR_UNSUPPORTED, "moe: hidden size %d is not a multiple of 4", hidden);
     YK_REQUIRE(experts <= ROUTE_MAX_EXPERTS && used <= 32 && used <= experts, YUUKA_ERR_UNSUPPORTED,
                "moe: %d experts / %d used exceeds the router kernel's limits (%d / 32)", experts, used, ROUTE_MAX_EXPERTS);
+    YK_REQUIRE(experts <= hidden, YUUKA_ERR_UNSUPPORTED, "moe: more experts (%d) than hidden columns (%d)", experts, hidden);
     RouteParams p{xn, router, sh_gate, hidden, experts, used, ids, weights, shared_gate};
-    const size_t smem = sizeof(float) * ((size_t)hidden + experts);
+    const size_t smem = sizeof(float) * (size_t)ROUTE_ROWS * (size_t)hidden;
+    YK_REQUIRE(smem <= 200 * 1024, YUUKA_ERR_UNSUPPORTED, "moe: hidden size %d is too wide for the router kernel", hidden);
     YK_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    launch_k(moe_route_kernel, rows, ROUTE_THREADS, smem, s, p);
+    dim3 grid((rows + ROUTE_ROWS - 1) / ROUTE_ROWS, (experts + 1 + ROUTE_EXPERTS - 1) / ROUTE_EXPERTS);
+    launch_k(moe_route_kernel, grid, ROUTE_THREADS, smem, s, p, rows, logits, counters);
     YK_CUDA(cudaGetLastError());
 }
 
