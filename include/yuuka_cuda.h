@@ -322,6 +322,31 @@ YUUKA_API yuuka_stream * yuuka_session_stream(yuuka_session * s);
 /* Kernel launches enqueued by the last yuuka_verify_launch. */
 YUUKA_API uint32_t yuuka_session_last_launch_count(const yuuka_session * s);
 
+/* ------------------------------------------------------------------------
+ * Host-side block allocator and block-table helpers (memory.Allocator and
+ * memory.Table, memory/memory.go:34-266). The free list is LIFO and starts
+ * descending, so a fresh allocator hands out block 0 first. No evictor hook:
+ * an exhausted pool answers YUUKA_ERR_ALLOCATION (ErrOutOfBlocks).
+ * ---------------------------------------------------------------------- */
+typedef struct yuuka_allocator yuuka_allocator;
+typedef struct yuuka_allocator_stats {
+    int32_t block_size, total, used, free, shared;
+    uint64_t allocated, released;
+} yuuka_allocator_stats;
+YUUKA_API yuuka_status yuuka_allocator_create(int32_t blocks, int32_t block_size, yuuka_allocator ** out);
+YUUKA_API void yuuka_allocator_destroy(yuuka_allocator * a);
+YUUKA_API yuuka_status yuuka_allocator_acquire(yuuka_allocator * a, int32_t * id);
+YUUKA_API yuuka_status yuuka_allocator_retain(yuuka_allocator * a, int32_t id);
+YUUKA_API yuuka_status yuuka_allocator_release(yuuka_allocator * a, int32_t id);
+YUUKA_API int32_t yuuka_allocator_refs(yuuka_allocator * a, int32_t id);
+YUUKA_API yuuka_status yuuka_allocator_stats_get(yuuka_allocator * a, yuuka_allocator_stats * out);
+/* Table.Cover: grows blocks[0 .. *count) (room for `capacity` ids) until `positions` token positions are
+ * mapped; all or nothing. Table.Map: position -> (block id, offset in block). */
+YUUKA_API yuuka_status yuuka_table_cover(yuuka_allocator * a, int32_t * blocks, int32_t * count, int32_t capacity,
+                                         int32_t positions);
+YUUKA_API yuuka_status yuuka_table_map(const int32_t * blocks, int32_t count, int32_t block_size, int32_t pos,
+                                       int32_t * block, int32_t * offset);
+
 /* Geometry of a session, for callers that drive it generically. */
 typedef struct yuuka_session_info {
     int32_t max_batch, max_nodes, capacity, block_size, pool_blocks, kv_format;

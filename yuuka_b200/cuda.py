@@ -117,6 +117,15 @@ SIGNATURES = {
                                 _u32, _u32, _vp]),
     "yuuka_gemm_quant_static": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _vp, _u64, _u32, _u64, _u64, _u64,
                                 _u32, _u32, _vp]),
+    "yuuka_allocator_create": (_i32, [_i32, _i32, _vp]),
+    "yuuka_allocator_destroy": (None, [_vp]),
+    "yuuka_allocator_acquire": (_i32, [_vp, _vp]),
+    "yuuka_allocator_retain": (_i32, [_vp, _i32]),
+    "yuuka_allocator_release": (_i32, [_vp, _i32]),
+    "yuuka_allocator_refs": (_i32, [_vp, _i32]),
+    "yuuka_allocator_stats_get": (_i32, [_vp, _vp]),
+    "yuuka_table_cover": (_i32, [_vp, _vp, _vp, _i32, _i32]),
+    "yuuka_table_map": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
     "yuuka_session_info_get": (_i32, [_vp, _vp]),
     "yuuka_spec_options_normalize": (None, [_vp]),
     "yuuka_spec_lookup_draft": (_i32, [_vp, _i32, _i32, _i32, _vp]),
@@ -299,6 +308,64 @@ def gemm_quant(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: int, n_o
                out_offset: int = 0, x_offset: int = 0, w_offset: int = 0, completion: Event | None = None):
     check(lib().yuuka_gemm_quant(stream.h, out.h, out_offset, x.h, x_offset, x_dtype, w.h, w_offset, w_dtype,
                                  n_in, n_out, rows, path, flags, completion.h if completion else None))
+
+
+class AllocatorStats(C.Structure):
+    _fields_ = [("block_size", C.c_int32), ("total", C.c_int32), ("used", C.c_int32), ("free", C.c_int32),
+                ("shared", C.c_int32), ("allocated", C.c_uint64), ("released", C.c_uint64)]
+
+
+class Allocator:
+    """memory.Allocator (memory/memory.go:34-179) behind the C ABI."""
+
+    def __init__(self, blocks: int, block_size: int):
+        self.h = C.c_void_p()
+        check(lib().yuuka_allocator_create(blocks, block_size, C.byref(self.h)))
+        self.block_size = block_size
+
+    def acquire(self) -> int:
+        i = C.c_int32()
+        check(lib().yuuka_allocator_acquire(self.h, C.byref(i)))
+        return i.value
+
+    def retain(self, block: int):
+        check(lib().yuuka_allocator_retain(self.h, block))
+
+    def release(self, block: int):
+        check(lib().yuuka_allocator_release(self.h, block))
+
+    def refs(self, block: int) -> int:
+        return lib().yuuka_allocator_refs(self.h, block)
+
+    def stats(self) -> AllocatorStats:
+        st = AllocatorStats()
+        check(lib().yuuka_allocator_stats_get(self.h, C.byref(st)))
+        return st
+
+    def close(self):
+        if self.h:
+            lib().yuuka_allocator_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class Table:
+    """memory.Table Cover / Map / Blocks (memory/memory.go:181-266) over an Allocator."""
+
+    def __init__(self, alloc: Allocator, capacity_blocks: int):
+        self.alloc = alloc
+        self._blocks = np.zeros(max(capacity_blocks, 1), np.int32)
+        self._count = C.c_int32(0)
+
+    def cover(self, positions: int):
+        check(lib().yuuka_table_cover(self.alloc.h, self._blocks.ctypes.data, C.byref(self._count), self._blocks.size, positions))
+
+    def blocks(self) -> np.ndarray:
+        return self._blocks[:self._count.value].copy()
+
+    def map(self, pos: int) -> tuple[int, int]:
+        b, o = C.c_int32(), C.c_int32()
+        check(lib().yuuka_table_map(self._blocks.ctypes.data, self._count.value, self.alloc.block_size, pos, C.byref(b), C.byref(o)))
+        return b.value, o.value
 
 
 FINISH_LENGTH, FINISH_STOP = 0, 1
