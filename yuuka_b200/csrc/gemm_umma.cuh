@@ -481,14 +481,16 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
 }
 
 // ---------------------------------------------------------------------------
-// Warp-specialised variant (tensor-map activations only): eight decode warps and one control warp.
+// Warp-specialised variant (tensor-map activations only): eight decode warps, a copy warp and an issue warp.
 // The decode warps never meet at a CTA-wide barrier inside a block of rows: each announces its
 // share of a stage on afull_bar (eight arrivals) and moves on to the next stage as soon as
-// empty_bar says the tensor pipe has drained it. Lane 0 of the control warp keeps the activation
-// copies UM_AHEAD chunks ahead, waits for (activations landed, weights decoded), issues the MMAs
-// and commits the stage back. tmem_free_bar (eight arrivals) tells it that the epilogue has read
-// the accumulator before the next block of rows overwrites it.
-constexpr int UM_WS_THREADS = (TW + 1) * 32;
+// empty_bar says the tensor pipe has drained it. Lane 0 of the copy warp starts the activation copy of
+// a stage as soon as it is free; lane 0 of the issue warp waits for (activations landed, weights
+// decoded), issues the MMAs and commits the stage back. tmem_free_bar (eight arrivals) tells it that
+// the epilogue has read the accumulator before the next block of rows overwrites it. (Sixteen decode
+// warps, two per tile on alternate chunks, measured slower on wide matrices: 96 registers per thread
+// spill and the doubled scale tables cost a ring stage.)
+constexpr int UM_WS_THREADS = (TW + 2) * 32;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -550,12 +552,15 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
 
     pdl_trigger();
     if (warp == TW) {
-        // ---------------- control warp ----------------
+        // ---------------- copy warp: starts the activation copy of a stage as soon as it is free ----------------
         pdl_wait();
         if (lane == 0) {
             // ring positions are advanced by hand: the ring depth is a run-time value and a division per
-            // chunk on this thread's critical path would cost more than the MMAs it issues
-            auto issue_x = [&](uint32_t stage, uint32_t in_block) {
+            // chunk on a single thread's critical path would cost more than the work it issues
+            uint32_t stage = 0, use = 0, in_block = 0;
+            for (uint32_t n = 0; n < total_chunks; n++) {
+                if (use > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[stage]), (use - 1) & 1))
+                    expired = true;
                 const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xfull_bar[stage]);
                 const int col0 = sb_begin * 256 + (int)in_block * UM_KC;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
@@ -564,24 +569,17 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                     :
                     : "r"(smem_base + stage * stage_bytes + UM_A_BYTES), "l"(&xmap), "r"(col0), "r"(0), "r"(bar)
                     : "memory");
-            };
-            uint32_t nstage = 0, nuse = 0, n_in_block = 0;  // chunk n = c + UM_AHEAD
-            auto advance_n = [&]() {
-                if (++nstage == p.stages) { nstage = 0; nuse++; }
-                if (++n_in_block == (uint32_t)chunks_per_block) n_in_block = 0;
-            };
-            for (uint32_t ci = 0; ci < UM_AHEAD && ci < total_chunks; ci++) {
-                issue_x(nstage, n_in_block);
-                advance_n();
+                if (++stage == p.stages) { stage = 0; use++; }
+                if (++in_block == (uint32_t)chunks_per_block) in_block = 0;
             }
+        }
+        __syncwarp();
+    } else if (warp == TW + 1) {
+        // ---------------- issue warp: (activations landed, weights decoded) -> MMAs -> stage released ----------------
+        if (lane == 0) {
             uint32_t stage = 0, use = 0, in_block = 0, blk = 0;
+            uint32_t a_addr = smem_base, b_addr = smem_base + UM_A_BYTES;
             for (uint32_t c = 0; c < total_chunks; c++) {
-                if (c + UM_AHEAD < total_chunks) {
-                    if (nuse > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[nstage]), (nuse - 1) & 1))
-                        expired = true;
-                    issue_x(nstage, n_in_block);
-                    advance_n();
-                }
                 // the epilogue of the previous block must have read the accumulator
                 if (in_block == 0 && blk > 0 && !expired &&
                     !mbar_wait((uint32_t)__cvta_generic_to_shared(&tmem_free_bar), (blk - 1) & 1))
@@ -589,8 +587,8 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                 if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&xfull_bar[stage]), use & 1)) expired = true;
                 if (!expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&afull_bar[stage]), use & 1)) expired = true;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = umma_desc(smem_base + stage * stage_bytes, UM_A_LBO, UM_A_SBO);
-                const uint64_t db = umma_desc_sw128(smem_base + stage * stage_bytes + UM_A_BYTES);
+                const uint64_t da = umma_desc(a_addr, UM_A_LBO, UM_A_SBO);
+                const uint64_t db = umma_desc_sw128(b_addr);
 #pragma unroll
                 for (int j = 0; j < UM_KC / 16; j++) {
                     const uint32_t accumulate = (in_block > 0 || j > 0) ? 1u : 0u;
@@ -609,7 +607,14 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                      (uint32_t)__cvta_generic_to_shared(&done_bar))
                                  : "memory");
-                if (++stage == p.stages) { stage = 0; use++; }
+                a_addr += stage_bytes;
+                b_addr += stage_bytes;
+                if (++stage == p.stages) {
+                    stage = 0;
+                    use++;
+                    a_addr = smem_base;
+                    b_addr = smem_base + UM_A_BYTES;
+                }
                 if (++in_block == (uint32_t)chunks_per_block) { in_block = 0; blk++; }
             }
         }
@@ -692,7 +697,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                     }
                 }
             }
-            // the accumulator has been read: the control warp may start the next block of rows
+            // the accumulator has been read: the issue warp may start the next block of rows
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive((uint32_t)__cvta_generic_to_shared(&tmem_free_bar));
