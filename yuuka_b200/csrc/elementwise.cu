@@ -61,7 +61,8 @@ __device__ __forceinline__ double block_sum_d(double v, double * red) {
 // scale = f32(1/sqrt(f64(mean + eps))), dst = src * scale * weight. Also emits the
 // prepared (fp16 + group sums) form of dst for the GEMM that consumes it.
 __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
-                               const float * __restrict__ weight, int cols, float eps, XPrepOut prep) {
+                               const float * __restrict__ weight, int cols, float eps, XPrepOut prep,
+                               unsigned long long * __restrict__ sumsq_out) {
     pdl_entry();
     __shared__ double red[32];
     const int r = blockIdx.x;
@@ -69,6 +70,8 @@ __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * 
     double sum = 0;
     for (int i = threadIdx.x; i < cols; i += blockDim.x) sum += (double)x[i] * (double)x[i];
     sum = block_sum_d(sum, red);
+    // (for GEMMs that fold the next norm in: this row's sum of squares in 2^-24 units)
+    if (sumsq_out && threadIdx.x == 0) sumsq_out[r] = (unsigned long long)(sum * 16777216.0);
     float mean = (float)(sum / (double)cols);
     float scale = (float)(1.0 / sqrt((double)(mean + eps)));
     if ((cols & 15) == 0) {
@@ -87,10 +90,10 @@ __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * 
 }
 
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight, int cols,
-                    int rows, float eps, XPrepOut prep) {
+                    int rows, float eps, XPrepOut prep, unsigned long long * sumsq_out) {
     YK_REQUIRE(!prep.xh || ((cols & 15) == 0 && (ldd & 3) == 0), YUUKA_ERR_UNSUPPORTED,
                "rmsnorm: prepared output needs a width that is a multiple of 16");
-    launch_k(rmsnorm_kernel, rows, 256, 0, s, dst, ldd, src, lds, weight, cols, eps, prep);
+    launch_k(rmsnorm_kernel, rows, 256, 0, s, dst, ldd, src, lds, weight, cols, eps, prep, sumsq_out);
     YK_CUDA(cudaGetLastError());
 }
 

@@ -519,6 +519,13 @@ struct yuuka_session {
     int * gdn_counters = nullptr;
     int * post_counter = nullptr;
     bool fuse_post_norm = false;
+    // RMSNorm folded into the GEMMs around it (NormFuse): one row of fixed-point sums of squares per norm
+    // point of a step, zeroed when the step starts; norm_point indexes the row behind the current prep_xn
+    bool fold_norm = false;          // the model allows it (every consumer and producer matrix is tile-ordered)
+    bool fold_step = false;          // ... and this step's row count does
+    unsigned long long * norm_sumsq = nullptr;  // [norm points][32]
+    int norm_point = 0;
+    bool xn_raw = false;             // prep_xn holds x * w * pre of norm_point (not normalised rows)
     int chain_rows = 0;  // rows per prompt chunk (prefill_logits / forward)
     // L2 prefetch of the next GEMM's weights: matrices in the order a step streams them
     bool prefetch_next = true;
@@ -566,7 +573,7 @@ void mark(yuuka_session * s, uint32_t code) {
 }
 
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOut prep, float * out, int ldo, int rows,
-          uint32_t flags, const GemmPostNorm * post = nullptr) {
+          uint32_t flags, const GemmPostNorm * post = nullptr, const float * produce_norm_w = nullptr) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     if (w.tiled) {
         TiledGemmArgs t;
@@ -585,6 +592,22 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.flags = flags;
         t.scratch = &s->gemm;
         if (post) t.post = *post;
+        if (s->fold_step) {
+            const yuuka_model_config & mc = s->model->cfg;
+            t.norm.eps = mc.rms_eps;
+            t.norm.cols = mc.hidden;
+            if (prep.xh == s->prep_xn.xh && s->xn_raw) {
+                // the rows in prep_xn are x * w * pre, not normalised: this GEMM applies scale / pre
+                t.norm.consume_now = s->norm_sumsq + (size_t)s->norm_point * 32;
+                t.norm.consume_prev = s->norm_sumsq + (size_t)(s->norm_point - 1) * 32;
+            }
+            if (produce_norm_w) {
+                t.norm.produce_w = produce_norm_w;
+                t.norm.produce_prev = s->norm_sumsq + (size_t)s->norm_point * 32;
+                t.norm.produce_sumsq = s->norm_sumsq + (size_t)(s->norm_point + 1) * 32;
+                t.norm.produce_prep = s->prep_xn;
+            }
+        }
         if (s->prefetch_next) {
             // where this matrix sits in the step's order, and what follows it
             const auto & order = s->gemm_order;
@@ -639,6 +662,13 @@ void gemm_residual_norm(yuuka_session * s, const Tensor & w, const float * in, i
         gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, &post);
         return;
     }
+    if (s->fold_step && norm_w) {
+        // the norm rides on this GEMM (producer) and on the next one to read prep_xn (consumer)
+        gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, nullptr, norm_w);
+        s->norm_point++;
+        s->xn_raw = true;
+        return;
+    }
     gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE);
     if (norm_w) {
         mark(s, YUUKA_OP_RMSNORM);
@@ -672,9 +702,15 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     mark(s, YUUKA_OP_EMBEDDING);
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
-    // the first layer's input norm; every later norm rides on the GEMM that finishes the residual stream
+    // the first layer's input norm is a kernel of its own; with 3..32 rows every later norm is folded into
+    // the GEMM that finishes the residual rows and the GEMM that reads them
+    s->fold_step = s->fold_norm && R >= 3 && R <= 32;
+    s->norm_point = 0;
+    s->xn_raw = false;
+    if (s->fold_step) YK_CUDA(cudaMemsetAsync(s->norm_sumsq, 0, sizeof(unsigned long long) * 32 * (size_t)(2 * c.block_count + 2), st));
     mark(s, YUUKA_OP_RMSNORM);
-    launch_rmsnorm(st, s->xn, H, s->x, H, m->layers[0].attn_norm, H, R, c.rms_eps, s->prep_xn);
+    launch_rmsnorm(st, s->xn, H, s->x, H, m->layers[0].attn_norm, H, R, c.rms_eps, s->prep_xn,
+                   s->fold_step ? s->norm_sumsq : nullptr);
     s->launches++;
     for (int i = 0; i < c.block_count; i++) {
         const LayerW & L = m->layers[i];
@@ -850,6 +886,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         // batch == 1: only the last row
         mark(s, YUUKA_OP_RMSNORM);
         launch_rmsnorm(st, s->xn, H, s->x + (int64_t)(R - 1) * H, H, m->output_norm, H, 1, c.rms_eps, s->prep_xn);
+        s->xn_raw = false;
         s->launches++;
         gemm(s, m->output, s->xn, H, s->prep_xn, s->logits + (int64_t)(R - 1) * c.vocab, c.vocab, 1, 0);
     }
@@ -1023,6 +1060,19 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->cfg = sc;
             if (const char * e = getenv("YUUKA_CUDA_NO_GRAPH")) s->use_graphs = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_FUSE_NORM")) s->fuse_post_norm = e[0] == '1';
+            {
+                // norm folding needs every matrix on either side of a norm in the tile-ordered form
+                bool ok = c.expert_count == 0 && c.hidden % 16 == 0 && model->output.tiled;
+                for (int i = 0; i < c.block_count && ok; i++) {
+                    const LayerW & L = model->layers[i];
+                    if (model->recurrent(i)) ok = L.proj.tiled && L.out.tiled;
+                    else ok = L.qk.tiled && (L.qk_has_v || L.v.tiled) && L.o.tiled;
+                    ok = ok && L.gate_up.tiled && L.ffn_down.tiled;
+                }
+                if (const char * e = getenv("YUUKA_CUDA_NO_FOLD_NORM")) ok = ok && !(e[0] == '1');
+                s->fold_norm = ok;
+                if (ok) s->norm_sumsq = dalloc<unsigned long long>((size_t)32 * (2 * c.block_count + 2), s->owned);
+            }
             if (const char * e = getenv("YUUKA_CUDA_NO_PREFETCH")) s->prefetch_next = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_PREFETCH_MB")) s->prefetch_bytes = (uint64_t)atoi(e) << 20;
             for (const LayerW & L : model->layers) {

@@ -617,11 +617,36 @@ struct TParams {
     const GemmSegment * segments;
     size_t expert_stride;
     const int32_t * row_index;
+    // optional, RMSNorm folded into the GEMMs on either side of it (see NormFuse in gemm_tiled.cuh):
+    // as the producer of a residual row this launch also writes fp16(x * nf_w * pre) with its 16-column
+    // sums and adds each row's sum of squares to nf_sumsq; as the consumer of such rows it multiplies its
+    // output rows by scale / pre. pre is the previous norm's scale of the row (from *_prev), which keeps
+    // the unnormalised fp16 values near unit range.
+    const float * nf_w;
+    const unsigned long long * nf_prev;  // producer: sums of squares behind `pre` (null: pre = 1)
+    unsigned long long * nf_sumsq;
+    __half * nf_xh;
+    __half2 * nf_xs16;
+    const unsigned long long * cs_now;   // consumer: sums of squares of its input rows
+    const unsigned long long * cs_prev;  // (null: pre = 1)
+    float nf_eps;
+    int nf_cols;                         // row width the sums of squares run over
     // optional: the matrix the next GEMM of the step will stream; its first bytes are asked into L2
     // while this kernel drains and the small kernels in between run
     const uint8_t * next_w;
     uint32_t next_lines;  // 128-byte lines
 };
+
+// 1 / rms of a row from its fixed-point sum of squares (2^-24 units). rmsNorm (model/qwen35/forward.go:
+// 460-470) takes 1 / sqrt in f64 and rounds to f32; here it is the f32 reciprocal square root (2 ulp), in
+// single precision throughout because every lane of every epilogue evaluates it: the f64 form cost more
+// than the kernels it replaced. Producer and consumer use this same function, so `pre` cancels exactly.
+constexpr float NF_INV_UNIT = 1.0f / 16777216.0f;
+__device__ __forceinline__ float nf_scale(unsigned long long sumsq, int cols, float eps) {
+    const float mean = __fdividef((float)sumsq * NF_INV_UNIT, (float)cols);
+    return rsqrtf(mean + eps);
+}
+__device__ __forceinline__ unsigned long long nf_fixed(float v) { return (unsigned long long)(v * 16777216.0f); }
 
 // rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
 // one warp per row, emitting f32 and the prepared form.
@@ -661,7 +686,8 @@ __device__ void post_rmsnorm_rows(const TParams & p, int warp, int lane) {
 // GROUPED: blockIdx.z walks a device-built list of row segments, each bound to one expert's matrix
 // (qwen35moe expert FFNs). A segment's rows are contiguous in the prepared-activation and output
 // arrays unless row_index redirects the activation rows.
-template <int DT, int NT, bool GROUPED>
+// FOLD: the RMSNorm on either side of this GEMM is folded into its epilogue (TParams::nf_* / cs_*).
+template <int DT, int NT, bool GROUPED, bool FOLD>
 __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParams p) {
     using C = Codec<DT>;
     using MM = Mma<DT, NT>;
@@ -854,15 +880,52 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             const int n_g = rt * 16 + g, n_h = n_g + 8;
             float * base = p.kchunks == 1 ? outp : p.partial + (size_t)blockIdx.y * Mrows * p.N;
             const int64_t ld = p.kchunks == 1 ? p.ldo : p.N;
+            const bool produce = FOLD && p.nf_w != nullptr && p.kchunks == 1;
 #pragma unroll
             for (int j = 0; j < NT; j++)
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int tok = 8 * j + 2 * t + (c & 1), n = (c & 2) ? n_h : n_g;
-                    if (tok < Mrows && n < p.N) {
-                        float * dst = base + (int64_t)tok * ld + n;
-                        if (p.kchunks == 1) *dst = p.accumulate ? *dst + acc[j][c] : acc[j][c];
-                        else __stcg(dst, acc[j][c]);
+                for (int e = 0; e < 2; e++) {
+                    const int tok = 8 * j + 2 * t + e;
+                    const bool tok_ok = tok < Mrows;
+                    float cs = 1.0f;
+                    if (FOLD && p.cs_now && p.kchunks == 1 && tok_ok)
+                        cs = nf_scale(p.cs_now[tok], p.nf_cols, p.nf_eps) /
+                             (p.cs_prev ? nf_scale(p.cs_prev[tok], p.nf_cols, p.nf_eps) : 1.0f);
+                    float v[2] = {0.0f, 0.0f};  // final values of columns n_g, n_h (producer only)
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        const int c = 2 * hh + e, n = hh ? n_h : n_g;
+                        if (tok_ok && n < p.N) {
+                            float * dst = base + (int64_t)tok * ld + n;
+                            if (p.kchunks == 1) {
+                                v[hh] = p.accumulate ? *dst + acc[j][c] * cs : acc[j][c] * cs;
+                                *dst = v[hh];
+                            } else {
+                                __stcg(dst, acc[j][c]);
+                            }
+                        }
+                    }
+                    if (produce) {
+                        // this tile is one 16-column group of the row: fp16(x * w * pre), the group sum, the squares
+                        const float pre = (p.nf_prev && tok_ok) ? nf_scale(p.nf_prev[tok], p.nf_cols, p.nf_eps) : 1.0f;
+                        const __half q_g = __float2half_rn(v[0] * pre * (n_g < p.N ? p.nf_w[n_g] : 0.0f));
+                        const __half q_h = __float2half_rn(v[1] * pre * (n_h < p.N ? p.nf_w[n_h] : 0.0f));
+                        float gs = __half2float(q_g) + __half2float(q_h);
+                        float sq = v[0] * v[0] + v[1] * v[1];
+#pragma unroll
+                        for (int o = 4; o < 32; o <<= 1) {
+                            gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        }
+                        if (tok_ok) {
+                            if (n_g < p.N) p.nf_xh[(size_t)tok * p.N + n_g] = q_g;
+                            if (n_h < p.N) p.nf_xh[(size_t)tok * p.N + n_h] = q_h;
+                            if (g == 0) {
+                                const __half hi = __float2half_rn(gs);
+                                p.nf_xs16[(size_t)tok * (p.N >> 4) + rt] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+                                atomicAdd(&p.nf_sumsq[tok], nf_fixed(sq));
+                            }
+                        }
                     }
                 }
         }
@@ -875,12 +938,41 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             if (last_flag) {
                 __threadfence();
                 const int row0 = grp * p.TG * 16, nrows = min(p.TG * 16, p.N - row0);
-                for (int i = threadIdx.x; i < Mrows * nrows; i += TW * 32) {
-                    const int tok = i / nrows, n = row0 + (i - tok * nrows);
+                // (with the norm folded in, N is a multiple of 16: a half warp holds one 16-column group of a row)
+                const int padded = (FOLD && p.nf_w) ? ((Mrows * nrows + 31) & ~31) : Mrows * nrows;
+                for (int i = threadIdx.x; i < padded; i += TW * 32) {
+                    const bool live = i < Mrows * nrows;
+                    const int tok = live ? i / nrows : 0, n = row0 + (live ? i - tok * nrows : 0);
                     float s = 0.0f;
-                    for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * Mrows + tok) * p.N + n);
-                    float * dst = outp + (int64_t)tok * p.ldo + n;
-                    *dst = p.accumulate ? *dst + s : s;
+                    if (live)
+                        for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * Mrows + tok) * p.N + n);
+                    if (FOLD && p.cs_now && live)
+                        s *= nf_scale(p.cs_now[tok], p.nf_cols, p.nf_eps) /
+                             (p.cs_prev ? nf_scale(p.cs_prev[tok], p.nf_cols, p.nf_eps) : 1.0f);
+                    float v = 0.0f;
+                    if (live) {
+                        float * dst = outp + (int64_t)tok * p.ldo + n;
+                        v = p.accumulate ? *dst + s : s;
+                        *dst = v;
+                    }
+                    if (FOLD && p.nf_w) {
+                        const float pre = (p.nf_prev && live) ? nf_scale(p.nf_prev[tok], p.nf_cols, p.nf_eps) : 1.0f;
+                        const __half qv = __float2half_rn(live ? v * pre * p.nf_w[n] : 0.0f);
+                        float gs = __half2float(qv), sq = v * v;
+#pragma unroll
+                        for (int o = 1; o < 16; o <<= 1) {
+                            gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        }
+                        if (live) {
+                            p.nf_xh[(size_t)tok * p.N + n] = qv;
+                            if ((lane & 15) == 0) {
+                                const __half hi = __float2half_rn(gs);
+                                p.nf_xs16[(size_t)tok * (p.N >> 4) + (n >> 4)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+                                atomicAdd(&p.nf_sumsq[tok], nf_fixed(sq));
+                            }
+                        }
+                    }
                 }
                 if (threadIdx.x == 0) p.counters[grp] = 0;
             }
@@ -1181,7 +1273,8 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
 template <int DT, int NT>
 static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
                             const TPlan & pl) {
-    auto kern = gemm_tiled_mma_kernel<DT, NT, false>;
+    const bool fold = a.norm.produce_w || a.norm.consume_now;
+    auto kern = fold ? gemm_tiled_mma_kernel<DT, NT, false, true> : gemm_tiled_mma_kernel<DT, NT, false, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
     p.kc = decode_consts(DT);
@@ -1201,6 +1294,17 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     p.n_groups = pl.n_groups;
     p.partial = a.scratch ? a.scratch->partial : nullptr;
     p.counters = a.scratch ? a.scratch->counters : nullptr;
+    if (a.norm.produce_w || a.norm.consume_now) {
+        p.nf_w = a.norm.produce_w;
+        p.nf_prev = a.norm.produce_prev;
+        p.nf_sumsq = a.norm.produce_sumsq;
+        p.nf_xh = a.norm.produce_prep.xh;
+        p.nf_xs16 = a.norm.produce_prep.xs16;
+        p.cs_now = a.norm.consume_now;
+        p.cs_prev = a.norm.consume_prev;
+        p.nf_eps = a.norm.eps;
+        p.nf_cols = a.norm.cols;
+    }
     if (a.next_w && m0 + 32 >= a.rows) {
         p.next_w = a.next_w;
         p.next_lines = (uint32_t)(a.next_bytes / 128);
@@ -1236,7 +1340,7 @@ static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const Gr
     const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
     YK_REQUIRE(pl.smem <= half_sm && pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
                "grouped gemm: %d columns of activations do not fit shared memory", a.n_in);
-    auto kern = gemm_tiled_mma_kernel<DT, 1, true>;
+    auto kern = gemm_tiled_mma_kernel<DT, 1, true, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
     p.kc = decode_consts(DT);
@@ -1450,6 +1554,14 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
     YK_REQUIRE(!a.post.norm_w || (a.post.dst && a.post.counter && a.n_out % 16 == 0 && a.ldo % 4 == 0 && a.post.ld % 4 == 0),
                YUUKA_ERR_INVALID_ARGUMENT, "gemm: the fused RMSNorm needs a destination, a counter and a width that is a multiple of 16");
     YK_REQUIRE(a.rows > 0 && a.n_out > 0 && a.n_in > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: invalid shape");
+    if (a.norm.produce_w || a.norm.consume_now) {
+        const uint32_t route = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
+        YK_REQUIRE(route == YUUKA_GEMM_PATH_MMA && a.rows <= 32 && (a.rows < UMMA_MIN_ROWS || !umma_enabled()),
+                   YUUKA_ERR_INTERNAL, "gemm: the folded RMSNorm runs on the register-fed mma route only (3..32 rows)");
+        YK_REQUIRE(!a.norm.produce_w || (a.n_out % 16 == 0 && a.norm.produce_sumsq && a.norm.produce_prep.xh && a.norm.produce_prep.xs16),
+                   YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs a width that is a multiple of 16 and its outputs");
+        YK_REQUIRE(a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
+    }
     YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u / width %d has no tiled layout",
                a.w_dtype, a.n_in);
     YK_REQUIRE(a.x_dtype == YUUKA_DTYPE_F32 || a.x_dtype == YUUKA_DTYPE_BF16, YUUKA_ERR_UNSUPPORTED,

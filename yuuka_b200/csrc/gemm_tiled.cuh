@@ -70,6 +70,24 @@ struct GroupedGemmArgs {
 };
 int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, const GroupedGemmArgs & a);
 
+// RMSNorm folded into the GEMMs around it (register-fed mma route, 3..32 rows). A GEMM that finishes
+// residual rows x (producer) also writes the prepared input of the next GEMM, fp16(x * w * pre) with its
+// 16-column sums, and adds every row's sum of squares (fixed point, 2^-24 units, integer atomics: the
+// result does not depend on the order of the CTAs) to produce_sumsq, which the caller zeroed. The GEMM
+// that reads those rows (consumer) multiplies its output rows by scale / pre, scale = 1 / rms(x) from
+// consume_now. pre = the scale of the row at the previous norm (produce_prev / consume_prev, null: 1)
+// keeps the unnormalised fp16 values near unit range whatever the magnitude of the residual stream.
+struct NormFuse {
+    const float * produce_w = nullptr;
+    const unsigned long long * produce_prev = nullptr;
+    unsigned long long * produce_sumsq = nullptr;
+    XPrepOut produce_prep;
+    const unsigned long long * consume_now = nullptr;
+    const unsigned long long * consume_prev = nullptr;
+    float eps = 0.0f;
+    int cols = 0;
+};
+
 struct TiledGemmArgs {
     const uint8_t * w = nullptr;  // tiled layout
     uint32_t w_dtype = 0;
@@ -84,6 +102,7 @@ struct TiledGemmArgs {
     uint32_t flags = 0;
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     GemmPostNorm post;
+    NormFuse norm;
     const uint8_t * next_w = nullptr;  // optional L2 prefetch hint: the next matrix to be streamed (mma route)
     uint64_t next_bytes = 0;
 };

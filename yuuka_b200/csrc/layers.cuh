@@ -33,7 +33,8 @@ void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table,
                       int vocab, const int32_t * tokens, int rows);
 // dst[r][:] = src[r][:] * rsqrt(mean(src^2) + eps) * weight (forward.go:460-470)
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight,
-                    int cols, int rows, float eps, XPrepOut prep = XPrepOut());
+                    int cols, int rows, float eps, XPrepOut prep = XPrepOut(),
+                    unsigned long long * sumsq_out = nullptr);
 // act[r][i] = silu(gate[r][i]) * up[r][i] (forward.go:307-309)
 void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
                      int rows, XPrepOut prep = XPrepOut());
