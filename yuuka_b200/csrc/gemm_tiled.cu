@@ -694,6 +694,9 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t xbar;
     __shared__ int last_flag;
+    // folded norm: per input row scale / pre (consumer) and pre (producer); per warp the norm weights
+    // of its row tile, fetched at the top of each group so that the epilogue does not wait on memory
+    __shared__ float cs_s[FOLD ? 32 : 1], pre_s[FOLD ? 32 : 1], nw_s[FOLD ? 2 * TW * 16 : 1];
     const uint8_t * wbase = p.w;
     const __half * xhp = p.xh;
     const __half2 * xsp = p.xs16;
@@ -749,6 +752,20 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&xbar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if constexpr (FOLD) {
+        const int m = (int)threadIdx.x - 32;  // second warp: the first issues the copies
+        if (m >= 0 && m < 32) {
+            float cs = 1.0f, pre = 1.0f;
+            if (m < Mrows) {
+                if (p.cs_now)
+                    cs = nf_scale(__ldcg(p.cs_now + m), p.nf_cols, p.nf_eps) /
+                         (p.cs_prev ? nf_scale(__ldcg(p.cs_prev + m), p.nf_cols, p.nf_eps) : 1.0f);
+                if (p.nf_prev) pre = nf_scale(__ldcg(p.nf_prev + m), p.nf_cols, p.nf_eps);
+            }
+            cs_s[m] = cs;
+            pre_s[m] = pre;
+        }
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
@@ -803,6 +820,9 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         const int rt = grp * p.TG + tile_in_group;
         const int rtc = min(rt, n_tiles - 1);
         const uint8_t * tile = wbase + rtc * rec_row;
+        // (two copies by group parity: a warp may start its next group while others still run the split-K tail)
+        float * nw = nw_s + (FOLD ? (((grp - (int)blockIdx.x) / (int)gridDim.x) & 1) * (TW * 16) : 0);
+        if (FOLD && p.nf_w && lane < 16) nw[warp * 16 + lane] = rt * 16 + lane < p.N ? p.nf_w[rt * 16 + lane] : 0.0f;
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; j++)
@@ -887,10 +907,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                 for (int e = 0; e < 2; e++) {
                     const int tok = 8 * j + 2 * t + e;
                     const bool tok_ok = tok < Mrows;
-                    float cs = 1.0f;
-                    if (FOLD && p.cs_now && p.kchunks == 1 && tok_ok)
-                        cs = nf_scale(p.cs_now[tok], p.nf_cols, p.nf_eps) /
-                             (p.cs_prev ? nf_scale(p.cs_prev[tok], p.nf_cols, p.nf_eps) : 1.0f);
+                    const float cs = FOLD ? cs_s[tok & 31] : 1.0f;
                     float v[2] = {0.0f, 0.0f};  // final values of columns n_g, n_h (producer only)
 #pragma unroll
                     for (int hh = 0; hh < 2; hh++) {
@@ -907,9 +924,9 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                     }
                     if (produce) {
                         // this tile is one 16-column group of the row: fp16(x * w * pre), the group sum, the squares
-                        const float pre = (p.nf_prev && tok_ok) ? nf_scale(p.nf_prev[tok], p.nf_cols, p.nf_eps) : 1.0f;
-                        const __half q_g = __float2half_rn(v[0] * pre * (n_g < p.N ? p.nf_w[n_g] : 0.0f));
-                        const __half q_h = __float2half_rn(v[1] * pre * (n_h < p.N ? p.nf_w[n_h] : 0.0f));
+                        const float pre = pre_s[tok & 31];
+                        const __half q_g = __float2half_rn(v[0] * pre * nw[warp * 16 + g]);
+                        const __half q_h = __float2half_rn(v[1] * pre * nw[warp * 16 + g + 8]);
                         float gs = __half2float(q_g) + __half2float(q_h);
                         float sq = v[0] * v[0] + v[1] * v[1];
 #pragma unroll
@@ -946,9 +963,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                     float s = 0.0f;
                     if (live)
                         for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * Mrows + tok) * p.N + n);
-                    if (FOLD && p.cs_now && live)
-                        s *= nf_scale(p.cs_now[tok], p.nf_cols, p.nf_eps) /
-                             (p.cs_prev ? nf_scale(p.cs_prev[tok], p.nf_cols, p.nf_eps) : 1.0f);
+                    if (FOLD) s *= cs_s[tok & 31];
                     float v = 0.0f;
                     if (live) {
                         float * dst = outp + (int64_t)tok * p.ldo + n;
@@ -956,8 +971,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                         *dst = v;
                     }
                     if (FOLD && p.nf_w) {
-                        const float pre = (p.nf_prev && live) ? nf_scale(p.nf_prev[tok], p.nf_cols, p.nf_eps) : 1.0f;
-                        const __half qv = __float2half_rn(live ? v * pre * p.nf_w[n] : 0.0f);
+                        const int nl = n - row0;  // row tile nl / 16 of the group belongs to warp (nl / 16) * KS
+                        const __half qv = __float2half_rn(live ? v * pre_s[tok & 31] * nw[(nl >> 4) * p.KS * 16 + (nl & 15)] : 0.0f);
                         float gs = __half2float(qv), sq = v * v;
 #pragma unroll
                         for (int o = 1; o < 16; o <<= 1) {
