@@ -230,3 +230,48 @@ def test_argument_validation(tiny):
     with pytest.raises(cuda.YuukaError):
         cuda.Model(gm.dev, bad)
     sess.close()
+
+
+def _verify_rows(gm, prompt, rows):
+    sess = cuda.Session(gm, max_batch=1, max_nodes=len(rows), capacity=128, kv_format=cuda.KV_F32)
+    sess.forward(prompt, want_logits=False)
+    res = sess.verify([rows], want_logits=True)
+    logits = res.logits[0].copy()
+    sess.close()
+    return logits
+
+
+def test_folded_epilogues_match_their_own_kernels(tiny, monkeypatch):
+    """RMSNorm folded into the neighbouring GEMMs and silu(gate) * up finished in the gate|up GEMM's
+    epilogue, against the same step with the row-wise kernels launched on their own."""
+    cfg, gm, om = tiny
+    prompt = synth.uniform_i32(20, 0, cfg["vocab"], 61).tolist()
+    rows = synth.uniform_i32(9, 0, cfg["vocab"], 62).tolist()
+    folded = _verify_rows(gm, prompt, rows)
+    monkeypatch.setenv("YUUKA_CUDA_NO_FOLD_SWIGLU", "1")
+    own_silu = _verify_rows(gm, prompt, rows)
+    # the epilogue evaluates the expression of the silu kernel on the same sums: identical bits
+    assert np.array_equal(folded, own_silu)
+    monkeypatch.setenv("YUUKA_CUDA_NO_FOLD_NORM", "1")
+    plain = _verify_rows(gm, prompt, rows)
+    # the folded norm rounds x * w * pre to fp16 before the scale is known: close, not identical
+    assert float(np.max(np.abs(folded - plain))) <= 4e-3
+
+
+def test_wide_hidden_narrow_ffn_model_matches_oracle():
+    """hidden 4096 with FFN 256: few row tiles and a long K, so the gate|up GEMM splits K across CTAs and
+    the SwiGLU epilogue runs in the CTA that sums the parts."""
+    cfg = dict(synth.tiny_config(), block_count=2, full_attention_interval=2, hidden=4096, ffn=256, vocab=1024)
+    tensors = synth.make_model(cfg, "q4_k_m", seed=11, unit_norms=False)
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, tensors)
+    om = yo.Model(cfg, tensors)
+    prompt = synth.uniform_i32(12, 0, cfg["vocab"], 63).tolist()
+    rows = synth.uniform_i32(9, 0, cfg["vocab"], 64).tolist()
+    st = yo.State(om, 64, yo.KV_F32)
+    st.forward(prompt)
+    _, _, want = st.verify_chain(rows[0], np.array(rows[1:], np.int32), want_logits=True)
+    got = _verify_rows(gm, prompt, rows)
+    err = float(np.max(np.abs(got - want)))
+    assert err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
+    st.close(); gm.close(); dev.close()

@@ -149,4 +149,41 @@ inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     YK_CUDA(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
 }
+
+// The same with thread-block clusters of cluster_x CTAs along x (gridDim.x a multiple of cluster_x).
+template <typename... KArgs, typename... Args>
+inline void launch_k_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, unsigned cluster_x,
+                             Args &&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = cluster_x;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    YK_CUDA(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
+}
+
+#if defined(__CUDACC__)
+// All threads of all CTAs of the cluster (hardware barrier; every CTA must reach it).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A double in the shared memory of CTA `rank` of this cluster, at the address `p` has in this CTA.
+__device__ __forceinline__ double ld_cluster_f64(const double * p, unsigned rank) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    double v;
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(remote) : "memory");
+    return v;
+}
+#endif
 }  // namespace yk

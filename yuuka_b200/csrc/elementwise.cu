@@ -103,13 +103,14 @@ __device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + ex
 __device__ __forceinline__ float silu_ref(float x) { return x * sigmoid_ref(x); }
 
 __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float * __restrict__ gate,
-                                const float * __restrict__ up, int ld, int cols, XPrepOut prep) {
+                                const float * __restrict__ up, int ld, int cols, XPrepOut prep, int gstride) {
     pdl_entry();
     const int r = blockIdx.y;
     for (int gq = blockIdx.x * blockDim.x + threadIdx.x; gq < (cols >> 4); gq += gridDim.x * blockDim.x) {
         float v[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = silu_ref(gate[(int64_t)r * ld + gq * 16 + i]) * up[(int64_t)r * ld + gq * 16 + i];
+        for (int i = 0; i < 16; i++)
+            v[i] = silu_ref(gate[(int64_t)r * ld + gq * gstride + i]) * up[(int64_t)r * ld + gq * gstride + i];
         float4 * d = reinterpret_cast<float4 *>(act + (int64_t)r * lda + gq * 16);
 #pragma unroll
         for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -117,11 +118,13 @@ __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float *
     }
 }
 
+// gstride: distance between consecutive 16-column groups of gate (and of up): 16 for plain rows, 32 when
+// gate and up alternate 16 columns at a time in one row.
 void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
-                     int rows, XPrepOut prep) {
+                     int rows, XPrepOut prep, int gstride) {
     YK_REQUIRE((cols & 15) == 0 && (lda & 3) == 0, YUUKA_ERR_UNSUPPORTED, "silu_mul: width must be a multiple of 16");
     dim3 grid(((cols >> 4) + 127) / 128, rows);
-    launch_k(silu_mul_kernel, grid, 128, 0, s, act, lda, gate, up, ld, cols, prep);
+    launch_k(silu_mul_kernel, grid, 128, 0, s, act, lda, gate, up, ld, cols, prep, gstride);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -134,7 +137,7 @@ struct PrepParams {
     const float * v; int ldv;
     const float * q_norm; const float * k_norm;
     int heads, kv_heads, hd, rope_dim;
-    double rope_base;
+    const float2 * rope_cs;  // [rows][rope_dim / 2] (cos, sin), see rope_table_kernel
     float eps;
     RowMeta rows;
     KvPool pool;
@@ -167,65 +170,85 @@ __device__ __forceinline__ int64_t kv_row_offset(const KvPool & pool, int seq, i
     return ((int64_t)block * pool.block_size + slot % pool.block_size) * pool.row_bytes;
 }
 
-// KVFormat.EncodeRow (model/qwen35/kv_format.go:75-131)
-__device__ void kv_encode_row(uint8_t * dst, int format, const float * src, int n) {
+// (cos, sin) of every row's RoPE angles, once per step: the rows keep their positions through all the
+// attention layers. Angles in f64 as the reference computes them (forward.go:503-505).
+__global__ void rope_table_kernel(float2 * __restrict__ cs, RowMeta rows, int rope_dim, double rope_base) {
+    pdl_entry();
+    const int r = blockIdx.x;
+    const int seq = r / rows.nodes;
+    const int pos = rows.pos0[seq] + rows.depth[r];
+    const int half = rope_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double theta = (double)pos * pow(rope_base, -2.0 * (double)i / (double)rope_dim);
+        cs[(int64_t)r * half + i] = make_float2((float)cos(theta), (float)sin(theta));
+    }
+}
+
+void launch_rope_table(cudaStream_t s, float2 * cs, const RowMeta & rows, int rope_dim, double rope_base) {
+    launch_k(rope_table_kernel, rows.batch * rows.nodes, 64, 0, s, cs, rows, rope_dim, rope_base);
+    YK_CUDA(cudaGetLastError());
+}
+
+// KVFormat.EncodeRow (model/qwen35/kv_format.go:75-131) for the n values of one head (n a multiple of
+// 32), by one warp; dst is the row in the pool, first the head's first element. Q8_0 blocks are 32
+// values, so a head's blocks are its own.
+__device__ void kv_encode_head(uint8_t * row, int format, const float * src, int first, int n) {
+    const int lane = threadIdx.x & 31;
     if (format == YUUKA_KV_F32) {
-        float * d = reinterpret_cast<float *>(dst);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = src[i];
+        float * d = reinterpret_cast<float *>(row) + first;
+        for (int i = lane; i < n; i += 32) d[i] = src[i];
     } else if (format == YUUKA_KV_F16) {
-        uint16_t * d = reinterpret_cast<uint16_t *>(dst);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = f32_to_f16_ref(src[i]);
+        uint16_t * d = reinterpret_cast<uint16_t *>(row) + first;
+        for (int i = lane; i < n; i += 32) d[i] = f32_to_f16_ref(src[i]);
     } else {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-        for (int blk = warp; blk < (n + 31) / 32; blk += nw) {
-            int i = blk * 32 + lane;
-            float v = i < n ? src[i] : 0.0f;
+        for (int blk = 0; blk < n / 32; blk++) {
+            const float v = src[blk * 32 + lane];
             float amax = fabsf(v);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            float scale = amax / 127.0f;
-            uint8_t * o = dst + blk * 34;
+            const float scale = amax / 127.0f;
+            uint8_t * o = row + (first / 32 + blk) * 34;
             if (lane == 0) *reinterpret_cast<uint16_t *>(o) = f32_to_f16_ref(scale);
             int8_t q = 0;
-            if (i < n && scale != 0.0f) q = (int8_t)(int)round((double)(v / scale));
+            if (scale != 0.0f) q = (int8_t)(int)round((double)(v / scale));
             o[2 + lane] = (uint8_t)q;
         }
     }
 }
 
-__global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
+// grid (rows, ceil((heads + 2 kv_heads) / 4)), one warp per unit of work: a query head (norm + RoPE in
+// place), a key head (norm + RoPE, then its slice of the pool row) or a value head (its slice of the pool row).
+__global__ void __launch_bounds__(128) attn_prep_kernel(const PrepParams p) {
     pdl_entry();
     const int r = blockIdx.x;
     const int seq = r / p.rows.nodes, node = r - seq * p.rows.nodes;
-    const int pos0 = p.rows.pos0[seq];
-    const int pos = pos0 + p.rows.depth[r];
-    const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    // angles in f64 as the reference computes them (forward.go:503-505), once per row
-    __shared__ float2 cs[128];
-    for (int i = threadIdx.x; i < p.rope_dim / 2; i += blockDim.x) {
-        double theta = (double)pos * pow(p.rope_base, -2.0 * (double)i / (double)p.rope_dim);
-        cs[i] = make_float2((float)cos(theta), (float)sin(theta));
-    }
-    __syncthreads();
-    for (int h = warp; h < p.heads + p.kv_heads; h += nw) {
-        if (h < p.heads)
-            norm_rope_head(p.q + (int64_t)r * p.ldq + (int64_t)h * 2 * p.hd, p.q_norm, p.hd, p.rope_dim, cs, p.eps);
-        else
-            norm_rope_head(p.k + (int64_t)r * p.ldk + (int64_t)(h - p.heads) * p.hd, p.k_norm, p.hd, p.rope_dim, cs, p.eps);
-    }
-    __syncthreads();
+    const int unit = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= p.heads + 2 * p.kv_heads) return;
+    const float2 * cs = p.rope_cs + (int64_t)r * (p.rope_dim / 2);
     // every row is stored at slot pos0 + node; the commit moves accepted rows of
     // a tree to their final positions
-    const int64_t off = kv_row_offset(p.pool, seq, pos0 + node);
-    kv_encode_row(p.pool.k + off, p.pool.format, p.k + (int64_t)r * p.ldk, p.pool.kv_dim);
-    kv_encode_row(p.pool.v + off, p.pool.format, p.v + (int64_t)r * p.ldv, p.pool.kv_dim);
+    if (unit < p.heads) {
+        norm_rope_head(p.q + (int64_t)r * p.ldq + (int64_t)unit * 2 * p.hd, p.q_norm, p.hd, p.rope_dim, cs, p.eps);
+    } else if (unit < p.heads + p.kv_heads) {
+        const int h = unit - p.heads;
+        float * k = p.k + (int64_t)r * p.ldk + (int64_t)h * p.hd;
+        norm_rope_head(k, p.k_norm, p.hd, p.rope_dim, cs, p.eps);
+        const int64_t off = kv_row_offset(p.pool, seq, p.rows.pos0[seq] + node);
+        kv_encode_head(p.pool.k + off, p.pool.format, k, h * p.hd, p.hd);
+    } else {
+        const int h = unit - p.heads - p.kv_heads;
+        const int64_t off = kv_row_offset(p.pool, seq, p.rows.pos0[seq] + node);
+        kv_encode_head(p.pool.v + off, p.pool.format, p.v + (int64_t)r * p.ldv + (int64_t)h * p.hd, h * p.hd, p.hd);
+    }
 }
 
 void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, const float * v, int ldv,
                       const float * q_norm, const float * k_norm, int heads, int kv_heads, int head_dim, int rope_dim,
-                      double rope_base, float eps, const RowMeta & rows, const KvPool & pool) {
-    PrepParams p{q, ldq, k, ldk, v, ldv, q_norm, k_norm, heads, kv_heads, head_dim, rope_dim, rope_base, eps, rows, pool};
-    launch_k(attn_prep_kernel, rows.batch * rows.nodes, 256, 0, s, p);
+                      const float2 * rope_cs, float eps, const RowMeta & rows, const KvPool & pool) {
+    YK_REQUIRE(head_dim % 32 == 0 && rope_cs, YUUKA_ERR_UNSUPPORTED, "attn_prep: head width %d is not a multiple of 32", head_dim);
+    PrepParams p{q, ldq, k, ldk, v, ldv, q_norm, k_norm, heads, kv_heads, head_dim, rope_dim, rope_cs, eps, rows, pool};
+    dim3 grid(rows.batch * rows.nodes, (heads + 2 * kv_heads + 3) / 4);
+    launch_k(attn_prep_kernel, grid, 128, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
 

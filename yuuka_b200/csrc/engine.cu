@@ -23,6 +23,7 @@ struct Tensor {
     uint64_t rows = 0, cols = 0, bytes = 0;
     bool owned = false;
     bool tiled = false;  // ptr holds the tile-ordered copy (gemm_tiled.cuh)
+    bool paired = false; // two matrices of equal shape interleaved 16 rows by 16 rows (ffn_gate | ffn_up)
     bool present() const { return ptr != nullptr; }
 };
 
@@ -159,6 +160,30 @@ Tensor fuse(yuuka_model * m, std::vector<const Tensor *> parts) {
     out.rows = rows;
     out.cols = parts[0]->cols;
     out.bytes = total;
+    return out;
+}
+
+// ffn_gate and ffn_up as one matrix, 16 rows of the first then the same 16 rows of the second: after
+// tiling, row tiles 2i and 2i+1 hold gate and up of the same 16 columns of the FFN, which lets one CTA
+// finish silu(gate) * up (forwardFFN, model/qwen35/forward.go:295-315) in its epilogue.
+Tensor fuse_paired(yuuka_model * m, const Tensor & a, const Tensor & b) {
+    Tensor out;
+    if (a.dtype != b.dtype || a.cols != b.cols || a.rows != b.rows || a.rows % 16 != 0) return out;
+    const uint64_t rb = row_bytes(a.dtype, a.cols), total = a.bytes + b.bytes;
+    void * ptr = nullptr;
+    cudaError_t err = cudaMalloc(&ptr, total + 256);
+    YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "fused weight allocation of %llu bytes failed",
+               (unsigned long long)total);
+    m->extra_allocs.push_back(ptr);
+    YK_CUDA(cudaMemcpy2D(ptr, 32 * rb, a.ptr, 16 * rb, 16 * rb, a.rows / 16, cudaMemcpyDeviceToDevice));
+    YK_CUDA(cudaMemcpy2D((uint8_t *)ptr + 16 * rb, 32 * rb, b.ptr, 16 * rb, 16 * rb, b.rows / 16, cudaMemcpyDeviceToDevice));
+    YK_CUDA(cudaMemset((uint8_t *)ptr + total, 0, 256));
+    out.ptr = (uint8_t *)ptr;
+    out.dtype = a.dtype;
+    out.rows = 2 * a.rows;
+    out.cols = a.cols;
+    out.bytes = total;
+    out.paired = true;
     return out;
 }
 
@@ -385,7 +410,8 @@ yuuka_status yuuka_model_finalize(yuuka_model * m) {
             L.ffn_gate = need(m, p + "ffn_gate.weight", c.ffn, H, false);
             L.ffn_up = need(m, p + "ffn_up.weight", c.ffn, H, false);
             L.ffn_down = need(m, p + "ffn_down.weight", H, c.ffn, false);
-            L.gate_up = fuse(m, {&L.ffn_gate, &L.ffn_up});
+            L.gate_up = fuse_paired(m, L.ffn_gate, L.ffn_up);
+            if (!L.gate_up.present()) L.gate_up = fuse(m, {&L.ffn_gate, &L.ffn_up});
             if (L.gate_up.present()) {
                 drop(m, p + "ffn_gate.weight");
                 drop(m, p + "ffn_up.weight");
@@ -505,6 +531,7 @@ struct yuuka_session {
     uint64_t * d_anc = nullptr;
     float *x = nullptr, *xn = nullptr, *qkv_attn = nullptr, *attn_out = nullptr, *gdn_out = nullptr;
     float *gate_up = nullptr, *act = nullptr, *logits = nullptr;
+    float2 * rope_cs = nullptr;  // [rows][rope_dim / 2] (cos, sin) of the step's rows, attention layers only
     // qwen35moe scratch: routing, expert-sorted (row, slot) pairs, expert and shared-expert activations
     int32_t *moe_ids = nullptr, *moe_pos = nullptr, *moe_row = nullptr;
     float * moe_logits = nullptr;  // [rows][experts] router logits
@@ -523,6 +550,7 @@ struct yuuka_session {
     // point of a step, zeroed when the step starts; norm_point indexes the row behind the current prep_xn
     bool fold_norm = false;          // the model allows it (every consumer and producer matrix is tile-ordered)
     bool fold_step = false;          // ... and this step's row count does
+    bool fold_swiglu = true;         // silu(gate) * up in the gate|up GEMM's epilogue (YUUKA_CUDA_NO_FOLD_SWIGLU=1: own kernel)
     unsigned long long * norm_sumsq = nullptr;  // [norm points][32]
     int norm_point = 0;
     bool xn_raw = false;             // prep_xn holds x * w * pre of norm_point (not normalised rows)
@@ -573,7 +601,8 @@ void mark(yuuka_session * s, uint32_t code) {
 }
 
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOut prep, float * out, int ldo, int rows,
-          uint32_t flags, const GemmPostNorm * post = nullptr, const float * produce_norm_w = nullptr) {
+          uint32_t flags, const GemmPostNorm * post = nullptr, const float * produce_norm_w = nullptr,
+          const XPrepOut * swiglu = nullptr) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     if (w.tiled) {
         TiledGemmArgs t;
@@ -592,6 +621,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.flags = flags;
         t.scratch = &s->gemm;
         if (post) t.post = *post;
+        if (swiglu) t.swiglu = *swiglu;
         if (s->fold_step) {
             const yuuka_model_config & mc = s->model->cfg;
             t.norm.eps = mc.rms_eps;
@@ -702,6 +732,10 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     mark(s, YUUKA_OP_EMBEDDING);
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
+    if (s->rope_cs) {
+        launch_rope_table(st, s->rope_cs, rows, c.rope_dim, c.rope_freq_base);
+        s->launches++;
+    }
     // the first layer's input norm is a kernel of its own; with 3..32 rows every later norm is folded into
     // the GEMM that finishes the residual rows and the GEMM that reads them
     s->fold_step = s->fold_norm && R >= 3 && R <= 32;
@@ -781,7 +815,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             pool.table_stride = s->table_stride;
             mark(s, YUUKA_OP_ATTN_PREP);
             launch_attn_prep(st, qb, nq, kb, nq, vb, nq, L.q_norm, L.k_norm, c.heads, c.kv_heads, c.head_dim, c.rope_dim,
-                             c.rope_freq_base, c.rms_eps, rows, pool);
+                             s->rope_cs, c.rms_eps, rows, pool);
             s->launches++;
             AttnScratch sc;
             const int G = c.heads / c.kv_heads;
@@ -868,15 +902,21 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             continue;
         }
         // forwardFFN (model/qwen35/forward.go:295-315); its input norm came with the mixer's output GEMM
-        if (L.gate_up.present()) {
-            gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
+        if (L.gate_up.present() && L.gate_up.paired && L.gate_up.tiled && L.ffn_down.tiled && s->fold_swiglu && R >= 3 && R <= 32) {
+            // silu(gate) * up leaves the GEMM's epilogue in the form the down projection reads
+            gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0, nullptr, nullptr, &s->prep_act);
         } else {
-            gemm(s, L.ffn_gate, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
-            gemm(s, L.ffn_up, s->xn, H, s->prep_xn, s->gate_up + F, 2 * F, R, 0);
+            const bool paired = L.gate_up.present() && L.gate_up.paired;
+            if (L.gate_up.present()) {
+                gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
+            } else {
+                gemm(s, L.ffn_gate, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0);
+                gemm(s, L.ffn_up, s->xn, H, s->prep_xn, s->gate_up + F, 2 * F, R, 0);
+            }
+            mark(s, YUUKA_OP_SILU_MUL);
+            launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + (paired ? 16 : F), 2 * F, F, R, s->prep_act, paired ? 32 : 16);
+            s->launches++;
         }
-        mark(s, YUUKA_OP_SILU_MUL);
-        launch_silu_mul(st, s->act, F, s->gate_up, s->gate_up + F, 2 * F, F, R, s->prep_act);
-        s->launches++;
         gemm_residual_norm(s, L.ffn_down, s->act, F, s->prep_act, R, next_norm);
     }
     // tail: final norm + LM head over the wanted rows (forward.go:147-151)
@@ -1073,6 +1113,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 s->fold_norm = ok;
                 if (ok) s->norm_sumsq = dalloc<unsigned long long>((size_t)32 * (2 * c.block_count + 2), s->owned);
             }
+            if (const char * e = getenv("YUUKA_CUDA_NO_FOLD_SWIGLU")) s->fold_swiglu = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_NO_PREFETCH")) s->prefetch_next = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_PREFETCH_MB")) s->prefetch_bytes = (uint64_t)atoi(e) << 20;
             for (const LayerW & L : model->layers) {
@@ -1146,6 +1187,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->gdn_counters = dalloc<int>((size_t)B * rank, s->owned);
             s->post_counter = dalloc<int>(4, s->owned);
             s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
+            if (c.rope_dim > 0) s->rope_cs = dalloc<float2>((size_t)R * (c.rope_dim / 2), s->owned);
             s->act = dalloc<float>((size_t)R * c.ffn, s->owned);
             auto prep_alloc = [&](int width) {
                 XPrepOut o;

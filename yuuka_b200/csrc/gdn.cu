@@ -103,9 +103,10 @@ __global__ void gdn_front_kernel(const ScanParams p) {
 // ---------------------------------------------------------------------------
 // Recurrence (recurrent.go:56-105) + gated RMSNorm (recurrent.go:39-50).
 // grid (S/32 column blocks, rank, batch), 4 warps: warp w holds state rows
-// [w*S/4, (w+1)*S/4) of 32 columns in registers. The last column block of a
-// head to finish applies the gated norm to the head's outputs and emits them as
-// f32 and in the prepared form the out-projection GEMM reads.
+// [w*S/4, (w+1)*S/4) of 32 columns in registers. The column blocks of a head are
+// one thread-block cluster: they exchange their sums of squares through
+// distributed shared memory, and each applies the gated norm to its own columns
+// and emits them as f32 and in the prepared form the out-projection GEMM reads.
 template <int S>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
     pdl_entry();
@@ -128,9 +129,9 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     float * red = bet + N;                // [GDN_WARPS][GDN_COLS]
     float * red2 = red + GDN_WARPS * GDN_COLS;
     int * par = reinterpret_cast<int *>(red2 + GDN_WARPS * GDN_COLS);  // [N]
-    __shared__ int last_flag;
-    __shared__ double nred[8 * GDN_WARPS];
-    __shared__ float gbuf[8 * S];  // gated outputs of a chunk of rows
+    float * o_s = reinterpret_cast<float *>(par + N);                   // [N][GDN_COLS] outputs of this column block
+    __shared__ double ssq[GDN_MAX_NODES];   // per row: sum of squares over this block's columns (read by the cluster)
+    __shared__ float scale_s[GDN_MAX_NODES];
 
     // stored state first: it does not depend on this step
     const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + warp * RPW) * S + col;
@@ -175,21 +176,24 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         const float * qx = qn + node * S + warp * RPW;
         const float dc = dec[node];
         // sk = (decay * S)^T k
-        float sk = 0.0f;
+        // (four running sums: the 32-term chain of dependent FMAs was the longest wait of a row)
+        float sk4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < RPW; i++) sk = fmaf(st[i] * dc, kx[i], sk);
+        for (int i = 0; i < RPW; i++) sk4[i & 3] = fmaf(st[i] * dc, kx[i], sk4[i & 3]);
+        float sk = (sk4[0] + sk4[1]) + (sk4[2] + sk4[3]);
         red[warp * GDN_COLS + lane] = sk;
         __syncthreads();
         sk = 0.0f;
 #pragma unroll
         for (int w = 0; w < GDN_WARPS; w++) sk += red[w * GDN_COLS + lane];
         const float d = (vv[node * GDN_COLS + lane] - sk) * bet[node];
-        float o = 0.0f;
+        float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int i = 0; i < RPW; i++) {
             st[i] = state_update(st[i], dc, kx[i], d);
-            o = fmaf(st[i], qx[i], o);
+            o4[i & 3] = fmaf(st[i], qx[i], o4[i & 3]);
         }
+        float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
         red2[warp * GDN_COLS + lane] = o;
         if (warp == 0) dd[node * GDN_COLS + lane] = d;
         __syncthreads();
@@ -198,68 +202,51 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
             o = 0.0f;
 #pragma unroll
             for (int w = 0; w < GDN_WARPS; w++) o += red2[w * GDN_COLS + lane];
-            __stcg(a.out + (int64_t)(seq * N + node) * inner + h * S + col, o);
+            o_s[node * GDN_COLS + lane] = o;
             a.dlog[(int64_t)(seq * N + node) * inner + h * S + col] = d;
         }
         cur = node;
     }
 
-    // ---- gated RMSNorm of the head, by the last column block to arrive ----
-    __threadfence();
+    // ---- gated RMSNorm of the head (recurrent.go:39-50) ----
+    // The S / 32 column blocks of a head form one thread-block cluster: each adds up the squares of its own
+    // columns, reads the others' sums through distributed shared memory, and finishes its own columns.
     __syncthreads();
-    if (threadIdx.x == 0) last_flag = atomicAdd(&a.counters[seq * a.rank + h], 1) == (int)gridDim.x - 1;
-    __syncthreads();
-    if (!last_flag) return;
-    __threadfence();
-    // eight rows at a time so that the loads of a chunk are all in flight together
-    constexpr int NB = 8;
-    for (int n0 = 0; n0 < N; n0 += NB) {
-        const int nb = min(NB, N - n0);
-        const int j = threadIdx.x;
-        float v[NB], zz[NB];
+    for (int node = warp; node < N; node += GDN_WARPS) {
+        const double v = (double)o_s[node * GDN_COLS + lane];
+        double sq = v * v;
 #pragma unroll
-        for (int b = 0; b < NB; b++) {
-            const int64_t r = seq * N + n0 + b;
-            const bool live = b < nb && j < S;
-            v[b] = live ? __ldcg(a.out + r * inner + h * S + j) : 0.0f;
-            zz[b] = live ? a.z[r * a.ldz + h * S + j] : 0.0f;
-        }
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-            double sq = (double)v[b] * (double)v[b];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (lane == 0) nred[b * GDN_WARPS + warp] = sq;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-            double tot = 0;
-            for (int w = 0; w < GDN_WARPS; w++) tot += nred[b * GDN_WARPS + w];
-            const float mean = (float)(tot / (double)S);
-            const float scale = (float)(1.0 / sqrt((double)(mean + a.eps)));
-            if (b < nb && j < S) {
-                float t = v[b];
-                t *= scale * a.norm[j];
-                gbuf[b * S + j] = t * silu_ref(zz[b]);
-            }
-        }
-        __syncthreads();
-        for (int gi = threadIdx.x; gi < nb * (S >> 4); gi += blockDim.x) {
-            const int b = gi / (S >> 4), part = gi - b * (S >> 4);
-            const int64_t r = seq * N + n0 + b;
-            float g16[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) g16[i] = gbuf[b * S + part * 16 + i];
-            float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + h * S + part * 16);
-#pragma unroll
-            for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
-            if (a.prep.xh)
-                xprep_store16(a.prep.xh + r * inner + h * S + part * 16, a.prep.xs16 + r * (inner >> 4) + ((h * S) >> 4) + part, g16);
-        }
-        __syncthreads();
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) ssq[node] = sq;
     }
-    if (threadIdx.x == 0) a.counters[seq * a.rank + h] = 0;
+    cluster_sync_all();
+    for (int node = threadIdx.x; node < N; node += blockDim.x) {
+        double tot = 0;
+        for (unsigned r = 0; r < gridDim.x; r++) tot += ld_cluster_f64(ssq + node, r);  // the cluster spans gridDim.x
+        const float mean = (float)(tot / (double)S);
+        scale_s[node] = (float)(1.0 / sqrt((double)(mean + a.eps)));
+    }
+    cluster_sync_all();  // scales visible to the CTA; no CTA leaves while another may still read its sums
+    for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
+        const int node = i / GDN_COLS, c = i - node * GDN_COLS;
+        const int64_t r = seq * N + node;
+        float t = o_s[i];
+        t *= scale_s[node] * a.norm[cb * GDN_COLS + c];
+        o_s[i] = t * silu_ref(a.z[r * a.ldz + h * S + cb * GDN_COLS + c]);
+    }
+    __syncthreads();
+    for (int gi = threadIdx.x; gi < N * (GDN_COLS >> 4); gi += blockDim.x) {
+        const int node = gi / (GDN_COLS >> 4), part = gi - node * (GDN_COLS >> 4);
+        const int64_t r = seq * N + node;
+        const int c0 = h * S + cb * GDN_COLS + part * 16;
+        float g16[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) g16[i] = o_s[node * GDN_COLS + part * 16 + i];
+        float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + c0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
+        if (a.prep.xh) xprep_store16(a.prep.xh + r * inner + c0, a.prep.xs16 + r * (inner >> 4) + (c0 >> 4), g16);
+    }
 }
 
 void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
@@ -271,14 +258,14 @@ void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
-    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 2 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS + N);
+    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS + N);
     dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_k(gdn_scan_kernel<128>, grid, GDN_WARPS * 32, smem, s, p);
+        launch_k_cluster(gdn_scan_kernel<128>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
     } else {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_k(gdn_scan_kernel<64>, grid, GDN_WARPS * 32, smem, s, p);
+        launch_k_cluster(gdn_scan_kernel<64>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
     }
     YK_CUDA(cudaGetLastError());
 }

@@ -631,6 +631,11 @@ struct TParams {
     const unsigned long long * cs_prev;  // (null: pre = 1)
     float nf_eps;
     int nf_cols;                         // row width the sums of squares run over
+    // optional (FOLD kernels): the matrix holds ffn_gate and ffn_up interleaved by row tile (tile 2i: gate
+    // rows 16i.., tile 2i+1: up rows 16i..). Instead of `out` the launch writes silu(gate) * up
+    // (forwardFFN, model/qwen35/forward.go:295-315) in prepared form, [M][N / 2].
+    __half * sw_xh;
+    __half2 * sw_xs16;
     // optional: the matrix the next GEMM of the step will stream; its first bytes are asked into L2
     // while this kernel drains and the small kernels in between run
     const uint8_t * next_w;
@@ -647,6 +652,8 @@ __device__ __forceinline__ float nf_scale(unsigned long long sumsq, int cols, fl
     return rsqrtf(mean + eps);
 }
 __device__ __forceinline__ unsigned long long nf_fixed(float v) { return (unsigned long long)(v * 16777216.0f); }
+// silu(g) * u with the expression of silu_mul_kernel (elementwise.cu), so both forms give the same bits
+__device__ __forceinline__ float swiglu(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
 // rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
 // one warp per row, emitting f32 and the prepared form.
@@ -896,7 +903,45 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             }
         }
         // ---- epilogue ----
-        if (kpart == 0 && rt < n_tiles) {
+        const bool sw_direct = FOLD && p.sw_xh != nullptr && p.kchunks == 1;
+        if (sw_direct) {
+            // the up tile's warp hands its sums to the gate tile's warp (KS warps earlier) through its own slot of red
+            const bool is_up = (tile_in_group & 1) != 0;
+            if (kpart == 0 && is_up) {
+                float * mine = red + warp * (NT * 128);
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) mine[(j * 4 + c) * 32 + lane] = acc[j][c];
+            }
+            __syncthreads();
+            if (kpart == 0 && !is_up && rt < n_tiles) {
+                const float * upv = red + (warp + p.KS) * (NT * 128);
+                const int half_n = p.N >> 1, col0 = (rt >> 1) * 16;
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int tok = 8 * j + 2 * t + e;
+                        const bool tok_ok = tok < Mrows;
+                        const float cs = cs_s[tok & 31];
+                        const __half q_g = __float2half_rn(swiglu(acc[j][e] * cs, upv[(j * 4 + e) * 32 + lane] * cs));
+                        const __half q_h = __float2half_rn(swiglu(acc[j][2 + e] * cs, upv[(j * 4 + 2 + e) * 32 + lane] * cs));
+                        float gs = __half2float(q_g) + __half2float(q_h);
+#pragma unroll
+                        for (int o = 4; o < 32; o <<= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                        if (tok_ok) {
+                            p.sw_xh[(size_t)tok * half_n + col0 + g] = q_g;
+                            p.sw_xh[(size_t)tok * half_n + col0 + g + 8] = q_h;
+                            if (g == 0) {
+                                const __half hi = __float2half_rn(gs);
+                                p.sw_xs16[(size_t)tok * (half_n >> 4) + (rt >> 1)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+                            }
+                        }
+                    }
+            }
+            if (p.KS == 1) __syncthreads();  // (with KS > 1 the barrier at the end of the group covers red)
+        } else if (kpart == 0 && rt < n_tiles) {
             const int n_g = rt * 16 + g, n_h = n_g + 8;
             float * base = p.kchunks == 1 ? outp : p.partial + (size_t)blockIdx.y * Mrows * p.N;
             const int64_t ld = p.kchunks == 1 ? p.ldo : p.N;
@@ -957,6 +1002,35 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                 const int row0 = grp * p.TG * 16, nrows = min(p.TG * 16, p.N - row0);
                 // (with the norm folded in, N is a multiple of 16: a half warp holds one 16-column group of a row)
                 const int padded = (FOLD && p.nf_w) ? ((Mrows * nrows + 31) & ~31) : Mrows * nrows;
+                if (FOLD && p.sw_xh) {
+                    // gate and up columns of the group, 16 by 16 (nrows is a multiple of 32: row tiles come in pairs)
+                    const int half_rows = nrows >> 1, half_n = p.N >> 1, live_n = Mrows * half_rows;
+                    for (int i = threadIdx.x; i < ((live_n + 31) & ~31); i += TW * 32) {
+                        const bool live = i < live_n;
+                        const int tok = live ? i / half_rows : 0, cl = live ? i - tok * half_rows : 0;
+                        const int n = row0 + (cl >> 4) * 32 + (cl & 15);
+                        float gsum = 0.0f, usum = 0.0f;
+                        if (live)
+                            for (int q = 0; q < p.kchunks; q++) {
+                                const float * src = p.partial + ((size_t)q * Mrows + tok) * p.N + n;
+                                gsum += __ldcg(src);
+                                usum += __ldcg(src + 16);
+                            }
+                        const float cs = cs_s[tok & 31];
+                        const __half qv = __float2half_rn(live ? swiglu(gsum * cs, usum * cs) : 0.0f);
+                        float gs = __half2float(qv);
+#pragma unroll
+                        for (int o = 1; o < 16; o <<= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                        if (live) {
+                            const int col = (row0 >> 1) + cl;
+                            p.sw_xh[(size_t)tok * half_n + col] = qv;
+                            if ((lane & 15) == 0) {
+                                const __half hi = __float2half_rn(gs);
+                                p.sw_xs16[(size_t)tok * (half_n >> 4) + (col >> 4)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+                            }
+                        }
+                    }
+                } else
                 for (int i = threadIdx.x; i < padded; i += TW * 32) {
                     const bool live = i < Mrows * nrows;
                     const int tok = live ? i / nrows : 0, n = row0 + (live ? i - tok * nrows : 0);
@@ -1185,40 +1259,50 @@ static int tab_of(uint32_t dtype) {
     }
 }
 
-static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int nt, int ks) {
+static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int nt, int ks, bool paired = false) {
     size_t x = (size_t)m * (nsb_chunk * 512 + 64);
     size_t xsum = (((size_t)m * (nsb_chunk * 64 + 16) + 127) / 128) * 128;
-    size_t red = ks > 1 ? (size_t)TW * nt * 128 * 4 : 0;
+    size_t red = (ks > 1 || paired) ? (size_t)TW * nt * 128 * 4 : 0;
     return x + xsum + (size_t)TW * tab_of(dtype) + red;
 }
 
-static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_out, int n_in, TPlan & pl) {
+// paired: row tiles 2i and 2i+1 must share a CTA (SwiGLU epilogue): at most TW / 2 warps per row tile,
+// and room in shared memory for the exchange between the two.
+static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_out, int n_in, TPlan & pl, bool paired = false) {
     const int nsb = n_in / 256, n_tiles = (n_out + 15) / 16;
     const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
     const int slots = 2 * dev->sm_count;  // CTAs that can be resident (two per SM)
     // warps per row tile: as many K parts as needed to give every resident CTA a group
     int ks = 1;
-    while (ks < TW && (n_tiles * ks) / TW < slots * 4 / 5 && nsb / (2 * ks) >= 1) ks *= 2;
+    while (ks < (paired ? TW / 2 : TW) && (n_tiles * ks) / TW < slots * 4 / 5 && nsb / (2 * ks) >= 1) ks *= 2;
+    // YUUKA_GEMM_PLAN=ks,kchunks overrides both choices (experiments; kchunks still grows until shared memory fits)
+    static const int forced_ks = [] { const char * e = getenv("YUUKA_GEMM_PLAN"); return e ? atoi(e) : 0; }();
+    static const int forced_kc = [] {
+        const char * e = getenv("YUUKA_GEMM_PLAN");
+        const char * c = e ? strchr(e, ',') : nullptr;
+        return c ? atoi(c + 1) : 0;
+    }();
+    if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || (forced_ks == 8 && !paired)) ks = forced_ks;
     pl.KS = ks;
     pl.TG = TW / ks;
     pl.n_groups = (n_tiles + pl.TG - 1) / pl.TG;
     // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
-    int kchunks = 1;
+    int kchunks = forced_kc > 0 ? forced_kc : 1;
     const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
     static const bool full_smem = [] { const char * e = getenv("YUUKA_GEMM_FULL_SMEM"); return e && e[0] == '1'; }();
     const size_t budget = full_smem ? dev->prop.sharedMemPerBlockOptin - 1024
                                     : (half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin);
     while (true) {
         int nsb_chunk = (nsb + kchunks - 1) / kchunks;
-        bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks) <= budget;
-        bool enough = pl.n_groups * kchunks >= slots / 2 || nsb_chunk < 2 * ks || nsb_chunk <= 2;
+        bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks, paired) <= budget;
+        bool enough = forced_kc > 0 || pl.n_groups * kchunks >= slots / 2 || nsb_chunk < 2 * ks || nsb_chunk <= 2;
         if (fits && enough) break;
         if (nsb_chunk == 1) break;
         kchunks++;
     }
     pl.nsb_chunk = (nsb + kchunks - 1) / kchunks;
     pl.kchunks = (nsb + pl.nsb_chunk - 1) / pl.nsb_chunk;
-    pl.smem = mma_smem(dtype, m, pl.nsb_chunk, nt, ks);
+    pl.smem = mma_smem(dtype, m, pl.nsb_chunk, nt, ks, paired);
     int per = slots / pl.kchunks;
     if (per < 1) per = 1;
     pl.grid_x = pl.n_groups < per ? pl.n_groups : per;
@@ -1275,12 +1359,14 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     }
     for (int m : {rows < 32 ? rows : 32, 32 < rows ? rows % 32 : 0}) {
         if (m <= 0) continue;
-        TPlan pl;
-        plan_tiled(dev, w_dtype, m, n_out, n_in, pl);
-        if (pl.kchunks > 1) {
-            uint64_t need = (uint64_t)pl.kchunks * m * n_out;
-            if (need > *partial_floats) *partial_floats = need;
-            if (pl.n_groups > *counters) *counters = pl.n_groups;
+        for (bool paired : {false, true}) {
+            TPlan pl;
+            plan_tiled(dev, w_dtype, m, n_out, n_in, pl, paired);
+            if (pl.kchunks > 1) {
+                uint64_t need = (uint64_t)pl.kchunks * m * n_out;
+                if (need > *partial_floats) *partial_floats = need;
+                if (pl.n_groups > *counters) *counters = pl.n_groups;
+            }
         }
     }
 }
@@ -1288,7 +1374,7 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
 template <int DT, int NT>
 static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
                             const TPlan & pl) {
-    const bool fold = a.norm.produce_w || a.norm.consume_now;
+    const bool fold = a.norm.produce_w || a.norm.consume_now || a.swiglu.xh;
     auto kern = fold ? gemm_tiled_mma_kernel<DT, NT, false, true> : gemm_tiled_mma_kernel<DT, NT, false, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
@@ -1317,6 +1403,12 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
         p.nf_xs16 = a.norm.produce_prep.xs16;
         p.cs_now = a.norm.consume_now;
         p.cs_prev = a.norm.consume_prev;
+        p.nf_eps = a.norm.eps;
+        p.nf_cols = a.norm.cols;
+    }
+    if (a.swiglu.xh) {
+        p.sw_xh = a.swiglu.xh + (int64_t)m0 * (a.n_out / 2);
+        p.sw_xs16 = a.swiglu.xs16 + (int64_t)m0 * (a.n_out / 32);
         p.nf_eps = a.norm.eps;
         p.nf_cols = a.norm.cols;
     }
@@ -1512,7 +1604,7 @@ static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGe
     for (int m0 = 0; m0 < a.rows; m0 += 32) {
         const int m = a.rows - m0 < 32 ? a.rows - m0 : 32;
         TPlan pl;
-        plan_tiled(dev, a.w_dtype, m, a.n_out, a.n_in, pl);
+        plan_tiled(dev, a.w_dtype, m, a.n_out, a.n_in, pl, a.swiglu.xh != nullptr);
         YK_REQUIRE(pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
                    "gemm: activations of %d rows x %d columns do not fit shared memory", m, a.n_in);
         if (pl.kchunks > 1)
@@ -1569,13 +1661,18 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
     YK_REQUIRE(!a.post.norm_w || (a.post.dst && a.post.counter && a.n_out % 16 == 0 && a.ldo % 4 == 0 && a.post.ld % 4 == 0),
                YUUKA_ERR_INVALID_ARGUMENT, "gemm: the fused RMSNorm needs a destination, a counter and a width that is a multiple of 16");
     YK_REQUIRE(a.rows > 0 && a.n_out > 0 && a.n_in > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: invalid shape");
-    if (a.norm.produce_w || a.norm.consume_now) {
+    if (a.swiglu.xh) {
+        YK_REQUIRE(a.swiglu.xs16 && a.n_out % 32 == 0 && !(a.flags & YUUKA_GEMM_ACCUMULATE) && !a.post.norm_w && !a.norm.produce_w,
+                   YUUKA_ERR_INVALID_ARGUMENT, "gemm: the SwiGLU epilogue needs gate and up tiles in pairs and a plain output");
+        YK_REQUIRE(!a.norm.consume_now || a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
+    }
+    if (a.norm.produce_w || a.norm.consume_now || a.swiglu.xh) {
         const uint32_t route = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
         YK_REQUIRE(route == YUUKA_GEMM_PATH_MMA && a.rows <= 32 && (a.rows < UMMA_MIN_ROWS || !umma_enabled()),
-                   YUUKA_ERR_INTERNAL, "gemm: the folded RMSNorm runs on the register-fed mma route only (3..32 rows)");
+                   YUUKA_ERR_INTERNAL, "gemm: folded epilogues (RMSNorm, SwiGLU) run on the register-fed mma route only (3..32 rows)");
         YK_REQUIRE(!a.norm.produce_w || (a.n_out % 16 == 0 && a.norm.produce_sumsq && a.norm.produce_prep.xh && a.norm.produce_prep.xs16),
                    YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs a width that is a multiple of 16 and its outputs");
-        YK_REQUIRE(a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
+        YK_REQUIRE(a.swiglu.xh || a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
     }
     YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u / width %d has no tiled layout",
                a.w_dtype, a.n_in);

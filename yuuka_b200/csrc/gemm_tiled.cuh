@@ -103,6 +103,9 @@ struct TiledGemmArgs {
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     GemmPostNorm post;
     NormFuse norm;
+    // Set: `w` holds ffn_gate and ffn_up interleaved by 16-row tile and the launch writes silu(gate) * up in
+    // prepared form, [rows][n_out / 2], instead of `out` (register-fed mma route, 3..32 rows).
+    XPrepOut swiglu;
     const uint8_t * next_w = nullptr;  // optional L2 prefetch hint: the next matrix to be streamed (mma route)
     uint64_t next_bytes = 0;
 };

@@ -35,14 +35,17 @@ void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table,
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight,
                     int cols, int rows, float eps, XPrepOut prep = XPrepOut(),
                     unsigned long long * sumsq_out = nullptr);
-// act[r][i] = silu(gate[r][i]) * up[r][i] (forward.go:307-309)
+// act[r][i] = silu(gate[r][i]) * up[r][i] (forward.go:307-309). gstride: distance between consecutive
+// 16-column groups of gate (and of up); 32 when the two alternate 16 columns at a time in one row.
 void launch_silu_mul(cudaStream_t s, float * act, int lda, const float * gate, const float * up, int ld, int cols,
-                     int rows, XPrepOut prep = XPrepOut());
+                     int rows, XPrepOut prep = XPrepOut(), int gstride = 16);
 // Per-head RMSNorm of q and k, RoPE at pos0 + depth, and the paged KV write of
 // every row at slot pos0 + node (forward.go:172-186, kv_pool.go:117-134).
+// rope_cs: (cos, sin) of each row's angles, [rows][rope_dim / 2], written once per step by launch_rope_table.
 void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, const float * v, int ldv,
                       const float * q_norm, const float * k_norm, int heads, int kv_heads, int head_dim,
-                      int rope_dim, double rope_base, float eps, const RowMeta & rows, const KvPool & pool);
+                      int rope_dim, const float2 * rope_cs, float eps, const RowMeta & rows, const KvPool & pool);
+void launch_rope_table(cudaStream_t s, float2 * cs, const RowMeta & rows, int rope_dim, double rope_base);
 // Paged attention of every row over the committed positions and the row's own
 // ancestors, split over key ranges, then merged and gated (forward.go:188-220).
 struct AttnScratch {
