@@ -209,6 +209,45 @@ YUUKA_API yuuka_status yuuka_model_set_tensor(yuuka_model * model, const char * 
 YUUKA_API yuuka_status yuuka_model_finalize(yuuka_model * model);
 YUUKA_API uint64_t yuuka_model_weight_bytes(const yuuka_model * model);
 
+/* ---- GGUF files (gguf/reader.go, gguf/metadata.go) ----
+ * A reader maps the file (and the other shards of a split model, named
+ * name-NNNNN-of-NNNNN.gguf) read-only and validates magic, version 2..3,
+ * metadata, the tensor directory, general.alignment, offsets, byte ranges and
+ * overlaps before anything is exposed (reader.go:248-393, 547-704). Malformed
+ * files give YUUKA_ERR_INVALID_ARGUMENT, unknown versions and tensor types
+ * YUUKA_ERR_UNSUPPORTED; the message names file and field. Pointers handed out
+ * stay valid until yuuka_gguf_close. */
+typedef struct yuuka_gguf yuuka_gguf;
+typedef struct yuuka_gguf_tensor {
+    const char * name;
+    uint32_t dtype;      /* GGML type id, the same numbers as yuuka_dtype */
+    uint32_t rank;
+    uint64_t dims[8];    /* GGML order: dims[0] is the contiguous row width (Tensor.Columns, reader.go:62-67) */
+    uint64_t bytes;
+    const void * data;   /* read-only mapping (Tensor.Data, reader.go:89-100) */
+} yuuka_gguf_tensor;
+YUUKA_API yuuka_status yuuka_gguf_open(const char * path, yuuka_gguf ** out);
+YUUKA_API void yuuka_gguf_close(yuuka_gguf * g);
+YUUKA_API uint32_t yuuka_gguf_version(const yuuka_gguf * g);
+YUUKA_API uint64_t yuuka_gguf_alignment(const yuuka_gguf * g);
+YUUKA_API uint64_t yuuka_gguf_tensor_count(const yuuka_gguf * g);
+YUUKA_API uint64_t yuuka_gguf_metadata_count(const yuuka_gguf * g);
+/* Tensors in directory order, shard after shard (Reader.Tensors), or by name (Reader.Tensor). */
+YUUKA_API yuuka_status yuuka_gguf_tensor_at(const yuuka_gguf * g, uint64_t index, yuuka_gguf_tensor * out);
+YUUKA_API yuuka_status yuuka_gguf_tensor_find(const yuuka_gguf * g, const char * name, yuuka_gguf_tensor * out);
+/* Reader.Int / Float / String (reader.go:741-782) with the conversions of Value.AsInt / AsFloat /
+ * AsString (metadata.go:87-128); a missing key or a value of another kind is YUUKA_ERR_INVALID_ARGUMENT. */
+YUUKA_API yuuka_status yuuka_gguf_meta_int(const yuuka_gguf * g, const char * key, int64_t * out);
+YUUKA_API yuuka_status yuuka_gguf_meta_float(const yuuka_gguf * g, const char * key, double * out);
+YUUKA_API yuuka_status yuuka_gguf_meta_string(const yuuka_gguf * g, const char * key, const char ** out, uint64_t * len);
+YUUKA_API yuuka_status yuuka_gguf_meta_array_len(const yuuka_gguf * g, const char * key, uint64_t * out);
+/* LoadConfig (model/qwen35/config.go:48-174): general.architecture qwen35 or qwen35moe, the
+ * <arch>.* hyperparameters, vocabulary size from tokenizer.ggml.tokens or <arch>.vocab_size. */
+YUUKA_API yuuka_status yuuka_gguf_model_config(const yuuka_gguf * g, yuuka_model_config * out);
+/* Opens the file, creates the model from its metadata, uploads every tensor verbatim and finalizes
+ * (engine/gpu/model.go:288-301 over model/qwen35/load.go:80-215). */
+YUUKA_API yuuka_status yuuka_model_load_gguf(yuuka_device * dev, const char * path, yuuka_model ** out);
+
 /* A session owns a paged KV pool, per-sequence block tables, positions and
  * recurrent state for max_batch sequences (engine/gpu/session.go:58-182 holds
  * one; serving needs many), plus the activations of one verify step of up to

@@ -120,7 +120,9 @@ const Tensor & need(const yuuka_model * m, const std::string & name, uint64_t ro
     auto it = m->tensors.find(name);
     YK_REQUIRE(it != m->tensors.end(), YUUKA_ERR_INVALID_ARGUMENT, "missing required tensor \"%s\"", name.c_str());
     const Tensor & t = it->second;
-    YK_REQUIRE(t.rows == rows && t.cols == cols, YUUKA_ERR_INVALID_ARGUMENT,
+    // F32 vectors are taken by element count (ssm_conv1d arrives as [kernel, channels]; model/qwen35/load.go:302-321
+    // reads it by byte count)
+    YK_REQUIRE(f32_vector ? t.rows * t.cols == rows * cols : (t.rows == rows && t.cols == cols), YUUKA_ERR_INVALID_ARGUMENT,
                "tensor \"%s\" has shape [%llu,%llu], want [%llu,%llu]", name.c_str(), (unsigned long long)t.cols,
                (unsigned long long)t.rows, (unsigned long long)cols, (unsigned long long)rows);
     if (f32_vector)

@@ -1272,9 +1272,17 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     const int nsb = n_in / 256, n_tiles = (n_out + 15) / 16;
     const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
     const int slots = 2 * dev->sm_count;  // CTAs that can be resident (two per SM)
-    // warps per row tile: as many K parts as needed to give every resident CTA a group
+    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
+    static const bool full_smem = [] { const char * e = getenv("YUUKA_GEMM_FULL_SMEM"); return e && e[0] == '1'; }();
+    const size_t budget = full_smem ? dev->prop.sharedMemPerBlockOptin - 1024
+                                    : (half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin);
+    // K chunks across CTAs that shared memory forces anyway (the activations of all rows must fit two CTAs per SM)
+    int kc_fit = 1;
+    while ((nsb + kc_fit - 1) / kc_fit > 1 && mma_smem(dtype, m, (nsb + kc_fit - 1) / kc_fit, nt, 2, paired) > budget) kc_fit++;
+    // warps per row tile: as many K parts as needed to give every resident CTA a (group, chunk). Measured on
+    // 2560 x 9216 Q6_K at 9 rows, where three chunks are forced: four warps per tile 27.7 us, eight 29.9 us.
     int ks = 1;
-    while (ks < (paired ? TW / 2 : TW) && (n_tiles * ks) / TW < slots * 4 / 5 && nsb / (2 * ks) >= 1) ks *= 2;
+    while (ks < (paired ? TW / 2 : TW) && (n_tiles * ks) / TW * kc_fit < slots * 4 / 5 && nsb / (2 * ks) >= 1) ks *= 2;
     // YUUKA_GEMM_PLAN=ks,kchunks overrides both choices (experiments; kchunks still grows until shared memory fits)
     static const int forced_ks = [] { const char * e = getenv("YUUKA_GEMM_PLAN"); return e ? atoi(e) : 0; }();
     static const int forced_kc = [] {
@@ -1288,10 +1296,6 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     pl.n_groups = (n_tiles + pl.TG - 1) / pl.TG;
     // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
     int kchunks = forced_kc > 0 ? forced_kc : 1;
-    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
-    static const bool full_smem = [] { const char * e = getenv("YUUKA_GEMM_FULL_SMEM"); return e && e[0] == '1'; }();
-    const size_t budget = full_smem ? dev->prop.sharedMemPerBlockOptin - 1024
-                                    : (half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin);
     while (true) {
         int nsb_chunk = (nsb + kchunks - 1) / kchunks;
         bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks, paired) <= budget;

@@ -56,6 +56,11 @@ class ModelConfig(C.Structure):
     ]
 
 
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("rank", C.c_uint32), ("dims", C.c_uint64 * 8),
+                ("bytes", C.c_uint64), ("data", C.c_void_p)]
+
+
 class SessionConfig(C.Structure):
     _fields_ = [("max_batch", C.c_int32), ("max_nodes", C.c_int32), ("capacity", C.c_int32),
                 ("block_size", C.c_int32), ("pool_blocks", C.c_int32), ("kv_format", C.c_int32),
@@ -137,6 +142,20 @@ SIGNATURES = {
     "yuuka_model_set_tensor": (_i32, [_vp, C.c_char_p, _u32, _vp, _u64, _u64]),
     "yuuka_model_finalize": (_i32, [_vp]),
     "yuuka_model_weight_bytes": (_u64, [_vp]),
+    "yuuka_gguf_open": (_i32, [C.c_char_p, _vp]),
+    "yuuka_gguf_close": (None, [_vp]),
+    "yuuka_gguf_version": (_u32, [_vp]),
+    "yuuka_gguf_alignment": (_u64, [_vp]),
+    "yuuka_gguf_tensor_count": (_u64, [_vp]),
+    "yuuka_gguf_metadata_count": (_u64, [_vp]),
+    "yuuka_gguf_tensor_at": (_i32, [_vp, _u64, _vp]),
+    "yuuka_gguf_tensor_find": (_i32, [_vp, C.c_char_p, _vp]),
+    "yuuka_gguf_meta_int": (_i32, [_vp, C.c_char_p, _vp]),
+    "yuuka_gguf_meta_float": (_i32, [_vp, C.c_char_p, _vp]),
+    "yuuka_gguf_meta_string": (_i32, [_vp, C.c_char_p, _vp, _vp]),
+    "yuuka_gguf_meta_array_len": (_i32, [_vp, C.c_char_p, _vp]),
+    "yuuka_gguf_model_config": (_i32, [_vp, _vp]),
+    "yuuka_model_load_gguf": (_i32, [_vp, C.c_char_p, _vp]),
     "yuuka_session_create": (_i32, [_vp, _vp, _vp]),
     "yuuka_session_destroy": (None, [_vp]),
     "yuuka_session_set_block_table": (_i32, [_vp, _i32, _vp, _i32]),
@@ -408,6 +427,75 @@ def gemm_quant_static(stream: Stream, out: Buffer, x: Buffer, w: Buffer, n_in: i
                                         n_in, n_out, rows, path, flags, completion.h if completion else None))
 
 
+class Gguf:
+    """Validated read-only view of a GGUF model file (gguf/reader.go). Host only."""
+
+    def __init__(self, path: str):
+        self.h = C.c_void_p()
+        check(lib().yuuka_gguf_open(os.fsencode(path), C.byref(self.h)))
+
+    @property
+    def version(self) -> int:
+        return lib().yuuka_gguf_version(self.h)
+
+    @property
+    def alignment(self) -> int:
+        return lib().yuuka_gguf_alignment(self.h)
+
+    def __len__(self) -> int:
+        return lib().yuuka_gguf_tensor_count(self.h)
+
+    @property
+    def metadata_count(self) -> int:
+        return lib().yuuka_gguf_metadata_count(self.h)
+
+    @staticmethod
+    def _view(t: GgufTensor) -> dict:
+        data = np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_uint8)), shape=(t.bytes,)) if t.bytes else np.zeros(0, np.uint8)
+        return dict(name=t.name.decode(), dtype=t.dtype, dims=[int(t.dims[i]) for i in range(t.rank)], bytes=int(t.bytes),
+                    data=data)
+
+    def tensor_at(self, index: int) -> dict:
+        t = GgufTensor()
+        check(lib().yuuka_gguf_tensor_at(self.h, index, C.byref(t)))
+        return self._view(t)
+
+    def tensor(self, name: str) -> dict:
+        t = GgufTensor()
+        check(lib().yuuka_gguf_tensor_find(self.h, name.encode(), C.byref(t)))
+        return self._view(t)
+
+    def meta_int(self, key: str) -> int:
+        v = C.c_int64()
+        check(lib().yuuka_gguf_meta_int(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def meta_float(self, key: str) -> float:
+        v = C.c_double()
+        check(lib().yuuka_gguf_meta_float(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def meta_string(self, key: str) -> str:
+        p, n = C.c_void_p(), C.c_uint64()
+        check(lib().yuuka_gguf_meta_string(self.h, key.encode(), C.byref(p), C.byref(n)))
+        return C.string_at(p, n.value).decode()
+
+    def meta_array_len(self, key: str) -> int:
+        v = C.c_uint64()
+        check(lib().yuuka_gguf_meta_array_len(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def model_config(self) -> dict:
+        c = ModelConfig()
+        check(lib().yuuka_gguf_model_config(self.h, C.byref(c)))
+        return {name: getattr(c, name) for name, _ in ModelConfig._fields_}
+
+    def close(self):
+        if self.h:
+            lib().yuuka_gguf_close(self.h)
+            self.h = C.c_void_p()
+
+
 class Model:
     """Device model: GGUF tensors uploaded verbatim (engine/gpu/model.go:288-301)."""
 
@@ -421,6 +509,21 @@ class Model:
             for name, (dtype, data, rows, cols) in tensors.items():
                 self.set_tensor(name, dtype, data, rows, cols)
             self.finalize()
+
+    @classmethod
+    def from_gguf(cls, dev: Device, path: str) -> "Model":
+        """yuuka_model_load_gguf: config from the file's metadata, every tensor uploaded, finalized."""
+        g = Gguf(path)
+        try:
+            cfg = g.model_config()
+        finally:
+            g.close()
+        self = cls.__new__(cls)
+        self.dev = dev
+        self.cfg = cfg
+        self.h = C.c_void_p()
+        check(lib().yuuka_model_load_gguf(dev.h, os.fsencode(path), C.byref(self.h)))
+        return self
 
     def set_tensor(self, name: str, dtype: int, data, rows: int, cols: int):
         a = np.ascontiguousarray(data)
