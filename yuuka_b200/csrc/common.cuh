@@ -111,7 +111,9 @@ inline void set_device(const yuuka_device * dev) { YK_CUDA(cudaSetDevice(dev->in
 // as no-ops and keeps plain stream order.
 // An explicit early trigger (griddepcontrol.launch_dependents at kernel entry)
 // measured slower on the 4B verify step (3.9 ms with it in every kernel, 3.3 ms
-// with it in the small kernels only, 3.1 ms with none), so both switches are 0.
+// with it in the small kernels only, 3.1 ms with none), so both switches are 0:
+// a dependent grid that is resident early and has to block in griddepcontrol.wait
+// for microseconds resumes late (about 7 us per occurrence on the delta-net pair).
 #ifdef __CUDACC__
 #ifndef YK_PDL_EARLY_TRIGGER
 #define YK_PDL_EARLY_TRIGGER 0
@@ -122,6 +124,17 @@ __device__ __forceinline__ void pdl_trigger() {
 #endif
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A late trigger: a kernel calls this once its long part is over (a GEMM after its last row group, the
+// delta-net scan after the recurrence). The dependent grid is released when every CTA has passed this
+// point or exited, so its launch latency overlaps the epilogues of the slowest CTAs instead of following them.
+#ifndef YK_PDL_LATE_TRIGGER
+#define YK_PDL_LATE_TRIGGER 1
+#endif
+__device__ __forceinline__ void pdl_trigger_late() {
+#if YK_PDL_LATE_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
 #ifndef YK_PDL_EARLY_SMALL
 #define YK_PDL_EARLY_SMALL 0
 #endif

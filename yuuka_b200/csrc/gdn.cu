@@ -45,6 +45,9 @@ struct ScanParams {
 // decay = exp(softplus(alpha + dt) * a) (forward.go:245-248).
 // grid (2*groups + rank, nodes, batch), S threads.
 __global__ void gdn_front_kernel(const ScanParams p) {
+    // (releasing the scan from here, so that it could fetch its state while this kernel runs, measured 7 us
+    // slower per layer: a dependent grid that starts early and really has to block in griddepcontrol.wait
+    // is woken late; only triggers placed at the end of a kernel have paid)
     pdl_entry();
     const GdnArgs & a = p.a;
     const int S = a.S, N = p.rows.nodes;
@@ -208,6 +211,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         cur = node;
     }
 
+    pdl_trigger_late();
     // ---- gated RMSNorm of the head (recurrent.go:39-50) ----
     // The S / 32 column blocks of a head form one thread-block cluster: each adds up the squares of its own
     // columns, reads the others' sums through distributed shared memory, and finishes its own columns.

@@ -640,6 +640,7 @@ struct TParams {
     // while this kernel drains and the small kernels in between run
     const uint8_t * next_w;
     uint32_t next_lines;  // 128-byte lines
+    int dbg_id;           // launch id for the YK_GEMM_TIMING stamps
 };
 
 // 1 / rms of a row from its fixed-point sum of squares (2^-24 units). rmsNorm (model/qwen35/forward.go:
@@ -654,6 +655,40 @@ __device__ __forceinline__ float nf_scale(unsigned long long sumsq, int cols, fl
 __device__ __forceinline__ unsigned long long nf_fixed(float v) { return (unsigned long long)(v * 16777216.0f); }
 // silu(g) * u with the expression of silu_mul_kernel (elementwise.cu), so both forms give the same bits
 __device__ __forceinline__ float swiglu(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
+
+// Development aid, compiled out by default: with -DYK_GEMM_TIMING=1 thread 0 of every CTA folds %globaltimer
+// stamps of five points of the kernel into a per-launch row (min of the first, max of the others), and
+// yuuka_debug_gemm_stamps copies the rows out. Launch ids count up from the last reset.
+#ifndef YK_GEMM_TIMING
+#define YK_GEMM_TIMING 0
+#endif
+#if YK_GEMM_TIMING
+__device__ unsigned long long g_gemm_stamps[1024][8];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// (rows 512..1023 double as per-CTA stamps of the two launches named by g_stamp_targets: row 512 + CTA index,
+// columns 0..3 for the first, 4..7 for the second)
+__device__ int g_stamp_targets[2];
+__device__ __forceinline__ void cta_stamp(int id, int slot) {
+    const int k = id == g_stamp_targets[0] ? 10 : (id == g_stamp_targets[1] ? 11 : 0);
+    if ((k == 10 || k == 11) && (slot == 1 || slot == 3 || slot == 4 || slot == 6)) {
+        const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+        const int col = (slot == 1 ? 0 : slot == 3 ? 1 : slot == 4 ? 2 : 3) + (k == 11 ? 4 : 0);
+        if (cta < 512) {
+            g_gemm_stamps[512 + cta][col] = gtime();
+            if (slot == 1) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); g_gemm_stamps[512 + cta][col] |= (unsigned long long)sm << 56; }
+        }
+    }
+}
+#define YK_STAMP_MIN(slot) do { if (threadIdx.x == 0) atomicMin(&g_gemm_stamps[p.dbg_id & 511][slot], gtime()); } while (0)
+#define YK_STAMP_MAX(slot) do { if (threadIdx.x == 0) { atomicMax(&g_gemm_stamps[p.dbg_id & 511][slot], gtime()); cta_stamp(p.dbg_id, slot); } } while (0)
+#else
+#define YK_STAMP_MIN(slot) do { } while (0)
+#define YK_STAMP_MAX(slot) do { } while (0)
+#endif
 
 // rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
 // one warp per row, emitting f32 and the prepared form.
@@ -701,6 +736,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t xbar;
     __shared__ int last_flag;
+    YK_STAMP_MIN(0);
+    YK_STAMP_MAX(1);
     // folded norm: per input row scale / pre (consumer) and pre (producer); per warp the norm weights
     // of its row tile, fetched at the top of each group so that the epilogue does not wait on memory
     __shared__ float cs_s[FOLD ? 32 : 1], pre_s[FOLD ? 32 : 1], nw_s[FOLD ? 2 * TW * 16 : 1];
@@ -753,6 +790,8 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (sb0 + 1 < sb1) prefetch_l2_range(wbase + rt * rec_row + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
     }
     pdl_wait();
+    YK_STAMP_MIN(2);
+    YK_STAMP_MAX(3);
 
     // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums ----
     if (threadIdx.x == 0) {
@@ -806,6 +845,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         }
         if (!ok) atomicExch(&g_gemm_wait_expired, 1);
     }
+    YK_STAMP_MAX(4);
 
     uint8_t * tab = tabs + warp * C::TAB;
     const uint8_t * xrow[NT];
@@ -1070,6 +1110,9 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         }
     }
 
+    pdl_trigger_late();
+    YK_STAMP_MIN(5);
+    YK_STAMP_MAX(6);
     if (p.next_w) {
         const uint32_t first = ((blockIdx.y * gridDim.x + blockIdx.x) * (TW * 32) + threadIdx.x);
         const uint32_t step = gridDim.x * gridDim.y * (TW * 32);
@@ -1375,6 +1418,33 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     }
 }
 
+#if YK_GEMM_TIMING
+static int g_dbg_next = 0;
+}  // namespace yk
+// out: 1024 x 8 stamps. mode 1: clear the stamps and restart launch ids at 0; mode 2: clear the stamps only.
+extern "C" __attribute__((visibility("default"))) int yuuka_debug_gemm_targets(int a, int b) {
+    const int t[2] = {a, b};
+    return cudaMemcpyToSymbol(yk::g_stamp_targets, t, sizeof t) == cudaSuccess ? 0 : -1;
+}
+extern "C" __attribute__((visibility("default"))) int yuuka_debug_gemm_stamps(unsigned long long * out, int mode) {
+    static unsigned long long host[1024][8];
+    if (cudaMemcpyFromSymbol(host, yk::g_gemm_stamps, sizeof host) != cudaSuccess) return -1;
+    if (out) memcpy(out, host, sizeof host);
+    if (mode) {
+        for (auto & row : host) {
+            row[0] = row[2] = row[5] = ~0ull;
+            row[1] = row[3] = row[4] = row[6] = row[7] = 0;
+        }
+        for (int r = 512; r < 1024; r++)
+            for (auto & v : host[r]) v = 0;
+        if (cudaMemcpyToSymbol(yk::g_gemm_stamps, host, sizeof host) != cudaSuccess) return -1;
+        if (mode == 1) yk::g_dbg_next = 0;
+    }
+    return yk::g_dbg_next;
+}
+namespace yk {
+#endif
+
 template <int DT, int NT>
 static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
                             const TPlan & pl) {
@@ -1432,6 +1502,9 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
         }
         p.post_counter = a.post.counter;
     }
+#if YK_GEMM_TIMING
+    p.dbg_id = g_dbg_next++;
+#endif
     dim3 grid(pl.grid_x, pl.kchunks);
     launch_k(kern, grid, TW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
