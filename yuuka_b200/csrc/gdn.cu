@@ -295,17 +295,51 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
     const int32_t * path = p.acc.path + (int64_t)seq * N;
     auto node_at = [&](int t) { return t == 0 ? 0 : path[t - 1]; };  // t = 0..a
     if ((int)blockIdx.x < p.rank) {
+        // One head's S x S state, read and written once as float4 (HBM-bound: 2 x 64 KiB per CTA at S = 128).
+        // A thread owns four columns j and walks the rows i; the accepted rows' d values for its columns
+        // stay in registers, their keys and decays in shared memory, nine accepted rows at a time.
+        constexpr int CH = 9;
         const int h = blockIdx.x, kh = h % p.groups;
         float * st = L.state + (int64_t)((p.seq_base + seq) * p.rank + h) * S * S;
-        for (int e = threadIdx.x; e < S * S; e += blockDim.x) {
-            const int i = e / S, j = e - i * S;
-            float v = st[e];
-            for (int t = 0; t <= a; t++) {
-                const int r = seq * N + node_at(t);
-                v = state_update(v, L.decay[(int64_t)r * p.rank + h], L.khat[(int64_t)r * (p.groups * S) + kh * S + i],
-                                 L.dlog[(int64_t)r * (p.rank * S) + h * S + j]);
+        __shared__ float kh_s[CH][128];
+        __shared__ float dec_s[CH];
+        __shared__ int row_s[CH];
+        const int quads = S >> 2;
+        const int j4 = threadIdx.x % quads, i0 = threadIdx.x / quads, istep = blockDim.x / quads;
+        for (int t0 = 0; t0 <= a; t0 += CH) {
+            const int nt = min(CH, a + 1 - t0);
+            __syncthreads();
+            if (threadIdx.x < nt) {
+                const int r = seq * N + node_at(t0 + threadIdx.x);
+                row_s[threadIdx.x] = r;
+                dec_s[threadIdx.x] = L.decay[(int64_t)r * p.rank + h];
             }
-            st[e] = v;
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < nt * S; idx += blockDim.x) {
+                const int t = idx / S, i = idx - t * S;
+                kh_s[t][i] = L.khat[(int64_t)row_s[t] * (p.groups * S) + kh * S + i];
+            }
+            float4 d[CH];
+#pragma unroll
+            for (int t = 0; t < CH; t++)
+                d[t] = t < nt ? *reinterpret_cast<const float4 *>(L.dlog + (int64_t)row_s[t] * (p.rank * S) + h * S + j4 * 4)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            __syncthreads();
+            for (int i = i0; i < S; i += istep) {
+                float4 * cell = reinterpret_cast<float4 *>(st + (int64_t)i * S + j4 * 4);
+                float4 v = *cell;
+#pragma unroll
+                for (int t = 0; t < CH; t++) {
+                    if (t < nt) {
+                        const float dc = dec_s[t], k = kh_s[t][i];
+                        v.x = state_update(v.x, dc, k, d[t].x);
+                        v.y = state_update(v.y, dc, k, d[t].y);
+                        v.z = state_update(v.z, dc, k, d[t].z);
+                        v.w = state_update(v.w, dc, k, d[t].w);
+                    }
+                }
+                *cell = v;
+            }
         }
     } else {
         // history after the step = last kernel-1 raw inputs of [old history, accepted rows]
