@@ -789,8 +789,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.kernel = c.conv_kernel;
             g.eps = c.rms_eps;
             mark(s, YUUKA_OP_GDN_SCAN);
-            launch_gdn_scan(st, g, rows);
-            s->launches += 2;
+            s->launches += launch_gdn_scan(st, g, rows);
             gemm_residual_norm(s, L.out, s->gdn_out, inner, s->prep_gdn, R, L.post_norm);
         } else {
             const int nq = s->n_qkv;

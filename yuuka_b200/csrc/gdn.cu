@@ -10,13 +10,15 @@
 // gdnPerTokenScan (model/qwen35/recurrent.go:56-105). Replaces
 // conv1d_chunk / gdn_prepare_splitreg / gdn_chunk_prepared of the reference
 // (kernels/hip/prefill/prefill.hip:274-521).
+#include <cstdlib>
+
 #include "layers.cuh"
 #include "xprep.cuh"
 
 namespace yk {
 
-constexpr int GDN_COLS = 32;   // state columns per CTA (one per lane)
-constexpr int GDN_WARPS = 4;   // state rows are split over the warps
+constexpr int GDN_COLS = 32;   // state columns per CTA
+constexpr int GDN_WARPS = 4;   // each owns 8 of the 32 columns
 constexpr int GDN_MAX_NODES = 64;
 
 // float exp: the CPU reference evaluates exp in f64 and rounds; the difference is below 2e-7 relative
@@ -105,43 +107,48 @@ __global__ void gdn_front_kernel(const ScanParams p) {
 
 // ---------------------------------------------------------------------------
 // Recurrence (recurrent.go:56-105) + gated RMSNorm (recurrent.go:39-50).
-// grid (S/32 column blocks, rank, batch), 4 warps: warp w holds state rows
-// [w*S/4, (w+1)*S/4) of 32 columns in registers. The column blocks of a head are
-// one thread-block cluster: they exchange their sums of squares through
-// distributed shared memory, and each applies the gated norm to its own columns
-// and emits them as f32 and in the prepared form the out-projection GEMM reads.
+// grid (S/32 column blocks, rank, batch), the column blocks of a head forming one thread-block
+// cluster; 4 warps. A warp owns 8 state columns outright: lane = (row quarter, column), S/4 state
+// rows per lane in registers, and the two sums over the state rows close with two shuffles, so the
+// rows of a step are walked without a CTA-wide barrier (an earlier form split the state rows over
+// the warps and met at two barriers per row: 1 us more per layer). For the gated norm the column
+// blocks exchange their sums of squares through distributed shared memory, and each finishes its
+// own columns and emits them as f32 and in the prepared form the out-projection GEMM reads.
+// Redoing the front end inside this kernel (every CTA its head's q and k group and its own v
+// columns) to save the launch in between measured 9 us slower per layer: the front end is only
+// cheap when spread over its 576 CTAs.
 template <int S>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
     pdl_entry();
-    constexpr int RPW = S / GDN_WARPS;
+    constexpr int RPL = S / 4;  // state rows per lane
     const GdnArgs & a = p.a;
     const int cb = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
     const int N = p.rows.nodes;
     const int kh = h % a.groups;
     const int key_dim = a.groups * S, inner = a.rank * S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int col = cb * GDN_COLS + lane;
+    const int rq = lane >> 3, cl = warp * 8 + (lane & 7);  // row quarter; column within the block
+    const int col = cb * GDN_COLS + cl;
 
     extern __shared__ __align__(16) float sm[];
     float * qn = sm;                      // [N][S]
     float * kn = qn + N * S;              // [N][S]
     float * vv = kn + N * S;              // [N][GDN_COLS]
     float * dd = vv + N * GDN_COLS;       // [N][GDN_COLS]
-    float * dec = dd + N * GDN_COLS;      // [N]
+    float * o_s = dd + N * GDN_COLS;      // [N][GDN_COLS] outputs of this column block
+    float * dec = o_s + N * GDN_COLS;     // [N]
     float * bet = dec + N;                // [N]
-    float * red = bet + N;                // [GDN_WARPS][GDN_COLS]
-    float * red2 = red + GDN_WARPS * GDN_COLS;
-    int * par = reinterpret_cast<int *>(red2 + GDN_WARPS * GDN_COLS);  // [N]
-    float * o_s = reinterpret_cast<float *>(par + N);                   // [N][GDN_COLS] outputs of this column block
-    __shared__ double ssq[GDN_MAX_NODES];   // per row: sum of squares over this block's columns (read by the cluster)
+    int * par = reinterpret_cast<int *>(bet + N);  // [N]
+    __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
 
-    // stored state first: it does not depend on this step
-    const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + warp * RPW) * S + col;
-    float st[RPW];
+    // stored state: the longest fetch (HBM), issued first
+    const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + rq * RPL) * S + col;
+    float st[RPL];
 #pragma unroll
-    for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
+    for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
 
+    // the front-end kernel has left normalised q and k, the conv output of v, beta and decay in global memory
     for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
         const int node = i / S, e = i - node * S;
         qn[i] = a.qn[(int64_t)(seq * N + node) * key_dim + kh * S + e];
@@ -158,63 +165,54 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     }
     __syncthreads();
 
+    // ---- recurrence (recurrent.go:56-105) ----
     int cur = -1;  // node whose state st currently holds (-1: the stored state)
     for (int node = 0; node < N; node++) {
         const int pnode = par[node];
         if (pnode != cur) {
-            // a sibling branch: rebuild the parent's state from the stored one
-            // by replaying the log of the parent's path
+            // a sibling branch: rebuild the parent's state from the stored one by replaying the log of its path
 #pragma unroll
-            for (int i = 0; i < RPW; i++) st[i] = s0[(int64_t)i * S];
+            for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
             int path[GDN_MAX_NODES], len = 0;
             for (int c = pnode; c >= 0; c = par[c]) path[len++] = c;
             for (int j = len - 1; j >= 0; j--) {
                 const int c = path[j];
-                const float dc = dec[c], dv = dd[c * GDN_COLS + lane];
+                const float dc = dec[c], dv = dd[c * GDN_COLS + cl];
 #pragma unroll
-                for (int i = 0; i < RPW; i++) st[i] = state_update(st[i], dc, kn[c * S + warp * RPW + i], dv);
+                for (int i = 0; i < RPL; i++) st[i] = state_update(st[i], dc, kn[c * S + rq * RPL + i], dv);
             }
         }
-        const float * kx = kn + node * S + warp * RPW;
-        const float * qx = qn + node * S + warp * RPW;
+        const float * kx = kn + node * S + rq * RPL;
+        const float * qx = qn + node * S + rq * RPL;
         const float dc = dec[node];
-        // sk = (decay * S)^T k
-        // (four running sums: the 32-term chain of dependent FMAs was the longest wait of a row)
+        // sk = (decay * S)^T k over this lane's rows, then over the four row quarters
         float sk4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < RPW; i++) sk4[i & 3] = fmaf(st[i] * dc, kx[i], sk4[i & 3]);
+        for (int i = 0; i < RPL; i++) sk4[i & 3] = fmaf(st[i] * dc, kx[i], sk4[i & 3]);
         float sk = (sk4[0] + sk4[1]) + (sk4[2] + sk4[3]);
-        red[warp * GDN_COLS + lane] = sk;
-        __syncthreads();
-        sk = 0.0f;
-#pragma unroll
-        for (int w = 0; w < GDN_WARPS; w++) sk += red[w * GDN_COLS + lane];
-        const float d = (vv[node * GDN_COLS + lane] - sk) * bet[node];
+        sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+        sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+        const float d = (vv[node * GDN_COLS + cl] - sk) * bet[node];
         float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < RPW; i++) {
+        for (int i = 0; i < RPL; i++) {
             st[i] = state_update(st[i], dc, kx[i], d);
             o4[i & 3] = fmaf(st[i], qx[i], o4[i & 3]);
         }
         float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-        red2[warp * GDN_COLS + lane] = o;
-        if (warp == 0) dd[node * GDN_COLS + lane] = d;
-        __syncthreads();
-        // red is rewritten only after the next barrier, red2 only after the one after that
-        if (warp == 0) {
-            o = 0.0f;
-#pragma unroll
-            for (int w = 0; w < GDN_WARPS; w++) o += red2[w * GDN_COLS + lane];
-            o_s[node * GDN_COLS + lane] = o;
+        o += __shfl_xor_sync(0xffffffffu, o, 8);
+        o += __shfl_xor_sync(0xffffffffu, o, 16);
+        if (rq == 0) {
+            o_s[node * GDN_COLS + cl] = o;
+            dd[node * GDN_COLS + cl] = d;
             a.dlog[(int64_t)(seq * N + node) * inner + h * S + col] = d;
         }
+        __syncwarp();  // dd of this row is read by the other row quarters when a later branch replays it
         cur = node;
     }
 
     pdl_trigger_late();
-    // ---- gated RMSNorm of the head (recurrent.go:39-50) ----
-    // The S / 32 column blocks of a head form one thread-block cluster: each adds up the squares of its own
-    // columns, reads the others' sums through distributed shared memory, and finishes its own columns.
+    // ---- gated RMSNorm of the head (recurrent.go:39-50), sums of squares exchanged across the cluster ----
     __syncthreads();
     for (int node = warp; node < N; node += GDN_WARPS) {
         const double v = (double)o_s[node * GDN_COLS + lane];
@@ -253,17 +251,17 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     }
 }
 
-void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
+int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per sequence", GDN_MAX_NODES);
     YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
     YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
     ScanParams p{a, rows};
     const int N = rows.nodes;
+    dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
-    size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 2 * N + 2 * GDN_WARPS * GDN_COLS + N);
-    dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
+    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         launch_k_cluster(gdn_scan_kernel<128>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
@@ -272,6 +270,7 @@ void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
         launch_k_cluster(gdn_scan_kernel<64>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
     }
     YK_CUDA(cudaGetLastError());
+    return 2;
 }
 
 // ---------------------------------------------------------------------------

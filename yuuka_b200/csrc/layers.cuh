@@ -82,8 +82,8 @@ struct GdnArgs {
     int groups, rank, S, kernel;
     float eps;
 };
-// conv + norms (one kernel), then the recurrence with the gated RMSNorm folded in (one kernel)
-void launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
+// conv + norms, the recurrence and the gated RMSNorm; returns the number of kernels launched
+int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
 // out[r][h][:] = rmsnorm(out[r][h][:]) * norm * silu(z[r][h][:]) (recurrent.go:39-50)
 void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
                           int S, int rows, float eps, XPrepOut prep = XPrepOut());
