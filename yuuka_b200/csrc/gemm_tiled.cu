@@ -789,14 +789,38 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (sb0 < sb1) C::load(wbase + rt * rec_row + (size_t)sb0 * C::REC, lane, cur);
         if (sb0 + 1 < sb1) prefetch_l2_range(wbase + rt * rec_row + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
     }
+    // (the barrier the activation copies complete on: set up while the previous kernel still runs)
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&xbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     pdl_wait();
     YK_STAMP_MIN(2);
     YK_STAMP_MAX(3);
 
-    // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums ----
-    if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&xbar)) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums,
+    // every row's pair issued by its own lane of the first warp ----
+    if (warp == 0) {
+        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
+        const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = (uint32_t)cnt * 64;
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * Mrows)
+                         : "memory");
+        __syncwarp();
+        for (int m = lane; m < Mrows; m += 32) {
+            const size_t mr = row_index ? (size_t)row_index[m] : (size_t)m;
+            const __half * srcx = xhp + (mr * p.nsb + c0) * 256;
+            const __half2 * srcs = xsp + (mr * p.nsb + c0) * 16;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * xstride)),
+                         "l"(srcx), "r"(row_bytes_x), "r"(bar)
+                         : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(xsum + (size_t)m * xsum_stride)),
+                         "l"(srcs), "r"(row_bytes_s), "r"(bar)
+                         : "memory");
+        }
     }
     if constexpr (FOLD) {
         const int m = (int)threadIdx.x - 32;  // second warp: the first issues the copies
@@ -811,26 +835,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             cs_s[m] = cs;
             pre_s[m] = pre;
         }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
-        const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = (uint32_t)cnt * 64;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * Mrows)
-                     : "memory");
-        for (int m = 0; m < Mrows; m++) {
-            const size_t mr = row_index ? (size_t)row_index[m] : (size_t)m;
-            const __half * srcx = xhp + (mr * p.nsb + c0) * 256;
-            const __half2 * srcs = xsp + (mr * p.nsb + c0) * 16;
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * xstride)),
-                         "l"(srcx), "r"(row_bytes_x), "r"(bar)
-                         : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(xsum + (size_t)m * xsum_stride)),
-                         "l"(srcs), "r"(row_bytes_s), "r"(bar)
-                         : "memory");
-        }
+        __syncthreads();  // the row scales are read by every warp's epilogue
     }
     {
         // bounded wait for the copies; on expiry the error word is set and the results are garbage
