@@ -293,7 +293,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
             "data": "synthetic", "config": workload_config(args),
             "accepted_per_step": accepted_total / args.steps, "emitted_per_step": emitted_total / args.steps,
             "e2e": {"value": emitted_all / t_e2e, "unit": UNIT, "ms_per_step": t_e2e / args.steps * 1e3,
-                    "h2d_bytes_per_step": rows * (4 + 4 + 4 + 8), "d2h_bytes_per_step": 4 + 2 * rows * 4},
+                    # one copy in: ancestor masks, tokens, parents, depths; one copy out: accepted count, path, emitted
+                    # tokens, plus the two device error words
+                    "h2d_bytes_per_step": rows * (8 + 4 + 4 + 4), "d2h_bytes_per_step": 4 + 2 * rows * 4 + 8},
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "gemm_tiled_mma_kernel (every quantized GEMM launch of a step, LM head included)",

@@ -527,6 +527,13 @@ struct yuuka_session {
     int32_t * d_tables = nullptr;
     std::vector<int> h_pos, h_pos_upper;
     // per step
+    // row metadata of a step, one device block [anc | tokens | parent | depth] filled by one copy from the
+    // page-locked mirror h_rows; results [accepted | path | emitted] likewise come back in one copy to h_results
+    uint8_t * d_rows = nullptr;
+    uint8_t * h_rows = nullptr;
+    int32_t * d_results = nullptr;
+    int32_t * h_results = nullptr;  // + two words for the device error flags
+    int rows_cap = 0;
     int32_t * d_tokens = nullptr;
     int32_t * d_parent = nullptr;
     int32_t * d_depth = nullptr;
@@ -984,9 +991,13 @@ void sync_and_check(yuuka_session * s) {
 // Uploads row metadata of a step: tokens, parents, depths, ancestor masks.
 void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t * tokens, const int32_t * parent) {
     const int vocab = s->model->cfg.vocab;
-    const int R = batch * nodes;
-    std::vector<int32_t> par(R), dep(R);
-    std::vector<uint64_t> anc(R);
+    const int R = batch * nodes, cap = s->rows_cap;
+    YK_REQUIRE(R <= cap, YUUKA_ERR_INTERNAL, "stage_rows: %d rows exceed the session's %d", R, cap);
+    // the previous copy out of the page-locked mirror has completed: every step is synchronized before the next is staged
+    uint64_t * anc = reinterpret_cast<uint64_t *>(s->h_rows);
+    int32_t * tok = reinterpret_cast<int32_t *>(s->h_rows + (size_t)cap * 8);
+    int32_t * par = tok + cap;
+    int32_t * dep = par + cap;
     for (int b = 0; b < batch; b++) {
         for (int i = 0; i < nodes; i++) {
             const int r = b * nodes + i;
@@ -995,6 +1006,7 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
             int p = parent ? parent[r] : i - 1;
             YK_REQUIRE((i == 0 && p == -1) || (i > 0 && p >= 0 && p < i), YUUKA_ERR_INVALID_ARGUMENT,
                        "parent[%d][%d] = %d is not a preceding row", b, i, p);
+            tok[r] = tokens[r];
             par[r] = p;
             dep[r] = i == 0 ? 0 : dep[b * nodes + p] + 1;
             anc[r] = (i == 0 ? 0ull : anc[b * nodes + p]) | (1ull << i);
@@ -1003,12 +1015,8 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
                    "token sequence of %d exceeds remaining context %d", nodes,
                    s->cfg.capacity - s->h_pos_upper[seq0 + b]);
     }
-    cudaStream_t st = s->stream.s;
-    YK_CUDA(cudaMemcpyAsync(s->d_tokens, tokens, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
-    YK_CUDA(cudaMemcpyAsync(s->d_parent, par.data(), sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
-    YK_CUDA(cudaMemcpyAsync(s->d_depth, dep.data(), sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
-    YK_CUDA(cudaMemcpyAsync(s->d_anc, anc.data(), sizeof(uint64_t) * R, cudaMemcpyHostToDevice, st));
-    YK_CUDA(cudaStreamSynchronize(st));  // the host vectors go out of scope
+    // one copy for the whole block (the arrays keep their capacity-sized offsets on both sides)
+    YK_CUDA(cudaMemcpyAsync(s->d_rows, s->h_rows, (size_t)cap * 20, cudaMemcpyHostToDevice, s->stream.s));
 }
 
 // Key-range bound used to size the attention grid. It is the session capacity,
@@ -1172,10 +1180,19 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             YK_CUDA(cudaMemcpy(s->d_tables, ident.data(), ident.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
             s->h_pos.assign(B, 0);
             s->h_pos_upper.assign(B, 0);
-            s->d_tokens = dalloc<int32_t>(R, s->owned);
-            s->d_parent = dalloc<int32_t>(R, s->owned);
-            s->d_depth = dalloc<int32_t>(R, s->owned);
-            s->d_anc = dalloc<uint64_t>(R, s->owned);
+            s->rows_cap = R;
+            s->d_rows = dalloc<uint8_t>((size_t)R * 20, s->owned);
+            s->d_anc = reinterpret_cast<uint64_t *>(s->d_rows);
+            s->d_tokens = reinterpret_cast<int32_t *>(s->d_rows + (size_t)R * 8);
+            s->d_parent = s->d_tokens + R;
+            s->d_depth = s->d_parent + R;
+            {
+                void * hp = nullptr;
+                YK_REQUIRE(cudaMallocHost(&hp, (size_t)R * 20 + sizeof(int32_t) * ((size_t)B + 2 * R + 2)) == cudaSuccess,
+                           YUUKA_ERR_ALLOCATION, "page-locked staging allocation failed");
+                s->h_rows = (uint8_t *)hp;
+                s->h_results = reinterpret_cast<int32_t *>(s->h_rows + (size_t)R * 20);
+            }
             const int H = c.hidden;
             s->x = dalloc<float>((size_t)R * H, s->owned);
             s->xn = dalloc<float>((size_t)R * H, s->owned);
@@ -1230,10 +1247,11 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->argmax.chunks = argmax_chunks(c.vocab);
             s->argmax.val = dalloc<float>((size_t)R * s->argmax.chunks, s->owned);
             s->argmax.idx = dalloc<int32_t>((size_t)R * s->argmax.chunks, s->owned);
-            s->acc.accepted = dalloc<int32_t>(B, s->owned);
+            s->d_results = dalloc<int32_t>((size_t)B + 2 * R, s->owned);
+            s->acc.accepted = s->d_results;
+            s->acc.path = s->d_results + B;
+            s->acc.emitted = s->acc.path + R;
             s->d_uniforms = dalloc<float>((size_t)R * 2, s->owned);
-            s->acc.path = dalloc<int32_t>(R, s->owned);
-            s->acc.emitted = dalloc<int32_t>(R, s->owned);
             {
                 // rows x splits of the flash-decoding partials, for the verify shape and for a prompt chunk
                 auto need = [&](int bx, int nx) {
@@ -1274,6 +1292,7 @@ void yuuka_session_destroy(yuuka_session * s) {
     }
     for (auto & g : s->graphs) cudaGraphExecDestroy(g.exec);
     for (void * p : s->owned) cudaFree(p);
+    if (s->h_rows) cudaFreeHost(s->h_rows);
     gemm_scratch_free(s->gemm);
     delete s;
 }
@@ -1508,14 +1527,22 @@ yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * b)
         set_device(s->model->dev);
         s->launched = false;
         s->staged = false;
-        sync_and_check(s);
+        // results and the device error flags come back behind the step's kernels; one synchronization for all
         const int B = s->st_batch, N = s->st_nodes;
-        std::vector<int32_t> acc(B);
+        const int maxB = s->cfg.max_batch, cap = s->rows_cap;
+        int32_t * err2 = s->h_results + maxB + 2 * cap;
+        if (s->st_mode != YUUKA_ACCEPT_NONE)
+            YK_CUDA(cudaMemcpyAsync(s->h_results, s->d_results, sizeof(int32_t) * ((size_t)maxB + 2 * cap), cudaMemcpyDeviceToHost,
+                                    s->stream.s));
+        enqueue_device_error_read(s->stream.s, err2);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        YK_REQUIRE((err2[0] | err2[1]) == 0, YUUKA_ERR_DEVICE, "a bounded wait inside a kernel expired (code %d); results are invalid",
+                   err2[0] | err2[1]);
+        const int32_t * acc = s->h_results;
         if (s->st_mode != YUUKA_ACCEPT_NONE) {
-            YK_CUDA(cudaMemcpy(acc.data(), s->acc.accepted, sizeof(int32_t) * B, cudaMemcpyDeviceToHost));
-            if (b->accepted) memcpy(b->accepted, acc.data(), sizeof(int32_t) * B);
-            if (b->emitted) YK_CUDA(cudaMemcpy(b->emitted, s->acc.emitted, sizeof(int32_t) * B * N, cudaMemcpyDeviceToHost));
-            if (b->path) YK_CUDA(cudaMemcpy(b->path, s->acc.path, sizeof(int32_t) * B * N, cudaMemcpyDeviceToHost));
+            if (b->accepted) memcpy(b->accepted, acc, sizeof(int32_t) * B);
+            if (b->path) memcpy(b->path, s->h_results + maxB, sizeof(int32_t) * B * N);
+            if (b->emitted) memcpy(b->emitted, s->h_results + maxB + cap, sizeof(int32_t) * B * N);
             for (int i = 0; i < B; i++) {
                 s->h_pos[s->st_seq0 + i] += acc[i] + 1;
                 s->h_pos_upper[s->st_seq0 + i] = s->h_pos[s->st_seq0 + i];

@@ -20,6 +20,12 @@ int read_device_error(const yuuka_device * dev) {
     return v | read_gemm_wait_expired();
 }
 
+// The same two flags copied behind the work already queued on `stream`, into two page-locked words.
+void enqueue_device_error_read(cudaStream_t stream, int * out2) {
+    YK_CUDA(cudaMemcpyFromSymbolAsync(out2, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+    enqueue_gemm_wait_expired_read(stream, out2 + 1);
+}
+
 // ===========================================================================
 // fp32 route
 

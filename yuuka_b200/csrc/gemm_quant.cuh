@@ -46,5 +46,6 @@ void gemm_scratch_free(GemmScratch & s);
 // Sticky device-side error word: set when a bounded wait inside a kernel gave
 // up. Reading it synchronises the device.
 int read_device_error(const yuuka_device * dev);
+void enqueue_device_error_read(cudaStream_t stream, int * out2);
 
 }  // namespace yk

@@ -1781,5 +1781,8 @@ int read_gemm_wait_expired() {
     cudaMemcpyFromSymbol(&v, g_gemm_wait_expired, sizeof(int));
     return v;
 }
+void enqueue_gemm_wait_expired_read(cudaStream_t stream, int * out) {
+    YK_CUDA(cudaMemcpyFromSymbolAsync(out, g_gemm_wait_expired, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+}
 
 }  // namespace yk

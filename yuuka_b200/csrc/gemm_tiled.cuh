@@ -117,5 +117,6 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
 
 // Non-zero once a bounded wait inside a GEMM kernel has expired (sticky).
 int read_gemm_wait_expired();
+void enqueue_gemm_wait_expired_read(cudaStream_t stream, int * out);
 
 }  // namespace yk
