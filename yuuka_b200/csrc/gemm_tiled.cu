@@ -21,6 +21,7 @@
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -1327,17 +1328,41 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     // K chunks across CTAs that shared memory forces anyway (the activations of all rows must fit two CTAs per SM)
     int kc_fit = 1;
     while ((nsb + kc_fit - 1) / kc_fit > 1 && mma_smem(dtype, m, (nsb + kc_fit - 1) / kc_fit, nt, 2, paired) > budget) kc_fit++;
-    // warps per row tile: as many K parts as needed to give every resident CTA a (group, chunk). Measured on
-    // 2560 x 9216 Q6_K at 9 rows, where three chunks are forced: four warps per tile 27.7 us, eight 29.9 us.
+    // warps per row tile (K parts inside a CTA): the choice that minimises waves x records per warp, where a
+    // wave is one (group, chunk) on every resident CTA slot and 0.7 of a record stands for the fixed cost of
+    // a group (table set-up, reduction, epilogue); ties go to fewer parts. Measured in the 4B step at 9 rows:
+    // 12352 x 2560 with two parts (193 groups, one wave of five records) 2.385 ms per step against 2.428 with
+    // four (386 groups on 296 slots: a quarter of the CTAs run two groups of three records); 2560 x 9216 Q6_K,
+    // where three chunks are forced, four parts 27.7 us against eight 29.9 us.
     int ks = 1;
-    while (ks < (paired ? TW / 2 : TW) && (n_tiles * ks) / TW * kc_fit < slots * 4 / 5 && nsb / (2 * ks) >= 1) ks *= 2;
-    // YUUKA_GEMM_PLAN=ks,kchunks overrides both choices (experiments; kchunks still grows until shared memory fits)
-    static const int forced_ks = [] { const char * e = getenv("YUUKA_GEMM_PLAN"); return e ? atoi(e) : 0; }();
-    static const int forced_kc = [] {
-        const char * e = getenv("YUUKA_GEMM_PLAN");
-        const char * c = e ? strchr(e, ',') : nullptr;
-        return c ? atoi(c + 1) : 0;
-    }();
+    {
+        const int nsb_c = (nsb + kc_fit - 1) / kc_fit;
+        double best = 1e30;
+        for (int k = 1; k <= (paired ? TW / 2 : TW); k *= 2) {
+            if (k > 1 && nsb_c < k) break;  // every warp keeps at least one record
+            const int groups = (n_tiles + TW / k - 1) / (TW / k);
+            const int waves = (groups * kc_fit + slots - 1) / slots;
+            const double cost = waves * ((nsb_c + k - 1) / k + 0.7);
+            if (cost < best - 1e-9) {
+                best = cost;
+                ks = k;
+            }
+        }
+    }
+    // YUUKA_GEMM_PLAN=ks,kchunks overrides both choices for every shape, YUUKA_GEMM_PLAN_<n_out>x<n_in>=ks,kchunks
+    // for one (experiments; kchunks still grows until shared memory fits)
+    int forced_ks = 0, forced_kc = 0;
+    {
+        char name[64];
+        snprintf(name, sizeof name, "YUUKA_GEMM_PLAN_%dx%d", n_out, n_in);
+        const char * e = getenv(name);
+        if (!e) e = getenv("YUUKA_GEMM_PLAN");
+        if (e) {
+            forced_ks = atoi(e);
+            const char * c = strchr(e, ',');
+            forced_kc = c ? atoi(c + 1) : 0;
+        }
+    }
     if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || (forced_ks == 8 && !paired)) ks = forced_ks;
     pl.KS = ks;
     pl.TG = TW / ks;
