@@ -143,3 +143,88 @@ def test_rejection_at_vanishing_temperature_accepts_what_greedy_accepts(full):
     assert int(r.accepted[0]) == int(g.accepted[0]) == 6
     assert r.emitted[0, :7].tolist() == g.emitted[0, :7].tolist()
     qb.free()
+
+
+def test_one_gpu_share_of_the_batched_tree_configuration(full):
+    """32 sequences (the per-GPU share of 256 on eight GPUs), 17-row trees, rejection sampling at T = 0.8,
+    permuted block tables, prompts of different lengths: the step is reproducible, every accepted path is a
+    root-to-node path of the tree whose tokens are the emitted ones, positions advance by what was emitted,
+    and at a vanishing temperature with one-hot drafts the walk is the greedy walk of the same step."""
+    cfg, dev, model = full["cfg"], full["dev"], full["model"]
+    V, B, bs = cfg["vocab"], 32, 16
+    parent = synth.tree_16()
+    N = parent.size
+    cap = 256
+    per = cap // bs
+    sess = cuda.Session(model, max_batch=B, max_nodes=N, capacity=cap, kv_format=cuda.KV_F16, block_size=bs)
+    perm = np.random.default_rng(11).permutation(B * per).astype(np.int32)
+    pend = []
+    for b in range(B):
+        sess.set_block_table(b, perm[b * per:(b + 1) * per])
+        prompt = synth.uniform_i32(48 + 5 * b, 0, V, 300 + b)
+        pend.append(int(np.argmax(sess.forward(prompt, seq=b))))
+    snaps = [sess.snapshot(b) for b in range(B)]
+    pos = [sess.position(b) for b in range(B)]
+
+    def rewind():
+        for b in range(B):
+            sess.restore(snaps[b], seq=b)
+            sess.set_position(b, pos[b])
+
+    tokens = synth.uniform_i32(B * N, 0, V, 77).reshape(B, N)
+    tokens[:, 0] = pend
+    # let a few branches carry the model's own choice, one and two levels deep (node 5 hangs off node 1)
+    lg = sess.verify(tokens, parent=parent, mode=cuda.ACCEPT_NONE, want_logits=True).logits
+    for b in range(0, B, 2):
+        tokens[b, 1] = int(np.argmax(lg[b, 0]))
+    rewind()
+    lg = sess.verify(tokens, parent=parent, mode=cuda.ACCEPT_NONE, want_logits=True).logits
+    for b in range(0, B, 4):
+        tokens[b, 5] = int(np.argmax(lg[b, 1]))
+    del lg
+    rewind()
+    noise = synth.normal_f32(B * N * 64, 1.0, 5).reshape(B, N, 64)
+    q = np.full((B, N, V), 1e-9, np.float32)
+    for b in range(B):
+        for i in range(N):
+            q[b, i, tokens[b, i]] = 0.5 + 0.4 * np.tanh(noise[b, i, 0])
+    # at T = 0.8 this model's distribution over 248,320 tokens is flat, so a draft is accepted (u q <= p) only where
+    # the draft model was much less sure than the target: the seeded branches get a tiny q
+    for b in range(0, B, 2):
+        q[b, 1, tokens[b, 1]] = 1e-7
+    for b in range(0, B, 4):
+        q[b, 5, tokens[b, 5]] = 1e-7
+    qb = dev.upload(q)
+    u = synth.uniform_f32(B * N * 2, 9).reshape(B, N, 2)
+    runs = []
+    for _ in range(2):
+        r = sess.verify(tokens, parent=parent, mode=cuda.ACCEPT_REJECTION, temperature=0.8, draft_probs=qb, uniforms=u)
+        runs.append((r.accepted.copy(), r.path.copy(), r.emitted.copy(), [sess.position(b) for b in range(B)]))
+        rewind()
+    assert all(np.array_equal(runs[0][k], runs[1][k]) for k in range(3)) and runs[0][3] == runs[1][3]
+    acc, path, emitted, newpos = runs[0]
+    assert acc.max() >= 2 and (acc[0::2] >= 1).all() and (acc[0::4] >= 2).all()
+    for b in range(B):
+        a, node = int(acc[b]), 0
+        for t in range(a):
+            nxt = int(path[b, t])
+            assert parent[nxt] == node and int(emitted[b, t]) == int(tokens[b, nxt])
+            node = nxt
+        assert 0 <= int(emitted[b, a]) < V
+        assert newpos[b] == pos[b] + a + 1
+    # vanishing temperature, one-hot drafts: the greedy walk of the same step
+    g = sess.verify(tokens, parent=parent)
+    g_out = (g.accepted.copy(), g.path.copy(), g.emitted.copy())
+    rewind()
+    q[:] = 0.0
+    for b in range(B):
+        q[b, np.arange(N), tokens[b]] = 1.0
+    qb.write(q)
+    c = sess.verify(tokens, parent=parent, mode=cuda.ACCEPT_REJECTION, temperature=1e-3, draft_probs=qb,
+                    uniforms=np.full((B, N, 2), 0.5, np.float32))
+    assert np.array_equal(c.accepted, g_out[0])
+    for b in range(B):
+        a = int(g_out[0][b])
+        assert c.path[b, :a].tolist() == g_out[1][b, :a].tolist() and c.emitted[b, :a + 1].tolist() == g_out[2][b, :a + 1].tolist()
+    qb.free()
+    sess.close()
