@@ -275,3 +275,33 @@ def test_wide_hidden_narrow_ffn_model_matches_oracle():
     err = float(np.max(np.abs(got - want)))
     assert err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
     st.close(); gm.close(); dev.close()
+
+
+@pytest.mark.parametrize("kv", [cuda.KV_F32, cuda.KV_F16])
+def test_long_prompts_run_as_wide_passes_with_mixer_sub_chunks(tiny, kv):
+    """Prompts beyond 64 tokens: 256-row passes for the GEMMs, 64-row sub-chunks for the delta-net scan, its
+    state commit and the attention, a ragged tail (300 = 256 + 44, 150 = 64 + 64 + 22)."""
+    cfg, gm, om = tiny
+    V = cfg["vocab"]
+    prompt = synth.uniform_i32(300, 0, V, 71)
+    st = yo.State(om, 512, kv)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=512, kv_format=kv)
+    lo = st.forward(prompt.tolist())
+    lg = sess.forward(prompt)
+    assert sess.position() == st.pos == 300
+    err = float(np.max(np.abs(lg - lo)))
+    assert err <= 2e-2 and cosine(lg, lo) >= 0.9999, (err, cosine(lg, lo))
+    assert np.max(np.abs(sess.snapshot().view(np.float32) - st.snapshot().view(np.float32))) <= 4e-3
+    # decoding continues from the committed state and KV rows
+    nxt = yo.argmax(lo)
+    err = float(np.max(np.abs(sess.forward([nxt]) - st.step(nxt))))
+    assert err <= 2e-2, err
+    sess.close(); st.close()
+    # all-position logits over 150 tokens
+    st = yo.State(om, 256, kv)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=256, kv_format=kv)
+    want = st.prefill_logits(prompt[:150])
+    got = sess.prefill_logits(prompt[:150])
+    err = float(np.max(np.abs(got - want)))
+    assert got.shape == (150, V) and err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
+    sess.close(); st.close()

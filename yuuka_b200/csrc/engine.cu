@@ -534,6 +534,8 @@ struct yuuka_session {
     int32_t * d_results = nullptr;
     int32_t * h_results = nullptr;  // + two words for the device error flags
     int rows_cap = 0;
+    int32_t * d_pos_sub = nullptr;   // [CHAIN_MAX_SUBS] first position of every sub-chunk of a wide prompt pass
+    int32_t * d_acc_sub = nullptr;   // [CHAIN_MAX_SUBS] rows - 1 of every sub-chunk (its forced acceptance)
     int32_t * d_tokens = nullptr;
     int32_t * d_parent = nullptr;
     int32_t * d_depth = nullptr;
@@ -724,15 +726,37 @@ enum LogitRows { LOGITS_NONE, LOGITS_LAST, LOGITS_ALL };
 
 // Prompt tokens run through the step kernels in chains of up to this many rows (the row masks are 64 bits
 // wide); from 48 rows on the GEMMs take the tensor-memory route.
-constexpr int CHAIN_ROWS = 64;
+// A prompt runs in passes of up to CHAIN_ROWS rows: the GEMMs and row-wise kernels take the whole pass (the
+// tensor-memory GEMM route decodes a weight tile once for up to 256 rows), the sequential mixers (delta-net
+// scan + state commit, attention front end + attention) walk it in sub-chunks of CHAIN_SUB rows, the limit
+// of their per-step row bookkeeping (64-bit ancestor masks).
+constexpr int CHAIN_ROWS = 256;
+constexpr int CHAIN_SUB = 64;
+constexpr int CHAIN_MAX_SUBS = CHAIN_ROWS / CHAIN_SUB;
 
 // Enqueues one step over sequences [seq0, seq0+batch) with `nodes` rows each.
-void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, LogitRows logit_rows, int max_total) {
+// sub > 0: a wide prompt pass of one sequence (see CHAIN_ROWS), staged by stage_rows with the same sub.
+void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, LogitRows logit_rows, int max_total,
+              int sub = 0) {
     yuuka_model * m = s->model;
     const yuuka_model_config & c = m->cfg;
     cudaStream_t st = s->stream.s;
     const int R = batch * nodes, H = c.hidden;
     RowMeta rows{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos0 + seq0, batch, nodes};
+    YK_REQUIRE(sub == 0 || (batch == 1 && mode == 3u && nodes <= CHAIN_MAX_SUBS * sub), YUUKA_ERR_INTERNAL,
+               "a wide pass is one forced-commit chain");
+    const int n_sub = sub > 0 ? (nodes + sub - 1) / sub : 1;
+    // sub-chunk k as a step of its own: rows [k * sub, ...), positions from d_pos_sub[k]
+    auto sub_rows = [&](int k) {
+        const int r0 = k * sub, n = nodes - r0 < sub ? nodes - r0 : sub;
+        return RowMeta{s->d_tokens + r0, s->d_parent + r0, s->d_depth + r0, s->d_anc + r0, s->d_pos_sub + k, 1, n};
+    };
+    int gdn_index = 0;  // position of the current recurrent layer in d_gdn_commit
+    if (sub > 0) {
+        // the per-layer commits of the sub-chunks walk the identity path 1, 2, 3, ...
+        launch_accept_all(st, rows, s->acc);
+        s->launches++;
+    }
     const int K1 = c.conv_kernel - 1;
     const int conv_dim = m->conv_dim(), inner = c.inner_size, rank = c.time_step_rank, S = c.state_size;
     const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
@@ -742,7 +766,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
     s->launches++;
     if (s->rope_cs) {
-        launch_rope_table(st, s->rope_cs, rows, c.rope_dim, c.rope_freq_base);
+        // (a wide pass: every sub-chunk counts positions from its own start; rows past the end are scratch)
+        RowMeta rr = sub > 0 ? RowMeta{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos_sub, n_sub, sub} : rows;
+        launch_rope_table(st, s->rope_cs, rr, c.rope_dim, c.rope_freq_base);
         s->launches++;
     }
     // the first layer's input norm is a kernel of its own; with 3..32 rows every later norm is folded into
@@ -796,7 +822,36 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.kernel = c.conv_kernel;
             g.eps = c.rms_eps;
             mark(s, YUUKA_OP_GDN_SCAN);
-            s->launches += launch_gdn_scan(st, g, rows);
+            if (sub == 0) {
+                s->launches += launch_gdn_scan(st, g, rows);
+            } else {
+                // sub-chunk after sub-chunk: scan, then this layer's state and conv history move on before the next
+                const int key_dim = c.group_count * S;
+                for (int k = 0; k < n_sub; k++) {
+                    const int64_t r0 = (int64_t)k * sub;
+                    GdnArgs gk = g;
+                    gk.proj = g.proj + r0 * np;
+                    gk.z = g.z + r0 * np;
+                    gk.out = g.out + r0 * inner;
+                    if (g.prep.xh) {
+                        gk.prep.xh = g.prep.xh + r0 * inner;
+                        gk.prep.xs16 = g.prep.xs16 + r0 * (inner / 16);
+                    }
+                    gk.qn = g.qn + r0 * key_dim;
+                    gk.vconv = g.vconv + r0 * inner;
+                    gk.beta = g.beta + r0 * rank;
+                    gk.khat = g.khat + r0 * key_dim;
+                    gk.dlog = g.dlog + r0 * inner;
+                    gk.decay = g.decay + r0 * rank;
+                    const RowMeta rk = sub_rows(k);
+                    s->launches += launch_gdn_scan(st, gk, rk);
+                    AcceptOut ak{s->d_acc_sub + k, s->acc.path, s->acc.emitted};
+                    launch_gdn_commit(st, s->d_gdn_commit + gdn_index, 1, c.group_count, rank, S, c.conv_kernel, conv_dim, seq0, rk,
+                                      ak, (int)r0);
+                    s->launches++;
+                }
+            }
+            gdn_index++;
             gemm_residual_norm(s, L.out, s->gdn_out, inner, s->prep_gdn, R, L.post_norm);
         } else {
             const int nq = s->n_qkv;
@@ -822,12 +877,14 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             pool.tables = s->d_tables + (int64_t)seq0 * s->table_stride;
             pool.table_stride = s->table_stride;
             mark(s, YUUKA_OP_ATTN_PREP);
-            launch_attn_prep(st, qb, nq, kb, nq, vb, nq, L.q_norm, L.k_norm, c.heads, c.kv_heads, c.head_dim, c.rope_dim,
-                             s->rope_cs, c.rms_eps, rows, pool);
-            s->launches++;
+            if (sub == 0) {
+                launch_attn_prep(st, qb, nq, kb, nq, vb, nq, L.q_norm, L.k_norm, c.heads, c.kv_heads, c.head_dim, c.rope_dim,
+                                 s->rope_cs, c.rms_eps, rows, pool);
+                s->launches++;
+            }
             AttnScratch sc;
             const int G = c.heads / c.kv_heads;
-            const int qtiles = (G * nodes + 39) / 40;
+            const int qtiles = (G * (sub > 0 ? sub : nodes) + 39) / 40;
             const int base = c.kv_heads * qtiles * batch;
             // about one CTA per SM at capacity (measured at a 1500-token context: 3.11 ms per step, against 3.16 with
             // two or four per SM: fewer partials for the merge kernel outweigh the shorter key ranges)
@@ -843,11 +900,29 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             sc.key_split = (((max_total + splits - 1) / splits + 31) / 32) * 32;
             sc.splits = (max_total + sc.key_split - 1) / sc.key_split;
             sc.partial = s->attn_partial;
-            YK_REQUIRE(attention_scratch_floats(R, c.heads, c.head_dim, sc.splits) <= s->attn_partial_floats,
+            YK_REQUIRE(attention_scratch_floats(sub > 0 ? sub : R, c.heads, c.head_dim, sc.splits) <= s->attn_partial_floats,
                        YUUKA_ERR_INTERNAL, "attention scratch is too small");
             mark(s, YUUKA_OP_ATTENTION);
-            s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
-                                            max_total, sc, s->prep_attn);
+            if (sub == 0) {
+                s->launches += launch_attention(st, s->attn_out, o_dim, qb, nq, c.heads, c.kv_heads, c.head_dim, rows, pool,
+                                                max_total, sc, s->prep_attn);
+            } else {
+                // a sub-chunk's K/V rows are in the pool before the next sub-chunk's queries look for them
+                const int half = c.rope_dim / 2;
+                for (int k = 0; k < n_sub; k++) {
+                    const int64_t r0 = (int64_t)k * sub;
+                    const RowMeta rk = sub_rows(k);
+                    launch_attn_prep(st, qb + r0 * nq, nq, kb + r0 * nq, nq, vb + r0 * nq, nq, L.q_norm, L.k_norm, c.heads,
+                                     c.kv_heads, c.head_dim, c.rope_dim, s->rope_cs + r0 * half, c.rms_eps, rk, pool);
+                    XPrepOut pk = s->prep_attn;
+                    if (pk.xh) {
+                        pk.xh += r0 * o_dim;
+                        pk.xs16 += r0 * (o_dim / 16);
+                    }
+                    s->launches += 1 + launch_attention(st, s->attn_out + r0 * o_dim, o_dim, qb + r0 * nq, nq, c.heads, c.kv_heads,
+                                                        c.head_dim, rk, pool, max_total, sc, pk);
+                }
+            }
             gemm_residual_norm(s, L.o, s->attn_out, o_dim, s->prep_attn, R, L.post_norm);
         }
         if (c.expert_count > 0) {
@@ -951,6 +1026,12 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         s->launches++;
     }
     mark(s, YUUKA_OP_COMMIT);
+    if (sub > 0) {
+        // every layer committed its own sub-chunks; a chain's K/V rows already sit at their final positions
+        launch_advance_positions(st, s->d_pos0 + seq0, s->acc, batch);
+        s->launches++;
+        return;
+    }
     if (!s->gdn_layers.empty()) {
         launch_gdn_commit(st, s->d_gdn_commit, (int)s->gdn_layers.size(), c.group_count, rank, S, c.conv_kernel, conv_dim,
                           seq0, rows, s->acc);
@@ -989,7 +1070,11 @@ void sync_and_check(yuuka_session * s) {
 }
 
 // Uploads row metadata of a step: tokens, parents, depths, ancestor masks.
-void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t * tokens, const int32_t * parent) {
+// sub > 0 (one sequence, a chain): the rows are a wide prompt pass whose mixers run in sub-chunks of `sub`
+// rows; parents, depths and ancestor masks then restart at every sub-chunk, and the sub-chunks' first
+// positions and forced acceptances go along.
+void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t * tokens, const int32_t * parent,
+                int sub = 0) {
     const int vocab = s->model->cfg.vocab;
     const int R = batch * nodes, cap = s->rows_cap;
     YK_REQUIRE(R <= cap, YUUKA_ERR_INTERNAL, "stage_rows: %d rows exceed the session's %d", R, cap);
@@ -1003,10 +1088,17 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
             const int r = b * nodes + i;
             YK_REQUIRE(tokens[r] >= 0 && tokens[r] < vocab, YUUKA_ERR_INVALID_ARGUMENT, "token id %d is out of range",
                        tokens[r]);
+            tok[r] = tokens[r];
+            if (sub > 0) {
+                const int j = i % sub;
+                par[r] = j - 1;
+                dep[r] = j;
+                anc[r] = j == 63 ? ~0ull : ((1ull << (j + 1)) - 1);
+                continue;
+            }
             int p = parent ? parent[r] : i - 1;
             YK_REQUIRE((i == 0 && p == -1) || (i > 0 && p >= 0 && p < i), YUUKA_ERR_INVALID_ARGUMENT,
                        "parent[%d][%d] = %d is not a preceding row", b, i, p);
-            tok[r] = tokens[r];
             par[r] = p;
             dep[r] = i == 0 ? 0 : dep[b * nodes + p] + 1;
             anc[r] = (i == 0 ? 0ull : anc[b * nodes + p]) | (1ull << i);
@@ -1015,8 +1107,16 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
                    "token sequence of %d exceeds remaining context %d", nodes,
                    s->cfg.capacity - s->h_pos_upper[seq0 + b]);
     }
+    int32_t * pos_sub = reinterpret_cast<int32_t *>(s->h_rows + (size_t)cap * 20);
+    int32_t * acc_sub = pos_sub + CHAIN_MAX_SUBS;
+    for (int k = 0; k < CHAIN_MAX_SUBS; k++) {
+        const int left = sub > 0 ? nodes - k * sub : 0;
+        pos_sub[k] = sub > 0 ? s->h_pos[seq0] + k * sub : 0;
+        acc_sub[k] = (left > sub ? sub : (left > 0 ? left : 1)) - 1;
+    }
     // one copy for the whole block (the arrays keep their capacity-sized offsets on both sides)
-    YK_CUDA(cudaMemcpyAsync(s->d_rows, s->h_rows, (size_t)cap * 20, cudaMemcpyHostToDevice, s->stream.s));
+    YK_CUDA(cudaMemcpyAsync(s->d_rows, s->h_rows, (size_t)cap * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t), cudaMemcpyHostToDevice,
+                            s->stream.s));
 }
 
 // Key-range bound used to size the attention grid. It is the session capacity,
@@ -1041,10 +1141,11 @@ void run_chain(yuuka_session * s, int seq, const int32_t * tokens, int n, float 
     for (int done = 0; done < n;) {
         const int chunk = n - done < s->chain_rows ? n - done : s->chain_rows;
         const bool last = done + chunk == n;
-        stage_rows(s, seq, 1, chunk, tokens + done, nullptr);
+        const int sub = chunk > CHAIN_SUB ? CHAIN_SUB : 0;
+        stage_rows(s, seq, 1, chunk, tokens + done, nullptr, sub);
         LogitRows lr = all_logits ? LOGITS_ALL : (last && last_logits ? LOGITS_LAST : LOGITS_NONE);
         s->launches = 0;
-        run_step(s, seq, 1, chunk, 3u /* forced commit */, lr, s->cfg.capacity);
+        run_step(s, seq, 1, chunk, 3u /* forced commit */, lr, s->cfg.capacity, sub);
         sync_and_check(s);
         if (all_logits)
             YK_CUDA(cudaMemcpy(all_logits + (int64_t)done * V, s->logits, sizeof(float) * (size_t)chunk * V,
@@ -1181,17 +1282,20 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->h_pos.assign(B, 0);
             s->h_pos_upper.assign(B, 0);
             s->rows_cap = R;
-            s->d_rows = dalloc<uint8_t>((size_t)R * 20, s->owned);
+            s->d_rows = dalloc<uint8_t>((size_t)R * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t), s->owned);
+            s->d_pos_sub = reinterpret_cast<int32_t *>(s->d_rows + (size_t)R * 20);
+            s->d_acc_sub = s->d_pos_sub + CHAIN_MAX_SUBS;
             s->d_anc = reinterpret_cast<uint64_t *>(s->d_rows);
             s->d_tokens = reinterpret_cast<int32_t *>(s->d_rows + (size_t)R * 8);
             s->d_parent = s->d_tokens + R;
             s->d_depth = s->d_parent + R;
             {
                 void * hp = nullptr;
-                YK_REQUIRE(cudaMallocHost(&hp, (size_t)R * 20 + sizeof(int32_t) * ((size_t)B + 2 * R + 2)) == cudaSuccess,
+                const size_t rows_bytes = (size_t)R * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t);
+                YK_REQUIRE(cudaMallocHost(&hp, rows_bytes + sizeof(int32_t) * ((size_t)B + 2 * R + 2)) == cudaSuccess,
                            YUUKA_ERR_ALLOCATION, "page-locked staging allocation failed");
                 s->h_rows = (uint8_t *)hp;
-                s->h_results = reinterpret_cast<int32_t *>(s->h_rows + (size_t)R * 20);
+                s->h_results = reinterpret_cast<int32_t *>(s->h_rows + rows_bytes);
             }
             const int H = c.hidden;
             s->x = dalloc<float>((size_t)R * H, s->owned);

@@ -280,6 +280,7 @@ struct CommitParams {
     const GdnLayerCommit * layers;
     int groups, rank, S, kernel, conv_dim;
     int seq_base;  // first sequence of the step within the session's state arrays
+    int row_base;  // first row of the step within the layer's per-row logs (sub-chunks of a wide prompt pass)
     RowMeta rows;
     AcceptOut acc;
 };
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
             const int nt = min(CH, a + 1 - t0);
             __syncthreads();
             if (threadIdx.x < nt) {
-                const int r = seq * N + node_at(t0 + threadIdx.x);
+                const int r = p.row_base + seq * N + node_at(t0 + threadIdx.x);
                 row_s[threadIdx.x] = r;
                 dec_s[threadIdx.x] = L.decay[(int64_t)r * p.rank + h];
             }
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
                 int src = n_new + t - K1 + 0;  // index into the accepted rows; negative = old history
                 // combined sequence index: old history occupies [-K1, -1], accepted rows [0, n_new-1];
                 // new history entry t takes combined index n_new - K1 + t
-                if (src >= 0) nv[t] = L.proj[(int64_t)(seq * N + node_at(src)) * L.ldp + c];
+                if (src >= 0) nv[t] = L.proj[(int64_t)(p.row_base + seq * N + node_at(src)) * L.ldp + c];
                 else nv[t] = hist[K1 + src];
             }
             for (int t = 0; t < K1; t++) hist[t] = nv[t];
@@ -359,9 +360,9 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
 }
 
 void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_layers, int groups, int rank, int S,
-                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc) {
+                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base) {
     if (n_layers == 0) return;
-    CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, rows, acc};
+    CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, row_base, rows, acc};
     dim3 grid(rank + 1, rows.batch, n_layers);
     launch_k(gdn_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());

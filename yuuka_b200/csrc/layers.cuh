@@ -123,7 +123,7 @@ struct GdnLayerCommit {
     float * state;
 };
 void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_layers, int groups, int rank, int S,
-                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc);
+                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base = 0);
 struct KvLayerCommit {
     uint8_t * k;
     uint8_t * v;
