@@ -182,8 +182,15 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
                 for (int i = 0; i < RPL; i++) st[i] = state_update(st[i], dc, kn[c * S + rq * RPL + i], dv);
             }
         }
-        const float * kx = kn + node * S + rq * RPL;
-        const float * qx = qn + node * S + rq * RPL;
+        // this lane's S/4 key and query values, fetched as float4 (a quarter of the shared-memory loads)
+        float kx[RPL], qx[RPL];
+#pragma unroll
+        for (int i = 0; i < RPL; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4 *>(kn + node * S + rq * RPL + i);
+            const float4 q4 = *reinterpret_cast<const float4 *>(qn + node * S + rq * RPL + i);
+            kx[i] = k4.x; kx[i + 1] = k4.y; kx[i + 2] = k4.z; kx[i + 3] = k4.w;
+            qx[i] = q4.x; qx[i + 1] = q4.y; qx[i + 2] = q4.z; qx[i + 3] = q4.w;
+        }
         const float dc = dec[node];
         // sk = (decay * S)^T k over this lane's rows, then over the four row quarters
         float sk4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -285,27 +292,36 @@ struct CommitParams {
     AcceptOut acc;
 };
 
-// grid (rank + 1, batch, layers): blocks 0..rank-1 update one head's state,
-// block `rank` rewrites the conv history.
-__global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
+// grid (4 * rank + 1, batch, layers): blocks 0..4*rank-1 update a quarter of one head's state (S/4 rows),
+// the last block rewrites the conv history.
+constexpr int COMMIT_PARTS = 4;
+__global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p) {
     pdl_entry();
     const GdnLayerCommit L = p.layers[blockIdx.z];
     const int seq = blockIdx.y, N = p.rows.nodes, S = p.S;
     const int a = p.acc.accepted[seq];
     const int32_t * path = p.acc.path + (int64_t)seq * N;
     auto node_at = [&](int t) { return t == 0 ? 0 : path[t - 1]; };  // t = 0..a
-    if ((int)blockIdx.x < p.rank) {
-        // One head's S x S state, read and written once as float4 (HBM-bound: 2 x 64 KiB per CTA at S = 128).
-        // A thread owns four columns j and walks the rows i; the accepted rows' d values for its columns
-        // stay in registers, their keys and decays in shared memory, nine accepted rows at a time.
-        constexpr int CH = 9;
-        const int h = blockIdx.x, kh = h % p.groups;
+    if ((int)blockIdx.x < COMMIT_PARTS * p.rank) {
+        // S/4 rows of one head's S x S state, read and written once as float4 however many rows were accepted.
+        // A thread owns four columns j and up to four rows i and keeps them in registers; the accepted rows'
+        // keys and decays pass through shared memory nine at a time, their d values through registers.
+        constexpr int CH = 9, MAXR = 4;
+        const int h = blockIdx.x / COMMIT_PARTS, part = blockIdx.x % COMMIT_PARTS, kh = h % p.groups;
+        const int rows_part = S / COMMIT_PARTS, i_base = part * rows_part;
         float * st = L.state + (int64_t)((p.seq_base + seq) * p.rank + h) * S * S;
-        __shared__ float kh_s[CH][128];
+        __shared__ float kh_s[CH][32];
         __shared__ float dec_s[CH];
         __shared__ int row_s[CH];
         const int quads = S >> 2;
         const int j4 = threadIdx.x % quads, i0 = threadIdx.x / quads, istep = blockDim.x / quads;
+        float4 v[MAXR];
+#pragma unroll
+        for (int q = 0; q < MAXR; q++) {
+            const int i = i0 + q * istep;
+            v[q] = i < rows_part ? *reinterpret_cast<const float4 *>(st + (int64_t)(i_base + i) * S + j4 * 4)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         for (int t0 = 0; t0 <= a; t0 += CH) {
             const int nt = min(CH, a + 1 - t0);
             __syncthreads();
@@ -315,9 +331,9 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
                 dec_s[threadIdx.x] = L.decay[(int64_t)r * p.rank + h];
             }
             __syncthreads();
-            for (int idx = threadIdx.x; idx < nt * S; idx += blockDim.x) {
-                const int t = idx / S, i = idx - t * S;
-                kh_s[t][i] = L.khat[(int64_t)row_s[t] * (p.groups * S) + kh * S + i];
+            for (int idx = threadIdx.x; idx < nt * rows_part; idx += blockDim.x) {
+                const int t = idx / rows_part, i = idx - t * rows_part;
+                kh_s[t][i] = L.khat[(int64_t)row_s[t] * (p.groups * S) + kh * S + i_base + i];
             }
             float4 d[CH];
 #pragma unroll
@@ -325,21 +341,26 @@ __global__ void __launch_bounds__(256) gdn_commit_kernel(const CommitParams p) {
                 d[t] = t < nt ? *reinterpret_cast<const float4 *>(L.dlog + (int64_t)row_s[t] * (p.rank * S) + h * S + j4 * 4)
                               : make_float4(0.f, 0.f, 0.f, 0.f);
             __syncthreads();
-            for (int i = i0; i < S; i += istep) {
-                float4 * cell = reinterpret_cast<float4 *>(st + (int64_t)i * S + j4 * 4);
-                float4 v = *cell;
 #pragma unroll
-                for (int t = 0; t < CH; t++) {
-                    if (t < nt) {
-                        const float dc = dec_s[t], k = kh_s[t][i];
-                        v.x = state_update(v.x, dc, k, d[t].x);
-                        v.y = state_update(v.y, dc, k, d[t].y);
-                        v.z = state_update(v.z, dc, k, d[t].z);
-                        v.w = state_update(v.w, dc, k, d[t].w);
+            for (int t = 0; t < CH; t++) {
+                if (t < nt) {
+                    const float dc = dec_s[t];
+#pragma unroll
+                    for (int q = 0; q < MAXR; q++) {
+                        const int i = i0 + q * istep;
+                        const float k = kh_s[t][i < rows_part ? i : 0];
+                        v[q].x = state_update(v[q].x, dc, k, d[t].x);
+                        v[q].y = state_update(v[q].y, dc, k, d[t].y);
+                        v[q].z = state_update(v[q].z, dc, k, d[t].z);
+                        v[q].w = state_update(v[q].w, dc, k, d[t].w);
                     }
                 }
-                *cell = v;
             }
+        }
+#pragma unroll
+        for (int q = 0; q < MAXR; q++) {
+            const int i = i0 + q * istep;
+            if (i < rows_part) *reinterpret_cast<float4 *>(st + (int64_t)(i_base + i) * S + j4 * 4) = v[q];
         }
     } else {
         // history after the step = last kernel-1 raw inputs of [old history, accepted rows]
@@ -363,7 +384,7 @@ void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_
                        int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base) {
     if (n_layers == 0) return;
     CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, row_base, rows, acc};
-    dim3 grid(rank + 1, rows.batch, n_layers);
+    dim3 grid(COMMIT_PARTS * rank + 1, rows.batch, n_layers);
     launch_k(gdn_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
