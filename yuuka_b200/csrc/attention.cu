@@ -431,14 +431,20 @@ __global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) attention_merge_ker
                                                                  const float * __restrict__ q, int ldq, int heads, int splits,
                                                                  XPrepOut prep) {
     pdl_entry();
-    __shared__ float w_s[MERGE_MAX_SPLITS];
+    __shared__ float w_s[MERGE_MAX_SPLITS], l_s[MERGE_MAX_SPLITS];
     __shared__ float inv_l;
     const int r = blockIdx.x / heads, head = blockIdx.x - r * heads;
     const int tid = threadIdx.x;
     const float * base = partial + ((int64_t)r * heads + head) * splits * (HD + 2);
     constexpr int THREADS = HD / 4 < 32 ? 32 : HD / 4;  // whole warps; threads beyond HD / 4 only help with the statistics
     const bool has_dims = tid < HD / 4;
-    for (int s = tid; s < splits; s += THREADS) w_s[s] = base[s * (HD + 2) + HD];  // the split's running maximum
+    // the split's running maximum and sum, all splits in flight at once (one lane summing them straight from
+    // global memory was a chain of dependent L2 round trips: 12 us of this kernel at 23 splits)
+    for (int s = tid; s < splits; s += THREADS) {
+        const float2 ml = *reinterpret_cast<const float2 *>(base + (size_t)s * (HD + 2) + HD);
+        w_s[s] = ml.x;
+        l_s[s] = ml.y;
+    }
     __syncthreads();
     if (tid < 32) {
         float M = -INFINITY;
@@ -454,7 +460,7 @@ __global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) attention_merge_ker
         if (tid == 0) {
             float L = 0.0f;
             for (int s = 0; s < splits; s++)
-                if (w_s[s] != 0.0f) L += base[s * (HD + 2) + HD + 1] * w_s[s];
+                if (w_s[s] != 0.0f) L += l_s[s] * w_s[s];
             inv_l = L > 0.0f ? 1.0f / L : 0.0f;
         }
     }
