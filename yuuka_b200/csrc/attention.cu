@@ -229,6 +229,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const Attn
     __half * ks = qlo + AM_ROWS * STR;
     __half * kl = ks + AM_KT * STR;  // low parts of K (KSPLIT only)
     __half * vs = KSPLIT ? kl + AM_KT * STR : kl;
+    float * sx = reinterpret_cast<float *>(vs + AM_KT * STR);  // [AM_WARPS][16][32] partial scores, see below
 
     const int seq = blockIdx.z;
     const int kvh = blockIdx.y % p.kv_heads, qt = blockIdx.y / p.kv_heads;
@@ -320,8 +321,13 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const Attn
             for (int c = 0; c < 4; c++) s[nt][c] = 0.0f;
         const __half * qh_row = qhi + (rb * 16 + g) * STR + 2 * t;
         const __half * ql_row = qlo + (rb * 16 + g) * STR + 2 * t;
-#pragma unroll 4
-        for (int kk = 0; kk < HD / 16; kk++) {
+        // the four warps of a row block share the head dimensions of the score product: each multiplies its
+        // quarter, the partial tiles meet in shared memory and every warp adds them in the same order (each
+        // warp redoing the whole product kept the tensor pipe busy four times as long)
+        constexpr int KQ = HD / 16 / 4;
+#pragma unroll
+        for (int kq = 0; kq < KQ; kq++) {
+            const int kk = dq * KQ + kq;
             uint32_t ah[4], al[4];
             ah[0] = *reinterpret_cast<const uint32_t *>(qh_row + 16 * kk);
             ah[1] = *reinterpret_cast<const uint32_t *>(qh_row + 8 * STR + 16 * kk);
@@ -342,6 +348,22 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const Attn
                     mma16816h(s[nt], ah, *reinterpret_cast<const uint32_t *>(lr), *reinterpret_cast<const uint32_t *>(lr + 8));
                 }
             }
+        }
+        {
+            float * mine = sx + warp * 512;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) mine[(nt * 4 + c) * 32 + lane] = s[nt][c];
+            asm volatile("bar.sync %0, 128;" ::"r"(rb + 1) : "memory");
+            const float * blk = sx + rb * 4 * 512;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int at = (nt * 4 + c) * 32 + lane;
+                    s[nt][c] = ((blk[at] + blk[512 + at]) + blk[1024 + at]) + blk[1536 + at];
+                }
         }
         // mask, online softmax; s[nt][0,1] -> row g, keys 8 nt + 2 t + {0,1}; s[nt][2,3] -> row g + 8
         uint32_t pa[2][4];  // probabilities as A fragments of the two 16-key steps
@@ -527,7 +549,8 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
         // tensor-core partials; keys are taken as they are from an F16 pool and split into hi + lo otherwise
         const bool ksplit = pool.format != YUUKA_KV_F16;
         const int qtiles = (G * rows.nodes + AM_ROWS - 1) / AM_ROWS;
-        const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * AM_ROWS + (ksplit ? 3 : 2) * AM_KT);
+        const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * AM_ROWS + (ksplit ? 3 : 2) * AM_KT) +
+                            sizeof(float) * AM_WARPS * 512;
         auto kern = ksplit ? attention_mma_kernel<HD, true> : attention_mma_kernel<HD, false>;
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
