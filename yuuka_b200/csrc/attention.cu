@@ -192,11 +192,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
 // ---------------------------------------------------------------------------
 // Tensor-core form of the partial kernel (mma.sync m16n8k16, fp16 operands, fp32 accumulate).
 // A CTA of twelve warps covers up to 48 query rows (three blocks of 16) of one KV head and one key
-// range; warp (rb, dq) owns row block rb and a quarter dq of the head dimension. Every warp of a
-// row block computes the same 16 x 32 score tile (queries as an fp16 hi + lo pair, so scores keep
-// fp32-level accuracy; keys are exact when the pool stores F16 rows, otherwise they are split the
-// same way), hence the same softmax statistics with no exchange between warps, and multiplies the
-// probabilities (fp16) with its own 16 x 32 x HD/4 slice of V, fetched with ldmatrix.trans.
+// range; warp (rb, dq) owns row block rb and a quarter dq of the head dimension. The warps of a row
+// block build the 16 x 32 score tile together, each over its quarter of the head dimension (queries
+// as an fp16 hi + lo pair, so scores keep fp32-level accuracy; keys are exact when the pool stores
+// F16 rows, otherwise they are split the same way), add the four partial tiles in one order, hence
+// hold the same softmax statistics, and each multiplies the probabilities (fp16) with its own
+// 16 x 32 x HD/4 slice of V, fetched with ldmatrix.trans.
 constexpr int AM_KT = 32;
 constexpr int AM_ROWS = 48;
 constexpr int AM_WARPS = 12;
