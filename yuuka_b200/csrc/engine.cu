@@ -555,8 +555,6 @@ struct yuuka_session {
     XPrepOut prep_xn, prep_attn, prep_gdn, prep_act;  // fp16 + group sums of the GEMM inputs
     float *gdn_qn = nullptr, *gdn_vconv = nullptr, *gdn_beta = nullptr;
     int * gdn_counters = nullptr;
-    int * post_counter = nullptr;
-    bool fuse_post_norm = false;
     // RMSNorm folded into the GEMMs around it (NormFuse): one row of fixed-point sums of squares per norm
     // point of a step, zeroed when the step starts; norm_point indexes the row behind the current prep_xn
     bool fold_norm = false;          // the model allows it (every consumer and producer matrix is tile-ordered)
@@ -612,8 +610,7 @@ void mark(yuuka_session * s, uint32_t code) {
 }
 
 void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOut prep, float * out, int ldo, int rows,
-          uint32_t flags, const GemmPostNorm * post = nullptr, const float * produce_norm_w = nullptr,
-          const XPrepOut * swiglu = nullptr) {
+          uint32_t flags, const float * produce_norm_w = nullptr, const XPrepOut * swiglu = nullptr) {
     mark(s, w.rows > 65536 ? YUUKA_OP_LM_HEAD : YUUKA_OP_GEMM);
     if (w.tiled) {
         TiledGemmArgs t;
@@ -631,7 +628,6 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.path = YUUKA_GEMM_PATH_AUTO;
         t.flags = flags;
         t.scratch = &s->gemm;
-        if (post) t.post = *post;
         if (swiglu) t.swiglu = *swiglu;
         if (s->fold_step) {
             const yuuka_model_config & mc = s->model->cfg;
@@ -683,29 +679,15 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
     s->launches += launch_gemm_quant(s->model->dev, s->stream.s, a);
 }
 
-// x += W * in, then xn = rmsnorm(x) * norm_w (skipped when norm_w is null). On the mma route the
-// norm runs inside the GEMM launch; otherwise as its own kernel.
+// x += W * in, then xn = rmsnorm(x) * norm_w (skipped when norm_w is null). With 3..32 rows the norm is
+// folded into this GEMM's epilogue and the next GEMM's; otherwise it runs as its own kernel.
 void gemm_residual_norm(yuuka_session * s, const Tensor & w, const float * in, int ld_in, XPrepOut prep_in, int rows,
                         const float * norm_w) {
     const yuuka_model_config & c = s->model->cfg;
     const int H = c.hidden;
-    // Measured on the 4B shape: the in-launch norm (last CTA, 9 rows) costs more than the 9-CTA kernel
-    // it replaces, because every other SM idles behind it. Kept behind a switch.
-    const bool fuse = s->fuse_post_norm && norm_w && w.tiled && rows > 2 && H % 16 == 0;
-    if (fuse) {
-        GemmPostNorm post;
-        post.norm_w = norm_w;
-        post.eps = c.rms_eps;
-        post.dst = s->xn;
-        post.ld = H;
-        post.prep = s->prep_xn;
-        post.counter = s->post_counter;
-        gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, &post);
-        return;
-    }
     if (s->fold_step && norm_w) {
         // the norm rides on this GEMM (producer) and on the next one to read prep_xn (consumer)
-        gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, nullptr, norm_w);
+        gemm(s, w, in, ld_in, prep_in, s->x, H, rows, YUUKA_GEMM_ACCUMULATE, norm_w);
         s->norm_point++;
         s->xn_raw = true;
         return;
@@ -987,7 +969,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         // forwardFFN (model/qwen35/forward.go:295-315); its input norm came with the mixer's output GEMM
         if (L.gate_up.present() && L.gate_up.paired && L.gate_up.tiled && L.ffn_down.tiled && s->fold_swiglu && R >= 3 && R <= 32) {
             // silu(gate) * up leaves the GEMM's epilogue in the form the down projection reads
-            gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0, nullptr, nullptr, &s->prep_act);
+            gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0, nullptr, &s->prep_act);
         } else {
             const bool paired = L.gate_up.present() && L.gate_up.paired;
             if (L.gate_up.present()) {
@@ -1209,7 +1191,6 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->model = model;
             s->cfg = sc;
             if (const char * e = getenv("YUUKA_CUDA_NO_GRAPH")) s->use_graphs = !(e[0] == '1');
-            if (const char * e = getenv("YUUKA_CUDA_FUSE_NORM")) s->fuse_post_norm = e[0] == '1';
             {
                 // norm folding needs every matrix on either side of a norm in the tile-ordered form
                 bool ok = c.expert_count == 0 && c.hidden % 16 == 0 && model->output.tiled;
@@ -1307,7 +1288,6 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->gdn_vconv = dalloc<float>((size_t)R * c.inner_size, s->owned);
             s->gdn_beta = dalloc<float>((size_t)R * rank, s->owned);
             s->gdn_counters = dalloc<int>((size_t)B * rank, s->owned);
-            s->post_counter = dalloc<int>(4, s->owned);
             s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
             if (c.rope_dim > 0) s->rope_cs = dalloc<float2>((size_t)R * (c.rope_dim / 2), s->owned);
             s->act = dalloc<float>((size_t)R * c.ffn, s->owned);

@@ -606,13 +606,6 @@ struct TParams {
     int n_groups;
     float * partial;
     int * counters;
-    // optional: RMSNorm of the finished output rows by the last CTA to arrive
-    const float * post_norm_w;
-    float post_eps;
-    float * post_dst;
-    int64_t post_ld;
-    XPrepOut post_prep;
-    int * post_counter;
     // optional (GROUPED kernels): per-blockIdx.z row segments, byte stride between expert matrices,
     // and the source row of every activation row
     const GemmSegment * segments;
@@ -690,41 +683,6 @@ __device__ __forceinline__ void cta_stamp(int id, int slot) {
 #define YK_STAMP_MIN(slot) do { } while (0)
 #define YK_STAMP_MAX(slot) do { } while (0)
 #endif
-
-// rmsNorm (model/qwen35/forward.go:460-470) of rows of `src` (written by other CTAs: read through L2),
-// one warp per row, emitting f32 and the prepared form.
-__device__ void post_rmsnorm_rows(const TParams & p, int warp, int lane) {
-    const int cols = p.N;
-    for (int m = warp; m < p.M; m += TW) {
-        const float * x = p.out + (int64_t)m * p.ldo;
-        double sum = 0;
-        for (int i = lane; i < cols; i += 32) {
-            const float v = __ldcg(x + i);
-            sum += (double)v * (double)v;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float mean = (float)(sum / (double)cols);
-        const float scale = (float)(1.0 / sqrt((double)(mean + p.post_eps)));
-        for (int gq = lane; gq < (cols >> 4); gq += 32) {
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float4 xv = __ldcg(reinterpret_cast<const float4 *>(x + gq * 16) + i);
-                const float4 wv = reinterpret_cast<const float4 *>(p.post_norm_w + gq * 16)[i];
-                v[4 * i] = xv.x * scale * wv.x;
-                v[4 * i + 1] = xv.y * scale * wv.y;
-                v[4 * i + 2] = xv.z * scale * wv.z;
-                v[4 * i + 3] = xv.w * scale * wv.w;
-            }
-            float4 * d = reinterpret_cast<float4 *>(p.post_dst + (int64_t)m * p.post_ld + gq * 16);
-#pragma unroll
-            for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            if (p.post_prep.xh)
-                xprep_store16(p.post_prep.xh + (int64_t)m * cols + gq * 16, p.post_prep.xs16 + (int64_t)m * (cols >> 4) + gq, v);
-        }
-    }
-}
 
 // GROUPED: blockIdx.z walks a device-built list of row segments, each bound to one expert's matrix
 // (qwen35moe expert FFNs). A segment's rows are contiguous in the prepared-activation and output
@@ -1124,19 +1082,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         const uint32_t step = gridDim.x * gridDim.y * (TW * 32);
         for (uint32_t line = first; line < p.next_lines; line += step) prefetch_l2(p.next_w + (size_t)line * 128);
     }
-
-    if (p.post_norm_w) {
-        // every CTA has written (and, with a K split across CTAs, finalised) its rows before it arrives here
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) last_flag = atomicAdd(p.post_counter, 1) == (int)(gridDim.x * gridDim.y) - 1;
-        __syncthreads();
-        if (last_flag) {
-            __threadfence();
-            post_rmsnorm_rows(p, warp, lane);  // (never with GROUPED: p.M and p.out are the launch-wide ones)
-            if (threadIdx.x == 0) *p.post_counter = 0;
-        }
-    }
 }
 
 // ===========================================================================
@@ -1520,18 +1465,6 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
         p.next_w = a.next_w;
         p.next_lines = (uint32_t)(a.next_bytes / 128);
     }
-    if (a.post.norm_w) {
-        p.post_norm_w = a.post.norm_w;
-        p.post_eps = a.post.eps;
-        p.post_dst = a.post.dst + (int64_t)m0 * a.post.ld;
-        p.post_ld = a.post.ld;
-        p.post_prep = a.post.prep;
-        if (p.post_prep.xh) {
-            p.post_prep.xh += (int64_t)m0 * a.n_out;
-            p.post_prep.xs16 += (int64_t)m0 * (a.n_out / 16);
-        }
-        p.post_counter = a.post.counter;
-    }
 #if YK_GEMM_TIMING
     p.dbg_id = g_dbg_next++;
 #endif
@@ -1717,7 +1650,7 @@ static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGe
         xs16 = a.scratch->xs16;
         launches++;
     }
-    if (a.rows >= UMMA_MIN_ROWS && umma_enabled() && !a.post.norm_w) return launches + launch_umma_dt<DT>(dev, s, a, xh);
+    if (a.rows >= UMMA_MIN_ROWS && umma_enabled()) return launches + launch_umma_dt<DT>(dev, s, a, xh);
     for (int m0 = 0; m0 < a.rows; m0 += 32) {
         const int m = a.rows - m0 < 32 ? a.rows - m0 : 32;
         TPlan pl;
@@ -1775,11 +1708,9 @@ static int launch_tiled_dt(const yuuka_device * dev, cudaStream_t s, const Tiled
 
 int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const TiledGemmArgs & a) {
     YK_REQUIRE(a.w && (a.x || a.xprep.xh) && a.out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: null operand");
-    YK_REQUIRE(!a.post.norm_w || (a.post.dst && a.post.counter && a.n_out % 16 == 0 && a.ldo % 4 == 0 && a.post.ld % 4 == 0),
-               YUUKA_ERR_INVALID_ARGUMENT, "gemm: the fused RMSNorm needs a destination, a counter and a width that is a multiple of 16");
     YK_REQUIRE(a.rows > 0 && a.n_out > 0 && a.n_in > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: invalid shape");
     if (a.swiglu.xh) {
-        YK_REQUIRE(a.swiglu.xs16 && a.n_out % 32 == 0 && !(a.flags & YUUKA_GEMM_ACCUMULATE) && !a.post.norm_w && !a.norm.produce_w,
+        YK_REQUIRE(a.swiglu.xs16 && a.n_out % 32 == 0 && !(a.flags & YUUKA_GEMM_ACCUMULATE) && !a.norm.produce_w,
                    YUUKA_ERR_INVALID_ARGUMENT, "gemm: the SwiGLU epilogue needs gate and up tiles in pairs and a plain output");
         YK_REQUIRE(!a.norm.consume_now || a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
     }

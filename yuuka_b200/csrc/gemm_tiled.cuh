@@ -33,17 +33,6 @@ inline uint64_t tiled_bytes(uint32_t dtype, uint64_t n_out, uint64_t n_in) {
 // dst (tiled_bytes long) <- GGUF rows at src. Rows beyond n_out are zero.
 void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uint32_t dtype, int n_out, int n_in);
 
-// RMSNorm of the GEMM's finished output rows, done inside the same launch by the
-// last CTA to finish (mma route only): dst = rmsnorm(out) * norm_w.
-struct GemmPostNorm {
-    const float * norm_w = nullptr;
-    float eps = 0.0f;
-    float * dst = nullptr;
-    int64_t ld = 0;
-    XPrepOut prep;
-    int * counter = nullptr;  // one int, zero between launches
-};
-
 // One run of at most 8 consecutive rows bound to one expert matrix (grouped GEMM). count <= 0 marks
 // an unused slot: the list has a fixed length so that the launch shape does not depend on the routing.
 struct GemmSegment {
@@ -101,7 +90,6 @@ struct TiledGemmArgs {
     uint32_t path = YUUKA_GEMM_PATH_AUTO;
     uint32_t flags = 0;
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
-    GemmPostNorm post;
     NormFuse norm;
     // Set: `w` holds ffn_gate and ffn_up interleaved by 16-row tile and the launch writes silu(gate) * up in
     // prepared form, [rows][n_out / 2], instead of `out` (register-fed mma route, 3..32 rows).
