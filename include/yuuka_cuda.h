@@ -347,8 +347,7 @@ typedef enum yuuka_op_code {
     YUUKA_OP_ATTENTION = 29,
     YUUKA_OP_LM_HEAD = 37,
     YUUKA_OP_SILU_MUL = 9,
-    YUUKA_OP_GDN_SCAN = 100,
-    YUUKA_OP_GDN_NORM_GATE = 101,
+    YUUKA_OP_GDN_SCAN = 100,    /* conv + norms, recurrence, gated norm (101 was the gated norm on its own) */
     YUUKA_OP_ACCEPT = 102,
     YUUKA_OP_COMMIT = 103,
     YUUKA_OP_MOE_ROUTE = 104,   /* router logits, top-k, grouping of (row, slot) pairs by expert */

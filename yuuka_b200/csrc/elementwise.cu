@@ -252,51 +252,4 @@ void launch_attn_prep(cudaStream_t s, float * q, int ldq, float * k, int ldk, co
     YK_CUDA(cudaGetLastError());
 }
 
-// ---------------------------------------------------------------------------
-// gated RMSNorm of the delta-net output (model/qwen35/recurrent.go:39-50)
-
-// one thread per 16 consecutive values; a head (S values) is S/16 adjacent lanes
-__global__ void gdn_norm_gate_kernel(float * __restrict__ out, int ldo, const float * __restrict__ z, int ldz,
-                                     const float * __restrict__ norm, int rank, int S, float eps, XPrepOut prep) {
-    pdl_entry();
-    const int r = blockIdx.y;
-    const int lanes = S >> 4;                              // 8 (S = 128) or 4 (S = 64)
-    const int gq = blockIdx.x * blockDim.x + threadIdx.x;  // 16-group index within the row
-    const bool live = gq < rank * lanes;
-    const int h = live ? gq / lanes : 0, part = gq - h * lanes;
-    float * row = out + (int64_t)r * ldo + (int64_t)h * S + part * 16;
-    const float * gate = z + (int64_t)r * ldz + (int64_t)h * S + part * 16;
-    float v[16];
-    double sum = 0;
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        v[i] = live ? row[i] : 0.0f;
-        sum += (double)v[i] * (double)v[i];
-    }
-    for (int o = 1; o < lanes; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (!live) return;
-    float mean = (float)(sum / (double)S);
-    float scale = (float)(1.0 / sqrt((double)(mean + eps)));
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        float t = v[i];
-        t *= scale * norm[part * 16 + i];
-        v[i] = t * silu_ref(gate[i]);
-    }
-    float4 * d = reinterpret_cast<float4 *>(row);
-#pragma unroll
-    for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    const int cols = rank * S;
-    if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
-}
-
-void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
-                          int S, int rows, float eps, XPrepOut prep) {
-    YK_REQUIRE(S == 64 || S == 128, YUUKA_ERR_UNSUPPORTED, "gdn_norm_gate: state size %d is not 64 or 128", S);
-    const int groups = rank * (S >> 4);
-    dim3 grid((groups + 127) / 128, rows);
-    launch_k(gdn_norm_gate_kernel, grid, 128, 0, s, out, ldo, z, ldz, norm, rank, S, eps, prep);
-    YK_CUDA(cudaGetLastError());
-}
-
 }  // namespace yk

@@ -554,7 +554,6 @@ struct yuuka_session {
     XPrepOut prep_moe_act, prep_sh_act;
     XPrepOut prep_xn, prep_attn, prep_gdn, prep_act;  // fp16 + group sums of the GEMM inputs
     float *gdn_qn = nullptr, *gdn_vconv = nullptr, *gdn_beta = nullptr;
-    int * gdn_counters = nullptr;
     // RMSNorm folded into the GEMMs around it (NormFuse): one row of fixed-point sums of squares per norm
     // point of a step, zeroed when the step starts; norm_point indexes the row behind the current prep_xn
     bool fold_norm = false;          // the model allows it (every consumer and producer matrix is tile-ordered)
@@ -794,7 +793,6 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             g.qn = s->gdn_qn;
             g.vconv = s->gdn_vconv;
             g.beta = s->gdn_beta;
-            g.counters = s->gdn_counters;
             g.khat = LS.khat;
             g.dlog = LS.dlog;
             g.decay = LS.decay;
@@ -1287,7 +1285,6 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->gdn_qn = dalloc<float>((size_t)R * c.group_count * S, s->owned);
             s->gdn_vconv = dalloc<float>((size_t)R * c.inner_size, s->owned);
             s->gdn_beta = dalloc<float>((size_t)R * rank, s->owned);
-            s->gdn_counters = dalloc<int>((size_t)B * rank, s->owned);
             s->gate_up = dalloc<float>((size_t)R * 2 * c.ffn, s->owned);
             if (c.rope_dim > 0) s->rope_cs = dalloc<float2>((size_t)R * (c.rope_dim / 2), s->owned);
             s->act = dalloc<float>((size_t)R * c.ffn, s->owned);

@@ -342,9 +342,6 @@ inline DecodeConsts decode_consts(uint32_t dtype) {
     return c;
 }
 
-#ifndef YK_GEMM_PINGPONG
-#define YK_GEMM_PINGPONG 0
-#endif
 #ifndef YK_GEMM_RUNTIME_CONSTS
 #define YK_GEMM_RUNTIME_CONSTS 1
 #endif
@@ -844,33 +841,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (grp != (int)blockIdx.x && sb0 + 1 < sb1)
             prefetch_l2_range(tile + (size_t)(sb0 + 1) * C::REC, (sb1 - sb0 - 1) * C::REC, lane);
 
-#if YK_GEMM_PINGPONG
-        // Two records per trip, the register buffers swapping roles: while one is consumed the other
-        // is in flight. At the end of the group `cur` holds the first record of the next group's tile.
-        const uint8_t * next_first = nullptr;
-        if (grp + (int)gridDim.x < p.n_groups) {
-            const int rtn = min((grp + (int)gridDim.x) * p.TG + tile_in_group, n_tiles - 1);
-            next_first = wbase + rtn * rec_row + (size_t)sb0 * C::REC;
-        }
-        for (int sb = sb0; sb < sb1; sb += 2) {
-            if (sb + 1 < sb1) C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
-            else if (next_first) C::load(next_first, lane, nxt);
-            MM::header(cur, lane, tab);
-            __syncwarp();
-            MM::run(cur, lane, tab, xrow, xsrow, sb - c0, acc, kc);
-            __syncwarp();
-            if (sb + 1 >= sb1) {
-                cur = nxt;
-                break;
-            }
-            if (sb + 2 < sb1) C::load(tile + (size_t)(sb + 2) * C::REC, lane, cur);
-            else if (next_first) C::load(next_first, lane, cur);
-            MM::header(nxt, lane, tab);
-            __syncwarp();
-            MM::run(nxt, lane, tab, xrow, xsrow, sb + 1 - c0, acc, kc);
-            __syncwarp();
-        }
-#else
         for (int sb = sb0; sb < sb1; sb++) {
             // prefetch the next record of this tile, or the first record of the next group's tile
             if (sb + 1 < sb1) {
@@ -885,7 +855,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             __syncwarp();
             cur = nxt;
         }
-#endif
 
         // ---- reduce the K parts of a row tile inside the CTA ----
         if (p.KS > 1) {

@@ -78,16 +78,11 @@ struct GdnArgs {
     float * khat;            // [rows][groups*S] log: normalised keys
     float * dlog;            // [rows][rank*S]   log: beta * (v - S^T k)
     float * decay;           // [rows][rank]     log: exp(alpha)
-    int * counters;          // [batch][rank] arrival counters, zero between launches
     int groups, rank, S, kernel;
     float eps;
 };
 // conv + norms, the recurrence and the gated RMSNorm; returns the number of kernels launched
 int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
-// out[r][h][:] = rmsnorm(out[r][h][:]) * norm * silu(z[r][h][:]) (recurrent.go:39-50)
-void launch_gdn_norm_gate(cudaStream_t s, float * out, int ldo, const float * z, int ldz, const float * norm, int rank,
-                          int S, int rows, float eps, XPrepOut prep = XPrepOut());
-
 // First-maximum argmax of every logits row (speculative.go:263-271) followed by
 // the greedy tree walk (speculative.go:193-202 generalised to a tree).
 struct AcceptOut {

@@ -21,7 +21,7 @@ GEMM_ACCUMULATE = 1
 GEMM_TILED = 2
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
 OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
-            100: "gdn_scan", 101: "gdn_norm_gate", 102: "accept", 103: "commit", 104: "moe_route", 105: "moe_experts",
+            100: "gdn_scan", 102: "accept", 103: "commit", 104: "moe_route", 105: "moe_experts",
             106: "moe_combine"}
 ABI_VERSION = 1
 
