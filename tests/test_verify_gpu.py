@@ -305,3 +305,42 @@ def test_long_prompts_run_as_wide_passes_with_mixer_sub_chunks(tiny, kv):
     err = float(np.max(np.abs(got - want)))
     assert got.shape == (150, V) and err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
     sess.close(); st.close()
+
+
+def test_mixed_tensor_types_take_the_unfused_routes():
+    """A file whose small projections stayed in F32 / F16 and whose gate and up differ in type: the fused
+    matrices (qkv|gate|beta|alpha, q|k, gate|up) cannot be built, untiled matrices take the generic kernel,
+    the norm is not folded, and the step still matches the oracle."""
+    cfg = synth.tiny_config()
+    tensors = synth.make_model(cfg, "q4_k", seed=21, unit_norms=False)
+    H, R = cfg["hidden"], cfg["time_step_rank"]
+    kv_dim = cfg["kv_heads"] * cfg["head_dim"]
+    n = 0
+    for name in list(tensors):
+        n += 1
+        if name.endswith("ssm_beta.weight") or name.endswith("ssm_alpha.weight"):
+            tensors[name] = (synth.F32, synth.normal_f32(R * H, 0.02, 900 + n), R, H)
+        elif name.endswith("attn_k.weight"):
+            k16 = synth.normal_f32(kv_dim * H, 0.02, 900 + n).astype(np.float16)
+            tensors[name] = (synth.F16, k16.view(np.uint8).copy(), kv_dim, H)
+        elif name.endswith("ffn_up.weight"):
+            tensors[name] = (synth.Q8_0, synth.normal_quant(cfg["ffn"], H, synth.Q8_0, 0.02, 900 + n), cfg["ffn"], H)
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, tensors)
+    om = yo.Model(cfg, tensors)
+    prompt = synth.uniform_i32(70, 0, cfg["vocab"], 81).tolist()     # one wide pass with two sub-chunks
+    rows = synth.uniform_i32(9, 0, cfg["vocab"], 82).tolist()
+    st = yo.State(om, 128, yo.KV_F32)
+    st.forward(prompt)
+    _, _, want = st.verify_chain(rows[0], np.array(rows[1:], np.int32), want_logits=True)
+    got = _verify_rows(gm, prompt, rows)
+    err = float(np.max(np.abs(got - want)))
+    assert err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
+    # one-row decode (fp32 routes everywhere) after the same prompt
+    sess = cuda.Session(gm, max_batch=1, max_nodes=2, capacity=128, kv_format=cuda.KV_F32)
+    sess.forward(prompt, want_logits=False)
+    st2 = yo.State(om, 128, yo.KV_F32)
+    st2.forward(prompt)
+    err = float(np.max(np.abs(sess.forward([rows[0]]) - st2.step(rows[0]))))
+    assert err <= 2e-2, err
+    sess.close(); st.close(); st2.close(); gm.close(); dev.close()
