@@ -344,3 +344,23 @@ def test_mixed_tensor_types_take_the_unfused_routes():
     err = float(np.max(np.abs(sess.forward([rows[0]]) - st2.step(rows[0]))))
     assert err <= 2e-2, err
     sess.close(); st.close(); st2.close(); gm.close(); dev.close()
+
+
+@pytest.mark.parametrize("scheme", ["q4_k", "q5_k", "q6_k"])
+def test_every_k_quant_through_the_folded_step(scheme):
+    """The 9-row step (folded norms, SwiGLU epilogue, split-free and K-split GEMMs) with all matrices in one
+    K-quant type, against the oracle."""
+    cfg = dict(synth.tiny_config(), block_count=4)
+    tensors = synth.make_model(cfg, scheme, seed=31, unit_norms=False)
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, tensors)
+    om = yo.Model(cfg, tensors)
+    prompt = synth.uniform_i32(30, 0, cfg["vocab"], 91).tolist()
+    rows = synth.uniform_i32(9, 0, cfg["vocab"], 92).tolist()
+    st = yo.State(om, 64, yo.KV_F32)
+    st.forward(prompt)
+    _, _, want = st.verify_chain(rows[0], np.array(rows[1:], np.int32), want_logits=True)
+    got = _verify_rows(gm, prompt, rows)
+    err = float(np.max(np.abs(got - want)))
+    assert err <= 2e-2 and cosine(got, want) >= 0.9999, (scheme, err, cosine(got, want))
+    st.close(); gm.close(); dev.close()
