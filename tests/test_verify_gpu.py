@@ -364,3 +364,45 @@ def test_every_k_quant_through_the_folded_step(scheme):
     err = float(np.max(np.abs(got - want)))
     assert err <= 2e-2 and cosine(got, want) >= 0.9999, (scheme, err, cosine(got, want))
     st.close(); gm.close(); dev.close()
+
+
+def test_widest_tree_and_single_row_steps(tiny):
+    """The limits of a step: 64 rows per sequence in a bushy random tree (the ancestor masks use all 64 bits,
+    branches rebuild their parents' recurrent state from the delta log), and the one-row step."""
+    cfg, gm, om = tiny
+    V = cfg["vocab"]
+    rng = np.random.default_rng(5)
+    parent = np.array([-1] + [int(rng.integers(max(0, i - 6), i)) for i in range(1, 64)], np.int32)
+    prompt = synth.uniform_i32(33, 0, V, 95).tolist()
+    tokens = synth.uniform_i32(64, 0, V, 96)
+    st = yo.State(om, 128, yo.KV_F32)
+    lo = st.forward(prompt)
+    tokens[0] = yo.argmax(lo)
+    # seed a greedy path three levels deep along existing children of the tree
+    sess = cuda.Session(gm, max_batch=1, max_nodes=64, capacity=128, kv_format=cuda.KV_F32)
+    sess.forward(prompt, want_logits=False)
+    node = 0
+    for _ in range(3):
+        kids = [i for i in range(1, 64) if parent[i] == node]
+        if not kids:
+            break
+        lg = sess.verify([tokens], parent=parent, mode=cuda.ACCEPT_NONE, want_logits=True).logits[0]
+        tokens[kids[-1]] = int(np.argmax(lg[node]))
+        node = kids[-1]
+    acc_o, path_o, em_o, log_o = st.verify_tree_greedy(tokens, parent, want_logits=True)
+    res = sess.verify([tokens], parent=parent, want_logits=True)
+    err = float(np.max(np.abs(res.logits[0] - log_o)))
+    assert err <= LOGIT_TOL and cosine(res.logits[0], log_o) >= 0.9999, err
+    gap = np.sort(log_o, -1)[:, -1] - np.sort(log_o, -1)[:, -2]
+    if gap.min() >= 1e-3:
+        a = int(res.accepted[0])
+        assert a == acc_o >= 1
+        assert res.path[0, :a].tolist() == path_o.tolist() and res.emitted[0, :a + 1].tolist() == em_o.tolist()
+        assert sess.position() == st.pos
+        assert np.max(np.abs(sess.snapshot().view(np.float32) - st.snapshot().view(np.float32))) <= 2e-3
+    with pytest.raises(cuda.YuukaError):              # a 65th row does not fit the 64-bit ancestor masks
+        cuda.Session(gm, max_batch=1, max_nodes=65, capacity=128)
+    # one row: nothing to accept, the bonus token is the argmax
+    one = sess.verify([[int(res.emitted[0, int(res.accepted[0])])]], want_logits=True)
+    assert int(one.accepted[0]) == 0 and int(one.emitted[0, 0]) == int(np.argmax(one.logits[0, 0]))
+    sess.close(); st.close()
