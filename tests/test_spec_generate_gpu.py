@@ -119,3 +119,19 @@ def test_generate_argument_errors(tiny):
             cuda.spec_generate(sess, prompt, n)
         assert e.value.status == 1
     sess.close()
+
+
+def test_generate_after_a_long_prompt(tiny):
+    """A 200-token prompt goes in as one wide pass (GEMMs over all rows, mixers in 64-row sub-chunks) before
+    the verify loop starts; the stream still equals greedy decoding."""
+    cfg, gm0, om0 = tiny
+    gm, om = damped_model(cfg, gm0.dev, 0.0)
+    prompt = synth.uniform_i32(200, 0, cfg["vocab"], 71).tolist()
+    n = 80
+    want, gaps = oracle_greedy(om, prompt, n, capacity=512)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=9, capacity=512, kv_format=cuda.KV_F16)
+    got, res = cuda.spec_generate(sess, prompt, n, max_draft=8, min_match=2)
+    same = agree(got, want, gaps)
+    assert same >= 40, f"stream forked at a near-tie after {same} tokens; pick another seed"
+    assert res.prompt_tokens == 200 and res.output_tokens == n and sess.position() >= 200 + n - 1
+    sess.close(); gm.close()
