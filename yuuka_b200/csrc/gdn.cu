@@ -149,14 +149,21 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
 
     // the front-end kernel has left normalised q and k, the conv output of v, beta and decay in global memory
-    for (int i = threadIdx.x; i < N * S; i += blockDim.x) {
-        const int node = i / S, e = i - node * S;
-        qn[i] = a.qn[(int64_t)(seq * N + node) * key_dim + kh * S + e];
-        kn[i] = a.khat[(int64_t)(seq * N + node) * key_dim + kh * S + e];
+    // (16-byte loads, eight in flight per thread: with 64 rows of a prompt sub-chunk a scalar loop spent most
+    // of the kernel waiting for one L2 round trip after another)
+    constexpr int SQ = S / 4;
+#pragma unroll 8
+    for (int i = threadIdx.x; i < N * SQ; i += blockDim.x) {
+        const int node = i / SQ, e4 = i - node * SQ;
+        const int64_t at = (int64_t)(seq * N + node) * key_dim + kh * S + e4 * 4;
+        reinterpret_cast<float4 *>(qn)[i] = *reinterpret_cast<const float4 *>(a.qn + at);
+        reinterpret_cast<float4 *>(kn)[i] = *reinterpret_cast<const float4 *>(a.khat + at);
     }
-    for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
-        const int node = i / GDN_COLS, e = i - node * GDN_COLS;
-        vv[i] = a.vconv[(int64_t)(seq * N + node) * inner + h * S + cb * GDN_COLS + e];
+#pragma unroll 4
+    for (int i = threadIdx.x; i < N * (GDN_COLS / 4); i += blockDim.x) {
+        const int node = i / (GDN_COLS / 4), e4 = i - node * (GDN_COLS / 4);
+        reinterpret_cast<float4 *>(vv)[i] =
+            *reinterpret_cast<const float4 *>(a.vconv + (int64_t)(seq * N + node) * inner + h * S + cb * GDN_COLS + e4 * 4);
     }
     for (int node = threadIdx.x; node < N; node += blockDim.x) {
         par[node] = p.rows.parent[seq * N + node];
@@ -236,12 +243,14 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         scale_s[node] = (float)(1.0 / sqrt((double)(mean + a.eps)));
     }
     cluster_sync_all();  // scales visible to the CTA; no CTA leaves while another may still read its sums
+#pragma unroll 8
     for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
         const int node = i / GDN_COLS, c = i - node * GDN_COLS;
         const int64_t r = seq * N + node;
+        const float zv = a.z[r * a.ldz + h * S + cb * GDN_COLS + c];
         float t = o_s[i];
         t *= scale_s[node] * a.norm[cb * GDN_COLS + c];
-        o_s[i] = t * silu_ref(a.z[r * a.ldz + h * S + cb * GDN_COLS + c]);
+        o_s[i] = t * silu_ref(zv);
     }
     __syncthreads();
     for (int gi = threadIdx.x; gi < N * (GDN_COLS >> 4); gi += blockDim.x) {
