@@ -301,9 +301,10 @@ struct CommitParams {
     AcceptOut acc;
 };
 
-// grid (4 * rank + 1, batch, layers): blocks 0..4*rank-1 update a quarter of one head's state (S/4 rows),
-// the last block rewrites the conv history.
+// grid (4 * rank + 8, batch, layers): blocks 0..4*rank-1 update a quarter of one head's state (S/4 rows),
+// the last eight rewrite the conv history, an eighth of the channels each.
 constexpr int COMMIT_PARTS = 4;
+constexpr int COMMIT_CONV_PARTS = 8;
 __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p) {
     pdl_entry();
     const GdnLayerCommit L = p.layers[blockIdx.z];
@@ -313,15 +314,18 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
     auto node_at = [&](int t) { return t == 0 ? 0 : path[t - 1]; };  // t = 0..a
     if ((int)blockIdx.x < COMMIT_PARTS * p.rank) {
         // S/4 rows of one head's S x S state, read and written once as float4 however many rows were accepted.
-        // A thread owns four columns j and up to four rows i and keeps them in registers; the accepted rows'
-        // keys and decays pass through shared memory nine at a time, their d values through registers.
-        constexpr int CH = 9, MAXR = 4;
+        // A thread owns four columns j and up to four rows i and keeps them in registers. The accepted rows'
+        // keys (this part's S/4 of them), d values and decays are brought into shared memory in one round of
+        // loads, all rows at once (up to 64 in a prompt sub-chunk: fetching them nine at a time between
+        // barriers made that commit a chain of L2 round trips, 57 us per layer).
+        constexpr int MAXR = 4;
         const int h = blockIdx.x / COMMIT_PARTS, part = blockIdx.x % COMMIT_PARTS, kh = h % p.groups;
         const int rows_part = S / COMMIT_PARTS, i_base = part * rows_part;
         float * st = L.state + (int64_t)((p.seq_base + seq) * p.rank + h) * S * S;
-        __shared__ float kh_s[CH][32];
-        __shared__ float dec_s[CH];
-        __shared__ int row_s[CH];
+        __shared__ float kh_s[GDN_MAX_NODES][32];
+        __shared__ __align__(16) float d_s[GDN_MAX_NODES][128];
+        __shared__ float dec_s[GDN_MAX_NODES];
+        __shared__ int row_s[GDN_MAX_NODES];
         const int quads = S >> 2;
         const int j4 = threadIdx.x % quads, i0 = threadIdx.x / quads, istep = blockDim.x / quads;
         float4 v[MAXR];
@@ -331,39 +335,34 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
             v[q] = i < rows_part ? *reinterpret_cast<const float4 *>(st + (int64_t)(i_base + i) * S + j4 * 4)
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int t0 = 0; t0 <= a; t0 += CH) {
-            const int nt = min(CH, a + 1 - t0);
-            __syncthreads();
-            if (threadIdx.x < nt) {
-                const int r = p.row_base + seq * N + node_at(t0 + threadIdx.x);
-                row_s[threadIdx.x] = r;
-                dec_s[threadIdx.x] = L.decay[(int64_t)r * p.rank + h];
-            }
-            __syncthreads();
-            for (int idx = threadIdx.x; idx < nt * rows_part; idx += blockDim.x) {
-                const int t = idx / rows_part, i = idx - t * rows_part;
-                kh_s[t][i] = L.khat[(int64_t)row_s[t] * (p.groups * S) + kh * S + i_base + i];
-            }
-            float4 d[CH];
+        const int nt = a + 1;  // <= N <= GDN_MAX_NODES
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+            const int r = p.row_base + seq * N + node_at(t);
+            row_s[t] = r;
+            dec_s[t] = L.decay[(int64_t)r * p.rank + h];
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * rows_part; idx += blockDim.x) {
+            const int t = idx / rows_part, i = idx - t * rows_part;
+            kh_s[t][i] = L.khat[(int64_t)row_s[t] * (p.groups * S) + kh * S + i_base + i];
+        }
+        for (int idx = threadIdx.x; idx < nt * quads; idx += blockDim.x) {
+            const int t = idx / quads, c4 = idx - t * quads;
+            reinterpret_cast<float4 *>(d_s[t])[c4] =
+                *reinterpret_cast<const float4 *>(L.dlog + (int64_t)row_s[t] * (p.rank * S) + h * S + c4 * 4);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; t++) {
+            const float dc = dec_s[t];
+            const float4 d = reinterpret_cast<const float4 *>(d_s[t])[j4];
 #pragma unroll
-            for (int t = 0; t < CH; t++)
-                d[t] = t < nt ? *reinterpret_cast<const float4 *>(L.dlog + (int64_t)row_s[t] * (p.rank * S) + h * S + j4 * 4)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-            __syncthreads();
-#pragma unroll
-            for (int t = 0; t < CH; t++) {
-                if (t < nt) {
-                    const float dc = dec_s[t];
-#pragma unroll
-                    for (int q = 0; q < MAXR; q++) {
-                        const int i = i0 + q * istep;
-                        const float k = kh_s[t][i < rows_part ? i : 0];
-                        v[q].x = state_update(v[q].x, dc, k, d[t].x);
-                        v[q].y = state_update(v[q].y, dc, k, d[t].y);
-                        v[q].z = state_update(v[q].z, dc, k, d[t].z);
-                        v[q].w = state_update(v[q].w, dc, k, d[t].w);
-                    }
-                }
+            for (int q = 0; q < MAXR; q++) {
+                const int i = i0 + q * istep;
+                const float k = kh_s[t][i < rows_part ? i : 0];
+                v[q].x = state_update(v[q].x, dc, k, d.x);
+                v[q].y = state_update(v[q].y, dc, k, d.y);
+                v[q].z = state_update(v[q].z, dc, k, d.z);
+                v[q].w = state_update(v[q].w, dc, k, d.w);
             }
         }
 #pragma unroll
@@ -372,19 +371,33 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
             if (i < rows_part) *reinterpret_cast<float4 *>(st + (int64_t)(i_base + i) * S + j4 * 4) = v[q];
         }
     } else {
-        // history after the step = last kernel-1 raw inputs of [old history, accepted rows]
+        // history after the step = last kernel-1 raw inputs of [old history, accepted rows]: entry t takes the
+        // combined index n_new - K1 + t, where the old history occupies [-K1, -1] and the accepted rows
+        // [0, n_new - 1]. The (at most kernel-1) source rows are looked up once per CTA; the channels are
+        // spread over COMMIT_CONV_PARTS CTAs (one CTA walking all channels with a path look-up per entry was
+        // a 45 us chain of dependent loads: most of this kernel's time).
         const int K1 = p.kernel - 1, n_new = a + 1;
-        for (int c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+        __shared__ int src_row[8];
+        if (threadIdx.x < K1) {
+            const int src = n_new + (int)threadIdx.x - K1;
+            src_row[threadIdx.x] = src >= 0 ? p.row_base + seq * N + node_at(src) : -1;
+        }
+        __syncthreads();
+        const int part = blockIdx.x - COMMIT_PARTS * p.rank;
+        const int per = (p.conv_dim + COMMIT_CONV_PARTS - 1) / COMMIT_CONV_PARTS;
+        const int c_end = min(p.conv_dim, (part + 1) * per);
+        for (int c = part * per + threadIdx.x; c < c_end; c += blockDim.x) {
             float * hist = L.conv_state + ((int64_t)(p.seq_base + seq) * p.conv_dim + c) * K1;
             float nv[8];
-            for (int t = 0; t < K1; t++) {
-                int src = n_new + t - K1 + 0;  // index into the accepted rows; negative = old history
-                // combined sequence index: old history occupies [-K1, -1], accepted rows [0, n_new-1];
-                // new history entry t takes combined index n_new - K1 + t
-                if (src >= 0) nv[t] = L.proj[(int64_t)(p.row_base + seq * N + node_at(src)) * L.ldp + c];
-                else nv[t] = hist[K1 + src];
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+                if (t >= K1) continue;
+                const int src = n_new + t - K1;
+                nv[t] = src >= 0 ? L.proj[(int64_t)src_row[t] * L.ldp + c] : hist[K1 + src];
             }
-            for (int t = 0; t < K1; t++) hist[t] = nv[t];
+#pragma unroll
+            for (int t = 0; t < 8; t++)
+                if (t < K1) hist[t] = nv[t];
         }
     }
 }
@@ -393,7 +406,7 @@ void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_
                        int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base) {
     if (n_layers == 0) return;
     CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, row_base, rows, acc};
-    dim3 grid(COMMIT_PARTS * rank + 1, rows.batch, n_layers);
+    dim3 grid(COMMIT_PARTS * rank + COMMIT_CONV_PARTS, rows.batch, n_layers);
     launch_k(gdn_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }
