@@ -59,22 +59,33 @@ struct WalkParams {
     AcceptOut out;
 };
 
-// one CTA per sequence: finish the argmax of each of its rows, then walk
-__global__ void __launch_bounds__(64) greedy_walk_kernel(const WalkParams p) {
+// one CTA per sequence: finish the argmax of each of its rows (a warp per row, lanes over the chunk maxima,
+// combined with the same tie rule), then one thread walks the tree, whose tokens and parents wait in shared memory
+constexpr int WALK_THREADS = 256;
+__global__ void __launch_bounds__(WALK_THREADS) greedy_walk_kernel(const WalkParams p) {
     pdl_entry();
-    __shared__ int want[64];
+    __shared__ int want[64], tok_s[64], par_s[64];
     const int seq = blockIdx.x, N = p.rows.nodes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int node = threadIdx.x; node < N; node += blockDim.x) {
+        tok_s[node] = p.rows.tokens[(int64_t)seq * N + node];
+        par_s[node] = p.rows.parent[(int64_t)seq * N + node];
+    }
+    for (int node = warp; node < N; node += WALK_THREADS / 32) {
         const int r = seq * N + node;
         float bv = -INFINITY;
         int bi = 0x7fffffff;
-        for (int c = 0; c < p.chunks; c++) best_of(bv, bi, p.val[(int64_t)r * p.chunks + c], p.idx[(int64_t)r * p.chunks + c]);
-        want[node] = bi == 0x7fffffff ? 0 : bi;
+        for (int c = lane; c < p.chunks; c += 32) best_of(bv, bi, p.val[(int64_t)r * p.chunks + c], p.idx[(int64_t)r * p.chunks + c]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            best_of(bv, bi, ov, oi);
+        }
+        if (lane == 0) want[node] = bi == 0x7fffffff ? 0 : bi;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int32_t * tokens = p.rows.tokens + (int64_t)seq * N;
-        const int32_t * parent = p.rows.parent + (int64_t)seq * N;
         int32_t * path = p.out.path + (int64_t)seq * N;
         int32_t * emitted = p.out.emitted + (int64_t)seq * N;
         int cur = 0, a = 0;
@@ -82,7 +93,7 @@ __global__ void __launch_bounds__(64) greedy_walk_kernel(const WalkParams p) {
             const int w = want[cur];
             int next = -1;
             for (int c = cur + 1; c < N; c++)
-                if (parent[c] == cur && tokens[c] == w) { next = c; break; }
+                if (par_s[c] == cur && tok_s[c] == w) { next = c; break; }
             emitted[a] = w;
             if (next < 0) break;
             path[a] = next;
@@ -104,7 +115,7 @@ int launch_accept_greedy(cudaStream_t s, const float * logits, int vocab, const 
     launch_k(argmax_partial_kernel, grid, 256, 0, s, logits, vocab, scratch.val, scratch.idx, scratch.chunks);
     YK_CUDA(cudaGetLastError());
     WalkParams p{scratch.val, scratch.idx, scratch.chunks, rows, out};
-    launch_k(greedy_walk_kernel, rows.batch, 64, 0, s, p);
+    launch_k(greedy_walk_kernel, rows.batch, WALK_THREADS, 0, s, p);
     YK_CUDA(cudaGetLastError());
     return 2;
 }
