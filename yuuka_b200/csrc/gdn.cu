@@ -172,6 +172,17 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     }
     __syncthreads();
 
+    // the gate values the last phase needs (up to three per thread: a 9-row step needs 2.25) are fetched
+    // now, so that the end of the kernel does not wait for them
+    constexpr int ZPRE = 3;
+    float zpre[ZPRE];
+#pragma unroll
+    for (int k = 0; k < ZPRE; k++) {
+        const int i = threadIdx.x + k * (GDN_WARPS * 32);
+        const int node = i / GDN_COLS, c = i - node * GDN_COLS;
+        zpre[k] = i < N * GDN_COLS ? a.z[(int64_t)(seq * N + node) * a.ldz + h * S + cb * GDN_COLS + c] : 0.0f;
+    }
+
     // ---- recurrence (recurrent.go:56-105) ----
     int cur = -1;  // node whose state st currently holds (-1: the stored state)
     for (int node = 0; node < N; node++) {
@@ -243,8 +254,18 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         scale_s[node] = (float)(1.0 / sqrt((double)(mean + a.eps)));
     }
     cluster_sync_all();  // scales visible to the CTA; no CTA leaves while another may still read its sums
+#pragma unroll
+    for (int k = 0; k < ZPRE; k++) {
+        const int i = threadIdx.x + k * (GDN_WARPS * 32);
+        if (i < N * GDN_COLS) {
+            const int node = i / GDN_COLS, c = i - node * GDN_COLS;
+            float t = o_s[i];
+            t *= scale_s[node] * a.norm[cb * GDN_COLS + c];
+            o_s[i] = t * silu_ref(zpre[k]);
+        }
+    }
 #pragma unroll 8
-    for (int i = threadIdx.x; i < N * GDN_COLS; i += blockDim.x) {
+    for (int i = threadIdx.x + ZPRE * (GDN_WARPS * 32); i < N * GDN_COLS; i += blockDim.x) {
         const int node = i / GDN_COLS, c = i - node * GDN_COLS;
         const int64_t r = seq * N + node;
         const float zv = a.z[r * a.ldz + h * S + cb * GDN_COLS + c];
