@@ -7,37 +7,6 @@
 namespace yk {
 
 // ---------------------------------------------------------------------------
-// embedding (replaces embedding_batch_f32_kernel, kernels/hip/prefill/prefill.hip:146)
-
-__global__ void embedding_kernel(float * __restrict__ x, int ldx, const uint8_t * __restrict__ table, uint32_t dtype,
-                                 int64_t rb, int hidden, int vocab, const int32_t * __restrict__ tokens) {
-    pdl_entry();
-    const int r = blockIdx.x;
-    int tok = tokens[r];
-    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // ids are validated on the host
-    const uint8_t * row = table + (int64_t)tok * rb;
-    for (int e8 = threadIdx.x; e8 < hidden / 8; e8 += blockDim.x) {
-        float w[8];
-        switch (dtype) {
-        case YUUKA_DTYPE_F32: decode8<YUUKA_DTYPE_F32>(row, e8, w); break;
-        case YUUKA_DTYPE_F16: decode8<YUUKA_DTYPE_F16>(row, e8, w); break;
-        case YUUKA_DTYPE_Q8_0: decode8<YUUKA_DTYPE_Q8_0>(row, e8, w); break;
-        case YUUKA_DTYPE_Q4_K: decode8<YUUKA_DTYPE_Q4_K>(row, e8, w); break;
-        case YUUKA_DTYPE_Q5_K: decode8<YUUKA_DTYPE_Q5_K>(row, e8, w); break;
-        default: decode8<YUUKA_DTYPE_Q6_K>(row, e8, w); break;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[(int64_t)r * ldx + e8 * 8 + i] = w[i];
-    }
-}
-
-void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
-                      const int32_t * tokens, int rows) {
-    launch_k(embedding_kernel, rows, 128, 0, s, x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens);
-    YK_CUDA(cudaGetLastError());
-}
-
-// ---------------------------------------------------------------------------
 // block-wide double sum
 
 __device__ __forceinline__ double warp_sum_d(double v) {
@@ -57,20 +26,15 @@ __device__ __forceinline__ double block_sum_d(double v, double * red) {
     return t;
 }
 
-// rmsNorm (model/qwen35/forward.go:460-470): f64 sum of squares, f32 mean,
-// scale = f32(1/sqrt(f64(mean + eps))), dst = src * scale * weight. Also emits the
-// prepared (fp16 + group sums) form of dst for the GEMM that consumes it.
-__global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
-                               const float * __restrict__ weight, int cols, float eps, XPrepOut prep,
-                               unsigned long long * __restrict__ sumsq_out) {
-    pdl_entry();
-    __shared__ double red[32];
-    const int r = blockIdx.x;
-    const float * x = src + (int64_t)r * lds;
+// rmsNorm (model/qwen35/forward.go:460-470) of one row by the whole CTA: f64 sum of squares, f32 mean,
+// scale = f32(1/sqrt(f64(mean + eps))), dst = x * scale * weight, with the prepared (fp16 + group sums)
+// form of dst for the GEMM that consumes it and, for GEMMs that fold the next norm in, the row's sum of
+// squares in 2^-24 units.
+__device__ void rmsnorm_row(float * __restrict__ dst_row, const float * __restrict__ x, const float * __restrict__ weight, int cols,
+                            float eps, XPrepOut prep, unsigned long long * __restrict__ sumsq_out, int r, double * red) {
     double sum = 0;
     for (int i = threadIdx.x; i < cols; i += blockDim.x) sum += (double)x[i] * (double)x[i];
     sum = block_sum_d(sum, red);
-    // (for GEMMs that fold the next norm in: this row's sum of squares in 2^-24 units)
     if (sumsq_out && threadIdx.x == 0) sumsq_out[r] = (unsigned long long)(sum * 16777216.0);
     float mean = (float)(sum / (double)cols);
     float scale = (float)(1.0 / sqrt((double)(mean + eps)));
@@ -79,14 +43,109 @@ __global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * 
             float v[16];
 #pragma unroll
             for (int i = 0; i < 16; i++) v[i] = x[gq * 16 + i] * scale * weight[gq * 16 + i];
-            float4 * d = reinterpret_cast<float4 *>(dst + (int64_t)r * ldd + gq * 16);
+            float4 * d = reinterpret_cast<float4 *>(dst_row + gq * 16);
 #pragma unroll
             for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
             if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
         }
     } else {
-        for (int i = threadIdx.x; i < cols; i += blockDim.x) dst[(int64_t)r * ldd + i] = x[i] * scale * weight[i];
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) dst_row[i] = x[i] * scale * weight[i];
     }
+}
+
+// ---------------------------------------------------------------------------
+// embedding (replaces embedding_batch_f32_kernel, kernels/hip/prefill/prefill.hip:146)
+
+// One CTA per row. With `first` set the CTA also does what the step's next two small kernels would do for
+// the row: the first layer's input RMSNorm and the row's RoPE angles (forward.go:503-505, f64).
+struct EmbedFirst {
+    const float * norm_w = nullptr;  // null: embedding only
+    float * xn = nullptr;
+    int ldxn = 0;
+    float eps = 0.0f;
+    XPrepOut prep;
+    unsigned long long * sumsq_out = nullptr;
+    float2 * rope_cs = nullptr;      // null: no table
+    RowMeta rows;
+    int rope_dim = 0;
+    double rope_base = 0.0;
+};
+
+__global__ void __launch_bounds__(256) embedding_kernel(float * __restrict__ x, int ldx, const uint8_t * __restrict__ table,
+                                                        uint32_t dtype, int64_t rb, int hidden, int vocab,
+                                                        const int32_t * __restrict__ tokens, const EmbedFirst first) {
+    pdl_entry();
+    __shared__ double red[32];
+    const int r = blockIdx.x;
+    int tok = tokens[r];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // ids are validated on the host
+    const uint8_t * row = table + (int64_t)tok * rb;
+    for (int e8 = threadIdx.x; e8 < hidden / 8; e8 += blockDim.x) {
+        float w[8];
+        switch (dtype) {
+        case YUUKA_DTYPE_F32: decode8<YUUKA_DTYPE_F32>(row, e8, w); break;
+        case YUUKA_DTYPE_F16: decode8<YUUKA_DTYPE_F16>(row, e8, w); break;
+        case YUUKA_DTYPE_Q8_0: decode8<YUUKA_DTYPE_Q8_0>(row, e8, w); break;
+        case YUUKA_DTYPE_Q4_K: decode8<YUUKA_DTYPE_Q4_K>(row, e8, w); break;
+        case YUUKA_DTYPE_Q5_K: decode8<YUUKA_DTYPE_Q5_K>(row, e8, w); break;
+        default: decode8<YUUKA_DTYPE_Q6_K>(row, e8, w); break;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[(int64_t)r * ldx + e8 * 8 + i] = w[i];
+    }
+    if (first.rope_cs) {
+        const int seq = r / first.rows.nodes;
+        const int pos = first.rows.pos0[seq] + first.rows.depth[r];
+        const int half = first.rope_dim / 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            double theta = (double)pos * pow(first.rope_base, -2.0 * (double)i / (double)first.rope_dim);
+            first.rope_cs[(int64_t)r * half + i] = make_float2((float)cos(theta), (float)sin(theta));
+        }
+    }
+    if (first.norm_w) {
+        __syncthreads();  // the row just written is read back by other threads of this CTA
+        rmsnorm_row(first.xn + (int64_t)r * first.ldxn, x + (int64_t)r * ldx, first.norm_w, hidden, first.eps, first.prep,
+                    first.sumsq_out, r, red);
+    }
+}
+
+void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
+                      const int32_t * tokens, int rows) {
+    launch_k(embedding_kernel, rows, 256, 0, s, x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens,
+             EmbedFirst());
+    YK_CUDA(cudaGetLastError());
+}
+
+// Embedding, the first layer's input norm and (rope_cs non-null) the rows' RoPE table in one launch. `table_rows` is the
+// row layout the RoPE positions are counted in (for a wide prompt pass: its sub-chunks as sequences).
+void launch_embedding_first(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
+                            const int32_t * tokens, int rows, const float * norm_w, float * xn, int ldxn, float eps, XPrepOut prep,
+                            unsigned long long * sumsq_out, float2 * rope_cs, const RowMeta & table_rows, int rope_dim,
+                            double rope_base) {
+    YK_REQUIRE(!prep.xh || ((hidden & 15) == 0 && (ldxn & 3) == 0), YUUKA_ERR_UNSUPPORTED,
+               "rmsnorm: prepared output needs a width that is a multiple of 16");
+    EmbedFirst f;
+    f.norm_w = norm_w;
+    f.xn = xn;
+    f.ldxn = ldxn;
+    f.eps = eps;
+    f.prep = prep;
+    f.sumsq_out = sumsq_out;
+    f.rope_cs = rope_cs;
+    f.rows = table_rows;
+    f.rope_dim = rope_dim;
+    f.rope_base = rope_base;
+    launch_k(embedding_kernel, rows, 256, 0, s, x, ldx, table, dtype, (int64_t)row_bytes(dtype, hidden), hidden, vocab, tokens, f);
+    YK_CUDA(cudaGetLastError());
+}
+
+__global__ void rmsnorm_kernel(float * __restrict__ dst, int ldd, const float * __restrict__ src, int lds,
+                               const float * __restrict__ weight, int cols, float eps, XPrepOut prep,
+                               unsigned long long * __restrict__ sumsq_out) {
+    pdl_entry();
+    __shared__ double red[32];
+    const int r = blockIdx.x;
+    rmsnorm_row(dst + (int64_t)r * ldd, src + (int64_t)r * lds, weight, cols, eps, prep, sumsq_out, r, red);
 }
 
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight, int cols,

@@ -743,25 +743,32 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
 
     s->order_pos = 0;
-    mark(s, YUUKA_OP_EMBEDDING);
-    launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
-    s->launches++;
-    if (s->rope_cs) {
-        // (a wide pass: every sub-chunk counts positions from its own start; rows past the end are scratch)
-        RowMeta rr = sub > 0 ? RowMeta{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos_sub, n_sub, sub} : rows;
-        launch_rope_table(st, s->rope_cs, rr, c.rope_dim, c.rope_freq_base);
-        s->launches++;
-    }
-    // the first layer's input norm is a kernel of its own; with 3..32 rows every later norm is folded into
-    // the GEMM that finishes the residual rows and the GEMM that reads them
+    // with 3..32 rows every norm after the first is folded into the GEMM that finishes the residual rows
+    // and the GEMM that reads them
     s->fold_step = s->fold_norm && R >= 3 && R <= 32;
     s->norm_point = 0;
     s->xn_raw = false;
     if (s->fold_step) YK_CUDA(cudaMemsetAsync(s->norm_sumsq, 0, sizeof(unsigned long long) * 32 * (size_t)(2 * c.block_count + 2), st));
-    mark(s, YUUKA_OP_RMSNORM);
-    launch_rmsnorm(st, s->xn, H, s->x, H, m->layers[0].attn_norm, H, R, c.rms_eps, s->prep_xn,
-                   s->fold_step ? s->norm_sumsq : nullptr);
-    s->launches++;
+    unsigned long long * sumsq0 = s->fold_step ? s->norm_sumsq : nullptr;
+    mark(s, YUUKA_OP_EMBEDDING);
+    if (sub == 0 && (H & 7) == 0) {
+        // embedding rows, the first layer's input norm and the rows' RoPE table: one launch, one CTA per row
+        launch_embedding_first(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R, m->layers[0].attn_norm,
+                               s->xn, H, c.rms_eps, s->prep_xn, sumsq0, s->rope_cs, rows, c.rope_dim, c.rope_freq_base);
+        s->launches++;
+    } else {
+        launch_embedding(st, s->x, H, m->embedding.ptr, m->embedding.dtype, H, c.vocab, s->d_tokens, R);
+        s->launches++;
+        if (s->rope_cs) {
+            // (a wide pass: every sub-chunk counts positions from its own start; rows past the end are scratch)
+            RowMeta rr = sub > 0 ? RowMeta{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos_sub, n_sub, sub} : rows;
+            launch_rope_table(st, s->rope_cs, rr, c.rope_dim, c.rope_freq_base);
+            s->launches++;
+        }
+        mark(s, YUUKA_OP_RMSNORM);
+        launch_rmsnorm(st, s->xn, H, s->x, H, m->layers[0].attn_norm, H, R, c.rms_eps, s->prep_xn, sumsq0);
+        s->launches++;
+    }
     for (int i = 0; i < c.block_count; i++) {
         const LayerW & L = m->layers[i];
         LayerState & LS = s->layers[i];

@@ -31,6 +31,12 @@ struct KvPool {
 // x[r][:] = dequantized row tokens[r] of the embedding table (forward.go:120-129)
 void launch_embedding(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden,
                       int vocab, const int32_t * tokens, int rows);
+// The same with the first layer's input RMSNorm of every row (and, rope_cs non-null, the rows' RoPE table, positions
+// counted in table_rows' layout) done by the row's CTA: one launch instead of three at the start of a step.
+void launch_embedding_first(cudaStream_t s, float * x, int ldx, const uint8_t * table, uint32_t dtype, int hidden, int vocab,
+                            const int32_t * tokens, int rows, const float * norm_w, float * xn, int ldxn, float eps, XPrepOut prep,
+                            unsigned long long * sumsq_out, float2 * rope_cs, const RowMeta & table_rows, int rope_dim,
+                            double rope_base);
 // dst[r][:] = src[r][:] * rsqrt(mean(src^2) + eps) * weight (forward.go:460-470)
 void launch_rmsnorm(cudaStream_t s, float * dst, int ldd, const float * src, int lds, const float * weight,
                     int cols, int rows, float eps, XPrepOut prep = XPrepOut(),
