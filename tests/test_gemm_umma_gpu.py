@@ -19,7 +19,7 @@ def dev():
 
 
 @pytest.mark.parametrize("dtype", [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.Q5_K])
-@pytest.mark.parametrize("rows", [48, 64, 100, 256, 300])
+@pytest.mark.parametrize("rows", [48, 64, 100, 256, 272, 300, 512, 600])
 def test_umma_route_matches_oracle(dev, dtype, rows):
     n_out, n_in = 520, 512   # five blocks of 128 weight rows, the last one partial; two superblocks
     w = synth.normal_quant(n_out, n_in, dtype, 0.02, 300 + dtype)

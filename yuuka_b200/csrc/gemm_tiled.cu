@@ -1324,13 +1324,29 @@ static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in, int rows) 
     return ks < 1 ? 1 : ks;
 }
 
+static bool umma_specialised() {
+    static const bool on = [] { const char * e = getenv("YUUKA_CUDA_UMMA_WS"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+// Activation rows of one tensor-memory launch. YUUKA_CUDA_UMMA_ROWS=256 keeps the warp-specialised kernel to one
+// accumulator.
+static int umma_rows_per_launch() {
+    static const int rows = [] {
+        const char * e = getenv("YUUKA_CUDA_UMMA_ROWS");
+        const int want = e ? atoi(e) : UM_MAX_N2;
+        return want > UM_MAX_N && umma_specialised() ? UM_MAX_N2 : UM_MAX_N;
+    }();
+    return rows;
+}
+
 void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int rows, int n_out, int n_in,
                              uint64_t * partial_floats, int * counters) {
     *partial_floats = 0;
     *counters = 0;
     if (!tiled_supported(w_dtype, n_in)) return;
     if (rows >= UMMA_MIN_ROWS) {
-        const int per_launch = rows < UM_MAX_N ? rows : UM_MAX_N;
+        const int per_launch = rows < umma_rows_per_launch() ? rows : umma_rows_per_launch();
         // enough for this row count and for every smaller one (fewer rows may split K further)
         int ks = 1, worst = 0;
         for (int m = UMMA_MIN_ROWS; m <= per_launch; m += 16) {
@@ -1545,9 +1561,11 @@ template <int DT>
 static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a, const __half * xh) {
     int launches = 0;
     const int n_blocks = (a.n_out + UM_ROWS - 1) / UM_ROWS;
-    // rows per launch: 256 with tensor-map copies; the padded cp.async stages are larger, so fewer fit
+    // rows per launch: 512 (two accumulators) with tensor-map copies and the warp-specialised kernel, 256 with the
+    // one-accumulator kernel; the padded cp.async stages are larger, so fewer fit
     const bool want_tma = tensor_map_encoder() != nullptr;
-    int max_n = UM_MAX_N;
+    const bool ws = want_tma && umma_specialised();
+    int max_n = ws ? umma_rows_per_launch() : UM_MAX_N;
     while (!want_tma && max_n > 16 &&
            (size_t)(UM_STAGES - 1) * (UM_A_BYTES + (size_t)(max_n / 8) * UM_B_SBO) + (size_t)TW * Codec<DT>::TAB + 1024 >
                dev->prop.sharedMemPerBlockOptin)
@@ -1568,8 +1586,11 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         p.accumulate = (a.flags & YUUKA_GEMM_ACCUMULATE) ? 1 : 0;
         p.tmem_cols = 32;
         while ((int)p.tmem_cols < p.npad) p.tmem_cols *= 2;
-        // instruction descriptor: D f32, A and B f16, both K-major, N = npad, M = 128
-        p.idesc = (1u << 4) | ((uint32_t)(p.npad >> 3) << 17) | ((uint32_t)(UM_ROWS >> 4) << 24);
+        // instruction descriptor: D f32, A and B f16, both K-major, N = rows of the accumulator, M = 128
+        const int n1 = p.npad < UM_MAX_N ? p.npad : UM_MAX_N;
+        p.idesc = (1u << 4) | ((uint32_t)(n1 >> 3) << 17) | ((uint32_t)(UM_ROWS >> 4) << 24);
+        p.idesc2 = p.npad > UM_MAX_N ? (1u << 4) | ((uint32_t)((p.npad - UM_MAX_N) >> 3) << 17) | ((uint32_t)(UM_ROWS >> 4) << 24) : 0u;
+        p.box_rows = (uint32_t)n1;
         if (ksplit > 1) {
             YK_REQUIRE(a.scratch && a.scratch->partial_floats >= (uint64_t)ksplit * m * a.n_out &&
                            a.scratch->counter_count >= n_blocks,
@@ -1579,18 +1600,16 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         }
         alignas(64) CUtensorMap xmap;
         memset(&xmap, 0, sizeof(xmap));
-        const bool tma = want_tma && make_x_map(&xmap, p.xh, m, a.n_in, p.npad);
+        const bool tma = want_tma && make_x_map(&xmap, p.xh, m, a.n_in, (int)p.box_rows);
         YK_REQUIRE(tma || !want_tma, YUUKA_ERR_INTERNAL, "umma gemm: the tensor map of the activations could not be encoded");
-        const size_t b_bytes = tma ? (size_t)p.npad * 128 : (size_t)(p.npad / 8) * UM_B_SBO;
+        const size_t b_bytes = tma ? (size_t)(p.idesc2 ? 2 : 1) * p.box_rows * 128 : (size_t)(p.npad / 8) * UM_B_SBO;
         p.stages = UM_STAGES;
         size_t smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
-        if (smem > dev->prop.sharedMemPerBlockOptin) {
-            p.stages = UM_STAGES - 1;
+        while (smem > dev->prop.sharedMemPerBlockOptin && p.stages > 2) {
+            p.stages--;
             smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
         }
         YK_REQUIRE(smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_INTERNAL, "umma gemm: stage buffers do not fit shared memory");
-        static const bool specialised = [] { const char * e = getenv("YUUKA_CUDA_UMMA_WS"); return !(e && e[0] == '0'); }();
-        const bool ws = tma && specialised;
         auto kern = ws ? gemm_umma_ws_kernel<DT> : (tma ? gemm_umma_kernel<DT, true> : gemm_umma_kernel<DT, false>);
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int per_split = dev->sm_count / ksplit > 0 ? dev->sm_count / ksplit : 1;

@@ -26,7 +26,8 @@ constexpr int UM_ROWS = 128;   // weight rows per CTA = UMMA M
 constexpr int UM_KC = 64;      // columns per stage
 constexpr int UM_STAGES = 4;
 constexpr int UM_AHEAD = 2;    // chunks of activations in flight ahead of the decode
-constexpr int UM_MAX_N = 256;  // activation rows per launch = UMMA N
+constexpr int UM_MAX_N = 256;  // activation rows of one accumulator = UMMA N
+constexpr int UM_MAX_N2 = 512; // activation rows per launch of the warp-specialised kernel: two accumulators fill tensor memory
 // Weight stage: dense core matrices. Padding them to 160 bytes removes the four-way bank conflicts of the
 // decode warps' 16-byte stores and measured the same overall (56.3 vs 55.8 us on 18432 x 2560 at 256 rows),
 // so the smaller stage is kept; -DYK_UMMA_A_LBO=160 builds the padded form.
@@ -53,7 +54,9 @@ struct UParams {
     int accumulate;
     uint32_t tmem_cols;   // power of two >= npad, >= 32
     uint32_t idesc;
-    uint32_t stages;      // ring depth: UM_STAGES, or one less when four stages do not fit shared memory
+    uint32_t idesc2;      // second accumulator (rows 256...), warp-specialised kernel with more than 256 rows; else 0
+    uint32_t box_rows;    // rows of one tensor-map box: npad, or 256 with two accumulators
+    uint32_t stages;      // ring depth: UM_STAGES, or fewer when four stages do not fit shared memory (at least 2)
     float * partial;      // [gridDim.y][M][N] when K is split across CTAs
     int * counters;       // one per block of 128 weight rows, zero between launches
 };
@@ -509,7 +512,9 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
     __shared__ uint32_t tmem_slot;
     __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t b_bytes = (uint32_t)p.npad * 128u;
+    const uint32_t halves = p.idesc2 ? 2u : 1u;
+    const uint32_t half_bytes = p.box_rows * 128u;
+    const uint32_t b_bytes = halves * half_bytes;
     const uint32_t stage_bytes = UM_A_BYTES + b_bytes;
     uint8_t * tabs = smem + (size_t)p.stages * stage_bytes;
 
@@ -564,11 +569,13 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                 const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xfull_bar[stage]);
                 const int col0 = sb_begin * 256 + (int)in_block * UM_KC;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                    :
-                    : "r"(smem_base + stage * stage_bytes + UM_A_BYTES), "l"(&xmap), "r"(col0), "r"(0), "r"(bar)
-                    : "memory");
+                for (uint32_t h = 0; h < halves; h++)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        :
+                        : "r"(smem_base + stage * stage_bytes + UM_A_BYTES + h * half_bytes), "l"(&xmap), "r"(col0),
+                          "r"((int)(h * UM_MAX_N)), "r"(bar)
+                        : "memory");
                 if (++stage == p.stages) { stage = 0; use++; }
                 if (++in_block == (uint32_t)chunks_per_block) in_block = 0;
             }
@@ -589,16 +596,21 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc(a_addr, UM_A_LBO, UM_A_SBO);
                 const uint64_t db = umma_desc_sw128(b_addr);
+                // rows 256... accumulate in tensor-memory columns 256...: the decoded weights are multiplied twice
+                for (uint32_t h = 0; h < halves; h++) {
+                    const uint32_t idesc = h ? p.idesc2 : p.idesc;
+                    const uint64_t dbh = db + (uint64_t)(h * (half_bytes >> 4));
 #pragma unroll
-                for (int j = 0; j < UM_KC / 16; j++) {
-                    const uint32_t accumulate = (in_block > 0 || j > 0) ? 1u : 0u;
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                        :
-                        : "r"(taddr), "l"(da + (uint64_t)(j * (2 * UM_A_LBO / 16))), "l"(db + (uint64_t)(j * 2)), "r"(p.idesc),
-                          "r"(accumulate), "r"(0u)
-                        : "memory");
+                    for (int j = 0; j < UM_KC / 16; j++) {
+                        const uint32_t accumulate = (in_block > 0 || j > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                            :
+                            : "r"(taddr + h * (uint32_t)UM_MAX_N), "l"(da + (uint64_t)(j * (2 * UM_A_LBO / 16))),
+                              "l"(dbh + (uint64_t)(j * 2)), "r"(idesc), "r"(accumulate), "r"(0u)
+                            : "memory");
+                    }
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                  (uint32_t)__cvta_generic_to_shared(&empty_bar[stage]))
