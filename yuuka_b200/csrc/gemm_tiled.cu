@@ -1311,14 +1311,24 @@ static bool umma_enabled() {
 }
 
 // K splits of the tensor-memory route: enough CTAs to fill the machine when the matrix has few
-// 128-row blocks, at least two superblocks each.
-static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in, int rows) {
+// 128-row blocks, at least two superblocks each. `separate` (may be null: then the in-kernel sum is the only
+// choice) is set when the parts are summed by a kernel of their own.
+static bool umma_specialised();
+static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in, int rows, bool * separate) {
     const int n_blocks = (n_out + UM_ROWS - 1) / UM_ROWS, nsb = n_in / 256;
     int ks = dev->sm_count / n_blocks;
     if (ks > nsb / 2) ks = nsb / 2;
+    if (separate) *separate = false;
+    static const int forced = [] { const char * e = getenv("YUUKA_CUDA_UMMA_KSPLIT"); return e ? atoi(e) : 0; }();
+    static const bool no_separate = [] { const char * e = getenv("YUUKA_CUDA_UMMA_INLINE_SUM"); return e && e[0] == '1'; }();
+    // Beyond 96 activation rows the decode of a narrow matrix (20 blocks of a 2560-row one) is spread over the
+    // whole machine and the parts are summed by every SM in a second launch; the output must allow 16-byte stores.
+    if (separate && forced == 0 && !no_separate && rows > 96 && ks > 2 && (n_out & 3) == 0 && umma_specialised()) {
+        *separate = true;
+        return ks < 8 ? ks : 8;
+    }
     // the last CTA of a block sums the parts alone: measured on 2560-row matrices, four parts pay up to
     // about 96 activation rows and two beyond (the sum grows with rows x parts, the decode it hides does not)
-    static const int forced = [] { const char * e = getenv("YUUKA_CUDA_UMMA_KSPLIT"); return e ? atoi(e) : 0; }();
     const int cap = forced > 0 ? forced : (rows <= 96 ? 4 : 2);
     if (ks > cap) ks = cap;
     return ks < 1 ? 1 : ks;
@@ -1350,12 +1360,14 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
         // enough for this row count and for every smaller one (fewer rows may split K further)
         int ks = 1, worst = 0;
         for (int m = UMMA_MIN_ROWS; m <= per_launch; m += 16) {
-            const int k = umma_ksplit(dev, n_out, n_in, m);
+            bool sep;
+            const int k = umma_ksplit(dev, n_out, n_in, m, &sep);
             if (k > ks) ks = k;
             if (k * m > worst) worst = k * m;
         }
         {
-            const int k = umma_ksplit(dev, n_out, n_in, per_launch);
+            bool sep;
+            const int k = umma_ksplit(dev, n_out, n_in, per_launch, &sep);
             if (k > ks) ks = k;
             if (k * per_launch > worst) worst = k * per_launch;
         }
@@ -1572,7 +1584,8 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         max_n -= 16;
     for (int m0 = 0; m0 < a.rows; m0 += max_n) {
         const int m = a.rows - m0 < max_n ? a.rows - m0 : max_n;
-        const int ksplit = umma_ksplit(dev, a.n_out, a.n_in, m);
+        bool separate = false;
+        const int ksplit = umma_ksplit(dev, a.n_out, a.n_in, m, ws && (a.ldo & 3) == 0 && ((uintptr_t)a.out & 15) == 0 ? &separate : nullptr);
         UParams p{};
         p.kc = decode_consts(DT);
         p.w = a.w;
@@ -1596,7 +1609,7 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
                            a.scratch->counter_count >= n_blocks,
                        YUUKA_ERR_INTERNAL, "umma gemm: split-K scratch is too small");
             p.partial = a.scratch->partial;
-            p.counters = a.scratch->counters;
+            p.counters = separate ? nullptr : a.scratch->counters;
         }
         alignas(64) CUtensorMap xmap;
         memset(&xmap, 0, sizeof(xmap));
@@ -1617,6 +1630,14 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         launch_k(kern, grid, ws ? UM_WS_THREADS : TW * 32, smem, s, p, xmap);
         YK_CUDA(cudaGetLastError());
         launches++;
+        if (separate && ksplit > 1) {
+            const int64_t quads = (int64_t)m * (a.n_out / 4);
+            const int64_t want = (quads + 255) / 256, most = (int64_t)dev->sm_count * 8;
+            launch_k(umma_reduce_kernel, (int)(want < most ? want : most), 256, 0, s, p.out, p.ldo, (const float *)p.partial, ksplit, m,
+                     a.n_out, p.accumulate);
+            YK_CUDA(cudaGetLastError());
+            launches++;
+        }
     }
     return launches;
 }

@@ -713,8 +713,9 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive((uint32_t)__cvta_generic_to_shared(&tmem_free_bar));
-            if (split) {
+            if (split && p.counters) {
                 // K is split across CTAs: the last one to finish this block of rows sums the parts in a fixed order
+                // (without counters the parts are summed by umma_reduce_kernel, launched next)
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");
                 if (threadIdx.x == 0) last_flag = atomicAdd(&p.counters[rb], 1) == (int)gridDim.y - 1;
@@ -760,6 +761,36 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
     __syncthreads();
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(p.tmem_cols) : "memory");
+}
+
+// Sum of the K parts of a split tensor-memory GEMM, in part order: out[tok][n] (+)= sum over parts of
+// partial[part][tok][n]. With many parts and hundreds of activation rows the whole machine sums; the last CTA
+// of a 128-row block doing it alone took longer than the decode the split saved.
+__global__ void __launch_bounds__(256) umma_reduce_kernel(float * __restrict__ out, int64_t ldo, const float * __restrict__ partial,
+                                                          int parts, int M, int N, int accumulate) {
+    pdl_entry();
+    const int n4 = N >> 2;
+    const int64_t total = (int64_t)M * n4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int tok = (int)(i / n4), n = (int)(i - (int64_t)tok * n4) * 4;
+        float4 * dst = reinterpret_cast<float4 *>(out + (int64_t)tok * ldo + n);
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int part = 0; part < parts; part++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(partial + ((size_t)part * M + tok) * N + n));
+            sum.x += v.x;
+            sum.y += v.y;
+            sum.z += v.z;
+            sum.w += v.w;
+        }
+        if (accumulate) {
+            const float4 old = *dst;
+            sum.x = old.x + sum.x;
+            sum.y = old.y + sum.y;
+            sum.z = old.z + sum.z;
+            sum.w = old.w + sum.w;
+        }
+        *dst = sum;
+    }
 }
 
 }  // namespace yk
