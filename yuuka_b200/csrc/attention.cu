@@ -199,8 +199,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
 // hold the same softmax statistics, and each multiplies the probabilities (fp16) with its own
 // 16 x 32 x HD/4 slice of V, fetched with ldmatrix.trans.
 constexpr int AM_KT = 32;
-constexpr int AM_ROWS = 48;
-constexpr int AM_WARPS = 12;
+// Query rows per CTA: 16 per row block of four warps; three row blocks (a 9-row tree of four query heads per KV head
+// fits), four when a sequence has more than 48 query rows per KV head (64 cover a 16-row tree in one pass over the keys).
+constexpr int AM_RB_SMALL = 3, AM_RB_LARGE = 4;
+
+int attention_query_tiles(int q_rows) {
+    const int per = 16 * (q_rows > 16 * AM_RB_SMALL ? AM_RB_LARGE : AM_RB_SMALL);
+    return (q_rows + per - 1) / per;
+}
 
 __device__ __forceinline__ void mma16816h(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -218,9 +224,10 @@ __device__ __forceinline__ __half split_half(float v, __half & lo) {
     return hi;
 }
 
-template <int HD, bool KSPLIT>
-__global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const AttnParams p) {
+template <int HD, bool KSPLIT, int RB>
+__global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParams p) {
     pdl_entry();
+    constexpr int AM_ROWS = 16 * RB, AM_WARPS = 4 * RB;
     constexpr int STR = HD + 8;   // halves per shared-memory row: 16 bytes of padding spread the banks
     constexpr int DW = HD / 4;    // head dimensions per warp
     constexpr int NT_O = DW / 8;  // 8-column output tiles per warp
@@ -281,19 +288,49 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const Attn
 #pragma unroll
         for (int c = 0; c < 4; c++) o[nt][c] = 0.0f;
 
-    for (int k0 = k_begin; k0 < k_end; k0 += AM_KT) {
-        __syncthreads();  // the previous tile has been consumed (and, first time, the queries are in place)
-        for (int i = threadIdx.x; i < AM_KT * (HD / 8); i += AM_WARPS * 32) {
+    // F16 pool: the 16-byte pieces of the next key tile are fetched into registers while this one is multiplied
+    constexpr int PIECES = AM_KT * (HD / 8);
+    constexpr int PER = (PIECES + AM_WARPS * 32 - 1) / (AM_WARPS * 32);
+    uint4 nk[PER], nv[PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < PER; u++) {
+            const int i = threadIdx.x + u * AM_WARPS * 32;
             const int j = i / (HD / 8), c8 = i - j * (HD / 8);
             const int pos = k0 + j;
-            uint4 kh4 = make_uint4(0, 0, 0, 0), kl4 = kh4, vh4 = kh4;
-            if (pos < k_end) {
+            nk[u] = make_uint4(0, 0, 0, 0);
+            nv[u] = nk[u];
+            if (i < PIECES && pos < k_end) {
                 const int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
                 const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
-                if (!KSPLIT) {
-                    kh4 = *reinterpret_cast<const uint4 *>(p.pool.k + off + (size_t)(kvh * HD + c8 * 8) * 2);
-                    vh4 = *reinterpret_cast<const uint4 *>(p.pool.v + off + (size_t)(kvh * HD + c8 * 8) * 2);
-                } else {
+                nk[u] = *reinterpret_cast<const uint4 *>(p.pool.k + off + (size_t)(kvh * HD + c8 * 8) * 2);
+                nv[u] = *reinterpret_cast<const uint4 *>(p.pool.v + off + (size_t)(kvh * HD + c8 * 8) * 2);
+            }
+        }
+    };
+    if (!KSPLIT && k_begin < k_end) fetch(k_begin);
+
+    for (int k0 = k_begin; k0 < k_end; k0 += AM_KT) {
+        __syncthreads();  // the previous tile has been consumed (and, first time, the queries are in place)
+        if (!KSPLIT) {
+#pragma unroll
+            for (int u = 0; u < PER; u++) {
+                const int i = threadIdx.x + u * AM_WARPS * 32;
+                const int j = i / (HD / 8), c8 = i - j * (HD / 8);
+                if (i < PIECES) {
+                    *reinterpret_cast<uint4 *>(ks + j * STR + c8 * 8) = nk[u];
+                    *reinterpret_cast<uint4 *>(vs + j * STR + c8 * 8) = nv[u];
+                }
+            }
+            if (k0 + AM_KT < k_end) fetch(k0 + AM_KT);
+        } else {
+            for (int i = threadIdx.x; i < PIECES; i += AM_WARPS * 32) {
+                const int j = i / (HD / 8), c8 = i - j * (HD / 8);
+                const int pos = k0 + j;
+                uint4 kh4 = make_uint4(0, 0, 0, 0), kl4 = kh4, vh4 = kh4;
+                if (pos < k_end) {
+                    const int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
+                    const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
                     float kw[8], vw[8];
                     kv_decode8(p.pool.k + off, p.pool.format, kvh * (HD / 8) + c8, kw);
                     kv_decode8(p.pool.v + off, p.pool.format, kvh * (HD / 8) + c8, vw);
@@ -307,10 +344,10 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attention_mma_kernel(const Attn
                     kl4 = *reinterpret_cast<const uint4 *>(ll);
                     vh4 = *reinterpret_cast<const uint4 *>(vv);
                 }
+                *reinterpret_cast<uint4 *>(ks + j * STR + c8 * 8) = kh4;
+                *reinterpret_cast<uint4 *>(kl + j * STR + c8 * 8) = kl4;
+                *reinterpret_cast<uint4 *>(vs + j * STR + c8 * 8) = vh4;
             }
-            *reinterpret_cast<uint4 *>(ks + j * STR + c8 * 8) = kh4;
-            if (KSPLIT) *reinterpret_cast<uint4 *>(kl + j * STR + c8 * 8) = kl4;
-            *reinterpret_cast<uint4 *>(vs + j * STR + c8 * 8) = vh4;
         }
         __syncthreads();
 
@@ -549,13 +586,15 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
     if (use_mma) {
         // tensor-core partials; keys are taken as they are from an F16 pool and split into hi + lo otherwise
         const bool ksplit = pool.format != YUUKA_KV_F16;
-        const int qtiles = (G * rows.nodes + AM_ROWS - 1) / AM_ROWS;
-        const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * AM_ROWS + (ksplit ? 3 : 2) * AM_KT) +
-                            sizeof(float) * AM_WARPS * 512;
-        auto kern = ksplit ? attention_mma_kernel<HD, true> : attention_mma_kernel<HD, false>;
+        const int qtiles = attention_query_tiles(G * rows.nodes);
+        const int rb = G * rows.nodes > 16 * AM_RB_SMALL ? AM_RB_LARGE : AM_RB_SMALL;
+        const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * 16 * rb + (ksplit ? 3 : 2) * AM_KT) +
+                            sizeof(float) * 4 * rb * 512;
+        auto kern = rb == AM_RB_LARGE ? (ksplit ? attention_mma_kernel<HD, true, AM_RB_LARGE> : attention_mma_kernel<HD, false, AM_RB_LARGE>)
+                                      : (ksplit ? attention_mma_kernel<HD, true, AM_RB_SMALL> : attention_mma_kernel<HD, false, AM_RB_SMALL>);
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid(sc.splits, kv_heads * qtiles, rows.batch);
-        launch_k(kern, grid, AM_WARPS * 32, smem, s, p);
+        launch_k(kern, grid, rb * 128, smem, s, p);
         YK_CUDA(cudaGetLastError());
     } else {
         const int qtiles = (G * rows.nodes + ATT_QT - 1) / ATT_QT;

@@ -6,6 +6,23 @@
 
 namespace yk {
 
+// 16 consecutive floats of a row; four 16-byte loads when the address allows it.
+__device__ __forceinline__ void load16(const float * __restrict__ p, float (&v)[16]) {
+    if (((uintptr_t)p & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 q = reinterpret_cast<const float4 *>(p)[i];
+            v[4 * i] = q.x;
+            v[4 * i + 1] = q.y;
+            v[4 * i + 2] = q.z;
+            v[4 * i + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = p[i];
+    }
+}
+
 // ---------------------------------------------------------------------------
 // block-wide double sum
 
@@ -40,9 +57,11 @@ __device__ void rmsnorm_row(float * __restrict__ dst_row, const float * __restri
     float scale = (float)(1.0 / sqrt((double)(mean + eps)));
     if ((cols & 15) == 0) {
         for (int gq = threadIdx.x; gq < (cols >> 4); gq += blockDim.x) {
-            float v[16];
+            float v[16], w[16];
+            load16(x + gq * 16, v);
+            load16(weight + gq * 16, w);
 #pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = x[gq * 16 + i] * scale * weight[gq * 16 + i];
+            for (int i = 0; i < 16; i++) v[i] = v[i] * scale * w[i];
             float4 * d = reinterpret_cast<float4 *>(dst_row + gq * 16);
 #pragma unroll
             for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -166,10 +185,11 @@ __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float *
     pdl_entry();
     const int r = blockIdx.y;
     for (int gq = blockIdx.x * blockDim.x + threadIdx.x; gq < (cols >> 4); gq += gridDim.x * blockDim.x) {
-        float v[16];
+        float v[16], u[16];
+        load16(gate + (int64_t)r * ld + gq * gstride, v);
+        load16(up + (int64_t)r * ld + gq * gstride, u);
 #pragma unroll
-        for (int i = 0; i < 16; i++)
-            v[i] = silu_ref(gate[(int64_t)r * ld + gq * gstride + i]) * up[(int64_t)r * ld + gq * gstride + i];
+        for (int i = 0; i < 16; i++) v[i] = silu_ref(v[i]) * u[i];
         float4 * d = reinterpret_cast<float4 *>(act + (int64_t)r * lda + gq * 16);
 #pragma unroll
         for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);

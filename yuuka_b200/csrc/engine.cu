@@ -871,7 +871,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             }
             AttnScratch sc;
             const int G = c.heads / c.kv_heads;
-            const int qtiles = (G * (sub > 0 ? sub : nodes) + 39) / 40;
+            const int qtiles = attention_query_tiles(G * (sub > 0 ? sub : nodes));
             const int base = c.kv_heads * qtiles * batch;
             // about one CTA per SM at capacity (measured at a 1500-token context: 3.11 ms per step, against 3.16 with
             // two or four per SM: fewer partials for the merge kernel outweigh the shorter key ranges)

@@ -63,6 +63,8 @@ int launch_attention(cudaStream_t s, float * out, int ldo, const float * q, int 
                      int head_dim, const RowMeta & rows, const KvPool & pool, int max_total_keys,
                      const AttnScratch & scratch, XPrepOut prep = XPrepOut());
 size_t attention_scratch_floats(int rows, int heads, int head_dim, int splits);
+// CTAs per (sequence, KV head) of the tensor-core kernel for q_rows = rows per sequence x query heads per KV head.
+int attention_query_tiles(int q_rows);
 
 // Gated DeltaNet over the rows of a step (forward.go:245-287, recurrent.go:56-105).
 struct GdnArgs {
