@@ -279,16 +279,17 @@ def test_wide_hidden_narrow_ffn_model_matches_oracle():
 
 @pytest.mark.parametrize("kv", [cuda.KV_F32, cuda.KV_F16])
 def test_long_prompts_run_as_wide_passes_with_mixer_sub_chunks(tiny, kv):
-    """Prompts beyond 64 tokens: 256-row passes for the GEMMs, 64-row sub-chunks for the delta-net scan, its
-    state commit and the attention, a ragged tail (300 = 256 + 44, 150 = 64 + 64 + 22)."""
+    """Prompts beyond 64 tokens: 512-row passes for the GEMMs (two tensor-memory accumulators beyond 256 rows),
+    64-row sub-chunks for the delta-net scan, its state commit and the attention, ragged tails
+    (600 = 512 + 64 + 24, 150 = 64 + 64 + 22)."""
     cfg, gm, om = tiny
     V = cfg["vocab"]
-    prompt = synth.uniform_i32(300, 0, V, 71)
-    st = yo.State(om, 512, kv)
-    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=512, kv_format=kv)
+    prompt = synth.uniform_i32(600, 0, V, 71)
+    st = yo.State(om, 768, kv)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=768, kv_format=kv)
     lo = st.forward(prompt.tolist())
     lg = sess.forward(prompt)
-    assert sess.position() == st.pos == 300
+    assert sess.position() == st.pos == 600
     err = float(np.max(np.abs(lg - lo)))
     assert err <= 2e-2 and cosine(lg, lo) >= 0.9999, (err, cosine(lg, lo))
     assert np.max(np.abs(sess.snapshot().view(np.float32) - st.snapshot().view(np.float32))) <= 4e-3

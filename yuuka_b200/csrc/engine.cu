@@ -708,10 +708,10 @@ enum LogitRows { LOGITS_NONE, LOGITS_LAST, LOGITS_ALL };
 // Prompt tokens run through the step kernels in chains of up to this many rows (the row masks are 64 bits
 // wide); from 48 rows on the GEMMs take the tensor-memory route.
 // A prompt runs in passes of up to CHAIN_ROWS rows: the GEMMs and row-wise kernels take the whole pass (the
-// tensor-memory GEMM route decodes a weight tile once for up to 256 rows), the sequential mixers (delta-net
+// tensor-memory GEMM route decodes a weight tile once for up to 512 rows), the sequential mixers (delta-net
 // scan + state commit, attention front end + attention) walk it in sub-chunks of CHAIN_SUB rows, the limit
 // of their per-step row bookkeeping (64-bit ancestor masks).
-constexpr int CHAIN_ROWS = 256;
+constexpr int CHAIN_ROWS = 512;
 constexpr int CHAIN_SUB = 64;
 constexpr int CHAIN_MAX_SUBS = CHAIN_ROWS / CHAIN_SUB;
 
