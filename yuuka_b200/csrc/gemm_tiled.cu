@@ -1617,10 +1617,11 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
         YK_REQUIRE(tma || !want_tma, YUUKA_ERR_INTERNAL, "umma gemm: the tensor map of the activations could not be encoded");
         const size_t b_bytes = tma ? (size_t)(p.idesc2 ? 2 : 1) * p.box_rows * 128 : (size_t)(p.npad / 8) * UM_B_SBO;
         p.stages = UM_STAGES;
-        size_t smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
+        const size_t tab_bytes = (size_t)(ws ? UM_DW : TW) * Codec<DT>::TAB;
+        size_t smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + tab_bytes + 1024;
         while (smem > dev->prop.sharedMemPerBlockOptin && p.stages > 2) {
             p.stages--;
-            smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + (size_t)TW * Codec<DT>::TAB + 1024;
+            smem = (size_t)p.stages * (UM_A_BYTES + b_bytes) + tab_bytes + 1024;
         }
         YK_REQUIRE(smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_INTERNAL, "umma gemm: stage buffers do not fit shared memory");
         auto kern = ws ? gemm_umma_ws_kernel<DT> : (tma ? gemm_umma_kernel<DT, true> : gemm_umma_kernel<DT, false>);

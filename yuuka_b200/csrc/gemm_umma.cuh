@@ -493,7 +493,18 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
 // the epilogue has read the accumulator before the next block of rows overwrites it. (Sixteen decode
 // warps, two per tile on alternate chunks, measured slower on wide matrices: 96 registers per thread
 // spill and the doubled scale tables cost a ring stage.)
-constexpr int UM_WS_THREADS = (TW + 2) * 32;
+// Decode warps of the warp-specialised kernel: TW (one per 16-row tile), or 2 * TW: the two warps of a tile take
+// alternate 64-column chunks of every record (-DYK_UMMA_DECODE_WARPS=16). Measured with sixteen (112 registers,
+// 60-260 bytes of spills): Q4_K 18432 x 2560 at 256 / 512 rows 52.7 -> 50.4 / 70.6 -> 65.7 us, but the Q6_K
+// LM head 567 -> 745 us and a 64-row step 6.66 -> 6.96 ms, so eight stay. Asking the records four or eight
+// superblocks ahead into L2 changed nothing either: neither the latency of the weight loads nor the number of
+// decoding warps is what bounds the loop.
+#ifndef YK_UMMA_DECODE_WARPS
+#define YK_UMMA_DECODE_WARPS 8
+#endif
+constexpr int UM_DW = YK_UMMA_DECODE_WARPS;
+static_assert(UM_DW == TW || UM_DW == 2 * TW, "one or two decode warps per 16-row tile");
+constexpr int UM_WS_THREADS = (UM_DW + 2) * 32;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -526,7 +537,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                          : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&done_bar)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_free_bar)), "r"(TW)
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_free_bar)), "r"(UM_DW)
                      : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -556,7 +567,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
     bool expired = false;
 
     pdl_trigger();
-    if (warp == TW) {
+    if (warp == UM_DW) {
         // ---------------- copy warp: starts the activation copy of a stage as soon as it is free ----------------
         pdl_wait();
         if (lane == 0) {
@@ -581,7 +592,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
             }
         }
         __syncwarp();
-    } else if (warp == TW + 1) {
+    } else if (warp == UM_DW + 1) {
         // ---------------- issue warp: (activations landed, weights decoded) -> MMAs -> stage released ----------------
         if (lane == 0) {
             uint32_t stage = 0, use = 0, in_block = 0, blk = 0;
@@ -635,22 +646,23 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
         // ---------------- decode warps ----------------
         uint8_t * tab = tabs + warp * C::TAB;
         const DecodeConsts kc = p.kc;
+        const int tile = warp % TW, parity = warp / TW;  // with two warps per tile: chunks q with (q & 1) == parity
         typename C::Regs cur, nxt;
         if (my_blocks > 0) {
-            const int rt = min(blockIdx.x * (UM_ROWS / 16) + warp, n_tiles - 1);
+            const int rt = min(blockIdx.x * (UM_ROWS / 16) + tile, n_tiles - 1);
             C::load(p.w + rt * rec_row + (size_t)sb_begin * C::REC, lane, cur);
         }
         pdl_wait();
         uint32_t stage = 0, use = 0, block_iter = 0;
         for (int rb = blockIdx.x; rb < n_blocks && chunks_per_block > 0; rb += gridDim.x, block_iter++) {
-            const int rt = min(rb * (UM_ROWS / 16) + warp, n_tiles - 1);
-            const uint8_t * tile = p.w + rt * rec_row;
+            const int rt = min(rb * (UM_ROWS / 16) + tile, n_tiles - 1);
+            const uint8_t * tile_w = p.w + rt * rec_row;
             const bool more_blocks = rb + (int)gridDim.x < n_blocks;
             for (int sb = sb_begin; sb < sb_end; sb++) {
                 if (sb + 1 < sb_end) {
-                    C::load(tile + (size_t)(sb + 1) * C::REC, lane, nxt);
+                    C::load(tile_w + (size_t)(sb + 1) * C::REC, lane, nxt);
                 } else if (more_blocks) {
-                    const int rtn = min((rb + (int)gridDim.x) * (UM_ROWS / 16) + warp, n_tiles - 1);
+                    const int rtn = min((rb + (int)gridDim.x) * (UM_ROWS / 16) + tile, n_tiles - 1);
                     C::load(p.w + rtn * rec_row + (size_t)sb_begin * C::REC, lane, nxt);
                 }
                 Mma<DT, 1>::header(cur, lane, tab);
@@ -658,12 +670,16 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     uint8_t * a_stage = smem + (size_t)stage * stage_bytes;
+                    if (UM_DW > TW && (q & 1) != parity) {
+                        if (++stage == p.stages) { stage = 0; use++; }
+                        continue;
+                    }
                     if (use > 0 && !expired && !mbar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[stage]), (use - 1) & 1))
                         expired = true;
-                    if (q == 0) umma_store_chunk<DT, 0>(cur, lane, tab, kc, a_stage, warp);
-                    else if (q == 1) umma_store_chunk<DT, 1>(cur, lane, tab, kc, a_stage, warp);
-                    else if (q == 2) umma_store_chunk<DT, 2>(cur, lane, tab, kc, a_stage, warp);
-                    else umma_store_chunk<DT, 3>(cur, lane, tab, kc, a_stage, warp);
+                    if (q == 0) umma_store_chunk<DT, 0>(cur, lane, tab, kc, a_stage, tile);
+                    else if (q == 1) umma_store_chunk<DT, 1>(cur, lane, tab, kc, a_stage, tile);
+                    else if (q == 2) umma_store_chunk<DT, 2>(cur, lane, tab, kc, a_stage, tile);
+                    else umma_store_chunk<DT, 3>(cur, lane, tab, kc, a_stage, tile);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive((uint32_t)__cvta_generic_to_shared(&afull_bar[stage]));
@@ -681,7 +697,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                 const int n = rb * UM_ROWS + quad * 32 + lane;
                 float * base = split ? p.partial + (size_t)blockIdx.y * p.M * p.N : p.out;
                 const int64_t ld = split ? p.N : p.ldo;
-                for (int c0 = (warp >> 2) * 32; c0 < p.npad; c0 += 64) {
+                for (int c0 = (warp >> 2) * 32; c0 < p.npad; c0 += (UM_DW / 4) * 32) {
                     uint32_t v[32];
                     const uint32_t src = taddr + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
                     asm volatile(
@@ -717,19 +733,19 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                 // K is split across CTAs: the last one to finish this block of rows sums the parts in a fixed order
                 // (without counters the parts are summed by umma_reduce_kernel, launched next)
                 __threadfence();
-                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(UM_DW * 32) : "memory");
                 if (threadIdx.x == 0) last_flag = atomicAdd(&p.counters[rb], 1) == (int)gridDim.y - 1;
-                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(UM_DW * 32) : "memory");
                 if (last_flag) {
                     __threadfence();
                     const int n0 = rb * UM_ROWS, nrows = min(UM_ROWS, p.N - n0);
                     const int total = p.M * nrows;
-                    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * TW * 32) {
+                    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * UM_DW * 32) {
                         float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f}, old[4];
                         float * dst[4];
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            const int i = min(i0 + u * TW * 32, total - 1);
+                            const int i = min(i0 + u * UM_DW * 32, total - 1);
                             const int tok = i / nrows, n = n0 + i - tok * nrows;
                             dst[u] = p.out + (int64_t)tok * p.ldo + n;
                             old[u] = p.accumulate ? *dst[u] : 0.0f;
@@ -738,7 +754,7 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                             float v[4];
 #pragma unroll
                             for (int u = 0; u < 4; u++) {
-                                const int i = min(i0 + u * TW * 32, total - 1);
+                                const int i = min(i0 + u * UM_DW * 32, total - 1);
                                 const int tok = i / nrows, n = n0 + i - tok * nrows;
                                 v[u] = __ldcg(p.partial + ((size_t)part * p.M + tok) * p.N + n);
                             }
@@ -747,11 +763,11 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                         }
 #pragma unroll
                         for (int u = 0; u < 4; u++)
-                            if (i0 + u * TW * 32 < total) *dst[u] = old[u] + sum[u];
+                            if (i0 + u * UM_DW * 32 < total) *dst[u] = old[u] + sum[u];
                     }
                     if (threadIdx.x == 0) p.counters[rb] = 0;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(TW * 32) : "memory");  // last_flag is reused by the next block
+                asm volatile("bar.sync 1, %0;" ::"n"(UM_DW * 32) : "memory");  // last_flag is reused by the next block
             }
         }
     }
