@@ -279,17 +279,17 @@ def test_wide_hidden_narrow_ffn_model_matches_oracle():
 
 @pytest.mark.parametrize("kv", [cuda.KV_F32, cuda.KV_F16])
 def test_long_prompts_run_as_wide_passes_with_mixer_sub_chunks(tiny, kv):
-    """Prompts beyond 64 tokens: 512-row passes for the GEMMs (two tensor-memory accumulators beyond 256 rows),
-    64-row sub-chunks for the delta-net scan, its state commit and the attention, ragged tails
-    (600 = 512 + 64 + 24, 150 = 64 + 64 + 22)."""
+    """Prompts beyond 64 tokens: one pass of up to 512 rows for the GEMMs (two tensor-memory accumulators
+    beyond 256 rows), 64-row sub-chunks for the delta-net scan, its state commit and the attention, ragged
+    tails (300 = 4 x 64 + 44, 150 = 64 + 64 + 22)."""
     cfg, gm, om = tiny
     V = cfg["vocab"]
-    prompt = synth.uniform_i32(600, 0, V, 71)
-    st = yo.State(om, 768, kv)
-    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=768, kv_format=kv)
+    prompt = synth.uniform_i32(300, 0, V, 71)
+    st = yo.State(om, 512, kv)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=512, kv_format=kv)
     lo = st.forward(prompt.tolist())
     lg = sess.forward(prompt)
-    assert sess.position() == st.pos == 600
+    assert sess.position() == st.pos == 300
     err = float(np.max(np.abs(lg - lo)))
     assert err <= 2e-2 and cosine(lg, lo) >= 0.9999, (err, cosine(lg, lo))
     assert np.max(np.abs(sess.snapshot().view(np.float32) - st.snapshot().view(np.float32))) <= 4e-3
@@ -306,6 +306,25 @@ def test_long_prompts_run_as_wide_passes_with_mixer_sub_chunks(tiny, kv):
     err = float(np.max(np.abs(got - want)))
     assert got.shape == (150, V) and err <= 2e-2 and cosine(got, want) >= 0.9999, (err, cosine(got, want))
     sess.close(); st.close()
+
+
+def test_prompt_longer_than_one_pass():
+    """600 tokens = a 512-row pass and an 88-row pass (64 + 24): state, conv history and KV rows carry over."""
+    cfg = dict(synth.tiny_config(), context_length=1024)
+    tensors = synth.make_model(cfg, "q8_0", seed=7, unit_norms=False)
+    dev = cuda.Device(0)
+    gm = cuda.Model(dev, cfg, tensors)
+    om = yo.Model(cfg, tensors)
+    prompt = synth.uniform_i32(600, 0, cfg["vocab"], 72)
+    st = yo.State(om, 640, yo.KV_F16)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=640, kv_format=cuda.KV_F16)
+    lo = st.forward(prompt.tolist())
+    lg = sess.forward(prompt)
+    assert sess.position() == st.pos == 600
+    err = float(np.max(np.abs(lg - lo)))
+    assert err <= 2e-2 and cosine(lg, lo) >= 0.9999, (err, cosine(lg, lo))
+    assert np.max(np.abs(sess.snapshot().view(np.float32) - st.snapshot().view(np.float32))) <= 4e-3
+    sess.close(); st.close(); gm.close(); dev.close()
 
 
 def test_mixed_tensor_types_take_the_unfused_routes():

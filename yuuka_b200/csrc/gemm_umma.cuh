@@ -493,6 +493,35 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_umma_kernel(const UParams p, 
 // the epilogue has read the accumulator before the next block of rows overwrites it. (Sixteen decode
 // warps, two per tile on alternate chunks, measured slower on wide matrices: 96 registers per thread
 // spill and the doubled scale tables cost a ring stage.)
+// 32 accumulator values of one weight row (this lane's) for 32 consecutive activation rows, to out[row][n]:
+// MODE 0 stores, 1 adds to what is there, 2 stores a K part past L1. `lim` = rows that exist. One pointer step
+// per value: the per-value bounds, mode and 64-bit index arithmetic of a generic loop were a third of the
+// kernel's instructions at 256 rows and half of them at 512.
+template <int MODE>
+__device__ __forceinline__ void umma_store_rows(float * dst, int64_t ld, const uint32_t (&v)[32], int lim) {
+    if (lim >= 32) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const float val = __uint_as_float(v[i]);
+            if (MODE == 2) __stcg(dst, val);
+            else if (MODE == 1) *dst += val;
+            else *dst = val;
+            dst += ld;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            if (i < lim) {
+                const float val = __uint_as_float(v[i]);
+                if (MODE == 2) __stcg(dst, val);
+                else if (MODE == 1) *dst += val;
+                else *dst = val;
+            }
+            dst += ld;
+        }
+    }
+}
+
 // Decode warps of the warp-specialised kernel: TW (one per 16-row tile), or 2 * TW: the two warps of a tile take
 // alternate 64-column chunks of every record (-DYK_UMMA_DECODE_WARPS=16). Measured with sixteen (112 registers,
 // 60-260 bytes of spills): Q4_K 18432 x 2560 at 256 / 512 rows 52.7 -> 50.4 / 70.6 -> 65.7 us, but the Q6_K
@@ -711,17 +740,11 @@ __global__ void __launch_bounds__(UM_WS_THREADS, 1) gemm_umma_ws_kernel(const UP
                         : "r"(src)
                         : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (n < p.N) {
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const int tok = c0 + i;
-                            if (tok < p.M) {
-                                float * dst = base + (int64_t)tok * ld + n;
-                                const float val = __uint_as_float(v[i]);
-                                if (split) __stcg(dst, val);
-                                else *dst = p.accumulate ? *dst + val : val;
-                            }
-                        }
+                    if (n < p.N && c0 < p.M) {
+                        float * dst = base + (int64_t)c0 * ld + n;
+                        if (split) umma_store_rows<2>(dst, ld, v, p.M - c0);
+                        else if (p.accumulate) umma_store_rows<1>(dst, ld, v, p.M - c0);
+                        else umma_store_rows<0>(dst, ld, v, p.M - c0);
                     }
                 }
             }
