@@ -82,6 +82,10 @@ YUUKA_API void yuuka_device_close(yuuka_device * dev);
 YUUKA_API yuuka_status yuuka_device_info_get(const yuuka_device * dev, yuuka_device_info * info);
 
 /* yuuka_hip.h:60-64 */
+/* Free and total bytes of device memory right now (cudaMemGetInfo): lets a host that
+ * sizes its pools from what is left, or a test, see what a call allocated. */
+YUUKA_API yuuka_status yuuka_device_memory_get(const yuuka_device * dev, uint64_t * free_bytes, uint64_t * total_bytes);
+
 YUUKA_API yuuka_status yuuka_buffer_alloc(yuuka_device * dev, uint64_t bytes, yuuka_buffer ** out);
 YUUKA_API void yuuka_buffer_free(yuuka_buffer * buf);
 YUUKA_API uint64_t yuuka_buffer_size(const yuuka_buffer * buf);
@@ -124,7 +128,14 @@ YUUKA_API yuuka_status yuuka_buffer_copy(yuuka_stream * stream, yuuka_buffer * d
  * GGUF row layout of w_dtype (replaces yuuka_gemv_batch, yuuka_hip.h:291-300,
  * and YUUKA_OP_LM_HEAD). x_dtype is F32 or BF16. Byte offsets select
  * sub-ranges of the buffers. flags: bit 0 adds the product to out instead of
- * overwriting it (GEMV_RESIDUAL, yuuka_hip.h:398-401). */
+ * overwriting it (GEMV_RESIDUAL, yuuka_hip.h:398-401).
+ * The call keeps one scratch area per device (prepared activations, split-K
+ * partial sums and arrival counters) that it grows with cudaMalloc when a larger
+ * shape arrives. Host threads may call concurrently (the growth is serialized), but
+ * kernels of two calls that can overlap on one device (different streams) share
+ * that area and race on it: keep the calls of a device on one stream or order them
+ * with events. Growing the area frees the old one, so a larger shape must not
+ * arrive while an earlier call's kernels may still run on another stream. */
 #define YUUKA_GEMM_ACCUMULATE 0x1u
 /* bit 1: w holds the tile-ordered copy made by yuuka_weights_tile (required by
  * the mma route and by the fast fp32 route; GGUF-layout weights take a slower
@@ -152,8 +163,12 @@ YUUKA_API yuuka_status yuuka_gemm_quant(yuuka_stream * stream,
  *    than YUUKA_GEMM_STATIC_SCRATCH_BYTES returns YUUKA_ERR_UNSUPPORTED and
  *    launches nothing; yuuka_last_error() names the bytes needed.
  *  - The first call on each device does the set-up (it looks up the array's
- *    device address, zeroes the counters and synchronizes the device): make
- *    that call before any stream capture begins. Later calls only launch.
+ *    device address, zeroes the counters, has the driver load the code of
+ *    every kernel this entry point can launch, whatever the shape, so that no
+ *    later call makes the driver place code in device memory, and synchronizes
+ *    the device): make that call before any stream capture begins. Later calls
+ *    only launch; yuuka_device_memory_get reports the same free bytes before
+ *    and after them.
  *  - One scratch per device: two calls whose kernels can overlap (different
  *    streams, or two host threads) race on it. Keep calls on one stream, or
  *    order them with events. */

@@ -1,6 +1,7 @@
 """The verify step at the full size of the graded configuration (4B-shaped dense model: 32 layers,
 hidden 2560, FFN 9216, vocabulary 248,320, Q4_K / Q6_K weights, 512-token prompt, 9 rows), through the
-C ABI. The CPU oracle needs about 1.5 s per token at this size, so the step is held to properties
+C ABI. The CPU oracle needs about 1.5 s per token at this size, so one test compares one step with it (a
+16-token prompt and a 9-row verify step, under a minute of CPU) and the others hold the step to properties
 that do not depend on size:
 
 * the same step run twice from the same state gives identical bits (fixed-order split-K sums, integer
@@ -17,6 +18,7 @@ that do not depend on size:
 import numpy as np
 import pytest
 
+from oracle import pyoracle as yo
 from yuuka_b200 import cuda, synth
 
 pytestmark = pytest.mark.gpu
@@ -31,11 +33,10 @@ def full():
     tensors = synth.make_model(cfg, "q4_k_m", seed=1)
     dev = cuda.Device(0)
     model = cuda.Model(dev, cfg, tensors)
-    del tensors
     sess = cuda.Session(model, max_batch=1, max_nodes=K + 1, capacity=1024, kv_format=cuda.KV_F16)
     prompt = synth.uniform_i32(PROMPT, 0, cfg["vocab"], 100)
     logits = sess.forward(prompt)
-    state = dict(cfg=cfg, dev=dev, model=model, sess=sess, first=int(np.argmax(logits)), snap=sess.snapshot(), pos=sess.position())
+    state = dict(cfg=cfg, dev=dev, model=model, tensors=tensors, sess=sess, first=int(np.argmax(logits)), snap=sess.snapshot(), pos=sess.position())
     yield state
     sess.close(); model.close(); dev.close()
 
@@ -228,3 +229,75 @@ def test_one_gpu_share_of_the_batched_tree_configuration(full):
         assert c.path[b, :a].tolist() == g_out[1][b, :a].tolist() and c.emitted[b, :a + 1].tolist() == g_out[2][b, :a + 1].tolist()
     qb.free()
     sess.close()
+
+
+def cosine(a, b):
+    a, b = a.ravel().astype(np.float64), b.ravel().astype(np.float64)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+
+def test_one_step_at_full_size_matches_the_oracle(full):
+    """A 16-token prompt and one 9-row chain step of the 32-layer, 248,320-token model against the CPU oracle
+    on the same packed weights: last-row prompt logits, all nine rows of step logits (max-abs 2e-2, cosine
+    0.9999), accepted count and emitted tokens (exact unless a deciding row sits within the logit error of a
+    tie), committed position and recurrent state (2e-3). The drafts are the GPU's own continuation with the
+    sixth token replaced, so that rows are accepted and rejected."""
+    cfg, model = full["cfg"], full["model"]
+    V = cfg["vocab"]
+    om = yo.Model(cfg, full["tensors"])
+    prompt = synth.uniform_i32(16, 0, V, 400).tolist()
+    sess = cuda.Session(model, max_batch=1, max_nodes=K + 1, capacity=64, kv_format=cuda.KV_F16)
+    st = yo.State(om, 64, yo.KV_F16)
+    lg, lo = sess.forward(prompt), st.forward(prompt)
+    err0 = float(np.max(np.abs(lg - lo)))
+    assert err0 <= 2e-2 and cosine(lg, lo) >= 0.9999, (err0, cosine(lg, lo))
+    pending = yo.argmax(lo)
+    snap, pos = sess.snapshot(), sess.position()
+    # the GPU's own continuation behind `pending` (dummy drafts: row 0 decides each token)
+    cont, p = [], pending
+    while len(cont) < K:
+        r = sess.verify([[p] + [0] * K])
+        p = int(r.emitted[0, 0])
+        cont.append(p)
+    drafts = np.array(cont, np.int32)
+    drafts[5] = (drafts[5] + 1) % V
+    sess.restore(snap)
+    sess.set_position(0, pos)
+    acc_o, em_o, log_o = st.verify_chain(pending, drafts, want_logits=True)
+    res = sess.verify([[pending] + drafts.tolist()], want_logits=True)
+    err = float(np.max(np.abs(res.logits[0] - log_o)))
+    assert err <= 2e-2 and cosine(res.logits[0], log_o) >= 0.9999, (err, cosine(res.logits[0], log_o))
+    top2 = np.partition(log_o[:acc_o + 1], -2, axis=-1)[:, -2:]
+    if float((top2[:, 1] - top2[:, 0]).min()) >= max(1e-3, 3.0 * err):
+        assert int(res.accepted[0]) == acc_o
+        assert res.emitted[0, :acc_o + 1].tolist() == em_o.tolist()
+        assert sess.position() == st.pos
+        sg, so = sess.snapshot().view(np.float32), st.snapshot().view(np.float32)
+        assert float(np.max(np.abs(sg - so))) <= 2e-3 * (1.0 + float(np.max(np.abs(so))))
+    assert 0 <= acc_o <= 5
+    sess.close(); st.close(); om.close()
+
+
+def test_wide_prompt_pass_of_a_small_vocabulary_model_has_its_split_k_scratch():
+    """A 512-row prompt pass splits K of the narrow 2560-row matrices (ssm_out, ffn_down: 9216 columns) into up
+    to eight parts whose partial sums need parts x 512 x 2560 floats. With the full vocabulary the LM head's
+    own plan happens to reserve more than that; a 1024-token vocabulary does not, so this model checks that
+    a session reserves for its widest pass. The 512-row pass must also agree with the same prompt fed as
+    two 256-row passes (same kernels, different K splits and accumulators)."""
+    cfg = synth.dense4b_config(layers=2, vocab=1024, context=1024)
+    cfg["full_attention_interval"] = 2
+    tensors = synth.make_model(cfg, "q4_k_m", seed=3)
+    dev = cuda.Device(0)
+    model = cuda.Model(dev, cfg, tensors)
+    del tensors
+    prompt = synth.uniform_i32(512, 0, cfg["vocab"], 401)
+    a = cuda.Session(model, max_batch=1, max_nodes=9, capacity=640, kv_format=cuda.KV_F16)
+    la = a.forward(prompt)                                  # one 512-row pass
+    b = cuda.Session(model, max_batch=1, max_nodes=9, capacity=640, kv_format=cuda.KV_F16)
+    b.forward(prompt[:256], want_logits=False)
+    lb = b.forward(prompt[256:])                            # two 256-row passes
+    assert a.position() == b.position() == 512
+    assert np.isfinite(la).all() and float(np.max(np.abs(la - lb))) <= 2e-2
+    sa, sb = a.snapshot().view(np.float32), b.snapshot().view(np.float32)
+    assert float(np.max(np.abs(sa - sb))) <= 4e-3 * (1.0 + float(np.max(np.abs(sb))))
+    a.close(); b.close(); model.close(); dev.close()

@@ -29,13 +29,17 @@ def tiled_weights(dev, stream, dtype, n_out, n_in, seed):
     return wb
 
 
-# (dtype, n_out, n_in, rows, path): split-K across CTAs, no split, fp32 route, bf16 rows > 32
+# (dtype, n_out, n_in, rows, path): split-K across CTAs, no split, fp32 route, rows > 32, and from 48 rows on
+# the tensor-memory route: 2560 outputs split K seven ways with the parts summed by a second kernel, 9216
+# outputs split it two ways with the sum inside the kernel; both keep their partial sums in the fixed array
 SHAPES = [
     (synth.Q6_K, 2560, 9216, 9, cuda.PATH_MMA),
     (synth.Q4_K, 2560, 2560, 9, cuda.PATH_MMA),
     (synth.Q4_K, 9216, 2560, 17, cuda.PATH_AUTO),
     (synth.Q8_0, 528, 2560, 2, cuda.PATH_AUTO),
     (synth.Q5_K, 520, 4096, 40, cuda.PATH_MMA),
+    (synth.Q4_K, 2560, 2560, 64, cuda.PATH_MMA),
+    (synth.Q6_K, 9216, 2560, 64, cuda.PATH_MMA),
 ]
 
 
@@ -61,6 +65,39 @@ def test_static_scratch_matches_allocating_entry_point(dev, dtype, n_out, n_in, 
             b.free()
     assert not np.array_equal(results[0], results[1])  # the two calls really had different inputs
     wb.free()
+    stream.destroy()
+
+
+def test_calls_after_the_first_leave_free_device_memory_unchanged(dev):
+    """What the entry point is for: once the first call on the device has done its set-up, calls allocate
+    nothing, whatever shape, type or route arrives next. Every buffer of the test exists before the first
+    reading of free memory; the shapes then grow and change kernels (fp32 route, the three register-fed
+    tile widths, the tensor-memory route with both kinds of K split), which would make yuuka_gemm_quant grow
+    its scratch and, with lazy module loading, make the driver load new kernels."""
+    stream = dev.stream()
+    cases = [(synth.Q8_0, 528, 2560, 2), (synth.Q4_K, 2560, 2560, 9), (synth.Q6_K, 2560, 9216, 9),
+             (synth.Q5_K, 520, 4096, 17), (synth.Q4_K, 9216, 2560, 40), (synth.Q4_K, 2560, 2560, 64),
+             (synth.Q6_K, 9216, 2560, 64)]
+    bufs = []
+    for i, (dtype, n_out, n_in, rows) in enumerate(cases):
+        wb = tiled_weights(dev, stream, dtype, n_out, n_in, 500 + i)
+        xb = dev.upload(synth.normal_f32(rows * n_in, 1.0, 600 + i))
+        ob = dev.alloc(rows * n_out * 4)
+        bufs.append((wb, xb, ob))
+    # the first call does the set-up
+    dtype, n_out, n_in, rows = cases[0]
+    cuda.gemm_quant_static(stream, bufs[0][2], bufs[0][1], bufs[0][0], n_in, n_out, rows, dtype, cuda.F32, cuda.PATH_AUTO,
+                           cuda.GEMM_TILED)
+    stream.synchronize()
+    free0, _ = dev.memory()
+    for (dtype, n_out, n_in, rows), (wb, xb, ob) in zip(cases, bufs):
+        cuda.gemm_quant_static(stream, ob, xb, wb, n_in, n_out, rows, dtype, cuda.F32, cuda.PATH_AUTO, cuda.GEMM_TILED)
+        stream.synchronize()
+        free, _ = dev.memory()
+        assert free == free0, f"{rows} rows x {n_out} x {n_in}: free memory moved by {free0 - free} bytes"
+        assert np.isfinite(ob.read(np.float32, rows * n_out)).all()
+    for wb, xb, ob in bufs:
+        wb.free(); xb.free(); ob.free()
     stream.destroy()
 
 

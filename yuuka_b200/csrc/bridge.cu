@@ -93,6 +93,17 @@ yuuka_status yuuka_device_info_get(const yuuka_device * dev, yuuka_device_info *
     });
 }
 
+yuuka_status yuuka_device_memory_get(const yuuka_device * dev, uint64_t * free_bytes, uint64_t * total_bytes) {
+    return guard([&] {
+        YK_REQUIRE(dev && free_bytes && total_bytes, YUUKA_ERR_INVALID_ARGUMENT, "device_memory_get: null argument");
+        set_device(dev);
+        size_t f = 0, t = 0;
+        YK_CUDA(cudaMemGetInfo(&f, &t));
+        *free_bytes = f;
+        *total_bytes = t;
+    });
+}
+
 yuuka_status yuuka_buffer_alloc(yuuka_device * dev, uint64_t bytes, yuuka_buffer ** out) {
     return guard([&] {
         YK_REQUIRE(dev && out, YUUKA_ERR_INVALID_ARGUMENT, "buffer_alloc: null argument");

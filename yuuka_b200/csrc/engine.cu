@@ -875,12 +875,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             const int base = c.kv_heads * qtiles * batch;
             // about one CTA per SM at capacity (measured at a 1500-token context: 3.11 ms per step, against 3.16 with
             // two or four per SM: fewer partials for the merge kernel outweigh the shorter key ranges)
-            static const int split_mult = [] {
-                const char * e = getenv("YUUKA_CUDA_ATTN_SPLIT_MULT");
-                const int v = e ? atoi(e) : 1;
-                return v < 1 ? 1 : (v > 4 ? 4 : v);
-            }();
-            int splits = (split_mult * m->dev->sm_count + base - 1) / base;
+            int splits = (m->dev->sm_count + base - 1) / base;
             int max_splits = (max_total + 31) / 32;
             if (splits > max_splits) splits = max_splits;
             if (splits < 1) splits = 1;
@@ -1211,7 +1206,6 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             }
             if (const char * e = getenv("YUUKA_CUDA_NO_FOLD_SWIGLU")) s->fold_swiglu = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_NO_PREFETCH")) s->prefetch_next = !(e[0] == '1');
-            if (const char * e = getenv("YUUKA_CUDA_PREFETCH_MB")) s->prefetch_bytes = (uint64_t)atoi(e) << 20;
             for (const LayerW & L : model->layers) {
                 for (const Tensor * t : {&L.proj, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.qk, &L.q, &L.k, &L.v, &L.o,
                                          &L.gate_up, &L.ffn_gate, &L.ffn_up, &L.ffn_down})
@@ -1351,8 +1345,10 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 s->attn_partial_floats = a > b ? a : b;
             }
             s->attn_partial = dalloc<float>(s->attn_partial_floats, s->owned, false);
-            // split-K scratch for every matrix shape of the step
-            for (int rows : {R < 32 ? R : 32, 1, R < 256 ? R : 256}) {
+            // split-K scratch for every matrix shape of the step and of a prompt pass: the register-fed route
+            // (up to 32 rows per launch), one row, and the tensor-memory route at the widest pass a launch
+            // takes (gemm_tiled_scratch_need covers every row count up to the one it is given)
+            for (int rows : {R < 32 ? R : 32, 1, R}) {
                 for (const LayerW & L : model->layers) {
                     for (const Tensor * t : {&L.q, &L.k, &L.v, &L.o, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.ffn_gate,
                                              &L.ffn_up, &L.ffn_down, &L.proj, &L.qk, &L.gate_up, &L.sh_gate, &L.sh_up,
@@ -1505,6 +1501,8 @@ yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b)
         validate_batch(s, b);
         YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_stage: the previous step has not been fetched");
         set_device(s->model->dev);
+        // staging again before a launch replaces the step; the earlier copy out of the page-locked mirror must have left it
+        if (s->staged) YK_CUDA(cudaStreamSynchronize(s->stream.s));
         stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent);
         if (b->mode == YUUKA_ACCEPT_REJECTION) {
             const int V = s->model->cfg.vocab;
@@ -1529,6 +1527,7 @@ yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b)
 yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
     return guard([&] {
         YK_REQUIRE(s && s->staged, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: no staged step");
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: the staged step is already running; fetch it first");
         set_device(s->model->dev);
         const int max_total = max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes);
         if (!s->use_graphs || s->st_mode == YUUKA_ACCEPT_REJECTION) {
@@ -1574,6 +1573,7 @@ yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes
     return guard([&] {
         YK_REQUIRE(s && s->staged && op_codes && op_times_ns && op_count, YUUKA_ERR_INVALID_ARGUMENT,
                    "verify_launch_profiled: null argument or no staged step");
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch_profiled: the staged step is already running; fetch it first");
         set_device(s->model->dev);
         s->launches = 0;
         s->profiling = true;

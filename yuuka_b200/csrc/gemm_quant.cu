@@ -5,6 +5,8 @@
 // tensor/quant.go:378-466; any dtype, any alignment) and the C ABI entry
 // points. The fast kernels read a tile-ordered copy of the matrix
 // (gemm_tiled.cu).
+#include <mutex>
+
 #include "gemm_quant.cuh"
 #include "gemm_tiled.cuh"
 #include "quant.cuh"
@@ -194,8 +196,11 @@ int launch_gemm_quant(const yuuka_device * dev, cudaStream_t stream, const GemmA
 // C ABI
 
 namespace {
-// one lazily grown scratch per device index for the kernel-level entry point
+// One lazily grown scratch per device index for the kernel-level entry point. The mutex covers its host
+// side (growing it frees and reallocates the buffers) and the launch that captures the pointers; the
+// device side is shared by every call on the device, as the header says.
 yk::GemmScratch g_scratch[16];
+std::mutex g_scratch_mutex;
 }  // namespace
 
 extern "C" yuuka_status yuuka_gemm_quant(yuuka_stream * stream, yuuka_buffer * out, uint64_t out_offset,
@@ -224,6 +229,7 @@ extern "C" yuuka_status yuuka_gemm_quant(yuuka_stream * stream, yuuka_buffer * o
                    "gemm_quant: activation and output offsets must be multiples of 16");
         yuuka_device * dev = stream->dev;
         YK_REQUIRE(dev->index >= 0 && dev->index < 16, YUUKA_ERR_UNSUPPORTED, "gemm_quant: device index out of range");
+        std::lock_guard<std::mutex> lock(g_scratch_mutex);
         GemmScratch & sc = g_scratch[dev->index];
         if (flags & YUUKA_GEMM_TILED) {
             YK_REQUIRE(tiled_supported(w_dtype, n_in), YUUKA_ERR_UNSUPPORTED,

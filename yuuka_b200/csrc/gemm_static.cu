@@ -31,7 +31,8 @@ std::mutex g_setup_mutex;
 uint64_t align256(uint64_t v) { return (v + 255) / 256 * 256; }
 
 // Once per device, with that device current: the array's address on this device,
-// and zeros in the counters (the kernels leave them at zero after every launch).
+// zeros in the counters (the kernels leave them at zero after every launch), and
+// the code of every kernel the entry point can launch brought onto the device.
 unsigned char * static_scratch_base(const yuuka_device * dev) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     StaticSetup & st = g_setup[dev->index];
@@ -43,6 +44,9 @@ unsigned char * static_scratch_base(const yuuka_device * dev) {
                cudaGetErrorString(err));
     YK_REQUIRE(((uintptr_t)ptr & 255) == 0, YUUKA_ERR_INTERNAL, "gemm_quant_static: scratch array is not 256-byte aligned");
     YK_CUDA(cudaMemset(ptr, 0, STATIC_COUNTER_BYTES));
+    // every kernel the routes below can pick is loaded now: with lazy module loading the driver would
+    // otherwise place a kernel's code in device memory at its first launch, in the middle of serving
+    yk::gemm_tiled_preload_kernels();
     YK_CUDA(cudaDeviceSynchronize());
     st.base = (unsigned char *)ptr;
     st.ready = true;

@@ -631,7 +631,6 @@ struct TParams {
     // while this kernel drains and the small kernels in between run
     const uint8_t * next_w;
     uint32_t next_lines;  // 128-byte lines
-    int dbg_id;           // launch id for the YK_GEMM_TIMING stamps
 };
 
 // 1 / rms of a row from its fixed-point sum of squares (2^-24 units). rmsNorm (model/qwen35/forward.go:
@@ -647,40 +646,6 @@ __device__ __forceinline__ unsigned long long nf_fixed(float v) { return (unsign
 // silu(g) * u with the expression of silu_mul_kernel (elementwise.cu), so both forms give the same bits
 __device__ __forceinline__ float swiglu(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-// Development aid, compiled out by default: with -DYK_GEMM_TIMING=1 thread 0 of every CTA folds %globaltimer
-// stamps of five points of the kernel into a per-launch row (min of the first, max of the others), and
-// yuuka_debug_gemm_stamps copies the rows out. Launch ids count up from the last reset.
-#ifndef YK_GEMM_TIMING
-#define YK_GEMM_TIMING 0
-#endif
-#if YK_GEMM_TIMING
-__device__ unsigned long long g_gemm_stamps[1024][8];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// (rows 512..1023 double as per-CTA stamps of the two launches named by g_stamp_targets: row 512 + CTA index,
-// columns 0..3 for the first, 4..7 for the second)
-__device__ int g_stamp_targets[2];
-__device__ __forceinline__ void cta_stamp(int id, int slot) {
-    const int k = id == g_stamp_targets[0] ? 10 : (id == g_stamp_targets[1] ? 11 : 0);
-    if ((k == 10 || k == 11) && (slot == 1 || slot == 3 || slot == 4 || slot == 6)) {
-        const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-        const int col = (slot == 1 ? 0 : slot == 3 ? 1 : slot == 4 ? 2 : 3) + (k == 11 ? 4 : 0);
-        if (cta < 512) {
-            g_gemm_stamps[512 + cta][col] = gtime();
-            if (slot == 1) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); g_gemm_stamps[512 + cta][col] |= (unsigned long long)sm << 56; }
-        }
-    }
-}
-#define YK_STAMP_MIN(slot) do { if (threadIdx.x == 0) atomicMin(&g_gemm_stamps[p.dbg_id & 511][slot], gtime()); } while (0)
-#define YK_STAMP_MAX(slot) do { if (threadIdx.x == 0) { atomicMax(&g_gemm_stamps[p.dbg_id & 511][slot], gtime()); cta_stamp(p.dbg_id, slot); } } while (0)
-#else
-#define YK_STAMP_MIN(slot) do { } while (0)
-#define YK_STAMP_MAX(slot) do { } while (0)
-#endif
-
 // GROUPED: blockIdx.z walks a device-built list of row segments, each bound to one expert's matrix
 // (qwen35moe expert FFNs). A segment's rows are contiguous in the prepared-activation and output
 // arrays unless row_index redirects the activation rows.
@@ -692,8 +657,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t xbar;
     __shared__ int last_flag;
-    YK_STAMP_MIN(0);
-    YK_STAMP_MAX(1);
     // folded norm: per input row scale / pre (consumer) and pre (producer); per warp the norm weights
     // of its row tile, fetched at the top of each group so that the epilogue does not wait on memory
     __shared__ float cs_s[FOLD ? 32 : 1], pre_s[FOLD ? 32 : 1], nw_s[FOLD ? 2 * TW * 16 : 1];
@@ -752,8 +715,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     }
     __syncthreads();
     pdl_wait();
-    YK_STAMP_MIN(2);
-    YK_STAMP_MAX(3);
 
     // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums,
     // every row's pair issued by its own lane of the first warp ----
@@ -806,7 +767,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         }
         if (!ok) atomicExch(&g_gemm_wait_expired, 1);
     }
-    YK_STAMP_MAX(4);
 
     uint8_t * tab = tabs + warp * C::TAB;
     const uint8_t * xrow[NT];
@@ -1044,8 +1004,6 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     }
 
     pdl_trigger_late();
-    YK_STAMP_MIN(5);
-    YK_STAMP_MAX(6);
     if (p.next_w) {
         const uint32_t first = ((blockIdx.y * gridDim.x + blockIdx.x) * (TW * 32) + threadIdx.x);
         const uint32_t step = gridDim.x * gridDim.y * (TW * 32);
@@ -1236,9 +1194,7 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
     const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
     const int slots = 2 * dev->sm_count;  // CTAs that can be resident (two per SM)
     const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
-    static const bool full_smem = [] { const char * e = getenv("YUUKA_GEMM_FULL_SMEM"); return e && e[0] == '1'; }();
-    const size_t budget = full_smem ? dev->prop.sharedMemPerBlockOptin - 1024
-                                    : (half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin);
+    const size_t budget = half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin;
     // K chunks across CTAs that shared memory forces anyway (the activations of all rows must fit two CTAs per SM)
     int kc_fit = 1;
     while ((nsb + kc_fit - 1) / kc_fit > 1 && mma_smem(dtype, m, (nsb + kc_fit - 1) / kc_fit, nt, 2, paired) > budget) kc_fit++;
@@ -1263,30 +1219,15 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
             }
         }
     }
-    // YUUKA_GEMM_PLAN=ks,kchunks overrides both choices for every shape, YUUKA_GEMM_PLAN_<n_out>x<n_in>=ks,kchunks
-    // for one (experiments; kchunks still grows until shared memory fits)
-    int forced_ks = 0, forced_kc = 0;
-    {
-        char name[64];
-        snprintf(name, sizeof name, "YUUKA_GEMM_PLAN_%dx%d", n_out, n_in);
-        const char * e = getenv(name);
-        if (!e) e = getenv("YUUKA_GEMM_PLAN");
-        if (e) {
-            forced_ks = atoi(e);
-            const char * c = strchr(e, ',');
-            forced_kc = c ? atoi(c + 1) : 0;
-        }
-    }
-    if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || (forced_ks == 8 && !paired)) ks = forced_ks;
     pl.KS = ks;
     pl.TG = TW / ks;
     pl.n_groups = (n_tiles + pl.TG - 1) / pl.TG;
     // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
-    int kchunks = forced_kc > 0 ? forced_kc : 1;
+    int kchunks = 1;
     while (true) {
         int nsb_chunk = (nsb + kchunks - 1) / kchunks;
         bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks, paired) <= budget;
-        bool enough = forced_kc > 0 || pl.n_groups * kchunks >= slots / 2 || nsb_chunk < 2 * ks || nsb_chunk <= 2;
+        bool enough = pl.n_groups * kchunks >= slots / 2 || nsb_chunk < 2 * ks || nsb_chunk <= 2;
         if (fits && enough) break;
         if (nsb_chunk == 1) break;
         kchunks++;
@@ -1319,18 +1260,17 @@ static int umma_ksplit(const yuuka_device * dev, int n_out, int n_in, int rows, 
     int ks = dev->sm_count / n_blocks;
     if (ks > nsb / 2) ks = nsb / 2;
     if (separate) *separate = false;
-    static const int forced = [] { const char * e = getenv("YUUKA_CUDA_UMMA_KSPLIT"); return e ? atoi(e) : 0; }();
     static const bool no_separate = [] { const char * e = getenv("YUUKA_CUDA_UMMA_INLINE_SUM"); return e && e[0] == '1'; }();
     // The decode of a narrow matrix (20 blocks of a 2560-row one) is spread over the whole machine and the parts
     // are summed by every SM in a second launch; the output must allow 16-byte stores. Measured on 2560 x 9216
     // against the in-kernel sum below: 38 vs 53-62 us at 48-96 rows, 59 vs 192 us at 512.
-    if (separate && forced == 0 && !no_separate && ks > 2 && (n_out & 3) == 0 && umma_specialised()) {
+    if (separate && !no_separate && ks > 2 && (n_out & 3) == 0 && umma_specialised()) {
         *separate = true;
         return ks < 8 ? ks : 8;
     }
     // the last CTA of a block sums the parts alone: measured on 2560-row matrices, four parts pay up to
     // about 96 activation rows and two beyond (the sum grows with rows x parts, the decode it hides does not)
-    const int cap = forced > 0 ? forced : (rows <= 96 ? 4 : 2);
+    const int cap = rows <= 96 ? 4 : 2;
     if (ks > cap) ks = cap;
     return ks < 1 ? 1 : ks;
 }
@@ -1391,33 +1331,6 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     }
 }
 
-#if YK_GEMM_TIMING
-static int g_dbg_next = 0;
-}  // namespace yk
-// out: 1024 x 8 stamps. mode 1: clear the stamps and restart launch ids at 0; mode 2: clear the stamps only.
-extern "C" __attribute__((visibility("default"))) int yuuka_debug_gemm_targets(int a, int b) {
-    const int t[2] = {a, b};
-    return cudaMemcpyToSymbol(yk::g_stamp_targets, t, sizeof t) == cudaSuccess ? 0 : -1;
-}
-extern "C" __attribute__((visibility("default"))) int yuuka_debug_gemm_stamps(unsigned long long * out, int mode) {
-    static unsigned long long host[1024][8];
-    if (cudaMemcpyFromSymbol(host, yk::g_gemm_stamps, sizeof host) != cudaSuccess) return -1;
-    if (out) memcpy(out, host, sizeof host);
-    if (mode) {
-        for (auto & row : host) {
-            row[0] = row[2] = row[5] = ~0ull;
-            row[1] = row[3] = row[4] = row[6] = row[7] = 0;
-        }
-        for (int r = 512; r < 1024; r++)
-            for (auto & v : host[r]) v = 0;
-        if (cudaMemcpyToSymbol(yk::g_gemm_stamps, host, sizeof host) != cudaSuccess) return -1;
-        if (mode == 1) yk::g_dbg_next = 0;
-    }
-    return yk::g_dbg_next;
-}
-namespace yk {
-#endif
-
 template <int DT, int NT>
 static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
                             const TPlan & pl) {
@@ -1463,9 +1376,6 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
         p.next_w = a.next_w;
         p.next_lines = (uint32_t)(a.next_bytes / 128);
     }
-#if YK_GEMM_TIMING
-    p.dbg_id = g_dbg_next++;
-#endif
     dim3 grid(pl.grid_x, pl.kchunks);
     launch_k(kern, grid, TW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
@@ -1482,15 +1392,12 @@ static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const Gr
     pl.nsb_chunk = nsb;
     pl.smem = mma_smem(DT, GEMM_SEGMENT_ROWS, nsb, 1, 1);
     // row groups per CTA: a CTA stages a segment's activation rows once and then walks that many groups
-    // (YUUKA_GEMM_GROUPED_PER_CTA overrides the choice)
-    static const int forced_per = [] { const char * e = getenv("YUUKA_GEMM_GROUPED_PER_CTA"); return e ? atoi(e) : 0; }();
     // (enough CTAs to fill the resident slots about twice when every slot of the segment list is in use.
     // Measured on the qwen35moe shape, 160 rows, 8 layers: 3.97 ms per step with one group per CTA, 3.81 with
     // two, 3.75 with four, 3.72 with eight)
     int per = (int)((int64_t)pl.n_groups * a.max_segments / (4 * dev->sm_count));
     if (per < 1) per = 1;
     if (per > pl.n_groups) per = pl.n_groups;
-    if (forced_per > 0) per = forced_per;
     pl.grid_x = (pl.n_groups + per - 1) / per;
     const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
     YK_REQUIRE(pl.smem <= half_sm && pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
@@ -1751,6 +1658,33 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
     default: YK_REQUIRE(false, YUUKA_ERR_UNSUPPORTED, "gemm: dtype %u has no tiled kernels", a.w_dtype);
     }
     return 0;
+}
+
+// Loads the code of every kernel launch_gemm_tiled can choose. With CUDA's lazy module loading the first
+// launch of a kernel makes the driver place its code in device memory; asking for the attributes does the
+// same ahead of time, so that a caller who must not allocate later (yuuka_gemm_quant_static) pays here.
+template <int DT>
+static void preload_dt() {
+    cudaFuncAttributes fa;
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 1, false, false>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 2, false, false>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 4, false, false>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_fp32_kernel<DT, float>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_fp32_kernel<DT, __nv_bfloat16>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_umma_ws_kernel<DT>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_umma_kernel<DT, true>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_umma_kernel<DT, false>));
+}
+void gemm_tiled_preload_kernels() {
+    cudaFuncAttributes fa;
+    preload_dt<YUUKA_DTYPE_Q4_K>();
+    preload_dt<YUUKA_DTYPE_Q5_K>();
+    preload_dt<YUUKA_DTYPE_Q6_K>();
+    preload_dt<YUUKA_DTYPE_Q8_0>();
+    YK_CUDA(cudaFuncGetAttributes(&fa, xprep_kernel<float>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, xprep_kernel<__nv_bfloat16>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, umma_reduce_kernel));
+    tensor_map_encoder();  // the driver entry point look-up happens once, here
 }
 
 int read_gemm_wait_expired() {

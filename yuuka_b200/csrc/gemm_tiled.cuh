@@ -103,6 +103,9 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
 void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int rows, int n_out, int n_in,
                              uint64_t * partial_floats, int * counters);
 
+// Makes the driver load the code of every kernel launch_gemm_tiled can launch (the current device).
+void gemm_tiled_preload_kernels();
+
 // Non-zero once a bounded wait inside a GEMM kernel has expired (sticky).
 int read_gemm_wait_expired();
 void enqueue_gemm_wait_expired_read(cudaStream_t stream, int * out);

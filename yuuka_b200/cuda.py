@@ -100,6 +100,7 @@ SIGNATURES = {
     "yuuka_device_open": (_i32, [_i32, _vp]),
     "yuuka_device_close": (None, [_vp]),
     "yuuka_device_info_get": (_i32, [_vp, _vp]),
+    "yuuka_device_memory_get": (_i32, [_vp, _vp, _vp]),
     "yuuka_buffer_alloc": (_i32, [_vp, _u64, _vp]),
     "yuuka_buffer_free": (None, [_vp]),
     "yuuka_buffer_size": (_u64, [_vp]),
@@ -218,6 +219,12 @@ class Device:
         info = DeviceInfo()
         check(lib().yuuka_device_info_get(self.h, C.byref(info)))
         return info
+
+    def memory(self) -> tuple[int, int]:
+        """(free, total) bytes of device memory right now."""
+        free, total = C.c_uint64(), C.c_uint64()
+        check(lib().yuuka_device_memory_get(self.h, C.byref(free), C.byref(total)))
+        return free.value, total.value
 
     def alloc(self, nbytes: int) -> "Buffer":
         return Buffer(self, nbytes)
