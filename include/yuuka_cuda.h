@@ -275,7 +275,15 @@ typedef struct yuuka_session_config {
     int32_t pool_blocks;   /* 0 = max_batch * ceil(capacity / block_size) */
     int32_t kv_format;     /* yuuka_kv_format */
     int32_t want_logits;   /* keep f32 logits [max_batch*max_nodes, vocab] for download */
+    uint32_t flags;        /* YUUKA_SESSION_* */
 } yuuka_session_config;
+/* Steps and prompt passes of 48 rows or more normally take the tensor-memory GEMM route, which rounds
+ * the decoded weights and the activations to fp16 (about 1e-3 relative per product; logits of a deep
+ * model then sit around 1e-2 of the fp32 CPU path, and a qwen35moe router may pick another expert at a
+ * near-tie). With this flag such passes run as 16-row passes of the register-fed route instead, which
+ * multiplies exact integer weights with two-half activations (fp32-level results, weights streamed once
+ * per 16 rows). */
+#define YUUKA_SESSION_EXACT_WIDE 0x1u
 
 YUUKA_API yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_config * cfg,
                                             yuuka_session ** out);

@@ -180,13 +180,16 @@ def test_tree_step_matches_oracle(geo):
 
 def test_batched_trees_with_permuted_block_tables(geo):
     """Four sequences x 16-row trees = 64 query rows per KV head (the widest attention tile) over permuted
-    block tables, contexts of different lengths, a different accepted branch in every sequence."""
+    block tables, contexts of different lengths, a different accepted branch in every sequence. 64 rows would
+    take the tensor-memory GEMM route with its fp16-rounded weights; the session asks for the exact route so
+    that every deciding row is clear of the logit error."""
     cfg, gm, om = geo
     V, B, cap, bs = cfg["vocab"], 4, 96, 16
     per = cap // bs
     parent = synth.tree_16()[:16].copy()
     N = parent.size
-    sess = cuda.Session(gm, max_batch=B, max_nodes=N, capacity=cap, kv_format=cuda.KV_F16, block_size=bs)
+    sess = cuda.Session(gm, max_batch=B, max_nodes=N, capacity=cap, kv_format=cuda.KV_F16, block_size=bs,
+                        flags=cuda.SESSION_EXACT_WIDE)
     perm = np.random.default_rng(13).permutation(B * per).astype(np.int32)
     tokens = np.zeros((B, N), np.int32)
     states = []
@@ -318,7 +321,10 @@ def test_rejection_walk_on_scaled_logits_full_vocabulary():
 
 def test_moe_block_with_256_experts_top_8():
     """32 sequences x 5-row chains = 160 rows through a two-layer qwen35moe model with 256 routed experts,
-    8 used, plus the shared expert."""
+    8 used, plus the shared expert. The router picks experts by comparing logits, so a row whose eighth and
+    ninth logits are closer than the error of its input changes expert and moves far; the session therefore
+    runs the dense matrices on the exact route (the tensor-memory route's fp16 rounding flips a few per cent
+    of the rows of such a step)."""
     cfg = dict(synth.tiny_config(), block_count=2, full_attention_interval=2, ffn=0, expert_count=256, expert_used=8,
                expert_ffn=256, shared_ffn=256)
     tensors = synth.make_model(cfg, "q4_k_m", seed=45, unit_norms=False)
@@ -326,7 +332,7 @@ def test_moe_block_with_256_experts_top_8():
     gm = cuda.Model(dev, cfg, tensors)
     om = yo.Model(cfg, tensors)
     V, B, N = cfg["vocab"], 32, 5
-    sess = cuda.Session(gm, max_batch=B, max_nodes=N, capacity=64, kv_format=cuda.KV_F16)
+    sess = cuda.Session(gm, max_batch=B, max_nodes=N, capacity=64, kv_format=cuda.KV_F16, flags=cuda.SESSION_EXACT_WIDE)
     tokens = np.zeros((B, N), np.int32)
     states = []
     for b in range(B):
@@ -344,7 +350,7 @@ def test_moe_block_with_256_experts_top_8():
         err = float(np.max(np.abs(res.logits[b] - log_o)))
         worst = max(worst, err)
         assert err <= LOGIT_TOL and cosine(res.logits[b], log_o) >= 0.9999, (b, err)
-        if float(top2_gap(log_o[:acc_o + 1]).min()) >= 1e-3:
+        if decisive(float(top2_gap(log_o[:acc_o + 1]).min()), err):
             assert int(res.accepted[b]) == acc_o
             assert res.emitted[b, :acc_o + 1].tolist() == em_o.tolist()
             assert sess.position(b) == states[b].pos

@@ -559,7 +559,7 @@ __global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) attention_merge_ker
         }
         if ((tid & 3) == 0 && has_dims) {
             const int cols = heads * HD, gq = head * (HD / 16) + (tid >> 2);
-            xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+            xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xl + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
         }
     }
 }

@@ -65,7 +65,7 @@ __device__ void rmsnorm_row(float * __restrict__ dst_row, const float * __restri
             float4 * d = reinterpret_cast<float4 *>(dst_row + gq * 16);
 #pragma unroll
             for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+            if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xl + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
         }
     } else {
         for (int i = threadIdx.x; i < cols; i += blockDim.x) dst_row[i] = x[i] * scale * weight[i];
@@ -193,7 +193,7 @@ __global__ void silu_mul_kernel(float * __restrict__ act, int lda, const float *
         float4 * d = reinterpret_cast<float4 *>(act + (int64_t)r * lda + gq * 16);
 #pragma unroll
         for (int i = 0; i < 4; i++) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
+        if (prep.xh) xprep_store16(prep.xh + (int64_t)r * cols + gq * 16, prep.xl + (int64_t)r * cols + gq * 16, prep.xs16 + (int64_t)r * (cols >> 4) + gq, v);
     }
 }
 

@@ -627,6 +627,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.path = YUUKA_GEMM_PATH_AUTO;
         t.flags = flags;
         t.scratch = &s->gemm;
+        t.exact_only = (s->cfg.flags & YUUKA_SESSION_EXACT_WIDE) != 0;
         if (swiglu) t.swiglu = *swiglu;
         if (s->fold_step) {
             const yuuka_model_config & mc = s->model->cfg;
@@ -822,6 +823,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
                     gk.out = g.out + r0 * inner;
                     if (g.prep.xh) {
                         gk.prep.xh = g.prep.xh + r0 * inner;
+                        gk.prep.xl = g.prep.xl + r0 * inner;
                         gk.prep.xs16 = g.prep.xs16 + r0 * (inner / 16);
                     }
                     gk.qn = g.qn + r0 * key_dim;
@@ -899,6 +901,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
                     XPrepOut pk = s->prep_attn;
                     if (pk.xh) {
                         pk.xh += r0 * o_dim;
+                        pk.xl += r0 * o_dim;
                         pk.xs16 += r0 * (o_dim / 16);
                     }
                     s->launches += 1 + launch_attention(st, s->attn_out + r0 * o_dim, o_dim, qb + r0 * nq, nq, c.heads, c.kv_heads,
@@ -1185,6 +1188,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
         if (sc.pool_blocks <= 0) sc.pool_blocks = per_seq * sc.max_batch;
         YK_REQUIRE(sc.kv_format == YUUKA_KV_F32 || sc.kv_format == YUUKA_KV_F16 || sc.kv_format == YUUKA_KV_Q8_0,
                    YUUKA_ERR_INVALID_ARGUMENT, "unknown KV format %d", sc.kv_format);
+        YK_REQUIRE((sc.flags & ~YUUKA_SESSION_EXACT_WIDE) == 0, YUUKA_ERR_INVALID_ARGUMENT, "unknown session flags 0x%x", sc.flags);
         set_device(model->dev);
         auto * s = new yuuka_session();
         try {
@@ -1293,6 +1297,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 XPrepOut o;
                 if (width % 16 == 0) {
                     o.xh = dalloc<__half>((size_t)R * width, s->owned);
+                    o.xl = dalloc<__half>((size_t)R * width, s->owned);
                     o.xs16 = dalloc<__half2>((size_t)R * (width / 16) + 4, s->owned);
                 }
                 return o;
@@ -1321,8 +1326,10 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 YK_REQUIRE(c.expert_ffn % 16 == 0 && c.shared_ffn % 16 == 0, YUUKA_ERR_UNSUPPORTED,
                            "expert feed-forward sizes must be multiples of 16");
                 s->prep_moe_act.xh = dalloc<__half>(P * c.expert_ffn, s->owned);
+                s->prep_moe_act.xl = dalloc<__half>(P * c.expert_ffn, s->owned);
                 s->prep_moe_act.xs16 = dalloc<__half2>(P * (c.expert_ffn / 16) + 4, s->owned);
                 s->prep_sh_act.xh = dalloc<__half>((size_t)R * c.shared_ffn, s->owned);
+                s->prep_sh_act.xl = dalloc<__half>((size_t)R * c.shared_ffn, s->owned);
                 s->prep_sh_act.xs16 = dalloc<__half2>((size_t)R * (c.shared_ffn / 16) + 4, s->owned);
             }
             if (sc.want_logits) s->logits = dalloc<float>((size_t)R * c.vocab, s->owned);

@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + c0);
 #pragma unroll
         for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
-        if (a.prep.xh) xprep_store16(a.prep.xh + r * inner + c0, a.prep.xs16 + r * (inner >> 4) + (c0 >> 4), g16);
+        if (a.prep.xh) xprep_store16(a.prep.xh + r * inner + c0, a.prep.xl + r * inner + c0, a.prep.xs16 + r * (inner >> 4) + (c0 >> 4), g16);
     }
 }
 

@@ -145,11 +145,14 @@ void gemm_scratch_reserve(const yuuka_device * dev, GemmScratch & s, uint32_t w_
     const uint64_t xneed = tiled_supported(w_dtype, n_in) ? (uint64_t)rows * n_in : 0;
     if (xneed > s.xh_elems) {
         if (s.xh) cudaFree(s.xh);
+        if (s.xl) cudaFree(s.xl);
         if (s.xs16) cudaFree(s.xs16);
         s.xh = nullptr;
+        s.xl = nullptr;
         s.xs16 = nullptr;
         s.xh_elems = 0;
         cudaError_t err = cudaMalloc(&s.xh, xneed * sizeof(__half));
+        if (err == cudaSuccess) err = cudaMalloc(&s.xl, xneed * sizeof(__half));
         if (err == cudaSuccess) err = cudaMalloc(&s.xs16, xneed / 16 * sizeof(__half2) + 16);
         YK_REQUIRE(err == cudaSuccess, YUUKA_ERR_ALLOCATION, "gemm activation scratch allocation failed");
         s.xh_elems = xneed;
@@ -169,6 +172,7 @@ void gemm_scratch_free(GemmScratch & s) {
     if (s.partial) cudaFree(s.partial);
     if (s.counters) cudaFree(s.counters);
     if (s.xh) cudaFree(s.xh);
+    if (s.xl) cudaFree(s.xl);
     if (s.xs16) cudaFree(s.xs16);
     s = GemmScratch();
 }

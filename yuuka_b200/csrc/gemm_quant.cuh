@@ -13,6 +13,7 @@ struct GemmScratch {
     int * counters = nullptr;    // one arrival counter per tile group, zero between launches
     int counter_count = 0;
     __half * xh = nullptr;       // prepared activations of a launch whose caller passed f32 / bf16
+    __half * xl = nullptr;
     __half2 * xs16 = nullptr;
     uint64_t xh_elems = 0;
 };

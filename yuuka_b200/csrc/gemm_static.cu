@@ -83,13 +83,13 @@ extern "C" yuuka_status yuuka_gemm_quant_static(yuuka_stream * stream, yuuka_buf
         yuuka_device * dev = stream->dev;
         YK_REQUIRE(dev->index >= 0 && dev->index < 16, YUUKA_ERR_UNSUPPORTED, "gemm_quant_static: device index out of range");
 
-        // carve the fixed array: counters | xh | xs16 | split-K partial sums
+        // carve the fixed array: counters | xh | xl | xs16 | split-K partial sums
         uint64_t partial_floats = 0;
         int counters = 0;
         gemm_tiled_scratch_need(dev, w_dtype, (int)rows, (int)n_out, (int)n_in, &partial_floats, &counters);
         const uint64_t xh_bytes = align256(rows * n_in * sizeof(__half));
         const uint64_t xs_bytes = align256(rows * n_in / 16 * sizeof(__half2) + 16);
-        const uint64_t need = STATIC_COUNTER_BYTES + xh_bytes + xs_bytes + align256(partial_floats * sizeof(float));
+        const uint64_t need = STATIC_COUNTER_BYTES + 2 * xh_bytes + xs_bytes + align256(partial_floats * sizeof(float));
         YK_REQUIRE((uint64_t)counters * sizeof(int) <= STATIC_COUNTER_BYTES && need <= YUUKA_GEMM_STATIC_SCRATCH_BYTES,
                    YUUKA_ERR_UNSUPPORTED,
                    "gemm_quant_static: rows=%llu n_out=%llu n_in=%llu needs %llu bytes of scratch (%d counters), the fixed "
@@ -103,10 +103,11 @@ extern "C" yuuka_status yuuka_gemm_quant_static(yuuka_stream * stream, yuuka_buf
         sc.counters = (int *)base;
         sc.counter_count = (int)(STATIC_COUNTER_BYTES / sizeof(int));
         sc.xh = (__half *)(base + STATIC_COUNTER_BYTES);
-        sc.xs16 = (__half2 *)(base + STATIC_COUNTER_BYTES + xh_bytes);
+        sc.xl = (__half *)(base + STATIC_COUNTER_BYTES + xh_bytes);
+        sc.xs16 = (__half2 *)(base + STATIC_COUNTER_BYTES + 2 * xh_bytes);
         sc.xh_elems = rows * n_in;
-        sc.partial = (float *)(base + STATIC_COUNTER_BYTES + xh_bytes + xs_bytes);
-        sc.partial_floats = (YUUKA_GEMM_STATIC_SCRATCH_BYTES - STATIC_COUNTER_BYTES - xh_bytes - xs_bytes) / sizeof(float);
+        sc.partial = (float *)(base + STATIC_COUNTER_BYTES + 2 * xh_bytes + xs_bytes);
+        sc.partial_floats = (YUUKA_GEMM_STATIC_SCRATCH_BYTES - STATIC_COUNTER_BYTES - 2 * xh_bytes - xs_bytes) / sizeof(float);
 
         TiledGemmArgs t;
         t.w = (const uint8_t *)w->ptr + w_offset;

@@ -31,7 +31,9 @@
 
 namespace yk {
 
-constexpr int TW = 8;            // warps per CTA
+constexpr int TW = 8;            // warps per CTA (fp32 kernel, tensor-memory kernels)
+constexpr int MW = 16;           // warps per CTA of the register-fed mma kernel: one CTA per SM
+constexpr int MMA_ROWS = 16;     // activation rows per launch of that kernel (two product columns each)
 constexpr uint32_t H2_1024 = 0x64006400u;
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4 * p) {
@@ -116,7 +118,9 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 * src, float (&v)[8]) 
 // the four lanes t that share a weight row: lane t holds elements 32k + 8t + b,
 // b = 0..7, i.e. MMA (k, h) takes elements 32k + 8t + 4h + {0,1,2,3} from lane
 // t. Activations therefore stay in natural order: the B fragments of MMAs
-// (k,0) and (k,1) are the 16 bytes x[32k + 8t .. 32k + 8t + 7]. A 4-byte weight
+// (k,0) and (k,1) are the 16 bytes x[32k + 8t .. 32k + 8t + 7]. (Q6_K: lane t
+// holds 32k + 4t + b and 32k + 16 + 4t + b, b = 0..3, see pos6; its B fragments
+// are the 8 bytes at x[32k + 16h + 4t].) A 4-byte weight
 // word stores its four elements in byte order (0, 2, 1, 3) so that the masks
 // 0x000f000f / (>>8) give the (k-lo, k-hi) halves of an A fragment directly.
 //
@@ -129,6 +133,11 @@ __device__ __forceinline__ int elem_in_chunk8(int c8) {  // byte position 0..7 o
     const int h = c8 >> 2, pos = c8 & 3;
     return 4 * h + ((pos & 1) * 2 + (pos >> 1));  // pos 0,1,2,3 -> element 0,2,1,3
 }
+// Q6_K only: which of the 32 positions of a sub-block element b (0..7) of lane t is. Q6_K scales cover 16
+// elements, so the first four elements of every lane come from the sub-block's first half and the last four
+// from its second half: MMA (k, h) then multiplies exactly the 16-element group 2k + h, whose scale is
+// applied to the product afterwards, in fp32. (The other types scale per 32 elements: position 8t + b.)
+__device__ __forceinline__ int pos6(int t, int b) { return b < 4 ? 4 * t + b : 16 + 4 * t + (b - 4); }
 
 template <> struct Codec<YUUKA_DTYPE_Q4_K> {
     static constexpr int SB = 144, REC = 16 * SB;
@@ -183,11 +192,11 @@ template <> struct Codec<YUUKA_DTYPE_Q6_K> {
         if (p < 2048) {
             const int q = p >> 4, c16 = p & 15, i = q >> 5, lane = q & 31, g = lane >> 2, t = lane & 3;
             r = g + 8 * (i >> 1);
-            o = 64 * (i & 1) + 32 * (c16 >> 3) + 8 * t + elem_in_chunk8(c16 & 7);
+            o = 64 * (i & 1) + 32 * (c16 >> 3) + pos6(t, elem_in_chunk8(c16 & 7));
         } else if (p < 3072) {
             const int q = (p - 2048) >> 4, c16 = p & 15, lane = q & 31, g = lane >> 2, t = lane & 3;
             r = g + 8 * (q >> 5);
-            o = 128 + 32 * (c16 >> 3) + 8 * t + elem_in_chunk8(c16 & 7);
+            o = 128 + 32 * (c16 >> 3) + pos6(t, elem_in_chunk8(c16 & 7));
         } else if (p < 3328) { r = (p - 3072) >> 4; o = 192 + (p & 15); }
         else { r = (p - 3328) >> 1; o = 208 + (p & 1); }
     }
@@ -268,7 +277,7 @@ void launch_tile_weights(cudaStream_t s, uint8_t * dst, const uint8_t * src, uin
 // only this form; row-wise producer kernels can emit it directly.
 
 template <typename XT>
-__global__ void xprep_kernel(__half * __restrict__ xh, __half2 * __restrict__ xs16, const XT * __restrict__ x, int64_t ldx,
+__global__ void xprep_kernel(__half * __restrict__ xh, __half * __restrict__ xl, __half2 * __restrict__ xs16, const XT * __restrict__ x, int64_t ldx,
                              int K, int M) {
     const int groups = K >> 4;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * groups; i += gridDim.x * blockDim.x) {
@@ -276,14 +285,14 @@ __global__ void xprep_kernel(__half * __restrict__ xh, __half2 * __restrict__ xs
         float v[16];
         load8(x + (int64_t)m * ldx + gq * 16, *reinterpret_cast<float(*)[8]>(v));
         load8(x + (int64_t)m * ldx + gq * 16 + 8, *reinterpret_cast<float(*)[8]>(v + 8));
-        xprep_store16(xh + (int64_t)m * K + gq * 16, xs16 + (int64_t)m * groups + gq, v);
+        xprep_store16(xh + (int64_t)m * K + gq * 16, xl + (int64_t)m * K + gq * 16, xs16 + (int64_t)m * groups + gq, v);
     }
 }
 
 template <typename XT>
-static void launch_xprep(cudaStream_t s, __half * xh, __half2 * xs16, const XT * x, int64_t ldx, int K, int M) {
+static void launch_xprep(cudaStream_t s, __half * xh, __half * xl, __half2 * xs16, const XT * x, int64_t ldx, int K, int M) {
     const int total = M * (K / 16);
-    xprep_kernel<XT><<<(total + 127) / 128, 128, 0, s>>>(xh, xs16, x, ldx, K, M);
+    xprep_kernel<XT><<<(total + 127) / 128, 128, 0, s>>>(xh, xl, xs16, x, ldx, K, M);
     YK_CUDA(cudaGetLastError());
 }
 
@@ -311,18 +320,6 @@ __device__ __forceinline__ void header_k4(const uint4 & hdr, int lane, uint8_t *
     }
 }
 
-// One MMA adding  sum_s16 A[row][s16] * xsum[tok][s16]  for eight 16-element groups base..base+7.
-// a_* are the (value, value) pairs for groups base+t and base+t+4 of rows g and g+8.
-template <int NT>
-__device__ __forceinline__ void sum_mma(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int t, int s16_base,
-                                        const uint8_t * const (&xsrow)[NT], float (&acc)[NT][4]) {
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-        const uint32_t * xs = reinterpret_cast<const uint32_t *>(xsrow[j]) + s16_base;
-        mma16816(acc[j], a0, a1, a2, a3, xs[t], xs[t + 4]);
-    }
-}
-
 // Bit masks and the fp16 "1024" pattern as run-time values (kernel parameters). A LOP3 takes one
 // immediate only; with two compile-time constants in (v & mask) | 0x6400'6400 the compiler emits two
 // instructions per weight pair, with values it cannot see through it emits one.
@@ -342,59 +339,15 @@ inline DecodeConsts decode_consts(uint32_t dtype) {
     return c;
 }
 
-#ifndef YK_GEMM_RUNTIME_CONSTS
-#define YK_GEMM_RUNTIME_CONSTS 1
-#endif
+// ---------------------------------------------------------------------------
+// Scaled decode (tensor-memory route, gemm_umma.cuh): block headers become per-warp tables of fp16
+// scales with which a packed weight turns into fp16(s * q) by one LOP3 and one fma.f16x2.
 
 template <int DT, int NT> struct Mma;
 
 template <int NT> struct Mma<YUUKA_DTYPE_Q4_K, NT> {
     using C = Codec<YUUKA_DTYPE_Q4_K>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4<C>(r.hdr, lane, tab); }
-    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
-        const int g = lane >> 2, t = lane & 3;
-        const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
-#pragma unroll
-        for (int jj = 0; jj < 2; jj++) {
-            const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
-            const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
-#pragma unroll
-            for (int jl = 0; jl < 2; jl++) {
-                const int j = 2 * jj + jl;
-                const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
-#pragma unroll
-                for (int n = 0; n < 2; n++) {
-                    const uint32_t mask = n ? kc.mf0 : kc.m0f;
-                    const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
-                    uint32_t a[2][4];
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
-                        a[h][0] = h2_fma(and_or(vg, mask, kc.magic), s_g, c_g);
-                        a[h][1] = h2_fma(and_or(vh, mask, kc.magic), s_h, c_h);
-                        a[h][2] = h2_fma(and_or(vg >> 8, mask, kc.magic), s_g, c_g);
-                        a[h][3] = h2_fma(and_or(vh >> 8, mask, kc.magic), s_h, c_h);
-                    }
-                    const int k = 2 * j + n;
-#pragma unroll
-                    for (int jt = 0; jt < NT; jt++) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
-                        mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                        mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-                    }
-                }
-            }
-        }
-        // - min * sum(x): 16-element groups s16 belong to sub-block s16 / 2
-        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
-        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int k0 = 4 * half + (t >> 1);
-            sum_mma<NT>(mg[k0], mh[k0], mg[k0 + 2], mh[k0 + 2], t, sbl * 16 + 8 * half, xsrow, acc);
-        }
-    }
 };
 
 template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
@@ -416,41 +369,6 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q5_K, NT> {
         a[1] = h2_fma(and_or(vh, mask, hibit<K, tgt, false>(hh, bit, kc.magic)), s_h, c_h);
         a[2] = h2_fma(and_or(vg >> 8, mask, hibit<K, tgt, true>(hg, bit, kc.magic)), s_g, c_g);
         a[3] = h2_fma(and_or(vh >> 8, mask, hibit<K, tgt, true>(hh, bit, kc.magic)), s_h, c_h);
-    }
-    template <int K>
-    __device__ static void subblock(const typename C::Regs & r, const uint8_t * tg, const uint8_t * th,
-                                    const uint8_t * const (&xrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
-        constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
-        const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
-        const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
-        const uint32_t hg[2] = {r.qh.x, r.qh.y}, hh[2] = {r.qh.z, r.qh.w};
-        const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
-        const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
-        uint32_t a[2][4];
-#pragma unroll
-        for (int h = 0; h < 2; h++) sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h], kc);
-#pragma unroll
-        for (int jt = 0; jt < NT; jt++) {
-            const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * K) * 2);
-            mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-            mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-        }
-    }
-    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
-        const int g = lane >> 2, t = lane & 3;
-        const uint8_t * tg = tab + g * C::SCL_STRIDE, * th = tab + (g + 8) * C::SCL_STRIDE;
-        subblock<0>(r, tg, th, xrow, sbl, acc, kc); subblock<1>(r, tg, th, xrow, sbl, acc, kc);
-        subblock<2>(r, tg, th, xrow, sbl, acc, kc); subblock<3>(r, tg, th, xrow, sbl, acc, kc);
-        subblock<4>(r, tg, th, xrow, sbl, acc, kc); subblock<5>(r, tg, th, xrow, sbl, acc, kc);
-        subblock<6>(r, tg, th, xrow, sbl, acc, kc); subblock<7>(r, tg, th, xrow, sbl, acc, kc);
-        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
-        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int k0 = 4 * half + (t >> 1);
-            sum_mma<NT>(mg[k0], mh[k0], mg[k0 + 2], mh[k0 + 2], t, sbl * 16 + 8 * half, xsrow, acc);
-        }
     }
 };
 
@@ -481,55 +399,9 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q6_K, NT> {
             mn2[2 * q + 1] = h2_mul(s1, H2_NEG32);
         }
     }
-    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
-        const int g = lane >> 2, t = lane & 3;
-        const uint2 * tg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE) + (t >> 1);
-        const uint2 * th = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE) + (t >> 1);
-#pragma unroll
-        for (int n6 = 0; n6 < 2; n6++) {
-            const uint32_t lg[4] = {r.ql[n6].x, r.ql[n6].y, r.ql[n6].z, r.ql[n6].w};
-            const uint32_t lh[4] = {r.ql[2 + n6].x, r.ql[2 + n6].y, r.ql[2 + n6].z, r.ql[2 + n6].w};
-            const uint32_t hg[2] = {n6 ? r.qh[0].z : r.qh[0].x, n6 ? r.qh[0].w : r.qh[0].y};
-            const uint32_t hh[2] = {n6 ? r.qh[1].z : r.qh[1].x, n6 ? r.qh[1].w : r.qh[1].y};
-#pragma unroll
-            for (int hsel = 0; hsel < 2; hsel++) {
-                const int lsh = 4 - 2 * hsel, rsh = 4 + 2 * hsel;
-#pragma unroll
-                for (int nib = 0; nib < 2; nib++) {
-                    const int k = 4 * n6 + hsel + 2 * nib;
-                    const uint2 eg = tg[2 * k], eh = th[2 * k];
-                    const uint32_t qm = nib ? kc.mf0 : kc.m0f, hm = nib ? kc.h8 : kc.h4;
-                    uint32_t a[2][4];
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
-                        a[h][0] = h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), eg.x, eg.y);
-                        a[h][1] = h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), eh.x, eh.y);
-                        a[h][2] = h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), eg.x, eg.y);
-                        a[h][3] = h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), eh.x, eh.y);
-                    }
-#pragma unroll
-                    for (int jt = 0; jt < NT; jt++) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
-                        mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                        mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-                    }
-                }
-            }
-        }
-        const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE);
-        const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int s0 = 8 * half + t;
-            sum_mma<NT>(mg[s0], mh[s0], mg[s0 + 4], mh[s0 + 4], t, sbl * 16 + 8 * half, xsrow, acc);
-        }
-    }
 };
 
-// Q8_0: scl[row][block] = (s, s). Bytes are biased by 128 to make them unsigned, converted exactly
-// (1024 + 128 + q), the bias subtracted exactly, then scaled: one rounding per weight.
+// Q8_0: scl[row][block] = (s, s).
 template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
     using C = Codec<YUUKA_DTYPE_Q8_0>;
     __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) {
@@ -541,13 +413,310 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
         scl[2] = dup_lo(db);
         scl[3] = dup_hi(db);
     }
+};
+
+// ---------------------------------------------------------------------------
+// Exact decode (register-fed route, 3..16 activation rows per launch). The fp16 operand of the tensor core
+// holds an integer that fp16 represents exactly, and every floating-point factor of the format is applied
+// to the fp32 product afterwards, so the weights enter the sum with the value tensor/quant.go gives them:
+//   Q4_K / Q5_K  w = d * (sc * q) - dmin * m: the operand is sc * q (at most 63 * 31), summed over the whole
+//                superblock; m (at most 63) times the sums of the activations goes through one more MMA per
+//                128 columns; d and dmin multiply the two fp32 sums once per superblock;
+//   Q6_K         w = d * sc * (q - 32): the operand is q - 32; MMA (k, h) covers the 16-element group 2k + h
+//                (see pos6), whose product is multiplied by d * sc;
+//   Q8_0         w = d * q: the operand is q, the product of a 32-element block is multiplied by d.
+// Activations enter as two fp16 halves, hi + lo, in neighbouring columns of the product (about 22 bits).
+
+constexpr uint32_t H2_ONE = 0x3C003C00u;      // 1
+constexpr uint32_t H2_NEG1056 = 0xE420E420u;  // -(1024 + 32)
+constexpr uint32_t H2_NEG96 = 0xD600D600u;    // -(64 + 32)
+
+template <int DT> struct XTab;
+template <> struct XTab<YUUKA_DTYPE_Q4_K> {
+    static constexpr int SCL_STRIDE = 80, MN_STRIDE = 48, MN_OFF = 16 * SCL_STRIDE, D_OFF = MN_OFF + 16 * MN_STRIDE,
+                         TAB = D_OFF + 16 * 8;
+    static constexpr bool SUMS = true;
+    static constexpr int XT_BYTES = 16;  // bytes of activations a lane reads per sub-block and step of t
+};
+template <> struct XTab<YUUKA_DTYPE_Q5_K> : XTab<YUUKA_DTYPE_Q4_K> {};
+template <> struct XTab<YUUKA_DTYPE_Q6_K> {
+    static constexpr int DS_STRIDE = 80, TAB = 16 * DS_STRIDE;
+    static constexpr bool SUMS = false;
+    static constexpr int XT_BYTES = 8;
+};
+template <> struct XTab<YUUKA_DTYPE_Q8_0> {
+    static constexpr int DS_STRIDE = 48, TAB = 16 * DS_STRIDE;
+    static constexpr bool SUMS = false;
+    static constexpr int XT_BYTES = 16;
+};
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t bits) { return __half2float(__ushort_as_half((unsigned short)(bits & 0xffffu))); }
+
+__device__ __forceinline__ void mma16816_zero(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// Q4_K / Q5_K header: hdr.x = d | dmin << 16, hdr.y/z/w = 12 scale bytes (getScaleMinK4, tensor/quant.go:96-103).
+// scl[row][pair j] = {sc_lo, -1024 sc_lo, sc_hi / 16, -64 sc_hi} (half2 each, integers); mn2[row][sub] = (m, m);
+// dd[row] = (d, -dmin) in fp32.
+template <typename X>
+__device__ __forceinline__ void header_k4_exact(const uint4 & hdr, int lane, uint8_t * tab) {
+    const int r = lane & 15, hf = lane >> 4;  // hf: pairs 2hf, 2hf+1
+    const uint32_t w0 = hdr.y, w1 = hdr.z, w2 = hdr.w;
+    const uint32_t sc4 = hf ? ((w2 & 0x0f0f0f0fu) | ((w0 >> 2) & 0x30303030u)) : (w0 & 0x3f3f3f3fu);
+    const uint32_t mn4 = hf ? (((w2 >> 4) & 0x0f0f0f0fu) | ((w1 >> 2) & 0x30303030u)) : (w1 & 0x3f3f3f3fu);
+    uint4 * scl = reinterpret_cast<uint4 *>(tab + r * X::SCL_STRIDE) + hf * 2;
+    uint2 * mn2 = reinterpret_cast<uint2 *>(tab + X::MN_OFF + r * X::MN_STRIDE) + hf * 2;
+#pragma unroll
+    for (int jl = 0; jl < 2; jl++) {
+        const uint32_t sp = h2_sub(jl ? bytes23_h2(sc4) : bytes01_h2(sc4), H2_1024);
+        const uint32_t mp = h2_sub(jl ? bytes23_h2(mn4) : bytes01_h2(mn4), H2_1024);
+        const uint32_t slo = dup_lo(sp), shi = dup_hi(sp);
+        scl[jl] = make_uint4(slo, h2_mul(slo, H2_NEG1024), h2_mul(shi, H2_INV16), h2_mul(shi, H2_NEG64));
+        mn2[jl] = make_uint2(dup_lo(mp), dup_hi(mp));
+    }
+    if (hf == 0) reinterpret_cast<float2 *>(tab + X::D_OFF)[r] = make_float2(f16_bits_to_f32(hdr.x), -f16_bits_to_f32(hdr.x >> 16));
+}
+
+// One MMA adding  sum_s16 A[row][s16] * xsum[tok][s16]  for eight 16-element groups base..base+7.
+// a_* are the (value, value) pairs for groups base+t and base+t+4 of rows g and g+8. A column that stands for
+// the lo half of an activation row takes no part (the sums already hold hi + lo).
+template <int NT>
+__device__ __forceinline__ void sum_mma(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, int t, int s16_base,
+                                        const uint8_t * const (&xsrow)[NT], bool lo_col, float (&acc)[NT][4]) {
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        const uint32_t * xs = reinterpret_cast<const uint32_t *>(xsrow[j]) + s16_base;
+        const uint32_t b0 = lo_col ? 0u : xs[t], b1 = lo_col ? 0u : xs[t + 4];
+        mma16816(acc[j], a0, a1, a2, a3, b0, b1);
+    }
+}
+
+// acc[j][c] += dg * q[j][c] (rows g: c < 2) or dh * q[j][c] (rows g + 8)
+template <int NT>
+__device__ __forceinline__ void fold_rows(float (&acc)[NT][4], const float (&q)[NT][4], float dg, float dh) {
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        acc[j][0] = fmaf(dg, q[j][0], acc[j][0]);
+        acc[j][1] = fmaf(dg, q[j][1], acc[j][1]);
+        acc[j][2] = fmaf(dh, q[j][2], acc[j][2]);
+        acc[j][3] = fmaf(dh, q[j][3], acc[j][3]);
+    }
+}
+
+// - dmin * sum_sub m[sub] * sum(x[sub]) of one Q4_K / Q5_K superblock
+template <typename X, int NT>
+__device__ __forceinline__ void min_part(const uint8_t * tab, int g, int t, int sbl, const uint8_t * const (&xsrow)[NT], bool lo_col,
+                                         float (&acc)[NT][4], float ndmin_g, float ndmin_h) {
+    float mq[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) mq[j][c] = 0.0f;
+    const uint32_t * mg = reinterpret_cast<const uint32_t *>(tab + X::MN_OFF + g * X::MN_STRIDE);
+    const uint32_t * mh = reinterpret_cast<const uint32_t *>(tab + X::MN_OFF + (g + 8) * X::MN_STRIDE);
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int k0 = 4 * half + (t >> 1);  // 16-element group 8 half + t belongs to sub-block 4 half + t / 2
+        sum_mma<NT>(mg[k0], mh[k0], mg[k0 + 2], mh[k0 + 2], t, sbl * 16 + 8 * half, xsrow, lo_col, mq);
+    }
+    fold_rows<NT>(acc, mq, ndmin_g, ndmin_h);
+}
+
+template <int DT, int NT> struct XMma;
+
+template <int NT> struct XMma<YUUKA_DTYPE_Q4_K, NT> {
+    using C = Codec<YUUKA_DTYPE_Q4_K>;
+    using X = XTab<YUUKA_DTYPE_Q4_K>;
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4_exact<X>(r.hdr, lane, tab); }
     __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
-                               const uint8_t * const (&xsrow)[NT], int sbl, float (&acc)[NT][4], const DecodeConsts & kc) {
+                               const uint8_t * const (&xsrow)[NT], bool lo_col, int sbl, float (&acc)[NT][4],
+                               const DecodeConsts & kc) {
+        const int g = lane >> 2, t = lane & 3;
+        const float2 dg = reinterpret_cast<const float2 *>(tab + X::D_OFF)[g], dh = reinterpret_cast<const float2 *>(tab + X::D_OFF)[g + 8];
+        min_part<X, NT>(tab, g, t, sbl, xsrow, lo_col, acc, dg.y, dh.y);
+        float q[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) q[j][c] = 0.0f;
+        const uint8_t * tg = tab + g * X::SCL_STRIDE, * th = tab + (g + 8) * X::SCL_STRIDE;
+#pragma unroll
+        for (int jj = 0; jj < 2; jj++) {
+            const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+            const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
+#pragma unroll
+            for (int jl = 0; jl < 2; jl++) {
+                const int j = 2 * jj + jl;
+                const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
+#pragma unroll
+                for (int n = 0; n < 2; n++) {
+                    const uint32_t mask = n ? kc.mf0 : kc.m0f;
+                    const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+                    uint32_t a[2][4];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t vg = qg[2 * jl + h], vh = qh[2 * jl + h];
+                        a[h][0] = h2_fma(and_or(vg, mask, kc.magic), s_g, c_g);
+                        a[h][1] = h2_fma(and_or(vh, mask, kc.magic), s_h, c_h);
+                        a[h][2] = h2_fma(and_or(vg >> 8, mask, kc.magic), s_g, c_g);
+                        a[h][3] = h2_fma(and_or(vh >> 8, mask, kc.magic), s_h, c_h);
+                    }
+                    const int k = 2 * j + n;
+#pragma unroll
+                    for (int jt = 0; jt < NT; jt++) {
+                        const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
+                        mma16816(q[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                        mma16816(q[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                    }
+                }
+            }
+        }
+        fold_rows<NT>(acc, q, dg.x, dh.x);
+    }
+};
+
+template <int NT> struct XMma<YUUKA_DTYPE_Q5_K, NT> {
+    using C = Codec<YUUKA_DTYPE_Q5_K>;
+    using X = XTab<YUUKA_DTYPE_Q5_K>;
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) { header_k4_exact<X>(r.hdr, lane, tab); }
+    template <int K>
+    __device__ static void subblock(const typename C::Regs & r, const uint8_t * tg, const uint8_t * th,
+                                    const uint8_t * const (&xrow)[NT], int sbl, float (&q)[NT][4], const DecodeConsts & kc) {
+        constexpr int j = K >> 1, n = K & 1, jj = j >> 1, jl = j & 1;
+        const uint32_t qg[4] = {r.q[jj].x, r.q[jj].y, r.q[jj].z, r.q[jj].w};
+        const uint32_t qh[4] = {r.q[2 + jj].x, r.q[2 + jj].y, r.q[2 + jj].z, r.q[2 + jj].w};
+        const uint32_t hg[2] = {r.qh.x, r.qh.y}, hh[2] = {r.qh.z, r.qh.w};
+        const uint4 sg = reinterpret_cast<const uint4 *>(tg)[j], sh = reinterpret_cast<const uint4 *>(th)[j];
+        const uint32_t s_g = n ? sg.z : sg.x, c_g = n ? sg.w : sg.y, s_h = n ? sh.z : sh.x, c_h = n ? sh.w : sh.y;
+        uint32_t a[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            Mma<YUUKA_DTYPE_Q5_K, 1>::template sub<K>(qg[2 * jl + h], qh[2 * jl + h], hg[h], hh[h], s_g, c_g, s_h, c_h, a[h], kc);
+#pragma unroll
+        for (int jt = 0; jt < NT; jt++) {
+            const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * K) * 2);
+            mma16816(q[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+            mma16816(q[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+        }
+    }
+    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
+                               const uint8_t * const (&xsrow)[NT], bool lo_col, int sbl, float (&acc)[NT][4],
+                               const DecodeConsts & kc) {
+        const int g = lane >> 2, t = lane & 3;
+        const float2 dg = reinterpret_cast<const float2 *>(tab + X::D_OFF)[g], dh = reinterpret_cast<const float2 *>(tab + X::D_OFF)[g + 8];
+        min_part<X, NT>(tab, g, t, sbl, xsrow, lo_col, acc, dg.y, dh.y);
+        float q[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) q[j][c] = 0.0f;
+        const uint8_t * tg = tab + g * X::SCL_STRIDE, * th = tab + (g + 8) * X::SCL_STRIDE;
+        subblock<0>(r, tg, th, xrow, sbl, q, kc); subblock<1>(r, tg, th, xrow, sbl, q, kc);
+        subblock<2>(r, tg, th, xrow, sbl, q, kc); subblock<3>(r, tg, th, xrow, sbl, q, kc);
+        subblock<4>(r, tg, th, xrow, sbl, q, kc); subblock<5>(r, tg, th, xrow, sbl, q, kc);
+        subblock<6>(r, tg, th, xrow, sbl, q, kc); subblock<7>(r, tg, th, xrow, sbl, q, kc);
+        fold_rows<NT>(acc, q, dg.x, dh.x);
+    }
+};
+
+// Q6_K: ds[row][s16] = d * sc[s16] in fp32 (tensor/quant.go:261-285).
+template <int NT> struct XMma<YUUKA_DTYPE_Q6_K, NT> {
+    using C = Codec<YUUKA_DTYPE_Q6_K>;
+    using X = XTab<YUUKA_DTYPE_Q6_K>;
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) {
+        const int row = lane & 15, hf = lane >> 4;  // hf: groups 8hf .. 8hf+7
+        const float d = f16_bits_to_f32(r.d);
+        const uint32_t wa = hf ? r.sc.z : r.sc.x, wb = hf ? r.sc.w : r.sc.y;
+        float4 * ds = reinterpret_cast<float4 *>(tab + row * X::DS_STRIDE) + hf * 2;
+        ds[0] = make_float4(d * (float)(int8_t)(wa & 0xff), d * (float)(int8_t)((wa >> 8) & 0xff), d * (float)(int8_t)((wa >> 16) & 0xff),
+                            d * (float)(int8_t)(wa >> 24));
+        ds[1] = make_float4(d * (float)(int8_t)(wb & 0xff), d * (float)(int8_t)((wb >> 8) & 0xff), d * (float)(int8_t)((wb >> 16) & 0xff),
+                            d * (float)(int8_t)(wb >> 24));
+    }
+    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
+                               const uint8_t * const (&xsrow)[NT], bool lo_col, int sbl, float (&acc)[NT][4],
+                               const DecodeConsts & kc) {
         (void)xsrow;
+        (void)lo_col;
+        const int g = lane >> 2;
+        const float4 * dsg = reinterpret_cast<const float4 *>(tab + g * X::DS_STRIDE);
+        const float4 * dsh = reinterpret_cast<const float4 *>(tab + (g + 8) * X::DS_STRIDE);
+#pragma unroll
+        for (int n6 = 0; n6 < 2; n6++) {
+            const uint32_t lg[4] = {r.ql[n6].x, r.ql[n6].y, r.ql[n6].z, r.ql[n6].w};
+            const uint32_t lh[4] = {r.ql[2 + n6].x, r.ql[2 + n6].y, r.ql[2 + n6].z, r.ql[2 + n6].w};
+            const uint32_t hg[2] = {n6 ? r.qh[0].z : r.qh[0].x, n6 ? r.qh[0].w : r.qh[0].y};
+            const uint32_t hh[2] = {n6 ? r.qh[1].z : r.qh[1].x, n6 ? r.qh[1].w : r.qh[1].y};
+            // scales of the eight groups 8 n6 .. 8 n6 + 7 of rows g and g + 8
+            const float4 sga = dsg[2 * n6], sgb = dsg[2 * n6 + 1], sha = dsh[2 * n6], shb = dsh[2 * n6 + 1];
+            const float sgv[8] = {sga.x, sga.y, sga.z, sga.w, sgb.x, sgb.y, sgb.z, sgb.w};
+            const float shv[8] = {sha.x, sha.y, sha.z, sha.w, shb.x, shb.y, shb.z, shb.w};
+#pragma unroll
+            for (int hsel = 0; hsel < 2; hsel++) {
+                const int lsh = 4 - 2 * hsel, rsh = 4 + 2 * hsel;
+#pragma unroll
+                for (int nib = 0; nib < 2; nib++) {
+                    const int k = 4 * n6 + hsel + 2 * nib;  // sub-block; its groups are 2k and 2k + 1
+                    const uint32_t qm = nib ? kc.mf0 : kc.m0f, hm = nib ? kc.h8 : kc.h4;
+                    const uint32_t one = nib ? H2_INV16 : H2_ONE, off = nib ? H2_NEG96 : H2_NEG1056;
+                    uint32_t a[2][4];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
+                        a[h][0] = h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), one, off);
+                        a[h][1] = h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), one, off);
+                        a[h][2] = h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), one, off);
+                        a[h][3] = h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), one, off);
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int gi = 2 * (hsel + 2 * nib) + h;  // group 2k + h, counted from 8 n6
+                        const float s_g = sgv[gi], s_h = shv[gi];
+#pragma unroll
+                        for (int jt = 0; jt < NT; jt++) {
+                            const uint2 b = *reinterpret_cast<const uint2 *>(xrow[jt] + (sbl * 256 + 32 * k + 16 * h) * 2);
+                            float tmp[4];
+                            mma16816_zero(tmp, a[h][0], a[h][1], a[h][2], a[h][3], b.x, b.y);
+                            acc[jt][0] = fmaf(s_g, tmp[0], acc[jt][0]);
+                            acc[jt][1] = fmaf(s_g, tmp[1], acc[jt][1]);
+                            acc[jt][2] = fmaf(s_h, tmp[2], acc[jt][2]);
+                            acc[jt][3] = fmaf(s_h, tmp[3], acc[jt][3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+};
+
+// Q8_0: ds[row][block] = d in fp32. Bytes are biased by 128 to make them unsigned, converted exactly
+// (1024 + 128 + q) and the bias subtracted exactly.
+template <int NT> struct XMma<YUUKA_DTYPE_Q8_0, NT> {
+    using C = Codec<YUUKA_DTYPE_Q8_0>;
+    using X = XTab<YUUKA_DTYPE_Q8_0>;
+    __device__ static void header(const typename C::Regs & r, int lane, uint8_t * tab) {
+        const int row = lane & 15, hf = lane >> 4;
+        const uint32_t da = hf ? r.d.z : r.d.x, db = hf ? r.d.w : r.d.y;
+        float4 * ds = reinterpret_cast<float4 *>(tab + row * X::DS_STRIDE) + hf;
+        ds[0] = make_float4(f16_bits_to_f32(da), f16_bits_to_f32(da >> 16), f16_bits_to_f32(db), f16_bits_to_f32(db >> 16));
+    }
+    __device__ static void run(const typename C::Regs & r, int lane, const uint8_t * tab, const uint8_t * const (&xrow)[NT],
+                               const uint8_t * const (&xsrow)[NT], bool lo_col, int sbl, float (&acc)[NT][4],
+                               const DecodeConsts & kc) {
+        (void)xsrow;
+        (void)lo_col;
         (void)kc;
         const int g = lane >> 2;
-        const uint32_t * sgp = reinterpret_cast<const uint32_t *>(tab + g * C::SCL_STRIDE);
-        const uint32_t * shp = reinterpret_cast<const uint32_t *>(tab + (g + 8) * C::SCL_STRIDE);
+        const float4 * dsg = reinterpret_cast<const float4 *>(tab + g * X::DS_STRIDE);
+        const float4 * dsh = reinterpret_cast<const float4 *>(tab + (g + 8) * X::DS_STRIDE);
+        const float4 g0 = dsg[0], g1 = dsg[1], h0 = dsh[0], h1 = dsh[1];
+        const float sgv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float shv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
         for (int kk = 0; kk < 4; kk++) {
             const uint32_t qg[4] = {r.q[kk].x, r.q[kk].y, r.q[kk].z, r.q[kk].w};
@@ -555,21 +724,25 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
 #pragma unroll
             for (int kl = 0; kl < 2; kl++) {
                 const int k = 2 * kk + kl;
-                const uint32_t sg = sgp[k], sh = shp[k];
                 uint32_t a[2][4];
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const uint32_t vg = qg[2 * kl + h] ^ 0x80808080u, vh = qh[2 * kl + h] ^ 0x80808080u;
-                    a[h][0] = h2_mul(h2_sub(bytes02_h2(vg), H2_1152), sg);
-                    a[h][1] = h2_mul(h2_sub(bytes02_h2(vh), H2_1152), sh);
-                    a[h][2] = h2_mul(h2_sub(bytes13_h2(vg), H2_1152), sg);
-                    a[h][3] = h2_mul(h2_sub(bytes13_h2(vh), H2_1152), sh);
+                    a[h][0] = h2_sub(bytes02_h2(vg), H2_1152);
+                    a[h][1] = h2_sub(bytes02_h2(vh), H2_1152);
+                    a[h][2] = h2_sub(bytes13_h2(vg), H2_1152);
+                    a[h][3] = h2_sub(bytes13_h2(vh), H2_1152);
                 }
 #pragma unroll
                 for (int jt = 0; jt < NT; jt++) {
                     const uint4 b = *reinterpret_cast<const uint4 *>(xrow[jt] + (sbl * 256 + 32 * k) * 2);
-                    mma16816(acc[jt], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                    mma16816(acc[jt], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                    float tmp[4];
+                    mma16816_zero(tmp, a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                    mma16816(tmp, a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                    acc[jt][0] = fmaf(sgv[k], tmp[0], acc[jt][0]);
+                    acc[jt][1] = fmaf(sgv[k], tmp[1], acc[jt][1]);
+                    acc[jt][2] = fmaf(shv[k], tmp[2], acc[jt][2]);
+                    acc[jt][3] = fmaf(shv[k], tmp[3], acc[jt][3]);
                 }
             }
         }
@@ -589,7 +762,8 @@ struct TParams {
     DecodeConsts kc;
     const uint8_t * w;
     int N, nsb;
-    const __half * xh;      // prepared activations [M][nsb * 256]
+    const __half * xh;      // prepared activations [M][nsb * 256], hi halves
+    const __half * xl;      // lo halves
     const __half2 * xs16;   // [M][nsb * 16]
     const void * x;         // fp32 route only
     int64_t ldx;
@@ -597,7 +771,7 @@ struct TParams {
     float * out;
     int64_t ldo;
     int accumulate;
-    int TG, KS;        // row tiles per group, warps per row tile (TG * KS == TW)
+    int TG, KS;        // row tiles per group, warps per row tile (TG * KS == warps of the CTA)
     int kchunks;       // gridDim.y
     int nsb_chunk;     // superblocks per CTA-level K chunk
     int n_groups;
@@ -609,14 +783,15 @@ struct TParams {
     size_t expert_stride;
     const int32_t * row_index;
     // optional, RMSNorm folded into the GEMMs on either side of it (see NormFuse in gemm_tiled.cuh):
-    // as the producer of a residual row this launch also writes fp16(x * nf_w * pre) with its 16-column
-    // sums and adds each row's sum of squares to nf_sumsq; as the consumer of such rows it multiplies its
-    // output rows by scale / pre. pre is the previous norm's scale of the row (from *_prev), which keeps
-    // the unnormalised fp16 values near unit range.
+    // as the producer of a residual row this launch also writes x * nf_w * pre in prepared form (both
+    // halves and the 16-column sums) and adds each row's sum of squares to nf_sumsq; as the consumer of
+    // such rows it multiplies its output rows by scale / pre. pre is the previous norm's scale of the row
+    // (from *_prev), which keeps the unnormalised values near unit range.
     const float * nf_w;
     const unsigned long long * nf_prev;  // producer: sums of squares behind `pre` (null: pre = 1)
     unsigned long long * nf_sumsq;
     __half * nf_xh;
+    __half * nf_xl;
     __half2 * nf_xs16;
     const unsigned long long * cs_now;   // consumer: sums of squares of its input rows
     const unsigned long long * cs_prev;  // (null: pre = 1)
@@ -626,6 +801,7 @@ struct TParams {
     // rows 16i.., tile 2i+1: up rows 16i..). Instead of `out` the launch writes silu(gate) * up
     // (forwardFFN, model/qwen35/forward.go:295-315) in prepared form, [M][N / 2].
     __half * sw_xh;
+    __half * sw_xl;
     __half2 * sw_xs16;
     // optional: the matrix the next GEMM of the step will stream; its first bytes are asked into L2
     // while this kernel drains and the small kernels in between run
@@ -646,22 +822,37 @@ __device__ __forceinline__ unsigned long long nf_fixed(float v) { return (unsign
 // silu(g) * u with the expression of silu_mul_kernel (elementwise.cu), so both forms give the same bits
 __device__ __forceinline__ float swiglu(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
+// One value of a prepared row: both halves into q_hi / q_lo, returns hi + lo (what the sums add up).
+__device__ __forceinline__ float prep_value(float v, __half & q_hi, __half & q_lo) {
+    xprep_split(v, q_hi, q_lo);
+    return __half2float(q_hi) + __half2float(q_lo);
+}
+__device__ __forceinline__ __half2 prep_sum(float gs) {
+    const __half hi = __float2half_rn(gs);
+    return __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+}
+
+// Register-fed kernel: one CTA of MW warps per SM, at most MMA_ROWS activation rows per launch. Row m of
+// the activations occupies two columns of the tensor-core product, 2m (hi half) and 2m + 1 (lo half), which
+// land in the same lane's accumulator pair and are added before anything else happens to them.
 // GROUPED: blockIdx.z walks a device-built list of row segments, each bound to one expert's matrix
 // (qwen35moe expert FFNs). A segment's rows are contiguous in the prepared-activation and output
 // arrays unless row_index redirects the activation rows.
 // FOLD: the RMSNorm on either side of this GEMM is folded into its epilogue (TParams::nf_* / cs_*).
 template <int DT, int NT, bool GROUPED, bool FOLD>
-__global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParams p) {
+__global__ void __launch_bounds__(MW * 32, 1) gemm_tiled_mma_kernel(const TParams p) {
     using C = Codec<DT>;
-    using MM = Mma<DT, NT>;
+    using X = XTab<DT>;
+    using MM = XMma<DT, NT>;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t xbar;
     __shared__ int last_flag;
     // folded norm: per input row scale / pre (consumer) and pre (producer); per warp the norm weights
     // of its row tile, fetched at the top of each group so that the epilogue does not wait on memory
-    __shared__ float cs_s[FOLD ? 32 : 1], pre_s[FOLD ? 32 : 1], nw_s[FOLD ? 2 * TW * 16 : 1];
+    __shared__ float cs_s[FOLD ? MMA_ROWS : 1], pre_s[FOLD ? MMA_ROWS : 1], nw_s[FOLD ? 2 * MW * 16 : 1];
     const uint8_t * wbase = p.w;
     const __half * xhp = p.xh;
+    const __half * xlp = p.xl;
     const __half2 * xsp = p.xs16;
     float * outp = p.out;
     int Mrows = p.M;
@@ -678,6 +869,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (p.row_index) row_index = p.row_index + sg.row0;
         else {
             xhp += (size_t)sg.row0 * p.nsb * 256;
+            xlp += (size_t)sg.row0 * p.nsb * 256;
             xsp += (size_t)sg.row0 * p.nsb * 16;
         }
     }
@@ -686,12 +878,12 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     const int c0 = blockIdx.y * p.nsb_chunk;
     const int c1 = min(p.nsb, c0 + p.nsb_chunk);
     const int cnt = c1 - c0;
-    const int xstride = p.nsb_chunk * 512 + 64;       // bytes of fp16 activations per row (+64: bank spread)
+    const int xstride = p.nsb_chunk * 512 + 64;       // bytes of one fp16 half of a row (+64: bank spread)
     const int xsum_stride = p.nsb_chunk * 64 + 16;    // bytes of 16-element sums per row
-    uint8_t * xs = smem;
-    uint8_t * xsum = xs + (size_t)Mrows * xstride;
-    uint8_t * tabs = xsum + (((size_t)Mrows * xsum_stride + 127) / 128) * 128;
-    float * red = reinterpret_cast<float *>(tabs + TW * C::TAB);
+    uint8_t * xs = smem;                              // [2 * Mrows]: row 2m = hi half of m, row 2m + 1 = lo half
+    uint8_t * xsum = xs + (size_t)2 * Mrows * xstride;
+    uint8_t * tabs = xsum + (X::SUMS ? (((size_t)Mrows * xsum_stride + 127) / 128) * 128 : 0);
+    float * red = reinterpret_cast<float *>(tabs + MW * X::TAB);
 
     const int tile_in_group = warp / p.KS, kpart = warp - tile_in_group * p.KS;
     const int sb0 = c0 + (cnt * kpart) / p.KS, sb1 = c0 + (cnt * (kpart + 1)) / p.KS;
@@ -716,32 +908,39 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
     __syncthreads();
     pdl_wait();
 
-    // ---- activations of this K chunk: one bulk copy per row for the fp16 values and one for the sums,
-    // every row's pair issued by its own lane of the first warp ----
+    // ---- activations of this K chunk: one bulk copy per row and half, and one for the sums where the type
+    // has a "- min" term, every row's copies issued by its own lane of the first warp ----
     if (warp == 0) {
         const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
-        const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = (uint32_t)cnt * 64;
+        const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = X::SUMS ? (uint32_t)cnt * 64 : 0u;
         if (lane == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((row_bytes_x + row_bytes_s) * Mrows)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((2u * row_bytes_x + row_bytes_s) * Mrows)
                          : "memory");
         __syncwarp();
         for (int m = lane; m < Mrows; m += 32) {
             const size_t mr = row_index ? (size_t)row_index[m] : (size_t)m;
-            const __half * srcx = xhp + (mr * p.nsb + c0) * 256;
-            const __half2 * srcs = xsp + (mr * p.nsb + c0) * 16;
+            const __half * srch = xhp + (mr * p.nsb + c0) * 256;
+            const __half * srcl = xlp + (mr * p.nsb + c0) * 256;
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)m * xstride)),
-                         "l"(srcx), "r"(row_bytes_x), "r"(bar)
+                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)(2 * m) * xstride)),
+                         "l"(srch), "r"(row_bytes_x), "r"(bar)
                          : "memory");
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(xsum + (size_t)m * xsum_stride)),
-                         "l"(srcs), "r"(row_bytes_s), "r"(bar)
+                             (uint32_t)__cvta_generic_to_shared(xs + (size_t)(2 * m + 1) * xstride)),
+                         "l"(srcl), "r"(row_bytes_x), "r"(bar)
                          : "memory");
+            if constexpr (X::SUMS) {
+                const __half2 * srcs = xsp + (mr * p.nsb + c0) * 16;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 (uint32_t)__cvta_generic_to_shared(xsum + (size_t)m * xsum_stride)),
+                             "l"(srcs), "r"(row_bytes_s), "r"(bar)
+                             : "memory");
+            }
         }
     }
     if constexpr (FOLD) {
         const int m = (int)threadIdx.x - 32;  // second warp: the first issues the copies
-        if (m >= 0 && m < 32) {
+        if (m >= 0 && m < MMA_ROWS) {
             float cs = 1.0f, pre = 1.0f;
             if (m < Mrows) {
                 if (p.cs_now)
@@ -768,28 +967,25 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
         if (!ok) atomicExch(&g_gemm_wait_expired, 1);
     }
 
-    uint8_t * tab = tabs + warp * C::TAB;
+    uint8_t * tab = tabs + warp * X::TAB;
+    // column 8j + g of the product: activation row (8j + g) / 2, hi half if g is even
+    const bool lo_col = (g & 1) != 0;
     const uint8_t * xrow[NT];
     const uint8_t * xsrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; j++) {
-        const int tok = min(8 * j + g, Mrows - 1);
-        xrow[j] = xs + (size_t)tok * xstride + t * 16;
-        xsrow[j] = xsum + (size_t)tok * xsum_stride;
+        const int col = min(8 * j + g, 2 * Mrows - 1);
+        xrow[j] = xs + (size_t)col * xstride + t * X::XT_BYTES;
+        xsrow[j] = xsum + (size_t)(col >> 1) * xsum_stride;
     }
 
-#if YK_GEMM_RUNTIME_CONSTS
     const DecodeConsts kc = p.kc;
-#else
-    const DecodeConsts kc = DT == YUUKA_DTYPE_Q5_K ? DecodeConsts{0x000f000fu, 0x00f000f0u, 0x64006400u, 0x00100010u, 0x01000100u}
-                                                   : DecodeConsts{0x000f000fu, 0x00f000f0u, 0x64006400u, 0x00300030u, 0x03000300u};
-#endif
     for (; grp < p.n_groups; grp += gridDim.x) {
         const int rt = grp * p.TG + tile_in_group;
         const int rtc = min(rt, n_tiles - 1);
         const uint8_t * tile = wbase + rtc * rec_row;
         // (two copies by group parity: a warp may start its next group while others still run the split-K tail)
-        float * nw = nw_s + (FOLD ? (((grp - (int)blockIdx.x) / (int)gridDim.x) & 1) * (TW * 16) : 0);
+        float * nw = nw_s + (FOLD ? (((grp - (int)blockIdx.x) / (int)gridDim.x) & 1) * (MW * 16) : 0);
         if (FOLD && p.nf_w && lane < 16) nw[warp * 16 + lane] = rt * 16 + lane < p.N ? p.nf_w[rt * 16 + lane] : 0.0f;
         float acc[NT][4];
 #pragma unroll
@@ -811,28 +1007,40 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             }
             MM::header(cur, lane, tab);
             __syncwarp();
-            MM::run(cur, lane, tab, xrow, xsrow, sb - c0, acc, kc);
+            MM::run(cur, lane, tab, xrow, xsrow, lo_col, sb - c0, acc, kc);
             __syncwarp();
             cur = nxt;
         }
 
+        // hi + lo columns of each activation row: lane (g, t) now holds, for row 4j + t, the sums of weight
+        // rows g (vg) and g + 8 (vh) of its tile
+        float vg[NT], vh[NT];
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            vg[j] = acc[j][0] + acc[j][1];
+            vh[j] = acc[j][2] + acc[j][3];
+        }
+
         // ---- reduce the K parts of a row tile inside the CTA ----
         if (p.KS > 1) {
-            float * mine = red + warp * (NT * 128);
+            float * mine = red + warp * (NT * 64);
 #pragma unroll
-            for (int j = 0; j < NT; j++)
-#pragma unroll
-                for (int c = 0; c < 4; c++) mine[(j * 4 + c) * 32 + lane] = acc[j][c];
+            for (int j = 0; j < NT; j++) {
+                mine[(2 * j) * 32 + lane] = vg[j];
+                mine[(2 * j + 1) * 32 + lane] = vh[j];
+            }
             __syncthreads();
             if (kpart == 0) {
 #pragma unroll
-                for (int j = 0; j < NT; j++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        float s = acc[j][c];
-                        for (int k = 1; k < p.KS; k++) s += red[(warp + k) * (NT * 128) + (j * 4 + c) * 32 + lane];
-                        acc[j][c] = s;
+                for (int j = 0; j < NT; j++) {
+                    float sg = vg[j], sh = vh[j];
+                    for (int k = 1; k < p.KS; k++) {
+                        sg += red[(warp + k) * (NT * 64) + (2 * j) * 32 + lane];
+                        sh += red[(warp + k) * (NT * 64) + (2 * j + 1) * 32 + lane];
                     }
+                    vg[j] = sg;
+                    vh[j] = sh;
+                }
             }
         }
         // ---- epilogue ----
@@ -841,88 +1049,90 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
             // the up tile's warp hands its sums to the gate tile's warp (KS warps earlier) through its own slot of red
             const bool is_up = (tile_in_group & 1) != 0;
             if (kpart == 0 && is_up) {
-                float * mine = red + warp * (NT * 128);
+                float * mine = red + warp * (NT * 64);
 #pragma unroll
-                for (int j = 0; j < NT; j++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) mine[(j * 4 + c) * 32 + lane] = acc[j][c];
+                for (int j = 0; j < NT; j++) {
+                    mine[(2 * j) * 32 + lane] = vg[j];
+                    mine[(2 * j + 1) * 32 + lane] = vh[j];
+                }
             }
             __syncthreads();
             if (kpart == 0 && !is_up && rt < n_tiles) {
-                const float * upv = red + (warp + p.KS) * (NT * 128);
+                const float * upv = red + (warp + p.KS) * (NT * 64);
                 const int half_n = p.N >> 1, col0 = (rt >> 1) * 16;
 #pragma unroll
-                for (int j = 0; j < NT; j++)
+                for (int j = 0; j < NT; j++) {
+                    const int tok = 4 * j + t;
+                    const bool tok_ok = tok < Mrows;
+                    const float cs = cs_s[tok & (MMA_ROWS - 1)];
+                    __half g_hi, g_lo, h_hi, h_lo;
+                    float gs = prep_value(swiglu(vg[j] * cs, upv[(2 * j) * 32 + lane] * cs), g_hi, g_lo) +
+                               prep_value(swiglu(vh[j] * cs, upv[(2 * j + 1) * 32 + lane] * cs), h_hi, h_lo);
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int tok = 8 * j + 2 * t + e;
-                        const bool tok_ok = tok < Mrows;
-                        const float cs = cs_s[tok & 31];
-                        const __half q_g = __float2half_rn(swiglu(acc[j][e] * cs, upv[(j * 4 + e) * 32 + lane] * cs));
-                        const __half q_h = __float2half_rn(swiglu(acc[j][2 + e] * cs, upv[(j * 4 + 2 + e) * 32 + lane] * cs));
-                        float gs = __half2float(q_g) + __half2float(q_h);
-#pragma unroll
-                        for (int o = 4; o < 32; o <<= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
-                        if (tok_ok) {
-                            p.sw_xh[(size_t)tok * half_n + col0 + g] = q_g;
-                            p.sw_xh[(size_t)tok * half_n + col0 + g + 8] = q_h;
-                            if (g == 0) {
-                                const __half hi = __float2half_rn(gs);
-                                p.sw_xs16[(size_t)tok * (half_n >> 4) + (rt >> 1)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
-                            }
-                        }
+                    for (int o = 4; o < 32; o <<= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                    if (tok_ok) {
+                        const size_t at = (size_t)tok * half_n + col0 + g;
+                        p.sw_xh[at] = g_hi;
+                        p.sw_xl[at] = g_lo;
+                        p.sw_xh[at + 8] = h_hi;
+                        p.sw_xl[at + 8] = h_lo;
+                        if (g == 0) p.sw_xs16[(size_t)tok * (half_n >> 4) + (rt >> 1)] = prep_sum(gs);
                     }
+                }
             }
-            if (p.KS == 1) __syncthreads();  // (with KS > 1 the barrier at the end of the group covers red)
+            __syncthreads();  // red is reused by the next group
         } else if (kpart == 0 && rt < n_tiles) {
             const int n_g = rt * 16 + g, n_h = n_g + 8;
             float * base = p.kchunks == 1 ? outp : p.partial + (size_t)blockIdx.y * Mrows * p.N;
             const int64_t ld = p.kchunks == 1 ? p.ldo : p.N;
             const bool produce = FOLD && p.nf_w != nullptr && p.kchunks == 1;
 #pragma unroll
-            for (int j = 0; j < NT; j++)
+            for (int j = 0; j < NT; j++) {
+                const int tok = 4 * j + t;
+                const bool tok_ok = tok < Mrows;
+                const float cs = FOLD ? cs_s[tok & (MMA_ROWS - 1)] : 1.0f;
+                float v[2] = {0.0f, 0.0f};  // final values of columns n_g, n_h (producer only)
 #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int tok = 8 * j + 2 * t + e;
-                    const bool tok_ok = tok < Mrows;
-                    const float cs = FOLD ? cs_s[tok & 31] : 1.0f;
-                    float v[2] = {0.0f, 0.0f};  // final values of columns n_g, n_h (producer only)
-#pragma unroll
-                    for (int hh = 0; hh < 2; hh++) {
-                        const int c = 2 * hh + e, n = hh ? n_h : n_g;
-                        if (tok_ok && n < p.N) {
-                            float * dst = base + (int64_t)tok * ld + n;
-                            if (p.kchunks == 1) {
-                                v[hh] = p.accumulate ? *dst + acc[j][c] * cs : acc[j][c] * cs;
-                                *dst = v[hh];
-                            } else {
-                                __stcg(dst, acc[j][c]);
-                            }
-                        }
-                    }
-                    if (produce) {
-                        // this tile is one 16-column group of the row: fp16(x * w * pre), the group sum, the squares
-                        const float pre = pre_s[tok & 31];
-                        const __half q_g = __float2half_rn(v[0] * pre * nw[warp * 16 + g]);
-                        const __half q_h = __float2half_rn(v[1] * pre * nw[warp * 16 + g + 8]);
-                        float gs = __half2float(q_g) + __half2float(q_h);
-                        float sq = v[0] * v[0] + v[1] * v[1];
-#pragma unroll
-                        for (int o = 4; o < 32; o <<= 1) {
-                            gs += __shfl_xor_sync(0xffffffffu, gs, o);
-                            sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                        }
-                        if (tok_ok) {
-                            if (n_g < p.N) p.nf_xh[(size_t)tok * p.N + n_g] = q_g;
-                            if (n_h < p.N) p.nf_xh[(size_t)tok * p.N + n_h] = q_h;
-                            if (g == 0) {
-                                const __half hi = __float2half_rn(gs);
-                                p.nf_xs16[(size_t)tok * (p.N >> 4) + rt] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
-                                atomicAdd(&p.nf_sumsq[tok], nf_fixed(sq));
-                            }
+                for (int hh = 0; hh < 2; hh++) {
+                    const int n = hh ? n_h : n_g;
+                    const float a = hh ? vh[j] : vg[j];
+                    if (tok_ok && n < p.N) {
+                        float * dst = base + (int64_t)tok * ld + n;
+                        if (p.kchunks == 1) {
+                            v[hh] = p.accumulate ? *dst + a * cs : a * cs;
+                            *dst = v[hh];
+                        } else {
+                            __stcg(dst, a);
                         }
                     }
                 }
+                if (produce) {
+                    // this tile is one 16-column group of the row: x * w * pre in both halves, the group sum, the squares
+                    const float pre = pre_s[tok & (MMA_ROWS - 1)];
+                    __half g_hi, g_lo, h_hi, h_lo;
+                    float gs = prep_value(v[0] * pre * nw[warp * 16 + g], g_hi, g_lo) + prep_value(v[1] * pre * nw[warp * 16 + g + 8], h_hi, h_lo);
+                    float sq = v[0] * v[0] + v[1] * v[1];
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) {
+                        gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    }
+                    if (tok_ok) {
+                        if (n_g < p.N) {
+                            p.nf_xh[(size_t)tok * p.N + n_g] = g_hi;
+                            p.nf_xl[(size_t)tok * p.N + n_g] = g_lo;
+                        }
+                        if (n_h < p.N) {
+                            p.nf_xh[(size_t)tok * p.N + n_h] = h_hi;
+                            p.nf_xl[(size_t)tok * p.N + n_h] = h_lo;
+                        }
+                        if (g == 0) {
+                            p.nf_xs16[(size_t)tok * (p.N >> 4) + rt] = prep_sum(gs);
+                            atomicAdd(&p.nf_sumsq[tok], nf_fixed(sq));
+                        }
+                    }
+                }
+            }
         }
         if (p.kchunks > 1) {
             // K is also split across CTAs: the last CTA to finish a group sums the chunks in order
@@ -938,7 +1148,7 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                 if (FOLD && p.sw_xh) {
                     // gate and up columns of the group, 16 by 16 (nrows is a multiple of 32: row tiles come in pairs)
                     const int half_rows = nrows >> 1, half_n = p.N >> 1, live_n = Mrows * half_rows;
-                    for (int i = threadIdx.x; i < ((live_n + 31) & ~31); i += TW * 32) {
+                    for (int i = threadIdx.x; i < ((live_n + 31) & ~31); i += MW * 32) {
                         const bool live = i < live_n;
                         const int tok = live ? i / half_rows : 0, cl = live ? i - tok * half_rows : 0;
                         const int n = row0 + (cl >> 4) * 32 + (cl & 15);
@@ -949,28 +1159,26 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                                 gsum += __ldcg(src);
                                 usum += __ldcg(src + 16);
                             }
-                        const float cs = cs_s[tok & 31];
-                        const __half qv = __float2half_rn(live ? swiglu(gsum * cs, usum * cs) : 0.0f);
-                        float gs = __half2float(qv);
+                        const float cs = cs_s[tok & (MMA_ROWS - 1)];
+                        __half q_hi, q_lo;
+                        float gs = prep_value(live ? swiglu(gsum * cs, usum * cs) : 0.0f, q_hi, q_lo);
 #pragma unroll
                         for (int o = 1; o < 16; o <<= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
                         if (live) {
                             const int col = (row0 >> 1) + cl;
-                            p.sw_xh[(size_t)tok * half_n + col] = qv;
-                            if ((lane & 15) == 0) {
-                                const __half hi = __float2half_rn(gs);
-                                p.sw_xs16[(size_t)tok * (half_n >> 4) + (col >> 4)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
-                            }
+                            p.sw_xh[(size_t)tok * half_n + col] = q_hi;
+                            p.sw_xl[(size_t)tok * half_n + col] = q_lo;
+                            if ((lane & 15) == 0) p.sw_xs16[(size_t)tok * (half_n >> 4) + (col >> 4)] = prep_sum(gs);
                         }
                     }
                 } else
-                for (int i = threadIdx.x; i < padded; i += TW * 32) {
+                for (int i = threadIdx.x; i < padded; i += MW * 32) {
                     const bool live = i < Mrows * nrows;
                     const int tok = live ? i / nrows : 0, n = row0 + (live ? i - tok * nrows : 0);
                     float s = 0.0f;
                     if (live)
                         for (int q = 0; q < p.kchunks; q++) s += __ldcg(p.partial + ((size_t)q * Mrows + tok) * p.N + n);
-                    if (FOLD) s *= cs_s[tok & 31];
+                    if (FOLD) s *= cs_s[tok & (MMA_ROWS - 1)];
                     float v = 0.0f;
                     if (live) {
                         float * dst = outp + (int64_t)tok * p.ldo + n;
@@ -979,18 +1187,19 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                     }
                     if (FOLD && p.nf_w) {
                         const int nl = n - row0;  // row tile nl / 16 of the group belongs to warp (nl / 16) * KS
-                        const __half qv = __float2half_rn(live ? v * pre_s[tok & 31] * nw[(nl >> 4) * p.KS * 16 + (nl & 15)] : 0.0f);
-                        float gs = __half2float(qv), sq = v * v;
+                        __half q_hi, q_lo;
+                        float gs = prep_value(live ? v * pre_s[tok & (MMA_ROWS - 1)] * nw[(nl >> 4) * p.KS * 16 + (nl & 15)] : 0.0f, q_hi, q_lo);
+                        float sq = v * v;
 #pragma unroll
                         for (int o = 1; o < 16; o <<= 1) {
                             gs += __shfl_xor_sync(0xffffffffu, gs, o);
                             sq += __shfl_xor_sync(0xffffffffu, sq, o);
                         }
                         if (live) {
-                            p.nf_xh[(size_t)tok * p.N + n] = qv;
+                            p.nf_xh[(size_t)tok * p.N + n] = q_hi;
+                            p.nf_xl[(size_t)tok * p.N + n] = q_lo;
                             if ((lane & 15) == 0) {
-                                const __half hi = __float2half_rn(gs);
-                                p.nf_xs16[(size_t)tok * (p.N >> 4) + (n >> 4)] = __halves2half2(hi, __float2half_rn(gs - __half2float(hi)));
+                                p.nf_xs16[(size_t)tok * (p.N >> 4) + (n >> 4)] = prep_sum(gs);
                                 atomicAdd(&p.nf_sumsq[tok], nf_fixed(sq));
                             }
                         }
@@ -998,15 +1207,15 @@ __global__ void __launch_bounds__(TW * 32, 2) gemm_tiled_mma_kernel(const TParam
                 }
                 if (threadIdx.x == 0) p.counters[grp] = 0;
             }
-        } else if (p.KS > 1) {
+        } else if (p.KS > 1 && !sw_direct) {
             __syncthreads();  // red is reused by the next group
         }
     }
 
     pdl_trigger_late();
     if (p.next_w) {
-        const uint32_t first = ((blockIdx.y * gridDim.x + blockIdx.x) * (TW * 32) + threadIdx.x);
-        const uint32_t step = gridDim.x * gridDim.y * (TW * 32);
+        const uint32_t first = ((blockIdx.y * gridDim.x + blockIdx.x) * (MW * 32) + threadIdx.x);
+        const uint32_t step = gridDim.x * gridDim.y * (MW * 32);
         for (uint32_t line = first; line < p.next_lines; line += step) prefetch_l2(p.next_w + (size_t)line * 128);
     }
 }
@@ -1109,6 +1318,21 @@ __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams 
                 const int8_t * scg = reinterpret_cast<const int8_t *>(hdrs[warp] + g * 32);
                 const int8_t * sch = reinterpret_cast<const int8_t *>(hdrs[warp] + (g + 8) * 32);
                 const float dg = ld_f16(hdrs[warp] + g * 32 + 16), dh = ld_f16(hdrs[warp] + (g + 8) * 32 + 16);
+                // four consecutive elements e..e+3 of rows g and g+8 (a lane's elements sit in two runs of four, pos6)
+                auto fma4 = [&](int e, const float * wg, const float * wh) {
+#pragma unroll
+                    for (int m = 0; m < F32_MT; m++) {
+                        if (m < p.M) {
+                            const float4 x0 = *reinterpret_cast<const float4 *>(xb + m * K + e);
+                            const float xv[4] = {x0.x, x0.y, x0.z, x0.w};
+#pragma unroll
+                            for (int b = 0; b < 4; b++) {
+                                ag[m] = fmaf(xv[b], wg[b], ag[m]);
+                                ah[m] = fmaf(xv[b], wh[b], ah[m]);
+                            }
+                        }
+                    }
+                };
 #pragma unroll
                 for (int n6 = 0; n6 < 2; n6++) {
                     const uint4 Lg = r.ql[n6], Lh = r.ql[2 + n6];
@@ -1116,19 +1340,21 @@ __global__ void __launch_bounds__(TW * 32) gemm_tiled_fp32_kernel(const TParams 
                     const uint32_t Hh0 = n6 ? r.qh[1].z : r.qh[1].x, Hh1 = n6 ? r.qh[1].w : r.qh[1].y;
 #pragma unroll
                     for (int g4 = 0; g4 < 4; g4++) {
-                        const int hsel = g4 & 1, nib = g4 >> 1, k = 4 * n6 + g4, s16 = 2 * k + (t >> 1);
-                        const float sg = dg * (float)scg[s16], sh = dh * (float)sch[s16];
+                        const int hsel = g4 & 1, nib = g4 >> 1, k = 4 * n6 + g4;
                         const uint32_t g0 = hsel ? Lg.z : Lg.x, g1 = hsel ? Lg.w : Lg.y;
                         const uint32_t h0 = hsel ? Lh.z : Lh.x, h1 = hsel ? Lh.w : Lh.y;
                         float wg[8], wh[8];
 #pragma unroll
                         for (int b = 0; b < 8; b++) {
+                            // elements 0..3 belong to the 16-element group 2k, elements 4..7 to group 2k + 1
+                            const float sg = dg * (float)scg[2 * k + (b >> 2)], sh = dh * (float)sch[2 * k + (b >> 2)];
                             const int vg = ((piece_byte(g0, g1, b) >> (4 * nib)) & 15) | (((piece_byte(Hg0, Hg1, b) >> (2 * g4)) & 3) << 4);
                             const int vh = ((piece_byte(h0, h1, b) >> (4 * nib)) & 15) | (((piece_byte(Hh0, Hh1, b) >> (2 * g4)) & 3) << 4);
                             wg[b] = sg * (float)(vg - 32);
                             wh[b] = sh * (float)(vh - 32);
                         }
-                        fma8(32 * k + 8 * t, wg, wh);
+                        fma4(32 * k + 4 * t, wg, wh);
+                        fma4(32 * k + 16 + 4 * t, wg + 4, wh + 4);
                     }
                 }
             } else {  // Q8_0
@@ -1172,75 +1398,68 @@ struct TPlan {
     size_t smem;
 };
 
-static int tab_of(uint32_t dtype) {
+static int xtab_of(uint32_t dtype) {
     switch (dtype) {
-    case YUUKA_DTYPE_Q6_K: return Codec<YUUKA_DTYPE_Q6_K>::TAB;
-    case YUUKA_DTYPE_Q8_0: return Codec<YUUKA_DTYPE_Q8_0>::TAB;
-    default: return Codec<YUUKA_DTYPE_Q4_K>::TAB;
+    case YUUKA_DTYPE_Q6_K: return XTab<YUUKA_DTYPE_Q6_K>::TAB;
+    case YUUKA_DTYPE_Q8_0: return XTab<YUUKA_DTYPE_Q8_0>::TAB;
+    default: return XTab<YUUKA_DTYPE_Q4_K>::TAB;
     }
 }
+static bool xtab_sums(uint32_t dtype) { return dtype == YUUKA_DTYPE_Q4_K || dtype == YUUKA_DTYPE_Q5_K; }
+static int mma_nt(int m) { return (2 * m + 7) / 8; }  // product columns: two per activation row, eight per MMA tile
 
-static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int nt, int ks, bool paired = false) {
-    size_t x = (size_t)m * (nsb_chunk * 512 + 64);
-    size_t xsum = (((size_t)m * (nsb_chunk * 64 + 16) + 127) / 128) * 128;
-    size_t red = (ks > 1 || paired) ? (size_t)TW * nt * 128 * 4 : 0;
-    return x + xsum + (size_t)TW * tab_of(dtype) + red;
+// dynamic shared memory of the register-fed kernel: both halves of m activation rows, their 16-column sums
+// (types with a "- min" term), one table per warp, and the exchange area of the K parts / SwiGLU pairs
+static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int ks, bool paired = false) {
+    size_t x = (size_t)2 * m * (nsb_chunk * 512 + 64);
+    size_t xsum = xtab_sums(dtype) ? (((size_t)m * (nsb_chunk * 64 + 16) + 127) / 128) * 128 : 0;
+    size_t red = (ks > 1 || paired) ? (size_t)MW * mma_nt(m) * 64 * 4 : 0;
+    return x + xsum + (size_t)MW * xtab_of(dtype) + red;
 }
 
-// paired: row tiles 2i and 2i+1 must share a CTA (SwiGLU epilogue): at most TW / 2 warps per row tile,
-// and room in shared memory for the exchange between the two.
+// How a matrix is cut into work for m (at most MMA_ROWS) activation rows: `kchunks` K chunks across CTAs and
+// KS warps per row tile inside a CTA (the other MW / KS row tiles of a group run beside it). The pair that
+// minimises waves x (records per warp + 0.7) + 0.3 per K chunk beyond the first, where a wave is one
+// (group, chunk) on every SM, 0.7 of a record stands for the fixed cost of a group (table set-up, reduction,
+// epilogue) and 0.3 for a chunk's share of the partial sums and their last-arrival sum; ties go to fewer
+// parts. Chunks start at what shared memory forces (the activations of all rows, both halves, must fit).
+// paired: row tiles 2i and 2i+1 must share a CTA (SwiGLU epilogue): at most MW / 2 warps per row tile.
 static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_out, int n_in, TPlan & pl, bool paired = false) {
     const int nsb = n_in / 256, n_tiles = (n_out + 15) / 16;
-    const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
-    const int slots = 2 * dev->sm_count;  // CTAs that can be resident (two per SM)
-    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
-    const size_t budget = half_sm < dev->prop.sharedMemPerBlockOptin ? half_sm : dev->prop.sharedMemPerBlockOptin;
-    // K chunks across CTAs that shared memory forces anyway (the activations of all rows must fit two CTAs per SM)
+    const int slots = dev->sm_count;  // one CTA per SM
+    const size_t budget = dev->prop.sharedMemPerBlockOptin - 4096;  // (static shared memory of the kernel: under 3 KB)
     int kc_fit = 1;
-    while ((nsb + kc_fit - 1) / kc_fit > 1 && mma_smem(dtype, m, (nsb + kc_fit - 1) / kc_fit, nt, 2, paired) > budget) kc_fit++;
-    // warps per row tile (K parts inside a CTA): the choice that minimises waves x records per warp, where a
-    // wave is one (group, chunk) on every resident CTA slot and 0.7 of a record stands for the fixed cost of
-    // a group (table set-up, reduction, epilogue); ties go to fewer parts. Measured in the 4B step at 9 rows:
-    // 12352 x 2560 with two parts (193 groups, one wave of five records) 2.385 ms per step against 2.428 with
-    // four (386 groups on 296 slots: a quarter of the CTAs run two groups of three records); 2560 x 9216 Q6_K,
-    // where three chunks are forced, four parts 27.7 us against eight 29.9 us.
-    int ks = 1;
-    {
-        const int nsb_c = (nsb + kc_fit - 1) / kc_fit;
-        double best = 1e30;
-        for (int k = 1; k <= (paired ? TW / 2 : TW); k *= 2) {
+    while ((nsb + kc_fit - 1) / kc_fit > 1 && mma_smem(dtype, m, (nsb + kc_fit - 1) / kc_fit, 2, paired) > budget) kc_fit++;
+    int ks = 1, kchunks = kc_fit;
+    double best = 1e30;
+    for (int kc = kc_fit; kc <= nsb && kc <= kc_fit + 3; kc++) {
+        const int nsb_c = (nsb + kc - 1) / kc, real_kc = (nsb + nsb_c - 1) / nsb_c;
+        if (real_kc != kc && kc != kc_fit) continue;  // same cut as a smaller count
+        for (int k = 1; k <= (paired ? MW / 2 : MW); k *= 2) {
             if (k > 1 && nsb_c < k) break;  // every warp keeps at least one record
-            const int groups = (n_tiles + TW / k - 1) / (TW / k);
-            const int waves = (groups * kc_fit + slots - 1) / slots;
-            const double cost = waves * ((nsb_c + k - 1) / k + 0.7);
+            if (mma_smem(dtype, m, nsb_c, k, paired) > budget) continue;
+            const int groups = (n_tiles + MW / k - 1) / (MW / k);
+            const int waves = (groups * real_kc + slots - 1) / slots;
+            const double cost = waves * ((nsb_c + k - 1) / k + 0.7) + (real_kc > 1 ? 0.3 * (real_kc - 1) : 0.0);
             if (cost < best - 1e-9) {
                 best = cost;
                 ks = k;
+                kchunks = real_kc;
             }
         }
     }
     pl.KS = ks;
-    pl.TG = TW / ks;
+    pl.TG = MW / ks;
     pl.n_groups = (n_tiles + pl.TG - 1) / pl.TG;
-    // CTA-level K chunks: when even KS = TW leaves SMs idle, or the activations do not fit two CTAs per SM
-    int kchunks = 1;
-    while (true) {
-        int nsb_chunk = (nsb + kchunks - 1) / kchunks;
-        bool fits = mma_smem(dtype, m, nsb_chunk, nt, ks, paired) <= budget;
-        bool enough = pl.n_groups * kchunks >= slots / 2 || nsb_chunk < 2 * ks || nsb_chunk <= 2;
-        if (fits && enough) break;
-        if (nsb_chunk == 1) break;
-        kchunks++;
-    }
     pl.nsb_chunk = (nsb + kchunks - 1) / kchunks;
     pl.kchunks = (nsb + pl.nsb_chunk - 1) / pl.nsb_chunk;
-    pl.smem = mma_smem(dtype, m, pl.nsb_chunk, nt, ks, paired);
+    pl.smem = mma_smem(dtype, m, pl.nsb_chunk, ks, paired);
     int per = slots / pl.kchunks;
     if (per < 1) per = 1;
     pl.grid_x = pl.n_groups < per ? pl.n_groups : per;
 }
 
-// Rows from which the tensor-memory route takes over from 32-row passes of the register-fed kernel.
+// Rows from which the tensor-memory route takes over from 16-row passes of the register-fed kernel.
 constexpr int UMMA_MIN_ROWS = 48;
 
 static bool umma_enabled() {
@@ -1317,7 +1536,7 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
             *counters = (n_out + UM_ROWS - 1) / UM_ROWS;
         }
     }
-    for (int m : {rows < 32 ? rows : 32, 32 < rows ? rows % 32 : 0}) {
+    for (int m : {rows < MMA_ROWS ? rows : MMA_ROWS, MMA_ROWS < rows ? rows % MMA_ROWS : 0}) {
         if (m <= 0) continue;
         for (bool paired : {false, true}) {
             TPlan pl;
@@ -1332,8 +1551,7 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
 }
 
 template <int DT, int NT>
-static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __half * xh, const __half2 * xs16, int m0, int m,
-                            const TPlan & pl) {
+static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const XPrepOut & xp, int m0, int m, const TPlan & pl) {
     const bool fold = a.norm.produce_w || a.norm.consume_now || a.swiglu.xh;
     auto kern = fold ? gemm_tiled_mma_kernel<DT, NT, false, true> : gemm_tiled_mma_kernel<DT, NT, false, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
@@ -1342,8 +1560,9 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     p.w = a.w;
     p.N = a.n_out;
     p.nsb = a.n_in / 256;
-    p.xh = xh + (int64_t)m0 * a.n_in;
-    p.xs16 = xs16 + (int64_t)m0 * (a.n_in / 16);
+    p.xh = xp.xh + (int64_t)m0 * a.n_in;
+    p.xl = xp.xl + (int64_t)m0 * a.n_in;
+    p.xs16 = xp.xs16 + (int64_t)m0 * (a.n_in / 16);
     p.M = m;
     p.out = a.out + (int64_t)m0 * a.ldo;
     p.ldo = a.ldo;
@@ -1356,53 +1575,56 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const __hal
     p.partial = a.scratch ? a.scratch->partial : nullptr;
     p.counters = a.scratch ? a.scratch->counters : nullptr;
     if (a.norm.produce_w || a.norm.consume_now) {
+        // (per-row arrays of the folded norm start at this launch's first row)
         p.nf_w = a.norm.produce_w;
-        p.nf_prev = a.norm.produce_prev;
-        p.nf_sumsq = a.norm.produce_sumsq;
-        p.nf_xh = a.norm.produce_prep.xh;
-        p.nf_xs16 = a.norm.produce_prep.xs16;
-        p.cs_now = a.norm.consume_now;
-        p.cs_prev = a.norm.consume_prev;
+        p.nf_prev = a.norm.produce_prev ? a.norm.produce_prev + m0 : nullptr;
+        p.nf_sumsq = a.norm.produce_sumsq ? a.norm.produce_sumsq + m0 : nullptr;
+        if (a.norm.produce_prep.xh) {
+            p.nf_xh = a.norm.produce_prep.xh + (int64_t)m0 * a.n_out;
+            p.nf_xl = a.norm.produce_prep.xl + (int64_t)m0 * a.n_out;
+            p.nf_xs16 = a.norm.produce_prep.xs16 + (int64_t)m0 * (a.n_out / 16);
+        }
+        p.cs_now = a.norm.consume_now ? a.norm.consume_now + m0 : nullptr;
+        p.cs_prev = a.norm.consume_prev ? a.norm.consume_prev + m0 : nullptr;
         p.nf_eps = a.norm.eps;
         p.nf_cols = a.norm.cols;
     }
     if (a.swiglu.xh) {
         p.sw_xh = a.swiglu.xh + (int64_t)m0 * (a.n_out / 2);
+        p.sw_xl = a.swiglu.xl + (int64_t)m0 * (a.n_out / 2);
         p.sw_xs16 = a.swiglu.xs16 + (int64_t)m0 * (a.n_out / 32);
         p.nf_eps = a.norm.eps;
         p.nf_cols = a.norm.cols;
     }
-    if (a.next_w && m0 + 32 >= a.rows) {
+    if (a.next_w && m0 + MMA_ROWS >= a.rows) {
         p.next_w = a.next_w;
         p.next_lines = (uint32_t)(a.next_bytes / 128);
     }
     dim3 grid(pl.grid_x, pl.kchunks);
-    launch_k(kern, grid, TW * 32, pl.smem, s, p);
+    launch_k(kern, grid, MW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
 template <int DT>
 static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const GroupedGemmArgs & a) {
     const int nsb = a.n_in / 256, n_tiles = (a.n_out + 15) / 16;
+    constexpr int NT = (2 * GEMM_SEGMENT_ROWS + 7) / 8;
     TPlan pl;
     pl.KS = 1;
-    pl.TG = TW;
-    pl.n_groups = (n_tiles + TW - 1) / TW;
+    pl.TG = MW;
+    pl.n_groups = (n_tiles + MW - 1) / MW;
     pl.kchunks = 1;
     pl.nsb_chunk = nsb;
-    pl.smem = mma_smem(DT, GEMM_SEGMENT_ROWS, nsb, 1, 1);
+    pl.smem = mma_smem(DT, GEMM_SEGMENT_ROWS, nsb, 1);
     // row groups per CTA: a CTA stages a segment's activation rows once and then walks that many groups
-    // (enough CTAs to fill the resident slots about twice when every slot of the segment list is in use.
-    // Measured on the qwen35moe shape, 160 rows, 8 layers: 3.97 ms per step with one group per CTA, 3.81 with
-    // two, 3.75 with four, 3.72 with eight)
-    int per = (int)((int64_t)pl.n_groups * a.max_segments / (4 * dev->sm_count));
+    // (enough CTAs to fill the SMs about twice when every slot of the segment list is in use)
+    int per = (int)((int64_t)pl.n_groups * a.max_segments / (2 * dev->sm_count));
     if (per < 1) per = 1;
     if (per > pl.n_groups) per = pl.n_groups;
     pl.grid_x = (pl.n_groups + per - 1) / per;
-    const size_t half_sm = (dev->prop.sharedMemPerMultiprocessor - 2 * 1024 - 2048) / 2;
-    YK_REQUIRE(pl.smem <= half_sm && pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
+    YK_REQUIRE(pl.smem + 4096 <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
                "grouped gemm: %d columns of activations do not fit shared memory", a.n_in);
-    auto kern = gemm_tiled_mma_kernel<DT, 1, true, false>;
+    auto kern = gemm_tiled_mma_kernel<DT, NT, true, false>;
     YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
     TParams p{};
     p.kc = decode_consts(DT);
@@ -1410,6 +1632,7 @@ static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const Gr
     p.N = a.n_out;
     p.nsb = nsb;
     p.xh = a.xprep.xh;
+    p.xl = a.xprep.xl;
     p.xs16 = a.xprep.xs16;
     p.M = GEMM_SEGMENT_ROWS;
     p.out = a.out;
@@ -1423,12 +1646,12 @@ static void launch_grouped_dt(const yuuka_device * dev, cudaStream_t s, const Gr
     p.expert_stride = a.expert_stride;
     p.row_index = a.row_index;
     dim3 grid(pl.grid_x, 1, a.max_segments);
-    launch_k(kern, grid, TW * 32, pl.smem, s, p);
+    launch_k(kern, grid, MW * 32, pl.smem, s, p);
     YK_CUDA(cudaGetLastError());
 }
 
 int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, const GroupedGemmArgs & a) {
-    YK_REQUIRE(a.w && a.xprep.xh && a.xprep.xs16 && a.out && a.segments, YUUKA_ERR_INVALID_ARGUMENT, "grouped gemm: null operand");
+    YK_REQUIRE(a.w && a.xprep.xh && a.xprep.xl && a.xprep.xs16 && a.out && a.segments, YUUKA_ERR_INVALID_ARGUMENT, "grouped gemm: null operand");
     YK_REQUIRE(a.n_out > 0 && a.n_in > 0 && a.max_segments > 0 && a.max_segments <= 65535, YUUKA_ERR_INVALID_ARGUMENT,
                "grouped gemm: invalid shape");
     YK_REQUIRE(tiled_supported(a.w_dtype, a.n_in), YUUKA_ERR_UNSUPPORTED, "grouped gemm: dtype %u / width %d has no tiled layout",
@@ -1554,34 +1777,38 @@ static int launch_umma_dt(const yuuka_device * dev, cudaStream_t s, const TiledG
 template <int DT>
 static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGemmArgs & a) {
     int launches = 0;
-    const __half * xh = a.xprep.xh;
-    const __half2 * xs16 = a.xprep.xs16;
-    if (!xh) {
+    XPrepOut xp = a.xprep;
+    if (!xp.xh) {
         // activations arrive as f32 / bf16: convert once into the scratch
-        YK_REQUIRE(a.x && a.scratch && a.scratch->xh && a.scratch->xh_elems >= (uint64_t)a.rows * a.n_in,
+        YK_REQUIRE(a.x && a.scratch && a.scratch->xh && a.scratch->xl && a.scratch->xh_elems >= (uint64_t)a.rows * a.n_in,
                    YUUKA_ERR_INTERNAL, "gemm: no prepared activations and no scratch to prepare them in");
         if (a.x_dtype == YUUKA_DTYPE_F32)
-            launch_xprep<float>(s, a.scratch->xh, a.scratch->xs16, (const float *)a.x, a.ldx, a.n_in, a.rows);
+            launch_xprep<float>(s, a.scratch->xh, a.scratch->xl, a.scratch->xs16, (const float *)a.x, a.ldx, a.n_in, a.rows);
         else
-            launch_xprep<__nv_bfloat16>(s, a.scratch->xh, a.scratch->xs16, (const __nv_bfloat16 *)a.x, a.ldx, a.n_in, a.rows);
-        xh = a.scratch->xh;
-        xs16 = a.scratch->xs16;
+            launch_xprep<__nv_bfloat16>(s, a.scratch->xh, a.scratch->xl, a.scratch->xs16, (const __nv_bfloat16 *)a.x, a.ldx, a.n_in, a.rows);
+        xp.xh = a.scratch->xh;
+        xp.xl = a.scratch->xl;
+        xp.xs16 = a.scratch->xs16;
         launches++;
     }
-    if (a.rows >= UMMA_MIN_ROWS && umma_enabled()) return launches + launch_umma_dt<DT>(dev, s, a, xh);
-    for (int m0 = 0; m0 < a.rows; m0 += 32) {
-        const int m = a.rows - m0 < 32 ? a.rows - m0 : 32;
+    if (a.rows >= UMMA_MIN_ROWS && umma_enabled() && !a.exact_only) return launches + launch_umma_dt<DT>(dev, s, a, xp.xh);
+    YK_REQUIRE(xp.xl && xp.xs16, YUUKA_ERR_INTERNAL, "gemm: the prepared activations lack their lo halves or sums");
+    for (int m0 = 0; m0 < a.rows; m0 += MMA_ROWS) {
+        const int m = a.rows - m0 < MMA_ROWS ? a.rows - m0 : MMA_ROWS;
         TPlan pl;
         plan_tiled(dev, a.w_dtype, m, a.n_out, a.n_in, pl, a.swiglu.xh != nullptr);
-        YK_REQUIRE(pl.smem <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
+        YK_REQUIRE(pl.smem + 4096 <= dev->prop.sharedMemPerBlockOptin, YUUKA_ERR_UNSUPPORTED,
                    "gemm: activations of %d rows x %d columns do not fit shared memory", m, a.n_in);
         if (pl.kchunks > 1)
             YK_REQUIRE(a.scratch && a.scratch->partial_floats >= (uint64_t)pl.kchunks * m * a.n_out &&
                            a.scratch->counter_count >= pl.n_groups,
                        YUUKA_ERR_INTERNAL, "gemm: split-K scratch is too small");
-        if (m <= 8) launch_mma_inst<DT, 1>(s, a, xh, xs16, m0, m, pl);
-        else if (m <= 16) launch_mma_inst<DT, 2>(s, a, xh, xs16, m0, m, pl);
-        else launch_mma_inst<DT, 4>(s, a, xh, xs16, m0, m, pl);
+        switch (mma_nt(m)) {
+        case 1: launch_mma_inst<DT, 1>(s, a, xp, m0, m, pl); break;
+        case 2: launch_mma_inst<DT, 2>(s, a, xp, m0, m, pl); break;
+        case 3: launch_mma_inst<DT, 3>(s, a, xp, m0, m, pl); break;
+        default: launch_mma_inst<DT, 4>(s, a, xp, m0, m, pl); break;
+        }
         launches++;
     }
     return launches;
@@ -1634,7 +1861,8 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
     }
     if (a.norm.produce_w || a.norm.consume_now || a.swiglu.xh) {
         const uint32_t route = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
-        YK_REQUIRE(route == YUUKA_GEMM_PATH_MMA && a.rows <= 32 && (a.rows < UMMA_MIN_ROWS || !umma_enabled()),
+        YK_REQUIRE(route == YUUKA_GEMM_PATH_MMA && a.rows <= 32 && (a.rows < UMMA_MIN_ROWS || !umma_enabled()) &&
+                       (!a.swiglu.xh || a.swiglu.xl) && (!a.norm.produce_w || a.norm.produce_prep.xl),
                    YUUKA_ERR_INTERNAL, "gemm: folded epilogues (RMSNorm, SwiGLU) run on the register-fed mma route only (3..32 rows)");
         YK_REQUIRE(!a.norm.produce_w || (a.n_out % 16 == 0 && a.norm.produce_sumsq && a.norm.produce_prep.xh && a.norm.produce_prep.xs16),
                    YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs a width that is a multiple of 16 and its outputs");
@@ -1668,6 +1896,7 @@ static void preload_dt() {
     cudaFuncAttributes fa;
     YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 1, false, false>));
     YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 2, false, false>));
+    YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 3, false, false>));
     YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_mma_kernel<DT, 4, false, false>));
     YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_fp32_kernel<DT, float>));
     YK_CUDA(cudaFuncGetAttributes(&fa, gemm_tiled_fp32_kernel<DT, __nv_bfloat16>));

@@ -89,6 +89,7 @@ struct TiledGemmArgs {
     int rows = 0, n_out = 0, n_in = 0;
     uint32_t path = YUUKA_GEMM_PATH_AUTO;
     uint32_t flags = 0;
+    bool exact_only = false;          // wide passes too stay on the register-fed route (16 rows per launch)
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     NormFuse norm;
     // Set: `w` holds ffn_gate and ffn_up interleaved by 16-row tile and the launch writes silu(gate) * up in

@@ -71,6 +71,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 // ---- scaled fragments of one 32-column sub-block K of a record, as the register-fed kernel forms
 // them: a[h][0], a[h][2] = row g, elements 8t + 4h + {0,1}, {2,3}; a[h][1], a[h][3] = row g + 8.
 // `mg`, `mh` receive the half2 that still has to be added (-min, or -32 * scale for Q6_K).
+__device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 template <int DT> struct SubBlock;
 
 template <> struct SubBlock<YUUKA_DTYPE_Q4_K> {
@@ -122,30 +128,35 @@ template <> struct SubBlock<YUUKA_DTYPE_Q5_K> {
 
 template <> struct SubBlock<YUUKA_DTYPE_Q6_K> {
     using C = Codec<YUUKA_DTYPE_Q6_K>;
+    // Q6_K records keep a lane's eight elements of a sub-block in two runs of four (pos6): a[0][*] are elements
+    // 4t + {0..3} (16-element group 2K), a[1][*] elements 16 + 4t + {0..3} (group 2K + 1). The offsets are added
+    // here, per group; mg / mh come back as zero.
     template <int K>
     __device__ static void frag(const typename C::Regs & r, int lane, const uint8_t * tab, const DecodeConsts & kc,
                                 uint32_t (&a)[2][4], uint32_t & mg, uint32_t & mh) {
         constexpr int n6 = K >> 2, nib = (K >> 1) & 1, hsel = K & 1;
         constexpr int lsh = 4 - 2 * hsel, rsh = 4 + 2 * hsel;
-        const int g = lane >> 2, t = lane & 3;
+        const int g = lane >> 2;
         const uint32_t lg[4] = {r.ql[n6].x, r.ql[n6].y, r.ql[n6].z, r.ql[n6].w};
         const uint32_t lh[4] = {r.ql[2 + n6].x, r.ql[2 + n6].y, r.ql[2 + n6].z, r.ql[2 + n6].w};
         const uint32_t hg[2] = {n6 ? r.qh[0].z : r.qh[0].x, n6 ? r.qh[0].w : r.qh[0].y};
         const uint32_t hh[2] = {n6 ? r.qh[1].z : r.qh[1].x, n6 ? r.qh[1].w : r.qh[1].y};
-        const int s16 = 2 * K + (t >> 1);  // the 16-element group this lane's eight elements belong to
-        const uint2 eg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE)[s16];
-        const uint2 eh = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE)[s16];
         const uint32_t qm = nib ? kc.mf0 : kc.m0f, hm = nib ? kc.h8 : kc.h4;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
+            const int s16 = 2 * K + h;
+            const uint2 eg = reinterpret_cast<const uint2 *>(tab + g * C::SCL_STRIDE)[s16];
+            const uint2 eh = reinterpret_cast<const uint2 *>(tab + (g + 8) * C::SCL_STRIDE)[s16];
+            const uint32_t og = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE)[s16];
+            const uint32_t oh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE)[s16];
             const uint32_t vg = lg[2 * hsel + h], vh = lh[2 * hsel + h];
-            a[h][0] = h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), eg.x, eg.y);
-            a[h][1] = h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), eh.x, eh.y);
-            a[h][2] = h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), eg.x, eg.y);
-            a[h][3] = h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), eh.x, eh.y);
+            a[h][0] = h2_add(h2_fma(and_or(vg, qm, and_or(hg[h] << lsh, hm, kc.magic)), eg.x, eg.y), og);
+            a[h][1] = h2_add(h2_fma(and_or(vh, qm, and_or(hh[h] << lsh, hm, kc.magic)), eh.x, eh.y), oh);
+            a[h][2] = h2_add(h2_fma(and_or(vg >> 8, qm, and_or(hg[h] >> rsh, hm, kc.magic)), eg.x, eg.y), og);
+            a[h][3] = h2_add(h2_fma(and_or(vh >> 8, qm, and_or(hh[h] >> rsh, hm, kc.magic)), eh.x, eh.y), oh);
         }
-        mg = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + g * C::MN_STRIDE)[s16];
-        mh = reinterpret_cast<const uint32_t *>(tab + C::MN_OFF + (g + 8) * C::MN_STRIDE)[s16];
+        mg = 0u;
+        mh = 0u;
     }
 };
 
@@ -174,12 +185,6 @@ template <> struct SubBlock<YUUKA_DTYPE_Q8_0> {
     }
 };
 
-__device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-
 // K-major, no swizzle: core matrix (8 rows x 16 bytes) at rowgroup * 1024 + kchunk * 128 inside a stage
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo = 128u, uint32_t sbo = 1024u) {
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
@@ -203,6 +208,16 @@ __device__ __forceinline__ void umma_store_subblock(const typename Codec<DT>::Re
     uint32_t a[2][4], mg, mh;
     SubBlock<DT>::template frag<K>(r, lane, tab, kc, a, mg, mh);
     const int g = lane >> 2, t = lane & 3;
+    if constexpr (DT == YUUKA_DTYPE_Q6_K) {
+        // two runs of four columns: 4t.. (first half of the sub-block) and 16 + 4t..
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int col = 16 * h + 4 * t, kchunk = 4 * kblk_in_stage + (col >> 3), off = g * 16 + (col & 7) * 2;
+            *reinterpret_cast<uint2 *>(a_stage + (2 * warp) * UM_A_SBO + kchunk * UM_A_LBO + off) = make_uint2(a[h][0], a[h][2]);
+            *reinterpret_cast<uint2 *>(a_stage + (2 * warp + 1) * UM_A_SBO + kchunk * UM_A_LBO + off) = make_uint2(a[h][1], a[h][3]);
+        }
+        return;
+    }
     const int kchunk = 4 * kblk_in_stage + t;  // eight columns each
     uint4 vg = make_uint4(a[0][0], a[0][2], a[1][0], a[1][2]);
     uint4 vh = make_uint4(a[0][1], a[0][3], a[1][1], a[1][3]);

@@ -20,6 +20,7 @@ PATH_AUTO, PATH_FP32, PATH_MMA = 0, 1, 2
 GEMM_ACCUMULATE = 1
 GEMM_TILED = 2
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
+SESSION_EXACT_WIDE = 1
 OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
             100: "gdn_scan", 102: "accept", 103: "commit", 104: "moe_route", 105: "moe_experts",
             106: "moe_combine"}
@@ -64,7 +65,7 @@ class GgufTensor(C.Structure):
 class SessionConfig(C.Structure):
     _fields_ = [("max_batch", C.c_int32), ("max_nodes", C.c_int32), ("capacity", C.c_int32),
                 ("block_size", C.c_int32), ("pool_blocks", C.c_int32), ("kv_format", C.c_int32),
-                ("want_logits", C.c_int32)]
+                ("want_logits", C.c_int32), ("flags", C.c_uint32)]
 
 
 class SessionInfo(C.Structure):
@@ -563,10 +564,11 @@ class Session:
     max_batch sequences (engine/gpu/session.go holds one sequence)."""
 
     def __init__(self, model: Model, max_batch: int = 1, max_nodes: int = 16, capacity: int = 512,
-                 kv_format: int = KV_F16, block_size: int = 0, pool_blocks: int = 0, want_logits: bool = True):
+                 kv_format: int = KV_F16, block_size: int = 0, pool_blocks: int = 0, want_logits: bool = True,
+                 flags: int = 0):
         self.model = model
         self.max_batch, self.max_nodes, self.capacity = max_batch, max_nodes, capacity
-        cfg = SessionConfig(max_batch, max_nodes, capacity, block_size, pool_blocks, kv_format, int(want_logits))
+        cfg = SessionConfig(max_batch, max_nodes, capacity, block_size, pool_blocks, kv_format, int(want_logits), flags)
         self.h = C.c_void_p()
         check(lib().yuuka_session_create(model.h, C.byref(cfg), C.byref(self.h)))
         self._staged = None
