@@ -1419,10 +1419,11 @@ static size_t mma_smem(uint32_t dtype, int m, int nsb_chunk, int ks, bool paired
 
 // How a matrix is cut into work for m (at most MMA_ROWS) activation rows: `kchunks` K chunks across CTAs and
 // KS warps per row tile inside a CTA (the other MW / KS row tiles of a group run beside it). The pair that
-// minimises waves x (records per warp + 0.7) + 0.3 per K chunk beyond the first, where a wave is one
+// minimises waves x (records per warp + 0.7) + 1.5 per K chunk beyond the first, where a wave is one
 // (group, chunk) on every SM, 0.7 of a record stands for the fixed cost of a group (table set-up, reduction,
-// epilogue) and 0.3 for a chunk's share of the partial sums and their last-arrival sum; ties go to fewer
-// parts. Chunks start at what shared memory forces (the activations of all rows, both halves, must fit).
+// epilogue) and 1.5 for a chunk's share of the partial sums and their last-arrival sum (measured on the 4B
+// step at 9 rows: 2.68 ms per step with 1.5, 2.76 ms with 0.3, which splits the 2560-column matrices three
+// ways across CTAs); ties go to fewer parts. Chunks start at what shared memory forces (the activations of all rows, both halves, must fit).
 // paired: row tiles 2i and 2i+1 must share a CTA (SwiGLU epilogue): at most MW / 2 warps per row tile.
 static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_out, int n_in, TPlan & pl, bool paired = false) {
     const int nsb = n_in / 256, n_tiles = (n_out + 15) / 16;
@@ -1440,7 +1441,7 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
             if (mma_smem(dtype, m, nsb_c, k, paired) > budget) continue;
             const int groups = (n_tiles + MW / k - 1) / (MW / k);
             const int waves = (groups * real_kc + slots - 1) / slots;
-            const double cost = waves * ((nsb_c + k - 1) / k + 0.7) + (real_kc > 1 ? 0.3 * (real_kc - 1) : 0.0);
+            const double cost = waves * ((nsb_c + k - 1) / k + 0.7) + (real_kc > 1 ? 1.5 * (real_kc - 1) : 0.0);
             if (cost < best - 1e-9) {
                 best = cost;
                 ks = k;
