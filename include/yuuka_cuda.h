@@ -293,6 +293,11 @@ YUUKA_API void yuuka_session_destroy(yuuka_session * s);
  * is the identity mapping over the sequence's own slice of the pool. */
 YUUKA_API yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const int32_t * blocks,
                                                      int32_t count);
+/* KVPool.CopyBlock (model/qwen35/kv_pool.go:156-170; engine/gpu/model.go:600-626): copies block src of the
+ * K and V pool of every attention layer onto block dst, device to device on the session stream and
+ * synchronously. The prefix cache uses it to give a request a private copy of a shared, partly filled
+ * block before the request appends to it. */
+YUUKA_API yuuka_status yuuka_session_copy_block(yuuka_session * s, int32_t dst_block, int32_t src_block);
 /* State.Reset / State.SetPos (model/qwen35/state.go:174-208) */
 YUUKA_API yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq);
 YUUKA_API yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t position);
@@ -346,6 +351,11 @@ typedef struct yuuka_verify_batch {
     int32_t * emitted;           /* [batch, nodes] */
     int32_t * path;              /* [batch, nodes] or NULL */
     float * logits;              /* optional host [batch, nodes, vocab]; needs want_logits */
+    /* [batch] or NULL: the session sequence behind each slot of the batch, distinct values in
+     * 0..max_batch-1; NULL means slot b is sequence b. A scheduler iteration verifies whichever of
+     * its runs are ready (scheduler/scheduler.go:590-623 walks them one DecodeOnce at a time): it
+     * lists their sequences here instead of moving state between slots. */
+    const int32_t * seq_ids;
 } yuuka_verify_batch;
 
 YUUKA_API yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_batch * batch);
@@ -447,7 +457,7 @@ typedef struct yuuka_spec_result {
     int32_t draft_tokens;   /* DraftTokens */
     int32_t accepted_draft; /* AcceptedDraft */
 } yuuka_spec_result;
-/* generateSpeculative, engine/speculative.go:68-251, for sequence 0 of the
+/* generateSpeculative, engine/speculative.go:68-251, for sequence seq of the
  * session: resets it, runs the prompt, then verify steps of [pending token,
  * prompt-lookup drafts] until max_tokens, a stop token (not emitted) or the
  * context capacity. tokens must hold max_tokens ids. The emitted stream equals

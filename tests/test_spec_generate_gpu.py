@@ -135,3 +135,18 @@ def test_generate_after_a_long_prompt(tiny):
     assert same >= 40, f"stream forked at a near-tie after {same} tokens; pick another seed"
     assert res.prompt_tokens == 200 and res.output_tokens == n and sess.position() >= 200 + n - 1
     sess.close(); gm.close()
+
+
+def test_generation_on_another_sequence_of_the_session(tiny):
+    """Sequence 2 of a three-sequence session generates the stream sequence 0 would, and leaves the others alone."""
+    cfg, gm, om = tiny
+    prompt = synth.uniform_i32(20, 0, cfg["vocab"], 31).tolist()
+    want, gaps = oracle_greedy(om, prompt, 24)
+    sess = cuda.Session(gm, max_batch=3, max_nodes=5, capacity=128, kv_format=cuda.KV_F32)
+    sess.forward([3, 4, 5], seq=0, want_logits=False)
+    got, res = cuda.spec_generate(sess, prompt, 24, max_draft=4, min_match=2, seq=2)
+    n = agree(got, want, gaps)
+    assert n >= 8
+    assert sess.position(0) == 3 and sess.position(1) == 0
+    assert sess.position(2) == len(prompt) + res.output_tokens - 1 or sess.position(2) == len(prompt) + res.output_tokens
+    sess.close()

@@ -426,3 +426,102 @@ def test_widest_tree_and_single_row_steps(tiny):
     one = sess.verify([[int(res.emitted[0, int(res.accepted[0])])]], want_logits=True)
     assert int(one.accepted[0]) == 0 and int(one.emitted[0, 0]) == int(np.argmax(one.logits[0, 0]))
     sess.close(); st.close()
+
+
+def test_batch_over_a_list_of_sequences_equals_the_sequences_alone(tiny):
+    """A scheduler verifies whichever runs are ready: sequences {5, 1, 6} of an eight-sequence session as one
+    batch (seq_ids) give the integers and the logits, bit for bit, of the same three sequences stepped one by
+    one, leave the other sequences untouched, and the next step may list them in another order."""
+    cfg, gm, om = tiny
+    V, B, N = cfg["vocab"], 8, 5
+    ids = [5, 1, 6]
+
+    def fresh():
+        sess = cuda.Session(gm, max_batch=B, max_nodes=N, capacity=96, kv_format=cuda.KV_F16)
+        pend = {}
+        for sq in range(B):
+            prompt = synth.uniform_i32(11 + 3 * sq, 0, V, 500 + sq)
+            pend[sq] = int(np.argmax(sess.forward(prompt, seq=sq)))
+        return sess, pend
+
+    toks = {sq: [0] + synth.uniform_i32(N - 1, 0, V, 600 + sq).tolist() for sq in range(B)}
+    a, pend = fresh()
+    for sq in ids:
+        toks[sq][0] = pend[sq]
+    alone = {}
+    for sq in ids:
+        r = a.verify([toks[sq]], want_logits=True, seq_ids=[sq])
+        alone[sq] = (int(r.accepted[0]), r.emitted[0].copy(), r.logits[0].copy(), a.position(sq))
+    b, _ = fresh()
+    before = {sq: (b.position(sq), b.snapshot(sq).copy()) for sq in range(B) if sq not in ids}
+    r = b.verify([toks[sq] for sq in ids], want_logits=True, seq_ids=ids)
+    for slot, sq in enumerate(ids):
+        acc, em, lg, pos = alone[sq]
+        assert int(r.accepted[slot]) == acc and np.array_equal(r.emitted[slot, :acc + 1], em[:acc + 1])
+        assert np.array_equal(r.logits[slot].view(np.uint32), lg.view(np.uint32))
+        assert b.position(sq) == pos
+        assert np.array_equal(b.snapshot(sq), a.snapshot(sq))
+    for sq, (pos, snap) in before.items():
+        assert b.position(sq) == pos and np.array_equal(b.snapshot(sq), snap)
+    # next step, other order and another subset; against the oracle for one of them
+    st = yo.State(om, 96, yo.KV_F16)
+    prompt = synth.uniform_i32(11 + 3 * 6, 0, V, 506).tolist()
+    lo = st.forward(prompt)
+    acc6, em6, _ = st.verify_chain(yo.argmax(lo), np.array(toks[6][1:], np.int32))
+    assert alone[6][0] == acc6 and alone[6][1][:acc6 + 1].tolist() == em6.tolist()
+    nxt6 = [int(em6[-1])] + synth.uniform_i32(N - 1, 0, V, 700).tolist()
+    nxt2 = [pend[2]] + synth.uniform_i32(N - 1, 0, V, 701).tolist()
+    r2 = b.verify([nxt6, nxt2], want_logits=True, seq_ids=[6, 2])
+    acc_o, em_o, log_o = st.verify_chain(nxt6[0], np.array(nxt6[1:], np.int32), want_logits=True)
+    assert float(np.max(np.abs(r2.logits[0] - log_o))) <= LOGIT_TOL
+    assert int(r2.accepted[0]) == acc_o and r2.emitted[0, :acc_o + 1].tolist() == em_o.tolist()
+    with pytest.raises(cuda.YuukaError):
+        b.verify([nxt6, nxt2], seq_ids=[3, 3])           # a sequence twice
+    with pytest.raises(cuda.YuukaError):
+        b.verify([nxt6, nxt2], seq_ids=[3, 8])           # outside the session
+    a.close(); b.close(); st.close()
+
+
+def test_copy_block_gives_a_private_copy_of_a_shared_prefix(tiny):
+    """KVPool.CopyBlock (model/qwen35/kv_pool.go:156-170): sequence 1 adopts sequence 0's prefix by pointing its
+    table at 0's full blocks and at a copy of the partly filled one; its logits then equal sequence 0's, and
+    what it appends lands in its own copy."""
+    cfg, gm, om = tiny
+    V, bs, cap = cfg["vocab"], 16, 64
+    per = cap // bs
+    sess = cuda.Session(gm, max_batch=2, max_nodes=4, capacity=cap, kv_format=cuda.KV_F16, block_size=bs)
+    prompt = synth.uniform_i32(24, 0, V, 800)            # one full block and half of the next
+    sess.forward(prompt, seq=0, want_logits=False)
+    # sequence 1: blocks of sequence 0 are 0..3, its own are 4..7
+    sess.copy_block(5, 1)
+    sess.set_block_table(1, [0, 5, 6, 7])
+    sess.restore(sess.snapshot(0), seq=1)
+    sess.set_position(1, 24)
+    nxt = synth.uniform_i32(3, 0, V, 801)
+    a = sess.forward(nxt, seq=0)
+    b = sess.forward(nxt, seq=1)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # the two sequences now diverge without disturbing one another
+    a2 = sess.forward([7], seq=0)
+    b2 = sess.forward([9], seq=1)
+    a3 = sess.forward([11], seq=0)
+    st = yo.State(om, cap, yo.KV_F16)
+    st.forward(prompt.tolist() + nxt.tolist() + [7])
+    assert float(np.max(np.abs(a3 - st.step(11)))) <= LOGIT_TOL
+    assert not np.array_equal(a2, b2)
+    with pytest.raises(cuda.YuukaError):
+        sess.copy_block(99, 0)
+    sess.close(); st.close()
+
+
+def test_a_step_cannot_be_launched_twice_before_it_is_fetched(tiny):
+    cfg, gm, om = tiny
+    sess = cuda.Session(gm, max_batch=1, max_nodes=4, capacity=32)
+    sess.forward([1, 2, 3], want_logits=False)
+    sess.stage([[5, 6, 7]])
+    sess.launch()
+    with pytest.raises(cuda.YuukaError):
+        sess.launch()                                    # would run and commit the same step again
+    res = sess.fetch()
+    assert sess.position() == 3 + int(res.accepted[0]) + 1
+    sess.close()

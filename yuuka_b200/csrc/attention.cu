@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
     const int kvh = blockIdx.y % p.kv_heads, qt = blockIdx.y / p.kv_heads;
     const int split = blockIdx.x;
     const int G = p.heads / p.kv_heads, N = p.rows.nodes;
-    const int pos0 = p.rows.pos0[seq];
+    const int sq = seq_of(p.rows, seq);
+    const int pos0 = p.rows.pos0[sq];
     const int total = pos0 + N;
     const int k_begin = split * p.key_split;
     const int k_end = min(total, k_begin + p.key_split);
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_partial_kernel(const
             int pos = k0 + j;
             float kw[8], vw[8];
             if (pos < k_end) {
-                int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
+                int block = p.pool.tables[(int64_t)sq * p.pool.table_stride + pos / p.pool.block_size];
                 int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
                 kv_decode8(p.pool.k + off, p.pool.format, kvh * (HD / 8) + c8, kw);
                 kv_decode8(p.pool.v + off, p.pool.format, kvh * (HD / 8) + c8, vw);
@@ -243,7 +244,8 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
     const int kvh = blockIdx.y % p.kv_heads, qt = blockIdx.y / p.kv_heads;
     const int split = blockIdx.x;
     const int G = p.heads / p.kv_heads, N = p.rows.nodes;
-    const int pos0 = p.rows.pos0[seq];
+    const int sq = seq_of(p.rows, seq);
+    const int pos0 = p.rows.pos0[sq];
     const int total = pos0 + N;
     const int k_begin = split * p.key_split;
     const int k_end = min(total, k_begin + p.key_split);
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
             nk[u] = make_uint4(0, 0, 0, 0);
             nv[u] = nk[u];
             if (i < PIECES && pos < k_end) {
-                const int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
+                const int block = p.pool.tables[(int64_t)sq * p.pool.table_stride + pos / p.pool.block_size];
                 const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
                 nk[u] = *reinterpret_cast<const uint4 *>(p.pool.k + off + (size_t)(kvh * HD + c8 * 8) * 2);
                 nv[u] = *reinterpret_cast<const uint4 *>(p.pool.v + off + (size_t)(kvh * HD + c8 * 8) * 2);
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
                 const int pos = k0 + j;
                 uint4 kh4 = make_uint4(0, 0, 0, 0), kl4 = kh4, vh4 = kh4;
                 if (pos < k_end) {
-                    const int block = p.pool.tables[(int64_t)seq * p.pool.table_stride + pos / p.pool.block_size];
+                    const int block = p.pool.tables[(int64_t)sq * p.pool.table_stride + pos / p.pool.block_size];
                     const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
                     float kw[8], vw[8];
                     kv_decode8(p.pool.k + off, p.pool.format, kvh * (HD / 8) + c8, kw);

@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(256) embedding_kernel(float * __restrict__ x, 
     }
     if (first.rope_cs) {
         const int seq = r / first.rows.nodes;
-        const int pos = first.rows.pos0[seq] + first.rows.depth[r];
+        const int pos = first.rows.pos0[seq_of(first.rows, seq)] + first.rows.depth[r];
         const int half = first.rope_dim / 2;
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             double theta = (double)pos * pow(first.rope_base, -2.0 * (double)i / (double)first.rope_dim);
@@ -255,7 +255,7 @@ __global__ void rope_table_kernel(float2 * __restrict__ cs, RowMeta rows, int ro
     pdl_entry();
     const int r = blockIdx.x;
     const int seq = r / rows.nodes;
-    const int pos = rows.pos0[seq] + rows.depth[r];
+    const int pos = rows.pos0[seq_of(rows, seq)] + rows.depth[r];
     const int half = rope_dim / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         double theta = (double)pos * pow(rope_base, -2.0 * (double)i / (double)rope_dim);
@@ -301,6 +301,7 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const PrepParams p) {
     pdl_entry();
     const int r = blockIdx.x;
     const int seq = r / p.rows.nodes, node = r - seq * p.rows.nodes;
+    const int sq = seq_of(p.rows, seq);
     const int unit = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= p.heads + 2 * p.kv_heads) return;
     const float2 * cs = p.rope_cs + (int64_t)r * (p.rope_dim / 2);
@@ -312,11 +313,11 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const PrepParams p) {
         const int h = unit - p.heads;
         float * k = p.k + (int64_t)r * p.ldk + (int64_t)h * p.hd;
         norm_rope_head(k, p.k_norm, p.hd, p.rope_dim, cs, p.eps);
-        const int64_t off = kv_row_offset(p.pool, seq, p.rows.pos0[seq] + node);
+        const int64_t off = kv_row_offset(p.pool, sq, p.rows.pos0[sq] + node);
         kv_encode_head(p.pool.k + off, p.pool.format, k, h * p.hd, p.hd);
     } else {
         const int h = unit - p.heads - p.kv_heads;
-        const int64_t off = kv_row_offset(p.pool, seq, p.rows.pos0[seq] + node);
+        const int64_t off = kv_row_offset(p.pool, sq, p.rows.pos0[sq] + node);
         kv_encode_head(p.pool.v + off, p.pool.format, p.v + (int64_t)r * p.ldv + (int64_t)h * p.hd, h * p.hd, p.hd);
     }
 }

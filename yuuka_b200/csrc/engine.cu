@@ -536,6 +536,7 @@ struct yuuka_session {
     int rows_cap = 0;
     int32_t * d_pos_sub = nullptr;   // [CHAIN_MAX_SUBS] first position of every sub-chunk of a wide prompt pass
     int32_t * d_acc_sub = nullptr;   // [CHAIN_MAX_SUBS] rows - 1 of every sub-chunk (its forced acceptance)
+    int32_t * d_seq_map = nullptr;   // [max_batch] which sequence each slot of the staged step is
     int32_t * d_tokens = nullptr;
     int32_t * d_parent = nullptr;
     int32_t * d_depth = nullptr;
@@ -576,6 +577,7 @@ struct yuuka_session {
     GemmScratch gemm;
     // staged step
     int st_seq0 = 0, st_batch = 0, st_nodes = 0;
+    std::vector<int> st_seqs;  // sequences of the staged step, slot by slot
     uint32_t st_mode = 0;
     float st_temperature = 0.0f;
     const float * st_draft_probs = nullptr;   // device, rejection mode
@@ -718,13 +720,17 @@ constexpr int CHAIN_MAX_SUBS = CHAIN_ROWS / CHAIN_SUB;
 
 // Enqueues one step over sequences [seq0, seq0+batch) with `nodes` rows each.
 // sub > 0: a wide prompt pass of one sequence (see CHAIN_ROWS), staged by stage_rows with the same sub.
+// mapped: the slots of the step are the sequences listed in d_seq_map (a verify batch; seq0 is 0 then);
+// otherwise slot b is sequence seq0 + b.
 void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, LogitRows logit_rows, int max_total,
-              int sub = 0) {
+              int sub = 0, bool mapped = false) {
     yuuka_model * m = s->model;
     const yuuka_model_config & c = m->cfg;
     cudaStream_t st = s->stream.s;
     const int R = batch * nodes, H = c.hidden;
     RowMeta rows{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos0 + seq0, batch, nodes};
+    if (mapped) rows.seq_map = s->d_seq_map;
+    YK_REQUIRE(!mapped || (seq0 == 0 && sub == 0), YUUKA_ERR_INTERNAL, "a mapped step starts at sequence 0 and has no sub-chunks");
     YK_REQUIRE(sub == 0 || (batch == 1 && mode == 3u && nodes <= CHAIN_MAX_SUBS * sub), YUUKA_ERR_INTERNAL,
                "a wide pass is one forced-commit chain");
     const int n_sub = sub > 0 ? (nodes + sub - 1) / sub : 1;
@@ -1031,7 +1037,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
         launch_kv_commit(st, s->d_kv_commit, (int)s->attn_layers.size(), geom, rows, s->acc);
         s->launches++;
     }
-    launch_advance_positions(st, s->d_pos0 + seq0, s->acc, batch);
+    launch_advance_positions(st, s->d_pos0 + seq0, s->acc, batch, rows.seq_map);
     s->launches++;
 }
 
@@ -1054,12 +1060,18 @@ void sync_and_check(yuuka_session * s) {
     YK_REQUIRE(err == 0, YUUKA_ERR_DEVICE, "a bounded wait inside a kernel expired (code %d); results are invalid", err);
 }
 
+// bytes of the per-step metadata block: ancestor masks, tokens, parents, depths of `cap` rows, the sub-chunk
+// positions and acceptances of a wide prompt pass, and the slot -> sequence map
+size_t rows_block_bytes(int cap, int max_batch) {
+    return (size_t)cap * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t) + (size_t)max_batch * sizeof(int32_t);
+}
+
 // Uploads row metadata of a step: tokens, parents, depths, ancestor masks.
 // sub > 0 (one sequence, a chain): the rows are a wide prompt pass whose mixers run in sub-chunks of `sub`
 // rows; parents, depths and ancestor masks then restart at every sub-chunk, and the sub-chunks' first
 // positions and forced acceptances go along.
 void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t * tokens, const int32_t * parent,
-                int sub = 0) {
+                int sub = 0, const int32_t * seq_ids = nullptr) {
     const int vocab = s->model->cfg.vocab;
     const int R = batch * nodes, cap = s->rows_cap;
     YK_REQUIRE(R <= cap, YUUKA_ERR_INTERNAL, "stage_rows: %d rows exceed the session's %d", R, cap);
@@ -1088,9 +1100,9 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
             dep[r] = i == 0 ? 0 : dep[b * nodes + p] + 1;
             anc[r] = (i == 0 ? 0ull : anc[b * nodes + p]) | (1ull << i);
         }
-        YK_REQUIRE(s->h_pos_upper[seq0 + b] + nodes <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
-                   "token sequence of %d exceeds remaining context %d", nodes,
-                   s->cfg.capacity - s->h_pos_upper[seq0 + b]);
+        const int sq = seq_ids ? seq_ids[b] : seq0 + b;
+        YK_REQUIRE(s->h_pos_upper[sq] + nodes <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
+                   "token sequence of %d exceeds remaining context %d", nodes, s->cfg.capacity - s->h_pos_upper[sq]);
     }
     int32_t * pos_sub = reinterpret_cast<int32_t *>(s->h_rows + (size_t)cap * 20);
     int32_t * acc_sub = pos_sub + CHAIN_MAX_SUBS;
@@ -1099,9 +1111,10 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
         pos_sub[k] = sub > 0 ? s->h_pos[seq0] + k * sub : 0;
         acc_sub[k] = (left > sub ? sub : (left > 0 ? left : 1)) - 1;
     }
+    int32_t * seq_map = acc_sub + CHAIN_MAX_SUBS;
+    for (int b = 0; b < s->cfg.max_batch; b++) seq_map[b] = b < batch ? (seq_ids ? seq_ids[b] : seq0 + b) : 0;
     // one copy for the whole block (the arrays keep their capacity-sized offsets on both sides)
-    YK_CUDA(cudaMemcpyAsync(s->d_rows, s->h_rows, (size_t)cap * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t), cudaMemcpyHostToDevice,
-                            s->stream.s));
+    YK_CUDA(cudaMemcpyAsync(s->d_rows, s->h_rows, rows_block_bytes(cap, s->cfg.max_batch), cudaMemcpyHostToDevice, s->stream.s));
 }
 
 // Key-range bound used to size the attention grid. It is the session capacity,
@@ -1151,6 +1164,16 @@ void validate_batch(const yuuka_session * s, const yuuka_verify_batch * b) {
     YK_REQUIRE(b->nodes > 0 && b->nodes <= s->cfg.max_nodes, YUUKA_ERR_INVALID_ARGUMENT,
                "verify: %d rows per sequence is outside 1..%d", b->nodes, s->cfg.max_nodes);
     YK_REQUIRE(b->tokens, YUUKA_ERR_INVALID_ARGUMENT, "verify: tokens is null");
+    if (b->seq_ids) {
+        std::vector<char> seen((size_t)s->cfg.max_batch, 0);
+        for (int i = 0; i < b->batch; i++) {
+            const int sq = b->seq_ids[i];
+            YK_REQUIRE(sq >= 0 && sq < s->cfg.max_batch, YUUKA_ERR_INVALID_ARGUMENT, "verify: sequence %d is outside 0..%d", sq,
+                       s->cfg.max_batch - 1);
+            YK_REQUIRE(!seen[(size_t)sq], YUUKA_ERR_INVALID_ARGUMENT, "verify: sequence %d appears twice in the batch", sq);
+            seen[(size_t)sq] = 1;
+        }
+    }
     YK_REQUIRE(b->mode == YUUKA_ACCEPT_GREEDY || b->mode == YUUKA_ACCEPT_NONE || b->mode == YUUKA_ACCEPT_REJECTION,
                YUUKA_ERR_INVALID_ARGUMENT, "verify: unknown acceptance mode %u", b->mode);
     if (b->mode == YUUKA_ACCEPT_REJECTION) {
@@ -1266,16 +1289,17 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             s->h_pos.assign(B, 0);
             s->h_pos_upper.assign(B, 0);
             s->rows_cap = R;
-            s->d_rows = dalloc<uint8_t>((size_t)R * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t), s->owned);
+            s->d_rows = dalloc<uint8_t>(rows_block_bytes(R, B), s->owned);
             s->d_pos_sub = reinterpret_cast<int32_t *>(s->d_rows + (size_t)R * 20);
             s->d_acc_sub = s->d_pos_sub + CHAIN_MAX_SUBS;
+            s->d_seq_map = s->d_acc_sub + CHAIN_MAX_SUBS;
             s->d_anc = reinterpret_cast<uint64_t *>(s->d_rows);
             s->d_tokens = reinterpret_cast<int32_t *>(s->d_rows + (size_t)R * 8);
             s->d_parent = s->d_tokens + R;
             s->d_depth = s->d_parent + R;
             {
                 void * hp = nullptr;
-                const size_t rows_bytes = (size_t)R * 20 + 2 * CHAIN_MAX_SUBS * sizeof(int32_t);
+                const size_t rows_bytes = rows_block_bytes(R, B);
                 YK_REQUIRE(cudaMallocHost(&hp, rows_bytes + sizeof(int32_t) * ((size_t)B + 2 * R + 2)) == cudaSuccess,
                            YUUKA_ERR_ALLOCATION, "page-locked staging allocation failed");
                 s->h_rows = (uint8_t *)hp;
@@ -1403,6 +1427,26 @@ yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const
     });
 }
 
+yuuka_status yuuka_session_copy_block(yuuka_session * s, int32_t dst_block, int32_t src_block) {
+    return guard([&] {
+        YK_REQUIRE(s, YUUKA_ERR_INVALID_ARGUMENT, "null session");
+        YK_REQUIRE(dst_block >= 0 && dst_block < s->cfg.pool_blocks && src_block >= 0 && src_block < s->cfg.pool_blocks,
+                   YUUKA_ERR_INVALID_ARGUMENT, "copy_block: block %d or %d is outside the KV pool of %d blocks", dst_block, src_block,
+                   s->cfg.pool_blocks);
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "copy_block: a launched verify step has not been fetched");
+        if (dst_block == src_block) return;
+        set_device(s->model->dev);
+        const size_t bytes = (size_t)s->cfg.block_size * s->kv_row_bytes;
+        for (int i : s->attn_layers) {
+            YK_CUDA(cudaMemcpyAsync(s->layers[i].k + (size_t)dst_block * bytes, s->layers[i].k + (size_t)src_block * bytes, bytes,
+                                    cudaMemcpyDeviceToDevice, s->stream.s));
+            YK_CUDA(cudaMemcpyAsync(s->layers[i].v + (size_t)dst_block * bytes, s->layers[i].v + (size_t)src_block * bytes, bytes,
+                                    cudaMemcpyDeviceToDevice, s->stream.s));
+        }
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+    });
+}
+
 yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq) {
     return guard([&] {
         check_seq(s, seq);
@@ -1510,7 +1554,9 @@ yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b)
         set_device(s->model->dev);
         // staging again before a launch replaces the step; the earlier copy out of the page-locked mirror must have left it
         if (s->staged) YK_CUDA(cudaStreamSynchronize(s->stream.s));
-        stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent);
+        stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent, 0, b->seq_ids);
+        s->st_seqs.resize((size_t)b->batch);
+        for (int i = 0; i < b->batch; i++) s->st_seqs[(size_t)i] = b->seq_ids ? b->seq_ids[i] : i;
         if (b->mode == YUUKA_ACCEPT_REJECTION) {
             const int V = s->model->cfg.vocab;
             if (!s->reject_residual) s->reject_residual = dalloc<unsigned long long>((size_t)s->cfg.max_batch * V, s->owned, false);
@@ -1540,7 +1586,7 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
         if (!s->use_graphs || s->st_mode == YUUKA_ACCEPT_REJECTION) {
             // (a rejection step carries a temperature and a buffer address that a replayed graph would freeze)
             s->launches = 0;
-            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total);
+            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
         } else {
             yuuka_session::StepGraph * gr = nullptr;
             for (auto & g : s->graphs)
@@ -1551,7 +1597,7 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
                 YK_CUDA(cudaStreamBeginCapture(s->stream.s, cudaStreamCaptureModeThreadLocal));
                 cudaGraph_t graph = nullptr;
                 try {
-                    run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total);
+                    run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
                 } catch (...) {
                     cudaStreamEndCapture(s->stream.s, &graph);
                     if (graph) cudaGraphDestroy(graph);
@@ -1569,7 +1615,7 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
             YK_CUDA(cudaGraphLaunch(gr->exec, s->stream.s));
         }
         if (s->st_mode != YUUKA_ACCEPT_NONE)
-            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
+            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seqs[(size_t)b]] += s->st_nodes;
         s->launched = true;
         if (completion) YK_CUDA(cudaEventRecord(completion->e, s->stream.s));
     });
@@ -1587,7 +1633,7 @@ yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes
         s->prof.clear();
         try {
             run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL,
-                     max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes));
+                     max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes), 0, true);
             mark(s, 0);
         } catch (...) {
             s->profiling = false;
@@ -1597,7 +1643,7 @@ yuuka_status yuuka_verify_launch_profiled(yuuka_session * s, uint32_t * op_codes
         }
         s->profiling = false;
         if (s->st_mode != YUUKA_ACCEPT_NONE)
-            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seq0 + b] += s->st_nodes;
+            for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seqs[(size_t)b]] += s->st_nodes;
         s->launched = true;
         cudaError_t err = cudaStreamSynchronize(s->stream.s);
         uint64_t n = s->prof.empty() ? 0 : s->prof.size() - 1;
@@ -1639,8 +1685,9 @@ yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * b)
             if (b->path) memcpy(b->path, s->h_results + maxB, sizeof(int32_t) * B * N);
             if (b->emitted) memcpy(b->emitted, s->h_results + maxB + cap, sizeof(int32_t) * B * N);
             for (int i = 0; i < B; i++) {
-                s->h_pos[s->st_seq0 + i] += acc[i] + 1;
-                s->h_pos_upper[s->st_seq0 + i] = s->h_pos[s->st_seq0 + i];
+                const int sq = s->st_seqs[(size_t)i];
+                s->h_pos[sq] += acc[i] + 1;
+                s->h_pos_upper[sq] = s->h_pos[sq];
             }
         }
         if (b->logits)

@@ -64,7 +64,7 @@ __global__ void gdn_front_kernel(const ScanParams p) {
     const int c = u * S + e;  // q units, then k units, then v units: exactly the conv row order
     float taps[8];
     {
-        const float * hist = a.conv_state + ((int64_t)seq * conv_dim + c) * K1;
+        const float * hist = a.conv_state + ((int64_t)seq_of(p.rows, seq) * conv_dim + c) * K1;
         int cur = node, hidx = K1 - 1;
 #pragma unroll
         for (int t = 7; t >= 0; t--) {
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     __shared__ float scale_s[GDN_MAX_NODES];
 
     // stored state: the longest fetch (HBM), issued first
-    const float * s0 = a.state + ((int64_t)(seq * a.rank + h) * S + rq * RPL) * S + col;
+    const float * s0 = a.state + ((int64_t)(seq_of(p.rows, seq) * a.rank + h) * S + rq * RPL) * S + col;
     float st[RPL];
 #pragma unroll
     for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
         constexpr int MAXR = 4;
         const int h = blockIdx.x / COMMIT_PARTS, part = blockIdx.x % COMMIT_PARTS, kh = h % p.groups;
         const int rows_part = S / COMMIT_PARTS, i_base = part * rows_part;
-        float * st = L.state + (int64_t)((p.seq_base + seq) * p.rank + h) * S * S;
+        float * st = L.state + (int64_t)((p.seq_base + seq_of(p.rows, seq)) * p.rank + h) * S * S;
         __shared__ float kh_s[GDN_MAX_NODES][32];
         __shared__ __align__(16) float d_s[GDN_MAX_NODES][128];
         __shared__ float dec_s[GDN_MAX_NODES];
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
         const int per = (p.conv_dim + COMMIT_CONV_PARTS - 1) / COMMIT_CONV_PARTS;
         const int c_end = min(p.conv_dim, (part + 1) * per);
         for (int c = part * per + threadIdx.x; c < c_end; c += blockDim.x) {
-            float * hist = L.conv_state + ((int64_t)(p.seq_base + seq) * p.conv_dim + c) * K1;
+            float * hist = L.conv_state + ((int64_t)(p.seq_base + seq_of(p.rows, seq)) * p.conv_dim + c) * K1;
             float nv[8];
 #pragma unroll
             for (int t = 0; t < 8; t++) {
@@ -448,14 +448,15 @@ __global__ void kv_commit_kernel(const KvCommitParams p) {
     const KvLayerCommit L = p.layers[blockIdx.y];
     const int seq = blockIdx.x, N = p.rows.nodes;
     const int a = p.acc.accepted[seq];
-    const int pos0 = p.rows.pos0[seq];
+    const int sq = seq_of(p.rows, seq);
+    const int pos0 = p.rows.pos0[sq];
     const int32_t * path = p.acc.path + (int64_t)seq * N;
     const int words = p.geom.row_bytes / 2;
     for (int t = 1; t <= a; t++) {
         const int node = path[t - 1];
         if (node != t) {
             auto off = [&](int slot) {
-                int block = p.geom.tables[(int64_t)seq * p.geom.table_stride + slot / p.geom.block_size];
+                int block = p.geom.tables[(int64_t)sq * p.geom.table_stride + slot / p.geom.block_size];
                 return ((int64_t)block * p.geom.block_size + slot % p.geom.block_size) * p.geom.row_bytes;
             };
             const int64_t src = off(pos0 + node), dst = off(pos0 + t);
@@ -481,14 +482,14 @@ void launch_kv_commit(cudaStream_t s, const KvLayerCommit * layers_dev, int n_la
     YK_CUDA(cudaGetLastError());
 }
 
-__global__ void advance_positions_kernel(int32_t * pos0, const int32_t * accepted, int batch) {
+__global__ void advance_positions_kernel(int32_t * pos0, const int32_t * accepted, int batch, const int32_t * seq_map) {
     pdl_entry();
     int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < batch) pos0[b] += accepted[b] + 1;
+    if (b < batch) pos0[seq_map ? seq_map[b] : b] += accepted[b] + 1;
 }
 
-void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch) {
-    launch_k(advance_positions_kernel, (batch + 127) / 128, 128, 0, s, pos0, acc.accepted, batch);
+void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch, const int32_t * seq_map) {
+    launch_k(advance_positions_kernel, (batch + 127) / 128, 128, 0, s, pos0, acc.accepted, batch, seq_map);
     YK_CUDA(cudaGetLastError());
 }
 

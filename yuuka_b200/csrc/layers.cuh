@@ -12,9 +12,16 @@ struct RowMeta {
     const int32_t * parent;    // [rows] node index of the preceding row within the sequence, -1 for node 0
     const int32_t * depth;     // [rows] number of ancestors
     const uint64_t * anc_mask; // [rows] bit j set iff node j is the row itself or one of its ancestors
-    const int32_t * pos0;      // [batch] committed positions of each sequence
+    const int32_t * pos0;      // committed positions, indexed by sequence (see seq_map)
     int batch, nodes;
+    // [batch] or null: which of the session's sequences each slot of the step is. Positions, block tables,
+    // recurrent state and conv history are indexed by it; everything that only lives for the step (rows,
+    // logits, results) is indexed by the slot. Null: slot b is sequence b of the arrays as passed.
+    const int32_t * seq_map = nullptr;
 };
+#ifdef __CUDACC__
+__device__ __forceinline__ int seq_of(const RowMeta & rows, int slot) { return rows.seq_map ? rows.seq_map[slot] : slot; }
+#endif
 
 struct KvPool {
     uint8_t * k;
@@ -133,7 +140,7 @@ struct KvLayerCommit {
 };
 void launch_kv_commit(cudaStream_t s, const KvLayerCommit * layers_dev, int n_layers, const KvPool & geom,
                       const RowMeta & rows, const AcceptOut & acc);
-void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch);
+void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch, const int32_t * seq_map = nullptr);
 
 // qwen35moe block (moe.cu)
 struct GemmSegment;

@@ -60,7 +60,6 @@ yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t *
     return guard([&] {
         YK_REQUIRE(s && prompt && req && tokens && result, YUUKA_ERR_INVALID_ARGUMENT, "spec_generate: null argument");
         *result = yuuka_spec_result{};
-        YK_REQUIRE(seq == 0, YUUKA_ERR_UNSUPPORTED, "spec_generate: drives sequence 0 of the session");
         YK_REQUIRE(n_prompt > 0, YUUKA_ERR_INVALID_ARGUMENT, "prompt is empty");
         YK_REQUIRE(req->max_tokens > 0, YUUKA_ERR_INVALID_ARGUMENT, "max tokens must be positive");
         yuuka_session_info info{};
@@ -86,8 +85,8 @@ yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t *
         result->prompt_tokens = n_prompt;
         result->finish_reason = YUUKA_FINISH_LENGTH;
 
-        inner(yuuka_session_reset(s, 0));
-        inner(yuuka_session_forward(s, 0, prompt, n_prompt, logits.data()));
+        inner(yuuka_session_reset(s, seq));
+        inner(yuuka_session_forward(s, seq, prompt, n_prompt, logits.data()));
         // argmaxLogit, engine/speculative.go:263-271: first index of the maximum
         int32_t pending = 0;
         for (int i = 1; i < info.vocab; i++)
@@ -122,6 +121,7 @@ yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t *
             vb.mode = YUUKA_ACCEPT_GREEDY;
             vb.accepted = &accepted;
             vb.emitted = emitted.data();
+            vb.seq_ids = &seq;
             inner(yuuka_verify_step(s, &vb));
             result->steps++;
             result->draft_tokens += k;

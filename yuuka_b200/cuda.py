@@ -90,7 +90,7 @@ class VerifyBatch(C.Structure):
     _fields_ = [("batch", C.c_int32), ("nodes", C.c_int32), ("tokens", C.c_void_p),
                 ("parent", C.c_void_p), ("mode", C.c_uint32), ("temperature", C.c_float),
                 ("draft_probs", C.c_void_p), ("uniforms", C.c_void_p), ("accepted", C.c_void_p),
-                ("emitted", C.c_void_p), ("path", C.c_void_p), ("logits", C.c_void_p)]
+                ("emitted", C.c_void_p), ("path", C.c_void_p), ("logits", C.c_void_p), ("seq_ids", C.c_void_p)]
 
 
 # name -> (restype, argtypes); the exported symbol list the ABI test checks
@@ -161,6 +161,7 @@ SIGNATURES = {
     "yuuka_session_create": (_i32, [_vp, _vp, _vp]),
     "yuuka_session_destroy": (None, [_vp]),
     "yuuka_session_set_block_table": (_i32, [_vp, _i32, _vp, _i32]),
+    "yuuka_session_copy_block": (_i32, [_vp, _i32, _i32]),
     "yuuka_session_reset": (_i32, [_vp, _i32]),
     "yuuka_session_set_position": (_i32, [_vp, _i32, _i32]),
     "yuuka_session_position": (_i32, [_vp, _i32, _vp]),
@@ -413,14 +414,15 @@ def spec_lookup_draft(history, max_draft: int, min_match: int) -> list[int]:
     return out[:n].tolist()
 
 
-def spec_generate(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, min_match: int = 0, stop_tokens=()):
-    """generateSpeculative (engine/speculative.go:68-251) on sequence 0 of sess; returns (tokens, SpecResult)."""
+def spec_generate(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, min_match: int = 0, stop_tokens=(),
+                  seq: int = 0):
+    """generateSpeculative (engine/speculative.go:68-251) on sequence seq of sess; returns (tokens, SpecResult)."""
     p = np.ascontiguousarray(prompt, np.int32)
     stops = np.ascontiguousarray(list(stop_tokens), np.int32)
     req = SpecRequest(max_tokens, SpecOptions(max_draft, min_match), stops.ctypes.data if stops.size else None, stops.size)
     out = np.zeros(max(max_tokens, 1), np.int32)
     res = SpecResult()
-    check(lib().yuuka_spec_generate(sess.h, 0, p.ctypes.data, p.size, C.byref(req), out.ctypes.data, C.byref(res)))
+    check(lib().yuuka_spec_generate(sess.h, seq, p.ctypes.data, p.size, C.byref(req), out.ctypes.data, C.byref(res)))
     return out[:res.output_tokens].tolist(), res
 
 
@@ -612,7 +614,10 @@ class Session:
                                           out.ctypes.data_as(C.c_void_p) if want_logits else None))
         return out
 
-    def _batch(self, tokens, parent, mode, want_logits, temperature=1.0, draft_probs=None, uniforms=None):
+    def copy_block(self, dst_block: int, src_block: int):
+        check(lib().yuuka_session_copy_block(self.h, dst_block, src_block))
+
+    def _batch(self, tokens, parent, mode, want_logits, temperature=1.0, draft_probs=None, uniforms=None, seq_ids=None):
         tokens = np.ascontiguousarray(tokens, np.int32)
         if tokens.ndim == 1:
             tokens = tokens[None, :]
@@ -638,6 +643,10 @@ class Session:
         vb.emitted = keep["emitted"].ctypes.data
         vb.path = keep["path"].ctypes.data
         vb.logits = keep["logits"].ctypes.data if want_logits else None
+        if seq_ids is not None:
+            keep["seq_ids"] = np.ascontiguousarray(seq_ids, np.int32)
+            assert keep["seq_ids"].size == B
+            vb.seq_ids = keep["seq_ids"].ctypes.data
         return vb, keep
 
     @staticmethod
@@ -645,18 +654,18 @@ class Session:
         return VerifyResult(keep["accepted"], keep["emitted"], keep["path"], keep["logits"])
 
     def verify(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False,
-               temperature: float = 1.0, draft_probs: "Buffer | None" = None, uniforms=None) -> VerifyResult:
+               temperature: float = 1.0, draft_probs: "Buffer | None" = None, uniforms=None, seq_ids=None) -> VerifyResult:
         """One verify step; tokens [batch, nodes] with the pending token in column 0.
 
         mode ACCEPT_REJECTION needs temperature, draft_probs (device Buffer, f32 [batch, nodes, vocab])
         and uniforms (f32 [batch, nodes, 2] in [0, 1)).
         """
-        vb, keep = self._batch(tokens, parent, mode, want_logits, temperature, draft_probs, uniforms)
+        vb, keep = self._batch(tokens, parent, mode, want_logits, temperature, draft_probs, uniforms, seq_ids)
         check(lib().yuuka_verify_step(self.h, C.byref(vb)))
         return self._result(keep)
 
-    def stage(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False):
-        vb, keep = self._batch(tokens, parent, mode, want_logits)
+    def stage(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False, seq_ids=None):
+        vb, keep = self._batch(tokens, parent, mode, want_logits, seq_ids=seq_ids)
         check(lib().yuuka_verify_stage(self.h, C.byref(vb)))
         self._staged = (vb, keep)
 
