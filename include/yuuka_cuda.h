@@ -463,6 +463,18 @@ typedef struct yuuka_spec_result {
  * context capacity. tokens must hold max_tokens ids. The emitted stream equals
  * plain greedy decoding. The session needs max_nodes >= 2 to draft at all
  * (drafts per step are capped at max_nodes - 1). Synchronous. */
+/* lookupDraft on the device (history: int32 ids in a device buffer): out receives the draft length and then the
+ * draft ids, int32[1 + max_draft]. Same result as yuuka_spec_lookup_draft, id for id. Synchronous. */
+YUUKA_API yuuka_status yuuka_spec_lookup_draft_device(yuuka_stream * stream, const yuuka_buffer * history, int32_t n,
+                                                      int32_t max_draft, int32_t min_match, yuuka_buffer * out);
+/* yuuka_spec_generate with the drafting done by a kernel between the steps (the step before verify in the
+ * loop, engine/speculative.go:161): every step has max_draft + 1 rows, the history stays on the device, and
+ * `burst` (1..64) steps are enqueued per host synchronization. The emitted stream is the same greedy stream.
+ * Stop tokens and max_tokens are applied when a burst returns, so the sequence may have run up to one burst
+ * past the last returned token; result->steps counts the steps that ran. */
+YUUKA_API yuuka_status yuuka_spec_generate_device(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
+                                                  const yuuka_spec_request * req, int32_t burst, int32_t * tokens,
+                                                  yuuka_spec_result * result);
 YUUKA_API yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
                                            const yuuka_spec_request * request, int32_t * tokens,
                                            yuuka_spec_result * result);

@@ -150,3 +150,65 @@ def test_generation_on_another_sequence_of_the_session(tiny):
     assert sess.position(0) == 3 and sess.position(1) == 0
     assert sess.position(2) == len(prompt) + res.output_tokens - 1 or sess.position(2) == len(prompt) + res.output_tokens
     sess.close()
+
+
+def test_device_lookup_draft_equals_the_host_lookup():
+    """lookupDraft on the device against yuuka_spec_lookup_draft: the reference's three vectors
+    (engine/speculative_test.go:139-151) and random histories over a small alphabet (many repeats)."""
+    dev = cuda.Device(0)
+    cases = [([1, 2, 3, 4, 1, 2], 3, 2), ([1, 2, 3, 4], 3, 2), ([5, 6, 7, 5, 6, 8, 5, 6], 2, 2)]
+    wants = [[3, 4, 1], [], [8, 5]]
+    for (h, md, mm), want in zip(cases, wants):
+        assert cuda.spec_lookup_draft(h, md, mm) == want
+        assert cuda.spec_lookup_draft_device(dev, h, md, mm) == want
+    rng = np.random.default_rng(9)
+    for trial in range(60):
+        n = int(rng.integers(1, 700))
+        alphabet = int(rng.integers(2, 12))
+        h = rng.integers(0, alphabet, n).astype(np.int32)
+        md, mm = int(rng.integers(1, 17)), int(rng.integers(1, 9))
+        assert cuda.spec_lookup_draft_device(dev, h, md, mm) == cuda.spec_lookup_draft(h, md, mm), (trial, n, md, mm)
+    dev.close()
+
+
+@pytest.mark.parametrize("scale,burst,min_match", [(0.0, 4, 2), (0.1, 3, 1), (1.0, 1, 2)])
+def test_device_drafted_generation_emits_the_greedy_stream(tiny, scale, burst, min_match):
+    """Steps of max_draft + 1 rows with the drafting between them on the device, `burst` steps per host
+    synchronization: same tokens as the host loop and as greedy decoding by the oracle, with drafts that
+    mostly hit (scale 0: the stream falls into a cycle), mostly miss (0.1) or hardly occur (the plain model)."""
+    cfg, gm0, om0 = tiny
+    if scale == 1.0:
+        gm, om, owned = gm0, om0, False
+    else:
+        gm, om = damped_model(cfg, gm0.dev, scale)
+        owned = True
+    prompt = synth.uniform_i32(12, 0, cfg["vocab"], 70).tolist()
+    n = 200
+    want, gaps = oracle_greedy(om, prompt, n, capacity=512)
+    a = cuda.Session(gm, max_batch=2, max_nodes=9, capacity=512, kv_format=cuda.KV_F32)
+    host, res_h = cuda.spec_generate(a, prompt, n, max_draft=8, min_match=min_match)
+    b = cuda.Session(gm, max_batch=2, max_nodes=9, capacity=512, kv_format=cuda.KV_F32)
+    got, res_d = cuda.spec_generate_device(b, prompt, n, max_draft=8, min_match=min_match, seq=1, burst=burst)
+    agreed = agree(got, want, gaps)
+    assert agreed >= 100, f"stream forked at a near-tie after {agreed} tokens; pick another seed"
+    assert len(got) == n and res_d.prompt_tokens == len(prompt) and res_d.finish_reason == cuda.FINISH_LENGTH
+    if agreed == n:
+        assert got == host
+    assert 0 <= res_d.accepted_draft <= res_d.draft_tokens
+    if scale == 0.0:
+        # the cycle is predicted: most drafts are accepted and far fewer steps than tokens run
+        assert res_d.accepted_draft > res_d.draft_tokens // 2 and res_d.steps < n // 2
+        assert res_d.draft_tokens == res_h.draft_tokens or res_d.steps <= res_h.steps + burst
+    elif scale == 0.1:
+        assert res_d.draft_tokens > 20 and res_d.accepted_draft < res_d.draft_tokens // 2
+    # a stop token ends the stream before it
+    stop = got[30]
+    cut, res_s = cuda.spec_generate_device(b, prompt, n, max_draft=8, min_match=min_match, seq=1, burst=burst, stop_tokens=[stop])
+    assert cut == got[:got.index(stop)] and res_s.finish_reason == cuda.FINISH_STOP
+    # capacity: generation ends when fewer than max_draft + 1 positions remain
+    small = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=40, kv_format=cuda.KV_F32)
+    tail, res_c = cuda.spec_generate_device(small, prompt, 1000, max_draft=4, min_match=min_match, burst=burst)
+    assert 40 - 12 - 5 <= len(tail) <= 40 - 12 and tail == got[:len(tail)] and small.position() <= 40
+    a.close(); b.close(); small.close()
+    if owned:
+        gm.close(); om.close()

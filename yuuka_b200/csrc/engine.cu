@@ -578,6 +578,12 @@ struct yuuka_session {
     // staged step
     int st_seq0 = 0, st_batch = 0, st_nodes = 0;
     std::vector<int> st_seqs;  // sequences of the staged step, slot by slot
+    // device-drafted generation (yuuka_spec_generate_device): token history of the generating sequence,
+    // its length, and [steps, draft tokens, accepted drafts, draft length of the staged step]
+    int32_t * d_hist = nullptr;
+    int32_t * d_hist_len = nullptr;
+    int32_t * d_spec_stats = nullptr;
+    int hist_cap = 0;
     uint32_t st_mode = 0;
     float st_temperature = 0.0f;
     const float * st_draft_probs = nullptr;   // device, rejection mode
@@ -1189,6 +1195,43 @@ void validate_batch(const yuuka_session * s, const yuuka_verify_batch * b) {
     YK_REQUIRE(s->logits, YUUKA_ERR_INVALID_ARGUMENT, "verify: the session has no logits buffer");
 }
 
+// Enqueues the kernels of the staged step on the session stream: by graph replay (captured at the first step
+// of a shape), or directly for a rejection step, which carries a temperature and a buffer address that a
+// replayed graph would freeze.
+void enqueue_staged_step(yuuka_session * s) {
+    const int max_total = max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes);
+    if (!s->use_graphs || s->st_mode == YUUKA_ACCEPT_REJECTION) {
+        s->launches = 0;
+        run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
+        return;
+    }
+    yuuka_session::StepGraph * gr = nullptr;
+    for (auto & g : s->graphs)
+        if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.mode == s->st_mode) gr = &g;
+    if (!gr) {
+        // first step of this shape: capture the kernel sequence once, replay it afterwards
+        s->launches = 0;
+        YK_CUDA(cudaStreamBeginCapture(s->stream.s, cudaStreamCaptureModeThreadLocal));
+        cudaGraph_t graph = nullptr;
+        try {
+            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
+        } catch (...) {
+            cudaStreamEndCapture(s->stream.s, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        YK_CUDA(cudaStreamEndCapture(s->stream.s, &graph));
+        cudaGraphExec_t exec = nullptr;
+        cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        YK_CUDA(err);
+        s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, exec, s->launches});
+        gr = &s->graphs.back();
+    }
+    s->launches = gr->launches;
+    YK_CUDA(cudaGraphLaunch(gr->exec, s->stream.s));
+}
+
 }  // namespace
 
 extern "C" {
@@ -1582,38 +1625,7 @@ yuuka_status yuuka_verify_launch(yuuka_session * s, yuuka_event * completion) {
         YK_REQUIRE(s && s->staged, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: no staged step");
         YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "verify_launch: the staged step is already running; fetch it first");
         set_device(s->model->dev);
-        const int max_total = max_total_keys(s, s->st_seq0, s->st_batch, s->st_nodes);
-        if (!s->use_graphs || s->st_mode == YUUKA_ACCEPT_REJECTION) {
-            // (a rejection step carries a temperature and a buffer address that a replayed graph would freeze)
-            s->launches = 0;
-            run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
-        } else {
-            yuuka_session::StepGraph * gr = nullptr;
-            for (auto & g : s->graphs)
-                if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.mode == s->st_mode) gr = &g;
-            if (!gr) {
-                // first step of this shape: capture the kernel sequence once, replay it afterwards
-                s->launches = 0;
-                YK_CUDA(cudaStreamBeginCapture(s->stream.s, cudaStreamCaptureModeThreadLocal));
-                cudaGraph_t graph = nullptr;
-                try {
-                    run_step(s, s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, LOGITS_ALL, max_total, 0, true);
-                } catch (...) {
-                    cudaStreamEndCapture(s->stream.s, &graph);
-                    if (graph) cudaGraphDestroy(graph);
-                    throw;
-                }
-                YK_CUDA(cudaStreamEndCapture(s->stream.s, &graph));
-                cudaGraphExec_t exec = nullptr;
-                cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
-                cudaGraphDestroy(graph);
-                YK_CUDA(err);
-                s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, exec, s->launches});
-                gr = &s->graphs.back();
-            }
-            s->launches = gr->launches;
-            YK_CUDA(cudaGraphLaunch(gr->exec, s->stream.s));
-        }
+        enqueue_staged_step(s);
         if (s->st_mode != YUUKA_ACCEPT_NONE)
             for (int b = 0; b < s->st_batch; b++) s->h_pos_upper[s->st_seqs[(size_t)b]] += s->st_nodes;
         s->launched = true;
@@ -1704,6 +1716,138 @@ yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_batch * b) 
         return st;
     }
     return yuuka_verify_fetch(s, b);
+}
+
+// generateSpeculative (engine/speculative.go:68-251) with the drafting on the device: every step has
+// max_draft + 1 rows, a kernel behind each step appends what it emitted to a device-resident history, looks up
+// the next draft there (lookupDraft, speculative.go:39-66) and writes the next step's token rows, so `burst`
+// steps are enqueued back to back and the host synchronizes once per burst. Rows the draft does not fill
+// repeat the pending token; the greedy walk accepts a row only if it is the model's own next token, so the
+// emitted stream is the greedy stream whatever the rows hold. Stop tokens and max_tokens are applied by the
+// host when a burst returns: the sequence may have run up to one burst past the end (its state is not
+// rewound; the reference resets the state before the next request).
+yuuka_status yuuka_spec_generate_device(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
+                                        const yuuka_spec_request * req, int32_t burst, int32_t * tokens,
+                                        yuuka_spec_result * result) {
+    return guard([&] {
+        YK_REQUIRE(s && prompt && req && tokens && result, YUUKA_ERR_INVALID_ARGUMENT, "spec_generate_device: null argument");
+        *result = yuuka_spec_result{};
+        check_seq(s, seq);
+        YK_REQUIRE(n_prompt > 0, YUUKA_ERR_INVALID_ARGUMENT, "prompt is empty");
+        YK_REQUIRE(req->max_tokens > 0, YUUKA_ERR_INVALID_ARGUMENT, "max tokens must be positive");
+        YK_REQUIRE(burst >= 1 && burst <= 64, YUUKA_ERR_INVALID_ARGUMENT, "spec_generate_device: burst %d is outside 1..64", burst);
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "a launched verify step has not been fetched");
+        YK_REQUIRE(s->logits, YUUKA_ERR_INVALID_ARGUMENT, "the session was created without want_logits");
+        const int cap = s->cfg.capacity, V = s->model->cfg.vocab;
+        YK_REQUIRE(n_prompt <= cap, YUUKA_ERR_INVALID_ARGUMENT, "prompt length %d exceeds context capacity %d", n_prompt, cap);
+        const int max_tokens = req->max_tokens < cap - n_prompt ? req->max_tokens : cap - n_prompt;
+        YK_REQUIRE(max_tokens > 0, YUUKA_ERR_INVALID_ARGUMENT, "no context space remains for generated tokens");
+        YK_REQUIRE(req->n_stop >= 0 && (req->n_stop == 0 || req->stop_tokens), YUUKA_ERR_INVALID_ARGUMENT,
+                   "spec_generate_device: stop token list is null");
+        yuuka_spec_options so = req->options;
+        yuuka_spec_options_normalize(&so);
+        if (so.max_draft > s->cfg.max_nodes - 1) so.max_draft = s->cfg.max_nodes - 1;
+        const int nodes = so.max_draft + 1;
+        set_device(s->model->dev);
+        cudaStream_t st = s->stream.s;
+        if (!s->d_hist) {
+            s->hist_cap = cap + 2;
+            s->d_hist = dalloc<int32_t>((size_t)s->hist_cap, s->owned);
+            s->d_hist_len = dalloc<int32_t>(1, s->owned);
+            s->d_spec_stats = dalloc<int32_t>(4, s->owned);
+        }
+        auto is_stop = [&](int32_t t) {
+            for (int i = 0; i < req->n_stop; i++)
+                if (req->stop_tokens[i] == t) return true;
+            return false;
+        };
+        result->prompt_tokens = n_prompt;
+        result->finish_reason = YUUKA_FINISH_LENGTH;
+
+        // prompt, first token (argmaxLogit, engine/speculative.go:263-271: first index of the maximum)
+        if (yuuka_session_reset(s, seq) != YUUKA_OK) throw StatusError{YUUKA_ERR_DEVICE};
+        std::vector<float> logits((size_t)V);
+        run_chain(s, seq, prompt, n_prompt, nullptr, logits.data());
+        int32_t pending = 0;
+        for (int i = 1; i < V; i++)
+            if (logits[(size_t)i] > logits[(size_t)pending]) pending = i;
+        int n_out = 0;
+        bool done = false;
+        auto emit = [&](int32_t t) {
+            if (is_stop(t)) {
+                result->finish_reason = YUUKA_FINISH_STOP;
+                return true;
+            }
+            tokens[n_out++] = t;
+            return n_out >= max_tokens;
+        };
+        done = emit(pending);
+        if (done) {
+            result->output_tokens = n_out;
+            return;
+        }
+        // history on the device: the prompt and the pending token
+        std::vector<int32_t> hist(prompt, prompt + n_prompt);
+        hist.push_back(pending);
+        int hist_len = (int)hist.size();
+        YK_CUDA(cudaMemcpyAsync(s->d_hist, hist.data(), hist.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+        YK_CUDA(cudaMemcpyAsync(s->d_hist_len, &hist_len, sizeof(int32_t), cudaMemcpyHostToDevice, st));
+        YK_CUDA(cudaMemsetAsync(s->d_spec_stats, 0, 4 * sizeof(int32_t), st));
+        // chain metadata of a step (parents, depths, ancestor masks, the slot's sequence); the token rows are
+        // written by the draft kernel
+        if (s->h_pos_upper[seq] + nodes > cap) {
+            // fewer than max_draft + 1 positions remain: generation ends here (the host loop would go on with
+            // shorter steps)
+            result->output_tokens = n_out;
+            return;
+        }
+        std::vector<int32_t> zeros((size_t)nodes, 0);
+        stage_rows(s, 0, 1, nodes, zeros.data(), nullptr, 0, &seq);
+        s->st_seq0 = 0;
+        s->st_batch = 1;
+        s->st_nodes = nodes;
+        s->st_mode = YUUKA_ACCEPT_GREEDY;
+        s->st_seqs.assign(1, seq);
+        DraftParams dp{};
+        dp.hist = s->d_hist;
+        dp.hist_len = s->d_hist_len;
+        dp.hist_cap = s->hist_cap;
+        dp.rows_tokens = s->d_tokens;
+        dp.nodes = nodes;
+        dp.max_draft = so.max_draft;
+        dp.min_match = so.min_match;
+        dp.stats = s->d_spec_stats;
+        launch_spec_draft(st, dp);
+        dp.accepted = s->acc.accepted;
+        dp.emitted = s->acc.emitted;
+        int32_t stats[4] = {0, 0, 0, 0};
+        while (!done) {
+            int enq = 0;
+            for (; enq < burst && s->h_pos_upper[seq] + nodes <= cap; enq++) {
+                enqueue_staged_step(s);
+                launch_spec_draft(st, dp);
+                s->h_pos_upper[seq] += nodes;
+            }
+            if (enq == 0) break;  // the context is full
+            int new_len = 0, pos = 0;
+            YK_CUDA(cudaMemcpyAsync(&new_len, s->d_hist_len, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+            YK_CUDA(cudaMemcpyAsync(&pos, s->d_pos0 + seq, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+            YK_CUDA(cudaMemcpyAsync(stats, s->d_spec_stats, sizeof stats, cudaMemcpyDeviceToHost, st));
+            sync_and_check(s);
+            s->h_pos[seq] = s->h_pos_upper[seq] = pos;
+            if (new_len > hist_len) {
+                hist.resize((size_t)new_len);
+                YK_CUDA(cudaMemcpy(hist.data() + hist_len, s->d_hist + hist_len, (size_t)(new_len - hist_len) * sizeof(int32_t),
+                                   cudaMemcpyDeviceToHost));
+                for (int i = hist_len; i < new_len && !done; i++) done = emit(hist[(size_t)i]);
+                hist_len = new_len;
+            }
+        }
+        result->output_tokens = n_out;
+        result->steps = stats[0];
+        result->draft_tokens = stats[1];
+        result->accepted_draft = stats[2];
+    });
 }
 
 yuuka_stream * yuuka_session_stream(yuuka_session * s) { return s ? &s->stream : nullptr; }

@@ -140,6 +140,24 @@ struct KvLayerCommit {
 };
 void launch_kv_commit(cudaStream_t s, const KvLayerCommit * layers_dev, int n_layers, const KvPool & geom,
                       const RowMeta & rows, const AcceptOut & acc);
+// Device-side prompt-lookup draft of one sequence (draft.cu). The kernel first appends the tokens the previous
+// step emitted (accepted != null) to the history, then looks up the next draft and writes the next step's token
+// rows: the pending token, the draft, and the pending token again in the rows the draft does not fill.
+struct DraftParams {
+    int32_t * hist;            // tokens of the sequence so far; the last one is pending (emitted, not yet run)
+    int32_t * hist_len;
+    int hist_cap;
+    const int32_t * accepted;  // the step that just ran: accepted count and emitted tokens of the slot, or null
+    const int32_t * emitted;
+    int32_t * rows_tokens;     // [nodes] token rows of the next step, or null
+    int nodes;
+    int max_draft, min_match;
+    int32_t * stats;           // [4] or null: steps, draft tokens, accepted drafts, draft length of the staged step
+    int32_t * draft_out;       // optional: the draft tokens alone
+    int32_t * k_out;           // optional: the draft length
+};
+void launch_spec_draft(cudaStream_t s, const DraftParams & p);
+
 void launch_advance_positions(cudaStream_t s, int32_t * pos0, const AcceptOut & acc, int batch, const int32_t * seq_map = nullptr);
 
 // qwen35moe block (moe.cu)

@@ -137,6 +137,8 @@ SIGNATURES = {
     "yuuka_spec_options_normalize": (None, [_vp]),
     "yuuka_spec_lookup_draft": (_i32, [_vp, _i32, _i32, _i32, _vp]),
     "yuuka_spec_generate": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp]),
+    "yuuka_spec_generate_device": (_i32, [_vp, _i32, _vp, _i32, _vp, _i32, _vp, _vp]),
+    "yuuka_spec_lookup_draft_device": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "yuuka_weights_tiled_bytes": (_u64, [_u32, _u64, _u64]),
     "yuuka_weights_tile": (_i32, [_vp, _vp, _u64, _vp, _u64, _u32, _u64, _u64, _vp]),
     "yuuka_model_create": (_i32, [_vp, _vp, _vp]),
@@ -424,6 +426,32 @@ def spec_generate(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, 
     res = SpecResult()
     check(lib().yuuka_spec_generate(sess.h, seq, p.ctypes.data, p.size, C.byref(req), out.ctypes.data, C.byref(res)))
     return out[:res.output_tokens].tolist(), res
+
+
+def spec_generate_device(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, min_match: int = 0, stop_tokens=(),
+                         seq: int = 0, burst: int = 4):
+    """yuuka_spec_generate_device: drafting on the device, `burst` steps per host synchronization."""
+    p = np.ascontiguousarray(prompt, np.int32)
+    stops = np.ascontiguousarray(list(stop_tokens), np.int32)
+    req = SpecRequest(max_tokens, SpecOptions(max_draft, min_match), stops.ctypes.data if stops.size else None, stops.size)
+    out = np.zeros(max(max_tokens, 1), np.int32)
+    res = SpecResult()
+    check(lib().yuuka_spec_generate_device(sess.h, seq, p.ctypes.data, p.size, C.byref(req), burst, out.ctypes.data,
+                                           C.byref(res)))
+    return out[:res.output_tokens].tolist(), res
+
+
+def spec_lookup_draft_device(dev: "Device", history, max_draft: int, min_match: int) -> list[int]:
+    h = np.ascontiguousarray(history, np.int32)
+    hb = dev.upload(h if h.size else np.zeros(1, np.int32))
+    ob = dev.alloc(4 * (1 + max(max_draft, 0)))
+    st = dev.stream()
+    check(lib().yuuka_spec_lookup_draft_device(st.h, hb.h, h.size, max_draft, min_match, ob.h))
+    out = ob.read(np.int32, 1 + max(max_draft, 0))
+    for b in (hb, ob):
+        b.free()
+    st.destroy()
+    return out[1:1 + int(out[0])].tolist()
 
 
 STATIC_SCRATCH_BYTES = 8 << 20
