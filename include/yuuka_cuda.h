@@ -141,6 +141,10 @@ YUUKA_API yuuka_status yuuka_buffer_copy(yuuka_stream * stream, yuuka_buffer * d
  * the mma route and by the fast fp32 route; GGUF-layout weights take a slower
  * generic kernel). */
 #define YUUKA_GEMM_TILED 0x2u
+/* bit 31, test hook: the register-fed kernel never issues the copies of its activations and its wait for them
+ * gives up after a short limit, so that the expiry path (device error word, YUUKA_ERR_DEVICE at the next
+ * session fetch) can be exercised with nothing in flight. The outputs of such a launch are garbage. */
+#define YUUKA_GEMM_TEST_DROP_COPIES 0x80000000u
 YUUKA_API yuuka_status yuuka_gemm_quant(yuuka_stream * stream,
                                         yuuka_buffer * out, uint64_t out_offset,
                                         const yuuka_buffer * x, uint64_t x_offset, uint32_t x_dtype,
@@ -284,6 +288,11 @@ typedef struct yuuka_session_config {
  * multiplies exact integer weights with two-half activations (fp32-level results, weights streamed once
  * per 16 rows). */
 #define YUUKA_SESSION_EXACT_WIDE 0x1u
+/* Test hook: every GEMM of the session's steps carries YUUKA_GEMM_TEST_DROP_COPIES. */
+#define YUUKA_SESSION_TEST_DROP_COPIES 0x80000000u
+/* Replaces the session's flags between steps (no step may be staged or in flight; captured steps are dropped,
+ * since the flags select kernels). */
+YUUKA_API yuuka_status yuuka_session_set_flags(yuuka_session * s, uint32_t flags);
 
 YUUKA_API yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_config * cfg,
                                             yuuka_session ** out);

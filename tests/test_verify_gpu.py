@@ -525,3 +525,55 @@ def test_a_step_cannot_be_launched_twice_before_it_is_fetched(tiny):
     res = sess.fetch()
     assert sess.position() == 3 + int(res.accepted[0]) + 1
     sess.close()
+
+
+def test_an_expired_device_wait_is_reported_once_and_the_path_keeps_working(tiny):
+    """Every wait inside a kernel is bounded; when one runs out the kernel sets a device error word and
+    carries on, and the step that sees the word fails with YUUKA_ERR_DEVICE. The wait is made to run out in
+    the safe way: a test flag makes the GEMM kernels of the session never issue the copies of their
+    activations (nothing is in flight when a CTA exits) and give up after a short limit. The failing step is
+    reported once, the word is cleared, and the same session then verifies correctly again."""
+    cfg, gm, om = tiny
+    V = cfg["vocab"]
+    prompt = synth.uniform_i32(20, 0, V, 901).tolist()
+    rows = synth.uniform_i32(5, 0, V, 902).tolist()
+    st = yo.State(om, 64, yo.KV_F32)
+    st.forward(prompt)
+    _, _, want = st.verify_chain(rows[0], np.array(rows[1:], np.int32), want_logits=True)
+    sess = cuda.Session(gm, max_batch=1, max_nodes=5, capacity=64, kv_format=cuda.KV_F32)
+    sess.forward(prompt, want_logits=False)
+    snap, pos = sess.snapshot(), sess.position()
+    good = sess.verify([rows], mode=cuda.ACCEPT_NONE, want_logits=True).logits[0].copy()
+    assert float(np.max(np.abs(good - want))) <= LOGIT_TOL
+    sess.set_flags(cuda.SESSION_TEST_DROP_COPIES)
+    with pytest.raises(cuda.YuukaError) as e:
+        sess.verify([rows], mode=cuda.ACCEPT_NONE, want_logits=True)
+    assert e.value.status == cuda.ERR_DEVICE and "bounded wait" in str(e.value)
+    # the flag off again: the word was cleared when it was reported, the session and the device still answer
+    sess.set_flags(0)
+    sess.restore(snap)
+    sess.set_position(0, pos)
+    again = sess.verify([rows], mode=cuda.ACCEPT_NONE, want_logits=True).logits[0]
+    assert np.array_equal(again.view(np.uint32), good.view(np.uint32))
+    # the kernel-level entry point carries the same hook; the next step of any session reports it
+    dev = gm.dev
+    stream = dev.stream()
+    n_out, n_in = 64, 256
+    w = synth.normal_quant(n_out, n_in, synth.Q8_0, 0.02, 3)
+    raw = dev.upload(w)
+    wb = dev.alloc(cuda.tiled_bytes(synth.Q8_0, n_out, n_in) + 256)
+    cuda.tile_weights(stream, wb, raw, synth.Q8_0, n_out, n_in)
+    xb = dev.upload(synth.normal_f32(4 * n_in, 1.0, 4))
+    ob = dev.alloc(4 * n_out * 4)
+    cuda.gemm_quant(stream, ob, xb, wb, n_in, n_out, 4, synth.Q8_0, cuda.F32, cuda.PATH_MMA,
+                    flags=cuda.GEMM_TILED | cuda.GEMM_TEST_DROP_COPIES)
+    stream.synchronize()
+    with pytest.raises(cuda.YuukaError) as e:
+        sess.verify([rows], mode=cuda.ACCEPT_NONE)
+    assert e.value.status == cuda.ERR_DEVICE
+    ok = sess.verify([rows], mode=cuda.ACCEPT_NONE, want_logits=True).logits[0]
+    assert np.array_equal(ok.view(np.uint32), good.view(np.uint32))
+    for b in (raw, wb, xb, ob):
+        b.free()
+    stream.destroy()
+    sess.close(); st.close()

@@ -636,6 +636,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.flags = flags;
         t.scratch = &s->gemm;
         t.exact_only = (s->cfg.flags & YUUKA_SESSION_EXACT_WIDE) != 0;
+        if (s->cfg.flags & YUUKA_SESSION_TEST_DROP_COPIES) t.flags |= YUUKA_GEMM_TEST_DROP_COPIES;
         if (swiglu) t.swiglu = *swiglu;
         if (s->fold_step) {
             const yuuka_model_config & mc = s->model->cfg;
@@ -1063,6 +1064,7 @@ void check_seq(const yuuka_session * s, int seq) {
 void sync_and_check(yuuka_session * s) {
     YK_CUDA(cudaStreamSynchronize(s->stream.s));
     int err = read_device_error(s->model->dev);
+    if (err != 0) clear_device_error(s->model->dev);  // reported once; later steps are judged on their own
     YK_REQUIRE(err == 0, YUUKA_ERR_DEVICE, "a bounded wait inside a kernel expired (code %d); results are invalid", err);
 }
 
@@ -1254,7 +1256,8 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
         if (sc.pool_blocks <= 0) sc.pool_blocks = per_seq * sc.max_batch;
         YK_REQUIRE(sc.kv_format == YUUKA_KV_F32 || sc.kv_format == YUUKA_KV_F16 || sc.kv_format == YUUKA_KV_Q8_0,
                    YUUKA_ERR_INVALID_ARGUMENT, "unknown KV format %d", sc.kv_format);
-        YK_REQUIRE((sc.flags & ~YUUKA_SESSION_EXACT_WIDE) == 0, YUUKA_ERR_INVALID_ARGUMENT, "unknown session flags 0x%x", sc.flags);
+        YK_REQUIRE((sc.flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
+                   "unknown session flags 0x%x", sc.flags);
         set_device(model->dev);
         auto * s = new yuuka_session();
         try {
@@ -1467,6 +1470,20 @@ yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const
         YK_CUDA(cudaStreamSynchronize(s->stream.s));
         YK_CUDA(cudaMemcpy(s->d_tables + (int64_t)seq * s->table_stride, blocks, sizeof(int32_t) * s->table_stride,
                            cudaMemcpyHostToDevice));
+    });
+}
+
+yuuka_status yuuka_session_set_flags(yuuka_session * s, uint32_t flags) {
+    return guard([&] {
+        YK_REQUIRE(s, YUUKA_ERR_INVALID_ARGUMENT, "null session");
+        YK_REQUIRE((flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
+                   "unknown session flags 0x%x", flags);
+        YK_REQUIRE(!s->staged && !s->launched, YUUKA_ERR_INVALID_ARGUMENT, "set_flags: a step is staged or in flight");
+        set_device(s->model->dev);
+        YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        for (auto & g : s->graphs) cudaGraphExecDestroy(g.exec);
+        s->graphs.clear();
+        s->cfg.flags = flags;
     });
 }
 
@@ -1689,6 +1706,7 @@ yuuka_status yuuka_verify_fetch(yuuka_session * s, const yuuka_verify_batch * b)
                                     s->stream.s));
         enqueue_device_error_read(s->stream.s, err2);
         YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        if ((err2[0] | err2[1]) != 0) clear_device_error(s->model->dev);  // reported once; later steps are judged on their own
         YK_REQUIRE((err2[0] | err2[1]) == 0, YUUKA_ERR_DEVICE, "a bounded wait inside a kernel expired (code %d); results are invalid",
                    err2[0] | err2[1]);
         const int32_t * acc = s->h_results;

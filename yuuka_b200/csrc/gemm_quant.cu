@@ -22,6 +22,13 @@ int read_device_error(const yuuka_device * dev) {
     return v | read_gemm_wait_expired();
 }
 
+void clear_device_error(const yuuka_device * dev) {
+    set_device(dev);
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_device_error, &zero, sizeof(int));
+    clear_gemm_wait_expired();
+}
+
 // The same two flags copied behind the work already queued on `stream`, into two page-locked words.
 void enqueue_device_error_read(cudaStream_t stream, int * out2) {
     YK_CUDA(cudaMemcpyFromSymbolAsync(out2, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));

@@ -47,6 +47,8 @@ void gemm_scratch_free(GemmScratch & s);
 // Sticky device-side error word: set when a bounded wait inside a kernel gave
 // up. Reading it synchronises the device.
 int read_device_error(const yuuka_device * dev);
+// Back to zero (after the error has been reported): the next steps are judged on their own.
+void clear_device_error(const yuuka_device * dev);
 void enqueue_device_error_read(cudaStream_t stream, int * out2);
 
 }  // namespace yk

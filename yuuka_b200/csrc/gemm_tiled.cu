@@ -807,6 +807,7 @@ struct TParams {
     // while this kernel drains and the small kernels in between run
     const uint8_t * next_w;
     uint32_t next_lines;  // 128-byte lines
+    int drop_copies;      // test hook (YUUKA_GEMM_TEST_DROP_COPIES): the activation copies are never issued
 };
 
 // 1 / rms of a row from its fixed-point sum of squares (2^-24 units). rmsNorm (model/qwen35/forward.go:
@@ -910,7 +911,7 @@ __global__ void __launch_bounds__(MW * 32, 1) gemm_tiled_mma_kernel(const TParam
 
     // ---- activations of this K chunk: one bulk copy per row and half, and one for the sums where the type
     // has a "- min" term, every row's copies issued by its own lane of the first warp ----
-    if (warp == 0) {
+    if (warp == 0 && !p.drop_copies) {
         const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
         const uint32_t row_bytes_x = (uint32_t)cnt * 512, row_bytes_s = X::SUMS ? (uint32_t)cnt * 64 : 0u;
         if (lane == 0)
@@ -957,7 +958,8 @@ __global__ void __launch_bounds__(MW * 32, 1) gemm_tiled_mma_kernel(const TParam
         // bounded wait for the copies; on expiry the error word is set and the results are garbage
         const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&xbar);
         uint32_t ok = 0;
-        for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+        const uint32_t limit = p.drop_copies ? (1u << 8) : (1u << 22);
+        for (uint32_t i = 0; i < limit && !ok; i++) {
             asm volatile(
                 "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                 : "=r"(ok)
@@ -1597,6 +1599,7 @@ static void launch_mma_inst(cudaStream_t s, const TiledGemmArgs & a, const XPrep
         p.nf_eps = a.norm.eps;
         p.nf_cols = a.norm.cols;
     }
+    p.drop_copies = (a.flags & YUUKA_GEMM_TEST_DROP_COPIES) ? 1 : 0;
     if (a.next_w && m0 + MMA_ROWS >= a.rows) {
         p.next_w = a.next_w;
         p.next_lines = (uint32_t)(a.next_bytes / 128);
@@ -1921,6 +1924,10 @@ int read_gemm_wait_expired() {
     int v = 0;
     cudaMemcpyFromSymbol(&v, g_gemm_wait_expired, sizeof(int));
     return v;
+}
+void clear_gemm_wait_expired() {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_wait_expired, &zero, sizeof(int));
 }
 void enqueue_gemm_wait_expired_read(cudaStream_t stream, int * out) {
     YK_CUDA(cudaMemcpyFromSymbolAsync(out, g_gemm_wait_expired, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));

@@ -109,6 +109,7 @@ void gemm_tiled_preload_kernels();
 
 // Non-zero once a bounded wait inside a GEMM kernel has expired (sticky).
 int read_gemm_wait_expired();
+void clear_gemm_wait_expired();
 void enqueue_gemm_wait_expired_read(cudaStream_t stream, int * out);
 
 }  // namespace yk

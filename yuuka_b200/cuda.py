@@ -21,6 +21,8 @@ GEMM_ACCUMULATE = 1
 GEMM_TILED = 2
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
 SESSION_EXACT_WIDE = 1
+SESSION_TEST_DROP_COPIES = 0x80000000
+GEMM_TEST_DROP_COPIES = 0x80000000
 OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
             100: "gdn_scan", 102: "accept", 103: "commit", 104: "moe_route", 105: "moe_experts",
             106: "moe_combine"}
@@ -164,6 +166,7 @@ SIGNATURES = {
     "yuuka_session_destroy": (None, [_vp]),
     "yuuka_session_set_block_table": (_i32, [_vp, _i32, _vp, _i32]),
     "yuuka_session_copy_block": (_i32, [_vp, _i32, _i32]),
+    "yuuka_session_set_flags": (_i32, [_vp, _u32]),
     "yuuka_session_reset": (_i32, [_vp, _i32]),
     "yuuka_session_set_position": (_i32, [_vp, _i32, _i32]),
     "yuuka_session_position": (_i32, [_vp, _i32, _vp]),
@@ -641,6 +644,9 @@ class Session:
         check(lib().yuuka_session_forward(self.h, seq, t.ctypes.data_as(C.c_void_p), t.size,
                                           out.ctypes.data_as(C.c_void_p) if want_logits else None))
         return out
+
+    def set_flags(self, flags: int):
+        check(lib().yuuka_session_set_flags(self.h, flags))
 
     def copy_block(self, dst_block: int, src_block: int):
         check(lib().yuuka_session_copy_block(self.h, dst_block, src_block))
