@@ -369,6 +369,17 @@ typedef struct yuuka_verify_batch {
 
 YUUKA_API yuuka_status yuuka_verify_step(yuuka_session * s, const yuuka_verify_batch * batch);
 
+/* The acceptance stage on its own, over f32 logits [batch, nodes, vocab] that are already on the device: the
+ * greedy walk (argmaxLogit first-maximum rule, engine/speculative.go:263-271, along the tree) or the rejection-
+ * sampling walk, with the arguments' meaning as in yuuka_verify_batch (tokens, parent, uniforms on the host;
+ * draft_probs on the device). Row metadata and scratch are allocated for the call. begin / end (optional) are
+ * recorded around the acceptance kernels. Synchronous. */
+YUUKA_API yuuka_status yuuka_accept_tree(yuuka_stream * stream, const yuuka_buffer * logits, int32_t batch, int32_t nodes,
+                                         int32_t vocab, const int32_t * tokens, const int32_t * parent, uint32_t mode,
+                                         float temperature, const yuuka_buffer * draft_probs, const float * uniforms,
+                                         int32_t * accepted, int32_t * emitted, int32_t * path, yuuka_event * begin,
+                                         yuuka_event * end);
+
 /* Device-resident variant for benchmarking and pipelined serving: inputs were
  * staged with yuuka_verify_stage, the step only enqueues kernels on the
  * session stream (no host synchronisation); results are fetched later. */

@@ -141,3 +141,51 @@ def test_rejection_arguments_are_validated(tiny):
     assert sess.position() == 3  # nothing ran
     q.free(); small.free()
     sess.close()
+
+
+def test_acceptance_case_of_the_kernel_microbenchmark_matches_the_oracle():
+    """fp32 logits N(0, 3) over 248,320 tokens for 16 sequences x 9 positions (the microbenchmark names 64
+    sequences; 16 keep the CPU side of the test to seconds), draft probabilities = softmax of the logits plus
+    N(0, 1) noise, temperature 0.7, seeded uniforms: yuuka_accept_tree returns the oracle's accepted counts,
+    paths and emitted tokens bit for bit, for the rejection walk and for the greedy walk."""
+    V, B, N, T = 248320, 16, 9, 0.7
+    dev = cuda.Device(0)
+    stream = dev.stream()
+    rng = np.random.default_rng(2026)
+    logits = (3.0 * rng.standard_normal((B, N, V), dtype=np.float32)).astype(np.float32)
+    parent = np.arange(-1, N - 1, dtype=np.int32)
+    q = np.zeros((B, N, V), np.float32)
+    tokens = np.zeros((B, N), np.int32)
+    tokens[:, 0] = rng.integers(0, V, B)
+    for b in range(B):
+        for c in range(1, N):
+            q[b, c] = softmax32(logits[b, c - 1] / T + rng.standard_normal(V, dtype=np.float32))
+            # half of the drafts are the draft model's most likely token, half are drawn from it
+            if (b + c) % 2:
+                tokens[b, c] = int(np.argmax(q[b, c]))
+            else:
+                p64 = q[b, c].astype(np.float64)
+                tokens[b, c] = rng.choice(V, p=p64 / p64.sum())
+    uniforms = np.minimum(rng.random((B, N, 2), dtype=np.float32), np.float32(0.99999994))
+    lb, qb = dev.upload(logits), dev.upload(q)
+    acc, em, path = cuda.accept_tree(stream, lb, tokens, V, parent=parent, mode=cuda.ACCEPT_REJECTION, temperature=T,
+                                     draft_probs=qb, uniforms=uniforms)
+    total = 0
+    for b in range(B):
+        a, p_o, e_o = yo.accept_rejection_tree(logits[b], q[b], tokens[b], parent, T, uniforms[b])
+        assert int(acc[b]) == a, b
+        assert path[b, :a].tolist() == p_o.tolist() and em[b, :a + 1].tolist() == e_o.tolist()
+        total += a
+    assert 0 < total < B * (N - 1)
+    # greedy walk over the same logits, with the first three drafts of every other sequence set to the argmax chain
+    for b in range(0, B, 2):
+        for c in range(1, 4):
+            tokens[b, c] = int(np.argmax(logits[b, c - 1]))
+    acc, em, path = cuda.accept_tree(stream, lb, tokens, V, parent=parent)
+    for b in range(B):
+        a, p_o, e_o = yo.accept_greedy_tree(logits[b], tokens[b], parent)
+        assert int(acc[b]) == a and path[b, :a].tolist() == p_o.tolist() and em[b, :a + 1].tolist() == e_o.tolist()
+        assert a >= 3 or b % 2
+    lb.free(); qb.free()
+    stream.destroy()
+    dev.close()

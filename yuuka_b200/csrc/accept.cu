@@ -6,6 +6,8 @@
 // cur the wanted token is argmax(logits[cur]); the lowest-numbered child of
 // cur that carries it is accepted and becomes cur; otherwise the wanted token
 // is emitted as the correction and the walk ends.
+#include <vector>
+
 #include "layers.cuh"
 
 namespace yk {
@@ -322,3 +324,84 @@ void launch_accept_all(cudaStream_t s, const RowMeta & rows, const AcceptOut & o
 int argmax_chunks(int vocab) { return (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK; }
 
 }  // namespace yk
+
+// ---------------------------------------------------------------------------
+// Kernel-level entry point: acceptance over logits that are already on the device (the acceptance case of the
+// kernel microbenchmark; hosts whose logits come from elsewhere). Row metadata and scratch live for the call.
+extern "C" yuuka_status yuuka_accept_tree(yuuka_stream * stream, const yuuka_buffer * logits, int32_t batch, int32_t nodes,
+                                          int32_t vocab, const int32_t * tokens, const int32_t * parent, uint32_t mode,
+                                          float temperature, const yuuka_buffer * draft_probs, const float * uniforms,
+                                          int32_t * accepted, int32_t * emitted, int32_t * path, yuuka_event * begin,
+                                          yuuka_event * end) {
+    using namespace yk;
+    return guard([&] {
+        YK_REQUIRE(stream && logits && tokens && accepted && emitted, YUUKA_ERR_INVALID_ARGUMENT, "accept_tree: null argument");
+        YK_REQUIRE(batch > 0 && nodes > 0 && nodes <= 64 && vocab > 0, YUUKA_ERR_INVALID_ARGUMENT, "accept_tree: invalid shape");
+        YK_REQUIRE(mode == YUUKA_ACCEPT_GREEDY || mode == YUUKA_ACCEPT_REJECTION, YUUKA_ERR_INVALID_ARGUMENT,
+                   "accept_tree: unknown acceptance mode %u", mode);
+        const uint64_t R = (uint64_t)batch * nodes, need = R * (uint64_t)vocab * sizeof(float);
+        YK_REQUIRE(logits->bytes >= need, YUUKA_ERR_INVALID_ARGUMENT, "accept_tree: logits buffer holds fewer than %llu bytes",
+                   (unsigned long long)need);
+        if (mode == YUUKA_ACCEPT_REJECTION) {
+            YK_REQUIRE(temperature > 0.0f && temperature == temperature, YUUKA_ERR_INVALID_ARGUMENT,
+                       "accept_tree: rejection sampling needs a temperature above zero");
+            YK_REQUIRE(uniforms && draft_probs && draft_probs->bytes >= need, YUUKA_ERR_INVALID_ARGUMENT,
+                       "accept_tree: rejection sampling needs uniforms and a draft_probs buffer of %llu bytes", (unsigned long long)need);
+            for (uint64_t i = 0; i < R * 2; i++)
+                YK_REQUIRE(uniforms[i] >= 0.0f && uniforms[i] < 1.0f, YUUKA_ERR_INVALID_ARGUMENT,
+                           "accept_tree: uniform draw %llu is outside [0, 1)", (unsigned long long)i);
+        }
+        // row metadata on the host
+        std::vector<int32_t> par(R), dep(R);
+        std::vector<unsigned long long> anc(R);
+        for (int b = 0; b < batch; b++)
+            for (int i = 0; i < nodes; i++) {
+                const size_t r = (size_t)b * nodes + i;
+                YK_REQUIRE(tokens[r] >= 0 && tokens[r] < vocab, YUUKA_ERR_INVALID_ARGUMENT, "token id %d is out of range", tokens[r]);
+                const int p = parent ? parent[r] : i - 1;
+                YK_REQUIRE((i == 0 && p == -1) || (i > 0 && p >= 0 && p < i), YUUKA_ERR_INVALID_ARGUMENT,
+                           "parent[%d][%d] = %d is not a preceding row", b, i, p);
+                par[r] = p;
+                dep[r] = i == 0 ? 0 : dep[(size_t)b * nodes + p] + 1;
+                anc[r] = (i == 0 ? 0ull : anc[(size_t)b * nodes + p]) | (1ull << i);
+            }
+        set_device(stream->dev);
+        const int chunks = argmax_chunks(vocab);
+        // one allocation: anc | tokens | parent | depth | accepted | path | emitted | uniforms | argmax val, idx | residual
+        const size_t o_anc = 0, o_tok = o_anc + R * 8, o_par = o_tok + R * 4, o_dep = o_par + R * 4, o_acc = o_dep + R * 4,
+                     o_path = o_acc + (size_t)batch * 4, o_em = o_path + R * 4, o_uni = o_em + R * 4, o_val = o_uni + R * 8,
+                     o_idx = o_val + R * chunks * 4, o_res = ((o_idx + R * chunks * 4 + 255) / 256) * 256,
+                     total = o_res + (mode == YUUKA_ACCEPT_REJECTION ? (size_t)batch * vocab * 8 : 0);
+        uint8_t * d = nullptr;
+        YK_REQUIRE(cudaMalloc((void **)&d, total) == cudaSuccess, YUUKA_ERR_ALLOCATION, "accept_tree: scratch allocation of %llu bytes failed",
+                   (unsigned long long)total);
+        try {
+            cudaStream_t st = stream->s;
+            YK_CUDA(cudaMemcpyAsync(d + o_anc, anc.data(), R * 8, cudaMemcpyHostToDevice, st));
+            YK_CUDA(cudaMemcpyAsync(d + o_tok, tokens, R * 4, cudaMemcpyHostToDevice, st));
+            YK_CUDA(cudaMemcpyAsync(d + o_par, par.data(), R * 4, cudaMemcpyHostToDevice, st));
+            YK_CUDA(cudaMemcpyAsync(d + o_dep, dep.data(), R * 4, cudaMemcpyHostToDevice, st));
+            if (mode == YUUKA_ACCEPT_REJECTION) YK_CUDA(cudaMemcpyAsync(d + o_uni, uniforms, R * 8, cudaMemcpyHostToDevice, st));
+            RowMeta rows{(const int32_t *)(d + o_tok), (const int32_t *)(d + o_par), (const int32_t *)(d + o_dep),
+                         (const uint64_t *)(d + o_anc), nullptr, batch, nodes};
+            AcceptOut out{(int32_t *)(d + o_acc), (int32_t *)(d + o_path), (int32_t *)(d + o_em)};
+            if (begin) YK_CUDA(cudaEventRecord(begin->e, st));
+            if (mode == YUUKA_ACCEPT_GREEDY) {
+                ArgmaxScratch sc{(float *)(d + o_val), (int32_t *)(d + o_idx), chunks};
+                launch_accept_greedy(st, (const float *)logits->ptr, vocab, rows, sc, out);
+            } else {
+                launch_accept_rejection(st, (const float *)logits->ptr, (const float *)draft_probs->ptr, (const float *)(d + o_uni),
+                                        (unsigned long long *)(d + o_res), vocab, temperature, rows, out);
+            }
+            if (end) YK_CUDA(cudaEventRecord(end->e, st));
+            YK_CUDA(cudaMemcpyAsync(accepted, d + o_acc, (size_t)batch * 4, cudaMemcpyDeviceToHost, st));
+            YK_CUDA(cudaMemcpyAsync(emitted, d + o_em, R * 4, cudaMemcpyDeviceToHost, st));
+            if (path) YK_CUDA(cudaMemcpyAsync(path, d + o_path, R * 4, cudaMemcpyDeviceToHost, st));
+            YK_CUDA(cudaStreamSynchronize(st));
+        } catch (...) {
+            cudaFree(d);
+            throw;
+        }
+        cudaFree(d);
+    });
+}

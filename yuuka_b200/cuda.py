@@ -176,6 +176,7 @@ SIGNATURES = {
     "yuuka_session_prefill_logits": (_i32, [_vp, _i32, _vp, _i32, _vp]),
     "yuuka_session_forward": (_i32, [_vp, _i32, _vp, _i32, _vp]),
     "yuuka_verify_step": (_i32, [_vp, _vp]),
+    "yuuka_accept_tree": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "yuuka_verify_stage": (_i32, [_vp, _vp]),
     "yuuka_verify_launch": (_i32, [_vp, _vp]),
     "yuuka_verify_fetch": (_i32, [_vp, _vp]),
@@ -429,6 +430,22 @@ def spec_generate(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, 
     res = SpecResult()
     check(lib().yuuka_spec_generate(sess.h, seq, p.ctypes.data, p.size, C.byref(req), out.ctypes.data, C.byref(res)))
     return out[:res.output_tokens].tolist(), res
+
+
+def accept_tree(stream: "Stream", logits: "Buffer", tokens, vocab: int, parent=None, mode: int = ACCEPT_GREEDY,
+                temperature: float = 1.0, draft_probs: "Buffer | None" = None, uniforms=None, begin: "Event | None" = None,
+                end: "Event | None" = None):
+    """yuuka_accept_tree: tokens [batch, nodes]; returns (accepted [batch], emitted [batch, nodes], path [batch, nodes])."""
+    tokens = np.ascontiguousarray(tokens, np.int32)
+    B, N = tokens.shape
+    par = None if parent is None else np.ascontiguousarray(np.broadcast_to(np.asarray(parent, np.int32), (B, N)))
+    uni = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
+    acc, em, path = np.zeros(B, np.int32), np.full((B, N), -1, np.int32), np.full((B, N), -1, np.int32)
+    check(lib().yuuka_accept_tree(stream.h, logits.h, B, N, vocab, tokens.ctypes.data, par.ctypes.data if par is not None else None,
+                                  mode, temperature, draft_probs.h if draft_probs is not None else None,
+                                  uni.ctypes.data if uni is not None else None, acc.ctypes.data, em.ctypes.data, path.ctypes.data,
+                                  begin.h if begin else None, end.h if end else None))
+    return acc, em, path
 
 
 def spec_generate_device(sess: "Session", prompt, max_tokens: int, max_draft: int = 0, min_match: int = 0, stop_tokens=(),
@@ -698,8 +715,9 @@ class Session:
         check(lib().yuuka_verify_step(self.h, C.byref(vb)))
         return self._result(keep)
 
-    def stage(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False, seq_ids=None):
-        vb, keep = self._batch(tokens, parent, mode, want_logits, seq_ids=seq_ids)
+    def stage(self, tokens, parent=None, mode: int = ACCEPT_GREEDY, want_logits: bool = False, seq_ids=None,
+              temperature: float = 1.0, draft_probs: "Buffer | None" = None, uniforms=None):
+        vb, keep = self._batch(tokens, parent, mode, want_logits, temperature, draft_probs, uniforms, seq_ids)
         check(lib().yuuka_verify_stage(self.h, C.byref(vb)))
         self._staged = (vb, keep)
 
