@@ -496,15 +496,23 @@ __device__ __forceinline__ void sum_mma(uint32_t a0, uint32_t a1, uint32_t a2, u
     }
 }
 
+// Two fp32 fused multiply-adds in one instruction (sm_100 packed f32x2): (a0, a1) += s * (t0, t1).
+__device__ __forceinline__ void fma2(float & a0, float & a1, float s, float t0, float t1) {
+    unsigned long long a, t, ss;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(t) : "f"(t0), "f"(t1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(ss) : "f"(s));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a) : "l"(ss), "l"(t));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(a));
+}
+
 // acc[j][c] += dg * q[j][c] (rows g: c < 2) or dh * q[j][c] (rows g + 8)
 template <int NT>
 __device__ __forceinline__ void fold_rows(float (&acc)[NT][4], const float (&q)[NT][4], float dg, float dh) {
 #pragma unroll
     for (int j = 0; j < NT; j++) {
-        acc[j][0] = fmaf(dg, q[j][0], acc[j][0]);
-        acc[j][1] = fmaf(dg, q[j][1], acc[j][1]);
-        acc[j][2] = fmaf(dh, q[j][2], acc[j][2]);
-        acc[j][3] = fmaf(dh, q[j][3], acc[j][3]);
+        fma2(acc[j][0], acc[j][1], dg, q[j][0], q[j][1]);
+        fma2(acc[j][2], acc[j][3], dh, q[j][2], q[j][3]);
     }
 }
 
@@ -682,10 +690,8 @@ template <int NT> struct XMma<YUUKA_DTYPE_Q6_K, NT> {
                             const uint2 b = *reinterpret_cast<const uint2 *>(xrow[jt] + (sbl * 256 + 32 * k + 16 * h) * 2);
                             float tmp[4];
                             mma16816_zero(tmp, a[h][0], a[h][1], a[h][2], a[h][3], b.x, b.y);
-                            acc[jt][0] = fmaf(s_g, tmp[0], acc[jt][0]);
-                            acc[jt][1] = fmaf(s_g, tmp[1], acc[jt][1]);
-                            acc[jt][2] = fmaf(s_h, tmp[2], acc[jt][2]);
-                            acc[jt][3] = fmaf(s_h, tmp[3], acc[jt][3]);
+                            fma2(acc[jt][0], acc[jt][1], s_g, tmp[0], tmp[1]);
+                            fma2(acc[jt][2], acc[jt][3], s_h, tmp[2], tmp[3]);
                         }
                     }
                 }
@@ -739,10 +745,8 @@ template <int NT> struct XMma<YUUKA_DTYPE_Q8_0, NT> {
                     float tmp[4];
                     mma16816_zero(tmp, a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                     mma16816(tmp, a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-                    acc[jt][0] = fmaf(sgv[k], tmp[0], acc[jt][0]);
-                    acc[jt][1] = fmaf(sgv[k], tmp[1], acc[jt][1]);
-                    acc[jt][2] = fmaf(shv[k], tmp[2], acc[jt][2]);
-                    acc[jt][3] = fmaf(shv[k], tmp[3], acc[jt][3]);
+                    fma2(acc[jt][0], acc[jt][1], sgv[k], tmp[0], tmp[1]);
+                    fma2(acc[jt][2], acc[jt][3], shv[k], tmp[2], tmp[3]);
                 }
             }
         }
