@@ -161,6 +161,8 @@ __device__ __forceinline__ unsigned long long target_weight(float logit, float m
 }
 
 constexpr int REJ_THREADS = 1024;
+constexpr int REJ_CLUSTER = 8;          // CTAs that share one sequence's vocabulary when it is large
+constexpr int REJ_CLUSTER_MIN_VOCAB = 32768;
 
 struct RejectParams {
     const float * logits;   // [batch][nodes][vocab]
@@ -173,24 +175,89 @@ struct RejectParams {
     AcceptOut out;
 };
 
-__device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long * red) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    __syncthreads();  // red may still be read from the previous use
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    unsigned long long t = 0;
-    for (int w = 0; w < REJ_THREADS / 32; w++) t += red[w];
-    return t;
-}
+// Sums and maxima over the CL CTAs that walk one sequence together. Every CTA reduces its own slice, leaves the
+// result in one of two shared-memory slots (alternating: a CTA can only be one exchange ahead of the slowest,
+// because the hardware barrier of exchange k + 1 needs every CTA to have finished reading exchange k), and reads
+// all CL slots after the cluster barrier. Integer sums and float maxima do not depend on the order, so every
+// CTA holds the same value and takes the same branches. CL = 1 degenerates to the block reduction.
+template <int CL> struct RejectExchange {
+    unsigned long long * red;   // [REJ_THREADS / 32]
+    unsigned long long * slot;  // [2]
+    int turn = 0;
 
+    __device__ unsigned long long block_sum(unsigned long long v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        __syncthreads();  // red may still be read from the previous use
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        unsigned long long t = 0;
+        for (int w = 0; w < REJ_THREADS / 32; w++) t += red[w];
+        return t;
+    }
+    __device__ float block_max(float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = (unsigned long long)__float_as_uint(v);
+        __syncthreads();
+        for (int w = 0; w < REJ_THREADS / 32; w++) v = fmaxf(v, __uint_as_float((uint32_t)red[w]));
+        return v;
+    }
+    // total over the cluster; *before (if given) receives the sum over the CTAs of lower rank
+    __device__ unsigned long long sum(unsigned long long v, unsigned long long * before = nullptr) {
+        const unsigned long long mine = block_sum(v);
+        if constexpr (CL == 1) {
+            if (before) *before = 0;
+            return mine;
+        } else {
+            if (threadIdx.x == 0) slot[turn] = mine;
+            cluster_sync_all();
+            unsigned long long tot = 0, low = 0;
+            const unsigned me = cluster_cta_rank();
+            for (unsigned c = 0; c < (unsigned)CL; c++) {
+                const unsigned long long x = ld_cluster_u64(slot + turn, c);
+                if (c < me) low += x;
+                tot += x;
+            }
+            if (before) *before = low;
+            turn ^= 1;
+            return tot;
+        }
+    }
+    __device__ float max(float v) {
+        v = block_max(v);
+        if constexpr (CL == 1) {
+            return v;
+        } else {
+            if (threadIdx.x == 0) slot[turn] = (unsigned long long)__float_as_uint(v);
+            cluster_sync_all();
+            for (unsigned c = 0; c < (unsigned)CL; c++) v = fmaxf(v, __uint_as_float((uint32_t)ld_cluster_u64(slot + turn, c)));
+            turn ^= 1;
+            return v;
+        }
+    }
+    // orders this cluster's global writes (the residual weights) before the reads that follow in other CTAs
+    __device__ void sync() {
+        if constexpr (CL == 1) __syncthreads();
+        else cluster_sync_all();
+    }
+};
+
+// One sequence per cluster of CL CTAs; CTA c of the cluster owns the vocabulary slice [c * slice, (c + 1) * slice).
+// All CTAs of a cluster walk the tree together: the deciding quantities (R, r[x], q[x], the uniforms) are the
+// same everywhere, so they take the same turns; only rank 0 writes the path.
+template <int CL>
 __global__ void __launch_bounds__(REJ_THREADS) rejection_walk_kernel(const RejectParams p) {
     pdl_entry();
     __shared__ unsigned long long red[REJ_THREADS / 32];
-    __shared__ float redf[REJ_THREADS / 32];
+    __shared__ unsigned long long slot[2];
     __shared__ int flag;
-    __shared__ int found;
-    const int seq = blockIdx.x, N = p.rows.nodes, V = p.vocab, tid = threadIdx.x;
+    RejectExchange<CL> ex{red, slot};
+    const unsigned rank = CL == 1 ? 0u : cluster_cta_rank();
+    const int seq = blockIdx.x / CL, N = p.rows.nodes, V = p.vocab, tid = threadIdx.x;
+    const int slice = CL == 1 ? V : (((V + CL - 1) / CL + 3) & ~3);
+    const int v0 = min(V, (int)rank * slice), v1 = min(V, v0 + slice);
     const int32_t * tokens = p.rows.tokens + (int64_t)seq * N;
     const int32_t * parent = p.rows.parent + (int64_t)seq * N;
     const float * U = p.u + (int64_t)seq * N * 2;
@@ -202,68 +269,68 @@ __global__ void __launch_bounds__(REJ_THREADS) rejection_walk_kernel(const Rejec
         const float * L = p.logits + ((int64_t)seq * N + cur) * V;
         // max of the row (order-independent)
         float mx = -INFINITY;
-        for (int i = tid; i < V; i += REJ_THREADS) mx = fmaxf(mx, L[i]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        __syncthreads();
-        if ((tid & 31) == 0) redf[tid >> 5] = mx;
-        __syncthreads();
-        for (int w = 0; w < REJ_THREADS / 32; w++) mx = fmaxf(mx, redf[w]);
+        for (int i = v0 + tid; i < v1; i += REJ_THREADS) mx = fmaxf(mx, L[i]);
+        mx = ex.max(mx);
         // target weights
         unsigned long long z = 0;
-        for (int i = tid; i < V; i += REJ_THREADS) {
+        for (int i = v0 + tid; i < v1; i += REJ_THREADS) {
             const unsigned long long w = target_weight(L[i], mx, p.inv_t);
             r[i] = w;
             z += w;
         }
-        const unsigned long long Z = block_sum_u64(z, red);
+        const unsigned long long Z = ex.sum(z);  // (its barrier also publishes r)
         unsigned long long R = Z;
         int next = -1;
         for (int c = cur + 1; c < N && next < 0; c++) {
             if (parent[c] != cur) continue;
             const float * q = p.q + ((int64_t)seq * N + c) * V;
-            __syncthreads();  // r of the previous pass is complete
+            __syncthreads();  // flag of the previous child has been read
             if (tid == 0) {
                 const int32_t x = tokens[c];
                 const float lhs = __fmul_rn(U[2 * c], q[x]);
-                flag = __dmul_rn((double)lhs, (double)R) <= (double)r[x];
+                flag = __dmul_rn((double)lhs, (double)R) <= (double)__ldcg(r + x);
             }
             __syncthreads();
             if (flag) {
                 next = c;
                 break;
             }
+            if constexpr (CL > 1) ex.sync();  // every CTA has read r[x] before its owner rewrites it
             unsigned long long sum = 0;
-            for (int i = tid; i < V; i += REJ_THREADS) {
+            for (int i = v0 + tid; i < v1; i += REJ_THREADS) {
                 const unsigned long long qr = (unsigned long long)__dmul_rn((double)q[i], (double)R);
                 const unsigned long long ri = r[i];
                 const unsigned long long nr = ri > qr ? ri - qr : 0ull;
                 r[i] = nr;
                 sum += nr;
             }
-            R = block_sum_u64(sum, red);
+            R = ex.sum(sum);
             if (R == 0) {
-                for (int i = tid; i < V; i += REJ_THREADS) r[i] = target_weight(L[i], mx, p.inv_t);
+                for (int i = v0 + tid; i < v1; i += REJ_THREADS) r[i] = target_weight(L[i], mx, p.inv_t);
                 R = Z;
+                ex.sync();
             }
         }
         if (next >= 0) {
-            if (tid == 0) {
+            if (tid == 0 && rank == 0) {
                 emitted[a] = tokens[next];
                 path[a] = next;
             }
             a++;
             cur = next;
+            if constexpr (CL > 1) ex.sync();  // r[x] has been read everywhere before the next node rewrites r
             continue;
         }
-        // residual draw: thread tid owns the contiguous range [lo, hi)
-        __syncthreads();
+        // residual draw: the smallest j whose inclusive prefix sum over r exceeds t. Thread tid of CTA c owns the
+        // contiguous range [lo, hi) of c's slice.
         unsigned long long t = (unsigned long long)__dmul_rn((double)U[2 * cur + 1], (double)R);
         if (t >= R) t = R - 1;
-        const int per = (V + REJ_THREADS - 1) / REJ_THREADS;
-        const int lo = min(V, tid * per), hi = min(V, lo + per);
+        const int per = (v1 - v0 + REJ_THREADS - 1) / REJ_THREADS;
+        const int lo = min(v1, v0 + tid * per), hi = min(v1, lo + per);
         unsigned long long mine = 0;
         for (int i = lo; i < hi; i++) mine += r[i];
+        unsigned long long below = 0;
+        ex.sum(mine, &below);  // total of the slices of lower rank
         // exclusive prefix of the per-thread sums: inside the warp, then across warps
         unsigned long long incl = mine;
 #pragma unroll
@@ -271,29 +338,29 @@ __global__ void __launch_bounds__(REJ_THREADS) rejection_walk_kernel(const Rejec
             const unsigned long long v = __shfl_up_sync(0xffffffffu, incl, o);
             if ((tid & 31) >= o) incl += v;
         }
-        if (tid == 0) found = V - 1;
         __syncthreads();
         if ((tid & 31) == 31) red[tid >> 5] = incl;
         __syncthreads();
-        unsigned long long before = incl - mine;
+        unsigned long long before = below + incl - mine;
         for (int w = 0; w < (tid >> 5); w++) before += red[w];
         if (before <= t && t < before + mine) {
             unsigned long long acc = before;
             for (int i = lo; i < hi; i++) {
                 acc += r[i];
                 if (acc > t) {
-                    found = i;
+                    emitted[a] = i;  // exactly one thread of the cluster: t < R = the total
                     break;
                 }
             }
         }
-        __syncthreads();
-        if (tid == 0) emitted[a] = found;
         break;
     }
-    for (int i = a + tid; i < N; i += REJ_THREADS) path[i] = -1;
-    for (int i = a + 1 + tid; i < N; i += REJ_THREADS) emitted[i] = -1;
-    if (tid == 0) p.out.accepted[seq] = a;
+    if (rank == 0) {
+        for (int i = a + tid; i < N; i += REJ_THREADS) path[i] = -1;
+        for (int i = a + 1 + tid; i < N; i += REJ_THREADS) emitted[i] = -1;
+        if (tid == 0) p.out.accepted[seq] = a;
+    }
+    if constexpr (CL > 1) cluster_sync_all();  // no CTA leaves while another may still read its slots
 }
 
 int launch_accept_rejection(cudaStream_t s, const float * logits, const float * draft_probs, const float * uniforms,
@@ -301,7 +368,10 @@ int launch_accept_rejection(cudaStream_t s, const float * logits, const float * 
                             const AcceptOut & out) {
     YK_REQUIRE(temperature > 0.0f, YUUKA_ERR_INVALID_ARGUMENT, "rejection sampling needs a temperature above zero");
     RejectParams p{logits, draft_probs, uniforms, residual, vocab, 1.0f / temperature, rows, out};
-    launch_k(rejection_walk_kernel, rows.batch, REJ_THREADS, 0, s, p);
+    if (vocab >= REJ_CLUSTER_MIN_VOCAB)
+        launch_k_cluster(rejection_walk_kernel<REJ_CLUSTER>, dim3(rows.batch * REJ_CLUSTER), REJ_THREADS, 0, s, REJ_CLUSTER, p);
+    else
+        launch_k(rejection_walk_kernel<1>, rows.batch, REJ_THREADS, 0, s, p);
     YK_CUDA(cudaGetLastError());
     return 1;
 }

@@ -198,5 +198,18 @@ __device__ __forceinline__ double ld_cluster_f64(const double * p, unsigned rank
     asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(remote) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned long long ld_cluster_u64(const unsigned long long * p, unsigned rank) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
 #endif
 }  // namespace yk
