@@ -483,6 +483,9 @@ typedef struct yuuka_spec_result {
  * context capacity. tokens must hold max_tokens ids. The emitted stream equals
  * plain greedy decoding. The session needs max_nodes >= 2 to draft at all
  * (drafts per step are capped at max_nodes - 1). Synchronous. */
+YUUKA_API yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
+                                           const yuuka_spec_request * request, int32_t * tokens,
+                                           yuuka_spec_result * result);
 /* lookupDraft on the device (history: int32 ids in a device buffer): out receives the draft length and then the
  * draft ids, int32[1 + max_draft]. Same result as yuuka_spec_lookup_draft, id for id. Synchronous. */
 YUUKA_API yuuka_status yuuka_spec_lookup_draft_device(yuuka_stream * stream, const yuuka_buffer * history, int32_t n,
@@ -495,9 +498,6 @@ YUUKA_API yuuka_status yuuka_spec_lookup_draft_device(yuuka_stream * stream, con
 YUUKA_API yuuka_status yuuka_spec_generate_device(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
                                                   const yuuka_spec_request * req, int32_t burst, int32_t * tokens,
                                                   yuuka_spec_result * result);
-YUUKA_API yuuka_status yuuka_spec_generate(yuuka_session * s, int32_t seq, const int32_t * prompt, int32_t n_prompt,
-                                           const yuuka_spec_request * request, int32_t * tokens,
-                                           yuuka_spec_result * result);
 
 #ifdef __cplusplus
 }

@@ -70,8 +70,9 @@ def test_mma_route_matches_oracle(dev, dtype, rows):
     want = yo.matmul(w, dtype, n_out, n_in, x)
     got = run_gemm(dev, w, dtype, n_out, n_in, x, cuda.PATH_MMA)
     err, cos = stats(got, want)
-    # fp16 operands, fp32 accumulate: outputs have std ~1
-    assert err <= 4e-3 and cos >= 0.999999, (err, cos)
+    # outputs have std ~1. Up to 47 rows: exact integer weights and two-half activations, fp32 accumulate (measured
+    # 1e-5); from 48 rows: the tensor-memory route with fp16-rounded operands
+    assert err <= (2e-4 if rows < 48 else 4e-3) and cos >= 0.999999, (err, cos)
 
 
 @pytest.mark.parametrize("n_out,n_in,dtype", [
@@ -85,7 +86,7 @@ def test_mma_route_model_shapes(dev, n_out, n_in, dtype):
     want = yo.matmul(w, dtype, n_out, n_in, x)
     got = run_gemm(dev, w, dtype, n_out, n_in, x, cuda.PATH_MMA)
     err, cos = stats(got, want)
-    assert err <= 8e-3 and cos >= 0.999999, (err, cos)
+    assert err <= 4e-4 and cos >= 0.999999, (err, cos)
     # run-twice bitwise determinism (split-K partials are reduced in a fixed order)
     again = run_gemm(dev, w, dtype, n_out, n_in, x, cuda.PATH_MMA)
     assert np.array_equal(got, again)
@@ -111,8 +112,8 @@ def test_lm_head_shape_q6_k(dev):
     want = yo.matmul(w, synth.Q6_K, n_out, n_in, x)
     got = run_gemm(dev, w, synth.Q6_K, n_out, n_in, x, cuda.PATH_AUTO)
     err, cos = stats(got, want)
-    assert err <= 8e-3 and cos >= 0.999999, (err, cos)
-    assert np.array_equal(np.argmax(got, -1), np.argmax(want, -1)) or err < 1e-3
+    assert err <= 4e-4 and cos >= 0.999999, (err, cos)
+    assert np.array_equal(np.argmax(got, -1), np.argmax(want, -1)) or err < 1e-4
 
 
 @pytest.mark.parametrize("dtype", [synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q5_K])
