@@ -71,6 +71,7 @@ def lib():
         "yo_apply_rope": (None, [vp, i32, i32, i32, i32, i32, C.c_double]),
         "yo_softmax_inplace": (None, [vp, i32]),
         "yo_gdn_per_token_scan": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
+        "yo_gdn_chunked_scan": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
         "yo_gdn_norm_gate": (None, [vp, vp, vp, i32, i32, i32, f32]),
         "yo_select_experts": (None, [vp, i32, vp, vp, i32]),
         "yo_sigmoid": (f32, [f32]), "yo_silu": (f32, [f32]), "yo_softplus": (f32, [f32]),
@@ -201,6 +202,17 @@ def gdn_per_token_scan(state, conv, alpha, beta, rows, groups, rank, S):
     assert state.dtype == np.float32 and state.flags.c_contiguous
     lib().yo_gdn_per_token_scan(_p(state), _p(conv), _p(alpha), _p(beta), _p(out), rows, groups,
                                 rank, S, conv_dim)
+    return out
+
+
+def gdn_chunked_scan(state, conv, alpha, beta, rows, groups, rank, S):
+    """The chunkwise WY form of the same recurrence. Updates state in place; returns out[rows, rank, S]."""
+    conv = _f32(conv)
+    conv_dim = conv.size // rows
+    out = np.zeros((rows, rank, S), np.float32)
+    alpha, beta = _f32(alpha), _f32(beta)
+    assert state.dtype == np.float32 and state.flags.c_contiguous
+    lib().yo_gdn_chunked_scan(_p(state), _p(conv), _p(alpha), _p(beta), _p(out), rows, groups, rank, S, conv_dim)
     return out
 
 

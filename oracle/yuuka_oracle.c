@@ -509,6 +509,142 @@ void yo_gdn_per_token_scan(float *state, const float *conv, const float *alpha, 
     free(sk);
 }
 
+/* gdnChunkedScan, model/qwen35/recurrent.go:107-351: the same recurrence in the chunkwise WY form, chunks of
+ * YO_GDN_CHUNK = 32 rows (recurrent.go:8). Within a chunk, relative to the state S_0 at its start, with g the
+ * cumulative log decay from the chunk start and g_c its last entry:
+ *   M = I + B, B[r][s] = beta_r (k_r . k_s) for s < r;  Z = (Q K^T on the lower triangle) M^-1
+ *   S_C = exp(g_c) S_0 + K^T (M^-1 diag(beta) (exp(g_c - g) V - exp(g_c) K S_0))
+ *   o_r = exp(g_r) (q_r S_0 + z_r (diag(beta exp(-g)) V - M^-1 diag(beta) K S_0))
+ * The summation orders of the reference are kept (inverse by rows, recurrent.go:307-331; triangular products,
+ * recurrent.go:335-351). */
+#define YO_GDN_CHUNK 32
+static void gdn_chunk_head(float *matrix, const float *conv, const float *alpha, const float *beta, float *out,
+                           int c0, int n, int h, int groups, int rank, int S, int conv_dim, float *scratch) {
+    const int C = YO_GDN_CHUNK;
+    const int kh = h % groups, key_dim = groups * S;
+    const float *qbase = conv + (int64_t)c0 * conv_dim + kh * S;
+    const float *kbase = conv + (int64_t)c0 * conv_dim + key_dim + kh * S;
+    const float *vbase = conv + (int64_t)c0 * conv_dim + 2 * key_dim + h * S;
+#define QROW(r) (qbase + (int64_t)(r) * conv_dim)
+#define KROW(r) (kbase + (int64_t)(r) * conv_dim)
+#define VROW(r) (vbase + (int64_t)(r) * conv_dim)
+#define BETA(r) (beta[(int64_t)(c0 + (r)) * rank + h])
+    float *lower = scratch;            /* [C][C], later Z */
+    float *minv = lower + C * C;       /* [C][C] */
+    float *logd = minv + C * C;        /* [C] */
+    float *prow = logd + C;            /* [C] */
+    float *kp = prow + C;              /* [C][S]  K S_0 */
+    float *qp = kp + C * S;            /* [C][S]  Q S_0 */
+    float *work = qp + C * S;          /* [C][S] */
+    float *ref = work + C * S;         /* [C][S] */
+    float *tmp = ref + C * S;          /* [S] */
+
+    float acc = 0;
+    for (int r = 0; r < n; r++) {
+        acc += alpha[(int64_t)(c0 + r) * rank + h];
+        logd[r] = acc;
+    }
+    const float gc = acc;
+    const float decay = (float)exp((double)gc);
+
+    for (int i = 0; i < C * C; i++) lower[i] = 0;
+    for (int r = 0; r < n; r++) {
+        const float br = BETA(r);
+        for (int s = 0; s < r; s++) lower[r * C + s] = br * dotf(KROW(r), KROW(s), S);
+    }
+    /* (I + lower)^-1, recurrent.go:307-331 */
+    for (int r = 0; r < n; r++) {
+        for (int s = 0; s < n; s++) minv[r * C + s] = 0;
+        minv[r * C + r] = 1;
+    }
+    for (int r = 1; r < n; r++)
+        for (int u = 0; u < r; u++) {
+            const float lu = lower[r * C + u];
+            if (lu == 0) continue;
+            for (int s = 0; s <= u; s++) minv[r * C + s] -= lu * minv[u * C + s];
+        }
+    /* Z over the block of lower */
+    float *zm = lower;
+    for (int r = 0; r < n; r++) {
+        for (int s = 0; s <= r; s++) prow[s] = dotf(QROW(r), KROW(s), S);
+        for (int s = 0; s <= r; s++) {
+            float sum = 0;
+            for (int u = s; u <= r; u++) sum += prow[u] * minv[u * C + s];
+            zm[r * C + s] = sum;
+        }
+    }
+    for (int r = 0; r < n; r++)
+        for (int s = 0; s < n; s++) minv[r * C + s] *= BETA(s);
+
+    for (int r = 0; r < n; r++) {
+        float *krow = kp + r * S, *qrow = qp + r * S;
+        for (int j = 0; j < S; j++) krow[j] = qrow[j] = 0;
+        for (int i = 0; i < S; i++) {
+            const float ki = KROW(r)[i], qi = QROW(r)[i];
+            const float *srow = matrix + i * S;
+            for (int j = 0; j < S; j++) {
+                krow[j] += ki * srow[j];
+                qrow[j] += qi * srow[j];
+            }
+        }
+    }
+    for (int r = 0; r < n; r++) {
+        const float scale = (float)exp((double)(gc - logd[r]));
+        for (int j = 0; j < S; j++) work[r * S + j] = scale * VROW(r)[j] - decay * kp[r * S + j];
+    }
+    /* ref = mb work, recurrent.go:335-351 */
+    for (int r = 0; r < n; r++) {
+        for (int j = 0; j < S; j++) tmp[j] = 0;
+        for (int s = 0; s <= r; s++) {
+            const float coef = minv[r * C + s];
+            if (coef == 0) continue;
+            for (int j = 0; j < S; j++) tmp[j] += coef * work[s * S + j];
+        }
+        memcpy(ref + r * S, tmp, sizeof(float) * (size_t)S);
+    }
+    for (int i = 0; i < S * S; i++) matrix[i] *= decay;
+    for (int r = 0; r < n; r++)
+        for (int i = 0; i < S; i++) {
+            const float ki = KROW(r)[i];
+            float *srow = matrix + i * S;
+            for (int j = 0; j < S; j++) srow[j] += ki * ref[r * S + j];
+        }
+    for (int r = 0; r < n; r++) {
+        const float br = BETA(r);
+        const float scale = (float)exp((double)(-logd[r]));
+        for (int j = 0; j < S; j++) work[r * S + j] = br * (scale * VROW(r)[j] - kp[r * S + j]);
+    }
+    for (int r = 0; r < n; r++) {
+        float *orow = ref + r * S;
+        for (int j = 0; j < S; j++) orow[j] = 0;
+        for (int s = 0; s <= r; s++) {
+            const float zs = zm[r * C + s];
+            for (int j = 0; j < S; j++) orow[j] += zs * work[s * S + j];
+        }
+    }
+    for (int r = 0; r < n; r++) {
+        const float scale = (float)exp((double)logd[r]);
+        float *head = out + ((int64_t)(c0 + r) * rank + h) * S;
+        for (int j = 0; j < S; j++) head[j] = scale * (qp[r * S + j] + ref[r * S + j]);
+    }
+#undef QROW
+#undef KROW
+#undef VROW
+#undef BETA
+}
+
+void yo_gdn_chunked_scan(float *state, const float *conv, const float *alpha, const float *beta, float *out,
+                         int rows, int groups, int rank, int S, int conv_dim) {
+    const int C = YO_GDN_CHUNK;
+    float *scratch = (float *)malloc(sizeof(float) * ((size_t)2 * C * C + 2 * C + (size_t)4 * C * S + S));
+    for (int c0 = 0; c0 < rows; c0 += C) {
+        const int n = rows - c0 < C ? rows - c0 : C;
+        for (int h = 0; h < rank; h++)
+            gdn_chunk_head(state + (int64_t)h * S * S, conv, alpha, beta, out, c0, n, h, groups, rank, S, conv_dim, scratch);
+    }
+    free(scratch);
+}
+
 /* model/qwen35/recurrent.go:39-50 */
 void yo_gdn_norm_gate(float *out, const float *z, const float *norm, int rows, int rank, int S,
                       float eps) {

@@ -73,6 +73,9 @@ void yo_apply_rope(float *vec, int heads, int stride, int head_dim, int rot_dim,
 void yo_softmax_inplace(float *x, int n);
 void yo_gdn_per_token_scan(float *state, const float *conv, const float *alpha, const float *beta,
                            float *out, int rows, int groups, int rank, int state_size, int conv_dim);
+/* gdnChunkedScan (model/qwen35/recurrent.go:107-351): the chunkwise WY form, chunks of 32 rows */
+void yo_gdn_chunked_scan(float *state, const float *conv, const float *alpha, const float *beta,
+                         float *out, int rows, int groups, int rank, int S, int conv_dim);
 void yo_gdn_norm_gate(float *out, const float *z, const float *norm, int rows, int rank,
                       int state_size, float eps);
 void yo_select_experts(const float *logits, int n_experts, int32_t *ids, float *weights, int k);

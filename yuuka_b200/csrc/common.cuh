@@ -206,6 +206,29 @@ __device__ __forceinline__ unsigned long long ld_cluster_u64(const unsigned long
     asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
     return v;
 }
+// Stores a float at the address `p` has in this CTA, in the shared memory of CTA `rank` of this cluster.
+__device__ __forceinline__ void st_cluster_f32(float * p, unsigned rank, float v) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float * p, unsigned rank) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f32x4(const float * p, unsigned rank) {  // p 16-byte aligned
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 __device__ __forceinline__ unsigned cluster_cta_rank() {
     unsigned r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

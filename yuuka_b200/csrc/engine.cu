@@ -566,6 +566,7 @@ struct yuuka_session {
     int chain_rows = 0;  // rows per prompt chunk (prefill_logits / forward)
     // L2 prefetch of the next GEMM's weights: matrices in the order a step streams them
     bool prefetch_next = true;
+    bool gdn_chunked = true;  // prompt sub-chunks through the chunkwise delta-net scan (YUUKA_CUDA_NO_GDN_CHUNK=1: row by row)
     uint64_t prefetch_bytes = 16ull << 20;  // measured: 16 MB ahead 3.09 ms/step, none 3.12, 48 MB 3.13
     std::vector<std::pair<const uint8_t *, uint64_t>> gemm_order;
     size_t order_pos = 0;
@@ -846,10 +847,12 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
                     gk.dlog = g.dlog + r0 * inner;
                     gk.decay = g.decay + r0 * rank;
                     const RowMeta rk = sub_rows(k);
-                    s->launches += launch_gdn_scan(st, gk, rk);
+                    // every row of a prompt sub-chunk is committed: the chunkwise form writes the state itself
+                    const bool chunked = s->gdn_chunked;
+                    s->launches += chunked ? launch_gdn_chunk(st, gk, rk) : launch_gdn_scan(st, gk, rk);
                     AcceptOut ak{s->d_acc_sub + k, s->acc.path, s->acc.emitted};
                     launch_gdn_commit(st, s->d_gdn_commit + gdn_index, 1, c.group_count, rank, S, c.conv_kernel, conv_dim, seq0, rk,
-                                      ak, (int)r0);
+                                      ak, (int)r0, chunked);
                     s->launches++;
                 }
             }
@@ -1279,6 +1282,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
             }
             if (const char * e = getenv("YUUKA_CUDA_NO_FOLD_SWIGLU")) s->fold_swiglu = !(e[0] == '1');
             if (const char * e = getenv("YUUKA_CUDA_NO_PREFETCH")) s->prefetch_next = !(e[0] == '1');
+            if (const char * e = getenv("YUUKA_CUDA_NO_GDN_CHUNK")) s->gdn_chunked = !(e[0] == '1');
             for (const LayerW & L : model->layers) {
                 for (const Tensor * t : {&L.proj, &L.qkv, &L.gate, &L.beta, &L.alpha, &L.out, &L.qk, &L.q, &L.k, &L.v, &L.o,
                                          &L.gate_up, &L.ffn_gate, &L.ffn_up, &L.ffn_down})

@@ -311,6 +311,469 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
 }
 
 // ---------------------------------------------------------------------------
+// Chunkwise (WY-form) scan for chains whose rows are all committed: the sub-chunks of a prompt pass.
+// gdnChunkedScan (model/qwen35/recurrent.go:107-351) expresses the rows of a chunk relative to the state S_0 at
+// its start; here the same algebra is arranged so that every decay factor is a ratio exp(g_r - g_s) <= 1 (the
+// reference scales the values by exp(-g), which overflows for strongly decaying heads over 64 rows). With g the
+// cumulative log decay, gam_r = exp(g_r), and d_r = beta_r (v_r - (decayed state)^T k_r) the per-token delta:
+//   (I + B) D = diag(beta) (V - diag(gam) K S_0),   B[r][s] = beta_r exp(g_r - g_s) (k_r . k_s)  for s < r
+//   o_r = gam_r q_r S_0 + sum_{s <= r} exp(g_r - g_s) (q_r . k_s) d_s
+//   S_C = gam_C S_0 + sum_s exp(g_C - g_s) k_s d_s^T
+// grid (S/32 column blocks, rank, batch), the column blocks of a head one cluster (gated norm as in the scan
+// kernel); a CTA owns 32 columns of the state, of V, D and the outputs, and computes the row-by-row matrices
+// (K K^T, Q K^T: they do not depend on the column) itself. fp32 FMA throughout. The state is rewritten in
+// place: no delta log, no separate state commit.
+constexpr int GC_THREADS = 512;
+constexpr int GC_PARTS = 8;   // lanes that share one tile of K K^T / Q K^T (each an eighth of the head dimension)
+
+template <int S>
+__global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanParams p) {
+    pdl_entry();
+    const GdnArgs & a = p.a;
+    const int cb = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
+    const int N = p.rows.nodes;
+    const int kh = h % a.groups;
+    const int key_dim = a.groups * S, inner = a.rank * S;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int KP = S + 4;            // pitch of a q / k row (16-byte aligned, rows spread over the banks)
+    constexpr int SP = GDN_COLS + 4;     // pitch of a row of the state block, VP of a row of v / scaled d: two lanes
+    constexpr int VP = GDN_COLS + 16;    // that read neighbouring rows hit disjoint banks
+    const int NT4 = (N + 3) >> 2;        // 4-row tiles
+    const int NPAD = NT4 * 4;
+    const int NP = NPAD + 1;             // pitch of the row-by-row matrices
+
+    extern __shared__ __align__(16) float sm[];
+    float * qn = sm;                          // [NPAD][KP]
+    float * kn = qn + NPAD * KP;              // [NPAD][KP]
+    float * s0 = kn + NPAD * KP;              // [S][SP]   this CTA's columns of the stored state
+    float * vv = s0 + S * SP;                 // [NPAD][VP] v, later exp(g_C - g_s) d_s
+    float * ks = vv + NPAD * VP;              // [NPAD][32] K S_0, then the right-hand side, then D
+    float * dd = ks + NPAD * GDN_COLS;        // [NPAD][32] D
+    float * o_s = dd + NPAD * GDN_COLS;       // [NPAD][32] Q S_0, then the outputs
+    float * Bm = o_s + NPAD * GDN_COLS;       // [NPAD][NP] beta_r w_rs (k_r . k_s), s < r
+    float * Am = Bm + NPAD * NP;              // [NPAD][NP] w_rs (q_r . k_s), s <= r
+    float * lg = Am + NPAD * NP;              // [NPAD] cumulative log decay
+    float * bet = lg + NPAD;                  // [NPAD]
+    float * Tm = bet + NPAD;                  // [NPAD / 16 rounded up][16][17] inverses of the diagonal blocks of I + B
+    float * stage = Tm + ((N + 15) / 16) * 16 * 17 + 3;  // [tiles][32] raw dot products of the tiles this CTA computed
+    stage -= (stage - sm) & 3;                            // (16-byte aligned)
+    __shared__ double ssq[GDN_MAX_NODES];
+    __shared__ float scale_s[GDN_MAX_NODES];
+
+    // ---- loads, asynchronous: q and k (needed first), then this CTA's block of the state; v, beta, decay ----
+    constexpr int SQ = S / 4;
+    for (int i = tid; i < NPAD * SQ; i += GC_THREADS) {
+        const int node = i / SQ, e4 = i - node * SQ;
+        if (node < N) {
+            const int64_t at = (int64_t)(seq * N + node) * key_dim + kh * S + e4 * 4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(qn + node * KP + e4 * 4)),
+                         "l"(a.qn + at) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(kn + node * KP + e4 * 4)),
+                         "l"(a.khat + at) : "memory");
+        } else {
+            *reinterpret_cast<float4 *>(qn + node * KP + e4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(kn + node * KP + e4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float * state = const_cast<float *>(a.state) + ((int64_t)(seq_of(p.rows, seq) * a.rank + h) * S) * S + cb * GDN_COLS;
+    for (int i = tid; i < S * (GDN_COLS / 4); i += GC_THREADS) {
+        const int row = i / (GDN_COLS / 4), c4 = i - row * (GDN_COLS / 4);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s0 + row * SP + c4 * 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(state + (int64_t)row * S + c4 * 4) : "memory");
+    }
+    for (int i = tid; i < NPAD * (GDN_COLS / 4); i += GC_THREADS) {
+        const int node = i / (GDN_COLS / 4), e4 = i - node * (GDN_COLS / 4);
+        if (node < N)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(vv + node * VP + e4 * 4)),
+                         "l"(a.vconv + (int64_t)(seq * N + node) * inner + h * S + cb * GDN_COLS + e4 * 4) : "memory");
+        else *reinterpret_cast<float4 *>(vv + node * VP + e4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the gate values and the norm weight the last phase needs (a 64-row chunk: four per thread) are fetched now
+    constexpr int ZPRE = GDN_MAX_NODES * GDN_COLS / GC_THREADS;
+    float zpre[ZPRE];
+#pragma unroll
+    for (int k = 0; k < ZPRE; k++) {
+        const int i = tid + k * GC_THREADS;
+        const int node = i / GDN_COLS, c = i - node * GDN_COLS;
+        zpre[k] = i < N * GDN_COLS ? a.z[(int64_t)(seq * N + node) * a.ldz + h * S + cb * GDN_COLS + c] : 0.0f;
+    }
+    const float norm_w = a.norm[cb * GDN_COLS + (tid & (GDN_COLS - 1))];
+    for (int node = tid; node < NPAD; node += GC_THREADS) {
+        float b = 0.0f, l = 0.0f;
+        if (node < N) {
+            b = a.beta[(int64_t)(seq * N + node) * a.rank + h];
+            const float dc = a.decay[(int64_t)(seq * N + node) * a.rank + h];
+            l = dc > 0.0f ? fmaxf(logf(dc), -100.0f) : -100.0f;  // a decay that underflowed still wipes the state
+        }
+        bet[node] = b;
+        o_s[node] = l;  // (scratch until the outputs are written)
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // q and k have landed; the state may still be on its way
+    cluster_sync_all();  // (also: every CTA of the cluster runs before another writes into its shared memory)
+    if (warp == 0) {
+        // inclusive scan of the (at most 64) log decays: two per lane
+        const float l0 = lane < NPAD ? o_s[lane] : 0.0f, l1 = lane + 32 < NPAD ? o_s[lane + 32] : 0.0f;
+        float s0v = l0, s1v = l1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float u0 = __shfl_up_sync(0xffffffffu, s0v, o), u1 = __shfl_up_sync(0xffffffffu, s1v, o);
+            if (lane >= o) { s0v += u0; s1v += u1; }
+        }
+        const float first = __shfl_sync(0xffffffffu, s0v, 31);
+        if (lane < NPAD) lg[lane] = s0v;
+        if (lane + 32 < NPAD) lg[lane + 32] = first + s1v;
+    }
+    __syncthreads();
+
+    // ---- K K^T and Q K^T on the lower triangle, 4 x 4 tiles, GC_PARTS lanes per tile ----
+    // The tiles are dealt round-robin to the CTAs of the cluster. Each leaves the raw dot products of its tiles in
+    // its own shared memory; after the cluster barrier every CTA gathers all tiles (its own and, through
+    // distributed shared memory, the others') and folds the decay ratios and beta in on the way into B and A.
+    const int n_tasks = NT4 * (NT4 + 1) / 2, CL = (int)gridDim.x;
+    {
+        // (whole warps walk the loop together: the lanes of a tile exchange their sums by shuffles)
+        const int total = (n_tasks - cb + CL - 1) / CL * GC_PARTS;
+        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
+            const int w = wbase + lane;
+            const bool live = w < total;  // uniform over the GC_PARTS lanes of a tile
+            const int task = live ? cb + CL * (w / GC_PARTS) : 0, part = w & (GC_PARTS - 1);
+            int rt = (int)((sqrtf(8.0f * (float)task + 1.0f) - 1.0f) * 0.5f);
+            while ((rt + 1) * (rt + 2) / 2 <= task) rt++;
+            while (rt * (rt + 1) / 2 > task) rt--;
+            const int st = task - rt * (rt + 1) / 2;
+            float g[4][4], q[4][4];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) g[x][y] = q[x][y] = 0.0f;
+            const float * kr = kn + (rt * 4) * KP, * qr = qn + (rt * 4) * KP, * kc = kn + (st * 4) * KP;
+            // lane `part` takes every GC_PARTS-th group of four dimensions: the lanes of a tile read neighbouring
+            // 16-byte pieces (a contiguous share per lane put all of them on the same banks)
+            for (int i = part * 4; live && i < S; i += 4 * GC_PARTS) {
+                float4 kc4[4], kr4[4], qr4[4];
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    kc4[x] = *reinterpret_cast<const float4 *>(kc + x * KP + i);
+                    kr4[x] = *reinterpret_cast<const float4 *>(kr + x * KP + i);
+                    qr4[x] = *reinterpret_cast<const float4 *>(qr + x * KP + i);
+                }
+#pragma unroll
+                for (int x = 0; x < 4; x++)
+#pragma unroll
+                    for (int y = 0; y < 4; y++) {
+                        g[x][y] = fmaf(kr4[x].x, kc4[y].x, g[x][y]);
+                        g[x][y] = fmaf(kr4[x].y, kc4[y].y, g[x][y]);
+                        g[x][y] = fmaf(kr4[x].z, kc4[y].z, g[x][y]);
+                        g[x][y] = fmaf(kr4[x].w, kc4[y].w, g[x][y]);
+                        q[x][y] = fmaf(qr4[x].x, kc4[y].x, q[x][y]);
+                        q[x][y] = fmaf(qr4[x].y, kc4[y].y, q[x][y]);
+                        q[x][y] = fmaf(qr4[x].z, kc4[y].z, q[x][y]);
+                        q[x][y] = fmaf(qr4[x].w, kc4[y].w, q[x][y]);
+                    }
+            }
+            // the GC_PARTS lanes of a tile are adjacent: fixed-order sum by three exchanges
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) {
+                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 1);
+                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 2);
+                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 4);
+                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 1);
+                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 2);
+                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 4);
+                }
+            // tile `task` of the staging area: 16 values of K K^T, then 16 of Q K^T; lane p writes one row of four
+            if (live) {
+                float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    if (part == x) row = make_float4(g[x][0], g[x][1], g[x][2], g[x][3]);
+                    if (part == x + 4) row = make_float4(q[x][0], q[x][1], q[x][2], q[x][3]);
+                }
+                *reinterpret_cast<float4 *>(stage + task * 32 + part * 4) = row;
+            }
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    cluster_sync_all();  // every CTA's tiles are in its staging area; this CTA's state block and v have landed
+    {
+        // (at most 136 tiles of eight rows of four values: three rows per thread, fetched together as 16-byte loads;
+        // single-word loads from the other CTAs' shared memory took 6.7 k cycles here)
+        constexpr int PER = (GDN_MAX_NODES / 4) * (GDN_MAX_NODES / 4 + 1) / 2 * 8 / GC_THREADS + 1;
+        float4 raw[PER];
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int e = tid + k * GC_THREADS;  // row e & 7 of tile e >> 3
+            const int owner = (e >> 3) % CL;
+            raw[k] = e >= n_tasks * 8    ? make_float4(0.f, 0.f, 0.f, 0.f)
+                     : owner == cb       ? *reinterpret_cast<const float4 *>(stage + e * 4)
+                                         : ld_cluster_f32x4(stage + e * 4, (unsigned)owner);
+        }
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int e = tid + k * GC_THREADS;
+            if (e >= n_tasks * 8) continue;
+            const int task = e >> 3, within = e & 7;
+            int rt = (int)((sqrtf(8.0f * (float)task + 1.0f) - 1.0f) * 0.5f);
+            while ((rt + 1) * (rt + 2) / 2 <= task) rt++;
+            while (rt * (rt + 1) / 2 > task) rt--;
+            const int r = rt * 4 + (within & 3), c0 = (task - rt * (rt + 1) / 2) * 4;
+            const float lr = lg[r], br = bet[r];
+            const float v4[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+#pragma unroll
+            for (int y = 0; y < 4; y++) {
+                const int c = c0 + y;
+                const float wgt = c <= r ? expf(lr - lg[c]) : 0.0f;
+                if (within < 4) Bm[r * NP + c] = c < r ? br * wgt * v4[y] : 0.0f;
+                else Am[r * NP + c] = wgt * v4[y];
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- K S_0 and Q S_0 for this CTA's columns: 4 x 4 tiles, two lanes per tile (alternate groups of four state rows) ----
+    {
+        const int total = 2 * NT4 * (GDN_COLS / 4) * 2;
+        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
+            const int w = wbase + lane;
+            const bool live = w < total;  // uniform over the two lanes of a tile
+            const int part = w & 1, t2 = live ? w >> 1 : 0;
+            const int ct = t2 % (GDN_COLS / 4), rt = (t2 / (GDN_COLS / 4)) % NT4, which = t2 / ((GDN_COLS / 4) * NT4);
+            const float * src = (which ? qn : kn) + (rt * 4) * KP;
+            float acc[4][4];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) acc[x][y] = 0.0f;
+            for (int i = part * 4; live && i < S; i += 8) {
+                float4 r4[4], s4[4];
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    r4[x] = *reinterpret_cast<const float4 *>(src + x * KP + i);
+                    s4[x] = *reinterpret_cast<const float4 *>(s0 + (i + x) * SP + ct * 4);
+                }
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    acc[x][0] = fmaf(r4[x].x, s4[0].x, acc[x][0]); acc[x][1] = fmaf(r4[x].x, s4[0].y, acc[x][1]);
+                    acc[x][2] = fmaf(r4[x].x, s4[0].z, acc[x][2]); acc[x][3] = fmaf(r4[x].x, s4[0].w, acc[x][3]);
+                    acc[x][0] = fmaf(r4[x].y, s4[1].x, acc[x][0]); acc[x][1] = fmaf(r4[x].y, s4[1].y, acc[x][1]);
+                    acc[x][2] = fmaf(r4[x].y, s4[1].z, acc[x][2]); acc[x][3] = fmaf(r4[x].y, s4[1].w, acc[x][3]);
+                    acc[x][0] = fmaf(r4[x].z, s4[2].x, acc[x][0]); acc[x][1] = fmaf(r4[x].z, s4[2].y, acc[x][1]);
+                    acc[x][2] = fmaf(r4[x].z, s4[2].z, acc[x][2]); acc[x][3] = fmaf(r4[x].z, s4[2].w, acc[x][3]);
+                    acc[x][0] = fmaf(r4[x].w, s4[3].x, acc[x][0]); acc[x][1] = fmaf(r4[x].w, s4[3].y, acc[x][1]);
+                    acc[x][2] = fmaf(r4[x].w, s4[3].z, acc[x][2]); acc[x][3] = fmaf(r4[x].w, s4[3].w, acc[x][3]);
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) acc[x][y] += __shfl_xor_sync(0xffffffffu, acc[x][y], 1);
+            if (live && part == 0) {
+                float * dst = (which ? o_s : ks) + (rt * 4) * GDN_COLS + ct * 4;
+#pragma unroll
+                for (int x = 0; x < 4; x++) *reinterpret_cast<float4 *>(dst + x * GDN_COLS) = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- right-hand side beta (v - gam K S_0); meanwhile two warps invert the 16 x 16 diagonal blocks of I + B ----
+    for (int i = tid; i < NPAD * GDN_COLS; i += GC_THREADS) {
+        const int r = i / GDN_COLS, c = i - r * GDN_COLS;
+        ks[i] = bet[r] * (vv[r * VP + c] - expf(lg[r]) * ks[i]);
+    }
+    if (warp >= GC_THREADS / 32 - 2) {
+        // half a warp per block, lane = column s of the inverse T: row r of T is e_r minus the rows before it
+        // weighted by row r of B (forward substitution, as inverseLower of recurrent.go:307-331 does for the
+        // whole chunk). Rows beyond the chunk have B = 0 and stay rows of the identity.
+        const int blk = (warp - (GC_THREADS / 32 - 2)) * 2 + (lane >> 4), sc = lane & 15, b0 = blk * 16;
+        if (b0 < N) {
+            float t[16];
+#pragma unroll
+            for (int r = 0; r < 16; r++) {
+                float v = r == sc ? 1.0f : 0.0f;
+                if (b0 + r < NPAD) {
+                    const float * brow = Bm + (b0 + r) * NP + b0;
+#pragma unroll
+                    for (int u = 0; u < r; u++) v = fmaf(-brow[u], t[u], v);
+                }
+                t[r] = v;
+                Tm[(blk * 16 + r) * 17 + sc] = v;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- forward substitution over the blocks: D_b = T_b (rhs_b - B[b][earlier] D[earlier]), a row per warp ----
+    for (int b0 = 0; b0 < N; b0 += 16) {
+        const int r = b0 + warp;  // GC_THREADS / 32 == 16 rows
+        if (b0 > 0) {
+            if (r < N) {
+                float acc0 = ks[r * GDN_COLS + lane], acc1 = 0.0f;
+                const float * brow = Bm + r * NP;
+#pragma unroll 8
+                for (int s2 = 0; s2 < b0; s2 += 2) {  // b0 is a multiple of 16
+                    acc0 = fmaf(-brow[s2], dd[s2 * GDN_COLS + lane], acc0);
+                    acc1 = fmaf(-brow[s2 + 1], dd[(s2 + 1) * GDN_COLS + lane], acc1);
+                }
+                ks[r * GDN_COLS + lane] = acc0 + acc1;
+            }
+            __syncthreads();
+        }
+        if (r < NPAD) {
+            const float * trow = Tm + r * 17;
+            float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 16; u += 2) {
+                if (u <= warp) acc0 = fmaf(trow[u], ks[(b0 + u) * GDN_COLS + lane], acc0);
+                if (u + 1 <= warp) acc1 = fmaf(trow[u + 1], ks[(b0 + u + 1) * GDN_COLS + lane], acc1);
+            }
+            dd[r * GDN_COLS + lane] = acc0 + acc1;
+        }
+        __syncthreads();
+    }
+    // vv <- exp(g_C - g_s) d_s for the state update
+    {
+        const float lc = lg[N - 1];
+        for (int i = tid; i < NPAD * GDN_COLS; i += GC_THREADS) {
+            const int r = i / GDN_COLS, c = i - r * GDN_COLS;
+            vv[r * VP + c] = r < N ? expf(lc - lg[r]) * dd[i] : 0.0f;
+        }
+    }
+    // ---- outputs: gam_r (Q S_0)_r + sum_{s <= r} A[r][s] d_s; warp w takes rows w, w + 16, ... ----
+    for (int r = warp; r < N; r += GC_THREADS / 32) {
+        float acc0 = expf(lg[r]) * o_s[r * GDN_COLS + lane], acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+        const float * arow = Am + r * NP;
+        int s2 = 0;
+#pragma unroll 4
+        for (; s2 + 3 <= r; s2 += 4) {
+            acc0 = fmaf(arow[s2], dd[s2 * GDN_COLS + lane], acc0);
+            acc1 = fmaf(arow[s2 + 1], dd[(s2 + 1) * GDN_COLS + lane], acc1);
+            acc2 = fmaf(arow[s2 + 2], dd[(s2 + 2) * GDN_COLS + lane], acc2);
+            acc3 = fmaf(arow[s2 + 3], dd[(s2 + 3) * GDN_COLS + lane], acc3);
+        }
+        for (; s2 <= r; s2++) acc0 = fmaf(arow[s2], dd[s2 * GDN_COLS + lane], acc0);
+        o_s[r * GDN_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
+    }
+    __syncthreads();
+
+    // ---- new state: gam_C S_0 + K^T (w d), 4 x 4 tiles, written in place ----
+    {
+        const float gam_c = expf(lg[N - 1]);
+        const int total = (S / 4) * (GDN_COLS / 4) * 2;  // two lanes per tile: even and odd rows of the chunk
+        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
+            const int w = wbase + lane;
+            const bool live = w < total;
+            const int part = w & 1, t2 = live ? w >> 1 : 0;
+            const int jt = t2 % (GDN_COLS / 4), it = t2 / (GDN_COLS / 4);
+            float acc[4][4];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) acc[x][y] = 0.0f;
+#pragma unroll 4
+            for (int s2 = part; live && s2 < N; s2 += 2) {
+                const float4 k4 = *reinterpret_cast<const float4 *>(kn + s2 * KP + it * 4);
+                const float4 d4 = *reinterpret_cast<const float4 *>(vv + s2 * VP + jt * 4);
+                acc[0][0] = fmaf(k4.x, d4.x, acc[0][0]); acc[0][1] = fmaf(k4.x, d4.y, acc[0][1]);
+                acc[0][2] = fmaf(k4.x, d4.z, acc[0][2]); acc[0][3] = fmaf(k4.x, d4.w, acc[0][3]);
+                acc[1][0] = fmaf(k4.y, d4.x, acc[1][0]); acc[1][1] = fmaf(k4.y, d4.y, acc[1][1]);
+                acc[1][2] = fmaf(k4.y, d4.z, acc[1][2]); acc[1][3] = fmaf(k4.y, d4.w, acc[1][3]);
+                acc[2][0] = fmaf(k4.z, d4.x, acc[2][0]); acc[2][1] = fmaf(k4.z, d4.y, acc[2][1]);
+                acc[2][2] = fmaf(k4.z, d4.z, acc[2][2]); acc[2][3] = fmaf(k4.z, d4.w, acc[2][3]);
+                acc[3][0] = fmaf(k4.w, d4.x, acc[3][0]); acc[3][1] = fmaf(k4.w, d4.y, acc[3][1]);
+                acc[3][2] = fmaf(k4.w, d4.z, acc[3][2]); acc[3][3] = fmaf(k4.w, d4.w, acc[3][3]);
+            }
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) acc[x][y] += __shfl_xor_sync(0xffffffffu, acc[x][y], 1);
+            if (live && part == 0) {
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    const float4 o4 = *reinterpret_cast<const float4 *>(s0 + (it * 4 + x) * SP + jt * 4);
+                    *reinterpret_cast<float4 *>(state + (int64_t)(it * 4 + x) * S + jt * 4) =
+                        make_float4(fmaf(gam_c, o4.x, acc[x][0]), fmaf(gam_c, o4.y, acc[x][1]), fmaf(gam_c, o4.z, acc[x][2]),
+                                    fmaf(gam_c, o4.w, acc[x][3]));
+                }
+            }
+        }
+    }
+
+    pdl_trigger_late();
+    // ---- gated RMSNorm of the head (recurrent.go:39-50), sums of squares exchanged across the cluster ----
+    for (int node = warp; node < N; node += GC_THREADS / 32) {
+        const double v = (double)o_s[node * GDN_COLS + lane];
+        double sq = v * v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) ssq[node] = sq;
+    }
+    cluster_sync_all();
+    for (int node = tid; node < N; node += GC_THREADS) {
+        double tot = 0;
+        for (unsigned r = 0; r < gridDim.x; r++) tot += ld_cluster_f64(ssq + node, r);  // the cluster spans gridDim.x
+        const float mean = (float)(tot / (double)S);
+        scale_s[node] = (float)(1.0 / sqrt((double)(mean + a.eps)));
+    }
+    cluster_sync_all();  // scales visible to the CTA; no CTA leaves while another may still read its sums
+#pragma unroll
+    for (int k = 0; k < ZPRE; k++) {
+        const int i = tid + k * GC_THREADS;
+        if (i < N * GDN_COLS) {
+            const int node = i / GDN_COLS;
+            o_s[i] = o_s[i] * (scale_s[node] * norm_w) * silu_ref(zpre[k]);
+        }
+    }
+    __syncthreads();
+    for (int gi = tid; gi < N * (GDN_COLS >> 4); gi += GC_THREADS) {
+        const int node = gi / (GDN_COLS >> 4), part = gi - node * (GDN_COLS >> 4);
+        const int64_t r = seq * N + node;
+        const int c0 = h * S + cb * GDN_COLS + part * 16;
+        float g16[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) g16[i] = o_s[node * GDN_COLS + part * 16 + i];
+        float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + c0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
+        if (a.prep.xh) xprep_store16(a.prep.xh + r * inner + c0, a.prep.xl + r * inner + c0, a.prep.xs16 + r * (inner >> 4) + (c0 >> 4), g16);
+    }
+}
+
+static size_t gdn_chunk_smem(int N, int S) {
+    const int npad = (N + 3) & ~3;
+    return sizeof(float) * ((size_t)2 * npad * (S + 4) + (size_t)S * (GDN_COLS + 4) + (size_t)npad * (GDN_COLS + 16) + (size_t)3 * npad * GDN_COLS +
+                            (size_t)2 * npad * (npad + 1) + 2 * npad + (size_t)((N + 15) / 16) * 16 * 17 + 4 +
+                            (size_t)(npad / 4) * (npad / 4 + 1) / 2 * 32);
+}
+
+// Front end + chunkwise scan of a chain whose rows are all committed; the state is rewritten in place (the conv
+// history still moves with launch_gdn_commit_conv). Returns the number of kernels launched.
+int launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
+    YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per sequence", GDN_MAX_NODES);
+    YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
+    YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
+    ScanParams p{a, rows};
+    const int N = rows.nodes;
+    dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
+    dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
+    launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
+    YK_CUDA(cudaGetLastError());
+    const size_t smem = gdn_chunk_smem(N, a.S);
+    if (a.S == 128) {
+        YK_CUDA(cudaFuncSetAttribute(gdn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        launch_k_cluster(gdn_chunk_kernel<128>, grid, GC_THREADS, smem, s, grid.x, p);
+    } else {
+        YK_CUDA(cudaFuncSetAttribute(gdn_chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        launch_k_cluster(gdn_chunk_kernel<64>, grid, GC_THREADS, smem, s, grid.x, p);
+    }
+    YK_CUDA(cudaGetLastError());
+    return 2;
+}
+
+// ---------------------------------------------------------------------------
 // commit
 
 struct CommitParams {
@@ -318,6 +781,7 @@ struct CommitParams {
     int groups, rank, S, kernel, conv_dim;
     int seq_base;  // first sequence of the step within the session's state arrays
     int row_base;  // first row of the step within the layer's per-row logs (sub-chunks of a wide prompt pass)
+    int conv_only; // the grid holds only the conv-history blocks (the chunkwise scan has written the state itself)
     RowMeta rows;
     AcceptOut acc;
 };
@@ -333,7 +797,7 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
     const int a = p.acc.accepted[seq];
     const int32_t * path = p.acc.path + (int64_t)seq * N;
     auto node_at = [&](int t) { return t == 0 ? 0 : path[t - 1]; };  // t = 0..a
-    if ((int)blockIdx.x < COMMIT_PARTS * p.rank) {
+    if (!p.conv_only && (int)blockIdx.x < COMMIT_PARTS * p.rank) {
         // S/4 rows of one head's S x S state, read and written once as float4 however many rows were accepted.
         // A thread owns four columns j and up to four rows i and keeps them in registers. The accepted rows'
         // keys (this part's S/4 of them), d values and decays are brought into shared memory in one round of
@@ -404,7 +868,7 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
             src_row[threadIdx.x] = src >= 0 ? p.row_base + seq * N + node_at(src) : -1;
         }
         __syncthreads();
-        const int part = blockIdx.x - COMMIT_PARTS * p.rank;
+        const int part = p.conv_only ? (int)blockIdx.x : (int)blockIdx.x - COMMIT_PARTS * p.rank;
         const int per = (p.conv_dim + COMMIT_CONV_PARTS - 1) / COMMIT_CONV_PARTS;
         const int c_end = min(p.conv_dim, (part + 1) * per);
         for (int c = part * per + threadIdx.x; c < c_end; c += blockDim.x) {
@@ -424,10 +888,11 @@ __global__ void __launch_bounds__(256, 4) gdn_commit_kernel(const CommitParams p
 }
 
 void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_layers, int groups, int rank, int S,
-                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base) {
+                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base,
+                       bool conv_only) {
     if (n_layers == 0) return;
-    CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, row_base, rows, acc};
-    dim3 grid(COMMIT_PARTS * rank + COMMIT_CONV_PARTS, rows.batch, n_layers);
+    CommitParams p{layers_dev, groups, rank, S, kernel, conv_dim, seq_base, row_base, conv_only ? 1 : 0, rows, acc};
+    dim3 grid(conv_only ? COMMIT_CONV_PARTS : COMMIT_PARTS * rank + COMMIT_CONV_PARTS, rows.batch, n_layers);
     launch_k(gdn_commit_kernel, grid, 256, 0, s, p);
     YK_CUDA(cudaGetLastError());
 }

@@ -98,6 +98,9 @@ struct GdnArgs {
 };
 // conv + norms, the recurrence and the gated RMSNorm; returns the number of kernels launched
 int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
+// the same for a chain whose rows are all committed, in the chunkwise WY form: the state is rewritten in place, no
+// delta log is written (the conv history moves with launch_gdn_commit(..., conv_only = true))
+int launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
 // First-maximum argmax of every logits row (speculative.go:263-271) followed by
 // the greedy tree walk (speculative.go:193-202 generalised to a tree).
 struct AcceptOut {
@@ -133,7 +136,8 @@ struct GdnLayerCommit {
     float * state;
 };
 void launch_gdn_commit(cudaStream_t s, const GdnLayerCommit * layers_dev, int n_layers, int groups, int rank, int S,
-                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base = 0);
+                       int kernel, int conv_dim, int seq_base, const RowMeta & rows, const AcceptOut & acc, int row_base = 0,
+                       bool conv_only = false);
 struct KvLayerCommit {
     uint8_t * k;
     uint8_t * v;
