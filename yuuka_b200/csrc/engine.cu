@@ -827,8 +827,15 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             if (sub == 0) {
                 s->launches += launch_gdn_scan(st, g, rows);
             } else {
-                // sub-chunk after sub-chunk: scan, then this layer's state and conv history move on before the next
+                // sub-chunk after sub-chunk: scan, then this layer's state and conv history move on before the next.
+                // Every row of a prompt pass is committed, so by default the front end runs once for the whole pass,
+                // the chunkwise form of the recurrence writes the state itself, and the conv history moves once.
                 const int key_dim = c.group_count * S;
+                const bool chunked = s->gdn_chunked;
+                if (chunked) {
+                    launch_gdn_front_chain(st, g, seq0, nodes);
+                    s->launches++;
+                }
                 for (int k = 0; k < n_sub; k++) {
                     const int64_t r0 = (int64_t)k * sub;
                     GdnArgs gk = g;
@@ -847,12 +854,21 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
                     gk.dlog = g.dlog + r0 * inner;
                     gk.decay = g.decay + r0 * rank;
                     const RowMeta rk = sub_rows(k);
-                    // every row of a prompt sub-chunk is committed: the chunkwise form writes the state itself
-                    const bool chunked = s->gdn_chunked;
-                    s->launches += chunked ? launch_gdn_chunk(st, gk, rk) : launch_gdn_scan(st, gk, rk);
+                    if (chunked) {
+                        launch_gdn_chunk(st, gk, rk);
+                        s->launches++;
+                        continue;
+                    }
+                    s->launches += launch_gdn_scan(st, gk, rk);
                     AcceptOut ak{s->d_acc_sub + k, s->acc.path, s->acc.emitted};
                     launch_gdn_commit(st, s->d_gdn_commit + gdn_index, 1, c.group_count, rank, S, c.conv_kernel, conv_dim, seq0, rk,
-                                      ak, (int)r0, chunked);
+                                      ak, (int)r0);
+                    s->launches++;
+                }
+                if (chunked) {
+                    // (rows = the whole pass, accepted = all of it: launch_accept_all has filled the identity path)
+                    launch_gdn_commit(st, s->d_gdn_commit + gdn_index, 1, c.group_count, rank, S, c.conv_kernel, conv_dim, seq0, rows,
+                                      s->acc, 0, true);
                     s->launches++;
                 }
             }

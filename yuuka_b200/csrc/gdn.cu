@@ -38,6 +38,7 @@ __device__ __forceinline__ float state_update(float s, float decay, float k, flo
 struct ScanParams {
     GdnArgs a;
     RowMeta rows;
+    int chain;  // front end only: the rows are one chain (row i follows row i - 1), however many there are
 };
 
 // ---------------------------------------------------------------------------
@@ -58,8 +59,10 @@ __global__ void gdn_front_kernel(const ScanParams p) {
     const int r = seq * N + node;
     __shared__ int par[GDN_MAX_NODES];
     __shared__ double red[4];
-    for (int i = threadIdx.x; i < N; i += blockDim.x) par[i] = p.rows.parent[seq * N + i];
-    __syncthreads();
+    if (!p.chain) {
+        for (int i = threadIdx.x; i < N; i += blockDim.x) par[i] = p.rows.parent[seq * N + i];
+        __syncthreads();
+    }
     const int e = threadIdx.x;
     const int c = u * S + e;  // q units, then k units, then v units: exactly the conv row order
     float taps[8];
@@ -71,7 +74,7 @@ __global__ void gdn_front_kernel(const ScanParams p) {
             if (t >= a.kernel) { taps[t] = 0.0f; continue; }
             if (cur >= 0) {
                 taps[t] = a.proj[(int64_t)(seq * N + cur) * a.ldp + c];
-                cur = par[cur];
+                cur = p.chain ? cur - 1 : par[cur];
             } else {
                 taps[t] = hist[hidx--];
             }
@@ -292,7 +295,7 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per sequence", GDN_MAX_NODES);
     YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
     YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
-    ScanParams p{a, rows};
+    ScanParams p{a, rows, 0};
     const int N = rows.nodes;
     dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
@@ -749,18 +752,29 @@ static size_t gdn_chunk_smem(int N, int S) {
                             (size_t)(npad / 4) * (npad / 4 + 1) / 2 * 32);
 }
 
-// Front end + chunkwise scan of a chain whose rows are all committed; the state is rewritten in place (the conv
-// history still moves with launch_gdn_commit_conv). Returns the number of kernels launched.
-int launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
-    YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per sequence", GDN_MAX_NODES);
+// The front end alone for one chain of any length (a whole prompt pass of one sequence): conv taps come from the
+// preceding rows of the pass and, for its first kernel - 1 rows, from the stored history.
+void launch_gdn_front_chain(cudaStream_t s, const GdnArgs & a, int seq_slot, int n_rows) {
     YK_REQUIRE(a.kernel >= 2 && a.kernel <= 8, YUUKA_ERR_UNSUPPORTED, "gdn: conv kernel %d is outside 2..8", a.kernel);
     YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
-    ScanParams p{a, rows};
-    const int N = rows.nodes;
-    dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
-    dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
+    (void)seq_slot;
+    RowMeta rows{};
+    rows.batch = 1;
+    rows.nodes = n_rows;
+    ScanParams p{a, rows, 1};
+    dim3 fgrid(2 * a.groups + a.rank, n_rows, 1);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
+}
+
+// Chunkwise scan of a chain of at most 64 rows that are all committed, after the front end has run for them; the
+// state is rewritten in place (the conv history still moves with launch_gdn_commit(..., conv_only)).
+void launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
+    YK_REQUIRE(rows.nodes <= GDN_MAX_NODES, YUUKA_ERR_UNSUPPORTED, "gdn: at most %d rows per chunk", GDN_MAX_NODES);
+    YK_REQUIRE(a.S == 64 || a.S == 128, YUUKA_ERR_UNSUPPORTED, "gdn: state size %d is not 64 or 128", a.S);
+    ScanParams p{a, rows, 0};
+    const int N = rows.nodes;
+    dim3 grid(a.S / GDN_COLS, a.rank, rows.batch);
     const size_t smem = gdn_chunk_smem(N, a.S);
     if (a.S == 128) {
         YK_CUDA(cudaFuncSetAttribute(gdn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -770,7 +784,6 @@ int launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
         launch_k_cluster(gdn_chunk_kernel<64>, grid, GC_THREADS, smem, s, grid.x, p);
     }
     YK_CUDA(cudaGetLastError());
-    return 2;
 }
 
 // ---------------------------------------------------------------------------

@@ -98,9 +98,11 @@ struct GdnArgs {
 };
 // conv + norms, the recurrence and the gated RMSNorm; returns the number of kernels launched
 int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
-// the same for a chain whose rows are all committed, in the chunkwise WY form: the state is rewritten in place, no
-// delta log is written (the conv history moves with launch_gdn_commit(..., conv_only = true))
-int launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
+// Prompt passes (one chain, every row committed): the front end once for the whole pass, then the chunkwise WY
+// form of the recurrence over chunks of at most 64 rows, which rewrites the state in place and writes no delta
+// log; the conv history moves once per pass with launch_gdn_commit(..., conv_only = true).
+void launch_gdn_front_chain(cudaStream_t s, const GdnArgs & a, int seq_slot, int n_rows);
+void launch_gdn_chunk(cudaStream_t s, const GdnArgs & a, const RowMeta & rows);
 // First-maximum argmax of every logits row (speculative.go:263-271) followed by
 // the greedy tree walk (speculative.go:193-202 generalised to a tree).
 struct AcceptOut {
