@@ -324,10 +324,54 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
 //   S_C = gam_C S_0 + sum_s exp(g_C - g_s) k_s d_s^T
 // grid (S/32 column blocks, rank, batch), the column blocks of a head one cluster (gated norm as in the scan
 // kernel); a CTA owns 32 columns of the state, of V, D and the outputs, and computes the row-by-row matrices
-// (K K^T, Q K^T: they do not depend on the column) itself. fp32 FMA throughout. The state is rewritten in
-// place: no delta log, no separate state commit.
+// (K K^T, Q K^T: they do not depend on the column) itself. The state is rewritten in place: no delta log, no
+// separate state commit.
+//
+// Every product is a tensor-core product, mma.sync m16n8k8 on tf32 operands, with both operands split into two
+// tf32 parts (x = hi + lo, three products: lo hi, hi lo, hi hi), which keeps fp32-level accuracy: the two forms
+// of the recurrence have to agree to 1e-4 (model/qwen35/recurrent_test.go:60-64). A first form of this kernel
+// on fp32 FMAs with 4 x 4 register tiles was bound by shared-memory loads and latency chains (48 k cycles per
+// 64-row chunk against 100 k for the row-by-row scan).
 constexpr int GC_THREADS = 512;
-constexpr int GC_PARTS = 8;   // lanes that share one tile of K K^T / Q K^T (each an eighth of the head dimension)
+constexpr int GC_WARPS = GC_THREADS / 32;
+constexpr int GC_CP = GDN_COLS + 8;  // pitch of the [row][32 columns] arrays and of the state block: the four k rows
+                                     // a B fragment reads fall on distinct banks (8 t + g)
+
+// x = hi + lo with hi the leading 10 mantissa bits (the tensor core ignores the low 13 bits of a tf32 operand, so
+// lo, exact in fp32, is used as it is: its own truncation is 2^-20 of x). Masking instead of cvt.rna.tf32: the
+// conversion instruction issues at a fraction of the ALU rate and was the whole cost of this kernel's products.
+__device__ __forceinline__ void tf32_split(float x, uint32_t & hi, uint32_t & lo) {
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// acc[j] += A (16 x 8 ksteps) * B (8 ksteps x 8, NT tiles side by side). fa(row, k) and fb(k, col) read one
+// element of the operands; lane (g, t) of the warp holds rows g, g + 8 and k columns t, t + 4 of A, k rows t, t + 4
+// and column g of B, and elements (g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1) of each 16 x 8 result.
+template <int NT, class FA, class FB>
+__device__ __forceinline__ void warp_mma_3x(float (&acc)[NT][4], int ksteps, FA fa, FB fb, int g, int t) {
+    for (int ks = 0; ks < ksteps; ks++) {
+        const int k0 = ks * 8;
+        uint32_t ah[4], al[4];
+        tf32_split(fa(g, k0 + t), ah[0], al[0]);
+        tf32_split(fa(g + 8, k0 + t), ah[1], al[1]);
+        tf32_split(fa(g, k0 + t + 4), ah[2], al[2]);
+        tf32_split(fa(g + 8, k0 + t + 4), ah[3], al[3]);
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            uint32_t bh[2], bl[2];
+            tf32_split(fb(k0 + t, 8 * j + g), bh[0], bl[0]);
+            tf32_split(fb(k0 + t + 4, 8 * j + g), bh[1], bl[1]);
+            mma_tf32(acc[j], al, bh);
+            mma_tf32(acc[j], ah, bl);
+            mma_tf32(acc[j], ah, bh);
+        }
+    }
+}
 
 template <int S>
 __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanParams p) {
@@ -338,34 +382,32 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
     const int kh = h % a.groups;
     const int key_dim = a.groups * S, inner = a.rank * S;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr int KP = S + 4;            // pitch of a q / k row (16-byte aligned, rows spread over the banks)
-    constexpr int SP = GDN_COLS + 4;     // pitch of a row of the state block, VP of a row of v / scaled d: two lanes
-    constexpr int VP = GDN_COLS + 16;    // that read neighbouring rows hit disjoint banks
-    const int NT4 = (N + 3) >> 2;        // 4-row tiles
-    const int NPAD = NT4 * 4;
-    const int NP = NPAD + 1;             // pitch of the row-by-row matrices
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int KP = S + 4;            // pitch of a q / k row: the eight rows an A fragment reads fall on banks 4 g + t
+    constexpr int CP = GC_CP;
+    const int MT = (N + 15) >> 4;        // 16-row tiles
+    const int NR = MT * 16;              // rows with padding (zero rows)
+    const int NP = NR + 4;               // pitch of the row-by-row matrices (banks 4 g + t again)
 
     extern __shared__ __align__(16) float sm[];
-    float * qn = sm;                          // [NPAD][KP]
-    float * kn = qn + NPAD * KP;              // [NPAD][KP]
-    float * s0 = kn + NPAD * KP;              // [S][SP]   this CTA's columns of the stored state
-    float * vv = s0 + S * SP;                 // [NPAD][VP] v, later exp(g_C - g_s) d_s
-    float * ks = vv + NPAD * VP;              // [NPAD][32] K S_0, then the right-hand side, then D
-    float * dd = ks + NPAD * GDN_COLS;        // [NPAD][32] D
-    float * o_s = dd + NPAD * GDN_COLS;       // [NPAD][32] Q S_0, then the outputs
-    float * Bm = o_s + NPAD * GDN_COLS;       // [NPAD][NP] beta_r w_rs (k_r . k_s), s < r
-    float * Am = Bm + NPAD * NP;              // [NPAD][NP] w_rs (q_r . k_s), s <= r
-    float * lg = Am + NPAD * NP;              // [NPAD] cumulative log decay
-    float * bet = lg + NPAD;                  // [NPAD]
-    float * Tm = bet + NPAD;                  // [NPAD / 16 rounded up][16][17] inverses of the diagonal blocks of I + B
-    float * stage = Tm + ((N + 15) / 16) * 16 * 17 + 3;  // [tiles][32] raw dot products of the tiles this CTA computed
-    stage -= (stage - sm) & 3;                            // (16-byte aligned)
+    float * qn = sm;                     // [NR][KP]
+    float * kn = qn + NR * KP;           // [NR][KP]
+    float * s0 = kn + NR * KP;           // [S][CP]  this CTA's columns of the stored state
+    float * vv = s0 + S * CP;            // [NR][CP] v, later exp(g_C - g_s) d_s
+    float * ks = vv + NR * CP;           // [NR][CP] K S_0, then the right-hand side
+    float * dd = ks + NR * CP;           // [NR][CP] D
+    float * o_s = dd + NR * CP;          // [NR][CP] Q S_0, then the outputs
+    float * Bm = o_s + NR * CP;          // [NR][NP] beta_r w_rs (k_r . k_s), s < r
+    float * Am = Bm + NR * NP;           // [NR][NP] w_rs (q_r . k_s), s <= r
+    float * Tm = Am + NR * NP;           // [NR][20] inverses of the 16 x 16 diagonal blocks of I + B
+    float * lg = Tm + NR * 20;           // [NR] cumulative log decay
+    float * bet = lg + NR;               // [NR]
     __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
 
-    // ---- loads, asynchronous: q and k (needed first), then this CTA's block of the state; v, beta, decay ----
+    // ---- loads, asynchronous: q and k (needed first), then this CTA's block of the state and v; beta, decay ----
     constexpr int SQ = S / 4;
-    for (int i = tid; i < NPAD * SQ; i += GC_THREADS) {
+    for (int i = tid; i < NR * SQ; i += GC_THREADS) {
         const int node = i / SQ, e4 = i - node * SQ;
         if (node < N) {
             const int64_t at = (int64_t)(seq * N + node) * key_dim + kh * S + e4 * 4;
@@ -382,15 +424,15 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
     float * state = const_cast<float *>(a.state) + ((int64_t)(seq_of(p.rows, seq) * a.rank + h) * S) * S + cb * GDN_COLS;
     for (int i = tid; i < S * (GDN_COLS / 4); i += GC_THREADS) {
         const int row = i / (GDN_COLS / 4), c4 = i - row * (GDN_COLS / 4);
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s0 + row * SP + c4 * 4);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(state + (int64_t)row * S + c4 * 4) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(s0 + row * CP + c4 * 4)),
+                     "l"(state + (int64_t)row * S + c4 * 4) : "memory");
     }
-    for (int i = tid; i < NPAD * (GDN_COLS / 4); i += GC_THREADS) {
+    for (int i = tid; i < NR * (GDN_COLS / 4); i += GC_THREADS) {
         const int node = i / (GDN_COLS / 4), e4 = i - node * (GDN_COLS / 4);
         if (node < N)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(vv + node * VP + e4 * 4)),
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(vv + node * CP + e4 * 4)),
                          "l"(a.vconv + (int64_t)(seq * N + node) * inner + h * S + cb * GDN_COLS + e4 * 4) : "memory");
-        else *reinterpret_cast<float4 *>(vv + node * VP + e4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        else *reinterpret_cast<float4 *>(vv + node * CP + e4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     // the gate values and the norm weight the last phase needs (a 64-row chunk: four per thread) are fetched now
@@ -403,7 +445,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
         zpre[k] = i < N * GDN_COLS ? a.z[(int64_t)(seq * N + node) * a.ldz + h * S + cb * GDN_COLS + c] : 0.0f;
     }
     const float norm_w = a.norm[cb * GDN_COLS + (tid & (GDN_COLS - 1))];
-    for (int node = tid; node < NPAD; node += GC_THREADS) {
+    for (int node = tid; node < NR; node += GC_THREADS) {
         float b = 0.0f, l = 0.0f;
         if (node < N) {
             b = a.beta[(int64_t)(seq * N + node) * a.rank + h];
@@ -414,10 +456,10 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
         o_s[node] = l;  // (scratch until the outputs are written)
     }
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // q and k have landed; the state may still be on its way
-    cluster_sync_all();  // (also: every CTA of the cluster runs before another writes into its shared memory)
+    __syncthreads();
     if (warp == 0) {
         // inclusive scan of the (at most 64) log decays: two per lane
-        const float l0 = lane < NPAD ? o_s[lane] : 0.0f, l1 = lane + 32 < NPAD ? o_s[lane + 32] : 0.0f;
+        const float l0 = lane < NR ? o_s[lane] : 0.0f, l1 = lane + 32 < NR ? o_s[lane + 32] : 0.0f;
         float s0v = l0, s1v = l1;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -425,290 +467,149 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
             if (lane >= o) { s0v += u0; s1v += u1; }
         }
         const float first = __shfl_sync(0xffffffffu, s0v, 31);
-        if (lane < NPAD) lg[lane] = s0v;
-        if (lane + 32 < NPAD) lg[lane + 32] = first + s1v;
+        if (lane < NR) lg[lane] = s0v;
+        if (lane + 32 < NR) lg[lane + 32] = first + s1v;
     }
     __syncthreads();
 
-    // ---- K K^T and Q K^T on the lower triangle, 4 x 4 tiles, GC_PARTS lanes per tile ----
-    // The tiles are dealt round-robin to the CTAs of the cluster. Each leaves the raw dot products of its tiles in
-    // its own shared memory; after the cluster barrier every CTA gathers all tiles (its own and, through
-    // distributed shared memory, the others') and folds the decay ratios and beta in on the way into B and A.
-    const int n_tasks = NT4 * (NT4 + 1) / 2, CL = (int)gridDim.x;
+    // ---- B and A: K K^T and Q K^T on the lower triangle (16 x 8 tiles whose columns start below the tile's last
+    // row), decay ratios and beta folded in on the way out; entries above the diagonal inside those tiles are zero ----
     {
-        // (whole warps walk the loop together: the lanes of a tile exchange their sums by shuffles)
-        const int total = (n_tasks - cb + CL - 1) / CL * GC_PARTS;
-        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
-            const int w = wbase + lane;
-            const bool live = w < total;  // uniform over the GC_PARTS lanes of a tile
-            const int task = live ? cb + CL * (w / GC_PARTS) : 0, part = w & (GC_PARTS - 1);
-            int rt = (int)((sqrtf(8.0f * (float)task + 1.0f) - 1.0f) * 0.5f);
-            while ((rt + 1) * (rt + 2) / 2 <= task) rt++;
-            while (rt * (rt + 1) / 2 > task) rt--;
-            const int st = task - rt * (rt + 1) / 2;
-            float g[4][4], q[4][4];
+        const int per_mat = MT * (MT + 1);  // sum over row tiles mt of 2 mt + 2 column tiles
+        for (int tile = warp; tile < 2 * per_mat; tile += GC_WARPS) {
+            const int mat = tile >= per_mat, rest = tile - mat * per_mat;
+            int mt = 0;
+            while ((mt + 1) * (mt + 2) <= rest) mt++;
+            const int nt = rest - mt * (mt + 1);
+            const float * arow = (mat ? qn : kn) + (16 * mt) * KP, * brow = kn + (8 * nt) * KP;
+            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+            warp_mma_3x<1>(acc, S / 8, [&](int r, int k) { return arow[r * KP + k]; }, [&](int k, int c) { return brow[c * KP + k]; }, g, t);
 #pragma unroll
-            for (int x = 0; x < 4; x++)
-#pragma unroll
-                for (int y = 0; y < 4; y++) g[x][y] = q[x][y] = 0.0f;
-            const float * kr = kn + (rt * 4) * KP, * qr = qn + (rt * 4) * KP, * kc = kn + (st * 4) * KP;
-            // lane `part` takes every GC_PARTS-th group of four dimensions: the lanes of a tile read neighbouring
-            // 16-byte pieces (a contiguous share per lane put all of them on the same banks)
-            for (int i = part * 4; live && i < S; i += 4 * GC_PARTS) {
-                float4 kc4[4], kr4[4], qr4[4];
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    kc4[x] = *reinterpret_cast<const float4 *>(kc + x * KP + i);
-                    kr4[x] = *reinterpret_cast<const float4 *>(kr + x * KP + i);
-                    qr4[x] = *reinterpret_cast<const float4 *>(qr + x * KP + i);
-                }
-#pragma unroll
-                for (int x = 0; x < 4; x++)
-#pragma unroll
-                    for (int y = 0; y < 4; y++) {
-                        g[x][y] = fmaf(kr4[x].x, kc4[y].x, g[x][y]);
-                        g[x][y] = fmaf(kr4[x].y, kc4[y].y, g[x][y]);
-                        g[x][y] = fmaf(kr4[x].z, kc4[y].z, g[x][y]);
-                        g[x][y] = fmaf(kr4[x].w, kc4[y].w, g[x][y]);
-                        q[x][y] = fmaf(qr4[x].x, kc4[y].x, q[x][y]);
-                        q[x][y] = fmaf(qr4[x].y, kc4[y].y, q[x][y]);
-                        q[x][y] = fmaf(qr4[x].z, kc4[y].z, q[x][y]);
-                        q[x][y] = fmaf(qr4[x].w, kc4[y].w, q[x][y]);
-                    }
-            }
-            // the GC_PARTS lanes of a tile are adjacent: fixed-order sum by three exchanges
-#pragma unroll
-            for (int x = 0; x < 4; x++)
-#pragma unroll
-                for (int y = 0; y < 4; y++) {
-                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 1);
-                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 2);
-                    g[x][y] += __shfl_xor_sync(0xffffffffu, g[x][y], 4);
-                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 1);
-                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 2);
-                    q[x][y] += __shfl_xor_sync(0xffffffffu, q[x][y], 4);
-                }
-            // tile `task` of the staging area: 16 values of K K^T, then 16 of Q K^T; lane p writes one row of four
-            if (live) {
-                float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    if (part == x) row = make_float4(g[x][0], g[x][1], g[x][2], g[x][3]);
-                    if (part == x + 4) row = make_float4(q[x][0], q[x][1], q[x][2], q[x][3]);
-                }
-                *reinterpret_cast<float4 *>(stage + task * 32 + part * 4) = row;
+            for (int e = 0; e < 4; e++) {
+                const int r = 16 * mt + g + (e >> 1) * 8, c = 8 * nt + 2 * t + (e & 1);
+                const float wgt = c <= r ? expf(lg[r] - lg[c]) : 0.0f;
+                if (mat) Am[r * NP + c] = wgt * acc[0][e];
+                else Bm[r * NP + c] = c < r ? bet[r] * wgt * acc[0][e] : 0.0f;
             }
         }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-    cluster_sync_all();  // every CTA's tiles are in its staging area; this CTA's state block and v have landed
-    {
-        // (at most 136 tiles of eight rows of four values: three rows per thread, fetched together as 16-byte loads;
-        // single-word loads from the other CTAs' shared memory took 6.7 k cycles here)
-        constexpr int PER = (GDN_MAX_NODES / 4) * (GDN_MAX_NODES / 4 + 1) / 2 * 8 / GC_THREADS + 1;
-        float4 raw[PER];
-#pragma unroll
-        for (int k = 0; k < PER; k++) {
-            const int e = tid + k * GC_THREADS;  // row e & 7 of tile e >> 3
-            const int owner = (e >> 3) % CL;
-            raw[k] = e >= n_tasks * 8    ? make_float4(0.f, 0.f, 0.f, 0.f)
-                     : owner == cb       ? *reinterpret_cast<const float4 *>(stage + e * 4)
-                                         : ld_cluster_f32x4(stage + e * 4, (unsigned)owner);
-        }
-#pragma unroll
-        for (int k = 0; k < PER; k++) {
-            const int e = tid + k * GC_THREADS;
-            if (e >= n_tasks * 8) continue;
-            const int task = e >> 3, within = e & 7;
-            int rt = (int)((sqrtf(8.0f * (float)task + 1.0f) - 1.0f) * 0.5f);
-            while ((rt + 1) * (rt + 2) / 2 <= task) rt++;
-            while (rt * (rt + 1) / 2 > task) rt--;
-            const int r = rt * 4 + (within & 3), c0 = (task - rt * (rt + 1) / 2) * 4;
-            const float lr = lg[r], br = bet[r];
-            const float v4[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
-#pragma unroll
-            for (int y = 0; y < 4; y++) {
-                const int c = c0 + y;
-                const float wgt = c <= r ? expf(lr - lg[c]) : 0.0f;
-                if (within < 4) Bm[r * NP + c] = c < r ? br * wgt * v4[y] : 0.0f;
-                else Am[r * NP + c] = wgt * v4[y];
-            }
-        }
-    }
     __syncthreads();
 
-    // ---- K S_0 and Q S_0 for this CTA's columns: 4 x 4 tiles, two lanes per tile (alternate groups of four state rows) ----
-    {
-        const int total = 2 * NT4 * (GDN_COLS / 4) * 2;
-        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
-            const int w = wbase + lane;
-            const bool live = w < total;  // uniform over the two lanes of a tile
-            const int part = w & 1, t2 = live ? w >> 1 : 0;
-            const int ct = t2 % (GDN_COLS / 4), rt = (t2 / (GDN_COLS / 4)) % NT4, which = t2 / ((GDN_COLS / 4) * NT4);
-            const float * src = (which ? qn : kn) + (rt * 4) * KP;
-            float acc[4][4];
+    // ---- K S_0 and Q S_0 for this CTA's columns: a warp per (matrix, 16-row tile, 16-column half) ----
+    for (int task = warp; task < 4 * MT; task += GC_WARPS) {
+        const int nh = task & 1, mt = (task >> 1) % MT, which = task / (2 * MT);
+        const float * arow = (which ? qn : kn) + (16 * mt) * KP, * bcol = s0 + 16 * nh;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        warp_mma_3x<2>(acc, S / 8, [&](int r, int k) { return arow[r * KP + k]; }, [&](int k, int c) { return bcol[k * CP + c]; }, g, t);
+        float * dst = (which ? o_s : ks) + (16 * mt) * CP + 16 * nh;
 #pragma unroll
-            for (int x = 0; x < 4; x++)
-#pragma unroll
-                for (int y = 0; y < 4; y++) acc[x][y] = 0.0f;
-            for (int i = part * 4; live && i < S; i += 8) {
-                float4 r4[4], s4[4];
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    r4[x] = *reinterpret_cast<const float4 *>(src + x * KP + i);
-                    s4[x] = *reinterpret_cast<const float4 *>(s0 + (i + x) * SP + ct * 4);
-                }
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    acc[x][0] = fmaf(r4[x].x, s4[0].x, acc[x][0]); acc[x][1] = fmaf(r4[x].x, s4[0].y, acc[x][1]);
-                    acc[x][2] = fmaf(r4[x].x, s4[0].z, acc[x][2]); acc[x][3] = fmaf(r4[x].x, s4[0].w, acc[x][3]);
-                    acc[x][0] = fmaf(r4[x].y, s4[1].x, acc[x][0]); acc[x][1] = fmaf(r4[x].y, s4[1].y, acc[x][1]);
-                    acc[x][2] = fmaf(r4[x].y, s4[1].z, acc[x][2]); acc[x][3] = fmaf(r4[x].y, s4[1].w, acc[x][3]);
-                    acc[x][0] = fmaf(r4[x].z, s4[2].x, acc[x][0]); acc[x][1] = fmaf(r4[x].z, s4[2].y, acc[x][1]);
-                    acc[x][2] = fmaf(r4[x].z, s4[2].z, acc[x][2]); acc[x][3] = fmaf(r4[x].z, s4[2].w, acc[x][3]);
-                    acc[x][0] = fmaf(r4[x].w, s4[3].x, acc[x][0]); acc[x][1] = fmaf(r4[x].w, s4[3].y, acc[x][1]);
-                    acc[x][2] = fmaf(r4[x].w, s4[3].z, acc[x][2]); acc[x][3] = fmaf(r4[x].w, s4[3].w, acc[x][3]);
-                }
-            }
-#pragma unroll
-            for (int x = 0; x < 4; x++)
-#pragma unroll
-                for (int y = 0; y < 4; y++) acc[x][y] += __shfl_xor_sync(0xffffffffu, acc[x][y], 1);
-            if (live && part == 0) {
-                float * dst = (which ? o_s : ks) + (rt * 4) * GDN_COLS + ct * 4;
-#pragma unroll
-                for (int x = 0; x < 4; x++) *reinterpret_cast<float4 *>(dst + x * GDN_COLS) = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
-            }
+        for (int j = 0; j < 2; j++) {
+            *reinterpret_cast<float2 *>(dst + g * CP + 8 * j + 2 * t) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2 *>(dst + (g + 8) * CP + 8 * j + 2 * t) = make_float2(acc[j][2], acc[j][3]);
         }
     }
     __syncthreads();
 
     // ---- right-hand side beta (v - gam K S_0); meanwhile two warps invert the 16 x 16 diagonal blocks of I + B ----
-    for (int i = tid; i < NPAD * GDN_COLS; i += GC_THREADS) {
+    for (int i = tid; i < NR * GDN_COLS; i += GC_THREADS) {
         const int r = i / GDN_COLS, c = i - r * GDN_COLS;
-        ks[i] = bet[r] * (vv[r * VP + c] - expf(lg[r]) * ks[i]);
+        ks[r * CP + c] = bet[r] * (vv[r * CP + c] - expf(lg[r]) * ks[r * CP + c]);
     }
-    if (warp >= GC_THREADS / 32 - 2) {
+    if (warp >= GC_WARPS - 2) {
         // half a warp per block, lane = column s of the inverse T: row r of T is e_r minus the rows before it
         // weighted by row r of B (forward substitution, as inverseLower of recurrent.go:307-331 does for the
         // whole chunk). Rows beyond the chunk have B = 0 and stay rows of the identity.
-        const int blk = (warp - (GC_THREADS / 32 - 2)) * 2 + (lane >> 4), sc = lane & 15, b0 = blk * 16;
+        const int blk = (warp - (GC_WARPS - 2)) * 2 + (lane >> 4), sc = lane & 15, b0 = blk * 16;
         if (b0 < N) {
-            float t[16];
+            float tv[16];
 #pragma unroll
             for (int r = 0; r < 16; r++) {
                 float v = r == sc ? 1.0f : 0.0f;
-                if (b0 + r < NPAD) {
-                    const float * brow = Bm + (b0 + r) * NP + b0;
+                const float * brow = Bm + (b0 + r) * NP + b0;
 #pragma unroll
-                    for (int u = 0; u < r; u++) v = fmaf(-brow[u], t[u], v);
-                }
-                t[r] = v;
-                Tm[(blk * 16 + r) * 17 + sc] = v;
+                for (int u = 0; u < r; u++) v = fmaf(-brow[u], tv[u], v);
+                tv[r] = v;
+                Tm[(b0 + r) * 20 + sc] = v;
             }
         }
     }
     __syncthreads();
-    // ---- forward substitution over the blocks: D_b = T_b (rhs_b - B[b][earlier] D[earlier]), a row per warp ----
+    // ---- forward substitution over the blocks: D_b = T_b (rhs_b - B[b][earlier] D[earlier]); a warp per 8 columns ----
     for (int b0 = 0; b0 < N; b0 += 16) {
-        const int r = b0 + warp;  // GC_THREADS / 32 == 16 rows
         if (b0 > 0) {
-            if (r < N) {
-                float acc0 = ks[r * GDN_COLS + lane], acc1 = 0.0f;
-                const float * brow = Bm + r * NP;
-#pragma unroll 8
-                for (int s2 = 0; s2 < b0; s2 += 2) {  // b0 is a multiple of 16
-                    acc0 = fmaf(-brow[s2], dd[s2 * GDN_COLS + lane], acc0);
-                    acc1 = fmaf(-brow[s2 + 1], dd[(s2 + 1) * GDN_COLS + lane], acc1);
-                }
-                ks[r * GDN_COLS + lane] = acc0 + acc1;
+            if (warp < 4) {
+                float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+                const float * arow = Bm + b0 * NP, * bcol = dd + 8 * warp;
+                warp_mma_3x<1>(acc, b0 / 8, [&](int r, int k) { return arow[r * NP + k]; }, [&](int k, int c) { return bcol[k * CP + c]; }, g, t);
+                float * dst = ks + b0 * CP + 8 * warp + 2 * t;
+                dst[g * CP] -= acc[0][0];
+                dst[g * CP + 1] -= acc[0][1];
+                dst[(g + 8) * CP] -= acc[0][2];
+                dst[(g + 8) * CP + 1] -= acc[0][3];
             }
             __syncthreads();
         }
-        if (r < NPAD) {
-            const float * trow = Tm + r * 17;
-            float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 16; u += 2) {
-                if (u <= warp) acc0 = fmaf(trow[u], ks[(b0 + u) * GDN_COLS + lane], acc0);
-                if (u + 1 <= warp) acc1 = fmaf(trow[u + 1], ks[(b0 + u + 1) * GDN_COLS + lane], acc1);
-            }
-            dd[r * GDN_COLS + lane] = acc0 + acc1;
+        if (warp < 4) {
+            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+            const float * arow = Tm + b0 * 20, * bcol = ks + b0 * CP + 8 * warp;
+            warp_mma_3x<1>(acc, 2, [&](int r, int k) { return arow[r * 20 + k]; }, [&](int k, int c) { return bcol[k * CP + c]; }, g, t);
+            float * dst = dd + b0 * CP + 8 * warp + 2 * t;
+            *reinterpret_cast<float2 *>(dst + g * CP) = make_float2(acc[0][0], acc[0][1]);
+            *reinterpret_cast<float2 *>(dst + (g + 8) * CP) = make_float2(acc[0][2], acc[0][3]);
         }
         __syncthreads();
     }
     // vv <- exp(g_C - g_s) d_s for the state update
     {
         const float lc = lg[N - 1];
-        for (int i = tid; i < NPAD * GDN_COLS; i += GC_THREADS) {
+        for (int i = tid; i < NR * GDN_COLS; i += GC_THREADS) {
             const int r = i / GDN_COLS, c = i - r * GDN_COLS;
-            vv[r * VP + c] = r < N ? expf(lc - lg[r]) * dd[i] : 0.0f;
+            vv[r * CP + c] = r < N ? expf(lc - lg[r]) * dd[r * CP + c] : 0.0f;
         }
-    }
-    // ---- outputs: gam_r (Q S_0)_r + sum_{s <= r} A[r][s] d_s; warp w takes rows w, w + 16, ... ----
-    for (int r = warp; r < N; r += GC_THREADS / 32) {
-        float acc0 = expf(lg[r]) * o_s[r * GDN_COLS + lane], acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
-        const float * arow = Am + r * NP;
-        int s2 = 0;
-#pragma unroll 4
-        for (; s2 + 3 <= r; s2 += 4) {
-            acc0 = fmaf(arow[s2], dd[s2 * GDN_COLS + lane], acc0);
-            acc1 = fmaf(arow[s2 + 1], dd[(s2 + 1) * GDN_COLS + lane], acc1);
-            acc2 = fmaf(arow[s2 + 2], dd[(s2 + 2) * GDN_COLS + lane], acc2);
-            acc3 = fmaf(arow[s2 + 3], dd[(s2 + 3) * GDN_COLS + lane], acc3);
-        }
-        for (; s2 <= r; s2++) acc0 = fmaf(arow[s2], dd[s2 * GDN_COLS + lane], acc0);
-        o_s[r * GDN_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
     }
     __syncthreads();
 
-    // ---- new state: gam_C S_0 + K^T (w d), 4 x 4 tiles, written in place ----
+    // ---- outputs gam_r (Q S_0)_r + sum_{s <= r} A[r][s] d_s (2 MT tasks) and the new state gam_C S_0 + K^T (w d),
+    // written in place (S / 8 tasks): a warp per 16 rows x 16 columns ----
     {
         const float gam_c = expf(lg[N - 1]);
-        const int total = (S / 4) * (GDN_COLS / 4) * 2;  // two lanes per tile: even and odd rows of the chunk
-        for (int wbase = warp * 32; wbase < total; wbase += GC_THREADS) {
-            const int w = wbase + lane;
-            const bool live = w < total;
-            const int part = w & 1, t2 = live ? w >> 1 : 0;
-            const int jt = t2 % (GDN_COLS / 4), it = t2 / (GDN_COLS / 4);
-            float acc[4][4];
+        for (int task = warp; task < 2 * MT + S / 8; task += GC_WARPS) {
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            if (task < 2 * MT) {
+                const int nh = task & 1, mt = task >> 1;
+                const float * arow = Am + (16 * mt) * NP, * bcol = dd + 16 * nh;
+                warp_mma_3x<2>(acc, 2 * mt + 2, [&](int r, int k) { return arow[r * NP + k]; }, [&](int k, int c) { return bcol[k * CP + c]; }, g, t);
+                float * dst = o_s + (16 * mt) * CP + 16 * nh;
+                const float g0 = expf(lg[16 * mt + g]), g1 = expf(lg[16 * mt + g + 8]);
 #pragma unroll
-            for (int x = 0; x < 4; x++)
+                for (int j = 0; j < 2; j++) {
+                    float2 * lo = reinterpret_cast<float2 *>(dst + g * CP + 8 * j + 2 * t), * hi = reinterpret_cast<float2 *>(dst + (g + 8) * CP + 8 * j + 2 * t);
+                    *lo = make_float2(fmaf(g0, lo->x, acc[j][0]), fmaf(g0, lo->y, acc[j][1]));
+                    *hi = make_float2(fmaf(g1, hi->x, acc[j][2]), fmaf(g1, hi->y, acc[j][3]));
+                }
+            } else {
+                const int e = task - 2 * MT, nh = e & 1, it = e >> 1;  // state rows 16 it .., columns 16 nh ..
+                const float * acol = kn + 16 * it, * bcol = vv + 16 * nh;
+                warp_mma_3x<2>(acc, NR / 8, [&](int r, int k) { return acol[k * KP + r]; }, [&](int k, int c) { return bcol[k * CP + c]; }, g, t);
+                const float * old = s0 + (16 * it) * CP + 16 * nh;
+                float * dst = state + (int64_t)(16 * it) * S + 16 * nh;
 #pragma unroll
-                for (int y = 0; y < 4; y++) acc[x][y] = 0.0f;
-#pragma unroll 4
-            for (int s2 = part; live && s2 < N; s2 += 2) {
-                const float4 k4 = *reinterpret_cast<const float4 *>(kn + s2 * KP + it * 4);
-                const float4 d4 = *reinterpret_cast<const float4 *>(vv + s2 * VP + jt * 4);
-                acc[0][0] = fmaf(k4.x, d4.x, acc[0][0]); acc[0][1] = fmaf(k4.x, d4.y, acc[0][1]);
-                acc[0][2] = fmaf(k4.x, d4.z, acc[0][2]); acc[0][3] = fmaf(k4.x, d4.w, acc[0][3]);
-                acc[1][0] = fmaf(k4.y, d4.x, acc[1][0]); acc[1][1] = fmaf(k4.y, d4.y, acc[1][1]);
-                acc[1][2] = fmaf(k4.y, d4.z, acc[1][2]); acc[1][3] = fmaf(k4.y, d4.w, acc[1][3]);
-                acc[2][0] = fmaf(k4.z, d4.x, acc[2][0]); acc[2][1] = fmaf(k4.z, d4.y, acc[2][1]);
-                acc[2][2] = fmaf(k4.z, d4.z, acc[2][2]); acc[2][3] = fmaf(k4.z, d4.w, acc[2][3]);
-                acc[3][0] = fmaf(k4.w, d4.x, acc[3][0]); acc[3][1] = fmaf(k4.w, d4.y, acc[3][1]);
-                acc[3][2] = fmaf(k4.w, d4.z, acc[3][2]); acc[3][3] = fmaf(k4.w, d4.w, acc[3][3]);
-            }
-#pragma unroll
-            for (int x = 0; x < 4; x++)
-#pragma unroll
-                for (int y = 0; y < 4; y++) acc[x][y] += __shfl_xor_sync(0xffffffffu, acc[x][y], 1);
-            if (live && part == 0) {
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    const float4 o4 = *reinterpret_cast<const float4 *>(s0 + (it * 4 + x) * SP + jt * 4);
-                    *reinterpret_cast<float4 *>(state + (int64_t)(it * 4 + x) * S + jt * 4) =
-                        make_float4(fmaf(gam_c, o4.x, acc[x][0]), fmaf(gam_c, o4.y, acc[x][1]), fmaf(gam_c, o4.z, acc[x][2]),
-                                    fmaf(gam_c, o4.w, acc[x][3]));
+                for (int j = 0; j < 2; j++) {
+                    const float2 o0 = *reinterpret_cast<const float2 *>(old + g * CP + 8 * j + 2 * t);
+                    const float2 o1 = *reinterpret_cast<const float2 *>(old + (g + 8) * CP + 8 * j + 2 * t);
+                    *reinterpret_cast<float2 *>(dst + (int64_t)g * S + 8 * j + 2 * t) = make_float2(fmaf(gam_c, o0.x, acc[j][0]), fmaf(gam_c, o0.y, acc[j][1]));
+                    *reinterpret_cast<float2 *>(dst + (int64_t)(g + 8) * S + 8 * j + 2 * t) = make_float2(fmaf(gam_c, o1.x, acc[j][2]), fmaf(gam_c, o1.y, acc[j][3]));
                 }
             }
         }
     }
+    __syncthreads();
 
     pdl_trigger_late();
     // ---- gated RMSNorm of the head (recurrent.go:39-50), sums of squares exchanged across the cluster ----
-    for (int node = warp; node < N; node += GC_THREADS / 32) {
-        const double v = (double)o_s[node * GDN_COLS + lane];
+    for (int node = warp; node < N; node += GC_WARPS) {
+        const double v = (double)o_s[node * CP + lane];
         double sq = v * v;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -726,8 +627,8 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
     for (int k = 0; k < ZPRE; k++) {
         const int i = tid + k * GC_THREADS;
         if (i < N * GDN_COLS) {
-            const int node = i / GDN_COLS;
-            o_s[i] = o_s[i] * (scale_s[node] * norm_w) * silu_ref(zpre[k]);
+            const int node = i / GDN_COLS, c = i - node * GDN_COLS;
+            o_s[node * CP + c] = o_s[node * CP + c] * (scale_s[node] * norm_w) * silu_ref(zpre[k]);
         }
     }
     __syncthreads();
@@ -737,7 +638,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
         const int c0 = h * S + cb * GDN_COLS + part * 16;
         float g16[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) g16[i] = o_s[node * GDN_COLS + part * 16 + i];
+        for (int i = 0; i < 16; i++) g16[i] = o_s[node * CP + part * 16 + i];
         float4 * dst = reinterpret_cast<float4 *>(a.out + r * inner + c0);
 #pragma unroll
         for (int i = 0; i < 4; i++) dst[i] = make_float4(g16[4 * i], g16[4 * i + 1], g16[4 * i + 2], g16[4 * i + 3]);
@@ -746,10 +647,8 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
 }
 
 static size_t gdn_chunk_smem(int N, int S) {
-    const int npad = (N + 3) & ~3;
-    return sizeof(float) * ((size_t)2 * npad * (S + 4) + (size_t)S * (GDN_COLS + 4) + (size_t)npad * (GDN_COLS + 16) + (size_t)3 * npad * GDN_COLS +
-                            (size_t)2 * npad * (npad + 1) + 2 * npad + (size_t)((N + 15) / 16) * 16 * 17 + 4 +
-                            (size_t)(npad / 4) * (npad / 4 + 1) / 2 * 32);
+    const size_t nr = (size_t)((N + 15) & ~15);
+    return sizeof(float) * (2 * nr * (S + 4) + (size_t)S * GC_CP + 4 * nr * GC_CP + 2 * nr * (nr + 4) + nr * 20 + 2 * nr);
 }
 
 // The front end alone for one chain of any length (a whole prompt pass of one sequence): conv taps come from the

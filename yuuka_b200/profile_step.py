@@ -6,8 +6,9 @@ Builds the synthetic Q4_K_M model (dense 4B shape, or the qwen35moe shape with
 --moe), feeds a short prompt to each of --batch sequences and runs a few verify
 steps of --rows rows per sequence with dummy drafts. Set YUUKA_CUDA_NO_GRAPH=1 to launch the kernels
 directly instead of replaying a captured graph (profilers then list them one
-by one). With --profiler-range the steps (not the model set-up or the prompt)
-run between cuProfilerStart and cuProfilerStop, for `ncu --profile-from-start off`.
+by one). With --profiler-range the steps (not the model set-up or the prompt), or with
+--profiler-range prompt the prompt passes, run between cuProfilerStart and cuProfilerStop, for
+`ncu --profile-from-start off`.
 Prints the per-step time measured with CUDA events.
 """
 from __future__ import annotations
@@ -31,7 +32,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="sequences per step")
     ap.add_argument("--per-op", action="store_true", help="one more step with an event pair around every operation")
     ap.add_argument("--moe", action="store_true", help="qwen35moe shape (256 experts, 8 used) instead of the dense 4B shape")
-    ap.add_argument("--profiler-range", action="store_true", help="cuProfilerStart / Stop around the verify steps")
+    ap.add_argument("--profiler-range", nargs="?", const="steps", default=None, choices=["steps", "prompt"],
+                    help="cuProfilerStart / Stop around the verify steps (default) or around the prompt passes")
     args = ap.parse_args()
     if args.moe:
         cfg = synth.moe_config(layers=args.layers, vocab=args.vocab, context=4096)
@@ -45,13 +47,17 @@ def main():
     B = args.batch
     sess = cuda.Session(model, max_batch=B, max_nodes=args.rows, capacity=cap, kv_format=cuda.KV_F16)
     pending = []
+    driver = ctypes.CDLL("libcuda.so.1") if args.profiler_range else None
+    if args.profiler_range == "prompt":
+        driver.cuProfilerStart()
     for b in range(B):
         prompt = synth.uniform_i32(args.prompt, 0, cfg["vocab"], 3 + b)
         pending.append(int(np.argmax(sess.forward(prompt, seq=b))))
+    if args.profiler_range == "prompt":
+        driver.cuProfilerStop()
     e0, e1 = dev.event(), dev.event()
     times = []
-    driver = ctypes.CDLL("libcuda.so.1") if args.profiler_range else None
-    if driver:
+    if args.profiler_range == "steps":
         driver.cuProfilerStart()
     for _ in range(args.steps):
         sess.stage([[pending[b]] + [1 + b] * (args.rows - 1) for b in range(B)])
@@ -60,7 +66,7 @@ def main():
         res = sess.fetch()
         times.append(e0.elapsed_ms(e1))
         pending = [int(res.emitted[b, int(res.accepted[b])]) for b in range(B)]
-    if driver:
+    if args.profiler_range == "steps":
         driver.cuProfilerStop()
     per_op = {}
     if args.per_op:
