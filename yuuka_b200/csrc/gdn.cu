@@ -472,25 +472,27 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gdn_chunk_kernel(const ScanPara
     }
     __syncthreads();
 
-    // ---- B and A: K K^T and Q K^T on the lower triangle (16 x 8 tiles whose columns start below the tile's last
-    // row), decay ratios and beta folded in on the way out; entries above the diagonal inside those tiles are zero ----
+    // ---- B and A: K K^T and Q K^T on the lower triangle (16 x 16 tiles up to the diagonal one), decay ratios and
+    // beta folded in on the way out; entries above the diagonal inside the diagonal tiles are zero ----
     {
-        const int per_mat = MT * (MT + 1);  // sum over row tiles mt of 2 mt + 2 column tiles
+        const int per_mat = MT * (MT + 1) / 2;
         for (int tile = warp; tile < 2 * per_mat; tile += GC_WARPS) {
             const int mat = tile >= per_mat, rest = tile - mat * per_mat;
             int mt = 0;
-            while ((mt + 1) * (mt + 2) <= rest) mt++;
-            const int nt = rest - mt * (mt + 1);
-            const float * arow = (mat ? qn : kn) + (16 * mt) * KP, * brow = kn + (8 * nt) * KP;
-            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-            warp_mma_3x<1>(acc, S / 8, [&](int r, int k) { return arow[r * KP + k]; }, [&](int k, int c) { return brow[c * KP + k]; }, g, t);
+            while ((mt + 1) * (mt + 2) / 2 <= rest) mt++;
+            const int nt = rest - mt * (mt + 1) / 2;
+            const float * arow = (mat ? qn : kn) + (16 * mt) * KP, * brow = kn + (16 * nt) * KP;
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            warp_mma_3x<2>(acc, S / 8, [&](int r, int k) { return arow[r * KP + k]; }, [&](int k, int c) { return brow[c * KP + k]; }, g, t);
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int r = 16 * mt + g + (e >> 1) * 8, c = 8 * nt + 2 * t + (e & 1);
-                const float wgt = c <= r ? expf(lg[r] - lg[c]) : 0.0f;
-                if (mat) Am[r * NP + c] = wgt * acc[0][e];
-                else Bm[r * NP + c] = c < r ? bet[r] * wgt * acc[0][e] : 0.0f;
-            }
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int r = 16 * mt + g + (e >> 1) * 8, c = 16 * nt + 8 * j + 2 * t + (e & 1);
+                    const float wgt = c <= r ? expf(lg[r] - lg[c]) : 0.0f;
+                    if (mat) Am[r * NP + c] = wgt * acc[j][e];
+                    else Bm[r * NP + c] = c < r ? bet[r] * wgt * acc[j][e] : 0.0f;
+                }
         }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
