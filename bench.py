@@ -422,7 +422,7 @@ def run_c1(args, rank: int, local_rank: int, world: int) -> None:
     for n_out, n_in, d in shapes:
         for m in (1, 2, 4, 9, 16, 64, 576):
             r = microbench.bench_gemm(dev, n_out, n_in, d, m, cuda.PATH_AUTO, iters=max(args.steps, 10), warmup=max(args.warmup, 3))
-            route = "fp32 CUDA cores" if m <= 2 else ("register-fed mma.sync, exact" if m < 48 else "tcgen05 + tensor memory")
+            route = "register-fed mma.sync, exact" if m < 48 else "tcgen05 + tensor memory"
             table.append({"n_out": n_out, "n_in": n_in, "dtype": d, "rows": m, "route": route, "us": round(r["ms"] * 1e3, 2),
                           "weight_gbs": round(r["weight_gbs"], 1), "hbm_frac": round(r["weight_gbs"] / peaks["hbm_gbs"], 4),
                           "tflops": round(r["tflops"], 2), "tensor_frac": round(r["tflops"] / peaks["bf16_tflops"], 4)})

@@ -119,10 +119,12 @@ YUUKA_API yuuka_status yuuka_buffer_copy(yuuka_stream * stream, yuuka_buffer * d
  * reference: yuuka_hip.h:209-300,340-440). All are asynchronous on stream.
  * ---------------------------------------------------------------------- */
 
-/* GEMM route. AUTO picks by row count; the others force one kernel family. */
+/* GEMM route. AUTO: tile-ordered weights go to the tensor-core kernels whatever the row count (the register-fed
+ * exact route up to 47 rows per launch, the tensor-memory route from 48), GGUF-ordered weights to the fp32
+ * kernel; the others force one kernel family. */
 #define YUUKA_GEMM_PATH_AUTO 0u
-#define YUUKA_GEMM_PATH_FP32 1u /* CUDA-core dot products, fp32 weights and activations */
-#define YUUKA_GEMM_PATH_MMA 2u  /* fp16-operand tensor-core MMA, fp32 accumulate */
+#define YUUKA_GEMM_PATH_FP32 1u /* CUDA-core dot products, the reference's fp32 decode arithmetic */
+#define YUUKA_GEMM_PATH_MMA 2u  /* tensor-core MMA on fp16 operands, fp32 accumulate */
 
 /* out[rows, n_out] (f32) = x[rows, n_in] * W[n_out, n_in]^T, W in the packed
  * GGUF row layout of w_dtype (replaces yuuka_gemv_batch, yuuka_hip.h:291-300,

@@ -689,7 +689,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
     s->launches += launch_gemm_quant(s->model->dev, s->stream.s, a);
 }
 
-// x += W * in, then xn = rmsnorm(x) * norm_w (skipped when norm_w is null). With 3..32 rows the norm is
+// x += W * in, then xn = rmsnorm(x) * norm_w (skipped when norm_w is null). With up to 32 rows the norm is
 // folded into this GEMM's epilogue and the next GEMM's; otherwise it runs as its own kernel.
 void gemm_residual_norm(yuuka_session * s, const Tensor & w, const float * in, int ld_in, XPrepOut prep_in, int rows,
                         const float * norm_w) {
@@ -758,9 +758,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     const int q_dim = m->q_dim(), kv_dim = m->kv_dim(), o_dim = m->o_dim(), F = c.ffn;
 
     s->order_pos = 0;
-    // with 3..32 rows every norm after the first is folded into the GEMM that finishes the residual rows
+    // with up to 32 rows every norm after the first is folded into the GEMM that finishes the residual rows
     // and the GEMM that reads them
-    s->fold_step = s->fold_norm && R >= 3 && R <= 32;
+    s->fold_step = s->fold_norm && R <= 32;
     s->norm_point = 0;
     s->xn_raw = false;
     if (s->fold_step) YK_CUDA(cudaMemsetAsync(s->norm_sumsq, 0, sizeof(unsigned long long) * 32 * (size_t)(2 * c.block_count + 2), st));
@@ -1002,7 +1002,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             continue;
         }
         // forwardFFN (model/qwen35/forward.go:295-315); its input norm came with the mixer's output GEMM
-        if (L.gate_up.present() && L.gate_up.paired && L.gate_up.tiled && L.ffn_down.tiled && s->fold_swiglu && R >= 3 && R <= 32) {
+        if (L.gate_up.present() && L.gate_up.paired && L.gate_up.tiled && L.ffn_down.tiled && s->fold_swiglu && R <= 32) {
             // silu(gate) * up leaves the GEMM's epilogue in the form the down projection reads
             gemm(s, L.gate_up, s->xn, H, s->prep_xn, s->gate_up, 2 * F, R, 0, nullptr, &s->prep_act);
         } else {

@@ -17,7 +17,7 @@
 // (long rows) goes through a scratch buffer and is finished by the last CTA to
 // arrive, also in a fixed order. Nothing here waits on another CTA.
 //
-// fp32 route (1-2 rows, tight-tolerance checks): same loads, the reference's
+// fp32 route (on request, for tight-tolerance checks): same loads, the reference's
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
 #include <cuda.h>
 
@@ -1868,10 +1868,10 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
         YK_REQUIRE(!a.norm.consume_now || a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
     }
     if (a.norm.produce_w || a.norm.consume_now || a.swiglu.xh) {
-        const uint32_t route = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
+        const uint32_t route = a.path == YUUKA_GEMM_PATH_AUTO ? YUUKA_GEMM_PATH_MMA : a.path;
         YK_REQUIRE(route == YUUKA_GEMM_PATH_MMA && a.rows <= 32 && (a.rows < UMMA_MIN_ROWS || !umma_enabled()) &&
                        (!a.swiglu.xh || a.swiglu.xl) && (!a.norm.produce_w || a.norm.produce_prep.xl),
-                   YUUKA_ERR_INTERNAL, "gemm: folded epilogues (RMSNorm, SwiGLU) run on the register-fed mma route only (3..32 rows)");
+                   YUUKA_ERR_INTERNAL, "gemm: folded epilogues (RMSNorm, SwiGLU) run on the register-fed mma route only (1..32 rows)");
         YK_REQUIRE(!a.norm.produce_w || (a.n_out % 16 == 0 && a.norm.produce_sumsq && a.norm.produce_prep.xh && a.norm.produce_prep.xs16),
                    YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs a width that is a multiple of 16 and its outputs");
         YK_REQUIRE(a.swiglu.xh || a.norm.cols > 0, YUUKA_ERR_INVALID_ARGUMENT, "gemm: the folded RMSNorm needs the row width");
@@ -1881,7 +1881,7 @@ int launch_gemm_tiled(const yuuka_device * dev, cudaStream_t stream, const Tiled
     YK_REQUIRE(a.x_dtype == YUUKA_DTYPE_F32 || a.x_dtype == YUUKA_DTYPE_BF16, YUUKA_ERR_UNSUPPORTED,
                "gemm: activation dtype %u is not F32 or BF16", a.x_dtype);
     YK_REQUIRE((!a.x || a.ldx >= a.n_in) && a.ldo >= a.n_out, YUUKA_ERR_INVALID_ARGUMENT, "gemm: leading dimension too small");
-    uint32_t path = a.path == YUUKA_GEMM_PATH_AUTO ? (a.rows <= 2 ? YUUKA_GEMM_PATH_FP32 : YUUKA_GEMM_PATH_MMA) : a.path;
+    uint32_t path = a.path == YUUKA_GEMM_PATH_AUTO ? YUUKA_GEMM_PATH_MMA : a.path;
     YK_REQUIRE(path == YUUKA_GEMM_PATH_FP32 || path == YUUKA_GEMM_PATH_MMA, YUUKA_ERR_INVALID_ARGUMENT,
                "gemm: unknown path %u", path);
     set_device(dev);

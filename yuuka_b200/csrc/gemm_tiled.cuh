@@ -59,7 +59,7 @@ struct GroupedGemmArgs {
 };
 int launch_gemm_tiled_grouped(const yuuka_device * dev, cudaStream_t stream, const GroupedGemmArgs & a);
 
-// RMSNorm folded into the GEMMs around it (register-fed mma route, 3..32 rows). A GEMM that finishes
+// RMSNorm folded into the GEMMs around it (register-fed mma route, up to 32 rows). A GEMM that finishes
 // residual rows x (producer) also writes the prepared input of the next GEMM, fp16(x * w * pre) with its
 // 16-column sums, and adds every row's sum of squares (fixed point, 2^-24 units, integer atomics: the
 // result does not depend on the order of the CTAs) to produce_sumsq, which the caller zeroed. The GEMM
@@ -93,7 +93,7 @@ struct TiledGemmArgs {
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     NormFuse norm;
     // Set: `w` holds ffn_gate and ffn_up interleaved by 16-row tile and the launch writes silu(gate) * up in
-    // prepared form, [rows][n_out / 2], instead of `out` (register-fed mma route, 3..32 rows).
+    // prepared form, [rows][n_out / 2], instead of `out` (register-fed mma route, up to 32 rows).
     XPrepOut swiglu;
     const uint8_t * next_w = nullptr;  // optional L2 prefetch hint: the next matrix to be streamed (mma route)
     uint64_t next_bytes = 0;
