@@ -290,6 +290,10 @@ typedef struct yuuka_session_config {
  * multiplies exact integer weights with two-half activations (fp32-level results, weights streamed once
  * per 16 rows). */
 #define YUUKA_SESSION_EXACT_WIDE 0x1u
+/* The other way round: steps of 33..47 rows, which by default run as three exact 16-row passes, also take the
+ * tensor-memory route (one pass over the weights: a 36-row step of the 4B model 8.1 -> 4.7 ms) at that route's
+ * fp16-rounded precision. For hosts that batch a handful of sequences per step and prefer the speed. */
+#define YUUKA_SESSION_WIDE_FROM_33 0x2u
 /* Test hook: every GEMM of the session's steps carries YUUKA_GEMM_TEST_DROP_COPIES. */
 #define YUUKA_SESSION_TEST_DROP_COPIES 0x80000000u
 /* Replaces the session's flags between steps (no step may be staged or in flight; captured steps are dropped,

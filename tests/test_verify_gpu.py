@@ -50,6 +50,11 @@ def greedy(om, prompt, n, kv=yo.KV_F32):
     return out
 
 
+def top2_gaps(logits):
+    part = np.partition(logits, -2, axis=-1)
+    return (part[..., -1] - part[..., -2]).ravel().tolist()
+
+
 @pytest.mark.parametrize("kv", [cuda.KV_F32, cuda.KV_F16, cuda.KV_Q8_0])
 def test_prefill_logits_match_oracle(tiny, kv):
     cfg, gm, om = tiny
@@ -72,7 +77,7 @@ def test_prefill_logits_match_oracle(tiny, kv):
     sess.close(); st.close()
 
 
-def test_single_row_steps_use_fp32_route_and_match_tightly(tiny):
+def test_single_row_steps_match_tightly(tiny):
     cfg, gm, om = tiny
     prompt = synth.uniform_i32(12, 0, cfg["vocab"], 22)
     st = yo.State(om, 64, yo.KV_F32)
@@ -80,7 +85,7 @@ def test_single_row_steps_use_fp32_route_and_match_tightly(tiny):
     for t in prompt:
         want = st.step(int(t))
         got = sess.forward([int(t)])
-    # one row per step: fp32 CUDA-core GEMMs, same decode arithmetic as the CPU
+    # one row per step: the exact register-fed route (integer weights, two-half activations, fp32 accumulation)
     assert float(np.max(np.abs(got - want))) <= 2e-4
     sess.close(); st.close()
 
@@ -185,6 +190,40 @@ def test_batched_sequences_with_permuted_block_tables(tiny):
         assert sess.position(b) == states[b].pos
         states[b].close()
     sess.close()
+
+
+def test_steps_of_33_to_47_rows_on_the_wide_route_on_request(tiny):
+    """Four sequences x nine rows: three exact 16-row passes by default, one pass of the tensor-memory route with
+    YUUKA_SESSION_WIDE_FROM_33. Both stay inside the path's logit bound; the flag changes the kernels that run."""
+    cfg, gm, om = tiny
+    V, B = cfg["vocab"], 4
+    states, pend, drafts, prompts = [], [], [], []
+    for b in range(B):
+        prompt = synth.uniform_i32(18 + 5 * b, 0, V, 60 + b).tolist()
+        st = yo.State(om, 96, yo.KV_F32)
+        p = yo.argmax(st.forward(prompt))
+        g = greedy(om, prompt + [p], 8, yo.KV_F32)
+        states.append(st); pend.append(p); prompts.append(prompt)
+        drafts.append(synth.corrupt_draft(np.array(g, np.int32), V, 0.3, 70 + b))
+    toks = np.array([[pend[b]] + drafts[b].tolist() for b in range(B)], np.int32)
+    want = [states[b].verify_chain(pend[b], drafts[b], want_logits=True) for b in range(B)]
+    counts = {}
+    for flags in (0, cuda.SESSION_WIDE_FROM_33):
+        sess = cuda.Session(gm, max_batch=B, max_nodes=9, capacity=96, kv_format=cuda.KV_F32, flags=flags)
+        for b in range(B):
+            sess.forward(prompts[b], seq=b, want_logits=False)
+        res = sess.verify(toks, want_logits=True)
+        counts[flags] = sess.last_launch_count
+        for b in range(B):
+            acc_o, em_o, log_o = want[b]
+            err = float(np.max(np.abs(res.logits[b] - log_o)))
+            assert err <= (5e-4 if flags == 0 else LOGIT_TOL), (flags, err)
+            if all(g >= max(1e-3, 3 * err) for g in top2_gaps(log_o)):
+                assert int(res.accepted[b]) == acc_o and res.emitted[b, :acc_o + 1].tolist() == em_o.tolist()
+        sess.close()
+    assert counts[0] != counts[cuda.SESSION_WIDE_FROM_33]
+    for st in states:
+        st.close()
 
 
 def test_snapshot_restore_round_trip_and_legacy_rollback(tiny):

@@ -637,6 +637,7 @@ void gemm(yuuka_session * s, const Tensor & w, const float * x, int ldx, XPrepOu
         t.flags = flags;
         t.scratch = &s->gemm;
         t.exact_only = (s->cfg.flags & YUUKA_SESSION_EXACT_WIDE) != 0;
+        t.wide_from_33 = (s->cfg.flags & YUUKA_SESSION_WIDE_FROM_33) != 0;
         if (s->cfg.flags & YUUKA_SESSION_TEST_DROP_COPIES) t.flags |= YUUKA_GEMM_TEST_DROP_COPIES;
         if (swiglu) t.swiglu = *swiglu;
         if (s->fold_step) {
@@ -1275,7 +1276,7 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
         if (sc.pool_blocks <= 0) sc.pool_blocks = per_seq * sc.max_batch;
         YK_REQUIRE(sc.kv_format == YUUKA_KV_F32 || sc.kv_format == YUUKA_KV_F16 || sc.kv_format == YUUKA_KV_Q8_0,
                    YUUKA_ERR_INVALID_ARGUMENT, "unknown KV format %d", sc.kv_format);
-        YK_REQUIRE((sc.flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
+        YK_REQUIRE((sc.flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_WIDE_FROM_33 | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
                    "unknown session flags 0x%x", sc.flags);
         set_device(model->dev);
         auto * s = new yuuka_session();
@@ -1496,7 +1497,7 @@ yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t seq, const
 yuuka_status yuuka_session_set_flags(yuuka_session * s, uint32_t flags) {
     return guard([&] {
         YK_REQUIRE(s, YUUKA_ERR_INVALID_ARGUMENT, "null session");
-        YK_REQUIRE((flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
+        YK_REQUIRE((flags & ~(YUUKA_SESSION_EXACT_WIDE | YUUKA_SESSION_WIDE_FROM_33 | YUUKA_SESSION_TEST_DROP_COPIES)) == 0, YUUKA_ERR_INVALID_ARGUMENT,
                    "unknown session flags 0x%x", flags);
         YK_REQUIRE(!s->staged && !s->launched, YUUKA_ERR_INVALID_ARGUMENT, "set_flags: a step is staged or in flight");
         set_device(s->model->dev);

@@ -1468,6 +1468,7 @@ static void plan_tiled(const yuuka_device * dev, uint32_t dtype, int m, int n_ou
 
 // Rows from which the tensor-memory route takes over from 16-row passes of the register-fed kernel.
 constexpr int UMMA_MIN_ROWS = 48;
+constexpr int UMMA_EARLY_ROWS = 33;  // on request: where three passes of the register-fed route would begin
 
 static bool umma_enabled() {
     static const bool on = [] {
@@ -1522,11 +1523,11 @@ void gemm_tiled_scratch_need(const yuuka_device * dev, uint32_t w_dtype, int row
     *partial_floats = 0;
     *counters = 0;
     if (!tiled_supported(w_dtype, n_in)) return;
-    if (rows >= UMMA_MIN_ROWS) {
+    if (rows >= UMMA_EARLY_ROWS) {
         const int per_launch = rows < umma_rows_per_launch() ? rows : umma_rows_per_launch();
         // enough for this row count and for every smaller one (fewer rows may split K further)
         int ks = 1, worst = 0;
-        for (int m = UMMA_MIN_ROWS; m <= per_launch; m += 16) {
+        for (int m = UMMA_EARLY_ROWS; m <= per_launch; m += (m < UMMA_MIN_ROWS ? UMMA_MIN_ROWS - m : 16)) {
             bool sep;
             const int k = umma_ksplit(dev, n_out, n_in, m, &sep);
             if (k > ks) ks = k;
@@ -1799,7 +1800,8 @@ static int launch_mma_dt(const yuuka_device * dev, cudaStream_t s, const TiledGe
         xp.xs16 = a.scratch->xs16;
         launches++;
     }
-    if (a.rows >= UMMA_MIN_ROWS && umma_enabled() && !a.exact_only) return launches + launch_umma_dt<DT>(dev, s, a, xp.xh);
+    if (a.rows >= (a.wide_from_33 ? UMMA_EARLY_ROWS : UMMA_MIN_ROWS) && umma_enabled() && !a.exact_only)
+        return launches + launch_umma_dt<DT>(dev, s, a, xp.xh);
     YK_REQUIRE(xp.xl && xp.xs16, YUUKA_ERR_INTERNAL, "gemm: the prepared activations lack their lo halves or sums");
     for (int m0 = 0; m0 < a.rows; m0 += MMA_ROWS) {
         const int m = a.rows - m0 < MMA_ROWS ? a.rows - m0 : MMA_ROWS;

@@ -90,6 +90,7 @@ struct TiledGemmArgs {
     uint32_t path = YUUKA_GEMM_PATH_AUTO;
     uint32_t flags = 0;
     bool exact_only = false;          // wide passes too stay on the register-fed route (16 rows per launch)
+    bool wide_from_33 = false;        // 33..47 rows take the tensor-memory route as well
     GemmScratch * scratch = nullptr;  // needed when the plan splits K across CTAs
     NormFuse norm;
     // Set: `w` holds ffn_gate and ffn_up interleaved by 16-row tile and the launch writes silu(gate) * up in

@@ -21,6 +21,7 @@ GEMM_ACCUMULATE = 1
 GEMM_TILED = 2
 ACCEPT_GREEDY, ACCEPT_REJECTION, ACCEPT_NONE = 0, 1, 2
 SESSION_EXACT_WIDE = 1
+SESSION_WIDE_FROM_33 = 2
 SESSION_TEST_DROP_COPIES = 0x80000000
 GEMM_TEST_DROP_COPIES = 0x80000000
 OP_NAMES = {16: "gemm", 18: "rmsnorm", 20: "attn_prep", 24: "embedding", 29: "attention", 37: "lm_head", 9: "silu_mul",
