@@ -578,6 +578,7 @@ struct yuuka_session {
     GemmScratch gemm;
     // staged step
     int st_seq0 = 0, st_batch = 0, st_nodes = 0;
+    int st_chains = 0;         // every sequence of the staged step is a chain (no row has a sibling)
     std::vector<int> st_seqs;  // sequences of the staged step, slot by slot
     // device-drafted generation (yuuka_spec_generate_device): token history of the generating sequence,
     // its length, and [steps, draft tokens, accepted drafts, draft length of the staged step]
@@ -594,7 +595,7 @@ struct yuuka_session {
     uint32_t launches = 0;
     // captured steps, keyed by (seq0, batch, nodes, mode)
     struct StepGraph {
-        int seq0, batch, nodes;
+        int seq0, batch, nodes, chains;
         uint32_t mode;
         cudaGraphExec_t exec;
         uint32_t launches;
@@ -738,6 +739,7 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     cudaStream_t st = s->stream.s;
     const int R = batch * nodes, H = c.hidden;
     RowMeta rows{s->d_tokens, s->d_parent, s->d_depth, s->d_anc, s->d_pos0 + seq0, batch, nodes};
+    rows.chains = sub > 0 ? 1 : s->st_chains;
     if (mapped) rows.seq_map = s->d_seq_map;
     YK_REQUIRE(!mapped || (seq0 == 0 && sub == 0), YUUKA_ERR_INTERNAL, "a mapped step starts at sequence 0 and has no sub-chunks");
     YK_REQUIRE(sub == 0 || (batch == 1 && mode == 3u && nodes <= CHAIN_MAX_SUBS * sub), YUUKA_ERR_INTERNAL,
@@ -746,7 +748,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
     // sub-chunk k as a step of its own: rows [k * sub, ...), positions from d_pos_sub[k]
     auto sub_rows = [&](int k) {
         const int r0 = k * sub, n = nodes - r0 < sub ? nodes - r0 : sub;
-        return RowMeta{s->d_tokens + r0, s->d_parent + r0, s->d_depth + r0, s->d_anc + r0, s->d_pos_sub + k, 1, n};
+        RowMeta rk{s->d_tokens + r0, s->d_parent + r0, s->d_depth + r0, s->d_anc + r0, s->d_pos_sub + k, 1, n};
+        rk.chains = 1;
+        return rk;
     };
     int gdn_index = 0;  // position of the current recurrent layer in d_gdn_commit
     if (sub > 0) {
@@ -1108,6 +1112,7 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
     int32_t * tok = reinterpret_cast<int32_t *>(s->h_rows + (size_t)cap * 8);
     int32_t * par = tok + cap;
     int32_t * dep = par + cap;
+    s->st_chains = 1;
     for (int b = 0; b < batch; b++) {
         for (int i = 0; i < nodes; i++) {
             const int r = b * nodes + i;
@@ -1124,6 +1129,7 @@ void stage_rows(yuuka_session * s, int seq0, int batch, int nodes, const int32_t
             int p = parent ? parent[r] : i - 1;
             YK_REQUIRE((i == 0 && p == -1) || (i > 0 && p >= 0 && p < i), YUUKA_ERR_INVALID_ARGUMENT,
                        "parent[%d][%d] = %d is not a preceding row", b, i, p);
+            if (p != i - 1) s->st_chains = 0;
             par[r] = p;
             dep[r] = i == 0 ? 0 : dep[b * nodes + p] + 1;
             anc[r] = (i == 0 ? 0ull : anc[b * nodes + p]) | (1ull << i);
@@ -1229,7 +1235,8 @@ void enqueue_staged_step(yuuka_session * s) {
     }
     yuuka_session::StepGraph * gr = nullptr;
     for (auto & g : s->graphs)
-        if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.mode == s->st_mode) gr = &g;
+        if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.chains == s->st_chains && g.mode == s->st_mode)
+            gr = &g;
     if (!gr) {
         // first step of this shape: capture the kernel sequence once, replay it afterwards
         s->launches = 0;
@@ -1247,7 +1254,7 @@ void enqueue_staged_step(yuuka_session * s) {
         cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
         cudaGraphDestroy(graph);
         YK_CUDA(err);
-        s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_mode, exec, s->launches});
+        s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_chains, s->st_mode, exec, s->launches});
         gr = &s->graphs.back();
     }
     s->launches = gr->launches;

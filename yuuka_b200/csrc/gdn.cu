@@ -120,7 +120,34 @@ __global__ void gdn_front_kernel(const ScanParams p) {
 // Redoing the front end inside this kernel (every CTA its head's q and k group and its own v
 // columns) to save the launch in between measured 9 us slower per layer: the front end is only
 // cheap when spread over its 576 CTAs.
-template <int S>
+// Depth-first (pre-order) numbering of the rows of a tree whose parents precede their children; children in
+// row order. One thread, at most GDN_MAX_NODES rows.
+__device__ __noinline__ void depth_first_order(const int * par, int N, int * order) {
+    unsigned long long seen = 0ull;
+    int cnt = 0, at = -1;
+    while (cnt < N) {
+        int next = -1;
+        for (int c = at + 1; c < N; c++)
+            if (!((seen >> c) & 1ull) && par[c] == at) {
+                next = c;
+                break;
+            }
+        if (next >= 0) {
+            order[cnt++] = next;
+            seen |= 1ull << next;
+            at = next;
+        } else if (at >= 0) {
+            at = par[at];
+        } else {
+            // (unreachable for a valid parent array: rows without a path to the root go last, in row order)
+            for (int c = 0; c < N; c++)
+                if (!((seen >> c) & 1ull)) order[cnt++] = c;
+        }
+    }
+}
+
+// TREE: the rows of a sequence may branch (the host staged parent pointers); they are then walked depth first.
+template <int S, bool TREE>
 __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanParams p) {
     pdl_entry();
     constexpr int RPL = S / 4;  // state rows per lane
@@ -144,6 +171,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     int * par = reinterpret_cast<int *>(bet + N);  // [N]
     __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
+    __shared__ int order_s[TREE ? GDN_MAX_NODES : 1];
 
     // stored state: the longest fetch (HBM), issued first
     const float * s0 = a.state + ((int64_t)(seq_of(p.rows, seq) * a.rank + h) * S + rq * RPL) * S + col;
@@ -186,9 +214,19 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         zpre[k] = i < N * GDN_COLS ? a.z[(int64_t)(seq * N + node) * a.ldz + h * S + cb * GDN_COLS + c] : 0.0f;
     }
 
+    // The rows are walked in depth-first order: a row then follows its parent directly unless it is a later
+    // sibling, so a branch is replayed from the stored state only when the walk backtracks. In row order
+    // (breadth first, as draft trees are numbered) almost every row of a tree switched branches: the 16-node
+    // tree of the batched configuration cost 24 replayed updates on top of its 16, depth first it costs 2.
+    if constexpr (TREE) {
+        if (threadIdx.x == 0) depth_first_order(par, N, order_s);
+        __syncthreads();
+    }
+
     // ---- recurrence (recurrent.go:56-105) ----
     int cur = -1;  // node whose state st currently holds (-1: the stored state)
-    for (int node = 0; node < N; node++) {
+    for (int step = 0; step < N; step++) {
+        const int node = TREE ? order_s[step] : step;
         const int pnode = par[node];
         if (pnode != cur) {
             // a sibling branch: rebuild the parent's state from the stored one by replaying the log of its path
@@ -302,12 +340,16 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
     const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N);
+    auto launch = [&](auto kern) {
+        YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        launch_k_cluster(kern, grid, GDN_WARPS * 32, smem, s, grid.x, p);
+    };
     if (a.S == 128) {
-        YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_k_cluster(gdn_scan_kernel<128>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
+        if (rows.chains) launch(gdn_scan_kernel<128, false>);
+        else launch(gdn_scan_kernel<128, true>);
     } else {
-        YK_CUDA(cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_k_cluster(gdn_scan_kernel<64>, grid, GDN_WARPS * 32, smem, s, grid.x, p);
+        if (rows.chains) launch(gdn_scan_kernel<64, false>);
+        else launch(gdn_scan_kernel<64, true>);
     }
     YK_CUDA(cudaGetLastError());
     return 2;

@@ -18,6 +18,9 @@ struct RowMeta {
     // recurrent state and conv history are indexed by it; everything that only lives for the step (rows,
     // logits, results) is indexed by the slot. Null: slot b is sequence b of the arrays as passed.
     const int32_t * seq_map = nullptr;
+    // set by the host when it staged no parent pointers: every sequence of the step is a chain (row i follows
+    // row i - 1), which lets the delta-net scan walk the rows in order without looking for branches
+    int chains = 0;
 };
 #ifdef __CUDACC__
 __device__ __forceinline__ int seq_of(const RowMeta & rows, int slot) { return rows.seq_map ? rows.seq_map[slot] : slot; }
