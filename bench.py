@@ -216,6 +216,14 @@ def run_reference_arm(args, rank: int) -> None:
 
 # --------------------------------------------------------------------------- helpers of the GPU arms
 
+def profiler_range(args, start: bool) -> None:
+    """cuProfilerStart / cuProfilerStop when --profiler-range was given: a profiler then sees the timed steps only."""
+    if getattr(args, "profiler_range", False):
+        import ctypes
+        drv = ctypes.CDLL("libcuda.so.1")
+        (drv.cuProfilerStart if start else drv.cuProfilerStop)()
+
+
 def init_dist(world: int, local_rank: int):
     if world <= 1:
         return None
@@ -312,6 +320,7 @@ def run_c2(args, rank: int, local_rank: int, world: int) -> None:
             barrier()
             emitted_total = accepted_total = 0
             dev_ms = 0.0
+            profiler_range(args, True)
             t_e2e = time.perf_counter()
         toks = np.concatenate(([pending], drafts[idx:idx + K_DRAFT])).astype(np.int32)
         sess.stage(toks)                       # host -> device: tokens and row metadata
@@ -551,6 +560,7 @@ def run_c3(args, rank: int, local_rank: int, world: int) -> None:
         if step == args.warmup:
             sync()
             dev_ms, emitted_total, accepted_total = 0.0, 0, 0
+            profiler_range(args, True)
             t_e2e = time.perf_counter()
         tokens[:, 0] = pend
         uniforms = synth.uniform_f32(B * N * 2, 900 + step).reshape(B, N, 2)
@@ -565,6 +575,7 @@ def run_c3(args, rank: int, local_rank: int, world: int) -> None:
         launches = sess.last_launch_count
     sync()
     t_e2e = time.perf_counter() - t_e2e
+    profiler_range(args, False)
     clocks = sampler.stop()
     ctx_now = [sess.position(b) for b in range(B)]
     tot = replicas.reduce_totals(dist, "cuda", dev_ms, t_e2e, float(emitted_total), float(accepted_total))
@@ -707,6 +718,8 @@ def main() -> None:
     ap.add_argument("--seqs", type=int, default=0, help="c3: sequences in all (default 256); c4: sequences per GPU (default 32)")
     ap.add_argument("--prompt", type=int, default=0, help="c4: prompt length (default 1024)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="cuProfilerStart / Stop around the timed steps (for ncu --profile-from-start off; numbers from such a run are not bench values)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

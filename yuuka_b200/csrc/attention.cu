@@ -204,8 +204,16 @@ constexpr int AM_KT = 32;
 // fits), four when a sequence has more than 48 query rows per KV head (64 cover a 16-row tree in one pass over the keys).
 constexpr int AM_RB_SMALL = 3, AM_RB_LARGE = 4;
 
+// Row blocks per CTA for q_rows query rows of one KV head: whichever of the two sizes walks the keys with fewer
+// row blocks in all (tiles x blocks per tile; the larger on a tie). 64 rows: one tile of four blocks; 68 rows (a
+// 17-row tree of four query heads): two tiles of three blocks rather than two of four.
+static int attention_row_blocks(int q_rows) {
+    const int small = (q_rows + 16 * AM_RB_SMALL - 1) / (16 * AM_RB_SMALL) * AM_RB_SMALL;
+    const int large = (q_rows + 16 * AM_RB_LARGE - 1) / (16 * AM_RB_LARGE) * AM_RB_LARGE;
+    return small < large ? AM_RB_SMALL : AM_RB_LARGE;
+}
 int attention_query_tiles(int q_rows) {
-    const int per = 16 * (q_rows > 16 * AM_RB_SMALL ? AM_RB_LARGE : AM_RB_SMALL);
+    const int per = 16 * attention_row_blocks(q_rows);
     return (q_rows + per - 1) / per;
 }
 
@@ -589,7 +597,7 @@ static int launch_attention_hd(cudaStream_t s, float * out, int ldo, const float
         // tensor-core partials; keys are taken as they are from an F16 pool and split into hi + lo otherwise
         const bool ksplit = pool.format != YUUKA_KV_F16;
         const int qtiles = attention_query_tiles(G * rows.nodes);
-        const int rb = G * rows.nodes > 16 * AM_RB_SMALL ? AM_RB_LARGE : AM_RB_SMALL;
+        const int rb = attention_row_blocks(G * rows.nodes);
         const size_t smem = sizeof(__half) * (size_t)(HD + 8) * (2 * 16 * rb + (ksplit ? 3 : 2) * AM_KT) +
                             sizeof(float) * 4 * rb * 512;
         auto kern = rb == AM_RB_LARGE ? (ksplit ? attention_mma_kernel<HD, true, AM_RB_LARGE> : attention_mma_kernel<HD, false, AM_RB_LARGE>)

@@ -915,6 +915,9 @@ void run_step(yuuka_session * s, int seq0, int batch, int nodes, uint32_t mode, 
             // about one CTA per SM at capacity (measured at a 1500-token context: 3.11 ms per step, against 3.16 with
             // two or four per SM: fewer partials for the merge kernel outweigh the shorter key ranges)
             int splits = (m->dev->sm_count + base - 1) / base;
+            // many sequences of different lengths: key ranges of at most 512 keys, so that the CTAs of a long context
+            // spread over the machine instead of one of them walking it alone (ranges beyond a sequence's end exit at once)
+            if (base >= m->dev->sm_count && splits < (max_total + 511) / 512) splits = (max_total + 511) / 512;
             int max_splits = (max_total + 31) / 32;
             if (splits > max_splits) splits = max_splits;
             if (splits < 1) splits = 1;
@@ -1443,8 +1446,10 @@ yuuka_status yuuka_session_create(yuuka_model * model, const yuuka_session_confi
                 // rows x splits of the flash-decoding partials, for the verify shape and for a prompt chunk
                 auto need = [&](int bx, int nx) {
                     const int G = c.heads / c.kv_heads, qt = (G * nx + 39) / 40;
-                    return (size_t)bx * nx * c.heads * (size_t)(4 * model->dev->sm_count / (c.kv_heads * qt * bx) + 2) *
-                           (size_t)(c.head_dim + 2);
+                    size_t splits = (size_t)(4 * model->dev->sm_count / (c.kv_heads * qt * bx) + 2);
+                    const size_t by_length = (size_t)(sc.capacity + 511) / 512 + 1;  // batched steps split the keys by length
+                    if (splits < by_length) splits = by_length;
+                    return (size_t)bx * nx * c.heads * splits * (size_t)(c.head_dim + 2);
                 };
                 const size_t a = need(B, N), b = need(1, s->chain_rows);
                 s->attn_partial_floats = a > b ? a : b;
