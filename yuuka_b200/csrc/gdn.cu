@@ -169,6 +169,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     float * dec = o_s + N * GDN_COLS;     // [N]
     float * bet = dec + N;                // [N]
     int * par = reinterpret_cast<int *>(bet + N);  // [N]
+    float * root_s = reinterpret_cast<float *>(par + N);  // TREE: [S / 4][threads] the state after row 0
     __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
     __shared__ int order_s[TREE ? GDN_MAX_NODES : 1];
@@ -229,11 +230,19 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         const int node = TREE ? order_s[step] : step;
         const int pnode = par[node];
         if (pnode != cur) {
-            // a sibling branch: rebuild the parent's state from the stored one by replaying the log of its path
-#pragma unroll
-            for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
+            // a sibling branch: rebuild the parent's state by replaying the log of its path, from the state after row 0
+            // (every row of a step descends from row 0, the pending token; a tree keeps that state in shared memory)
+            // or, failing that, from the stored one
             int path[GDN_MAX_NODES], len = 0;
-            for (int c = pnode; c >= 0; c = par[c]) path[len++] = c;
+            if (TREE && pnode >= 0) {
+#pragma unroll
+                for (int i = 0; i < RPL; i++) st[i] = root_s[i * (GDN_WARPS * 32) + threadIdx.x];
+                for (int c = pnode; c > 0; c = par[c]) path[len++] = c;
+            } else {
+#pragma unroll
+                for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
+                for (int c = pnode; c >= 0; c = par[c]) path[len++] = c;
+            }
             for (int j = len - 1; j >= 0; j--) {
                 const int c = path[j];
                 const float dc = dec[c], dv = dd[c * GDN_COLS + cl];
@@ -272,6 +281,10 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
             o_s[node * GDN_COLS + cl] = o;
             dd[node * GDN_COLS + cl] = d;
             a.dlog[(int64_t)(seq * N + node) * inner + h * S + col] = d;
+        }
+        if (TREE && node == 0) {
+#pragma unroll
+            for (int i = 0; i < RPL; i++) root_s[i * (GDN_WARPS * 32) + threadIdx.x] = st[i];
         }
         __syncwarp();  // dd of this row is read by the other row quarters when a later branch replays it
         cur = node;
@@ -339,7 +352,7 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
-    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N);
+    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N + (rows.chains ? 0 : (size_t)(a.S / 4) * GDN_WARPS * 32));
     auto launch = [&](auto kern) {
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         launch_k_cluster(kern, grid, GDN_WARPS * 32, smem, s, grid.x, p);
