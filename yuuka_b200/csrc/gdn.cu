@@ -35,6 +35,26 @@ __device__ __forceinline__ float state_update(float s, float decay, float k, flo
     return fmaf(k, d, s * decay);
 }
 
+// Two fp32 lanes per instruction (fma.rn.f32x2 / mul.rn.f32x2): the same IEEE results as the scalar forms, half the
+// instructions. The recurrence keeps its state, keys and queries as such pairs.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<const unsigned long long *>(&a)), "l"(*reinterpret_cast<const unsigned long long *>(&b)),
+          "l"(*reinterpret_cast<const unsigned long long *>(&c)));
+    return *reinterpret_cast<const float2 *>(&d);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<const unsigned long long *>(&a)), "l"(*reinterpret_cast<const unsigned long long *>(&b)));
+    return *reinterpret_cast<const float2 *>(&d);
+}
+// state_update on a pair: S <- S * decay + k * d
+__device__ __forceinline__ float2 state_update2(float2 s, float2 decay, float2 k, float2 d) { return fma2(k, d, mul2(s, decay)); }
+
 struct ScanParams {
     GdnArgs a;
     RowMeta rows;
@@ -169,16 +189,17 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     float * dec = o_s + N * GDN_COLS;     // [N]
     float * bet = dec + N;                // [N]
     int * par = reinterpret_cast<int *>(bet + N);  // [N]
-    float * root_s = reinterpret_cast<float *>(par + N);  // TREE: [S / 4][threads] the state after row 0
+    // TREE: [S / 8][threads] pairs, the state after row 0 (8-byte aligned: the arrays before it hold 2 N S + 99 N words)
+    float * root_s = reinterpret_cast<float *>(par + N + (N & 1));
     __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
     __shared__ int order_s[TREE ? GDN_MAX_NODES : 1];
 
     // stored state: the longest fetch (HBM), issued first
     const float * s0 = a.state + ((int64_t)(seq_of(p.rows, seq) * a.rank + h) * S + rq * RPL) * S + col;
-    float st[RPL];
+    float2 st[RPL / 2];  // state rows (2 i, 2 i + 1) of this lane's quarter, one column
 #pragma unroll
-    for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
+    for (int i = 0; i < RPL / 2; i++) st[i] = make_float2(s0[(int64_t)(2 * i) * S], s0[(int64_t)(2 * i + 1) * S]);
 
     // the front-end kernel has left normalised q and k, the conv output of v, beta and decay in global memory
     // (16-byte loads, eight in flight per thread: with 64 rows of a prompt sub-chunk a scalar loop spent most
@@ -236,45 +257,54 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
             int path[GDN_MAX_NODES], len = 0;
             if (TREE && pnode >= 0) {
 #pragma unroll
-                for (int i = 0; i < RPL; i++) st[i] = root_s[i * (GDN_WARPS * 32) + threadIdx.x];
+                for (int i = 0; i < RPL / 2; i++) st[i] = reinterpret_cast<const float2 *>(root_s)[i * (GDN_WARPS * 32) + threadIdx.x];
                 for (int c = pnode; c > 0; c = par[c]) path[len++] = c;
             } else {
 #pragma unroll
-                for (int i = 0; i < RPL; i++) st[i] = s0[(int64_t)i * S];
+                for (int i = 0; i < RPL / 2; i++) st[i] = make_float2(s0[(int64_t)(2 * i) * S], s0[(int64_t)(2 * i + 1) * S]);
                 for (int c = pnode; c >= 0; c = par[c]) path[len++] = c;
             }
             for (int j = len - 1; j >= 0; j--) {
                 const int c = path[j];
                 const float dc = dec[c], dv = dd[c * GDN_COLS + cl];
+                const float2 dc2 = make_float2(dc, dc), dv2 = make_float2(dv, dv);
 #pragma unroll
-                for (int i = 0; i < RPL; i++) st[i] = state_update(st[i], dc, kn[c * S + rq * RPL + i], dv);
+                for (int i = 0; i < RPL / 2; i++)
+                    st[i] = state_update2(st[i], dc2, *reinterpret_cast<const float2 *>(kn + c * S + rq * RPL + 2 * i), dv2);
             }
         }
         // this lane's S/4 key and query values, fetched as float4 (a quarter of the shared-memory loads)
-        float kx[RPL], qx[RPL];
+        float2 kx[RPL / 2], qx[RPL / 2];
 #pragma unroll
         for (int i = 0; i < RPL; i += 4) {
             const float4 k4 = *reinterpret_cast<const float4 *>(kn + node * S + rq * RPL + i);
             const float4 q4 = *reinterpret_cast<const float4 *>(qn + node * S + rq * RPL + i);
-            kx[i] = k4.x; kx[i + 1] = k4.y; kx[i + 2] = k4.z; kx[i + 3] = k4.w;
-            qx[i] = q4.x; qx[i + 1] = q4.y; qx[i + 2] = q4.z; qx[i + 3] = q4.w;
+            kx[i / 2] = make_float2(k4.x, k4.y); kx[i / 2 + 1] = make_float2(k4.z, k4.w);
+            qx[i / 2] = make_float2(q4.x, q4.y); qx[i / 2 + 1] = make_float2(q4.z, q4.w);
         }
         const float dc = dec[node];
-        // sk = (decay * S)^T k over this lane's rows, then over the four row quarters
-        float sk4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float2 dc2 = make_float2(dc, dc);
+        // sk = (decay * S)^T k over this lane's rows (four partial sums: rows i mod 4), then over the four row quarters
+        float2 sd[RPL / 2], sk01 = make_float2(0.0f, 0.0f), sk23 = sk01;
 #pragma unroll
-        for (int i = 0; i < RPL; i++) sk4[i & 3] = fmaf(st[i] * dc, kx[i], sk4[i & 3]);
-        float sk = (sk4[0] + sk4[1]) + (sk4[2] + sk4[3]);
+        for (int i = 0; i < RPL / 2; i++) {
+            sd[i] = mul2(st[i], dc2);
+            if (i & 1) sk23 = fma2(sd[i], kx[i], sk23);
+            else sk01 = fma2(sd[i], kx[i], sk01);
+        }
+        float sk = (sk01.x + sk01.y) + (sk23.x + sk23.y);
         sk += __shfl_xor_sync(0xffffffffu, sk, 8);
         sk += __shfl_xor_sync(0xffffffffu, sk, 16);
         const float d = (vv[node * GDN_COLS + cl] - sk) * bet[node];
-        float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float2 d2 = make_float2(d, d);
+        float2 o01 = make_float2(0.0f, 0.0f), o23 = o01;
 #pragma unroll
-        for (int i = 0; i < RPL; i++) {
-            st[i] = state_update(st[i], dc, kx[i], d);
-            o4[i & 3] = fmaf(st[i], qx[i], o4[i & 3]);
+        for (int i = 0; i < RPL / 2; i++) {
+            st[i] = fma2(kx[i], d2, sd[i]);  // state_update with the product S * decay already at hand
+            if (i & 1) o23 = fma2(st[i], qx[i], o23);
+            else o01 = fma2(st[i], qx[i], o01);
         }
-        float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+        float o = (o01.x + o01.y) + (o23.x + o23.y);
         o += __shfl_xor_sync(0xffffffffu, o, 8);
         o += __shfl_xor_sync(0xffffffffu, o, 16);
         if (rq == 0) {
@@ -284,7 +314,7 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
         }
         if (TREE && node == 0) {
 #pragma unroll
-            for (int i = 0; i < RPL; i++) root_s[i * (GDN_WARPS * 32) + threadIdx.x] = st[i];
+            for (int i = 0; i < RPL / 2; i++) reinterpret_cast<float2 *>(root_s)[i * (GDN_WARPS * 32) + threadIdx.x] = st[i];
         }
         __syncwarp();  // dd of this row is read by the other row quarters when a later branch replays it
         cur = node;
@@ -352,7 +382,7 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
-    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N + (rows.chains ? 0 : (size_t)(a.S / 4) * GDN_WARPS * 32));
+    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N + (rows.chains ? 0 : (size_t)(a.S / 4) * GDN_WARPS * 32 + 1));
     auto launch = [&](auto kern) {
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         launch_k_cluster(kern, grid, GDN_WARPS * 32, smem, s, grid.x, p);
