@@ -3,19 +3,18 @@
 // Replaces, for the verify step, kernels/hip/gemm/lm_head.hip,
 // gemv/gemv_quant.hip:317 and the small-row use of gemm/wmma_gemm.hip.
 //
-// mma route. A warp owns a 16-row tile and a range of superblocks. Per
-// superblock it issues coalesced 16-byte-per-lane loads of the next record
-// (register double buffer), decodes the current record's block headers into a
-// per-warp scale table, and turns packed weights into fp16 directly in
-// mma.sync.m16n8k16 A-fragment registers: one LOP3 places a nibble in the
-// mantissa of 1024.0 and one fma.f16x2 with (s, -1024 s) yields s*q. The
-// "- min" of Q4_K/Q5_K (and the -32 / -128 offsets of Q6_K / Q8_0) is not
-// applied per weight: it is one more MMA per superblock against per-sub-block
-// sums of the activations. Activations are staged once per CTA as fp16 in the
-// k-order the fragments use. Warps of a CTA that share a row tile split K and
-// are summed through shared memory in a fixed order; a split of K across CTAs
-// (long rows) goes through a scratch buffer and is finished by the last CTA to
-// arrive, also in a fixed order. Nothing here waits on another CTA.
+// mma route (register-fed, exact). A warp owns a 16-row tile and a range of superblocks. Per superblock it
+// issues coalesced 16-byte-per-lane loads of the next record (register double buffer), decodes the current
+// record's block headers into a per-warp table, and builds mma.sync.m16n8k16 A fragments that hold exactly
+// representable integers: one LOP3 places a nibble in the mantissa of 1024.0 and one fma.f16x2 with
+// (sc, -1024 sc) yields sc * q for Q4_K / Q5_K (6-bit scale times quant, at most 1953); Q6_K uses q - 32,
+// Q8_0 uses q. What is not an integer is applied in fp32 to the fp32 products: the superblock's d and -dmin
+// once per 256 columns (the "- m" term is one more MMA per 128 columns of the 6-bit mins against
+// per-16-column sums of the activations), d * sc per 16-column group of Q6_K, d per 32-column block of Q8_0.
+// Activations are staged once per CTA as two fp16 halves (hi + lo = 22 bits of x) that occupy neighbouring
+// product columns and are added after the record loop. Warps of a CTA that share a row tile split K and are
+// summed through shared memory in a fixed order; a split of K across CTAs (long rows) goes through a scratch
+// buffer and is finished by the last CTA to arrive, also in a fixed order. Nothing here waits on another CTA.
 //
 // fp32 route (on request, for tight-tolerance checks): same loads, the reference's
 // own fp32 decode (tensor/quant.go:105-125,261-285), CUDA-core FMAs.
