@@ -2,18 +2,18 @@
 // accumulator in tensor memory. Included by gemm_tiled.cu (it uses that file's
 // record codecs and header decoders).
 //
-// From about 48 rows on, re-decoding the packed weights for every 32-row pass of
-// the register-fed MMA kernel costs more than the arithmetic. Here a CTA owns
-// 128 weight rows and up to 256 activation rows: eight warps decode one 16-row
-// tile each into fp16 (s * q - min), 64 columns at a time, and store it into a
-// shared-memory stage in the K-major core-matrix layout (8 rows x 16 bytes,
-// no swizzle); the matching 64 columns of the prepared activations arrive in the
-// same stage by cp.async. One thread then issues four tcgen05.mma (M = 128,
-// N = rows padded to 16, K = 16 each) that accumulate D[weight row][activation
-// row] in tensor memory, and tcgen05.commit releases the stage through an
-// mbarrier when they have read it. Three stages let decoding run ahead of the
-// tensor pipe. The epilogue reads the accumulator with tcgen05.ld (lane = weight
-// row, column = activation row) and writes out[row][n], 128 bytes per warp store.
+// From 48 rows on (33 on request), re-decoding the packed weights for every 16-row pass of the
+// register-fed MMA kernel costs more than the arithmetic. Here a CTA owns 128 weight rows and up to
+// 256 activation rows (512 in the warp-specialised kernel, on two accumulators): eight warps decode one
+// 16-row tile each into fp16 (s * q - min, rounded: this route does not have the register-fed route's
+// exactness), 64 columns at a time, and store it into a shared-memory stage in the K-major core-matrix
+// layout (8 rows x 16 bytes, no swizzle); the matching 64 columns of the prepared activations (their fp16
+// hi halves) arrive in the same stage by a tensor-map copy (cp.async where the encoder is not available).
+// One thread then issues four tcgen05.mma (M = 128, N = rows padded to 16, K = 16 each) that accumulate
+// D[weight row][activation row] in tensor memory, and tcgen05.commit releases the stage through an
+// mbarrier when they have read it. The ring of stages lets decoding run ahead of the tensor pipe. The
+// epilogue reads the accumulator with tcgen05.ld (lane = weight row, column = activation row) and writes
+// out[row][n], 128 bytes per warp store.
 //
 // Every mbarrier wait is bounded; on expiry the device error word is set, the
 // kernel carries on (results are then garbage), frees its tensor memory and
