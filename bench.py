@@ -336,6 +336,7 @@ def run_c2(args, rank: int, local_rank: int, world: int) -> None:
         launches = sess.last_launch_count
     barrier()
     t_e2e = time.perf_counter() - t_e2e
+    profiler_range(args, False)
     clocks = sampler.stop()
 
     # per-op attribution on three more steps (not part of the timed region)
