@@ -181,15 +181,19 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     const int col = cb * GDN_COLS + cl;
 
     extern __shared__ __align__(16) float sm[];
-    float * qn = sm;                      // [N][S]
-    float * kn = qn + N * S;              // [N][S]
-    float * vv = kn + N * S;              // [N][GDN_COLS]
+    // q and k rows are stored quarter by quarter with four words of padding after each (QP words per quarter): the
+    // four row quarters of a warp read their 16-byte pieces from distinct banks (dense rows put all four on the
+    // same ones: more bank conflicts than loads in the profile of the batched step)
+    constexpr int QP = RPL + 4, SP4 = 4 * QP;
+    float * qn = sm;                      // [N][4][QP]
+    float * kn = qn + N * SP4;            // [N][4][QP]
+    float * vv = kn + N * SP4;            // [N][GDN_COLS]
     float * dd = vv + N * GDN_COLS;       // [N][GDN_COLS]
     float * o_s = dd + N * GDN_COLS;      // [N][GDN_COLS] outputs of this column block
     float * dec = o_s + N * GDN_COLS;     // [N]
     float * bet = dec + N;                // [N]
     int * par = reinterpret_cast<int *>(bet + N);  // [N]
-    // TREE: [S / 8][threads] pairs, the state after row 0 (8-byte aligned: the arrays before it hold 2 N S + 99 N words)
+    // TREE: [S / 8][threads] pairs, the state after row 0 (8-byte aligned: the arrays before it hold 2 N (S + 16) + 99 N words)
     float * root_s = reinterpret_cast<float *>(par + N + (N & 1));
     __shared__ double ssq[GDN_MAX_NODES];
     __shared__ float scale_s[GDN_MAX_NODES];
@@ -209,8 +213,9 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
     for (int i = threadIdx.x; i < N * SQ; i += blockDim.x) {
         const int node = i / SQ, e4 = i - node * SQ;
         const int64_t at = (int64_t)(seq * N + node) * key_dim + kh * S + e4 * 4;
-        reinterpret_cast<float4 *>(qn)[i] = *reinterpret_cast<const float4 *>(a.qn + at);
-        reinterpret_cast<float4 *>(kn)[i] = *reinterpret_cast<const float4 *>(a.khat + at);
+        const int spot = node * SP4 + (e4 / (RPL / 4)) * QP + (e4 % (RPL / 4)) * 4;
+        *reinterpret_cast<float4 *>(qn + spot) = *reinterpret_cast<const float4 *>(a.qn + at);
+        *reinterpret_cast<float4 *>(kn + spot) = *reinterpret_cast<const float4 *>(a.khat + at);
     }
 #pragma unroll 4
     for (int i = threadIdx.x; i < N * (GDN_COLS / 4); i += blockDim.x) {
@@ -270,15 +275,15 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_scan_kernel(const ScanPara
                 const float2 dc2 = make_float2(dc, dc), dv2 = make_float2(dv, dv);
 #pragma unroll
                 for (int i = 0; i < RPL / 2; i++)
-                    st[i] = state_update2(st[i], dc2, *reinterpret_cast<const float2 *>(kn + c * S + rq * RPL + 2 * i), dv2);
+                    st[i] = state_update2(st[i], dc2, *reinterpret_cast<const float2 *>(kn + c * SP4 + rq * QP + 2 * i), dv2);
             }
         }
         // this lane's S/4 key and query values, fetched as float4 (a quarter of the shared-memory loads)
         float2 kx[RPL / 2], qx[RPL / 2];
 #pragma unroll
         for (int i = 0; i < RPL; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4 *>(kn + node * S + rq * RPL + i);
-            const float4 q4 = *reinterpret_cast<const float4 *>(qn + node * S + rq * RPL + i);
+            const float4 k4 = *reinterpret_cast<const float4 *>(kn + node * SP4 + rq * QP + i);
+            const float4 q4 = *reinterpret_cast<const float4 *>(qn + node * SP4 + rq * QP + i);
             kx[i / 2] = make_float2(k4.x, k4.y); kx[i / 2 + 1] = make_float2(k4.z, k4.w);
             qx[i / 2] = make_float2(q4.x, q4.y); qx[i / 2 + 1] = make_float2(q4.z, q4.w);
         }
@@ -382,7 +387,7 @@ int launch_gdn_scan(cudaStream_t s, const GdnArgs & a, const RowMeta & rows) {
     dim3 fgrid(2 * a.groups + a.rank, N, rows.batch);
     launch_k(gdn_front_kernel, fgrid, a.S, 0, s, p);
     YK_CUDA(cudaGetLastError());
-    const size_t smem = sizeof(float) * ((size_t)2 * N * a.S + 3 * N * GDN_COLS + 3 * N + (rows.chains ? 0 : (size_t)(a.S / 4) * GDN_WARPS * 32 + 1));
+    const size_t smem = sizeof(float) * ((size_t)2 * N * (a.S + 16) + 3 * N * GDN_COLS + 3 * N + (rows.chains ? 0 : (size_t)(a.S / 4) * GDN_WARPS * 32 + 1));
     auto launch = [&](auto kern) {
         YK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         launch_k_cluster(kern, grid, GDN_WARPS * 32, smem, s, grid.x, p);
