@@ -415,30 +415,43 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
         }
         // mask, online softmax; s[nt][0,1] -> row g, keys 8 nt + 2 t + {0,1}; s[nt][2,3] -> row g + 8
         uint32_t pa[2][4];  // probabilities as A fragments of the two 16-key steps
+        // a tile that lies entirely in the committed context is visible to every row: no mask, no range test
+        const bool plain_tile = k0 + AM_KT <= min(pos0, k_end);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             float sv[4][2];
             float mx = -INFINITY;
+            if (plain_tile) {
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++)
+                for (int nt = 0; nt < 4; nt++)
 #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int pos = k0 + 8 * nt + 2 * t + e;
-                    const bool vis = pos < k_end && row_ok[h] && (pos < pos0 || ((mask[h] >> (pos - pos0)) & 1ull));
-                    sv[nt][e] = vis ? s[nt][2 * h + e] * scale : -INFINITY;
-                    mx = fmaxf(mx, sv[nt][e]);
-                }
+                    for (int e = 0; e < 2; e++) {
+                        sv[nt][e] = row_ok[h] ? s[nt][2 * h + e] * scale : -INFINITY;
+                        mx = fmaxf(mx, sv[nt][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int pos = k0 + 8 * nt + 2 * t + e;
+                        const bool vis = pos < k_end && row_ok[h] && (pos < pos0 || ((mask[h] >> (pos - pos0)) & 1ull));
+                        sv[nt][e] = vis ? s[nt][2 * h + e] * scale : -INFINITY;
+                        mx = fmaxf(mx, sv[nt][e]);
+                    }
+            }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m[h], mx);
             float corr = 1.0f, sum = 0.0f;
             float pr[4][2];
-            if (m_new != -INFINITY) corr = expf(m[h] - m_new);
+            if (m_new != -INFINITY) corr = __expf(m[h] - m_new);
 #pragma unroll
             for (int nt = 0; nt < 4; nt++)
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    const float pv = (m_new != -INFINITY && sv[nt][e] != -INFINITY) ? expf(sv[nt][e] - m_new) : 0.0f;
+                    // (ex2.approx: the value is rounded to fp16 on the next line, 2^-11 against the approximation's 2^-22)
+                    const float pv = (m_new != -INFINITY && sv[nt][e] != -INFINITY) ? __expf(sv[nt][e] - m_new) : 0.0f;
                     pr[nt][e] = __half2float(__float2half_rn(pv));  // the value the tensor core will see
                     sum += pr[nt][e];
                 }
