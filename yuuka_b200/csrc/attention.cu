@@ -302,6 +302,8 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
     constexpr int PIECES = AM_KT * (HD / 8);
     constexpr int PER = (PIECES + AM_WARPS * 32 - 1) / (AM_WARPS * 32);
     uint4 nk[PER], nv[PER];
+    // (block sizes are powers of two in practice: a shift and a mask instead of two integer divisions per piece)
+    const int bsz = p.pool.block_size, bshift = (bsz & (bsz - 1)) == 0 ? __ffs(bsz) - 1 : -1;
     auto fetch = [&](int k0) {
 #pragma unroll
         for (int u = 0; u < PER; u++) {
@@ -311,8 +313,9 @@ __global__ void __launch_bounds__(RB * 128) attention_mma_kernel(const AttnParam
             nk[u] = make_uint4(0, 0, 0, 0);
             nv[u] = nk[u];
             if (i < PIECES && pos < k_end) {
-                const int block = p.pool.tables[(int64_t)sq * p.pool.table_stride + pos / p.pool.block_size];
-                const int64_t off = ((int64_t)block * p.pool.block_size + pos % p.pool.block_size) * p.pool.row_bytes;
+                const int bi = bshift >= 0 ? pos >> bshift : pos / bsz, within = bshift >= 0 ? pos & (bsz - 1) : pos - bi * bsz;
+                const int block = p.pool.tables[(int64_t)sq * p.pool.table_stride + bi];
+                const int64_t off = ((int64_t)block * bsz + within) * p.pool.row_bytes;
                 nk[u] = *reinterpret_cast<const uint4 *>(p.pool.k + off + (size_t)(kvh * HD + c8 * 8) * 2);
                 nv[u] = *reinterpret_cast<const uint4 *>(p.pool.v + off + (size_t)(kvh * HD + c8 * 8) * 2);
             }
