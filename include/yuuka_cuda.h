@@ -313,7 +313,9 @@ YUUKA_API yuuka_status yuuka_session_set_block_table(yuuka_session * s, int32_t 
  * synchronously. The prefix cache uses it to give a request a private copy of a shared, partly filled
  * block before the request appends to it. */
 YUUKA_API yuuka_status yuuka_session_copy_block(yuuka_session * s, int32_t dst_block, int32_t src_block);
-/* State.Reset / State.SetPos (model/qwen35/state.go:174-208) */
+/* State.Reset / State.SetPos (model/qwen35/state.go:174-208). Reset, set_position and restore are refused with
+ * YUUKA_ERR_INVALID_ARGUMENT between yuuka_verify_launch and yuuka_verify_fetch: the fetch adds what the step
+ * accepted to the positions these calls would replace. */
 YUUKA_API yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq);
 YUUKA_API yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t position);
 YUUKA_API yuuka_status yuuka_session_position(yuuka_session * s, int32_t seq, int32_t * position);

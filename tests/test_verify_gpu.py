@@ -561,8 +561,51 @@ def test_a_step_cannot_be_launched_twice_before_it_is_fetched(tiny):
     sess.launch()
     with pytest.raises(cuda.YuukaError):
         sess.launch()                                    # would run and commit the same step again
+    snap = sess.snapshot()                               # reading the state behind the step is fine
+    for call in (lambda: sess.reset(0), lambda: sess.set_position(0, 2), lambda: sess.restore(snap)):
+        with pytest.raises(cuda.YuukaError):
+            call()                                       # the fetch would add to positions these calls replace
     res = sess.fetch()
     assert sess.position() == 3 + int(res.accepted[0]) + 1
+    sess.close()
+
+
+def test_a_refused_batch_does_not_leave_the_earlier_staged_step_launchable(tiny):
+    cfg, gm, om = tiny
+    sess = cuda.Session(gm, max_batch=1, max_nodes=4, capacity=32)
+    sess.forward([1, 2, 3], want_logits=False)
+    sess.stage([[5, 6, 7]])
+    with pytest.raises(cuda.YuukaError):
+        sess.stage([[5, 6, cfg["vocab"]]])               # refused after two of its rows replaced the staged ones
+    with pytest.raises(cuda.YuukaError):
+        sess.launch()                                    # nothing is staged any more
+    res = sess.verify([[5, 6, 7]])
+    assert sess.position() == 3 + int(res.accepted[0]) + 1
+    sess.close()
+
+
+def test_more_step_shapes_than_the_session_keeps_captured(tiny):
+    """A session replays a captured launch sequence per step shape and keeps a bounded number of them (48,
+    least recently used dropped first). 60 shapes (4 batch sizes x 15 row counts) run through one session; the
+    first shape, whose capture has been dropped by then, must give the same bits when it runs again."""
+    cfg, gm, om = tiny
+    V = cfg["vocab"]
+    sess = cuda.Session(gm, max_batch=4, max_nodes=15, capacity=64, kv_format=cuda.KV_F32)
+    for b in range(4):
+        sess.forward(synth.uniform_i32(6 + b, 0, V, 950 + b).tolist(), seq=b, want_logits=False)
+    rows = synth.uniform_i32(4 * 15, 0, V, 960).reshape(4, 15)
+
+    def run(batch, nodes):
+        return sess.verify([rows[b, :nodes].tolist() for b in range(batch)], mode=cuda.ACCEPT_NONE,
+                           want_logits=True).logits.copy()
+
+    first = run(1, 1)
+    mid = run(3, 7)
+    for batch in range(1, 5):
+        for nodes in range(1, 16):
+            run(batch, nodes)
+    assert np.array_equal(run(1, 1).view(np.uint32), first.view(np.uint32))
+    assert np.array_equal(run(3, 7).view(np.uint32), mid.view(np.uint32))
     sess.close()
 
 

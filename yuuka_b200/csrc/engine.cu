@@ -3,6 +3,7 @@
 // prefillAllLogits) lives here behind the C ABI, so one call runs a whole
 // verify step: k+1 (or tree) rows through every layer, on-device acceptance,
 // KV / recurrent-state commit.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -593,7 +594,10 @@ struct yuuka_session {
     unsigned long long * reject_residual = nullptr;  // [max_batch][vocab], allocated by the first rejection step
     bool staged = false, launched = false;
     uint32_t launches = 0;
-    // captured steps, keyed by (seq0, batch, nodes, mode)
+    // captured steps, keyed by (seq0, batch, nodes, chains, mode), least recently used first; at most
+    // MAX_STEP_GRAPHS are kept (a scheduler that varies batch and row counts freely would otherwise
+    // accumulate one instantiated graph of a few hundred nodes per shape for the life of the session)
+    static constexpr size_t MAX_STEP_GRAPHS = 48;
     struct StepGraph {
         int seq0, batch, nodes, chains;
         uint32_t mode;
@@ -1237,9 +1241,14 @@ void enqueue_staged_step(yuuka_session * s) {
         return;
     }
     yuuka_session::StepGraph * gr = nullptr;
-    for (auto & g : s->graphs)
-        if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.chains == s->st_chains && g.mode == s->st_mode)
-            gr = &g;
+    for (size_t i = 0; i < s->graphs.size(); i++) {
+        const auto & g = s->graphs[i];
+        if (g.seq0 == s->st_seq0 && g.batch == s->st_batch && g.nodes == s->st_nodes && g.chains == s->st_chains && g.mode == s->st_mode) {
+            std::rotate(s->graphs.begin() + (std::ptrdiff_t)i, s->graphs.begin() + (std::ptrdiff_t)i + 1, s->graphs.end());
+            gr = &s->graphs.back();
+            break;
+        }
+    }
     if (!gr) {
         // first step of this shape: capture the kernel sequence once, replay it afterwards
         s->launches = 0;
@@ -1257,6 +1266,12 @@ void enqueue_staged_step(yuuka_session * s) {
         cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
         cudaGraphDestroy(graph);
         YK_CUDA(err);
+        if (s->graphs.size() >= yuuka_session::MAX_STEP_GRAPHS) {
+            // no replay of it is in flight: a new shape is captured only behind a synchronization (the fetch of the
+            // step before it, or the prompt pass of a device-drafted generation)
+            cudaGraphExecDestroy(s->graphs.front().exec);
+            s->graphs.erase(s->graphs.begin());
+        }
         s->graphs.push_back({s->st_seq0, s->st_batch, s->st_nodes, s->st_chains, s->st_mode, exec, s->launches});
         gr = &s->graphs.back();
     }
@@ -1543,6 +1558,8 @@ yuuka_status yuuka_session_copy_block(yuuka_session * s, int32_t dst_block, int3
 yuuka_status yuuka_session_reset(yuuka_session * s, int32_t seq) {
     return guard([&] {
         check_seq(s, seq);
+        // (the fetch of a launched step adds what it accepted to the host's copy of the positions)
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "session_reset: a launched verify step has not been fetched");
         set_device(s->model->dev);
         cudaStream_t st = s->stream.s;
         for (int i : s->gdn_layers) {
@@ -1560,6 +1577,7 @@ yuuka_status yuuka_session_set_position(yuuka_session * s, int32_t seq, int32_t 
         check_seq(s, seq);
         YK_REQUIRE(position >= 0 && position <= s->cfg.capacity, YUUKA_ERR_INVALID_ARGUMENT,
                    "position %d exceeds capacity %d", position, s->cfg.capacity);
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "session_set_position: a launched verify step has not been fetched");
         set_device(s->model->dev);
         YK_CUDA(cudaStreamSynchronize(s->stream.s));
         YK_CUDA(cudaMemcpy(s->d_pos0 + seq, &position, sizeof(int32_t), cudaMemcpyHostToDevice));
@@ -1618,6 +1636,7 @@ yuuka_status yuuka_session_restore(yuuka_session * s, int32_t seq, const void * 
         YK_REQUIRE(src && bytes == yuuka_session_snapshot_bytes(s), YUUKA_ERR_INVALID_ARGUMENT,
                    "state snapshot is %llu bytes, want %llu", (unsigned long long)bytes,
                    (unsigned long long)yuuka_session_snapshot_bytes(s));
+        YK_REQUIRE(!s->launched, YUUKA_ERR_INVALID_ARGUMENT, "session_restore: a launched verify step has not been fetched");
         set_device(s->model->dev);
         YK_CUDA(cudaStreamSynchronize(s->stream.s));
         const uint8_t * o = (const uint8_t *)src;
@@ -1647,6 +1666,7 @@ yuuka_status yuuka_verify_stage(yuuka_session * s, const yuuka_verify_batch * b)
         set_device(s->model->dev);
         // staging again before a launch replaces the step; the earlier copy out of the page-locked mirror must have left it
         if (s->staged) YK_CUDA(cudaStreamSynchronize(s->stream.s));
+        s->staged = false;  // a batch refused half way through must not leave the earlier step launchable over its rows
         stage_rows(s, 0, b->batch, b->nodes, b->tokens, b->parent, 0, b->seq_ids);
         s->st_seqs.resize((size_t)b->batch);
         for (int i = 0; i < b->batch; i++) s->st_seqs[(size_t)i] = b->seq_ids ? b->seq_ids[i] : i;
