@@ -415,7 +415,7 @@ template <int NT> struct Mma<YUUKA_DTYPE_Q8_0, NT> {
 };
 
 // ---------------------------------------------------------------------------
-// Exact decode (register-fed route, 3..16 activation rows per launch). The fp16 operand of the tensor core
+// Exact decode (register-fed route, 1..16 activation rows per launch). The fp16 operand of the tensor core
 // holds an integer that fp16 represents exactly, and every floating-point factor of the format is applied
 // to the fp32 product afterwards, so the weights enter the sum with the value tensor/quant.go gives them:
 //   Q4_K / Q5_K  w = d * (sc * q) - dmin * m: the operand is sc * q (at most 63 * 31), summed over the whole
