@@ -137,17 +137,21 @@ def profiled_traffic_ratio() -> tuple[float | None, str]:
 # --------------------------------------------------------------------------- CPU arm
 
 def cpu_reference_steps(steps: int, warmup: int, layers: int, tensors: dict | None = None, prompt_len: int = 16,
-                        threads: int = 0) -> dict:
+                        threads: int = 0, budget_s: float | None = None) -> dict:
     """Real verify steps of the CPU path (oracle port of engine/speculative.go over model/qwen35: one forwardOne
     per row, row-parallel matvec) on all host cores: the 32-layer model, `warmup + steps` 9-row steps whose drafts
     are the path's own greedy continuation corrupted with p = 0.3. The bounded part is the prompt (16 tokens
-    instead of 512: a step of the CPU path reads the same weights whatever the context) and the number of steps."""
+    instead of 512: a step of the CPU path reads the same weights whatever the context) and the number of steps:
+    with budget_s the loop ends after the first timed step (of at least three) that finishes past that many seconds
+    of stepping, and the result says how many steps were timed."""
     from oracle import pyoracle as yo
     from yuuka_b200 import synth
 
     # all host cores, whatever OMP_NUM_THREADS says (torch.distributed.run sets it to 1)
     yo.lib().yo_set_threads(threads if threads > 0 else (os.cpu_count() or 1))
     cores = yo.lib().yo_get_threads()
+    if budget_s is not None:
+        steps = min(steps, 400)                   # (bounds the context the two states are created with)
     total = warmup + steps
     cap = prompt_len + (total + 2) * (K_DRAFT + 1) + 16
     cfg = synth.dense4b_config(layers=layers, context=max(cap, 64))
@@ -175,7 +179,10 @@ def cpu_reference_steps(steps: int, warmup: int, layers: int, tensors: dict | No
     need(1)
     idx = 1                                       # cont[0] is the pending token
     times, emitted_total, accepted_total = [], 0, 0
+    t_begin = time.perf_counter()
     for step in range(total):
+        if budget_s is not None and len(times) >= 3 and time.perf_counter() - t_begin > budget_s:
+            break
         need(idx + K_DRAFT)
         drafts = np.array([r[idx + i] if u[idx + i] < P_CORRUPT else cont[idx + i] for i in range(K_DRAFT)], np.int32)
         t0 = time.perf_counter()
@@ -202,9 +209,11 @@ def cpu_reference_steps(steps: int, warmup: int, layers: int, tensors: dict | No
 def run_reference_arm(args, rank: int) -> None:
     if rank != 0:
         return
-    base = cpu_reference_steps(args.steps, args.warmup, args.layers)
+    # every step is a real step of the CPU path (seconds each): the run is bounded in time, and `steps` is the
+    # number of steps that were timed (= the request when it fits)
+    base = cpu_reference_steps(args.steps, args.warmup, args.layers, budget_s=240.0)
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+            "steps": base["steps"], "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args), "accepted_per_step": base["accepted_per_step"],
             "emitted_per_step": base["emitted_per_step"], "cpu_baseline": base,
